@@ -1,0 +1,166 @@
+"""Framework-independent half of elastic training: the State object that can
+be committed / restored / synced, and the retry loop around the user's
+training function.
+
+Parity: horovod/common/elastic.py:26-175.
+"""
+import functools
+import queue
+
+from horovod_b200.common.exceptions import HorovodInternalError, HostsUpdatedInterrupt
+
+
+class HostUpdateResult:
+    no_update = 0
+    removed = 1
+    added = 2
+    mixed = 3
+
+
+class _NotificationManager:
+    """Fan-out of host-change messages from the elastic driver to the State
+    objects of this process. The worker-side notification service (started by
+    the launcher glue) calls handle_hosts_updated()."""
+
+    def __init__(self):
+        self._listeners = set()
+        self._service = None
+
+    def init(self):
+        if self._service is not None:
+            return
+        try:
+            from horovod_b200.runner.elastic.worker import start_notification_service
+            self._service = start_notification_service(self)
+        except Exception:
+            self._service = None
+
+    def register_listener(self, listener):
+        self._listeners.add(listener)
+
+    def remove_listener(self, listener):
+        self._listeners.discard(listener)
+
+    def handle_hosts_updated(self, timestamp, update_res):
+        for listener in list(self._listeners):
+            listener.on_hosts_updated(timestamp, update_res)
+
+
+notification_manager = _NotificationManager()
+
+
+class State:
+    """State that must survive a change of membership.
+
+    ``commit()`` saves a copy and checks for host changes; ``restore()`` goes
+    back to the last commit after a failure; ``sync()`` makes every rank equal
+    to rank 0 after a reset.
+    """
+
+    def __init__(self, bcast_object, get_rank):
+        self._bcast_object = bcast_object
+        self._rank = get_rank
+        self._host_messages = queue.Queue()
+        self._last_updated_timestamp = 0
+        self._reset_callbacks = []
+
+    def register_reset_callbacks(self, callbacks):
+        """Functions called after every reset, e.g. to rescale the learning
+        rate to the new world size."""
+        self._reset_callbacks.extend(callbacks)
+
+    def on_reset(self):
+        self._host_messages = queue.Queue()
+        self.reset()
+        for cb in self._reset_callbacks:
+            cb()
+
+    def on_hosts_updated(self, timestamp, update_res):
+        self._host_messages.put((timestamp, update_res))
+
+    def commit(self):
+        self.save()
+        self.check_host_updates()
+
+    def check_host_updates(self):
+        """Raises HostsUpdatedInterrupt on all ranks together if the driver
+        reported a change since the last check."""
+        last = prev = self._last_updated_timestamp
+        all_update = HostUpdateResult.no_update
+        while not self._host_messages.empty():
+            timestamp, update = self._host_messages.get()
+            if timestamp > last:
+                last = timestamp
+                all_update |= update
+        # Rank 0 decides so that everybody raises at the same commit.
+        prev, self._last_updated_timestamp, all_update = self._bcast_object(
+            (prev, last, all_update), name="hvd.elastic.host_updates")
+        if self._last_updated_timestamp > prev:
+            raise HostsUpdatedInterrupt(all_update == HostUpdateResult.removed)
+
+    def save(self):
+        raise NotImplementedError()
+
+    def restore(self):
+        raise NotImplementedError()
+
+    def sync(self):
+        raise NotImplementedError()
+
+    def reset(self):
+        pass
+
+
+class ObjectState(State):
+    """State made of plain picklable attributes given as keyword arguments."""
+
+    def __init__(self, bcast_object, get_rank, **kwargs):
+        self._saved_state = kwargs
+        self._set_attrs()
+        super().__init__(bcast_object=bcast_object, get_rank=get_rank)
+
+    def save(self):
+        new_state = {}
+        for attr in self._saved_state.keys():
+            new_state[attr] = getattr(self, attr)
+        self._saved_state = new_state
+
+    def restore(self):
+        self._set_attrs()
+
+    def sync(self):
+        if self._saved_state:
+            self._saved_state = self._bcast_object(self._saved_state,
+                                                   name="hvd.elastic.object_state")
+            self._set_attrs()
+
+    def _set_attrs(self):
+        for attr, value in self._saved_state.items():
+            setattr(self, attr, value)
+
+
+def run_fn(func, reset):
+    """Wraps ``func(state, ...)`` in the elastic retry loop."""
+
+    @functools.wraps(func)
+    def wrapper(state, *args, **kwargs):
+        notification_manager.init()
+        notification_manager.register_listener(state)
+        skip_sync = False
+        try:
+            while True:
+                if not skip_sync:
+                    state.sync()
+                try:
+                    return func(state, *args, **kwargs)
+                except HorovodInternalError:
+                    state.restore()
+                    skip_sync = False
+                except HostsUpdatedInterrupt as e:
+                    skip_sync = e.skip_sync
+                reset()
+                state.on_reset()
+        finally:
+            notification_manager.remove_listener(state)
+
+    return wrapper

@@ -1,0 +1,15 @@
+// Python access to device-side diagnostics and raw kernel entry points.
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "../ops/gpu_ops.h"
+
+namespace py = pybind11;
+
+namespace hvd {
+
+void BindGpuDiagnostics(py::module_& m) {
+  m.def("gpu_backend", &GpuBackendDescription);
+}
+
+}  // namespace hvd

@@ -1,0 +1,29 @@
+"""``import horovod_b200.torch as hvd`` — the PyTorch API.
+
+Parity: horovod/torch/__init__.py:34-54.
+"""
+from horovod_b200.common.exceptions import HorovodInternalError, HostsUpdatedInterrupt
+from horovod_b200.common.process_sets import (ProcessSet, add_process_set,
+                                              global_process_set, process_set_ids,
+                                              remove_process_set)
+from horovod_b200.torch import elastic
+from horovod_b200.torch.compression import Compression
+from horovod_b200.torch.functions import (allgather_object, broadcast_object,
+                                          broadcast_optimizer_state, broadcast_parameters)
+from horovod_b200.torch.mpi_ops import (Adasum, Average, Max, Min, Product, Sum, allgather,
+                                        allgather_async, allreduce, allreduce_,
+                                        allreduce_async, allreduce_async_, alltoall,
+                                        alltoall_async, broadcast, broadcast_,
+                                        broadcast_async, broadcast_async_, ccl_built,
+                                        cross_rank, cross_size, cuda_built, ddl_built,
+                                        gloo_built, gloo_enabled, gpu_backend,
+                                        grouped_allreduce, grouped_allreduce_,
+                                        grouped_allreduce_async, grouped_allreduce_async_,
+                                        init, is_homogeneous, is_initialized, join,
+                                        local_rank, local_size, mpi_built, mpi_enabled,
+                                        mpi_threads_supported, nccl_built, poll, rank,
+                                        reducescatter, reducescatter_async, rocm_built,
+                                        shutdown, size, sparse_allreduce_async,
+                                        start_timeline, stop_timeline, synchronize)
+from horovod_b200.torch.optimizer import DistributedOptimizer
+from horovod_b200.torch.sync_batch_norm import SyncBatchNorm

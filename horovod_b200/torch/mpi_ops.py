@@ -1,0 +1,481 @@
+"""Collective operations on torch tensors.
+
+Every op exists in an asynchronous form returning a handle (``*_async``),
+an in-place form (trailing underscore) and a blocking, autograd-aware form.
+All of them accept ``process_set=``. Tensors are identified across ranks by
+``name``; unnamed ops get ``<op>.noname.<handle>``, so unnamed ops must be
+issued in the same order on every rank.
+
+Parity: horovod/torch/mpi_ops.py:63-903. Extensions: reducescatter, bf16,
+Min/Max/Product, process_set on every op.
+"""
+import torch
+
+from horovod_b200 import _C
+from horovod_b200.common.basics import HorovodBasics
+from horovod_b200.common.exceptions import HorovodInternalError
+from horovod_b200.common.process_sets import _resolve, global_process_set
+from horovod_b200.common.util import (get_average_backwards_compatibility_fun,
+                                      num_rank_is_power_2)
+from horovod_b200.torch.compression import Compression
+
+_basics = HorovodBasics()
+
+init = _basics.init
+shutdown = _basics.shutdown
+is_initialized = _basics.is_initialized
+size = _basics.size
+local_size = _basics.local_size
+cross_size = _basics.cross_size
+rank = _basics.rank
+local_rank = _basics.local_rank
+cross_rank = _basics.cross_rank
+is_homogeneous = _basics.is_homogeneous
+start_timeline = _basics.start_timeline
+stop_timeline = _basics.stop_timeline
+mpi_threads_supported = _basics.mpi_threads_supported
+mpi_enabled = _basics.mpi_enabled
+mpi_built = _basics.mpi_built
+gloo_enabled = _basics.gloo_enabled
+gloo_built = _basics.gloo_built
+nccl_built = _basics.nccl_built
+ddl_built = _basics.ddl_built
+ccl_built = _basics.ccl_built
+cuda_built = _basics.cuda_built
+rocm_built = _basics.rocm_built
+gpu_backend = _basics.gpu_backend
+
+
+class _ReduceOps:
+    Average = 0
+    Sum = 1
+    Adasum = 2
+    Min = 3
+    Max = 4
+    Product = 5
+
+
+Average = _ReduceOps.Average
+Sum = _ReduceOps.Sum
+Adasum = _ReduceOps.Adasum
+Min = _ReduceOps.Min
+Max = _ReduceOps.Max
+Product = _ReduceOps.Product
+
+handle_average_backwards_compatibility = get_average_backwards_compatibility_fun(_ReduceOps)
+
+# handle -> (kind, extra) so that synchronize() knows how to shape the result.
+_handle_map = {}
+
+
+def _check_tensor(tensor):
+    if not isinstance(tensor, torch.Tensor):
+        raise ValueError("Horovod collectives need torch tensors, got %s" % type(tensor))
+    if tensor.is_sparse:
+        raise ValueError("Sparse tensors are not supported by this op; use "
+                         "sparse_allreduce_async or sparse_as_dense=True.")
+    if not tensor.is_contiguous():
+        raise ValueError("Horovod collectives need contiguous tensors; "
+                         "call .contiguous() first.")
+
+
+def _check_adasum(op, process_set):
+    if op != Adasum:
+        return
+    ps_size = process_set.size() if process_set is not None else size()
+    if not num_rank_is_power_2(ps_size):
+        raise NotImplementedError(
+            "Running Adasum needs a power-of-two number of ranks; this set has %d." % ps_size)
+
+
+def _scaled_op(op, prescale_factor, postscale_factor):
+    return int(op), float(prescale_factor), float(postscale_factor)
+
+
+def _allreduce_async(tensor, output, name, op, prescale_factor, postscale_factor, process_set):
+    _check_tensor(tensor)
+    _check_adasum(op, process_set)
+    if op == Average and not (tensor.is_floating_point() or tensor.is_complex()):
+        # Integer averaging: sum on the wire, floor-divide afterwards, as the
+        # framework's integer division would.
+        handle = _C.allreduce_async(tensor, output, name or "", Sum, float(prescale_factor),
+                                    float(postscale_factor), _resolve(process_set))
+        divisor = process_set.size() if process_set is not None else size()
+        _handle_map[handle] = ("allreduce_intavg", divisor)
+        return handle
+    handle = _C.allreduce_async(tensor, output, name or "", *_scaled_op(
+        op, prescale_factor, postscale_factor), _resolve(process_set))
+    _handle_map[handle] = ("allreduce", None)
+    return handle
+
+
+def allreduce_async(tensor, average=None, name=None, op=None, prescale_factor=1.0,
+                    postscale_factor=1.0, process_set=global_process_set):
+    """Starts an allreduce of ``tensor`` into a new tensor and returns a
+    handle for poll() / synchronize()."""
+    op = handle_average_backwards_compatibility(op, average)
+    output = tensor.new_empty(tensor.shape)
+    return _allreduce_async(tensor, output, name, op, prescale_factor, postscale_factor,
+                            process_set)
+
+
+class HorovodAllreduce(torch.autograd.Function):
+    """Allreduce whose gradient is the allreduce of the incoming gradient."""
+
+    @staticmethod
+    def forward(ctx, tensor, average, name, op, prescale_factor, postscale_factor, process_set):
+        ctx.average = average
+        ctx.op = op
+        ctx.prescale_factor = prescale_factor
+        ctx.postscale_factor = postscale_factor
+        ctx.process_set = process_set
+        handle = allreduce_async(tensor, average, name, op, prescale_factor,
+                                 postscale_factor, process_set)
+        return synchronize(handle)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return (allreduce(grad_output, average=ctx.average, op=ctx.op,
+                          prescale_factor=ctx.prescale_factor,
+                          postscale_factor=ctx.postscale_factor,
+                          process_set=ctx.process_set),
+                None, None, None, None, None, None)
+
+
+def allreduce(tensor, average=None, name=None, compression=Compression.none, op=None,
+              prescale_factor=1.0, postscale_factor=1.0, process_set=global_process_set):
+    """Reduces ``tensor`` over all ranks of the process set and returns the
+    result on every rank. Differentiable. ``op`` is Average (default), Sum,
+    Adasum, Min, Max or Product."""
+    tensor_compressed, ctx = compression.compress(tensor)
+    summed = HorovodAllreduce.apply(tensor_compressed, average, name, op,
+                                    prescale_factor, postscale_factor, process_set)
+    return compression.decompress(summed, ctx)
+
+
+def allreduce_async_(tensor, average=None, name=None, op=None, prescale_factor=1.0,
+                     postscale_factor=1.0, process_set=global_process_set):
+    """In-place asynchronous allreduce."""
+    op = handle_average_backwards_compatibility(op, average)
+    return _allreduce_async(tensor, tensor, name, op, prescale_factor, postscale_factor,
+                            process_set)
+
+
+def allreduce_(tensor, average=None, name=None, op=None, prescale_factor=1.0,
+               postscale_factor=1.0, process_set=global_process_set):
+    """In-place blocking allreduce."""
+    handle = allreduce_async_(tensor, average, name, op, prescale_factor,
+                              postscale_factor, process_set)
+    return synchronize(handle)
+
+
+def _grouped_allreduce_async(tensors, outputs, name, op, prescale_factor, postscale_factor,
+                             process_set):
+    for t in tensors:
+        _check_tensor(t)
+    _check_adasum(op, process_set)
+    int_avg = op == Average and any(not t.is_floating_point() for t in tensors)
+    wire_op = Sum if int_avg else op
+    handle = _C.grouped_allreduce_async(list(tensors), list(outputs), name or "",
+                                        int(wire_op), float(prescale_factor),
+                                        float(postscale_factor), _resolve(process_set))
+    if int_avg:
+        divisor = process_set.size() if process_set is not None else size()
+        _handle_map[handle] = ("grouped_intavg", divisor)
+    else:
+        _handle_map[handle] = ("grouped", None)
+    return handle
+
+
+def grouped_allreduce_async(tensors, average=None, name=None, op=None, prescale_factor=1.0,
+                            postscale_factor=1.0, process_set=global_process_set):
+    """Allreduce of a list of tensors negotiated and fused as one unit."""
+    op = handle_average_backwards_compatibility(op, average)
+    outputs = [t.new_empty(t.shape) for t in tensors]
+    return _grouped_allreduce_async(tensors, outputs, name, op, prescale_factor,
+                                    postscale_factor, process_set)
+
+
+class HorovodGroupedAllreduce(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, average, name, op, prescale_factor, postscale_factor, process_set,
+                *tensors):
+        ctx.average = average
+        ctx.op = op
+        ctx.prescale_factor = prescale_factor
+        ctx.postscale_factor = postscale_factor
+        ctx.process_set = process_set
+        handle = grouped_allreduce_async(list(tensors), average, name, op, prescale_factor,
+                                         postscale_factor, process_set)
+        return tuple(synchronize(handle))
+
+    @staticmethod
+    def backward(ctx, *grad_output):
+        grads = grouped_allreduce(list(grad_output), average=ctx.average, op=ctx.op,
+                                  prescale_factor=ctx.prescale_factor,
+                                  postscale_factor=ctx.postscale_factor,
+                                  process_set=ctx.process_set)
+        return (None, None, None, None, None, None, *grads)
+
+
+def grouped_allreduce(tensors, average=None, name=None, compression=Compression.none,
+                      op=None, prescale_factor=1.0, postscale_factor=1.0,
+                      process_set=global_process_set):
+    """Blocking, differentiable grouped allreduce. Returns a list."""
+    compressed, ctxs = zip(*[compression.compress(t) for t in tensors]) if tensors else ((), ())
+    summed = HorovodGroupedAllreduce.apply(average, name, op, prescale_factor,
+                                           postscale_factor, process_set, *compressed)
+    return [compression.decompress(t, c) for t, c in zip(summed, ctxs)]
+
+
+def grouped_allreduce_async_(tensors, average=None, name=None, op=None, prescale_factor=1.0,
+                             postscale_factor=1.0, process_set=global_process_set):
+    op = handle_average_backwards_compatibility(op, average)
+    return _grouped_allreduce_async(tensors, tensors, name, op, prescale_factor,
+                                    postscale_factor, process_set)
+
+
+def grouped_allreduce_(tensors, average=None, name=None, op=None, prescale_factor=1.0,
+                       postscale_factor=1.0, process_set=global_process_set):
+    handle = grouped_allreduce_async_(tensors, average, name, op, prescale_factor,
+                                      postscale_factor, process_set)
+    return synchronize(handle)
+
+
+def sparse_allreduce_async(tensor, name, op, process_set=global_process_set):
+    """Allreduce of a sparse COO tensor as two allgathers (indices, values).
+    Returns a function that waits and builds the result."""
+    t = tensor.coalesce() if not tensor.is_coalesced() else tensor
+    indices_handle = allgather_async(t._indices().transpose(0, 1).contiguous(),
+                                     name="%s.indices" % name, process_set=process_set)
+    values_handle = allgather_async(t._values(), name="%s.values" % name,
+                                    process_set=process_set)
+
+    def handle():
+        indices = synchronize(indices_handle)
+        values = synchronize(values_handle)
+        n = process_set.size() if process_set is not None else size()
+        values = values / n if op == Average else values
+        if indices.dim() == 0 or values.dim() == 0:
+            return t.new_empty(t.shape)
+        return torch.sparse_coo_tensor(indices.transpose(0, 1), values, t.shape)
+
+    return handle
+
+
+def allgather_async(tensor, name=None, process_set=global_process_set):
+    """Starts concatenating ``tensor`` from all ranks along dimension 0
+    (dimension 0 may differ between ranks)."""
+    _check_tensor(tensor)
+    handle = _C.allgather_async(tensor, name or "", _resolve(process_set))
+    _handle_map[handle] = ("allgather", None)
+    return handle
+
+
+class HorovodAllgather(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tensor, name, process_set):
+        ctx.dim = tensor.shape[0]
+        ctx.process_set = process_set
+        handle = allgather_async(tensor, name, process_set)
+        return synchronize(handle)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        ps = ctx.process_set
+        grad_reduced = allreduce(grad_output, average=True, process_set=ps)
+        dim_t = torch.tensor([ctx.dim], dtype=torch.int64)
+        dims = allgather(dim_t, process_set=ps).view(-1)
+        r = ps.rank() if ps is not None else rank()
+        offset = int(dims[:r].sum().item()) if r != 0 else 0
+        return grad_reduced.narrow(0, offset, ctx.dim), None, None
+
+
+def allgather(tensor, name=None, process_set=global_process_set):
+    """Blocking, differentiable allgather."""
+    return HorovodAllgather.apply(tensor, name, process_set)
+
+
+def _broadcast_async(tensor, output, root_rank, name, process_set):
+    _check_tensor(tensor)
+    handle = _C.broadcast_async(tensor, output, int(root_rank), name or "",
+                                _resolve(process_set))
+    _handle_map[handle] = ("broadcast", None)
+    return handle
+
+
+def broadcast_async(tensor, root_rank, name=None, process_set=global_process_set):
+    """Starts broadcasting ``tensor`` from global rank ``root_rank``."""
+    output = tensor.new_empty(tensor.shape)
+    return _broadcast_async(tensor, output, root_rank, name, process_set)
+
+
+class HorovodBroadcast(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tensor, root_rank, name, process_set):
+        ctx.root_rank = root_rank
+        ctx.process_set = process_set
+        handle = broadcast_async(tensor, root_rank, name, process_set)
+        return synchronize(handle)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        grad_reduced = allreduce(grad_output, average=True, process_set=ctx.process_set)
+        if rank() != ctx.root_rank:
+            grad_reduced *= 0
+        return grad_reduced, None, None, None
+
+
+def broadcast(tensor, root_rank, name=None, process_set=global_process_set):
+    """Blocking, differentiable broadcast."""
+    return HorovodBroadcast.apply(tensor, root_rank, name, process_set)
+
+
+def broadcast_async_(tensor, root_rank, name=None, process_set=global_process_set):
+    return _broadcast_async(tensor, tensor, root_rank, name, process_set)
+
+
+def broadcast_(tensor, root_rank, name=None, process_set=global_process_set):
+    handle = broadcast_async_(tensor, root_rank, name, process_set)
+    return synchronize(handle)
+
+
+def _splits_list(splits):
+    if splits is None:
+        return []
+    if isinstance(splits, torch.Tensor):
+        if splits.dim() != 1 or splits.dtype not in (torch.int32, torch.int64):
+            raise ValueError("splits must be a 1-D integer tensor")
+        return [int(v) for v in splits.cpu().tolist()]
+    return [int(v) for v in splits]
+
+
+def alltoall_async(tensor, splits=None, name=None, process_set=global_process_set):
+    """Starts an all-to-all: rows ``splits[i]`` of dimension 0 go to rank i
+    (an even split when ``splits`` is None)."""
+    _check_tensor(tensor)
+    handle = _C.alltoall_async(tensor, _splits_list(splits), name or "",
+                               _resolve(process_set))
+    _handle_map[handle] = ("alltoall", splits is not None)
+    return handle
+
+
+class HorovodAlltoall(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tensor, splits, name, process_set):
+        handle = alltoall_async(tensor, splits, name, process_set)
+        result = synchronize(handle)
+        ctx.process_set = process_set
+        if splits is None:
+            # Even split both ways.
+            ctx.recvsplits = None
+            return result
+        output, recv = result
+        ctx.recvsplits = recv
+        ctx.mark_non_differentiable(recv)
+        return output, recv
+
+    @staticmethod
+    def backward(ctx, grad_output, *dead_gradients):
+        out = alltoall(grad_output, splits=ctx.recvsplits, process_set=ctx.process_set)
+        grad = out[0] if isinstance(out, tuple) else out
+        return grad, None, None, None
+
+
+def alltoall(tensor, splits=None, name=None, process_set=global_process_set):
+    """Blocking, differentiable all-to-all. Returns ``output`` or, when
+    ``splits`` was given, ``(output, received_splits)``."""
+    return HorovodAlltoall.apply(tensor, splits, name, process_set)
+
+
+def reducescatter_async(tensor, name=None, op=Average, prescale_factor=1.0,
+                        postscale_factor=1.0, process_set=global_process_set):
+    """Starts a reduce-scatter: the reduction of ``tensor`` over all ranks is
+    split along dimension 0 and rank r keeps chunk r (the first
+    ``dim0 % size`` ranks get one extra row)."""
+    _check_tensor(tensor)
+    if op == Adasum:
+        raise ValueError("reducescatter does not support Adasum")
+    handle = _C.reducescatter_async(tensor, name or "", int(op), float(prescale_factor),
+                                    float(postscale_factor), _resolve(process_set))
+    _handle_map[handle] = ("reducescatter", None)
+    return handle
+
+
+class HorovodReducescatter(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tensor, name, op, prescale_factor, postscale_factor, process_set):
+        ctx.op = op
+        ctx.process_set = process_set
+        ctx.scale = prescale_factor * postscale_factor
+        handle = reducescatter_async(tensor, name, op, prescale_factor, postscale_factor,
+                                     process_set)
+        return synchronize(handle)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        ps = ctx.process_set
+        n = ps.size() if ps is not None else size()
+        grad = allgather(grad_output.contiguous(), process_set=ps) * ctx.scale
+        if ctx.op == Average:
+            grad = grad / n
+        return grad, None, None, None, None, None
+
+
+def reducescatter(tensor, name=None, compression=Compression.none, op=Average,
+                  prescale_factor=1.0, postscale_factor=1.0, process_set=global_process_set):
+    """Blocking, differentiable reduce-scatter."""
+    tensor_compressed, ctx = compression.compress(tensor)
+    out = HorovodReducescatter.apply(tensor_compressed, name, op, prescale_factor,
+                                     postscale_factor, process_set)
+    return compression.decompress(out, ctx)
+
+
+def poll(handle):
+    """True once the op behind ``handle`` has run (CPU) or been launched
+    (GPU); synchronize() will then not block the host."""
+    return _C.poll(handle)
+
+
+def synchronize(handle):
+    """Waits for an asynchronous op and returns its result. GPU ops are
+    chained onto the current CUDA stream rather than host-synchronised."""
+    if handle not in _handle_map:
+        return None
+    kind, extra = _handle_map.pop(handle)
+    try:
+        outputs, recv_splits, _ = _C.wait_and_clear(handle)
+    except RuntimeError as e:
+        raise HorovodInternalError(e)
+    if kind == "allreduce":
+        return outputs[0]
+    if kind == "allreduce_intavg":
+        outputs[0].copy_(torch.div(outputs[0], extra, rounding_mode="floor"))
+        return outputs[0]
+    if kind == "grouped":
+        return list(outputs)
+    if kind == "grouped_intavg":
+        for o in outputs:
+            if not o.is_floating_point():
+                o.copy_(torch.div(o, extra, rounding_mode="floor"))
+            else:
+                o.div_(extra)
+        return list(outputs)
+    if kind == "alltoall":
+        out = outputs[0]
+        if extra:
+            return out, torch.tensor(recv_splits, dtype=torch.int32)
+        return out
+    return outputs[0]
+
+
+def join(device=-1, process_set=global_process_set):
+    """Tells the other ranks this rank has no more data. Blocks until every
+    rank has joined; meanwhile this rank contributes zeros to their
+    allreduces. Returns the rank that joined last."""
+    handle = _C.join_async(_resolve(process_set))
+    try:
+        _, _, last = _C.wait_and_clear(handle)
+    except RuntimeError as e:
+        raise HorovodInternalError(e)
+    return last

@@ -16,6 +16,9 @@ import sys
 import sysconfig
 
 PKG = os.path.dirname(os.path.abspath(__file__))
+# When run as a script the package directory lands on sys.path, where its
+# "torch" subpackage would shadow PyTorch.
+sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != PKG]
 ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 BUILD = os.path.join(ROOT, "build")

@@ -1,0 +1,139 @@
+// Allgather, broadcast and alltoall as one "exchange" kernel: every outbound
+// segment is copied from local tensor storage straight into the destination
+// rank's staging buffer over NVLink (peer stores; a segment addressed to all
+// ranks is written once through the multicast mapping with multimem.st when
+// available), one cross-GPU barrier follows, and every inbound segment is
+// copied from the local staging buffer into its final tensor.
+//
+// A segment is owned by the same CTA index on the sending and the receiving
+// rank (small segments by a hash of their staging offset, large ones split
+// evenly), so CTA b only waits for CTA b of its peers.
+//
+// Replaces ncclAllGather / grouped ncclBroadcast / ncclBcast per tensor /
+// grouped ncclSend+ncclRecv and the cudaMemcpyAsync loops around them
+// (horovod/common/ops/nccl_operations.cc:468-727,
+// horovod/common/ops/gpu_operations.cc:350-363).
+#include "device_utils.cuh"
+
+namespace hvd {
+namespace kern {
+
+namespace {
+
+constexpr int THREADS = 512;
+constexpr int64_t SMALL_SEGMENT = 64 * 1024;
+
+// Byte range of a segment that CTA b is responsible for.
+__device__ __forceinline__ void my_range(int64_t staging_off, int64_t bytes,
+                                         int b, int G, int64_t* lo, int64_t* hi) {
+  if (bytes <= SMALL_SEGMENT) {
+    const int owner = static_cast<int>((staging_off >> 8) % G);
+    *lo = 0;
+    *hi = owner == b ? bytes : 0;
+    return;
+  }
+  int64_t chunk = (bytes + G - 1) / G;
+  chunk = (chunk + 255) & ~int64_t(255);
+  *lo = min(bytes, b * chunk);
+  *hi = min(bytes, *lo + chunk);
+}
+
+enum Target { TO_PEER, TO_ALL_MC, TO_ALL_LOOP, LOCAL_COPY };
+
+// Cooperative copy of [lo, hi) bytes. dst_base/dst_all select the target.
+__device__ __forceinline__ void copy_bytes(const char* src, char* dst,
+                                           int64_t n, Target target,
+                                           const SymmCtx& ctx,
+                                           int64_t staging_off) {
+  if (n <= 0) return;
+  // `dst` is the local-view address; for TO_ALL_* the same offset is used in
+  // every rank's buffer.
+  const bool vec_ok =
+      ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0;
+  if (vec_ok) {
+    const int64_t nv = n >> 4;
+    for (int64_t i = threadIdx.x; i < nv; i += THREADS) {
+      const uint4 v = ld16(reinterpret_cast<const uint4*>(src) + i);
+      if (target == TO_ALL_MC) {
+        multimem_st16(ctx.mc + staging_off + (i << 4), v);
+      } else if (target == TO_ALL_LOOP) {
+        for (int p = 0; p < ctx.world; ++p)
+          st16(ctx.peers[p] + staging_off + (i << 4), v);
+      } else {
+        st16(reinterpret_cast<uint4*>(dst) + i, v);
+      }
+    }
+    src += nv << 4;
+    dst += nv << 4;
+    staging_off += nv << 4;
+    n -= nv << 4;
+  }
+  // Tail, or everything when the pointers are not 16-byte aligned.
+  for (int64_t i = threadIdx.x; i < n; i += THREADS) {
+    const char c = src[i];
+    if (target == TO_ALL_MC || target == TO_ALL_LOOP) {
+      for (int p = 0; p < ctx.world; ++p)
+        reinterpret_cast<volatile char*>(ctx.peers[p] + staging_off)[i] = c;
+    } else {
+      reinterpret_cast<volatile char*>(dst)[i] = c;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(THREADS)
+exchange_kernel(ExchangePlan plan, SymmCtx ctx) {
+  const int b = blockIdx.x, G = gridDim.x;
+  for (int s = 0; s < plan.n_out; ++s) {
+    const int64_t off = plan.out_staging_off[s], bytes = plan.out_bytes[s];
+    int64_t lo, hi;
+    my_range(off, bytes, b, G, &lo, &hi);
+    if (lo >= hi) continue;
+    const char* src = static_cast<const char*>(plan.out_src[s]) + lo;
+    const int dst_rank = plan.out_dst_rank[s];
+    if (dst_rank >= 0) {
+      copy_bytes(src, ctx.peers[dst_rank] + off + lo, hi - lo, TO_PEER, ctx, off + lo);
+    } else {
+      copy_bytes(src, ctx.local + off + lo, hi - lo,
+                 ctx.mc != nullptr ? TO_ALL_MC : TO_ALL_LOOP, ctx, off + lo);
+    }
+  }
+  if (!cta_barrier(ctx, ctx.epoch + 1, b, 1)) return;
+  for (int s = 0; s < plan.n_in; ++s) {
+    const int64_t off = plan.in_staging_off[s], bytes = plan.in_bytes[s];
+    int64_t lo, hi;
+    my_range(off, bytes, b, G, &lo, &hi);
+    if (lo >= hi) continue;
+    char* dst = static_cast<char*>(plan.in_dst[s]);
+    if (dst == nullptr) continue;
+    copy_bytes(ctx.local + off + lo, dst + lo, hi - lo, LOCAL_COPY, ctx, 0);
+  }
+  // Keep peers from overwriting this staging buffer with their next
+  // exchange before it has been drained.
+  cta_barrier(ctx, ctx.epoch + 2, b, 2);
+}
+
+__global__ void barrier_only_kernel(SymmCtx ctx) {
+  cta_barrier(ctx, ctx.epoch + 1, blockIdx.x, 1);
+}
+
+}  // namespace
+
+cudaError_t LaunchExchange(const ExchangePlan& plan, int num_ctas,
+                           const SymmCtx& ctx, cudaStream_t stream) {
+  if (num_ctas < 1 || num_ctas > SYMM_MAX_BLOCKS) return cudaErrorInvalidValue;
+  CountKernelLaunches(1);
+  exchange_kernel<<<num_ctas, THREADS, 0, stream>>>(plan, ctx);
+  return cudaGetLastError();
+}
+
+cudaError_t LaunchBarrierOnly(int num_ctas, int bank, const SymmCtx& ctx,
+                              cudaStream_t stream) {
+  (void)bank;  // the caller already pointed ctx.flags_* at the bank
+  if (num_ctas < 1 || num_ctas > SYMM_MAX_BLOCKS) return cudaErrorInvalidValue;
+  CountKernelLaunches(1);
+  barrier_only_kernel<<<num_ctas, 32, 0, stream>>>(ctx);
+  return cudaGetLastError();
+}
+
+}  // namespace kern
+}  // namespace hvd

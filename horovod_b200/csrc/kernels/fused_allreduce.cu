@@ -1,0 +1,222 @@
+// Fused multi-tensor allreduce over NVLink: one launch gathers the tensors
+// (prescale + cast to the wire type), reduces across GPUs and scatters the
+// result back (cast + postscale). Three cross-GPU algorithms share the
+// gather/scatter code:
+//   ONESHOT  every rank loads every peer's staging buffer and reduces all of
+//            it: one barrier before the loads, latency-optimal.
+//   TWOSHOT  rank r reduces chunk r from all peers (peer loads) and stores
+//            the result into every peer's staging buffer (peer stores).
+//   NVLS     same decomposition, but multimem.ld_reduce sums the chunk inside
+//            the NVSwitch and multimem.st broadcasts it.
+// CTA b of one rank only ever depends on CTA b of the other ranks (the data
+// is partitioned so that what CTA b reads from a peer was written by CTA b
+// there), so no grid-wide synchronisation is needed.
+#include "tensor_walk.cuh"
+
+namespace hvd {
+namespace kern {
+
+namespace {
+
+constexpr int THREADS = 512;
+
+template <typename T, typename W, typename S>
+__device__ __forceinline__ void pack_range(const TensorList& tl, uint4* stage,
+                                           int64_t lo, int64_t hi, S scale,
+                                           bool do_scale) {
+  constexpr int N = 16 / sizeof(W);
+  if (lo >= hi) return;
+  int cur = find_tensor(tl, (lo + threadIdx.x) * N);
+  for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS)
+    st16(stage + v, gather_vec<T, W, S>(tl, cur, v * N, scale, do_scale));
+}
+
+template <typename T, typename W, typename S>
+__device__ __forceinline__ void unpack_range(const TensorList& tl,
+                                             const uint4* stage, int64_t lo,
+                                             int64_t hi, S scale, bool do_scale) {
+  constexpr int N = 16 / sizeof(W);
+  if (lo >= hi) return;
+  int cur = find_tensor(tl, (lo + threadIdx.x) * N);
+  for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS)
+    scatter_vec<T, W, S>(tl, cur, v * N, ld16(stage + v), scale, do_scale);
+}
+
+template <typename T, typename W, int ALGO>
+__global__ void __launch_bounds__(THREADS)
+fused_allreduce_kernel(TensorList tl, SymmCtx ctx,
+                       typename ScaleT<T>::type prescale,
+                       typename ScaleT<T>::type postscale) {
+  using S = typename ScaleT<T>::type;
+  constexpr int N = 16 / sizeof(W);
+  const int64_t nvec = __ldg(tl.offsets + tl.n) / N;
+  const int world = ctx.world, rank = ctx.rank;
+  const int G = gridDim.x, b = blockIdx.x;
+  const bool pre = prescale != S(1), post = postscale != S(1);
+  uint4* stage = reinterpret_cast<uint4*>(ctx.local);
+
+  if constexpr (ALGO == static_cast<int>(Algo::LOCAL)) {
+    const int64_t per = (nvec + G - 1) / G;
+    const int64_t lo = b * per, hi = min(lo + per, nvec);
+    if (lo >= hi) return;
+    int cin = find_tensor(tl, (lo + threadIdx.x) * N), cout = cin;
+    const S both = prescale * postscale;
+    for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS) {
+      uint4 x = gather_vec<T, W, S>(tl, cin, v * N, both, pre || post);
+      scatter_vec<T, W, S>(tl, cout, v * N, x, S(1), false);
+    }
+    return;
+  } else if constexpr (ALGO == static_cast<int>(Algo::ONESHOT)) {
+    const int64_t per = (nvec + G - 1) / G;
+    const int64_t lo = b * per, hi = min(lo + per, nvec);
+    pack_range<T, W, S>(tl, stage, lo, hi, prescale, pre);
+    if (!cta_barrier(ctx, ctx.epoch + 1, b, 1)) return;
+    if (lo < hi) {
+      int cur = find_tensor(tl, (lo + threadIdx.x) * N);
+      for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS) {
+        uint4 in[SYMM_MAX_RANKS];
+#pragma unroll
+        for (int p = 0; p < SYMM_MAX_RANKS; ++p)
+          if (p < world) in[p] = ld16(reinterpret_cast<const uint4*>(ctx.peers[p]) + v);
+        VecAcc<W> acc;
+        acc.zero();
+#pragma unroll
+        for (int p = 0; p < SYMM_MAX_RANKS; ++p)
+          if (p < world) acc.add(in[p]);
+        scatter_vec<T, W, S>(tl, cur, v * N, acc.pack(), postscale, post);
+      }
+    }
+    // Nobody may repack its staging buffer while a peer still reads it.
+    cta_barrier(ctx, ctx.epoch + 2, b, 2);
+    return;
+  } else {
+    const int64_t per_rank = (nvec + world - 1) / world;
+    const int64_t per_cta = (per_rank + G - 1) / G;
+    for (int r = 0; r < world; ++r) {
+      const int64_t lo = r * per_rank + b * per_cta;
+      const int64_t hi = min(lo + per_cta, min((r + 1) * per_rank, nvec));
+      pack_range<T, W, S>(tl, stage, lo, hi, prescale, pre);
+    }
+    if (!cta_barrier(ctx, ctx.epoch + 1, b, 1)) return;
+    {
+      const int64_t lo = rank * per_rank + b * per_cta;
+      const int64_t hi = min(lo + per_cta, min((rank + 1) * per_rank, nvec));
+      if constexpr (ALGO == static_cast<int>(Algo::NVLS)) {
+        uint4* mc = reinterpret_cast<uint4*>(ctx.mc);
+        int64_t v = lo + threadIdx.x;
+        for (; v + 3 * THREADS < hi; v += 4 * THREADS) {
+          uint4 x0 = Multimem<W>::ld_reduce(mc + v);
+          uint4 x1 = Multimem<W>::ld_reduce(mc + v + THREADS);
+          uint4 x2 = Multimem<W>::ld_reduce(mc + v + 2 * THREADS);
+          uint4 x3 = Multimem<W>::ld_reduce(mc + v + 3 * THREADS);
+          multimem_st16(mc + v, x0);
+          multimem_st16(mc + v + THREADS, x1);
+          multimem_st16(mc + v + 2 * THREADS, x2);
+          multimem_st16(mc + v + 3 * THREADS, x3);
+        }
+        for (; v < hi; v += THREADS)
+          multimem_st16(mc + v, Multimem<W>::ld_reduce(mc + v));
+      } else {
+        for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS) {
+          uint4 in[SYMM_MAX_RANKS];
+#pragma unroll
+          for (int i = 0; i < SYMM_MAX_RANKS; ++i) {
+            // Start at a different peer on every rank to spread the load.
+            if (i < world) {
+              int p = rank + i;
+              if (p >= world) p -= world;
+              in[i] = ld16(reinterpret_cast<const uint4*>(ctx.peers[p]) + v);
+            }
+          }
+          VecAcc<W> acc;
+          acc.zero();
+#pragma unroll
+          for (int i = 0; i < SYMM_MAX_RANKS; ++i)
+            if (i < world) acc.add(in[i]);
+          const uint4 sum = acc.pack();
+#pragma unroll
+          for (int i = 0; i < SYMM_MAX_RANKS; ++i) {
+            if (i < world) {
+              int p = rank + i;
+              if (p >= world) p -= world;
+              st16(reinterpret_cast<uint4*>(ctx.peers[p]) + v, sum);
+            }
+          }
+        }
+      }
+    }
+    if (!cta_barrier(ctx, ctx.epoch + 2, b, 2)) return;
+    for (int r = 0; r < world; ++r) {
+      const int64_t lo = r * per_rank + b * per_cta;
+      const int64_t hi = min(lo + per_cta, min((r + 1) * per_rank, nvec));
+      unpack_range<T, W, S>(tl, stage, lo, hi, postscale, post);
+    }
+  }
+}
+
+template <typename T, typename W>
+cudaError_t LaunchTyped(const TensorList& tl, double prescale, double postscale,
+                        Algo algo, int num_ctas, const SymmCtx& ctx,
+                        cudaStream_t stream) {
+  using S = typename ScaleT<T>::type;
+  const S pre = static_cast<S>(prescale), post = static_cast<S>(postscale);
+  switch (algo) {
+  case Algo::LOCAL:
+    fused_allreduce_kernel<T, W, 0><<<num_ctas, THREADS, 0, stream>>>(tl, ctx, pre, post);
+    break;
+  case Algo::ONESHOT:
+    fused_allreduce_kernel<T, W, 1><<<num_ctas, THREADS, 0, stream>>>(tl, ctx, pre, post);
+    break;
+  case Algo::TWOSHOT:
+    fused_allreduce_kernel<T, W, 2><<<num_ctas, THREADS, 0, stream>>>(tl, ctx, pre, post);
+    break;
+  case Algo::NVLS:
+    if constexpr (std::is_same<W, float>::value || std::is_same<W, __half>::value ||
+                  std::is_same<W, __nv_bfloat16>::value) {
+      if (ctx.mc == nullptr) return cudaErrorInvalidValue;
+      fused_allreduce_kernel<T, W, 3><<<num_ctas, THREADS, 0, stream>>>(tl, ctx, pre, post);
+    } else {
+      return cudaErrorInvalidValue;
+    }
+    break;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t LaunchFusedAllreduce(const TensorList& tl, DataType dtype,
+                                 DataType wire, double prescale,
+                                 double postscale, Algo algo, int num_ctas,
+                                 const SymmCtx& ctx, cudaStream_t stream) {
+  if (num_ctas < 1 || num_ctas > SYMM_MAX_BLOCKS) return cudaErrorInvalidValue;
+  CountKernelLaunches(1);
+  if (dtype == DataType::FLOAT32 && wire == DataType::BFLOAT16)
+    return LaunchTyped<float, __nv_bfloat16>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+  if (dtype == DataType::FLOAT32 && wire == DataType::FLOAT16)
+    return LaunchTyped<float, __half>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+  if (dtype != wire) return cudaErrorInvalidValue;
+  switch (dtype) {
+  case DataType::FLOAT32:
+    return LaunchTyped<float, float>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+  case DataType::FLOAT16:
+    return LaunchTyped<__half, __half>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+  case DataType::BFLOAT16:
+    return LaunchTyped<__nv_bfloat16, __nv_bfloat16>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+  case DataType::FLOAT64:
+    return LaunchTyped<double, double>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+  case DataType::INT32:
+    return LaunchTyped<int32_t, int32_t>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+  case DataType::INT64:
+    return LaunchTyped<int64_t, int64_t>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+  case DataType::UINT8:
+    return LaunchTyped<uint8_t, uint8_t>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+  case DataType::INT8:
+    return LaunchTyped<int8_t, int8_t>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+  default:
+    return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace kern
+}  // namespace hvd

@@ -1,0 +1,144 @@
+// Host-side launch API of the sm_100a collective kernels. Every kernel works
+// on symmetric memory (see symm/symm_arena.h): data moves between GPUs by
+// loads/stores on peer pointers or by `multimem` instructions on the
+// multicast mapping, issued from inside the kernel. Cross-GPU
+// synchronisation uses per-(rank, CTA) flag words with release/acquire
+// semantics and a monotonically increasing epoch; every wait is bounded and
+// reports a timeout through a host-visible status record instead of hanging.
+//
+// These kernels replace the reference's pack -> NCCL -> unpack sequences
+// (horovod/common/ops/nccl_operations.cc:156-727 and
+// horovod/common/ops/cuda/cuda_kernels.cu:44-321).
+#pragma once
+
+#include <cstdint>
+
+#include <cuda_runtime_api.h>
+
+#include "../common/common.h"
+#include "../symm/symm_arena.h"
+
+namespace hvd {
+namespace kern {
+
+// Kernel-side view of the symmetric arena for one launch.
+struct SymmCtx {
+  int rank;
+  int world;
+  char* local;
+  char* peers[SYMM_MAX_RANKS];
+  char* mc;  // null when multicast is unavailable
+  uint32_t* flags_local;
+  uint32_t* flags_peers[SYMM_MAX_RANKS];
+  uint32_t epoch;  // flags of this launch take values epoch+1, epoch+2, ...
+  unsigned long long timeout_ns;
+  int* status;  // host-mapped KernelStatus
+};
+
+// Written by a kernel whose bounded wait ran out. code 0 = fine.
+struct KernelStatus {
+  int code;   // 1 = timeout waiting for a peer flag
+  int peer;   // rank that never arrived
+  int phase;  // which barrier inside the kernel
+  int block;  // CTA that gave up
+};
+
+enum class Algo : int {
+  LOCAL = 0,    // world == 1: scaled copy only
+  ONESHOT = 1,  // every rank reads all peers and reduces the whole buffer
+  TWOSHOT = 2,  // reduce-scatter by peer loads + allgather by peer stores
+  NVLS = 3,     // multimem.ld_reduce + multimem.st through the switch
+};
+
+// Per-launch tensor list, in device memory. Tensor i occupies elements
+// [offsets[i], offsets[i] + counts[i]) of the fused index space; offsets are
+// multiples of 16 bytes of the wire type; offsets[n] is the padded total.
+// A null input contributes zeros; a null output discards the result.
+struct TensorList {
+  int n;
+  const int64_t* offsets;  // n + 1 entries
+  const int64_t* counts;   // n entries
+  const void* const* in;   // n entries
+  void* const* out;        // n entries
+};
+
+// Number of barrier epochs a launch of each kernel consumes.
+constexpr uint32_t EPOCHS_PER_LAUNCH = 4;
+// The Adasum driver launches 2 * log2(world) + 2 kernels, one epoch each.
+constexpr uint32_t ADASUM_EPOCHS = 16;
+
+// Fused multi-tensor allreduce (sum): gather from tensor storage with
+// prescale and cast to the wire type, reduce across GPUs, postscale, cast
+// back and scatter to the outputs, in one launch.
+// dtype: element type of the tensors. wire: element type in the staging
+// buffer and on NVLink (same as dtype, or FLOAT16/BFLOAT16 for FLOAT32
+// tensors). Returns cudaErrorInvalidValue for unsupported combinations.
+cudaError_t LaunchFusedAllreduce(const TensorList& tensors, DataType dtype,
+                                 DataType wire, double prescale,
+                                 double postscale, Algo algo, int num_ctas,
+                                 const SymmCtx& ctx, cudaStream_t stream);
+
+// Fused reduce-scatter: like the first half of the two-shot allreduce; rank
+// r's output receives elements [shard_begin[r], shard_begin[r+1]) of the
+// single input tensor (element offsets; ragged shards allowed).
+cudaError_t LaunchFusedReducescatter(const void* in, void* out, int64_t count,
+                                     const int64_t* shard_begin_dev,
+                                     DataType dtype, double prescale,
+                                     double postscale, bool use_nvls,
+                                     int num_ctas, const SymmCtx& ctx,
+                                     cudaStream_t stream);
+
+// Generic "push through staging" exchange used by allgather, broadcast and
+// alltoall: phase 1 copies each outbound segment from local tensors into the
+// staging buffer of its destination rank (peer stores, or one multimem.st
+// when a segment goes to everyone), a cross-GPU barrier follows, phase 2
+// copies inbound segments from the local staging buffer into their final
+// tensors. dst_rank[i] = -1 means "all ranks".
+struct ExchangePlan {
+  int n_out;
+  const void* const* out_src;     // local source pointers
+  const int64_t* out_staging_off; // byte offset in the destination staging
+  const int64_t* out_bytes;
+  const int32_t* out_dst_rank;
+  int n_in;
+  void* const* in_dst;            // local destination pointers
+  const int64_t* in_staging_off;  // byte offset in the local staging
+  const int64_t* in_bytes;
+};
+cudaError_t LaunchExchange(const ExchangePlan& plan, int num_ctas,
+                           const SymmCtx& ctx, cudaStream_t stream);
+
+// Adasum over symmetric memory. Tensors are packed into staging as fp32
+// (prescaled), combined pairwise over log2(world) levels with per-tensor
+// dot / squared norms accumulated in fp64, and scattered back. `scratch`
+// holds 3 * n doubles per level per rank inside the staging area (offset
+// given in bytes, 256-byte aligned).
+cudaError_t LaunchAdasum(const TensorList& tensors, DataType dtype,
+                         double prescale, double postscale,
+                         int64_t scratch_off, int num_ctas, const SymmCtx& ctx,
+                         cudaStream_t stream);
+
+// Stand-alone helpers (NCCL path and odd cases).
+// Batched (optionally scaled / casting) copy between tensor storage and a
+// contiguous fusion buffer. to_buffer: tensors -> buffer, else the reverse.
+// total_elements (the padded fused length) only sizes the grid.
+cudaError_t LaunchPackUnpack(const TensorList& tensors, DataType dtype,
+                             DataType wire, void* buffer, double scale,
+                             bool to_buffer, int64_t total_elements,
+                             cudaStream_t stream);
+// out[i] = in[i] * scale for any dtype (integers scale in double).
+cudaError_t LaunchScaleBuffer(const void* in, void* out, int64_t count,
+                              DataType dtype, double scale,
+                              cudaStream_t stream);
+
+// Number of kernels of this library launched so far in this process (every
+// Launch* function counts the kernels it enqueues).
+uint64_t KernelLaunchCount();
+void CountKernelLaunches(int n);
+
+// Test hook: a kernel that runs one cross-GPU barrier and nothing else.
+cudaError_t LaunchBarrierOnly(int num_ctas, int bank, const SymmCtx& ctx,
+                              cudaStream_t stream);
+
+}  // namespace kern
+}  // namespace hvd

@@ -1,0 +1,170 @@
+// Fused reduce-scatter over NVLink: the input tensor is packed (prescaled)
+// into the local staging buffer shard by shard, each shard starting on a
+// 256-byte boundary; after one cross-GPU barrier rank r sums shard r from
+// every peer (peer loads, or one multimem.ld_reduce per 16 bytes) and writes
+// the postscaled result directly into its output tensor. Shards may be
+// ragged (the first dim0 % size ranks own one extra row).
+//
+// Replaces ncclReduceScatter + ncclReduce for the remainder
+// (horovod/common/ops/nccl_operations.cc:342,356) and backs the public
+// reducescatter op.
+#include "tensor_walk.cuh"
+
+namespace hvd {
+namespace kern {
+
+namespace {
+
+constexpr int THREADS = 512;
+
+template <typename T, bool NVLS>
+__global__ void __launch_bounds__(THREADS)
+reducescatter_kernel(const T* in, T* out, const int64_t* shard_begin,
+                     SymmCtx ctx, typename ScaleT<T>::type prescale,
+                     typename ScaleT<T>::type postscale) {
+  using S = typename ScaleT<T>::type;
+  constexpr int N = 16 / sizeof(T);
+  const int world = ctx.world, rank = ctx.rank;
+  const int b = blockIdx.x, G = gridDim.x;
+  const bool pre = prescale != S(1), post = postscale != S(1);
+
+  // Staging layout: shard r starts at vector index vbase[r].
+  __shared__ int64_t sb[SYMM_MAX_RANKS + 1];
+  __shared__ int64_t vbase[SYMM_MAX_RANKS + 1];
+  if (threadIdx.x == 0) {
+    int64_t v = 0;
+    for (int r = 0; r <= world; ++r) {
+      sb[r] = shard_begin[r];
+      vbase[r] = v;
+      if (r < world) {
+        int64_t n = shard_begin[r + 1] - shard_begin[r];
+        int64_t vecs = (n + N - 1) / N;
+        v += (vecs + 15) & ~int64_t(15);  // 256-byte aligned shard starts
+      }
+    }
+  }
+  __syncthreads();
+  uint4* stage = reinterpret_cast<uint4*>(ctx.local);
+
+  // Phase 1: pack slice b of every shard.
+  for (int r = 0; r < world; ++r) {
+    const int64_t n = sb[r + 1] - sb[r];
+    const int64_t vecs = (n + N - 1) / N;
+    const int64_t per = (vecs + G - 1) / G;
+    const int64_t lo = b * per, hi = min(lo + per, vecs);
+    const T* src = in + sb[r];
+    const bool aligned = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
+    for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS) {
+      WireVec<T> w;
+      w.raw = make_uint4(0, 0, 0, 0);
+      const int64_t e0 = v * N;
+      if (aligned && e0 + N <= n) {
+        w.raw = ld16_stream(reinterpret_cast<const uint4*>(src) + v);
+        if (pre) {
+#pragma unroll
+          for (int i = 0; i < N; ++i) w.e[i] = scale_cast<T>(w.e[i], prescale, true);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i)
+          if (e0 + i < n) w.e[i] = scale_cast<T>(src[e0 + i], prescale, pre);
+      }
+      st16(stage + vbase[r] + v, w.raw);
+    }
+  }
+  if (!cta_barrier(ctx, ctx.epoch + 1, b, 1)) return;
+
+  // Phase 2: reduce slice b of my shard and write it out.
+  {
+    const int64_t n = sb[rank + 1] - sb[rank];
+    const int64_t vecs = (n + N - 1) / N;
+    const int64_t per = (vecs + G - 1) / G;
+    const int64_t lo = b * per, hi = min(lo + per, vecs);
+    const bool aligned = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS) {
+      WireVec<T> w;
+      if constexpr (NVLS) {
+        w.raw = Multimem<T>::ld_reduce(reinterpret_cast<const uint4*>(ctx.mc) +
+                                       vbase[rank] + v);
+      } else {
+        uint4 x[SYMM_MAX_RANKS];
+#pragma unroll
+        for (int p = 0; p < SYMM_MAX_RANKS; ++p)
+          if (p < world)
+            x[p] = ld16(reinterpret_cast<const uint4*>(ctx.peers[p]) + vbase[rank] + v);
+        VecAcc<T> acc;
+        acc.zero();
+#pragma unroll
+        for (int p = 0; p < SYMM_MAX_RANKS; ++p)
+          if (p < world) acc.add(x[p]);
+        w.raw = acc.pack();
+      }
+      const int64_t e0 = v * N;
+      if (post) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) w.e[i] = scale_cast<T>(w.e[i], postscale, true);
+      }
+      if (aligned && e0 + N <= n) {
+        st16_stream(reinterpret_cast<uint4*>(out) + v, w.raw);
+      } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i)
+          if (e0 + i < n) out[e0 + i] = w.e[i];
+      }
+    }
+  }
+  cta_barrier(ctx, ctx.epoch + 2, b, 2);
+}
+
+template <typename T>
+cudaError_t LaunchTyped(const void* in, void* out, const int64_t* shard_begin,
+                        double prescale, double postscale, bool nvls,
+                        int num_ctas, const SymmCtx& ctx, cudaStream_t stream) {
+  using S = typename ScaleT<T>::type;
+  constexpr bool can_nvls = std::is_same<T, float>::value ||
+                            std::is_same<T, __half>::value ||
+                            std::is_same<T, __nv_bfloat16>::value;
+  if constexpr (can_nvls) {
+    if (nvls && ctx.mc != nullptr) {
+      reducescatter_kernel<T, true><<<num_ctas, THREADS, 0, stream>>>(
+          static_cast<const T*>(in), static_cast<T*>(out), shard_begin, ctx,
+          static_cast<S>(prescale), static_cast<S>(postscale));
+      return cudaGetLastError();
+    }
+  }
+  reducescatter_kernel<T, false><<<num_ctas, THREADS, 0, stream>>>(
+      static_cast<const T*>(in), static_cast<T*>(out), shard_begin, ctx,
+      static_cast<S>(prescale), static_cast<S>(postscale));
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t LaunchFusedReducescatter(const void* in, void* out, int64_t count,
+                                     const int64_t* shard_begin_dev,
+                                     DataType dtype, double prescale,
+                                     double postscale, bool use_nvls,
+                                     int num_ctas, const SymmCtx& ctx,
+                                     cudaStream_t stream) {
+  (void)count;
+  if (num_ctas < 1 || num_ctas > SYMM_MAX_BLOCKS) return cudaErrorInvalidValue;
+  CountKernelLaunches(1);
+#define HVD_RS(T)                                                             \
+  return LaunchTyped<T>(in, out, shard_begin_dev, prescale, postscale,        \
+                        use_nvls, num_ctas, ctx, stream)
+  switch (dtype) {
+  case DataType::FLOAT32: HVD_RS(float);
+  case DataType::FLOAT16: HVD_RS(__half);
+  case DataType::BFLOAT16: HVD_RS(__nv_bfloat16);
+  case DataType::FLOAT64: HVD_RS(double);
+  case DataType::INT32: HVD_RS(int32_t);
+  case DataType::INT64: HVD_RS(int64_t);
+  case DataType::UINT8: HVD_RS(uint8_t);
+  case DataType::INT8: HVD_RS(int8_t);
+  default: return cudaErrorInvalidValue;
+  }
+#undef HVD_RS
+}
+
+}  // namespace kern
+}  // namespace hvd

@@ -1,0 +1,256 @@
+// Broadcast, allgather and alltoall on device tensors, all expressed as
+// segment lists for the exchange kernel: outbound segments go from local
+// tensors into the staging buffer of their destination rank(s), inbound
+// segments go from the local staging buffer into the final tensors.
+#include <algorithm>
+#include <cstring>
+
+#include "../common/logging.h"
+#include "../common/process_set.h"
+#include "gpu_internal.h"
+
+namespace hvd {
+
+namespace {
+constexpr int64_t STAGING_ALIGN = 256;
+}
+
+void GpuOps::LaunchExchangeSegments(const std::vector<OutSeg>& out,
+                                    const std::vector<InSeg>& in, SymmSet& set) {
+  DescriptorRing::Slot slot = ring_.Acquire();
+  const size_t no = out.size(), ni = in.size();
+  const void** d_src;
+  int64_t *d_ooff, *d_obytes, *d_ioff, *d_ibytes;
+  int32_t* d_dst_rank;
+  void** d_dst;
+  const void** h_src = slot.Alloc<const void*>(no + 1, &d_src);
+  int64_t* h_ooff = slot.Alloc<int64_t>(no + 1, &d_ooff);
+  int64_t* h_obytes = slot.Alloc<int64_t>(no + 1, &d_obytes);
+  int32_t* h_dst_rank = slot.Alloc<int32_t>(no + 1, &d_dst_rank);
+  void** h_dst = slot.Alloc<void*>(ni + 1, &d_dst);
+  int64_t* h_ioff = slot.Alloc<int64_t>(ni + 1, &d_ioff);
+  int64_t* h_ibytes = slot.Alloc<int64_t>(ni + 1, &d_ibytes);
+  if (!h_src || !h_ooff || !h_obytes || !h_dst_rank || !h_dst || !h_ioff || !h_ibytes)
+    throw std::runtime_error("exchange plan does not fit a descriptor slot");
+  int64_t bytes = 0;
+  for (size_t i = 0; i < no; ++i) {
+    h_src[i] = out[i].src;
+    h_ooff[i] = out[i].staging_off;
+    h_obytes[i] = out[i].bytes;
+    h_dst_rank[i] = out[i].dst;
+    bytes += out[i].bytes;
+  }
+  for (size_t i = 0; i < ni; ++i) {
+    h_dst[i] = in[i].dst;
+    h_ioff[i] = in[i].staging_off;
+    h_ibytes[i] = in[i].bytes;
+    bytes += in[i].bytes;
+  }
+  ring_.Commit(slot, stream_);
+  kern::ExchangePlan plan;
+  plan.n_out = static_cast<int>(no);
+  plan.out_src = d_src;
+  plan.out_staging_off = d_ooff;
+  plan.out_bytes = d_obytes;
+  plan.out_dst_rank = d_dst_rank;
+  plan.n_in = static_cast<int>(ni);
+  plan.in_dst = d_dst;
+  plan.in_staging_off = d_ioff;
+  plan.in_bytes = d_ibytes;
+  kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH);
+  cudaError_t err = kern::LaunchExchange(plan, PickCtas(bytes), ctx, stream_);
+  ring_.Release(slot, stream_);
+  if (err != cudaSuccess)
+    throw std::runtime_error(std::string("exchange kernel launch failed: ") +
+                             cudaGetErrorString(err));
+}
+
+// Every rank builds the same global list of "blocks" (source rank, bytes,
+// who receives it); blocks are laid out in the staging buffer in order and
+// processed in rounds that fit its capacity. A block larger than the
+// capacity is cut into parts first. All of this is deterministic, so the
+// ranks agree on rounds and offsets without talking.
+namespace {
+struct Block {
+  int src_rank;        // set rank that owns the data
+  int dst_rank;        // receiving set rank, or -1 for everybody
+  const char* src;     // valid on src_rank only
+  char* dst;           // where this rank wants the data (null = not wanted)
+  int64_t bytes;
+};
+}  // namespace
+
+static void RunBlocks(GpuOps* self, std::vector<Block>& blocks, SymmSet& set,
+                      const std::function<void(const std::vector<GpuOps::OutSeg>&,
+                                               const std::vector<GpuOps::InSeg>&)>& launch) {
+  (void)self;
+  const int64_t cap = static_cast<int64_t>(set.data_bytes);
+  // Split oversized blocks.
+  std::vector<Block> parts;
+  for (auto& b : blocks) {
+    int64_t pos = 0;
+    if (b.bytes == 0) continue;
+    while (pos < b.bytes) {
+      int64_t take = std::min(b.bytes - pos, cap / 2 / STAGING_ALIGN * STAGING_ALIGN);
+      Block p = b;
+      p.src = b.src ? b.src + pos : nullptr;
+      p.dst = b.dst ? b.dst + pos : nullptr;
+      p.bytes = take;
+      parts.push_back(p);
+      pos += take;
+    }
+  }
+  size_t next = 0;
+  while (next < parts.size()) {
+    std::vector<GpuOps::OutSeg> out;
+    std::vector<GpuOps::InSeg> in;
+    // Offsets are per destination buffer: a block for everybody advances all
+    // cursors, a point-to-point block only its destination's.
+    std::vector<int64_t> cursor(set.world, 0);
+    size_t n = 0;
+    while (next + n < parts.size() && n < 4096) {
+      const Block& b = parts[next + n];
+      int64_t padded = RoundUp(b.bytes, STAGING_ALIGN);
+      int64_t off;
+      if (b.dst_rank < 0) {
+        off = *std::max_element(cursor.begin(), cursor.end());
+        if (off + padded > cap) break;
+        for (auto& c : cursor) c = off + padded;
+      } else {
+        off = cursor[b.dst_rank];
+        if (off + padded > cap) break;
+        cursor[b.dst_rank] = off + padded;
+      }
+      if (b.src_rank == set.rank)
+        out.push_back({b.src, off, b.bytes, b.dst_rank});
+      if ((b.dst_rank < 0 || b.dst_rank == set.rank) && b.dst != nullptr)
+        in.push_back({b.dst, off, b.bytes});
+      ++n;
+    }
+    if (n == 0) throw std::runtime_error("exchange block exceeds staging capacity");
+    launch(out, in);
+    next += n;
+  }
+}
+
+Status GpuOps::SymmBroadcast(std::vector<TensorTableEntry>& entries,
+                             SymmSet& set) {
+  Timeline& tl = state_.timeline;
+  WaitForInputs(entries);
+  tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
+  std::vector<Block> blocks;
+  for (auto& e : entries) {
+    Block b;
+    b.src_rank = e.root_rank;
+    b.dst_rank = -1;
+    b.src = static_cast<const char*>(e.input);
+    b.dst = static_cast<char*>(e.output);
+    // The root already holds the data unless it asked for a separate output.
+    if (set.rank == e.root_rank && e.input == e.output) b.dst = nullptr;
+    b.bytes = e.size_bytes();
+    blocks.push_back(b);
+  }
+  RunBlocks(this, blocks, set,
+            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i) {
+              LaunchExchangeSegments(o, i, set);
+            });
+  tl.ActivityEndAll(entries);
+  return Complete(entries);
+}
+
+Status GpuOps::SymmAllgather(std::vector<TensorTableEntry>& entries,
+                             const Response& response, SymmSet& set) {
+  Timeline& tl = state_.timeline;
+  const int n = set.world;
+  WaitForInputs(entries);
+  std::vector<Block> blocks;
+  for (size_t i = 0; i < entries.size(); ++i) {
+    TensorTableEntry& e = entries[i];
+    int64_t slice = static_cast<int64_t>(DataTypeSize(e.dtype));
+    for (int d = 1; d < e.shape.dims(); ++d) slice *= e.shape.dim_size(d);
+    int64_t rows = 0;
+    for (int r = 0; r < n; ++r) rows += response.tensor_sizes[i * n + r];
+    std::vector<int64_t> dims = e.shape.to_vector();
+    dims[0] = rows;
+    tl.ActivityStart(e.name, HVD_ACT_ALLOCATE_OUTPUT);
+    void* out = nullptr;
+    Status st = e.context->AllocateOutput(TensorShape(dims), stream_, &out);
+    tl.ActivityEnd(e.name);
+    if (!st.ok()) return st;
+    e.output = out;
+    int64_t disp = 0;
+    for (int r = 0; r < n; ++r) {
+      Block b;
+      b.src_rank = r;
+      b.dst_rank = -1;
+      b.src = r == set.rank ? static_cast<const char*>(e.input) : nullptr;
+      b.dst = static_cast<char*>(out) + disp;
+      b.bytes = response.tensor_sizes[i * n + r] * slice;
+      disp += b.bytes;
+      blocks.push_back(b);
+    }
+  }
+  tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
+  RunBlocks(this, blocks, set,
+            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i) {
+              LaunchExchangeSegments(o, i, set);
+            });
+  tl.ActivityEndAll(entries);
+  return Complete(entries);
+}
+
+Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries,
+                            ProcessSet& ps, SymmSet& set) {
+  Timeline& tl = state_.timeline;
+  const int n = set.world, me = set.rank;
+  WaitForInputs(entries);
+  std::vector<Block> blocks;
+  for (auto& e : entries) {
+    int64_t slice = static_cast<int64_t>(DataTypeSize(e.dtype));
+    for (int d = 1; d < e.shape.dims(); ++d) slice *= e.shape.dim_size(d);
+    // Full split matrix over the control plane: all[r * n + p] = rows rank r
+    // sends to rank p.
+    std::vector<int32_t> all(static_cast<size_t>(n) * n);
+    ps.comm.Allgather(e.splits.data(), sizeof(int32_t) * n, all.data());
+    std::vector<int32_t> recv(n);
+    int64_t rows = 0;
+    for (int r = 0; r < n; ++r) {
+      recv[r] = all[r * n + me];
+      rows += recv[r];
+    }
+    std::vector<int64_t> dims = e.shape.to_vector();
+    dims[0] = rows;
+    tl.ActivityStart(e.name, HVD_ACT_ALLOCATE_OUTPUT);
+    void* out = nullptr;
+    Status st = e.context->AllocateOutput(TensorShape(dims), stream_, &out);
+    tl.ActivityEnd(e.name);
+    if (!st.ok()) return st;
+    e.output = out;
+    e.context->SetReceivedSplits(recv);
+    std::vector<int64_t> send_off(n, 0), recv_off(n, 0);
+    for (int p = 1; p < n; ++p) {
+      send_off[p] = send_off[p - 1] + e.splits[p - 1] * slice;
+      recv_off[p] = recv_off[p - 1] + recv[p - 1] * slice;
+    }
+    for (int r = 0; r < n; ++r) {
+      for (int p = 0; p < n; ++p) {
+        Block b;
+        b.src_rank = r;
+        b.dst_rank = p;
+        b.bytes = static_cast<int64_t>(all[r * n + p]) * slice;
+        b.src = r == me ? static_cast<const char*>(e.input) + send_off[p] : nullptr;
+        b.dst = p == me ? static_cast<char*>(out) + recv_off[r] : nullptr;
+        blocks.push_back(b);
+      }
+    }
+  }
+  tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
+  RunBlocks(this, blocks, set,
+            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i) {
+              LaunchExchangeSegments(o, i, set);
+            });
+  tl.ActivityEndAll(entries);
+  return Complete(entries);
+}
+
+}  // namespace hvd

@@ -1,0 +1,168 @@
+// Private declarations shared by the files that implement the device
+// executor (gpu_ops.cc: lifecycle and dispatch; gpu_symm_ops.cc: the NVLink
+// kernel paths; nccl_ops.cc: the NCCL path).
+#pragma once
+
+#include <functional>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include <cuda_runtime_api.h>
+
+#include "../common/global_state.h"
+#include "../common/thread_pool.h"
+#include "../kernels/kernels.h"
+#include "../symm/symm_arena.h"
+#include "op_executor.h"
+
+namespace hvd {
+
+#define HVD_CUDA(call)                                                        \
+  do {                                                                        \
+    cudaError_t e_ = (call);                                                  \
+    if (e_ != cudaSuccess)                                                    \
+      throw std::runtime_error(std::string(#call) + " failed: " +             \
+                               cudaGetErrorString(e_));                       \
+  } while (0)
+
+// Pool of completion events; an event returns to the pool when the last
+// holder (a handle record in the binding) lets go of it.
+class DoneEventPool : public std::enable_shared_from_this<DoneEventPool> {
+public:
+  std::shared_ptr<void> Get();
+
+private:
+  std::mutex mu_;
+  std::vector<cudaEvent_t> free_;
+};
+
+// Ring of host-pinned / device buffer pairs used to hand per-launch
+// descriptors (tensor lists, exchange plans) to kernels: fill the host half,
+// one async copy, kernel reads the device half. A slot is reused only after
+// the kernel that read it has finished.
+class DescriptorRing {
+public:
+  struct Slot {
+    int index = 0;
+    char* host = nullptr;
+    char* dev = nullptr;
+    size_t capacity = 0;
+    size_t used = 0;
+    // Reserves `bytes` (256-byte aligned) and returns host/device addresses.
+    template <typename T> T* Alloc(size_t count, T** dev_ptr) {
+      size_t bytes = (count * sizeof(T) + 255) & ~size_t(255);
+      if (used + bytes > capacity) return nullptr;
+      T* h = reinterpret_cast<T*>(host + used);
+      *dev_ptr = reinterpret_cast<T*>(dev + used);
+      used += bytes;
+      return h;
+    }
+  };
+  ~DescriptorRing();
+  void Create(size_t slot_bytes, int slots);
+  void Destroy();
+  Slot Acquire();
+  void Commit(Slot& slot, cudaStream_t stream);
+  void Release(const Slot& slot, cudaStream_t stream);
+  size_t slot_bytes() const { return slot_bytes_; }
+
+private:
+  struct SlotState {
+    cudaEvent_t done = nullptr;
+    bool used = false;
+  };
+  size_t slot_bytes_ = 0;
+  char* host_ = nullptr;
+  char* dev_ = nullptr;
+  std::vector<SlotState> slots_;
+  int next_ = 0;
+};
+
+// What a process set needs to run kernels over the arena: the subset of
+// peer pointers in set-rank order, its flag region and its epoch counter.
+struct SymmSet {
+  int rank = 0;
+  int world = 1;
+  bool nvls = false;  // multicast usable (set covers the whole arena)
+  char* local = nullptr;
+  char* peers[SYMM_MAX_RANKS] = {};
+  char* mc = nullptr;
+  uint32_t* flags_local = nullptr;
+  uint32_t* flags_peers[SYMM_MAX_RANKS] = {};
+  uint32_t epoch = 0;
+  size_t data_bytes = 0;
+};
+
+class NcclOps;
+
+class GpuOps : public OpExecutor {
+public:
+  explicit GpuOps(GlobalState& s);
+  ~GpuOps() override;
+
+  Status Execute(std::vector<TensorTableEntry>& entries,
+                 const Response& response, ProcessSet& ps) override;
+  void Shutdown() override;
+
+  // Segments handed to the exchange kernel.
+  struct OutSeg { const void* src; int64_t staging_off; int64_t bytes; int32_t dst; };
+  struct InSeg { void* dst; int64_t staging_off; int64_t bytes; };
+
+  // Used by the NCCL path.
+  cudaStream_t stream() const { return stream_; }
+  DescriptorRing& ring() { return ring_; }
+  GlobalState& state() { return state_; }
+  void WaitForInputs(const std::vector<TensorTableEntry>& entries);
+  Status Complete(std::vector<TensorTableEntry>& entries);
+
+private:
+  void EnsureDevice(int device);
+  void EnsureArena(ProcessSet& ps);
+  SymmSet* GetSymmSet(ProcessSet& ps);
+  kern::SymmCtx MakeCtx(SymmSet& set, uint32_t epochs);
+  Status CheckKernelStatus();
+  int PickCtas(int64_t bytes) const;
+  kern::Algo PickAlgo(const SymmSet& set, DataType wire, int64_t bytes) const;
+
+  Status SymmAllreduce(std::vector<TensorTableEntry>& entries,
+                       const Response& response, SymmSet& set, bool adasum);
+  Status SymmBroadcast(std::vector<TensorTableEntry>& entries, SymmSet& set);
+  Status SymmAllgather(std::vector<TensorTableEntry>& entries,
+                       const Response& response, SymmSet& set);
+  Status SymmAlltoall(std::vector<TensorTableEntry>& entries, ProcessSet& ps,
+                      SymmSet& set);
+  Status SymmReducescatter(std::vector<TensorTableEntry>& entries,
+                           SymmSet& set);
+  // One exchange-kernel launch for the given segment lists.
+  void LaunchExchangeSegments(const std::vector<OutSeg>& out,
+                              const std::vector<InSeg>& in, SymmSet& set);
+
+  GlobalState& state_;
+  std::shared_ptr<DoneEventPool> events_;
+  std::string backend_pref_;
+  bool async_completion_ = true;
+  bool want_nvls_ = true;
+  unsigned long long timeout_ns_ = 0;
+  int64_t oneshot_max_ = 0, nvls_min_ = 0;
+  int forced_ctas_ = 0;
+  std::string forced_algo_;
+  int device_ = -1;
+  cudaStream_t stream_ = nullptr;
+  ThreadPool finalizer_;
+  DescriptorRing ring_;
+  SymmArena arena_;
+  bool arena_tried_ = false;
+  kern::KernelStatus* status_host_ = nullptr;  // mapped pinned memory
+  int* status_dev_ = nullptr;
+  std::map<int32_t, std::unique_ptr<SymmSet>> sets_;
+  std::unique_ptr<NcclOps> nccl_;
+  bool shut_down_ = false;
+};
+
+// Published for diagnostics.
+void SetGpuBackendDescription(const std::string& s);
+
+}  // namespace hvd

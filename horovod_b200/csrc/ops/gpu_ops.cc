@@ -1,6 +1,369 @@
 #include "gpu_ops.h"
 
+#include <algorithm>
+#include <cstring>
+
+#include "../common/env.h"
+#include "../common/logging.h"
+#include "../common/operations.h"
+#include "gpu_internal.h"
+#include "nccl_ops.h"
+
 namespace hvd {
-void RegisterGpuOps() {}
-std::string GpuBackendDescription() { return "none"; }
+
+namespace {
+std::mutex g_desc_mu;
+std::string g_backend_desc = "none";
+}  // namespace
+
+void SetGpuBackendDescription(const std::string& s) {
+  std::lock_guard<std::mutex> l(g_desc_mu);
+  g_backend_desc = s;
+}
+
+std::string GpuBackendDescription() {
+  std::lock_guard<std::mutex> l(g_desc_mu);
+  return g_backend_desc;
+}
+
+void RegisterGpuOps() {
+  hvd_set_gpu_ops_factory([](GlobalState& s) -> std::unique_ptr<OpExecutor> {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+      cudaGetLastError();
+      SetGpuBackendDescription("none");
+      return nullptr;
+    }
+    SetGpuBackendDescription("pending (no device collective has run yet)");
+    return std::unique_ptr<OpExecutor>(new GpuOps(s));
+  });
+}
+
+// ---------------------------------------------------------------------------
+
+std::shared_ptr<void> DoneEventPool::Get() {
+  cudaEvent_t e = nullptr;
+  {
+    std::lock_guard<std::mutex> l(mu_);
+    if (!free_.empty()) {
+      e = free_.back();
+      free_.pop_back();
+    }
+  }
+  if (e == nullptr) HVD_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  std::weak_ptr<DoneEventPool> weak = shared_from_this();
+  return std::shared_ptr<void>(e, [weak](void* p) {
+    if (auto pool = weak.lock()) {
+      std::lock_guard<std::mutex> l(pool->mu_);
+      pool->free_.push_back(static_cast<cudaEvent_t>(p));
+    }
+    // Pool gone (shutdown): the event is reclaimed with the context.
+  });
+}
+
+DescriptorRing::~DescriptorRing() { Destroy(); }
+
+void DescriptorRing::Create(size_t slot_bytes, int slots) {
+  slot_bytes_ = slot_bytes;
+  slots_.resize(slots);
+  HVD_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&host_), slot_bytes * slots,
+                         cudaHostAllocDefault));
+  HVD_CUDA(cudaMalloc(reinterpret_cast<void**>(&dev_), slot_bytes * slots));
+  for (auto& s : slots_) {
+    HVD_CUDA(cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming));
+    s.used = false;
+  }
+}
+
+void DescriptorRing::Destroy() {
+  for (auto& s : slots_)
+    if (s.done) cudaEventDestroy(s.done);
+  slots_.clear();
+  if (host_) cudaFreeHost(host_);
+  if (dev_) cudaFree(dev_);
+  host_ = dev_ = nullptr;
+}
+
+DescriptorRing::Slot DescriptorRing::Acquire() {
+  SlotState& s = slots_[next_];
+  if (s.used) HVD_CUDA(cudaEventSynchronize(s.done));
+  Slot out;
+  out.index = next_;
+  out.host = host_ + slot_bytes_ * next_;
+  out.dev = dev_ + slot_bytes_ * next_;
+  out.capacity = slot_bytes_;
+  out.used = 0;
+  next_ = (next_ + 1) % static_cast<int>(slots_.size());
+  return out;
+}
+
+void DescriptorRing::Commit(Slot& slot, cudaStream_t stream) {
+  if (slot.used > 0)
+    HVD_CUDA(cudaMemcpyAsync(slot.dev, slot.host, slot.used,
+                             cudaMemcpyHostToDevice, stream));
+}
+
+void DescriptorRing::Release(const Slot& slot, cudaStream_t stream) {
+  SlotState& s = slots_[slot.index];
+  HVD_CUDA(cudaEventRecord(s.done, stream));
+  s.used = true;
+}
+
+// ---------------------------------------------------------------------------
+
+GpuOps::GpuOps(GlobalState& s) : state_(s), events_(new DoneEventPool()) {
+  backend_pref_ = EnvString(HVD_ENV_GPU_BACKEND, "symm");
+  async_completion_ = EnvBool(HVD_ENV_ENABLE_ASYNC_COMPLETION, !s.elastic_enabled);
+  want_nvls_ = EnvBool(HVD_ENV_SYMM_NVLS, true);
+  timeout_ns_ = static_cast<unsigned long long>(
+                    EnvInt(HVD_ENV_SPIN_TIMEOUT_MS, 20000)) * 1000000ull;
+  oneshot_max_ = EnvInt(HVD_ENV_ONESHOT_MAX, 512 * 1024);
+  nvls_min_ = EnvInt(HVD_ENV_NVLS_MIN, 512 * 1024);
+  forced_ctas_ = static_cast<int>(EnvInt(HVD_ENV_COMM_CTAS, 0));
+  forced_algo_ = EnvString(HVD_ENV_ALGO, "auto");
+}
+
+GpuOps::~GpuOps() { Shutdown(); }
+
+void GpuOps::EnsureDevice(int device) {
+  if (device_ == device) return;
+  if (device_ >= 0)
+    throw std::runtime_error(
+        "All CUDA tensors given to Horovod by one process must live on one "
+        "device (first saw cuda:" + std::to_string(device_) + ", now cuda:" +
+        std::to_string(device) + ").");
+  HVD_CUDA(cudaSetDevice(device));
+  int lo = 0, hi = 0;
+  HVD_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+  HVD_CUDA(cudaStreamCreateWithPriority(&stream_, cudaStreamNonBlocking, hi));
+  ring_.Create(1 << 20, 8);
+  HVD_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&status_host_),
+                         sizeof(kern::KernelStatus), cudaHostAllocMapped));
+  std::memset(status_host_, 0, sizeof(kern::KernelStatus));
+  HVD_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev_),
+                                    status_host_, 0));
+  finalizer_.Start(1);
+  device_ = device;
+}
+
+void GpuOps::EnsureArena(ProcessSet& ps) {
+  if (arena_tried_ || ps.id != 0) return;
+  arena_tried_ = true;
+  const bool one_node = state_.config.local_size == state_.config.size;
+  if (backend_pref_ == "nccl" || !one_node ||
+      state_.config.size > SYMM_MAX_RANKS) {
+    SetGpuBackendDescription("nccl");
+    return;
+  }
+  size_t mb = static_cast<size_t>(EnvInt(HVD_ENV_SYMM_BUFFER_MB, 512));
+  // The token doubles as socket-name salt: distinct per job and per init.
+  uint64_t token = state_.config.token ^ 0x9e3779b97f4a7c15ull;
+  Status st = arena_.Create(ps.comm, device_, mb << 20, want_nvls_, token);
+  if (!st.ok()) {
+    HVD_LOG(WARNING) << st.reason()
+                     << " -- device collectives fall back to NCCL.";
+    SetGpuBackendDescription("nccl (symmetric memory unavailable: " +
+                             st.reason() + ")");
+    return;
+  }
+  const SymmArenaInfo& a = arena_.info();
+  SetGpuBackendDescription(
+      "symm ranks=" + std::to_string(a.world) + " nvls=" +
+      std::to_string(a.multicast ? 1 : 0) + " staging_mb=" +
+      std::to_string(a.data_bytes >> 20));
+  HVD_LOG(INFO) << "symmetric memory ready: " << GpuBackendDescription();
+}
+
+SymmSet* GpuOps::GetSymmSet(ProcessSet& ps) {
+  if (!arena_.valid()) return nullptr;
+  auto it = sets_.find(ps.id);
+  if (it != sets_.end()) return it->second.get();
+  if (ps.id >= SYMM_FLAG_SETS) return nullptr;  // no flag region left
+  const SymmArenaInfo& a = arena_.info();
+  std::unique_ptr<SymmSet> set(new SymmSet());
+  const auto& ranks = ps.ranks();  // global == arena ranks on one node
+  set->world = static_cast<int>(ranks.size());
+  set->rank = ps.comm.rank();
+  set->data_bytes = a.data_bytes;
+  const size_t region = static_cast<size_t>(SYMM_FLAG_BANKS) * SYMM_MAX_RANKS *
+                        SYMM_MAX_BLOCKS;  // uint32 words per set
+  for (int i = 0; i < set->world; ++i) {
+    set->peers[i] = static_cast<char*>(a.peers[ranks[i]]);
+    set->flags_peers[i] = a.flags[ranks[i]] + region * ps.id;
+  }
+  set->local = set->peers[set->rank];
+  set->flags_local = set->flags_peers[set->rank];
+  set->nvls = a.multicast && set->world == a.world;
+  set->mc = set->nvls ? static_cast<char*>(a.mc) : nullptr;
+  // Fresh flag words for this set, agreed before anyone signals.
+  HVD_CUDA(cudaMemsetAsync(set->flags_local, 0, region * sizeof(uint32_t), stream_));
+  HVD_CUDA(cudaStreamSynchronize(stream_));
+  ps.comm.Barrier();
+  SymmSet* raw = set.get();
+  sets_[ps.id] = std::move(set);
+  return raw;
+}
+
+kern::SymmCtx GpuOps::MakeCtx(SymmSet& set, uint32_t epochs) {
+  kern::SymmCtx c;
+  std::memset(&c, 0, sizeof(c));
+  c.rank = set.rank;
+  c.world = set.world;
+  c.local = set.local;
+  for (int i = 0; i < set.world; ++i) {
+    c.peers[i] = set.peers[i];
+    c.flags_peers[i] = set.flags_peers[i];
+  }
+  c.mc = set.mc;
+  c.flags_local = set.flags_local;
+  c.epoch = set.epoch;
+  c.timeout_ns = timeout_ns_;
+  c.status = status_dev_;
+  set.epoch += epochs;
+  return c;
+}
+
+Status GpuOps::CheckKernelStatus() {
+  if (status_host_ != nullptr && status_host_->code != 0) {
+    return Status::UnknownError(
+        "A collective kernel timed out waiting for rank " +
+        std::to_string(status_host_->peer) + " (phase " +
+        std::to_string(status_host_->phase) +
+        "). The peer process probably died or stalled.");
+  }
+  return Status::OK();
+}
+
+int GpuOps::PickCtas(int64_t bytes) const {
+  if (forced_ctas_ > 0) return std::min(forced_ctas_, SYMM_MAX_BLOCKS);
+  // Few CTAs for latency-bound sizes, more as the message grows; capped well
+  // below the SM count so backward keeps most of the GPU.
+  if (bytes <= 64 * 1024) return 4;
+  if (bytes <= 1 << 20) return 16;
+  if (bytes <= 16 << 20) return 32;
+  return 64;
+}
+
+kern::Algo GpuOps::PickAlgo(const SymmSet& set, DataType wire,
+                            int64_t bytes) const {
+  if (set.world == 1) return kern::Algo::LOCAL;
+  const bool nvls_type = wire == DataType::FLOAT32 || wire == DataType::FLOAT16 ||
+                         wire == DataType::BFLOAT16;
+  if (forced_algo_ == "oneshot") return kern::Algo::ONESHOT;
+  if (forced_algo_ == "twoshot") return kern::Algo::TWOSHOT;
+  if (forced_algo_ == "nvls" && set.nvls && nvls_type) return kern::Algo::NVLS;
+  if (bytes <= oneshot_max_) return kern::Algo::ONESHOT;
+  if (set.nvls && nvls_type && bytes >= nvls_min_) return kern::Algo::NVLS;
+  return kern::Algo::TWOSHOT;
+}
+
+void GpuOps::WaitForInputs(const std::vector<TensorTableEntry>& entries) {
+  const ReadyEvent* last = nullptr;
+  for (auto& e : entries) {
+    if (e.ready && e.ready.get() != last) {
+      e.ready->StreamWait(stream_);
+      last = e.ready.get();
+    }
+  }
+}
+
+Status GpuOps::Complete(std::vector<TensorTableEntry>& entries) {
+  std::shared_ptr<void> done = events_->Get();
+  HVD_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(done.get()), stream_));
+  Timeline& tl = state_.timeline;
+  if (async_completion_ && !tl.Initialized()) {
+    Status st = CheckKernelStatus();
+    for (auto& e : entries) e.Finish(st, done);
+    return Status::InProgress();
+  }
+  // Host-synchronised completion: a finalizer thread waits for the event,
+  // so errors and timeline end times belong to this very op.
+  auto shared = std::make_shared<std::vector<TensorTableEntry>>(std::move(entries));
+  entries.clear();
+  finalizer_.Submit([this, shared, done] {
+    cudaError_t err = cudaEventSynchronize(static_cast<cudaEvent_t>(done.get()));
+    Status st = err == cudaSuccess
+                    ? CheckKernelStatus()
+                    : Status::UnknownError(std::string("CUDA error: ") +
+                                           cudaGetErrorString(err));
+    for (auto& e : *shared) {
+      state_.timeline.End(e.name);
+      e.Finish(st, done);
+    }
+  });
+  return Status::InProgress();
+}
+
+Status GpuOps::Execute(std::vector<TensorTableEntry>& entries,
+                       const Response& response, ProcessSet& ps) {
+  if (entries.empty()) return Status::OK();
+  int device = -1;
+  for (auto& e : entries)
+    if (e.device != CPU_DEVICE_ID && (e.input || e.output)) device = e.device;
+  if (device < 0) device = device_ >= 0 ? device_ : state_.config.local_rank;
+  EnsureDevice(device);
+  HVD_CUDA(cudaSetDevice(device_));
+  Status pending = CheckKernelStatus();
+  if (!pending.ok()) return pending;
+  EnsureArena(ps);
+  SymmSet* set = GetSymmSet(ps);
+
+  const bool sum_like = response.reduce_op == ReduceOp::SUM ||
+                        response.reduce_op == ReduceOp::AVERAGE ||
+                        response.reduce_op == ReduceOp::ADASUM;
+  bool use_symm = set != nullptr;
+  if (use_symm) {
+    switch (response.type) {
+    case Response::ALLREDUCE:
+    case Response::REDUCESCATTER:
+      use_symm = sum_like && response.dtype != DataType::BOOL &&
+                 response.dtype != DataType::INT16 &&
+                 response.dtype != DataType::UINT16;
+      break;
+    case Response::ADASUM:
+      use_symm = response.dtype == DataType::FLOAT32 ||
+                 response.dtype == DataType::FLOAT16 ||
+                 response.dtype == DataType::BFLOAT16;
+      break;
+    default:
+      break;
+    }
+  }
+  if (use_symm) {
+    switch (response.type) {
+    case Response::ALLREDUCE: return SymmAllreduce(entries, response, *set, false);
+    case Response::ADASUM: return SymmAllreduce(entries, response, *set, true);
+    case Response::BROADCAST: return SymmBroadcast(entries, *set);
+    case Response::ALLGATHER: return SymmAllgather(entries, response, *set);
+    case Response::ALLTOALL: return SymmAlltoall(entries, ps, *set);
+    case Response::REDUCESCATTER: return SymmReducescatter(entries, *set);
+    default: break;
+    }
+  }
+  if (!nccl_) nccl_.reset(new NcclOps(*this));
+  return nccl_->Execute(entries, response, ps);
+}
+
+void GpuOps::Shutdown() {
+  if (shut_down_) return;
+  shut_down_ = true;
+  if (device_ >= 0) {
+    cudaSetDevice(device_);
+    if (stream_) cudaStreamSynchronize(stream_);
+  }
+  finalizer_.Shutdown();
+  if (nccl_) nccl_->Shutdown();
+  nccl_.reset();
+  sets_.clear();
+  // Every rank reaches this point through the coordinated shutdown, after
+  // its last kernel finished, so nobody is touching peer mappings any more.
+  arena_.Destroy();
+  ring_.Destroy();
+  if (status_host_) cudaFreeHost(status_host_);
+  status_host_ = nullptr;
+  if (stream_) cudaStreamDestroy(stream_);
+  stream_ = nullptr;
+  SetGpuBackendDescription("none");
+}
+
 }  // namespace hvd

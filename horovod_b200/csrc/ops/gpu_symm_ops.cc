@@ -1,0 +1,180 @@
+// Device collectives over symmetric memory: builds the per-launch
+// descriptors, picks algorithm and grid, and launches the NVLink kernels on
+// the communication stream.
+#include <algorithm>
+#include <cstring>
+
+#include "../common/logging.h"
+#include "../common/process_set.h"
+#include "gpu_internal.h"
+
+namespace hvd {
+
+namespace {
+
+// A run of elements of one tensor that goes into one launch. Tensors larger
+// than the staging buffer are cut into several pieces.
+struct Piece {
+  const char* in;
+  char* out;
+  int64_t count;
+};
+
+constexpr int64_t STAGING_ALIGN = 256;
+
+}  // namespace
+
+Status GpuOps::SymmAllreduce(std::vector<TensorTableEntry>& entries,
+                             const Response& response, SymmSet& set,
+                             bool adasum) {
+  Timeline& tl = state_.timeline;
+  const DataType dtype = response.dtype;
+  // Adasum stages fp32 whatever the tensor type.
+  const DataType wire = (adasum && set.world > 1) ? DataType::FLOAT32 : dtype;
+  const int64_t es = static_cast<int64_t>(DataTypeSize(dtype));
+  const int64_t ws = static_cast<int64_t>(DataTypeSize(wire));
+  const int64_t align_elems = FUSION_ALIGN_BYTES / ws;
+
+  WaitForInputs(entries);
+  tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
+
+  // Room for data; Adasum also keeps 3 doubles per tensor per level behind it.
+  int64_t capacity = static_cast<int64_t>(set.data_bytes);
+  if (adasum) capacity -= RoundUp(int64_t(entries.size()) * 3 * 8 * 4 + 4096, 4096);
+  const int64_t cap_elems = capacity / ws / align_elems * align_elems;
+
+  // Cut into pieces no larger than the staging capacity.
+  std::vector<Piece> pieces;
+  for (auto& e : entries) {
+    int64_t n = e.num_elements(), pos = 0;
+    if (n == 0) continue;
+    if (adasum && n > cap_elems)
+      return Status::InvalidArgument(
+          "Adasum tensor '" + e.name + "' does not fit the symmetric staging "
+          "buffer; raise HOROVOD_SYMM_BUFFER_MB.");
+    while (pos < n) {
+      int64_t take = std::min(n - pos, cap_elems);
+      Piece p;
+      p.in = e.input ? static_cast<const char*>(e.input) + pos * es : nullptr;
+      p.out = e.output ? static_cast<char*>(e.output) + pos * es : nullptr;
+      p.count = take;
+      pieces.push_back(p);
+      pos += take;
+    }
+  }
+
+  size_t next = 0;
+  while (next < pieces.size()) {
+    // Greedy batch of pieces that fits the staging buffer and one
+    // descriptor slot.
+    DescriptorRing::Slot slot = ring_.Acquire();
+    const size_t max_n =
+        std::min<size_t>(pieces.size() - next, (slot.capacity - 4096) / 40);
+    int64_t total = 0;
+    size_t n = 0;
+    while (n < max_n) {
+      int64_t padded = RoundUp(pieces[next + n].count, align_elems);
+      if (n > 0 && total + padded > cap_elems) break;
+      total += padded;
+      ++n;
+    }
+    int64_t *d_off, *d_cnt;
+    const void** d_in;
+    void** d_out;
+    int64_t* h_off = slot.Alloc<int64_t>(n + 1, &d_off);
+    int64_t* h_cnt = slot.Alloc<int64_t>(n, &d_cnt);
+    const void** h_in = slot.Alloc<const void*>(n, &d_in);
+    void** h_out = slot.Alloc<void*>(n, &d_out);
+    if (!h_off || !h_cnt || !h_in || !h_out)
+      return Status::UnknownError("descriptor slot too small");
+    int64_t off = 0;
+    for (size_t i = 0; i < n; ++i) {
+      const Piece& p = pieces[next + i];
+      h_off[i] = off;
+      h_cnt[i] = p.count;
+      h_in[i] = p.in;
+      h_out[i] = p.out;
+      off += RoundUp(p.count, align_elems);
+    }
+    h_off[n] = off;
+    ring_.Commit(slot, stream_);
+
+    kern::TensorList list;
+    list.n = static_cast<int>(n);
+    list.offsets = d_off;
+    list.counts = d_cnt;
+    list.in = d_in;
+    list.out = d_out;
+    const int64_t bytes = off * ws;
+    cudaError_t err;
+    if (adasum && set.world > 1) {
+      kern::SymmCtx ctx = MakeCtx(set, kern::ADASUM_EPOCHS);
+      int64_t scratch_off = RoundUp(bytes, 4096);
+      err = kern::LaunchAdasum(list, dtype, response.prescale,
+                               response.postscale, scratch_off, PickCtas(bytes),
+                               ctx, stream_);
+    } else {
+      kern::Algo algo = PickAlgo(set, wire, bytes);
+      kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH);
+      err = kern::LaunchFusedAllreduce(list, dtype, adasum ? dtype : wire,
+                                       response.prescale, response.postscale,
+                                       algo, PickCtas(bytes), ctx, stream_);
+    }
+    ring_.Release(slot, stream_);
+    if (err != cudaSuccess)
+      return Status::UnknownError(std::string("fused allreduce launch failed: ") +
+                                  cudaGetErrorString(err));
+    next += n;
+  }
+  tl.ActivityEndAll(entries);
+  return Complete(entries);
+}
+
+Status GpuOps::SymmReducescatter(std::vector<TensorTableEntry>& entries,
+                                 SymmSet& set) {
+  Timeline& tl = state_.timeline;
+  WaitForInputs(entries);
+  for (auto& e : entries) {
+    const int64_t es = static_cast<int64_t>(DataTypeSize(e.dtype));
+    const int n = set.world, me = set.rank;
+    int64_t rows = e.shape.dim_size(0), slice = 1;
+    for (int d = 1; d < e.shape.dims(); ++d) slice *= e.shape.dim_size(d);
+    const int64_t base = rows / n, extra = rows % n;
+    std::vector<int64_t> dims = e.shape.to_vector();
+    dims[0] = base + (me < extra ? 1 : 0);
+    tl.ActivityStart(e.name, HVD_ACT_ALLOCATE_OUTPUT);
+    void* out = nullptr;
+    Status st = e.context->AllocateOutput(TensorShape(dims), stream_, &out);
+    tl.ActivityEnd(e.name);
+    if (!st.ok()) return st;
+    e.output = out;
+
+    DescriptorRing::Slot slot = ring_.Acquire();
+    int64_t* d_sb;
+    int64_t* h_sb = slot.Alloc<int64_t>(n + 1, &d_sb);
+    int64_t staged = 0;
+    for (int r = 0; r <= n; ++r) {
+      h_sb[r] = (r * base + std::min<int64_t>(r, extra)) * slice;
+      if (r > 0)
+        staged += RoundUp((h_sb[r] - h_sb[r - 1]) * es, STAGING_ALIGN);
+    }
+    if (staged > static_cast<int64_t>(set.data_bytes))
+      return Status::InvalidArgument(
+          "reducescatter tensor '" + e.name + "' does not fit the symmetric "
+          "staging buffer; raise HOROVOD_SYMM_BUFFER_MB.");
+    ring_.Commit(slot, stream_);
+    kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH);
+    tl.ActivityStart(e.name, HVD_ACT_FUSED_KERNEL);
+    cudaError_t err = kern::LaunchFusedReducescatter(
+        e.input, out, e.num_elements(), d_sb, e.dtype, e.prescale, e.postscale,
+        set.nvls, PickCtas(staged), ctx, stream_);
+    tl.ActivityEnd(e.name);
+    ring_.Release(slot, stream_);
+    if (err != cudaSuccess)
+      return Status::UnknownError(std::string("reducescatter launch failed: ") +
+                                  cudaGetErrorString(err));
+  }
+  return Complete(entries);
+}
+
+}  // namespace hvd

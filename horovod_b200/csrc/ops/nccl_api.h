@@ -1,0 +1,31 @@
+// Function table of the NCCL entry points used by the NCCL data path,
+// filled by dlopen/dlsym at run time.
+#pragma once
+
+#include <nccl.h>
+
+namespace hvd {
+
+struct NcclApi {
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*);
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int);
+  ncclResult_t (*CommDestroy)(ncclComm_t);
+  ncclResult_t (*CommAbort)(ncclComm_t);
+  const char* (*GetErrorString)(ncclResult_t);
+  ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t,
+                            ncclRedOp_t, ncclComm_t, cudaStream_t);
+  ncclResult_t (*Broadcast)(const void*, void*, size_t, ncclDataType_t, int,
+                            ncclComm_t, cudaStream_t);
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t,
+                            ncclComm_t, cudaStream_t);
+  ncclResult_t (*ReduceScatter)(const void*, void*, size_t, ncclDataType_t,
+                                ncclRedOp_t, ncclComm_t, cudaStream_t);
+  ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t,
+                       cudaStream_t);
+  ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t,
+                       cudaStream_t);
+  ncclResult_t (*GroupStart)();
+  ncclResult_t (*GroupEnd)();
+};
+}  // namespace hvd
+

@@ -1,0 +1,232 @@
+#include "nccl_ops.h"
+
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "../common/logging.h"
+#include "../common/process_set.h"
+#include "gpu_internal.h"
+#include "nccl_api.h"
+
+namespace hvd {
+
+namespace {
+
+const NcclApi* LoadNccl(std::string* error) {
+  static NcclApi api;
+  static bool tried = false, ok = false;
+  static std::string err;
+  if (!tried) {
+    tried = true;
+    void* lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+    if (lib == nullptr) lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (lib == nullptr) {
+      err = std::string("cannot load libnccl.so.2: ") + dlerror();
+    } else {
+      bool all = true;
+      auto sym = [&](const char* name) {
+        void* p = dlsym(lib, name);
+        if (p == nullptr) {
+          all = false;
+          err = std::string("libnccl lacks ") + name;
+        }
+        return p;
+      };
+#define HVD_NCCL_SYM(field, name) \
+  api.field = reinterpret_cast<decltype(api.field)>(sym(name))
+      HVD_NCCL_SYM(GetUniqueId, "ncclGetUniqueId");
+      HVD_NCCL_SYM(CommInitRank, "ncclCommInitRank");
+      HVD_NCCL_SYM(CommDestroy, "ncclCommDestroy");
+      HVD_NCCL_SYM(CommAbort, "ncclCommAbort");
+      HVD_NCCL_SYM(GetErrorString, "ncclGetErrorString");
+      HVD_NCCL_SYM(AllReduce, "ncclAllReduce");
+      HVD_NCCL_SYM(Broadcast, "ncclBroadcast");
+      HVD_NCCL_SYM(AllGather, "ncclAllGather");
+      HVD_NCCL_SYM(ReduceScatter, "ncclReduceScatter");
+      HVD_NCCL_SYM(Send, "ncclSend");
+      HVD_NCCL_SYM(Recv, "ncclRecv");
+      HVD_NCCL_SYM(GroupStart, "ncclGroupStart");
+      HVD_NCCL_SYM(GroupEnd, "ncclGroupEnd");
+#undef HVD_NCCL_SYM
+      ok = all;
+    }
+  }
+  if (!ok && error) *error = err;
+  return ok ? &api : nullptr;
+}
+
+#define HVD_NCCL(call)                                                        \
+  do {                                                                        \
+    ncclResult_t r_ = (call);                                                 \
+    if (r_ != ncclSuccess)                                                    \
+      throw std::runtime_error(std::string(#call) + " failed: " +             \
+                               api_->GetErrorString(r_));                     \
+  } while (0)
+
+bool NcclType(DataType t, ncclDataType_t* out) {
+  switch (t) {
+  case DataType::UINT8:
+  case DataType::BOOL: *out = ncclUint8; return true;
+  case DataType::INT8: *out = ncclInt8; return true;
+  case DataType::INT32: *out = ncclInt32; return true;
+  case DataType::INT64: *out = ncclInt64; return true;
+  case DataType::FLOAT16: *out = ncclFloat16; return true;
+  case DataType::FLOAT32: *out = ncclFloat32; return true;
+  case DataType::FLOAT64: *out = ncclFloat64; return true;
+  case DataType::BFLOAT16: *out = ncclBfloat16; return true;
+  default: return false;
+  }
+}
+
+ncclRedOp_t NcclOp(ReduceOp op, DataType t) {
+  if (t == DataType::BOOL)
+    return (op == ReduceOp::MIN || op == ReduceOp::PRODUCT) ? ncclMin : ncclMax;
+  switch (op) {
+  case ReduceOp::MIN: return ncclMin;
+  case ReduceOp::MAX: return ncclMax;
+  case ReduceOp::PRODUCT: return ncclProd;
+  default: return ncclSum;
+  }
+}
+
+}  // namespace
+
+NcclOps::NcclOps(GpuOps& gpu) : gpu_(gpu) {
+  std::string err;
+  api_ = LoadNccl(&err);
+  if (api_ == nullptr) HVD_LOG(WARNING) << "NCCL path unavailable: " << err;
+}
+
+NcclOps::~NcclOps() { Shutdown(); }
+
+void NcclOps::Shutdown() {
+  if (api_ != nullptr)
+    for (auto& kv : comms_)
+      if (kv.second) api_->CommDestroy(static_cast<ncclComm_t>(kv.second));
+  comms_.clear();
+  if (fusion_) cudaFree(fusion_);
+  fusion_ = nullptr;
+  fusion_bytes_ = 0;
+}
+
+void* NcclOps::CommFor(ProcessSet& ps) {
+  auto it = comms_.find(ps.id);
+  if (it != comms_.end()) return it->second;
+  // Rank 0 of the set creates the id; it travels over the control plane.
+  ncclUniqueId id;
+  std::memset(&id, 0, sizeof(id));
+  if (ps.comm.rank() == 0) HVD_NCCL(api_->GetUniqueId(&id));
+  ps.comm.Bcast(&id, sizeof(id), 0);
+  ncclComm_t comm = nullptr;
+  HVD_NCCL(api_->CommInitRank(&comm, ps.comm.size(), id, ps.comm.rank()));
+  ps.comm.Barrier();
+  comms_[ps.id] = comm;
+  return comm;
+}
+
+void* NcclOps::Fusion(size_t bytes) {
+  if (bytes > fusion_bytes_) {
+    if (fusion_) {
+      HVD_CUDA(cudaStreamSynchronize(gpu_.stream()));
+      cudaFree(fusion_);
+    }
+    fusion_bytes_ = std::max<size_t>(bytes, 64u << 20);
+    HVD_CUDA(cudaMalloc(&fusion_, fusion_bytes_));
+  }
+  return fusion_;
+}
+
+Status NcclOps::Execute(std::vector<TensorTableEntry>& entries,
+                        const Response& response, ProcessSet& ps) {
+  if (api_ == nullptr)
+    return Status::PreconditionError(
+        "This collective needs NCCL (symmetric memory is not usable for it) "
+        "but libnccl.so.2 could not be loaded.");
+  void* comm = CommFor(ps);
+  gpu_.WaitForInputs(entries);
+  switch (response.type) {
+  case Response::ALLREDUCE: return Allreduce(entries, response, comm);
+  case Response::BROADCAST: return Broadcast(entries, comm);
+  case Response::ALLGATHER: return Allgather(entries, response, ps, comm);
+  case Response::ALLTOALL: return Alltoall(entries, ps, comm);
+  case Response::REDUCESCATTER: return Reducescatter(entries, ps, comm);
+  case Response::ADASUM:
+    return Status::PreconditionError(
+        "Adasum on CUDA tensors runs only on the symmetric-memory backend "
+        "(one node, at most 8 ranks, fp32/fp16/bf16).");
+  default:
+    return Status::InvalidArgument("unsupported NCCL collective");
+  }
+}
+
+Status NcclOps::Allreduce(std::vector<TensorTableEntry>& entries,
+                          const Response& response, void* comm_v) {
+  ncclComm_t comm = static_cast<ncclComm_t>(comm_v);
+  cudaStream_t stream = gpu_.stream();
+  Timeline& tl = gpu_.state().timeline;
+  ncclDataType_t nt;
+  if (!NcclType(response.dtype, &nt))
+    return Status::InvalidArgument(std::string("NCCL cannot reduce dtype ") +
+                                   DataTypeName(response.dtype));
+  const ncclRedOp_t op = NcclOp(response.reduce_op, response.dtype);
+  const DataType dtype = response.dtype;
+  const int64_t es = static_cast<int64_t>(DataTypeSize(dtype));
+
+  if (entries.size() == 1 && entries[0].input && entries[0].output) {
+    TensorTableEntry& e = entries[0];
+    const void* src = e.input;
+    if (response.prescale != 1.0) {
+      kern::LaunchScaleBuffer(e.input, e.output, e.num_elements(), dtype,
+                              response.prescale, stream);
+      src = e.output;
+    }
+    tl.ActivityStart(e.name, HVD_ACT_NCCL_ALLREDUCE);
+    HVD_NCCL(api_->AllReduce(src, e.output, e.num_elements(), nt, op, comm, stream));
+    tl.ActivityEnd(e.name);
+    if (response.postscale != 1.0)
+      kern::LaunchScaleBuffer(e.output, e.output, e.num_elements(), dtype,
+                              response.postscale, stream);
+    return gpu_.Complete(entries);
+  }
+
+  // Fused: pack(+prescale) -> ncclAllReduce -> unpack(+postscale).
+  const int64_t align = FUSION_ALIGN_BYTES / es;
+  const size_t n = entries.size();
+  DescriptorRing::Slot slot = gpu_.ring().Acquire();
+  int64_t *d_off, *d_cnt;
+  const void** d_in;
+  void** d_out;
+  int64_t* h_off = slot.Alloc<int64_t>(n + 1, &d_off);
+  int64_t* h_cnt = slot.Alloc<int64_t>(n, &d_cnt);
+  const void** h_in = slot.Alloc<const void*>(n, &d_in);
+  void** h_out = slot.Alloc<void*>(n, &d_out);
+  if (!h_off || !h_cnt || !h_in || !h_out)
+    return Status::UnknownError("descriptor slot too small");
+  int64_t off = 0;
+  for (size_t i = 0; i < n; ++i) {
+    h_off[i] = off;
+    h_cnt[i] = entries[i].num_elements();
+    h_in[i] = entries[i].input;
+    h_out[i] = entries[i].output;
+    off += RoundUp(h_cnt[i], align);
+  }
+  h_off[n] = off;
+  gpu_.ring().Commit(slot, stream);
+  kern::TensorList list = {static_cast<int>(n), d_off, d_cnt, d_in, d_out};
+  void* buf = Fusion(static_cast<size_t>(off * es));
+  tl.ActivityStartAll(entries, HVD_ACT_MEMCPY_IN_FUSION_BUFFER);
+  kern::LaunchPackUnpack(list, dtype, dtype, buf, response.prescale, true, off, stream);
+  tl.ActivityEndAll(entries);
+  tl.ActivityStartAll(entries, HVD_ACT_NCCL_ALLREDUCE);
+  HVD_NCCL(api_->AllReduce(buf, buf, off, nt, op, comm, stream));
+  tl.ActivityEndAll(entries);
+  tl.ActivityStartAll(entries, HVD_ACT_MEMCPY_OUT_FUSION_BUFFER);
+  kern::LaunchPackUnpack(list, dtype, dtype, buf, response.postscale, false, off, stream);
+  tl.ActivityEndAll(entries);
+  gpu_.ring().Release(slot, stream);
+  return gpu_.Complete(entries);
+}
+
+}  // namespace hvd

@@ -1,0 +1,49 @@
+// NCCL data path for device tensors: the measured baseline (it issues the
+// same pack -> NCCL call -> unpack sequence per fused response as the
+// reference) and the fallback where symmetric memory cannot be used (more
+// than one node, more than 8 ranks, reductions other than sum, no peer
+// access). The library is opened with dlopen so nothing links against it.
+//
+// Parity: horovod/common/ops/nccl_operations.cc:65-727.
+#pragma once
+
+#include <map>
+#include <memory>
+#include <vector>
+
+#include "op_executor.h"
+
+namespace hvd {
+
+class GpuOps;
+struct NcclApi;
+
+class NcclOps {
+public:
+  explicit NcclOps(GpuOps& gpu);
+  ~NcclOps();
+  Status Execute(std::vector<TensorTableEntry>& entries,
+                 const Response& response, ProcessSet& ps);
+  void Shutdown();
+
+private:
+  void* CommFor(ProcessSet& ps);
+  void* Fusion(size_t bytes);
+  Status Allreduce(std::vector<TensorTableEntry>& entries,
+                   const Response& response, void* comm);
+  Status Broadcast(std::vector<TensorTableEntry>& entries, void* comm);
+  Status Allgather(std::vector<TensorTableEntry>& entries,
+                   const Response& response, ProcessSet& ps, void* comm);
+  Status Alltoall(std::vector<TensorTableEntry>& entries, ProcessSet& ps,
+                  void* comm);
+  Status Reducescatter(std::vector<TensorTableEntry>& entries, ProcessSet& ps,
+                       void* comm);
+
+  GpuOps& gpu_;
+  const NcclApi* api_ = nullptr;
+  std::map<int32_t, void*> comms_;
+  void* fusion_ = nullptr;
+  size_t fusion_bytes_ = 0;
+};
+
+}  // namespace hvd

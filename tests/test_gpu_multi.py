@@ -1,0 +1,159 @@
+"""Multi-GPU checks of the NVLink kernels against plain PyTorch fp32/fp64
+references computed from every rank's seeded inputs. Runs as child processes,
+one per GPU; skipped when fewer GPUs are present."""
+import os
+
+import pytest
+import torch
+
+from parallel_utils import run_parallel
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _world():
+    n = _ngpu()
+    return 8 if n >= 8 else 4 if n >= 4 else 2
+
+
+def _inputs(seed_rank, n, dtype):
+    g = torch.Generator().manual_seed(1000 + seed_rank)
+    if dtype.is_floating_point:
+        return torch.randn(n, generator=g, dtype=torch.float32).to(dtype)
+    return torch.randint(-50, 50, (n,), generator=g).to(dtype)
+
+
+def _collectives(rank, size, algo):
+    os.environ["HOROVOD_ALLREDUCE_ALGO"] = algo
+    os.environ["HOROVOD_SPIN_TIMEOUT_MS"] = "5000"
+    import horovod_b200.torch as hvd
+    from horovod_b200 import _C
+    hvd.init()
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    report = {}
+    sizes = [1, 17, 4096, 100003, (1 << 20) + 5]
+    for dtype in (torch.float32, torch.bfloat16, torch.float16, torch.int32, torch.float64):
+        for n in sizes:
+            if algo == "nvls" and dtype in (torch.int32, torch.float64):
+                continue
+            x = _inputs(rank, n, dtype).to(dev)
+            out = hvd.allreduce(x, op=hvd.Sum, name="ar.%s.%d" % (dtype, n))
+            ref = sum(_inputs(r, n, dtype).double() for r in range(size))
+            tol = {torch.float32: 1e-5, torch.float64: 1e-12, torch.int32: 0,
+                   torch.bfloat16: 4e-2, torch.float16: 8e-3}[dtype]
+            err = (out.double().cpu() - ref).abs().max().item()
+            scale = max(1.0, ref.abs().max().item())
+            assert err <= tol * scale * size, (str(dtype), n, err)
+    # Average with pre/post scale over a fused group of odd-sized tensors.
+    shapes = [3, 129, 2048, 77777, 5]
+    xs = [_inputs(rank * 31 + i, s, torch.float32).to(dev) for i, s in enumerate(shapes)]
+    outs = hvd.grouped_allreduce(xs, op=hvd.Average, name="grp")
+    for i, (s, o) in enumerate(zip(shapes, outs)):
+        ref = sum(_inputs(r * 31 + i, s, torch.float32).double() for r in range(size)) / size
+        assert (o.double().cpu() - ref).abs().max().item() < 1e-5
+    # allgather with a different dim 0 on every rank
+    rows = rank + 1
+    ag = hvd.allgather(torch.full((rows, 3), float(rank), device=dev), name="ag")
+    exp = torch.cat([torch.full((r + 1, 3), float(r)) for r in range(size)])
+    assert torch.equal(ag.cpu(), exp)
+    # broadcast from the last rank, odd length
+    b = torch.arange(1001, device=dev, dtype=torch.float32) * (rank + 1)
+    hvd.broadcast_(b, root_rank=size - 1, name="bc")
+    assert torch.equal(b.cpu(), torch.arange(1001, dtype=torch.float32) * size)
+    # alltoall with uneven splits: rank r sends (p + 1) rows to rank p
+    splits = [p + 1 for p in range(size)]
+    src = torch.cat([torch.full((p + 1, 2), float(rank * 100 + p)) for p in range(size)]).to(dev)
+    out, recv = hvd.alltoall(src, splits=splits, name="a2a")
+    assert recv.tolist() == [rank + 1] * size
+    exp = torch.cat([torch.full((rank + 1, 2), float(r * 100 + rank)) for r in range(size)])
+    assert torch.equal(out.cpu(), exp)
+    # reducescatter with ragged shards
+    rs_rows = 2 * size + 1
+    x = _inputs(rank + 500, rs_rows * 5, torch.float32).view(rs_rows, 5).to(dev)
+    out = hvd.reducescatter(x, op=hvd.Sum, name="rs")
+    full = sum(_inputs(r + 500, rs_rows * 5, torch.float32).view(rs_rows, 5).double()
+               for r in range(size))
+    base, extra = divmod(rs_rows, size)
+    start = rank * base + min(rank, extra)
+    mine = full[start:start + base + (1 if rank < extra else 0)]
+    assert (out.double().cpu() - mine).abs().max().item() < 1e-5
+    report["backend"] = hvd.gpu_backend()
+    report["launches"] = _C.kernel_launch_count()
+    torch.cuda.synchronize()
+    hvd.shutdown()
+    return report
+
+
+@pytest.mark.parametrize("algo", ["auto", "oneshot", "twoshot", "nvls"])
+def test_collectives_against_reference(algo):
+    out = run_parallel(_collectives, np=_world(), args=(algo,), timeout=300)
+    for rep in out:
+        assert rep["backend"].startswith("symm"), rep["backend"]
+        assert rep["launches"] > 0
+
+
+def _adasum(rank, size):
+    os.environ["HOROVOD_SPIN_TIMEOUT_MS"] = "5000"
+    import horovod_b200.torch as hvd
+    hvd.init()
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+
+    def oracle(vs):
+        vs = [v.double() for v in vs]
+        while len(vs) > 1:
+            nxt = []
+            for i in range(0, len(vs), 2):
+                a, b = vs[i], vs[i + 1]
+                dot, na, nb = (a * b).sum(), (a * a).sum(), (b * b).sum()
+                ca = 1 - dot / (2 * na) if na > 0 else 1.0
+                cb = 1 - dot / (2 * nb) if nb > 0 else 1.0
+                nxt.append(ca * a + cb * b)
+            vs = nxt
+        return vs[0]
+
+    shapes = [5, 1000, 33333]
+    xs = [_inputs(rank * 7 + i, s, torch.float32).to(dev) for i, s in enumerate(shapes)]
+    outs = hvd.grouped_allreduce(xs, op=hvd.Adasum, name="adasum")
+    for i, (s, o) in enumerate(zip(shapes, outs)):
+        ref = oracle([_inputs(r * 7 + i, s, torch.float32) for r in range(size)])
+        assert (o.double().cpu() - ref).abs().max().item() < 1e-4, (s,)
+    # identical inputs combine to the same vector (average-like behaviour)
+    same = torch.arange(64, dtype=torch.float32, device=dev) + 1
+    o = hvd.allreduce(same, op=hvd.Adasum, name="adasum.same")
+    assert (o - same).abs().max().item() < 1e-4
+    torch.cuda.synchronize()
+    hvd.shutdown()
+    return True
+
+
+def test_adasum_matches_pairwise_oracle():
+    assert all(run_parallel(_adasum, np=_world(), timeout=300))
+
+
+def _nccl_backend(rank, size):
+    os.environ["HOROVOD_GPU_BACKEND"] = "nccl"
+    import horovod_b200.torch as hvd
+    hvd.init()
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    xs = [torch.full((n,), float(rank + 1), device=dev) for n in (7, 4096, 100001)]
+    outs = hvd.grouped_allreduce(xs, op=hvd.Sum, name="g")
+    tot = float(sum(range(1, size + 1)))
+    ok = all(bool((o == tot).all()) for o in outs)
+    m = hvd.allreduce(torch.full((9,), float(rank), device=dev), op=hvd.Max, name="max")
+    ok = ok and bool((m == size - 1).all())
+    backend = hvd.gpu_backend()
+    torch.cuda.synchronize()
+    hvd.shutdown()
+    return ok, backend
+
+
+def test_nccl_baseline_path():
+    for ok, backend in run_parallel(_nccl_backend, np=2, timeout=300):
+        assert ok and backend.startswith("nccl")

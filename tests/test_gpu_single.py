@@ -1,0 +1,92 @@
+"""Single-GPU checks of the device path through the public API: with one
+rank every collective still runs the library's own kernels (the LOCAL
+variants), so packing, scaling, casting and scattering are exercised."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def hvd():
+    import horovod_b200.torch as hvd
+    hvd.init()
+    torch.cuda.set_device(0)
+    yield hvd
+    hvd.shutdown()
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16,
+                                   torch.float64, torch.int32, torch.int64])
+@pytest.mark.parametrize("n", [1, 15, 16, 17, 1000, 1 << 20])
+def test_allreduce_identity_and_scale(hvd, dtype, n):
+    from horovod_b200 import _C
+    x = (torch.arange(n, device=_dev()) % 97).to(dtype)
+    before = _C.kernel_launch_count()
+    y = hvd.allreduce(x, op=hvd.Sum, name="s.%s.%d" % (dtype, n))
+    assert _C.kernel_launch_count() > before, "native kernel did not run"
+    assert torch.equal(y, x)
+    if dtype.is_floating_point:
+        z = hvd.allreduce(x, op=hvd.Sum, prescale_factor=0.5, postscale_factor=4.0,
+                          name="p.%s.%d" % (dtype, n))
+        ref = (x.float() * 0.5).to(dtype).float() * 4.0 if dtype != torch.float64 else x * 2.0
+        torch.testing.assert_close(z.float(), ref.float().to(z.device), rtol=1e-2, atol=1e-2)
+
+
+def test_grouped_allreduce_many_odd_tensors(hvd):
+    torch.manual_seed(0)
+    sizes = [1, 3, 17, 255, 256, 257, 4099, 65537] * 20 + [1 << 20]
+    xs = [torch.randn(s, device=_dev()) for s in sizes]
+    # odd alignments: views that start 4 bytes into an allocation
+    xs += [torch.randn(1001, device=_dev())[1:] for _ in range(5)]
+    ys = hvd.grouped_allreduce([x.contiguous() for x in xs], op=hvd.Average, name="grp")
+    for x, y in zip(xs, ys):
+        torch.testing.assert_close(y, x, rtol=0, atol=0)
+
+
+def test_inplace_and_async(hvd):
+    x = torch.randn(12345, device=_dev())
+    ref = x.clone()
+    h = hvd.allreduce_async_(x, op=hvd.Sum, postscale_factor=3.0, name="inplace")
+    out = hvd.synchronize(h)
+    assert out.data_ptr() == x.data_ptr()
+    torch.testing.assert_close(x, ref * 3.0)
+
+
+def test_other_collectives_single_rank(hvd):
+    x = torch.randn(7, 5, device=_dev())
+    torch.testing.assert_close(hvd.allgather(x, name="ag"), x)
+    torch.testing.assert_close(hvd.broadcast(x, 0, name="bc"), x)
+    torch.testing.assert_close(hvd.alltoall(x, name="a2a"), x)
+    out, splits = hvd.alltoall(x, splits=[7], name="a2a.s")
+    torch.testing.assert_close(out, x)
+    assert splits.tolist() == [7]
+    torch.testing.assert_close(hvd.reducescatter(x, op=hvd.Sum, name="rs"), x)
+
+
+def test_compression_and_optimizer_step(hvd, monkeypatch):
+    monkeypatch.setenv("HOROVOD_FORCE_HOOKS", "1")
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(64, 32), torch.nn.ReLU(),
+                                torch.nn.Linear(32, 4)).to(_dev())
+    ref = torch.nn.Sequential(torch.nn.Linear(64, 32), torch.nn.ReLU(),
+                              torch.nn.Linear(32, 4)).to(_dev())
+    ref.load_state_dict(model.state_dict())
+    opt = hvd.DistributedOptimizer(torch.optim.SGD(model.parameters(), lr=0.1),
+                                   named_parameters=model.named_parameters())
+    ropt = torch.optim.SGD(ref.parameters(), lr=0.1)
+    x = torch.randn(16, 64, device=_dev())
+    y = torch.randint(0, 4, (16,), device=_dev())
+    for _ in range(3):
+        for m, o in ((model, opt), (ref, ropt)):
+            o.zero_grad()
+            torch.nn.functional.cross_entropy(m(x), y).backward()
+            o.step()
+    for a, b in zip(model.parameters(), ref.parameters()):
+        torch.testing.assert_close(a, b, rtol=1e-6, atol=1e-6)
+
+

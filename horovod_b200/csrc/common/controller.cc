@@ -116,6 +116,13 @@ ResponseList Controller::ComputeResponseList(bool shutdown_requested,
   result.shutdown = cc.should_shut_down() || (!cache_on && should_shut_down);
 
   const bool need_communication = !(cache_on && !cc.uncached_in_queue());
+  if (!msgs.empty() || !cc.cache_hits().empty())
+    HVD_LOG_RANK(TRACE, comm_->global_ranks()[comm_->rank()])
+        << "negotiate: " << msgs.size() << " uncached request(s), "
+        << cc.cache_hits().size() << " common cache hit(s), "
+        << cache_.num_active_bits() << " cache bit(s), "
+        << (need_communication ? "coordinator round" : "cache fast path")
+        << (join.joined ? ", joined" : "");
 
   if (!need_communication) {
     if (cc.cache_hits().empty()) return result;

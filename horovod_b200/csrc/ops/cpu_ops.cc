@@ -70,6 +70,9 @@ private:
       counts[i] = entries[i].num_elements();
       total += RoundUp(counts[i], align_elems);
     }
+    // A lone tensor is reduced without padding, on every rank alike (a rank
+    // that joined has no output pointer but must send the same byte count).
+    if (entries.size() == 1) total = counts[0];
     void* buf;
     bool in_place = entries.size() == 1 && entries[0].output != nullptr;
     if (in_place) {
@@ -77,7 +80,6 @@ private:
       if (e.input != nullptr && e.input != e.output)
         std::memcpy(e.output, e.input, static_cast<size_t>(counts[0] * es));
       buf = e.output;
-      total = counts[0];
     } else {
       tl.ActivityStartAll(entries, HVD_ACT_MEMCPY_IN_FUSION_BUFFER);
       fusion_.assign(static_cast<size_t>(total * es), 0);

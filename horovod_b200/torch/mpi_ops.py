@@ -135,7 +135,7 @@ class HorovodAllreduce(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output):
-        return (allreduce(grad_output, average=ctx.average, op=ctx.op,
+        return (allreduce(grad_output.contiguous(), average=ctx.average, op=ctx.op,
                           prescale_factor=ctx.prescale_factor,
                           postscale_factor=ctx.postscale_factor,
                           process_set=ctx.process_set),
@@ -211,7 +211,8 @@ class HorovodGroupedAllreduce(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, *grad_output):
-        grads = grouped_allreduce(list(grad_output), average=ctx.average, op=ctx.op,
+        grads = grouped_allreduce([g.contiguous() for g in grad_output],
+                                  average=ctx.average, op=ctx.op,
                                   prescale_factor=ctx.prescale_factor,
                                   postscale_factor=ctx.postscale_factor,
                                   process_set=ctx.process_set)
@@ -283,7 +284,7 @@ class HorovodAllgather(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         ps = ctx.process_set
-        grad_reduced = allreduce(grad_output, average=True, process_set=ps)
+        grad_reduced = allreduce(grad_output.contiguous(), average=True, process_set=ps)
         dim_t = torch.tensor([ctx.dim], dtype=torch.int64)
         dims = allgather(dim_t, process_set=ps).view(-1)
         r = ps.rank() if ps is not None else rank()
@@ -320,7 +321,8 @@ class HorovodBroadcast(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output):
-        grad_reduced = allreduce(grad_output, average=True, process_set=ctx.process_set)
+        grad_reduced = allreduce(grad_output.contiguous(), average=True,
+                                 process_set=ctx.process_set)
         if rank() != ctx.root_rank:
             grad_reduced *= 0
         return grad_reduced, None, None, None
@@ -377,7 +379,8 @@ class HorovodAlltoall(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output, *dead_gradients):
-        out = alltoall(grad_output, splits=ctx.recvsplits, process_set=ctx.process_set)
+        out = alltoall(grad_output.contiguous(), splits=ctx.recvsplits,
+                       process_set=ctx.process_set)
         grad = out[0] if isinstance(out, tuple) else out
         return grad, None, None, None
 

@@ -8,6 +8,20 @@ import traceback
 from horovod_b200.runner.http.http_server import RendezvousServer
 
 
+def _plain(obj):
+    """Tensors travel back as numpy arrays (no shared-memory handles that die
+    with the child)."""
+    import torch
+    if isinstance(obj, torch.Tensor):
+        t = obj.detach().cpu()
+        return t.float().numpy() if t.dtype in (torch.bfloat16, torch.float16) else t.numpy()
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_plain(o) for o in obj)
+    if isinstance(obj, dict):
+        return {k: _plain(v) for k, v in obj.items()}
+    return obj
+
+
 def _child(fn, rank, size, port, env, args, q):
     try:
         os.environ.update({
@@ -22,7 +36,7 @@ def _child(fn, rank, size, port, env, args, q):
         import torch
         torch.set_num_threads(1)
         result = fn(rank, size, *args)
-        q.put((rank, "ok", result))
+        q.put((rank, "ok", _plain(result)))
     except BaseException:
         q.put((rank, "error", traceback.format_exc()))
 

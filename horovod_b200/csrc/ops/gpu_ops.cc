@@ -356,7 +356,15 @@ void GpuOps::Shutdown() {
   nccl_.reset();
   sets_.clear();
   // Every rank reaches this point through the coordinated shutdown, after
-  // its last kernel finished, so nobody is touching peer mappings any more.
+  // its last kernel finished. Meet once more on the control plane so that
+  // no rank unmaps memory a slower peer's last kernel may still read; if a
+  // peer is gone already there is nobody left to protect.
+  if (arena_.valid() && state_.config.size > 1) {
+    try {
+      state_.process_sets.Get(0).comm.Barrier();
+    } catch (const std::exception&) {
+    }
+  }
   arena_.Destroy();
   ring_.Destroy();
   if (status_host_) cudaFreeHost(status_host_);

@@ -230,11 +230,22 @@ std::string NameOrDefault(const std::string& name, const char* op, int handle) {
   return std::string(op) + ".noname." + std::to_string(handle);
 }
 
-TensorTableEntry MakeEntry(const at::Tensor& input, const at::Tensor* output,
-                           const std::shared_ptr<HandleRecord>& rec) {
-  if (!input.is_contiguous())
+// Element-wise collectives accept any dense layout (e.g. channels_last) as
+// long as the output has the same strides; the others need row-major.
+void CheckLayout(const at::Tensor& input, const at::Tensor* output,
+                 bool dense_ok) {
+  bool ok = input.is_contiguous() ||
+            (dense_ok && input.is_non_overlapping_and_dense() &&
+             (output == nullptr || output->strides() == input.strides()));
+  if (!ok)
     throw std::invalid_argument(
         "Horovod collectives need contiguous tensors; call .contiguous().");
+}
+
+TensorTableEntry MakeEntry(const at::Tensor& input, const at::Tensor* output,
+                           const std::shared_ptr<HandleRecord>& rec,
+                           bool dense_ok = false) {
+  CheckLayout(input, output, dense_ok);
   TensorTableEntry e;
   e.input = input.data_ptr();
   e.output = output ? output->data_ptr() : nullptr;
@@ -265,7 +276,7 @@ int AllreduceAsync(const at::Tensor& tensor, const at::Tensor& output,
   int handle = Handles().Allocate(rec);
   std::vector<TensorTableEntry> entries;
   try {
-    entries.push_back(MakeEntry(tensor, &output, rec));
+    entries.push_back(MakeEntry(tensor, &output, rec, /*dense_ok=*/true));
   } catch (...) {
     Handles().Release(handle);
     throw;
@@ -304,9 +315,7 @@ int GroupedAllreduceAsync(const std::vector<at::Tensor>& tensors,
         throw std::invalid_argument(
             "grouped_allreduce: all tensors must be on the same device");
       TensorTableEntry e;
-      if (!tensors[i].is_contiguous())
-        throw std::invalid_argument(
-            "Horovod collectives need contiguous tensors; call .contiguous().");
+      CheckLayout(tensors[i], &outputs[i], /*dense_ok=*/true);
       e.input = tensors[i].data_ptr();
       e.output = outputs[i].data_ptr();
       e.shape = TensorShape(tensors[i].sizes().vec());
@@ -360,7 +369,7 @@ int BroadcastAsync(const at::Tensor& tensor, const at::Tensor& output,
   int handle = Handles().Allocate(rec);
   TensorTableEntry e;
   try {
-    e = MakeEntry(tensor, &output, rec);
+    e = MakeEntry(tensor, &output, rec, /*dense_ok=*/true);
   } catch (...) {
     Handles().Release(handle);
     throw;

@@ -68,13 +68,22 @@ handle_average_backwards_compatibility = get_average_backwards_compatibility_fun
 _handle_map = {}
 
 
-def _check_tensor(tensor):
+def _is_dense(tensor):
+    """Contiguous in some memory format (e.g. channels_last): element-wise
+    collectives only need the same dense layout on every rank."""
+    return (tensor.is_contiguous()
+            or (tensor.dim() == 4 and tensor.is_contiguous(memory_format=torch.channels_last))
+            or (tensor.dim() == 5
+                and tensor.is_contiguous(memory_format=torch.channels_last_3d)))
+
+
+def _check_tensor(tensor, dense_ok=False):
     if not isinstance(tensor, torch.Tensor):
         raise ValueError("Horovod collectives need torch tensors, got %s" % type(tensor))
     if tensor.is_sparse:
         raise ValueError("Sparse tensors are not supported by this op; use "
                          "sparse_allreduce_async or sparse_as_dense=True.")
-    if not tensor.is_contiguous():
+    if not (tensor.is_contiguous() or (dense_ok and _is_dense(tensor))):
         raise ValueError("Horovod collectives need contiguous tensors; "
                          "call .contiguous() first.")
 
@@ -93,7 +102,7 @@ def _scaled_op(op, prescale_factor, postscale_factor):
 
 
 def _allreduce_async(tensor, output, name, op, prescale_factor, postscale_factor, process_set):
-    _check_tensor(tensor)
+    _check_tensor(tensor, dense_ok=True)
     _check_adasum(op, process_set)
     if op == Average and not (tensor.is_floating_point() or tensor.is_complex()):
         # Integer averaging: sum on the wire, floor-divide afterwards, as the
@@ -114,7 +123,7 @@ def allreduce_async(tensor, average=None, name=None, op=None, prescale_factor=1.
     """Starts an allreduce of ``tensor`` into a new tensor and returns a
     handle for poll() / synchronize()."""
     op = handle_average_backwards_compatibility(op, average)
-    output = tensor.new_empty(tensor.shape)
+    output = torch.empty_like(tensor)
     return _allreduce_async(tensor, output, name, op, prescale_factor, postscale_factor,
                             process_set)
 
@@ -172,7 +181,7 @@ def allreduce_(tensor, average=None, name=None, op=None, prescale_factor=1.0,
 def _grouped_allreduce_async(tensors, outputs, name, op, prescale_factor, postscale_factor,
                              process_set):
     for t in tensors:
-        _check_tensor(t)
+        _check_tensor(t, dense_ok=True)
     _check_adasum(op, process_set)
     int_avg = op == Average and any(not t.is_floating_point() for t in tensors)
     wire_op = Sum if int_avg else op
@@ -191,7 +200,7 @@ def grouped_allreduce_async(tensors, average=None, name=None, op=None, prescale_
                             postscale_factor=1.0, process_set=global_process_set):
     """Allreduce of a list of tensors negotiated and fused as one unit."""
     op = handle_average_backwards_compatibility(op, average)
-    outputs = [t.new_empty(t.shape) for t in tensors]
+    outputs = [torch.empty_like(t) for t in tensors]
     return _grouped_allreduce_async(tensors, outputs, name, op, prescale_factor,
                                     postscale_factor, process_set)
 
@@ -298,7 +307,7 @@ def allgather(tensor, name=None, process_set=global_process_set):
 
 
 def _broadcast_async(tensor, output, root_rank, name, process_set):
-    _check_tensor(tensor)
+    _check_tensor(tensor, dense_ok=True)
     handle = _C.broadcast_async(tensor, output, int(root_rank), name or "",
                                 _resolve(process_set))
     _handle_map[handle] = ("broadcast", None)
@@ -307,7 +316,7 @@ def _broadcast_async(tensor, output, root_rank, name, process_set):
 
 def broadcast_async(tensor, root_rank, name=None, process_set=global_process_set):
     """Starts broadcasting ``tensor`` from global rank ``root_rank``."""
-    output = tensor.new_empty(tensor.shape)
+    output = torch.empty_like(tensor)
     return _broadcast_async(tensor, output, root_rank, name, process_set)
 
 

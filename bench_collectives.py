@@ -1,0 +1,137 @@
+"""Collective sweep: allreduce (fp32, bf16), reducescatter, allgather,
+broadcast and alltoall on one tensor from 1 KB to 1 GB in powers of two, plus
+a grouped allreduce of 64 fp32 tensors with log-uniform sizes in 4 KB-4 MB.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 \
+        --master-addr 127.0.0.1 --master-port 29500 bench_collectives.py \
+        --backend symm --max-mb 1024
+
+Every number is device time of the whole response on the communication
+stream (CUDA events around the launches, after the producer wait), maximum
+over ranks, median over iterations. ``--backend nccl`` runs the same harness
+over the NCCL path (pack -> NCCL -> unpack as the reference issues it), which
+is the baseline of the comparison. Bus bandwidth follows the usual
+conventions: allreduce 2(N-1)/N * S / t, reducescatter/allgather (N-1)/N * S_total / t,
+broadcast S / t, alltoall (N-1)/N * S / t. The roofline for each op is its
+bytes over NVLink at the measured 770 GB/s per direction per GPU.
+Rank 0 prints one JSON line per (op, dtype, size).
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+
+ALLREDUCE, ALLGATHER, BROADCAST, ALLTOALL, REDUCESCATTER = 0, 1, 2, 5, 6
+LINK_GBS = 770.0
+
+
+def main():
+    p = argparse.ArgumentParser()
+    p.add_argument("--backend", default="symm", choices=["symm", "nccl"])
+    p.add_argument("--min-kb", type=int, default=1)
+    p.add_argument("--max-mb", type=int, default=256)
+    p.add_argument("--iters", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--ops", default="allreduce,allreduce_bf16,reducescatter,allgather,"
+                                    "broadcast,alltoall,grouped")
+    p.add_argument("--algo", default=None, help="force oneshot|twoshot|nvls")
+    p.add_argument("--ctas", type=int, default=0)
+    args = p.parse_args()
+
+    os.environ["HOROVOD_GPU_BACKEND"] = args.backend
+    os.environ["HOROVOD_GPU_OP_TIMING"] = "1"
+    os.environ["HOROVOD_FUSION_THRESHOLD"] = str(256 << 20)
+    if args.algo:
+        os.environ["HOROVOD_ALLREDUCE_ALGO"] = args.algo
+    if args.ctas:
+        os.environ["HOROVOD_COMM_CTAS"] = str(args.ctas)
+
+    import torch
+    import horovod_b200.torch as hvd
+    from horovod_b200 import _C
+
+    hvd.init()
+    n, rank = hvd.size(), hvd.rank()
+    torch.cuda.set_device(hvd.local_rank())
+    dev = torch.device("cuda", hvd.local_rank())
+    torch.manual_seed(rank)
+
+    def measure(fn, want_type):
+        """Runs fn() warmup+iters times, one response at a time, and returns
+        the median device time (us, max over ranks) of the matching ops."""
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        _C.gpu_op_stats()
+        for _ in range(args.iters):
+            fn()
+        torch.cuda.synchronize()
+        mine = [t[3] for t in _C.gpu_op_stats() if t[0] == want_type]
+        mine = mine[-args.iters:]
+        t = torch.tensor(mine, dtype=torch.float64)
+        t = hvd.allreduce(t, op=hvd.Max, name="sweep.times.%d" % len(mine))
+        return statistics.median(t.tolist())
+
+    def emit(op, dtype, nbytes, us, bus_factor, wire_bytes):
+        if rank != 0:
+            return
+        bus = nbytes * bus_factor / (us * 1e-6) / 1e9 if us > 0 else 0.0
+        roof_us = wire_bytes / (LINK_GBS * 1e9) * 1e6
+        print(json.dumps({"op": op, "dtype": dtype, "bytes": nbytes, "n_gpus": n,
+                          "backend": args.backend, "device_us": round(us, 2),
+                          "bus_gbs": round(bus, 2),
+                          "roofline_us": round(roof_us, 2),
+                          "frac_of_nvlink_roofline": round(roof_us / us, 4) if us > 0 else None,
+                          "gradient_path": hvd.gpu_backend()}), flush=True)
+
+    ops = args.ops.split(",")
+    sizes = []
+    s = args.min_kb << 10
+    while s <= args.max_mb << 20:
+        sizes.append(s)
+        s <<= 1
+
+    for nbytes in sizes:
+        if "allreduce" in ops:
+            x = torch.randn(nbytes // 4, device=dev)
+            us = measure(lambda: hvd.allreduce_(x, op=hvd.Sum, name="sw.ar"), ALLREDUCE)
+            emit("allreduce", "fp32", nbytes, us, 2 * (n - 1) / n, nbytes * (n - 1) / n)
+        if "allreduce_bf16" in ops:
+            x = torch.randn(nbytes // 2, device=dev).bfloat16()
+            us = measure(lambda: hvd.allreduce_(x, op=hvd.Sum, name="sw.arb"), ALLREDUCE)
+            emit("allreduce", "bf16", nbytes, us, 2 * (n - 1) / n, nbytes * (n - 1) / n)
+        if "reducescatter" in ops and nbytes >= 4 * n:
+            x = torch.randn(nbytes // 4 // n * n, device=dev)
+            us = measure(lambda: hvd.reducescatter(x, op=hvd.Sum, name="sw.rs"), REDUCESCATTER)
+            emit("reducescatter", "fp32", nbytes, us, (n - 1) / n, nbytes * (n - 1) / n)
+        if "allgather" in ops and nbytes // n >= 4:
+            x = torch.randn(nbytes // 4 // n, device=dev)
+            us = measure(lambda: hvd.allgather(x, name="sw.ag"), ALLGATHER)
+            emit("allgather", "fp32", nbytes, us, (n - 1) / n, nbytes * (n - 1) / n)
+        if "broadcast" in ops:
+            x = torch.randn(nbytes // 4, device=dev)
+            us = measure(lambda: hvd.broadcast_(x, root_rank=0, name="sw.bc"), BROADCAST)
+            emit("broadcast", "fp32", nbytes, us, 1.0, nbytes)
+        if "alltoall" in ops and nbytes // n >= 4:
+            x = torch.randn(nbytes // 4 // n * n, device=dev)
+            us = measure(lambda: hvd.alltoall(x, name="sw.a2a"), ALLTOALL)
+            emit("alltoall", "fp32", nbytes, us, (n - 1) / n, nbytes * (n - 1) / n)
+
+    if "grouped" in ops:
+        g = torch.Generator().manual_seed(0)
+        import math
+        logs = torch.rand(64, generator=g) * (math.log(4 << 20) - math.log(4 << 10)) \
+            + math.log(4 << 10)
+        counts = [max(1, int(math.exp(v)) // 4) for v in logs.tolist()]
+        xs = [torch.randn(c, device=dev) for c in counts]
+        total = sum(c * 4 for c in counts)
+        us = measure(lambda: hvd.grouped_allreduce_(xs, op=hvd.Sum, name="sw.grp"), ALLREDUCE)
+        emit("grouped_allreduce_64", "fp32", total, us, 2 * (n - 1) / n, total * (n - 1) / n)
+
+    hvd.shutdown()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -115,9 +115,11 @@ def _layout_from_env():
             raise RuntimeError("HOROVOD_RANK/SIZE are set but the rendezvous "
                                "address HOROVOD_GLOO_RENDEZVOUS_ADDR/PORT is not.")
         kv = _HttpKV(addr, port)
-        if env.get("HOROVOD_ELASTIC") == "1":
-            # Elastic jobs ask the driver for their place on every (re)init;
-            # the request blocks until all live workers have arrived.
+        if env.get("HOROVOD_ELASTIC") == "1" and _GENERATION[0] > 0:
+            # Re-initialisation inside an elastic job: ask the driver for this
+            # worker's new place. The request blocks until every worker that
+            # survived the previous round has asked. (A freshly spawned worker
+            # instead uses the layout and round number it was started with.)
             host = env.get("HOROVOD_HOSTNAME", socket.gethostname())
             key = "%s:%s" % (host, env.get("HOROVOD_LOCAL_RANK", "0"))
             timeout = float(env.get("HOROVOD_ELASTIC_TIMEOUT", "600"))
@@ -131,6 +133,8 @@ def _layout_from_env():
             for n in names:
                 os.environ["HOROVOD_" + n.upper()] = str(layout[n])
             scope = "global_%d" % (vals[6] if len(vals) > 6 else 0)
+        elif env.get("HOROVOD_ELASTIC") == "1":
+            scope = "global_%s" % env.get("HOROVOD_ELASTIC_ROUND", "0")
         else:
             scope = "global"
         advertise = _route_ip(addr, port)

@@ -168,3 +168,4 @@ cudaError_t LaunchFusedReducescatter(const void* in, void* out, int64_t count,
 
 }  // namespace kern
 }  // namespace hvd
+

@@ -111,6 +111,16 @@ public:
   struct OutSeg { const void* src; int64_t staging_off; int64_t bytes; int32_t dst; };
   struct InSeg { void* dst; int64_t staging_off; int64_t bytes; };
 
+  // Device-time record of one executed response (HOROVOD_GPU_OP_TIMING=1).
+  struct OpTiming {
+    int type;        // Response::Type
+    int64_t bytes;   // payload bytes of the response on this rank
+    int tensors;
+    float device_us;
+  };
+  // Waits for the recorded ops to finish and returns (and clears) the list.
+  std::vector<OpTiming> DrainTimings();
+
   // Used by the NCCL path.
   cudaStream_t stream() const { return stream_; }
   DescriptorRing& ring() { return ring_; }
@@ -160,7 +170,22 @@ private:
   std::map<int32_t, std::unique_ptr<SymmSet>> sets_;
   std::unique_ptr<NcclOps> nccl_;
   bool shut_down_ = false;
+
+  struct PendingTiming {
+    cudaEvent_t t0, t1;
+    int type;
+    int64_t bytes;
+    int tensors;
+  };
+  bool timing_ = false;
+  std::mutex timing_mu_;
+  std::vector<PendingTiming> pending_timings_;
+  std::vector<cudaEvent_t> timing_events_;  // free list
 };
+
+// The executor of the running job (null when there is none); used by the
+// diagnostics binding.
+GpuOps* CurrentGpuOps();
 
 // Published for diagnostics.
 void SetGpuBackendDescription(const std::string& s);

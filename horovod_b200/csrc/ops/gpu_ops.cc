@@ -1,6 +1,7 @@
 #include "gpu_ops.h"
 
 #include <algorithm>
+#include <atomic>
 #include <cstring>
 
 #include "../common/env.h"
@@ -14,7 +15,10 @@ namespace hvd {
 namespace {
 std::mutex g_desc_mu;
 std::string g_backend_desc = "none";
+std::atomic<GpuOps*> g_current{nullptr};
 }  // namespace
+
+GpuOps* CurrentGpuOps() { return g_current.load(); }
 
 void SetGpuBackendDescription(const std::string& s) {
   std::lock_guard<std::mutex> l(g_desc_mu);
@@ -121,6 +125,8 @@ GpuOps::GpuOps(GlobalState& s) : state_(s), events_(new DoneEventPool()) {
   nvls_min_ = EnvInt(HVD_ENV_NVLS_MIN, 512 * 1024);
   forced_ctas_ = static_cast<int>(EnvInt(HVD_ENV_COMM_CTAS, 0));
   forced_algo_ = EnvString(HVD_ENV_ALGO, "auto");
+  timing_ = EnvBool("HOROVOD_GPU_OP_TIMING", false);
+  g_current = this;
 }
 
 GpuOps::~GpuOps() { Shutdown(); }
@@ -329,6 +335,32 @@ Status GpuOps::Execute(std::vector<TensorTableEntry>& entries,
       break;
     }
   }
+  PendingTiming pt = {nullptr, nullptr, static_cast<int>(response.type), 0,
+                      static_cast<int>(entries.size())};
+  if (timing_) {
+    for (auto& e : entries) pt.bytes += e.size_bytes();
+    WaitForInputs(entries);  // producer wait must not count as op time
+    std::lock_guard<std::mutex> l(timing_mu_);
+    for (cudaEvent_t* ev : {&pt.t0, &pt.t1}) {
+      if (!timing_events_.empty()) {
+        *ev = timing_events_.back();
+        timing_events_.pop_back();
+      } else {
+        HVD_CUDA(cudaEventCreate(ev));
+      }
+    }
+    HVD_CUDA(cudaEventRecord(pt.t0, stream_));
+  }
+  struct TimingCloser {
+    GpuOps* self;
+    PendingTiming* pt;
+    ~TimingCloser() {
+      if (pt->t1 == nullptr) return;
+      cudaEventRecord(pt->t1, self->stream_);
+      std::lock_guard<std::mutex> l(self->timing_mu_);
+      self->pending_timings_.push_back(*pt);
+    }
+  } closer{this, &pt};
   if (use_symm) {
     switch (response.type) {
     case Response::ALLREDUCE: return SymmAllreduce(entries, response, *set, false);
@@ -344,9 +376,32 @@ Status GpuOps::Execute(std::vector<TensorTableEntry>& entries,
   return nccl_->Execute(entries, response, ps);
 }
 
+std::vector<GpuOps::OpTiming> GpuOps::DrainTimings() {
+  std::vector<PendingTiming> pending;
+  {
+    std::lock_guard<std::mutex> l(timing_mu_);
+    pending.swap(pending_timings_);
+  }
+  std::vector<OpTiming> out;
+  for (auto& p : pending) {
+    OpTiming t = {p.type, p.bytes, p.tensors, 0.f};
+    float ms = 0.f;
+    if (cudaEventSynchronize(p.t1) == cudaSuccess &&
+        cudaEventElapsedTime(&ms, p.t0, p.t1) == cudaSuccess)
+      t.device_us = ms * 1000.f;
+    out.push_back(t);
+    std::lock_guard<std::mutex> l(timing_mu_);
+    timing_events_.push_back(p.t0);
+    timing_events_.push_back(p.t1);
+  }
+  return out;
+}
+
 void GpuOps::Shutdown() {
   if (shut_down_) return;
   shut_down_ = true;
+  GpuOps* self = this;
+  g_current.compare_exchange_strong(self, nullptr);
   if (device_ >= 0) {
     cudaSetDevice(device_);
     if (stream_) cudaStreamSynchronize(stream_);

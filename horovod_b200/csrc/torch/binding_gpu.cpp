@@ -3,6 +3,7 @@
 #include <pybind11/stl.h>
 
 #include "../kernels/kernels.h"
+#include "../ops/gpu_internal.h"
 #include "../ops/gpu_ops.h"
 
 namespace py = pybind11;
@@ -11,6 +12,20 @@ namespace hvd {
 
 void BindGpuDiagnostics(py::module_& m) {
   m.def("gpu_backend", &GpuBackendDescription);
+  m.def("gpu_op_stats", []() {
+    // (response type, payload bytes, tensors, device microseconds) of every
+    // device collective since the last call; needs HOROVOD_GPU_OP_TIMING=1.
+    py::list out;
+    GpuOps* ops = CurrentGpuOps();
+    if (ops == nullptr) return out;
+    std::vector<GpuOps::OpTiming> t;
+    {
+      py::gil_scoped_release release;
+      t = ops->DrainTimings();
+    }
+    for (auto& x : t) out.append(py::make_tuple(x.type, x.bytes, x.tensors, x.device_us));
+    return out;
+  });
   m.def("kernel_launch_count", &kern::KernelLaunchCount,
         "Kernels of this library launched so far in this process.");
 }

@@ -177,7 +177,9 @@ def launch_gloo_elastic(command, exec_command, settings, env, get_common_interfa
     run_env = create_run_env_vars(server_ip, port, nics, elastic=True)
 
     def run_slot(slot_info, events):
-        return exec_command(command, slot_info, run_env, env, settings, events)
+        # A new worker joins the rendezvous round during which it is started.
+        env_now = dict(run_env, HOROVOD_ELASTIC_ROUND=str(driver.rendezvous_round()))
+        return exec_command(command, slot_info, env_now, env, settings, events)
 
     try:
         driver.start(settings.num_proc, run_slot)

@@ -30,6 +30,8 @@ namespace hvd {
 // Defined in binding_gpu.cpp: topology / symmetric-memory diagnostics and
 // raw kernel entry points used by the GPU tests and benchmarks.
 void BindGpuDiagnostics(py::module_& m);
+// Defined in binding_testing.cpp.
+void BindTesting(py::module_& m);
 
 namespace {
 
@@ -534,4 +536,5 @@ PYBIND11_MODULE(_C, m) {
   m.def("wait_and_clear", &WaitAndClear);
 
   BindGpuDiagnostics(m);
+  BindTesting(m);
 }

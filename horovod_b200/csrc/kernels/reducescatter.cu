@@ -169,3 +169,138 @@ cudaError_t LaunchFusedReducescatter(const void* in, void* out, int64_t count,
 }  // namespace kern
 }  // namespace hvd
 
+// ---------------------------------------------------------------------------
+// Entry point that allocates nothing (declared in no_alloc.h).
+
+#include "no_alloc.h"
+
+#include <cstdio>
+#include <mutex>
+
+namespace hvd {
+namespace kern {
+namespace {
+
+// Layout of the static scratch: bookkeeping first, staging data after it.
+constexpr size_t NA_SHARDS_OFF = 0;       // int64[2]: shard bounds {0, count}
+constexpr size_t NA_STATUS_OFF = 256;     // int[4]: timeout record (unused by a group of one)
+constexpr size_t NA_FLAGS_OFF = 4096;     // uint32[SYMM_MAX_RANKS * SYMM_MAX_BLOCKS]
+constexpr size_t NA_DATA_OFF = 32768;     // staging for the prescaled input
+constexpr size_t NA_TOTAL = NA_DATA_OFF + HVD_B200_NOALLOC_MAX_BYTES;
+static_assert(NA_FLAGS_OFF + SYMM_MAX_RANKS * SYMM_MAX_BLOCKS * 4 <= NA_DATA_OFF,
+              "flag words must fit before the staging area");
+
+// In host code this name is only a handle for the runtime's symbol table,
+// never a device address: host code must go through cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NA_TOTAL];
+
+constexpr int NA_MAX_DEVICES = 64;
+std::mutex g_na_mu;
+unsigned char* g_na_base[NA_MAX_DEVICES] = {};
+
+// Resets what this call relies on: shard bounds for a group of one and the
+// barrier flag words (the previous call left its epoch values there).
+__global__ void noalloc_prepare_kernel(unsigned char* base, long long count) {
+  int64_t* sb = reinterpret_cast<int64_t*>(base + NA_SHARDS_OFF);
+  uint32_t* flags = reinterpret_cast<uint32_t*>(base + NA_FLAGS_OFF);
+  int* status = reinterpret_cast<int*>(base + NA_STATUS_OFF);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    sb[0] = 0;
+    sb[1] = count;
+    status[0] = status[1] = status[2] = status[3] = 0;
+  }
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x;
+       i < SYMM_MAX_RANKS * SYMM_MAX_BLOCKS; i += gridDim.x * blockDim.x)
+    flags[i] = 0;
+}
+
+int Fail(int code, char* err, unsigned long err_len, const char* what,
+         const char* detail = "") {
+  if (err != nullptr && err_len > 0)
+    std::snprintf(err, err_len, "hvd_b200_reducescatter1_noalloc: %s%s", what, detail);
+  return code;
+}
+
+}  // namespace
+}  // namespace kern
+}  // namespace hvd
+
+extern "C" __attribute__((visibility("default"))) int
+hvd_b200_reducescatter1_noalloc(const void* in, void* out, long long count,
+                                int dtype, double prescale, double postscale,
+                                void* stream_v, char* err, unsigned long err_len) {
+  using namespace hvd;
+  using namespace hvd::kern;
+  DataType dt = static_cast<DataType>(dtype);
+  switch (dt) {
+  case DataType::UINT8: case DataType::INT8: case DataType::INT32:
+  case DataType::INT64: case DataType::FLOAT16: case DataType::FLOAT32:
+  case DataType::FLOAT64: case DataType::BFLOAT16:
+    break;
+  default:
+    return Fail(2, err, err_len, "unsupported dtype id");
+  }
+  if (count < 0) return Fail(2, err, err_len, "negative element count");
+  if (count == 0) return 0;
+  if (in == nullptr || out == nullptr)
+    return Fail(2, err, err_len, "null input or output pointer");
+  const unsigned long long bytes =
+      static_cast<unsigned long long>(count) * DataTypeSize(dt);
+  if (bytes > HVD_B200_NOALLOC_MAX_BYTES) {
+    char detail[128];
+    std::snprintf(detail, sizeof(detail),
+                  " (%llu bytes requested, limit %u bytes)", bytes,
+                  static_cast<unsigned>(HVD_B200_NOALLOC_MAX_BYTES));
+    return Fail(1, err, err_len, "input larger than the built-in scratch", detail);
+  }
+
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess)
+    return Fail(3, err, err_len, "cudaGetDevice failed: ", cudaGetErrorString(e));
+  if (device < 0 || device >= NA_MAX_DEVICES)
+    return Fail(3, err, err_len, "device ordinal out of range");
+  unsigned char* base = nullptr;
+  {
+    // Once per device, with that device current: resolve the device address
+    // of the static array.
+    std::lock_guard<std::mutex> lock(g_na_mu);
+    if (g_na_base[device] == nullptr) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (e != cudaSuccess)
+        return Fail(3, err, err_len, "cudaGetSymbolAddress failed: ",
+                    cudaGetErrorString(e));
+      g_na_base[device] = static_cast<unsigned char*>(p);
+    }
+    base = g_na_base[device];
+  }
+
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  noalloc_prepare_kernel<<<8, 512, 0, stream>>>(base, count);
+  e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return Fail(3, err, err_len, "launch of the prepare kernel failed: ",
+                cudaGetErrorString(e));
+
+  SymmCtx ctx;
+  std::memset(&ctx, 0, sizeof(ctx));
+  ctx.rank = 0;
+  ctx.world = 1;
+  ctx.local = reinterpret_cast<char*>(base + NA_DATA_OFF);
+  ctx.peers[0] = ctx.local;
+  ctx.mc = nullptr;
+  ctx.flags_local = reinterpret_cast<uint32_t*>(base + NA_FLAGS_OFF);
+  ctx.flags_peers[0] = ctx.flags_local;
+  ctx.epoch = 0;
+  ctx.timeout_ns = 1000000000ull;  // a group of one never waits for anybody
+  ctx.status = reinterpret_cast<int*>(base + NA_STATUS_OFF);
+  const int ctas = bytes <= (64u << 10) ? 4 : 16;
+  e = LaunchFusedReducescatter(
+      in, out, count, reinterpret_cast<const int64_t*>(base + NA_SHARDS_OFF), dt,
+      prescale, postscale, /*use_nvls=*/false, ctas, ctx, stream);
+  if (e != cudaSuccess)
+    return Fail(3, err, err_len, "launch of the reduce-scatter kernel failed: ",
+                cudaGetErrorString(e));
+  return 0;
+}

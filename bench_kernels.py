@@ -1,0 +1,114 @@
+"""Single-GPU micro-benchmark of the library's local kernels, reported against
+the measured HBM copy bandwidth (MEASURED_PEAKS.json: hbm_gbs).
+
+    python bench_kernels.py                 # all cases
+    python bench_kernels.py --case fused_local --mb 512 --iters 3   # small ncu target
+
+Cases
+  fused_local   the fused multi-tensor allreduce kernel on one rank (LOCAL
+                variant): reads 161 ResNet-50-shaped gradient tensors, scales
+                and writes them back in one launch (read + write = 2x bytes).
+  fused_fp16    same with float16 tensors.
+  reducescatter reduce-scatter kernel on one rank: stage -> reduce -> write
+                (read + write staging + read staging + write = 4x bytes).
+  exchange      allgather of one rank through the exchange kernel (4x bytes).
+
+Timing is device time of the response on the communication stream (CUDA
+events around the launches). Inputs are larger than L2 (126 MB) unless --mb
+says otherwise. Prints one JSON line per case.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+
+os.environ["HOROVOD_GPU_OP_TIMING"] = "1"
+os.environ.setdefault("HOROVOD_FUSION_THRESHOLD", str(1 << 30))
+
+
+def resnet50_like_sizes(total_elems):
+    """161 tensor sizes with ResNet-50's skew (a few large convolutions, many
+    tiny batch-norm vectors), scaled to about total_elems."""
+    base = []
+    for planes, blocks in ((64, 3), (128, 4), (256, 6), (512, 3)):
+        for b in range(blocks):
+            inp = planes * 4 if b else max(64, planes * 2)
+            base += [inp * planes, planes, planes, planes * planes * 9, planes, planes,
+                     planes * planes * 4, planes * 4, planes * 4]
+            if b == 0:
+                base += [inp * planes * 4, planes * 4, planes * 4]
+    base += [64 * 3 * 49, 64, 64, 2048 * 1000, 1000]
+    base = base[:161]
+    scale = total_elems / float(sum(base))
+    return [max(1, int(s * scale)) for s in base]
+
+
+def main():
+    p = argparse.ArgumentParser()
+    p.add_argument("--case", default="all")
+    p.add_argument("--mb", type=int, default=512, help="payload per case in MB")
+    p.add_argument("--iters", type=int, default=10)
+    p.add_argument("--warmup", type=int, default=3)
+    args = p.parse_args()
+
+    import torch
+    import horovod_b200.torch as hvd
+    from horovod_b200 import _C
+
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)),
+                                            "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    peak_src = "measured" if peaks else "fallback"
+
+    hvd.init()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    nbytes = args.mb << 20
+
+    def run(name, fn, want_type, algorithmic_bytes):
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        _C.gpu_op_stats()
+        for _ in range(args.iters):
+            fn()
+        torch.cuda.synchronize()
+        us = [t[3] for t in _C.gpu_op_stats() if t[0] == want_type][-args.iters:]
+        med = statistics.median(us)
+        gbs = algorithmic_bytes / (med * 1e-6) / 1e9
+        print(json.dumps({"case": name, "payload_mb": args.mb, "device_us": round(med, 1),
+                          "algorithmic_gbs": round(gbs, 1),
+                          "frac_of_%s_hbm_copy" % peak_src: round(gbs / hbm, 3),
+                          "hbm_gbs_peak": hbm}), flush=True)
+
+    cases = ["fused_local", "fused_fp16", "reducescatter", "exchange"] \
+        if args.case == "all" else [args.case]
+    if "fused_local" in cases:
+        xs = [torch.randn(n, device=dev) for n in resnet50_like_sizes(nbytes // 4)]
+        total = sum(x.numel() * 4 for x in xs)
+        run("fused_local", lambda: hvd.grouped_allreduce_(xs, op=hvd.Sum, postscale_factor=0.5,
+                                                          name="k.fused"), 0, 2 * total)
+    if "fused_fp16" in cases:
+        xs = [torch.randn(n, device=dev).half() for n in resnet50_like_sizes(nbytes // 2)]
+        total = sum(x.numel() * 2 for x in xs)
+        run("fused_fp16", lambda: hvd.grouped_allreduce_(xs, op=hvd.Sum, postscale_factor=0.5,
+                                                         name="k.fused16"), 0, 2 * total)
+    if "reducescatter" in cases:
+        n = min(nbytes, 448 << 20) // 4
+        x = torch.randn(n, device=dev)
+        run("reducescatter", lambda: hvd.reducescatter(x, op=hvd.Sum, name="k.rs"), 6, 4 * n * 4)
+    if "exchange" in cases:
+        n = min(nbytes, 192 << 20) // 4
+        x = torch.randn(n, device=dev)
+        run("exchange", lambda: hvd.allgather(x, name="k.ag"), 1, 4 * n * 4)
+    hvd.shutdown()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -222,6 +222,9 @@ struct TensorTableEntry {
   void* output = nullptr;
   TensorShape shape;
   DataType dtype = DataType::FLOAT32;
+  // Element type on the wire for reductions (set equal to dtype unless the
+  // caller asked for a 16-bit wire format for fp32 data).
+  DataType wire_dtype = DataType::FLOAT32;
   int device = CPU_DEVICE_ID;
   int root_rank = 0;
   ReduceOp reduce_op = ReduceOp::SUM;

@@ -342,6 +342,11 @@ Response Controller::ConstructResponse(const std::string& name,
             << first.prescale << ", " << first.postscale
             << "), but another rank sent factors (" << reqs[i].prescale
             << ", " << reqs[i].postscale << ").";
+      } else if (reqs[i].wire_dtype != first.wire_dtype) {
+        bad = true;
+        err << "Mismatched compression: One rank sends "
+            << DataTypeName(first.wire_dtype) << " on the wire, but another rank sends "
+            << DataTypeName(reqs[i].wire_dtype) << ".";
       } else if (reqs[i].reduce_op != first.reduce_op) {
         bad = true;
         err << "Mismatched reduction operations: One rank requested "
@@ -450,6 +455,7 @@ Response Controller::ConstructResponse(const std::string& name,
   resp.postscale = first.postscale;
   resp.reduce_op = first.reduce_op;
   resp.root_rank = first.root_rank;
+  resp.wire_dtype = (type == Request::ALLREDUCE) ? first.wire_dtype : first.dtype;
   switch (type) {
   case Request::ALLREDUCE: resp.type = Response::ALLREDUCE; break;
   case Request::ALLGATHER: resp.type = Response::ALLGATHER; break;
@@ -466,7 +472,9 @@ int64_t Controller::ResponseBytes(const Response& r) const {
   int64_t es = static_cast<int64_t>(DataTypeSize(r.dtype));
   int64_t total = 0;
   if (IsReduction(r.type)) {
-    for (auto n : r.tensor_sizes) total += RoundUp(n * es, FUSION_ALIGN_BYTES);
+    int64_t ws = r.type == Response::ALLREDUCE
+                     ? static_cast<int64_t>(DataTypeSize(r.wire_dtype)) : es;
+    for (auto n : r.tensor_sizes) total += RoundUp(n * ws, FUSION_ALIGN_BYTES);
   } else if (r.type == Response::BROADCAST) {
     for (auto n : r.tensor_sizes) total += RoundUp(n, FUSION_ALIGN_BYTES);
   } else if (r.type == Response::ALLGATHER) {
@@ -509,7 +517,8 @@ void Controller::FuseResponses(std::deque<Response>& responses,
         if (compatible && reduction)
           compatible = next.prescale == r.prescale &&
                        next.postscale == r.postscale &&
-                       next.reduce_op == r.reduce_op;
+                       next.reduce_op == r.reduce_op &&
+                       next.wire_dtype == r.wire_dtype;
         if (compatible && r.type == Response::BROADCAST)
           compatible = next.root_rank == r.root_rank;
         if (compatible && bytes + nb <= threshold) {

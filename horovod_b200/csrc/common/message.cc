@@ -44,6 +44,7 @@ void Request::Serialize(WireWriter& w) const {
   for (auto d : shape) w.i64(d);
   w.f64(prescale);
   w.f64(postscale);
+  w.u8(static_cast<uint8_t>(wire_dtype));
 }
 
 Request Request::Parse(WireReader& r) {
@@ -62,6 +63,7 @@ Request Request::Parse(WireReader& r) {
   for (auto& d : q.shape) d = r.i64();
   q.prescale = r.f64();
   q.postscale = r.f64();
+  q.wire_dtype = static_cast<DataType>(r.u8());
   return q;
 }
 
@@ -108,6 +110,7 @@ void Response::Serialize(WireWriter& w) const {
   w.f64(postscale);
   w.i32(last_joined_rank);
   w.i32(root_rank);
+  w.u8(static_cast<uint8_t>(wire_dtype));
 }
 
 Response Response::Parse(WireReader& r) {
@@ -132,6 +135,7 @@ Response Response::Parse(WireReader& r) {
   p.postscale = r.f64();
   p.last_joined_rank = r.i32();
   p.root_rank = r.i32();
+  p.wire_dtype = static_cast<DataType>(r.u8());
   return p;
 }
 

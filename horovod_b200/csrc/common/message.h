@@ -94,6 +94,9 @@ public:
   std::vector<int64_t> shape;
   double prescale = 1.0;
   double postscale = 1.0;
+  // Element type on the wire (fp32 tensors may travel as fp16/bf16, cast
+  // inside the collective kernel); equals dtype when there is no cast.
+  DataType wire_dtype = DataType::FLOAT32;
 
   void Serialize(WireWriter& w) const;
   static Request Parse(WireReader& r);
@@ -136,6 +139,7 @@ public:
   double postscale = 1.0;
   int32_t last_joined_rank = -1;
   int32_t root_rank = 0;  // BROADCAST only
+  DataType wire_dtype = DataType::FLOAT32;  // reductions only
 
   void add_name(const std::string& n) { names.push_back(n); }
   std::string names_string() const;

@@ -466,6 +466,7 @@ Request MakeRequest(const TensorTableEntry& e, Request::Type type, int rank) {
   q.shape = e.shape.to_vector();
   q.prescale = e.prescale;
   q.postscale = e.postscale;
+  q.wire_dtype = e.wire_dtype;
   return q;
 }
 
@@ -497,6 +498,11 @@ Status EnqueueTensorAllreduces(std::vector<TensorTableEntry>& entries,
   std::vector<Request> requests;
   int64_t now = NowMicros();
   for (auto& e : entries) {
+    const bool cast_ok = e.dtype == DataType::FLOAT32 && e.device != CPU_DEVICE_ID &&
+                         (e.wire_dtype == DataType::FLOAT16 ||
+                          e.wire_dtype == DataType::BFLOAT16) &&
+                         type == Request::ALLREDUCE;
+    if (!cast_ok) e.wire_dtype = e.dtype;
     e.reduce_op = wire_op;
     e.prescale = prescale;
     e.postscale = postscale;

@@ -39,6 +39,7 @@ ResponseCache::CacheState ResponseCache::cached(const Request& q) const {
   bool same = same_type && p.dtype == q.dtype && same_shape &&
               p.device == q.device && p.prescale == q.prescale &&
               p.postscale == q.postscale && p.reduce_op == q.reduce_op &&
+              (q.type != Request::ALLREDUCE || p.wire_dtype == q.wire_dtype) &&
               (q.type != Request::BROADCAST || p.root_rank == q.root_rank);
   return same ? CacheState::HIT : CacheState::INVALID;
 }
@@ -87,6 +88,8 @@ void ResponseCache::put(const Response& response, const TensorQueue& queue,
     single.reduce_op = response.reduce_op;
     single.prescale = response.prescale;
     single.postscale = response.postscale;
+    single.wire_dtype = response.wire_dtype;
+    single.root_rank = response.root_rank;
     for (size_t k = 0; k < per_tensor; ++k)
       single.tensor_sizes.push_back(response.tensor_sizes[i * per_tensor + k]);
 
@@ -95,6 +98,7 @@ void ResponseCache::put(const Response& response, const TensorQueue& queue,
     p.prescale = response.prescale;
     p.postscale = response.postscale;
     p.reduce_op = response.reduce_op;
+    p.wire_dtype = response.wire_dtype;
     p.root_rank = 0;
     p.device = response.devices.empty() ? CPU_DEVICE_ID : response.devices[0];
     p.shape_is_synthetic = true;

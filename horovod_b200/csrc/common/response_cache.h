@@ -59,6 +59,7 @@ private:
     double prescale, postscale;
     ReduceOp reduce_op;
     int32_t root_rank;
+    DataType wire_dtype;
   };
   struct Entry {
     Response response;

@@ -67,6 +67,7 @@ void TensorQueue::GetTensorEntriesFromResponse(
     TensorTableEntry e;
     e.name = name;
     e.dtype = response.dtype;
+    e.wire_dtype = response.wire_dtype;
     e.reduce_op = response.reduce_op;
     e.prescale = response.prescale;
     e.postscale = response.postscale;

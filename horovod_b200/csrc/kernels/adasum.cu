@@ -56,10 +56,9 @@ adasum_pack_kernel(TensorList tl, SymmCtx ctx, float prescale, double* scratch,
     scratch[i] = 0.0;
   if (lo >= hi) return;
   uint4* stage = reinterpret_cast<uint4*>(ctx.local);
-  int cur = find_tensor(tl, (lo + threadIdx.x) * N);
   const bool pre = prescale != 1.0f;
-  for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS)
-    st16(stage + v, gather_vec<T, float, float>(tl, cur, v * N, prescale, pre));
+  gather_range<T, float, float, THREADS>(tl, lo, hi, prescale, pre,
+                                         [stage](int64_t v, uint4 x) { st16(stage + v, x); });
 }
 
 __device__ __forceinline__ void flush_sums(double* dst, int t, double d,
@@ -189,11 +188,9 @@ adasum_gather_kernel(TensorList tl, SymmCtx ctx, int levels, uint32_t epoch,
     const int64_t len = own.hi - own.lo;
     const int64_t per = (len + gridDim.x - 1) / gridDim.x;
     const int64_t lo = own.lo + blockIdx.x * per, hi = min(lo + per, own.hi);
-    if (lo + threadIdx.x >= hi) continue;
     const uint4* src = reinterpret_cast<const uint4*>(ctx.peers[q]);
-    int cur = find_tensor(tl, (lo + threadIdx.x) * N);
-    for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS)
-      scatter_vec<T, float, float>(tl, cur, v * N, ld16(src + v), postscale, post);
+    scatter_range<T, float, float, THREADS>(tl, lo, hi, postscale, post,
+                                            [src](int64_t v) { return ld16(src + v); });
   }
   // Peers may still be reading this rank's piece.
   cta_barrier(ctx, epoch + 1, blockIdx.x, 31);

@@ -20,26 +20,20 @@ namespace {
 
 constexpr int THREADS = 512;
 
-template <typename T, typename W, typename S>
+template <typename T, typename W, typename S, int UNROLL = 4>
 __device__ __forceinline__ void pack_range(const TensorList& tl, uint4* stage,
                                            int64_t lo, int64_t hi, S scale,
                                            bool do_scale) {
-  constexpr int N = 16 / sizeof(W);
-  if (lo >= hi) return;
-  int cur = find_tensor(tl, (lo + threadIdx.x) * N);
-  for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS)
-    st16(stage + v, gather_vec<T, W, S>(tl, cur, v * N, scale, do_scale));
+  gather_range<T, W, S, THREADS, UNROLL>(tl, lo, hi, scale, do_scale,
+                                 [stage](int64_t v, uint4 x) { st16(stage + v, x); });
 }
 
 template <typename T, typename W, typename S>
 __device__ __forceinline__ void unpack_range(const TensorList& tl,
                                              const uint4* stage, int64_t lo,
                                              int64_t hi, S scale, bool do_scale) {
-  constexpr int N = 16 / sizeof(W);
-  if (lo >= hi) return;
-  int cur = find_tensor(tl, (lo + threadIdx.x) * N);
-  for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS)
-    scatter_vec<T, W, S>(tl, cur, v * N, ld16(stage + v), scale, do_scale);
+  scatter_range<T, W, S, THREADS>(tl, lo, hi, scale, do_scale,
+                                  [stage](int64_t v) { return ld16(stage + v); });
 }
 
 template <typename T, typename W, int ALGO>
@@ -58,34 +52,35 @@ fused_allreduce_kernel(TensorList tl, SymmCtx ctx,
   if constexpr (ALGO == static_cast<int>(Algo::LOCAL)) {
     const int64_t per = (nvec + G - 1) / G;
     const int64_t lo = b * per, hi = min(lo + per, nvec);
-    if (lo >= hi) return;
-    int cin = find_tensor(tl, (lo + threadIdx.x) * N), cout = cin;
+    // No staging on a single rank: gather (scale, round through the wire
+    // type) and write straight back to the outputs.
     const S both = prescale * postscale;
-    for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS) {
-      uint4 x = gather_vec<T, W, S>(tl, cin, v * N, both, pre || post);
-      scatter_vec<T, W, S>(tl, cout, v * N, x, S(1), false);
-    }
+    int cout = lo < hi ? find_tensor(tl, lo * N) : 0;
+    gather_range<T, W, S, THREADS>(
+        tl, lo, hi, both, pre || post, [&](int64_t v, uint4 x) {
+          // Vectors arrive in increasing order per thread only inside one
+          // tensor; re-seek when the walker moved on to the next tensor.
+          if (v * N < __ldg(tl.offsets + cout)) cout = find_tensor(tl, v * N);
+          scatter_vec<T, W, S>(tl, cout, v * N, x, S(1), false);
+        });
     return;
   } else if constexpr (ALGO == static_cast<int>(Algo::ONESHOT)) {
     const int64_t per = (nvec + G - 1) / G;
     const int64_t lo = b * per, hi = min(lo + per, nvec);
-    pack_range<T, W, S>(tl, stage, lo, hi, prescale, pre);
+    pack_range<T, W, S, 1>(tl, stage, lo, hi, prescale, pre);
     if (!cta_barrier(ctx, ctx.epoch + 1, b, 1)) return;
-    if (lo < hi) {
-      int cur = find_tensor(tl, (lo + threadIdx.x) * N);
-      for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS) {
-        uint4 in[SYMM_MAX_RANKS];
+    scatter_range<T, W, S, THREADS, 1>(tl, lo, hi, postscale, post, [&](int64_t v) {
+      uint4 in[SYMM_MAX_RANKS];
 #pragma unroll
-        for (int p = 0; p < SYMM_MAX_RANKS; ++p)
-          if (p < world) in[p] = ld16(reinterpret_cast<const uint4*>(ctx.peers[p]) + v);
-        VecAcc<W> acc;
-        acc.zero();
+      for (int p = 0; p < SYMM_MAX_RANKS; ++p)
+        if (p < world) in[p] = ld16(reinterpret_cast<const uint4*>(ctx.peers[p]) + v);
+      VecAcc<W> acc;
+      acc.zero();
 #pragma unroll
-        for (int p = 0; p < SYMM_MAX_RANKS; ++p)
-          if (p < world) acc.add(in[p]);
-        scatter_vec<T, W, S>(tl, cur, v * N, acc.pack(), postscale, post);
-      }
-    }
+      for (int p = 0; p < SYMM_MAX_RANKS; ++p)
+        if (p < world) acc.add(in[p]);
+      return acc.pack();
+    });
     // Nobody may repack its staging buffer while a peer still reads it.
     cta_barrier(ctx, ctx.epoch + 2, b, 2);
     return;

@@ -28,13 +28,12 @@ pack_unpack_kernel(TensorList tl, uint4* buffer, typename ScaleT<T>::type scale)
   const int64_t lo = blockIdx.x * per, hi = min(lo + per, nvec);
   if (lo >= hi) return;
   const bool do_scale = scale != S(1);
-  int cur = find_tensor(tl, (lo + threadIdx.x) * N);
-  for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS) {
-    if constexpr (TO_BUFFER)
-      st16(buffer + v, gather_vec<T, W, S>(tl, cur, v * N, scale, do_scale));
-    else
-      scatter_vec<T, W, S>(tl, cur, v * N, ld16(buffer + v), scale, do_scale);
-  }
+  if constexpr (TO_BUFFER)
+    gather_range<T, W, S, THREADS>(tl, lo, hi, scale, do_scale,
+                                   [buffer](int64_t v, uint4 x) { st16(buffer + v, x); });
+  else
+    scatter_range<T, W, S, THREADS>(tl, lo, hi, scale, do_scale,
+                                    [buffer](int64_t v) { return ld16(buffer + v); });
 }
 
 template <typename T, typename W>

@@ -134,6 +134,175 @@ __device__ __forceinline__ void scatter_vec(const TensorList& tl, int& cur,
   }
 }
 
+// ---- range walkers ---------------------------------------------------------
+// The per-vector functions above look the tensor up for every 16 bytes. The
+// walkers below are what the kernels use for bulk work: the CTA goes through
+// the tensors that overlap its range together, and inside one tensor runs a
+// tight, four-way unrolled vector loop with no per-vector bookkeeping, so
+// many loads are in flight per thread. `sink(v, raw)` receives fused vector
+// index v and its 16 bytes; `source(v)` provides them.
+
+template <typename T, typename W, typename S>
+__device__ __forceinline__ uint4 convert_in(const uint4* raw, S scale, bool do_scale) {
+  constexpr int N = 16 / sizeof(W);
+  constexpr int LOADS = (N * sizeof(T) + 15) / 16;
+  if constexpr (std::is_same<T, W>::value) {
+    if (!do_scale) return raw[0];
+  }
+  union { uint4 r[LOADS]; T e[N]; } in;
+#pragma unroll
+  for (int i = 0; i < LOADS; ++i) in.r[i] = raw[i];
+  WireVec<W> out;
+#pragma unroll
+  for (int i = 0; i < N; ++i) out.e[i] = scale_cast<W>(in.e[i], scale, do_scale);
+  return out.raw;
+}
+
+template <typename T, typename W, typename S, int THREADS, int UNROLL = 4,
+          typename Sink>
+__device__ __forceinline__ void gather_range(const TensorList& tl, int64_t lo,
+                                             int64_t hi, S scale, bool do_scale,
+                                             Sink sink) {
+  constexpr int N = 16 / sizeof(W);
+  // Tensor elements narrower than the wire type (Adasum stages fp16 as
+  // fp32) take the element-wise path; the vector path needs whole 16-byte
+  // loads per wire vector.
+  constexpr bool VEC = N * sizeof(T) >= 16;
+  constexpr int LOADS = VEC ? N * sizeof(T) / 16 : 1;
+  if (lo >= hi) return;
+  for (int t = find_tensor(tl, lo * N); t < tl.n; ++t) {
+    const int64_t toff = __ldg(tl.offsets + t);
+    if (toff >= hi * N) break;
+    const int64_t tend = __ldg(tl.offsets + t + 1);
+    const int64_t cnt = __ldg(tl.counts + t);
+    const T* src = static_cast<const T*>(ldg_ptr(tl.in + t));
+    const int64_t v0 = max(lo, toff / N), v1 = min(hi, tend / N);
+    // Vectors that lie entirely inside the tensor's data.
+    const int64_t vfull = src ? max(v0, min(v1, (toff + cnt) / N)) : v0;
+    if (VEC && src != nullptr && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+      const uint4* s4 = reinterpret_cast<const uint4*>(src) - (toff / N) * LOADS;
+      int64_t v = v0 + threadIdx.x;
+      for (; v + (UNROLL - 1) * THREADS < vfull; v += UNROLL * THREADS) {
+        uint4 raw[UNROLL][LOADS];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+          for (int i = 0; i < LOADS; ++i)
+            raw[u][i] = ld16_stream(s4 + (v + u * THREADS) * LOADS + i);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+          sink(v + u * THREADS, convert_in<T, W, S>(raw[u], scale, do_scale));
+      }
+      for (; v < vfull; v += THREADS) {
+        uint4 raw[LOADS];
+#pragma unroll
+        for (int i = 0; i < LOADS; ++i) raw[i] = ld16_stream(s4 + v * LOADS + i);
+        sink(v, convert_in<T, W, S>(raw, scale, do_scale));
+      }
+    } else if (src != nullptr) {
+      for (int64_t v = v0 + threadIdx.x; v < vfull; v += THREADS) {
+        WireVec<W> out;
+        const T* p = src + (v * N - toff);
+#pragma unroll
+        for (int i = 0; i < N; ++i) out.e[i] = scale_cast<W>(p[i], scale, do_scale);
+        sink(v, out.raw);
+      }
+    }
+    // Ragged last vector and alignment padding (zeros).
+    for (int64_t v = vfull + threadIdx.x; v < v1; v += THREADS) {
+      WireVec<W> out;
+      out.raw = make_uint4(0, 0, 0, 0);
+      const int64_t local = v * N - toff;
+      if (src != nullptr) {
+#pragma unroll
+        for (int i = 0; i < N; ++i)
+          if (local + i < cnt) out.e[i] = scale_cast<W>(src[local + i], scale, do_scale);
+      }
+      sink(v, out.raw);
+    }
+  }
+}
+
+template <typename T, typename W, typename S>
+__device__ __forceinline__ void convert_out(uint4 raw, S scale, bool do_scale, uint4* out) {
+  constexpr int N = 16 / sizeof(W);
+  constexpr int STORES = (N * sizeof(T) + 15) / 16;
+  if constexpr (std::is_same<T, W>::value) {
+    if (!do_scale) {
+      out[0] = raw;
+      return;
+    }
+  }
+  WireVec<W> in;
+  in.raw = raw;
+  union { uint4 r[STORES]; T e[N]; } o;
+#pragma unroll
+  for (int i = 0; i < N; ++i) o.e[i] = scale_cast<T>(in.e[i], scale, do_scale);
+#pragma unroll
+  for (int i = 0; i < STORES; ++i) out[i] = o.r[i];
+}
+
+template <typename T, typename W, typename S, int THREADS, int UNROLL = 4,
+          typename Source>
+__device__ __forceinline__ void scatter_range(const TensorList& tl, int64_t lo,
+                                              int64_t hi, S scale, bool do_scale,
+                                              Source source) {
+  constexpr int N = 16 / sizeof(W);
+  constexpr bool VEC = N * sizeof(T) >= 16;
+  constexpr int STORES = VEC ? N * sizeof(T) / 16 : 1;
+  if (lo >= hi) return;
+  for (int t = find_tensor(tl, lo * N); t < tl.n; ++t) {
+    const int64_t toff = __ldg(tl.offsets + t);
+    if (toff >= hi * N) break;
+    const int64_t tend = __ldg(tl.offsets + t + 1);
+    const int64_t cnt = __ldg(tl.counts + t);
+    T* dst = static_cast<T*>(const_cast<void*>(ldg_ptr(tl.out + t)));
+    if (dst == nullptr) continue;
+    const int64_t v0 = max(lo, toff / N), v1 = min(hi, tend / N);
+    const int64_t vfull = max(v0, min(v1, (toff + cnt) / N));
+    if (VEC && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+      uint4* d4 = reinterpret_cast<uint4*>(dst) - (toff / N) * STORES;
+      int64_t v = v0 + threadIdx.x;
+      for (; v + (UNROLL - 1) * THREADS < vfull; v += UNROLL * THREADS) {
+        uint4 raw[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) raw[u] = source(v + u * THREADS);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          uint4 o[STORES];
+          convert_out<T, W, S>(raw[u], scale, do_scale, o);
+#pragma unroll
+          for (int i = 0; i < STORES; ++i)
+            st16_stream(d4 + (v + u * THREADS) * STORES + i, o[i]);
+        }
+      }
+      for (; v < vfull; v += THREADS) {
+        uint4 o[STORES];
+        convert_out<T, W, S>(source(v), scale, do_scale, o);
+#pragma unroll
+        for (int i = 0; i < STORES; ++i) st16_stream(d4 + v * STORES + i, o[i]);
+      }
+    } else {
+      for (int64_t v = v0 + threadIdx.x; v < vfull; v += THREADS) {
+        WireVec<W> in;
+        in.raw = source(v);
+        T* p = dst + (v * N - toff);
+#pragma unroll
+        for (int i = 0; i < N; ++i) p[i] = scale_cast<T>(in.e[i], scale, do_scale);
+      }
+    }
+    for (int64_t v = vfull + threadIdx.x; v < v1; v += THREADS) {
+      const int64_t local = v * N - toff;
+      if (local >= cnt) continue;  // pure padding
+      WireVec<W> in;
+      in.raw = source(v);
+#pragma unroll
+      for (int i = 0; i < N; ++i)
+        if (local + i < cnt) dst[local + i] = scale_cast<T>(in.e[i], scale, do_scale);
+    }
+  }
+}
+
 // Sum of `world` wire vectors in the accumulation type of W.
 template <typename W> struct VecAcc {
   using A = typename Acc<W>::type;

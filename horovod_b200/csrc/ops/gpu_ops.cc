@@ -246,8 +246,8 @@ int GpuOps::PickCtas(int64_t bytes) const {
   // below the SM count so backward keeps most of the GPU.
   if (bytes <= 64 * 1024) return 4;
   if (bytes <= 1 << 20) return 16;
-  if (bytes <= 16 << 20) return 32;
-  return 64;
+  if (bytes <= 16 << 20) return 48;
+  return 96;
 }
 
 kern::Algo GpuOps::PickAlgo(const SymmSet& set, DataType wire,

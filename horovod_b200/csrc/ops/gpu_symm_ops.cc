@@ -30,7 +30,9 @@ Status GpuOps::SymmAllreduce(std::vector<TensorTableEntry>& entries,
   Timeline& tl = state_.timeline;
   const DataType dtype = response.dtype;
   // Adasum stages fp32 whatever the tensor type.
-  const DataType wire = (adasum && set.world > 1) ? DataType::FLOAT32 : dtype;
+  const DataType wire = (adasum && set.world > 1)
+                            ? DataType::FLOAT32
+                            : (adasum ? dtype : response.wire_dtype);
   const int64_t es = static_cast<int64_t>(DataTypeSize(dtype));
   const int64_t ws = static_cast<int64_t>(DataTypeSize(wire));
   const int64_t align_elems = FUSION_ALIGN_BYTES / ws;
@@ -116,9 +118,13 @@ Status GpuOps::SymmAllreduce(std::vector<TensorTableEntry>& entries,
     } else {
       kern::Algo algo = PickAlgo(set, wire, bytes);
       kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH);
+      int ctas = PickCtas(bytes);
+      // A single rank waits for nobody: use the whole GPU for the copy.
+      if (algo == kern::Algo::LOCAL && forced_ctas_ <= 0)
+        ctas = static_cast<int>(std::min<int64_t>(296, std::max<int64_t>(1, bytes >> 16)));
       err = kern::LaunchFusedAllreduce(list, dtype, adasum ? dtype : wire,
                                        response.prescale, response.postscale,
-                                       algo, PickCtas(bytes), ctx, stream_);
+                                       algo, ctas, ctx, stream_);
     }
     ring_.Release(slot, stream_);
     if (err != cudaSuccess)

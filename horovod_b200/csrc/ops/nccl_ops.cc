@@ -167,14 +167,16 @@ Status NcclOps::Allreduce(std::vector<TensorTableEntry>& entries,
   cudaStream_t stream = gpu_.stream();
   Timeline& tl = gpu_.state().timeline;
   ncclDataType_t nt;
-  if (!NcclType(response.dtype, &nt))
-    return Status::InvalidArgument(std::string("NCCL cannot reduce dtype ") +
-                                   DataTypeName(response.dtype));
-  const ncclRedOp_t op = NcclOp(response.reduce_op, response.dtype);
   const DataType dtype = response.dtype;
-  const int64_t es = static_cast<int64_t>(DataTypeSize(dtype));
+  // fp32 tensors may travel as fp16/bf16: the cast happens in pack/unpack.
+  const DataType wire = response.wire_dtype;
+  if (!NcclType(wire, &nt))
+    return Status::InvalidArgument(std::string("NCCL cannot reduce dtype ") +
+                                   DataTypeName(wire));
+  const ncclRedOp_t op = NcclOp(response.reduce_op, response.dtype);
+  const int64_t es = static_cast<int64_t>(DataTypeSize(wire));
 
-  if (entries.size() == 1 && entries[0].input && entries[0].output) {
+  if (wire == dtype && entries.size() == 1 && entries[0].input && entries[0].output) {
     TensorTableEntry& e = entries[0];
     const void* src = e.input;
     if (response.prescale != 1.0) {
@@ -217,13 +219,13 @@ Status NcclOps::Allreduce(std::vector<TensorTableEntry>& entries,
   kern::TensorList list = {static_cast<int>(n), d_off, d_cnt, d_in, d_out};
   void* buf = Fusion(static_cast<size_t>(off * es));
   tl.ActivityStartAll(entries, HVD_ACT_MEMCPY_IN_FUSION_BUFFER);
-  kern::LaunchPackUnpack(list, dtype, dtype, buf, response.prescale, true, off, stream);
+  kern::LaunchPackUnpack(list, dtype, wire, buf, response.prescale, true, off, stream);
   tl.ActivityEndAll(entries);
   tl.ActivityStartAll(entries, HVD_ACT_NCCL_ALLREDUCE);
   HVD_NCCL(api_->AllReduce(buf, buf, off, nt, op, comm, stream));
   tl.ActivityEndAll(entries);
   tl.ActivityStartAll(entries, HVD_ACT_MEMCPY_OUT_FUSION_BUFFER);
-  kern::LaunchPackUnpack(list, dtype, dtype, buf, response.postscale, false, off, stream);
+  kern::LaunchPackUnpack(list, dtype, wire, buf, response.postscale, false, off, stream);
   tl.ActivityEndAll(entries);
   gpu_.ring().Release(slot, stream);
   return gpu_.Complete(entries);

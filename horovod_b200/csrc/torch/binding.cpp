@@ -253,6 +253,7 @@ TensorTableEntry MakeEntry(const at::Tensor& input, const at::Tensor* output,
   e.output = output ? output->data_ptr() : nullptr;
   e.shape = TensorShape(input.sizes().vec());
   e.dtype = ToDataType(input.scalar_type());
+  e.wire_dtype = e.dtype;
   e.device = DeviceOf(input);
   e.context = std::make_shared<TorchOpContext>(rec, input.options(), e.device);
   if (e.device != CPU_DEVICE_ID)
@@ -270,7 +271,7 @@ void FailHandle(int handle, const Status& st) {
 
 int AllreduceAsync(const at::Tensor& tensor, const at::Tensor& output,
                    const std::string& name, int op, double prescale,
-                   double postscale, int process_set) {
+                   double postscale, int process_set, int wire_dtype) {
   auto rec = std::make_shared<HandleRecord>();
   rec->device = DeviceOf(tensor);
   rec->inputs = {tensor};
@@ -284,6 +285,8 @@ int AllreduceAsync(const at::Tensor& tensor, const at::Tensor& output,
     throw;
   }
   entries[0].name = NameOrDefault(name, "allreduce", handle);
+  entries[0].wire_dtype =
+      wire_dtype >= 0 ? static_cast<DataType>(wire_dtype) : entries[0].dtype;
   Status st = EnqueueTensorAllreduces(entries, static_cast<ReduceOp>(op),
                                       prescale, postscale, process_set);
   if (!st.ok()) FailHandle(handle, st);
@@ -293,7 +296,7 @@ int AllreduceAsync(const at::Tensor& tensor, const at::Tensor& output,
 int GroupedAllreduceAsync(const std::vector<at::Tensor>& tensors,
                           const std::vector<at::Tensor>& outputs,
                           const std::string& name, int op, double prescale,
-                          double postscale, int process_set) {
+                          double postscale, int process_set, int wire_dtype) {
   if (tensors.size() != outputs.size())
     throw std::invalid_argument("grouped_allreduce: tensors/outputs mismatch");
   auto rec = std::make_shared<HandleRecord>();
@@ -322,6 +325,7 @@ int GroupedAllreduceAsync(const std::vector<at::Tensor>& tensors,
       e.output = outputs[i].data_ptr();
       e.shape = TensorShape(tensors[i].sizes().vec());
       e.dtype = ToDataType(tensors[i].scalar_type());
+      e.wire_dtype = wire_dtype >= 0 ? static_cast<DataType>(wire_dtype) : e.dtype;
       e.device = rec->device;
       if (e.device != CPU_DEVICE_ID) {
         if (!shared_ready)
@@ -525,8 +529,12 @@ PYBIND11_MODULE(_C, m) {
   m.def("process_set_ranks", &hvd_process_set_ranks);
   m.def("process_set_ids", &hvd_process_set_ids);
 
-  m.def("allreduce_async", &AllreduceAsync);
-  m.def("grouped_allreduce_async", &GroupedAllreduceAsync);
+  m.def("allreduce_async", &AllreduceAsync, py::arg("tensor"), py::arg("output"),
+        py::arg("name"), py::arg("op"), py::arg("prescale"), py::arg("postscale"),
+        py::arg("process_set"), py::arg("wire_dtype") = -1);
+  m.def("grouped_allreduce_async", &GroupedAllreduceAsync, py::arg("tensors"),
+        py::arg("outputs"), py::arg("name"), py::arg("op"), py::arg("prescale"),
+        py::arg("postscale"), py::arg("process_set"), py::arg("wire_dtype") = -1);
   m.def("allgather_async", &AllgatherAsync);
   m.def("broadcast_async", &BroadcastAsync);
   m.def("alltoall_async", &AlltoallAsync);

@@ -101,7 +101,19 @@ def _scaled_op(op, prescale_factor, postscale_factor):
     return int(op), float(prescale_factor), float(postscale_factor)
 
 
-def _allreduce_async(tensor, output, name, op, prescale_factor, postscale_factor, process_set):
+_WIRE_IDS = {torch.float16: 6, torch.bfloat16: 10}
+
+
+def _wire_id(tensor, wire_dtype):
+    """Wire format id for the native call: fp32 CUDA tensors can be cast to a
+    16-bit type inside the collective kernel; anything else is sent as is."""
+    if wire_dtype is None or not tensor.is_cuda or tensor.dtype != torch.float32:
+        return -1
+    return _WIRE_IDS.get(wire_dtype, -1)
+
+
+def _allreduce_async(tensor, output, name, op, prescale_factor, postscale_factor, process_set,
+                     wire_dtype=None):
     _check_tensor(tensor, dense_ok=True)
     _check_adasum(op, process_set)
     if op == Average and not (tensor.is_floating_point() or tensor.is_complex()):
@@ -113,7 +125,8 @@ def _allreduce_async(tensor, output, name, op, prescale_factor, postscale_factor
         _handle_map[handle] = ("allreduce_intavg", divisor)
         return handle
     handle = _C.allreduce_async(tensor, output, name or "", *_scaled_op(
-        op, prescale_factor, postscale_factor), _resolve(process_set))
+        op, prescale_factor, postscale_factor), _resolve(process_set),
+        _wire_id(tensor, wire_dtype) if op in (Average, Sum) else -1)
     _handle_map[handle] = ("allreduce", None)
     return handle
 
@@ -163,11 +176,14 @@ def allreduce(tensor, average=None, name=None, compression=Compression.none, op=
 
 
 def allreduce_async_(tensor, average=None, name=None, op=None, prescale_factor=1.0,
-                     postscale_factor=1.0, process_set=global_process_set):
-    """In-place asynchronous allreduce."""
+                     postscale_factor=1.0, process_set=global_process_set, wire_dtype=None):
+    """In-place asynchronous allreduce. ``wire_dtype`` (torch.float16 or
+    torch.bfloat16) makes an fp32 CUDA tensor travel in that format: the
+    casts happen inside the collective kernel instead of as separate torch
+    kernels, and the tensor itself stays fp32."""
     op = handle_average_backwards_compatibility(op, average)
     return _allreduce_async(tensor, tensor, name, op, prescale_factor, postscale_factor,
-                            process_set)
+                            process_set, wire_dtype)
 
 
 def allreduce_(tensor, average=None, name=None, op=None, prescale_factor=1.0,
@@ -179,7 +195,7 @@ def allreduce_(tensor, average=None, name=None, op=None, prescale_factor=1.0,
 
 
 def _grouped_allreduce_async(tensors, outputs, name, op, prescale_factor, postscale_factor,
-                             process_set):
+                             process_set, wire_dtype=None):
     for t in tensors:
         _check_tensor(t, dense_ok=True)
     _check_adasum(op, process_set)
@@ -187,7 +203,11 @@ def _grouped_allreduce_async(tensors, outputs, name, op, prescale_factor, postsc
     wire_op = Sum if int_avg else op
     handle = _C.grouped_allreduce_async(list(tensors), list(outputs), name or "",
                                         int(wire_op), float(prescale_factor),
-                                        float(postscale_factor), _resolve(process_set))
+                                        float(postscale_factor), _resolve(process_set),
+                                        _wire_id(tensors[0], wire_dtype)
+                                        if tensors and wire_op in (Average, Sum)
+                                        and all(t.dtype == torch.float32 and t.is_cuda
+                                                for t in tensors) else -1)
     if int_avg:
         divisor = process_set.size() if process_set is not None else size()
         _handle_map[handle] = ("grouped_intavg", divisor)
@@ -239,10 +259,11 @@ def grouped_allreduce(tensors, average=None, name=None, compression=Compression.
 
 
 def grouped_allreduce_async_(tensors, average=None, name=None, op=None, prescale_factor=1.0,
-                             postscale_factor=1.0, process_set=global_process_set):
+                             postscale_factor=1.0, process_set=global_process_set,
+                             wire_dtype=None):
     op = handle_average_backwards_compatibility(op, average)
     return _grouped_allreduce_async(tensors, tensors, name, op, prescale_factor,
-                                    postscale_factor, process_set)
+                                    postscale_factor, process_set, wire_dtype)
 
 
 def grouped_allreduce_(tensors, average=None, name=None, op=None, prescale_factor=1.0,

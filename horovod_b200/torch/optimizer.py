@@ -142,8 +142,17 @@ class _DistributedOptimizer(torch.optim.Optimizer):
                 tensor = tensor.to_dense()
             else:
                 return self._sparse_allreduce_grad_async(p, name)
-        tensor_compressed, ctx = self._compression.compress(tensor)
         pre, post = self._scale_factors()
+        wire = getattr(self._compression, "wire_dtype", None)
+        if wire is not None and tensor.is_cuda and tensor.dtype == torch.float32 \
+                and self.op in (Average, Sum):
+            # The cast to the 16-bit wire format and back happens inside the
+            # collective kernel; the gradient tensor stays fp32.
+            handle = allreduce_async_(tensor, name=name, op=self.op, prescale_factor=pre,
+                                      postscale_factor=post, process_set=self.process_set,
+                                      wire_dtype=wire)
+            return handle, (tensor, None)
+        tensor_compressed, ctx = self._compression.compress(tensor)
         handle = allreduce_async_(tensor_compressed, name=name, op=self.op,
                                   prescale_factor=pre, postscale_factor=post,
                                   process_set=self.process_set)
@@ -241,7 +250,7 @@ class _DistributedOptimizer(torch.optim.Optimizer):
                     done_handles[handle] = synchronize(handle)
                 outputs = done_handles[handle]
                 gi = self._p_to_group[p]
-                idx = self._groups[gi].index(p)
+                idx = next(i for i, q in enumerate(self._groups[gi]) if q is p)
                 tensors, ctxs = ctx
                 self._allreduce_delay[p] = self.backward_passes_per_step
                 out = outputs[idx] if outputs is not None else tensors[idx]

@@ -56,6 +56,16 @@ def _collectives(rank, size, algo):
     for i, (s, o) in enumerate(zip(shapes, outs)):
         ref = sum(_inputs(r * 31 + i, s, torch.float32).double() for r in range(size)) / size
         assert (o.double().cpu() - ref).abs().max().item() < 1e-5
+    # fp32 gradients with a 16-bit wire format (cast fused into the kernel)
+    for wire, tol in ((torch.bfloat16, 4e-2), (torch.float16, 8e-3)):
+        xs = [_inputs(rank * 13 + i, s, torch.float32).to(dev) for i, s in enumerate(shapes)]
+        hvd.synchronize(hvd.grouped_allreduce_async_(xs, op=hvd.Average, wire_dtype=wire,
+                                                     name="wire.%s" % wire))
+        for i, (s, o) in enumerate(zip(shapes, xs)):
+            assert o.dtype == torch.float32
+            ref = sum(_inputs(r * 13 + i, s, torch.float32).to(wire).double()
+                      for r in range(size)) / size
+            assert (o.double().cpu() - ref).abs().max().item() < tol * size, (str(wire), s)
     # allgather with a different dim 0 on every rank
     rows = rank + 1
     ag = hvd.allgather(torch.full((rows, 3), float(rank), device=dev), name="ag")

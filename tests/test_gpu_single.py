@@ -57,6 +57,16 @@ def test_inplace_and_async(hvd):
     torch.testing.assert_close(x, ref * 3.0)
 
 
+def test_wire_cast_happens_inside_the_kernel(hvd):
+    x = torch.randn(100003, device=_dev())
+    for wire in (torch.bfloat16, torch.float16):
+        y = x.clone()
+        hvd.synchronize(hvd.allreduce_async_(y, op=hvd.Sum, postscale_factor=2.0,
+                                             wire_dtype=wire, name="wire.%s" % wire))
+        assert y.dtype == torch.float32
+        torch.testing.assert_close(y, x.to(wire).float() * 2.0, rtol=0, atol=0)
+
+
 def test_other_collectives_single_rank(hvd):
     x = torch.randn(7, 5, device=_dev())
     torch.testing.assert_close(hvd.allgather(x, name="ag"), x)

@@ -52,8 +52,7 @@ __device__ __forceinline__ void copy_bytes(const char* src, char* dst,
       ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0;
   if (vec_ok) {
     const int64_t nv = n >> 4;
-    for (int64_t i = threadIdx.x; i < nv; i += THREADS) {
-      const uint4 v = ld16(reinterpret_cast<const uint4*>(src) + i);
+    auto put = [&](int64_t i, uint4 v) {
       if (target == TO_ALL_MC) {
         multimem_st16(ctx.mc + staging_off + (i << 4), v);
       } else if (target == TO_ALL_LOOP) {
@@ -62,7 +61,19 @@ __device__ __forceinline__ void copy_bytes(const char* src, char* dst,
       } else {
         st16(reinterpret_cast<uint4*>(dst) + i, v);
       }
+    };
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    int64_t i = threadIdx.x;
+    // Four loads in flight per thread before the first store.
+    for (; i + 3 * THREADS < nv; i += 4 * THREADS) {
+      const uint4 a = ld16(s4 + i), b = ld16(s4 + i + THREADS);
+      const uint4 c = ld16(s4 + i + 2 * THREADS), d = ld16(s4 + i + 3 * THREADS);
+      put(i, a);
+      put(i + THREADS, b);
+      put(i + 2 * THREADS, c);
+      put(i + 3 * THREADS, d);
     }
+    for (; i < nv; i += THREADS) put(i, ld16(s4 + i));
     src += nv << 4;
     dst += nv << 4;
     staging_off += nv << 4;

@@ -54,14 +54,15 @@ fused_allreduce_kernel(TensorList tl, SymmCtx ctx,
     const int64_t lo = b * per, hi = min(lo + per, nvec);
     // No staging on a single rank: gather (scale, round through the wire
     // type) and write straight back to the outputs.
-    const S both = prescale * postscale;
     int cout = lo < hi ? find_tensor(tl, lo * N) : 0;
+    // Same arithmetic as the multi-rank variants: prescale, round to the
+    // wire type, postscale.
     gather_range<T, W, S, THREADS>(
-        tl, lo, hi, both, pre || post, [&](int64_t v, uint4 x) {
+        tl, lo, hi, prescale, pre, [&](int64_t v, uint4 x) {
           // Vectors arrive in increasing order per thread only inside one
           // tensor; re-seek when the walker moved on to the next tensor.
           if (v * N < __ldg(tl.offsets + cout)) cout = find_tensor(tl, v * N);
-          scatter_vec<T, W, S>(tl, cout, v * N, x, S(1), false);
+          scatter_vec<T, W, S>(tl, cout, v * N, x, postscale, post);
         });
     return;
   } else if constexpr (ALGO == static_cast<int>(Algo::ONESHOT)) {

@@ -54,21 +54,38 @@ reducescatter_kernel(const T* in, T* out, const int64_t* shard_begin,
     const int64_t lo = b * per, hi = min(lo + per, vecs);
     const T* src = in + sb[r];
     const bool aligned = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
-    for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS) {
+    // Full, aligned vectors first (four loads in flight per thread), then
+    // the ragged rest element by element.
+    const int64_t vfull = aligned ? max(lo, min(hi, n / N)) : lo;
+    {
+      const uint4* s4 = reinterpret_cast<const uint4*>(src);
+      uint4* d4 = stage + vbase[r];
+      auto conv = [&](uint4 raw) {
+        if (!pre) return raw;
+        WireVec<T> w;
+        w.raw = raw;
+#pragma unroll
+        for (int i = 0; i < N; ++i) w.e[i] = scale_cast<T>(w.e[i], prescale, true);
+        return w.raw;
+      };
+      int64_t v = lo + threadIdx.x;
+      for (; v + 3 * THREADS < vfull; v += 4 * THREADS) {
+        const uint4 a = ld16_stream(s4 + v), b2 = ld16_stream(s4 + v + THREADS);
+        const uint4 c = ld16_stream(s4 + v + 2 * THREADS), d = ld16_stream(s4 + v + 3 * THREADS);
+        st16(d4 + v, conv(a));
+        st16(d4 + v + THREADS, conv(b2));
+        st16(d4 + v + 2 * THREADS, conv(c));
+        st16(d4 + v + 3 * THREADS, conv(d));
+      }
+      for (; v < vfull; v += THREADS) st16(d4 + v, conv(ld16_stream(s4 + v)));
+    }
+    for (int64_t v = vfull + threadIdx.x; v < hi; v += THREADS) {
       WireVec<T> w;
       w.raw = make_uint4(0, 0, 0, 0);
       const int64_t e0 = v * N;
-      if (aligned && e0 + N <= n) {
-        w.raw = ld16_stream(reinterpret_cast<const uint4*>(src) + v);
-        if (pre) {
 #pragma unroll
-          for (int i = 0; i < N; ++i) w.e[i] = scale_cast<T>(w.e[i], prescale, true);
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < N; ++i)
-          if (e0 + i < n) w.e[i] = scale_cast<T>(src[e0 + i], prescale, pre);
-      }
+      for (int i = 0; i < N; ++i)
+        if (e0 + i < n) w.e[i] = scale_cast<T>(src[e0 + i], prescale, pre);
       st16(stage + vbase[r] + v, w.raw);
     }
   }

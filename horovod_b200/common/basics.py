@@ -318,6 +318,12 @@ class HorovodBasics:
     def rocm_built(self):
         return False
 
+    def topology(self):
+        """What the GPUs of this box look like: peer access / P2P attributes
+        between every pair, active NVLink links, NVLink multicast support
+        (dict; device_count is 0 without a GPU)."""
+        return _native().gpu_topology()
+
     def gpu_backend(self):
         """Which device data path is active: "symm ..." (NVLink kernels over
         symmetric memory), "nccl" or "none"."""

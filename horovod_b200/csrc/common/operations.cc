@@ -6,6 +6,7 @@
 #include "../ops/cpu_ops.h"
 #include "env.h"
 #include "logging.h"
+#include "nvtx_op_range.h"
 
 namespace hvd {
 
@@ -235,6 +236,7 @@ void BackgroundThreadLoop(GlobalState& s) {
     DiscoverLayout(s);
 
     s.elastic_enabled = EnvBool(HVD_ENV_ELASTIC, false);
+    NvtxSetEnabled(!EnvBool(HVD_ENV_DISABLE_NVTX, false));
     s.dynamic_process_sets = EnvBool("HOROVOD_DYNAMIC_PROCESS_SETS", false);
 
     std::string tl = EnvString(HVD_ENV_TIMELINE);
@@ -453,6 +455,17 @@ Status FindSet(int32_t id, ProcessSet** out) {
   return Status::OK();
 }
 
+// Opens an NVTX range now and closes it when the entry completes.
+void AttachNvtxRange(TensorTableEntry& e, NvtxOp op) {
+  NvtxRangeId id = NvtxRangeStart(op, e.name, e.size_bytes());
+  if (id == 0) return;
+  StatusCallback inner = std::move(e.callback);
+  e.callback = [inner, id](const Completion& c) {
+    NvtxRangeEnd(id);
+    if (inner) inner(c);
+  };
+}
+
 Request MakeRequest(const TensorTableEntry& e, Request::Type type, int rank) {
   Request q;
   q.request_rank = rank;
@@ -509,6 +522,7 @@ Status EnqueueTensorAllreduces(std::vector<TensorTableEntry>& entries,
     e.process_set_id = process_set_id;
     e.group_id = group_id;
     e.enqueue_us = now;
+    AttachNvtxRange(e, entries.size() > 1 ? NvtxOp::GROUPED_ALLREDUCE : NvtxOp::ALLREDUCE);
     requests.push_back(MakeRequest(e, type, ps->comm.rank()));
   }
   st = ps->tensor_queue.AddToTensorQueueMulti(entries, requests);
@@ -526,6 +540,7 @@ Status EnqueueTensorAllgather(TensorTableEntry entry, int32_t process_set_id) {
   if (!st.ok()) return st;
   entry.process_set_id = process_set_id;
   entry.enqueue_us = NowMicros();
+  AttachNvtxRange(entry, NvtxOp::ALLGATHER);
   Request q = MakeRequest(entry, Request::ALLGATHER, ps->comm.rank());
   return ps->tensor_queue.AddToTensorQueue(std::move(entry), std::move(q));
 }
@@ -547,6 +562,7 @@ Status EnqueueTensorBroadcast(TensorTableEntry entry, int root_rank,
   entry.root_rank = set_root;
   entry.process_set_id = process_set_id;
   entry.enqueue_us = NowMicros();
+  AttachNvtxRange(entry, NvtxOp::BROADCAST);
   Request q = MakeRequest(entry, Request::BROADCAST, ps->comm.rank());
   return ps->tensor_queue.AddToTensorQueue(std::move(entry), std::move(q));
 }
@@ -582,6 +598,7 @@ Status EnqueueTensorAlltoall(TensorTableEntry entry, int32_t process_set_id) {
   }
   entry.process_set_id = process_set_id;
   entry.enqueue_us = NowMicros();
+  AttachNvtxRange(entry, NvtxOp::ALLTOALL);
   Request q = MakeRequest(entry, Request::ALLTOALL, ps->comm.rank());
   return ps->tensor_queue.AddToTensorQueue(std::move(entry), std::move(q));
 }
@@ -603,6 +620,7 @@ Status EnqueueTensorReducescatter(TensorTableEntry entry, ReduceOp op,
   entry.postscale = postscale;
   entry.process_set_id = process_set_id;
   entry.enqueue_us = NowMicros();
+  AttachNvtxRange(entry, NvtxOp::REDUCESCATTER);
   Request q = MakeRequest(entry, Request::REDUCESCATTER, ps->comm.rank());
   return ps->tensor_queue.AddToTensorQueue(std::move(entry), std::move(q));
 }

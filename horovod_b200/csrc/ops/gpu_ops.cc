@@ -8,6 +8,7 @@
 #include "../common/logging.h"
 #include "../common/operations.h"
 #include "gpu_internal.h"
+#include "../symm/topology.h"
 #include "nccl_ops.h"
 
 namespace hvd {
@@ -161,6 +162,8 @@ void GpuOps::EnsureArena(ProcessSet& ps) {
     SetGpuBackendDescription("nccl");
     return;
   }
+  if (state_.config.rank == 0)
+    HVD_LOG(INFO) << "GPU topology: " << DiscoverTopology().Summary();
   size_t mb = static_cast<size_t>(EnvInt(HVD_ENV_SYMM_BUFFER_MB, 512));
   // The token doubles as socket-name salt: distinct per job and per init.
   uint64_t token = state_.config.token ^ 0x9e3779b97f4a7c15ull;

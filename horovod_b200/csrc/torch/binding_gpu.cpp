@@ -5,6 +5,7 @@
 #include "../kernels/kernels.h"
 #include "../ops/gpu_internal.h"
 #include "../ops/gpu_ops.h"
+#include "../symm/topology.h"
 
 namespace py = pybind11;
 
@@ -12,6 +13,22 @@ namespace hvd {
 
 void BindGpuDiagnostics(py::module_& m) {
   m.def("gpu_backend", &GpuBackendDescription);
+  m.def("gpu_topology", []() {
+    GpuTopology t = DiscoverTopology();
+    py::dict d;
+    d["device_count"] = t.device_count;
+    d["names"] = t.names;
+    d["sm_counts"] = t.sm_counts;
+    d["memory_bytes"] = t.memory_bytes;
+    d["multicast_supported"] = t.multicast_supported;
+    d["nvlink_active_links"] = t.nvlink_active_links;
+    d["peer_access"] = t.peer_access;
+    d["native_atomics"] = t.native_atomics;
+    d["performance_rank"] = t.performance_rank;
+    d["all_pairs_peer"] = t.all_pairs_peer;
+    d["summary"] = t.Summary();
+    return d;
+  });
   m.def("gpu_op_stats", []() {
     // (response type, payload bytes, tensors, device microseconds) of every
     // device collective since the last call; needs HOROVOD_GPU_OP_TIMING=1.

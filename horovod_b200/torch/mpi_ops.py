@@ -44,6 +44,7 @@ ccl_built = _basics.ccl_built
 cuda_built = _basics.cuda_built
 rocm_built = _basics.rocm_built
 gpu_backend = _basics.gpu_backend
+topology = _basics.topology
 
 
 class _ReduceOps:

@@ -37,6 +37,8 @@ def parse_args():
                    choices=["resnet50", "bert-large", "gpt2-medium"])
     p.add_argument("--batch", type=int, default=0, help="per-GPU batch (0 = config default)")
     p.add_argument("--backend", default=None, help="symm | nccl (HOROVOD_GPU_BACKEND)")
+    p.add_argument("--symmetric-gradients", type=int, default=1,
+                   help="1: gradients live in the symmetric heap and are reduced in place")
     return p.parse_args()
 
 
@@ -173,7 +175,8 @@ def main():
     (model, base_opt, host_x, host_y, to_dev, loss_fn, batch, cfg, metric,
      unit) = build_workload(args, torch, device)
     if args.model == "resnet50":
-        opt = hvd.DistributedOptimizer(base_opt, named_parameters=model.named_parameters())
+        opt = hvd.DistributedOptimizer(base_opt, named_parameters=model.named_parameters(),
+                                       symmetric_gradients=bool(args.symmetric_gradients))
     elif args.model == "bert-large":
         opt = hvd.DistributedOptimizer(base_opt, named_parameters=model.named_parameters(),
                                        compression=hvd.Compression.fp16)
@@ -253,6 +256,8 @@ def main():
                     "l2": "inputs larger than L2 (%.0f MB activations+batch per step)"
                           % (h2d / 1e6),
                     "gradient_path": hvd.gpu_backend(),
+                    "symmetric_gradients": bool(args.symmetric_gradients and args.gpus > 1
+                                                and args.model == "resnet50"),
                     "fusion_threshold_mb": 128, "cycle_time_ms": 1.0})
         out = {
             "metric": metric, "value": round(value, 2), "unit": unit,

@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(THREADS)
 adasum_pack_kernel(TensorList tl, SymmCtx ctx, float prescale, double* scratch,
                    int scratch_doubles) {
   constexpr int N = 4;
-  const int64_t nvec = __ldg(tl.offsets + tl.n) / N;
+  const int64_t nvec = tl.offsets[tl.n] / N;
   const int64_t per = (nvec + gridDim.x - 1) / gridDim.x;
   const int64_t lo = blockIdx.x * per, hi = min(lo + per, nvec);
   for (int i = blockIdx.x * THREADS + threadIdx.x; i < scratch_doubles;
@@ -74,7 +74,7 @@ adasum_dots_kernel(TensorList tl, SymmCtx ctx, int level, uint32_t epoch,
                    double* scratch_level) {
   constexpr int N = 4;
   if (!cta_barrier(ctx, epoch, blockIdx.x, 10 + 2 * level)) return;
-  const int64_t nvec = __ldg(tl.offsets + tl.n) / N;
+  const int64_t nvec = tl.offsets[tl.n] / N;
   const Range keep = owned_range(nvec, ctx.rank, level + 1);
   const int partner = ctx.rank ^ (1 << level);
   const bool lower = ((ctx.rank >> level) & 1) == 0;
@@ -92,7 +92,7 @@ adasum_dots_kernel(TensorList tl, SymmCtx ctx, int level, uint32_t epoch,
     int cur = find_tensor(tl, (lo + threadIdx.x) * N);
     for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS) {
       const int64_t elem = v * N;
-      while (cur + 1 < tl.n && elem >= __ldg(tl.offsets + cur + 1)) ++cur;
+      while (cur + 1 < tl.n && elem >= tl.offsets[cur + 1]) ++cur;
       if (cur != t) {
         flush_sums(scratch_level, t, d, na, nb);
         t = cur;
@@ -131,7 +131,7 @@ adasum_combine_kernel(TensorList tl, SymmCtx ctx, int level, uint32_t epoch,
                       int64_t scratch_level_off) {
   constexpr int N = 4;
   if (!cta_barrier(ctx, epoch, blockIdx.x, 11 + 2 * level)) return;
-  const int64_t nvec = __ldg(tl.offsets + tl.n) / N;
+  const int64_t nvec = tl.offsets[tl.n] / N;
   const Range keep = owned_range(nvec, ctx.rank, level + 1);
   const int partner = ctx.rank ^ (1 << level);
   const bool lower = ((ctx.rank >> level) & 1) == 0;
@@ -149,7 +149,7 @@ adasum_combine_kernel(TensorList tl, SymmCtx ctx, int level, uint32_t epoch,
   float ca = 1.f, cb = 1.f;
   for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS) {
     const int64_t elem = v * N;
-    while (cur + 1 < tl.n && elem >= __ldg(tl.offsets + cur + 1)) ++cur;
+    while (cur + 1 < tl.n && elem >= tl.offsets[cur + 1]) ++cur;
     if (cur != t) {
       t = cur;
       double d = 0, na = 0, nb = 0;
@@ -181,7 +181,7 @@ adasum_gather_kernel(TensorList tl, SymmCtx ctx, int levels, uint32_t epoch,
                      float postscale) {
   constexpr int N = 4;
   if (!cta_barrier(ctx, epoch, blockIdx.x, 30)) return;
-  const int64_t nvec = __ldg(tl.offsets + tl.n) / N;
+  const int64_t nvec = tl.offsets[tl.n] / N;
   const bool post = postscale != 1.0f;
   for (int q = 0; q < ctx.world; ++q) {
     const Range own = owned_range(nvec, q, levels);

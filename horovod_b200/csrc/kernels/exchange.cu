@@ -91,9 +91,48 @@ __device__ __forceinline__ void copy_bytes(const char* src, char* dst,
   }
 }
 
+// INLINE: the plan rides in the kernel parameters and is copied to shared
+// memory first (parameter reads with compile-time offsets only); else it is
+// read from device memory.
+template <bool INLINE>
 __global__ void __launch_bounds__(THREADS)
-exchange_kernel(ExchangePlan plan, SymmCtx ctx) {
+exchange_kernel(const InlineExchange inl, const ExchangePlan plan_dev, SymmCtx ctx) {
   const int b = blockIdx.x, G = gridDim.x;
+  constexpr int SEGS = INLINE ? INLINE_SEGMENTS : 1;
+  __shared__ const void* s_out_src[SEGS];
+  __shared__ int64_t s_out_off[SEGS];
+  __shared__ int64_t s_out_bytes[SEGS];
+  __shared__ int32_t s_out_rank[SEGS];
+  __shared__ void* s_in_dst[SEGS];
+  __shared__ int64_t s_in_off[SEGS];
+  __shared__ int64_t s_in_bytes[SEGS];
+  ExchangePlan plan = plan_dev;
+  if constexpr (INLINE) {
+#pragma unroll
+    for (int i = 0; i < INLINE_SEGMENTS; ++i) {
+      if (threadIdx.x == i && i < inl.n_out) {
+        s_out_src[i] = inl.out_src[i];
+        s_out_off[i] = inl.out_staging_off[i];
+        s_out_bytes[i] = inl.out_bytes[i];
+        s_out_rank[i] = inl.out_dst_rank[i];
+      }
+      if (threadIdx.x == 32 + i && i < inl.n_in) {
+        s_in_dst[i] = inl.in_dst[i];
+        s_in_off[i] = inl.in_staging_off[i];
+        s_in_bytes[i] = inl.in_bytes[i];
+      }
+    }
+    __syncthreads();
+    plan.n_out = inl.n_out;
+    plan.out_src = s_out_src;
+    plan.out_staging_off = s_out_off;
+    plan.out_bytes = s_out_bytes;
+    plan.out_dst_rank = s_out_rank;
+    plan.n_in = inl.n_in;
+    plan.in_dst = s_in_dst;
+    plan.in_staging_off = s_in_off;
+    plan.in_bytes = s_in_bytes;
+  }
   for (int s = 0; s < plan.n_out; ++s) {
     const int64_t off = plan.out_staging_off[s], bytes = plan.out_bytes[s];
     int64_t lo, hi;
@@ -130,10 +169,15 @@ __global__ void barrier_only_kernel(SymmCtx ctx) {
 }  // namespace
 
 cudaError_t LaunchExchange(const ExchangePlan& plan, int num_ctas,
-                           const SymmCtx& ctx, cudaStream_t stream) {
+                           const SymmCtx& ctx, cudaStream_t stream,
+                           const InlineExchange* inline_plan) {
   if (num_ctas < 1 || num_ctas > SYMM_MAX_BLOCKS) return cudaErrorInvalidValue;
   CountKernelLaunches(1);
-  exchange_kernel<<<num_ctas, THREADS, 0, stream>>>(plan, ctx);
+  static const InlineExchange kNoInline = {};
+  if (inline_plan != nullptr && (inline_plan->n_out > 0 || inline_plan->n_in > 0))
+    exchange_kernel<true><<<num_ctas, THREADS, 0, stream>>>(*inline_plan, plan, ctx);
+  else
+    exchange_kernel<false><<<num_ctas, THREADS, 0, stream>>>(kNoInline, plan, ctx);
   return cudaGetLastError();
 }
 

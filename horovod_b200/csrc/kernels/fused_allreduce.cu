@@ -36,14 +36,89 @@ __device__ __forceinline__ void unpack_range(const TensorList& tl,
                                   [stage](int64_t v) { return ld16(stage + v); });
 }
 
-template <typename T, typename W, int ALGO>
+// Sum of chunk vectors [lo, hi) over all ranks by peer loads, result stored
+// into every rank's staging buffer. WORLD is a compile-time copy of
+// ctx.world so that the loads of several vectors are all issued before the
+// first add (UNROLL vectors x WORLD peers in flight per thread).
+template <typename W, int WORLD, int UNROLL>
+__device__ __forceinline__ void reduce_chunk_p2p(const SymmCtx& ctx, int64_t lo,
+                                                 int64_t hi) {
+  const int rank = ctx.rank;
+  const uint4* src[WORLD];
+  uint4* dst[WORLD];
+#pragma unroll
+  for (int i = 0; i < WORLD; ++i) {
+    // Start at a different peer on every rank to spread the load.
+    int p = rank + i;
+    if (p >= WORLD) p -= WORLD;
+    src[i] = reinterpret_cast<const uint4*>(ctx.peers[p]);
+    dst[i] = reinterpret_cast<uint4*>(ctx.peers[p]);
+  }
+  int64_t v = lo + threadIdx.x;
+  for (; v + (UNROLL - 1) * THREADS < hi; v += UNROLL * THREADS) {
+    uint4 in[UNROLL][WORLD];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+      for (int i = 0; i < WORLD; ++i) in[u][i] = ld16(src[i] + v + u * THREADS);
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      VecAcc<W> acc;
+      acc.zero();
+#pragma unroll
+      for (int i = 0; i < WORLD; ++i) acc.add(in[u][i]);
+      const uint4 sum = acc.pack();
+#pragma unroll
+      for (int i = 0; i < WORLD; ++i) st16(dst[i] + v + u * THREADS, sum);
+    }
+  }
+  for (; v < hi; v += THREADS) {
+    VecAcc<W> acc;
+    acc.zero();
+#pragma unroll
+    for (int i = 0; i < WORLD; ++i) acc.add(ld16(src[i] + v));
+    const uint4 sum = acc.pack();
+#pragma unroll
+    for (int i = 0; i < WORLD; ++i) st16(dst[i] + v, sum);
+  }
+}
+
+// INLINE: the tensor list rides in the kernel parameters (`inl`) and is
+// copied to shared memory first (parameter reads with compile-time offsets
+// only); else it is read from device memory (`tl_dev`).
+template <typename T, typename W, int ALGO, bool INLINE>
 __global__ void __launch_bounds__(THREADS)
-fused_allreduce_kernel(TensorList tl, SymmCtx ctx,
-                       typename ScaleT<T>::type prescale,
+fused_allreduce_kernel(const InlineTensors inl, const TensorList tl_dev,
+                       SymmCtx ctx, typename ScaleT<T>::type prescale,
                        typename ScaleT<T>::type postscale) {
   using S = typename ScaleT<T>::type;
   constexpr int N = 16 / sizeof(W);
-  const int64_t nvec = __ldg(tl.offsets + tl.n) / N;
+  __shared__ int64_t s_offsets[INLINE ? INLINE_TENSORS + 1 : 1];
+  __shared__ int64_t s_counts[INLINE ? INLINE_TENSORS : 1];
+  __shared__ const void* s_in[INLINE ? INLINE_TENSORS : 1];
+  __shared__ void* s_out[INLINE ? INLINE_TENSORS : 1];
+  TensorList tl = tl_dev;
+  if constexpr (INLINE) {
+#pragma unroll
+    for (int i = 0; i < INLINE_TENSORS; ++i) {
+      if (threadIdx.x == i && i < inl.n) {
+        s_offsets[i] = inl.offsets[i];
+        s_counts[i] = inl.counts[i];
+        s_in[i] = inl.in[i];
+        s_out[i] = inl.out[i];
+      }
+    }
+#pragma unroll
+    for (int i = 1; i <= INLINE_TENSORS; ++i)
+      if (threadIdx.x == 32 && i == inl.n) s_offsets[i] = inl.offsets[i];
+    __syncthreads();
+    tl.n = inl.n;
+    tl.offsets = s_offsets;
+    tl.counts = s_counts;
+    tl.in = s_in;
+    tl.out = s_out;
+  }
+  const int64_t nvec = tl.offsets[tl.n] / N;
   const int world = ctx.world, rank = ctx.rank;
   const int G = gridDim.x, b = blockIdx.x;
   const bool pre = prescale != S(1), post = postscale != S(1);
@@ -61,7 +136,7 @@ fused_allreduce_kernel(TensorList tl, SymmCtx ctx,
         tl, lo, hi, prescale, pre, [&](int64_t v, uint4 x) {
           // Vectors arrive in increasing order per thread only inside one
           // tensor; re-seek when the walker moved on to the next tensor.
-          if (v * N < __ldg(tl.offsets + cout)) cout = find_tensor(tl, v * N);
+          if (v * N < tl.offsets[cout]) cout = find_tensor(tl, v * N);
           scatter_vec<T, W, S>(tl, cout, v * N, x, postscale, post);
         });
     return;
@@ -82,8 +157,9 @@ fused_allreduce_kernel(TensorList tl, SymmCtx ctx,
         if (p < world) acc.add(in[p]);
       return acc.pack();
     });
-    // Nobody may repack its staging buffer while a peer still reads it.
-    cta_barrier(ctx, ctx.epoch + 2, b, 2);
+    // Nobody may repack its staging buffer while a peer still reads it
+    // (unless the caller alternates between two staging regions).
+    if (!ctx.skip_end_barrier) cta_barrier(ctx, ctx.epoch + 2, b, 2);
     return;
   } else {
     const int64_t per_rank = (nvec + world - 1) / world;
@@ -113,31 +189,14 @@ fused_allreduce_kernel(TensorList tl, SymmCtx ctx,
         for (; v < hi; v += THREADS)
           multimem_st16(mc + v, Multimem<W>::ld_reduce(mc + v));
       } else {
-        for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS) {
-          uint4 in[SYMM_MAX_RANKS];
-#pragma unroll
-          for (int i = 0; i < SYMM_MAX_RANKS; ++i) {
-            // Start at a different peer on every rank to spread the load.
-            if (i < world) {
-              int p = rank + i;
-              if (p >= world) p -= world;
-              in[i] = ld16(reinterpret_cast<const uint4*>(ctx.peers[p]) + v);
-            }
-          }
-          VecAcc<W> acc;
-          acc.zero();
-#pragma unroll
-          for (int i = 0; i < SYMM_MAX_RANKS; ++i)
-            if (i < world) acc.add(in[i]);
-          const uint4 sum = acc.pack();
-#pragma unroll
-          for (int i = 0; i < SYMM_MAX_RANKS; ++i) {
-            if (i < world) {
-              int p = rank + i;
-              if (p >= world) p -= world;
-              st16(reinterpret_cast<uint4*>(ctx.peers[p]) + v, sum);
-            }
-          }
+        switch (world) {
+        case 2: reduce_chunk_p2p<W, 2, 4>(ctx, lo, hi); break;
+        case 3: reduce_chunk_p2p<W, 3, 2>(ctx, lo, hi); break;
+        case 4: reduce_chunk_p2p<W, 4, 2>(ctx, lo, hi); break;
+        case 5: reduce_chunk_p2p<W, 5, 1>(ctx, lo, hi); break;
+        case 6: reduce_chunk_p2p<W, 6, 1>(ctx, lo, hi); break;
+        case 7: reduce_chunk_p2p<W, 7, 1>(ctx, lo, hi); break;
+        default: reduce_chunk_p2p<W, 8, 1>(ctx, lo, hi); break;
         }
       }
     }
@@ -150,27 +209,25 @@ fused_allreduce_kernel(TensorList tl, SymmCtx ctx,
   }
 }
 
-template <typename T, typename W>
-cudaError_t LaunchTyped(const TensorList& tl, double prescale, double postscale,
-                        Algo algo, int num_ctas, const SymmCtx& ctx,
-                        cudaStream_t stream) {
-  using S = typename ScaleT<T>::type;
-  const S pre = static_cast<S>(prescale), post = static_cast<S>(postscale);
+template <typename T, typename W, bool INLINE>
+cudaError_t LaunchAlgo(const InlineTensors& inl, const TensorList& tl, Algo algo,
+                       int num_ctas, const SymmCtx& ctx, cudaStream_t stream,
+                       typename ScaleT<T>::type pre, typename ScaleT<T>::type post) {
   switch (algo) {
   case Algo::LOCAL:
-    fused_allreduce_kernel<T, W, 0><<<num_ctas, THREADS, 0, stream>>>(tl, ctx, pre, post);
+    fused_allreduce_kernel<T, W, 0, INLINE><<<num_ctas, THREADS, 0, stream>>>(inl, tl, ctx, pre, post);
     break;
   case Algo::ONESHOT:
-    fused_allreduce_kernel<T, W, 1><<<num_ctas, THREADS, 0, stream>>>(tl, ctx, pre, post);
+    fused_allreduce_kernel<T, W, 1, INLINE><<<num_ctas, THREADS, 0, stream>>>(inl, tl, ctx, pre, post);
     break;
   case Algo::TWOSHOT:
-    fused_allreduce_kernel<T, W, 2><<<num_ctas, THREADS, 0, stream>>>(tl, ctx, pre, post);
+    fused_allreduce_kernel<T, W, 2, INLINE><<<num_ctas, THREADS, 0, stream>>>(inl, tl, ctx, pre, post);
     break;
   case Algo::NVLS:
     if constexpr (std::is_same<W, float>::value || std::is_same<W, __half>::value ||
                   std::is_same<W, __nv_bfloat16>::value) {
       if (ctx.mc == nullptr) return cudaErrorInvalidValue;
-      fused_allreduce_kernel<T, W, 3><<<num_ctas, THREADS, 0, stream>>>(tl, ctx, pre, post);
+      fused_allreduce_kernel<T, W, 3, INLINE><<<num_ctas, THREADS, 0, stream>>>(inl, tl, ctx, pre, post);
     } else {
       return cudaErrorInvalidValue;
     }
@@ -179,36 +236,49 @@ cudaError_t LaunchTyped(const TensorList& tl, double prescale, double postscale,
   return cudaGetLastError();
 }
 
+template <typename T, typename W>
+cudaError_t LaunchTyped(const TensorList& tl, double prescale, double postscale,
+                        Algo algo, int num_ctas, const SymmCtx& ctx,
+                        cudaStream_t stream, const InlineTensors* inline_list) {
+  using S = typename ScaleT<T>::type;
+  const S pre = static_cast<S>(prescale), post = static_cast<S>(postscale);
+  static const InlineTensors kNoInline = {};
+  if (inline_list != nullptr && inline_list->n > 0)
+    return LaunchAlgo<T, W, true>(*inline_list, tl, algo, num_ctas, ctx, stream, pre, post);
+  return LaunchAlgo<T, W, false>(kNoInline, tl, algo, num_ctas, ctx, stream, pre, post);
+}
+
 }  // namespace
 
 cudaError_t LaunchFusedAllreduce(const TensorList& tl, DataType dtype,
                                  DataType wire, double prescale,
                                  double postscale, Algo algo, int num_ctas,
-                                 const SymmCtx& ctx, cudaStream_t stream) {
+                                 const SymmCtx& ctx, cudaStream_t stream,
+                                 const InlineTensors* inline_list) {
   if (num_ctas < 1 || num_ctas > SYMM_MAX_BLOCKS) return cudaErrorInvalidValue;
   CountKernelLaunches(1);
   if (dtype == DataType::FLOAT32 && wire == DataType::BFLOAT16)
-    return LaunchTyped<float, __nv_bfloat16>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+    return LaunchTyped<float, __nv_bfloat16>(tl, prescale, postscale, algo, num_ctas, ctx, stream, inline_list);
   if (dtype == DataType::FLOAT32 && wire == DataType::FLOAT16)
-    return LaunchTyped<float, __half>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+    return LaunchTyped<float, __half>(tl, prescale, postscale, algo, num_ctas, ctx, stream, inline_list);
   if (dtype != wire) return cudaErrorInvalidValue;
   switch (dtype) {
   case DataType::FLOAT32:
-    return LaunchTyped<float, float>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+    return LaunchTyped<float, float>(tl, prescale, postscale, algo, num_ctas, ctx, stream, inline_list);
   case DataType::FLOAT16:
-    return LaunchTyped<__half, __half>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+    return LaunchTyped<__half, __half>(tl, prescale, postscale, algo, num_ctas, ctx, stream, inline_list);
   case DataType::BFLOAT16:
-    return LaunchTyped<__nv_bfloat16, __nv_bfloat16>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+    return LaunchTyped<__nv_bfloat16, __nv_bfloat16>(tl, prescale, postscale, algo, num_ctas, ctx, stream, inline_list);
   case DataType::FLOAT64:
-    return LaunchTyped<double, double>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+    return LaunchTyped<double, double>(tl, prescale, postscale, algo, num_ctas, ctx, stream, inline_list);
   case DataType::INT32:
-    return LaunchTyped<int32_t, int32_t>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+    return LaunchTyped<int32_t, int32_t>(tl, prescale, postscale, algo, num_ctas, ctx, stream, inline_list);
   case DataType::INT64:
-    return LaunchTyped<int64_t, int64_t>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+    return LaunchTyped<int64_t, int64_t>(tl, prescale, postscale, algo, num_ctas, ctx, stream, inline_list);
   case DataType::UINT8:
-    return LaunchTyped<uint8_t, uint8_t>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+    return LaunchTyped<uint8_t, uint8_t>(tl, prescale, postscale, algo, num_ctas, ctx, stream, inline_list);
   case DataType::INT8:
-    return LaunchTyped<int8_t, int8_t>(tl, prescale, postscale, algo, num_ctas, ctx, stream);
+    return LaunchTyped<int8_t, int8_t>(tl, prescale, postscale, algo, num_ctas, ctx, stream, inline_list);
   default:
     return cudaErrorInvalidValue;
   }

@@ -33,6 +33,10 @@ struct SymmCtx {
   uint32_t epoch;  // flags of this launch take values epoch+1, epoch+2, ...
   unsigned long long timeout_ns;
   int* status;  // host-mapped KernelStatus
+  // When non-zero the kernel may skip its trailing barrier: the caller
+  // guarantees that the staging region used by this launch is not written
+  // again before every peer has passed a later barrier (double buffering).
+  int skip_end_barrier;
 };
 
 // Written by a kernel whose bounded wait ran out. code 0 = fine.
@@ -62,6 +66,18 @@ struct TensorList {
   void* const* out;        // n entries
 };
 
+// Small tensor lists travel inside the kernel's parameters instead of device
+// memory, which saves the host-to-device descriptor copy in front of
+// latency-bound launches.
+constexpr int INLINE_TENSORS = 32;
+struct InlineTensors {
+  int n;  // 0 = not used, read the TensorList in device memory
+  int64_t offsets[INLINE_TENSORS + 1];
+  int64_t counts[INLINE_TENSORS];
+  const void* in[INLINE_TENSORS];
+  void* out[INLINE_TENSORS];
+};
+
 // Number of barrier epochs a launch of each kernel consumes.
 constexpr uint32_t EPOCHS_PER_LAUNCH = 4;
 // The Adasum driver launches 2 * log2(world) + 2 kernels, one epoch each.
@@ -73,10 +89,35 @@ constexpr uint32_t ADASUM_EPOCHS = 16;
 // dtype: element type of the tensors. wire: element type in the staging
 // buffer and on NVLink (same as dtype, or FLOAT16/BFLOAT16 for FLOAT32
 // tensors). Returns cudaErrorInvalidValue for unsupported combinations.
+// `inline_list` (optional): the same list carried in the kernel parameters;
+// when given, `tensors` is ignored.
 cudaError_t LaunchFusedAllreduce(const TensorList& tensors, DataType dtype,
                                  DataType wire, double prescale,
                                  double postscale, Algo algo, int num_ctas,
-                                 const SymmCtx& ctx, cudaStream_t stream);
+                                 const SymmCtx& ctx, cudaStream_t stream,
+                                 const InlineTensors* inline_list = nullptr);
+
+// In-place allreduce (sum, then scale) of byte ranges of the symmetric arena:
+// range i covers bytes [byte_off[i], byte_off[i] + bytes[i]) of every rank's
+// arena (offsets from the arena base, 16-byte aligned starts); vec_start is
+// the running count of 16-byte vectors (a ragged tail counts as one), n + 1
+// entries. No staging, no copies: see inplace_allreduce.cu.
+struct RangeList {
+  int n;
+  const int64_t* vec_start;
+  const int64_t* byte_off;
+  const int64_t* bytes;
+};
+struct InlineRanges {
+  int n;  // 0 = not used
+  int64_t vec_start[INLINE_TENSORS + 1];
+  int64_t byte_off[INLINE_TENSORS];
+  int64_t bytes[INLINE_TENSORS];
+};
+cudaError_t LaunchInplaceAllreduce(const RangeList& ranges, DataType dtype,
+                                   double scale, bool use_nvls, int num_ctas,
+                                   const SymmCtx& ctx, cudaStream_t stream,
+                                   const InlineRanges* inline_ranges = nullptr);
 
 // Fused reduce-scatter: like the first half of the two-shot allreduce; rank
 // r's output receives elements [shard_begin[r], shard_begin[r+1]) of the
@@ -105,8 +146,21 @@ struct ExchangePlan {
   const int64_t* in_staging_off;  // byte offset in the local staging
   const int64_t* in_bytes;
 };
+// Short plans can ride in the kernel parameters (no descriptor copy).
+constexpr int INLINE_SEGMENTS = 16;
+struct InlineExchange {
+  int n_out, n_in;  // both 0 = not used
+  const void* out_src[INLINE_SEGMENTS];
+  int64_t out_staging_off[INLINE_SEGMENTS];
+  int64_t out_bytes[INLINE_SEGMENTS];
+  int32_t out_dst_rank[INLINE_SEGMENTS];
+  void* in_dst[INLINE_SEGMENTS];
+  int64_t in_staging_off[INLINE_SEGMENTS];
+  int64_t in_bytes[INLINE_SEGMENTS];
+};
 cudaError_t LaunchExchange(const ExchangePlan& plan, int num_ctas,
-                           const SymmCtx& ctx, cudaStream_t stream);
+                           const SymmCtx& ctx, cudaStream_t stream,
+                           const InlineExchange* inline_plan = nullptr);
 
 // Adasum over symmetric memory. Tensors are packed into staging as fp32
 // (prescaled), combined pairwise over log2(world) levels with per-tensor

@@ -23,7 +23,7 @@ __global__ void __launch_bounds__(THREADS)
 pack_unpack_kernel(TensorList tl, uint4* buffer, typename ScaleT<T>::type scale) {
   using S = typename ScaleT<T>::type;
   constexpr int N = 16 / sizeof(W);
-  const int64_t nvec = __ldg(tl.offsets + tl.n) / N;
+  const int64_t nvec = tl.offsets[tl.n] / N;
   const int64_t per = (nvec + gridDim.x - 1) / gridDim.x;
   const int64_t lo = blockIdx.x * per, hi = min(lo + per, nvec);
   if (lo >= hi) return;

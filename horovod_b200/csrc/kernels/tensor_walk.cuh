@@ -34,21 +34,12 @@ __device__ __forceinline__ W scale_cast(T v, S scale, bool do_scale) {
   }
 }
 
-__device__ __forceinline__ const void* ldg_ptr(const void* const* p) {
-  return reinterpret_cast<const void*>(
-      __ldg(reinterpret_cast<const unsigned long long*>(p)));
-}
-__device__ __forceinline__ const void* ldg_ptr(void* const* p) {
-  return reinterpret_cast<const void*>(
-      __ldg(reinterpret_cast<const unsigned long long*>(p)));
-}
-
 // First tensor whose range may contain fused element `elem`.
 __device__ __forceinline__ int find_tensor(const TensorList& tl, int64_t elem) {
   int lo = 0, hi = tl.n - 1;
   while (lo < hi) {
     int mid = (lo + hi + 1) >> 1;
-    if (__ldg(tl.offsets + mid) <= elem) lo = mid; else hi = mid - 1;
+    if (tl.offsets[mid] <= elem) lo = mid; else hi = mid - 1;
   }
   return lo;
 }
@@ -61,10 +52,10 @@ __device__ __forceinline__ uint4 gather_vec(const TensorList& tl, int& cur,
                                             int64_t elem, S scale,
                                             bool do_scale) {
   constexpr int N = 16 / sizeof(W);
-  while (cur + 1 < tl.n && elem >= __ldg(tl.offsets + cur + 1)) ++cur;
-  const int64_t local = elem - __ldg(tl.offsets + cur);
-  const int64_t cnt = __ldg(tl.counts + cur);
-  const T* src = static_cast<const T*>(ldg_ptr(tl.in + cur));
+  while (cur + 1 < tl.n && elem >= tl.offsets[cur + 1]) ++cur;
+  const int64_t local = elem - tl.offsets[cur];
+  const int64_t cnt = tl.counts[cur];
+  const T* src = static_cast<const T*>(tl.in[cur]);
   WireVec<W> out;
   out.raw = make_uint4(0, 0, 0, 0);
   if (src == nullptr || local >= cnt) return out.raw;
@@ -100,10 +91,10 @@ __device__ __forceinline__ void scatter_vec(const TensorList& tl, int& cur,
                                             int64_t elem, uint4 raw, S scale,
                                             bool do_scale) {
   constexpr int N = 16 / sizeof(W);
-  while (cur + 1 < tl.n && elem >= __ldg(tl.offsets + cur + 1)) ++cur;
-  const int64_t local = elem - __ldg(tl.offsets + cur);
-  const int64_t cnt = __ldg(tl.counts + cur);
-  T* dst = static_cast<T*>(const_cast<void*>(ldg_ptr(tl.out + cur)));
+  while (cur + 1 < tl.n && elem >= tl.offsets[cur + 1]) ++cur;
+  const int64_t local = elem - tl.offsets[cur];
+  const int64_t cnt = tl.counts[cur];
+  T* dst = static_cast<T*>(tl.out[cur]);
   if (dst == nullptr || local >= cnt) return;
   dst += local;
   WireVec<W> in;
@@ -171,11 +162,11 @@ __device__ __forceinline__ void gather_range(const TensorList& tl, int64_t lo,
   constexpr int LOADS = VEC ? N * sizeof(T) / 16 : 1;
   if (lo >= hi) return;
   for (int t = find_tensor(tl, lo * N); t < tl.n; ++t) {
-    const int64_t toff = __ldg(tl.offsets + t);
+    const int64_t toff = tl.offsets[t];
     if (toff >= hi * N) break;
-    const int64_t tend = __ldg(tl.offsets + t + 1);
-    const int64_t cnt = __ldg(tl.counts + t);
-    const T* src = static_cast<const T*>(ldg_ptr(tl.in + t));
+    const int64_t tend = tl.offsets[t + 1];
+    const int64_t cnt = tl.counts[t];
+    const T* src = static_cast<const T*>(tl.in[t]);
     const int64_t v0 = max(lo, toff / N), v1 = min(hi, tend / N);
     // Vectors that lie entirely inside the tensor's data.
     const int64_t vfull = src ? max(v0, min(v1, (toff + cnt) / N)) : v0;
@@ -252,11 +243,11 @@ __device__ __forceinline__ void scatter_range(const TensorList& tl, int64_t lo,
   constexpr int STORES = VEC ? N * sizeof(T) / 16 : 1;
   if (lo >= hi) return;
   for (int t = find_tensor(tl, lo * N); t < tl.n; ++t) {
-    const int64_t toff = __ldg(tl.offsets + t);
+    const int64_t toff = tl.offsets[t];
     if (toff >= hi * N) break;
-    const int64_t tend = __ldg(tl.offsets + t + 1);
-    const int64_t cnt = __ldg(tl.counts + t);
-    T* dst = static_cast<T*>(const_cast<void*>(ldg_ptr(tl.out + t)));
+    const int64_t tend = tl.offsets[t + 1];
+    const int64_t cnt = tl.counts[t];
+    T* dst = static_cast<T*>(tl.out[t]);
     if (dst == nullptr) continue;
     const int64_t v0 = max(lo, toff / N), v1 = min(hi, tend / N);
     const int64_t vfull = max(v0, min(v1, (toff + cnt) / N));

@@ -17,49 +17,75 @@ constexpr int64_t STAGING_ALIGN = 256;
 
 void GpuOps::LaunchExchangeSegments(const std::vector<OutSeg>& out,
                                     const std::vector<InSeg>& in, SymmSet& set) {
-  DescriptorRing::Slot slot = ring_.Acquire();
   const size_t no = out.size(), ni = in.size();
-  const void** d_src;
-  int64_t *d_ooff, *d_obytes, *d_ioff, *d_ibytes;
-  int32_t* d_dst_rank;
-  void** d_dst;
-  const void** h_src = slot.Alloc<const void*>(no + 1, &d_src);
-  int64_t* h_ooff = slot.Alloc<int64_t>(no + 1, &d_ooff);
-  int64_t* h_obytes = slot.Alloc<int64_t>(no + 1, &d_obytes);
-  int32_t* h_dst_rank = slot.Alloc<int32_t>(no + 1, &d_dst_rank);
-  void** h_dst = slot.Alloc<void*>(ni + 1, &d_dst);
-  int64_t* h_ioff = slot.Alloc<int64_t>(ni + 1, &d_ioff);
-  int64_t* h_ibytes = slot.Alloc<int64_t>(ni + 1, &d_ibytes);
-  if (!h_src || !h_ooff || !h_obytes || !h_dst_rank || !h_dst || !h_ioff || !h_ibytes)
-    throw std::runtime_error("exchange plan does not fit a descriptor slot");
   int64_t bytes = 0;
-  for (size_t i = 0; i < no; ++i) {
-    h_src[i] = out[i].src;
-    h_ooff[i] = out[i].staging_off;
-    h_obytes[i] = out[i].bytes;
-    h_dst_rank[i] = out[i].dst;
-    bytes += out[i].bytes;
-  }
-  for (size_t i = 0; i < ni; ++i) {
-    h_dst[i] = in[i].dst;
-    h_ioff[i] = in[i].staging_off;
-    h_ibytes[i] = in[i].bytes;
-    bytes += in[i].bytes;
-  }
-  ring_.Commit(slot, stream_);
+  for (auto& o : out) bytes += o.bytes;
+  for (auto& i : in) bytes += i.bytes;
   kern::ExchangePlan plan;
-  plan.n_out = static_cast<int>(no);
-  plan.out_src = d_src;
-  plan.out_staging_off = d_ooff;
-  plan.out_bytes = d_obytes;
-  plan.out_dst_rank = d_dst_rank;
-  plan.n_in = static_cast<int>(ni);
-  plan.in_dst = d_dst;
-  plan.in_staging_off = d_ioff;
-  plan.in_bytes = d_ibytes;
-  kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH);
-  cudaError_t err = kern::LaunchExchange(plan, PickCtas(bytes), ctx, stream_);
-  ring_.Release(slot, stream_);
+  std::memset(&plan, 0, sizeof(plan));
+  cudaError_t err;
+  if (no <= kern::INLINE_SEGMENTS && ni <= kern::INLINE_SEGMENTS) {
+    // Short plan: carried in the kernel parameters.
+    kern::InlineExchange inl;
+    inl.n_out = static_cast<int>(no);
+    inl.n_in = static_cast<int>(ni);
+    for (size_t i = 0; i < no; ++i) {
+      inl.out_src[i] = out[i].src;
+      inl.out_staging_off[i] = out[i].staging_off;
+      inl.out_bytes[i] = out[i].bytes;
+      inl.out_dst_rank[i] = out[i].dst;
+    }
+    for (size_t i = 0; i < ni; ++i) {
+      inl.in_dst[i] = in[i].dst;
+      inl.in_staging_off[i] = in[i].staging_off;
+      inl.in_bytes[i] = in[i].bytes;
+    }
+    if (no == 0 && ni == 0) inl.n_out = 0;
+    kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH);
+    // An empty inline plan would read as "not used": give the kernel the
+    // (equally empty) device plan in that case.
+    err = kern::LaunchExchange(plan, PickCtas(bytes), ctx, stream_,
+                               (no || ni) ? &inl : nullptr);
+  } else {
+    DescriptorRing::Slot slot = ring_.Acquire();
+    const void** d_src;
+    int64_t *d_ooff, *d_obytes, *d_ioff, *d_ibytes;
+    int32_t* d_dst_rank;
+    void** d_dst;
+    const void** h_src = slot.Alloc<const void*>(no + 1, &d_src);
+    int64_t* h_ooff = slot.Alloc<int64_t>(no + 1, &d_ooff);
+    int64_t* h_obytes = slot.Alloc<int64_t>(no + 1, &d_obytes);
+    int32_t* h_dst_rank = slot.Alloc<int32_t>(no + 1, &d_dst_rank);
+    void** h_dst = slot.Alloc<void*>(ni + 1, &d_dst);
+    int64_t* h_ioff = slot.Alloc<int64_t>(ni + 1, &d_ioff);
+    int64_t* h_ibytes = slot.Alloc<int64_t>(ni + 1, &d_ibytes);
+    if (!h_src || !h_ooff || !h_obytes || !h_dst_rank || !h_dst || !h_ioff || !h_ibytes)
+      throw std::runtime_error("exchange plan does not fit a descriptor slot");
+    for (size_t i = 0; i < no; ++i) {
+      h_src[i] = out[i].src;
+      h_ooff[i] = out[i].staging_off;
+      h_obytes[i] = out[i].bytes;
+      h_dst_rank[i] = out[i].dst;
+    }
+    for (size_t i = 0; i < ni; ++i) {
+      h_dst[i] = in[i].dst;
+      h_ioff[i] = in[i].staging_off;
+      h_ibytes[i] = in[i].bytes;
+    }
+    ring_.Commit(slot, stream_);
+    plan.n_out = static_cast<int>(no);
+    plan.out_src = d_src;
+    plan.out_staging_off = d_ooff;
+    plan.out_bytes = d_obytes;
+    plan.out_dst_rank = d_dst_rank;
+    plan.n_in = static_cast<int>(ni);
+    plan.in_dst = d_dst;
+    plan.in_staging_off = d_ioff;
+    plan.in_bytes = d_ibytes;
+    kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH);
+    err = kern::LaunchExchange(plan, PickCtas(bytes), ctx, stream_);
+    ring_.Release(slot, stream_);
+  }
   if (err != cudaSuccess)
     throw std::runtime_error(std::string("exchange kernel launch failed: ") +
                              cudaGetErrorString(err));

@@ -3,6 +3,7 @@
 // kernel paths; nccl_ops.cc: the NCCL path).
 #pragma once
 
+#include <atomic>
 #include <functional>
 #include <map>
 #include <memory>
@@ -93,7 +94,14 @@ struct SymmSet {
   uint32_t* flags_local = nullptr;
   uint32_t* flags_peers[SYMM_MAX_RANKS] = {};
   uint32_t epoch = 0;
-  size_t data_bytes = 0;
+  size_t data_bytes = 0;  // general staging capacity
+  // Global set only: two small regions behind the general staging area that
+  // one-shot allreduces alternate between, which lets them drop their
+  // trailing barrier (a region is rewritten only two launches later, after
+  // every peer has passed the barrier of the launch in between).
+  int64_t oneshot_off[2] = {0, 0};
+  int64_t oneshot_bytes = 0;
+  uint32_t oneshot_count = 0;
 };
 
 class NcclOps;
@@ -121,6 +129,18 @@ public:
   // Waits for the recorded ops to finish and returns (and clears) the list.
   std::vector<OpTiming> DrainTimings();
 
+  // Symmetric heap: memory inside the arena that callers can hold tensors
+  // in. Allocation is a bump pointer and must be called with the same sizes
+  // in the same order on every rank (the offset is what makes a tensor
+  // symmetric). Returns the local address, or nullptr when the arena does
+  // not exist or the heap is full. Thread-safe.
+  void* SymmHeapAlloc(size_t bytes, int64_t* offset);
+  // Offset from the arena base if [p, p+bytes) lies inside the local heap.
+  bool InSymmHeap(const void* p, int64_t bytes, int64_t* offset) const;
+  int64_t symm_heap_bytes() const { return heap_bytes_; }
+  int64_t symm_heap_used() const { return heap_used_.load(); }
+  int device() const { return device_; }
+
   // Used by the NCCL path.
   cudaStream_t stream() const { return stream_; }
   DescriptorRing& ring() { return ring_; }
@@ -132,7 +152,8 @@ private:
   void EnsureDevice(int device);
   void EnsureArena(ProcessSet& ps);
   SymmSet* GetSymmSet(ProcessSet& ps);
-  kern::SymmCtx MakeCtx(SymmSet& set, uint32_t epochs);
+  kern::SymmCtx MakeCtx(SymmSet& set, uint32_t epochs, int64_t staging_off = 0,
+                        bool skip_end_barrier = false);
   Status CheckKernelStatus();
   int PickCtas(int64_t bytes) const;
   kern::Algo PickAlgo(const SymmSet& set, DataType wire, int64_t bytes) const;
@@ -146,6 +167,10 @@ private:
                       SymmSet& set);
   Status SymmReducescatter(std::vector<TensorTableEntry>& entries,
                            SymmSet& set);
+  // Zero-copy path for tensors living in the symmetric heap. Returns false
+  // (and launches nothing) when the entries do not qualify.
+  bool TryInplaceAllreduce(std::vector<TensorTableEntry>& entries,
+                           const Response& response, SymmSet& set, Status* status);
   // One exchange-kernel launch for the given segment lists.
   void LaunchExchangeSegments(const std::vector<OutSeg>& out,
                               const std::vector<InSeg>& in, SymmSet& set);
@@ -158,6 +183,7 @@ private:
   unsigned long long timeout_ns_ = 0;
   int64_t oneshot_max_ = 0, nvls_min_ = 0;
   int forced_ctas_ = 0;
+  bool inline_descriptors_ = true;
   std::string forced_algo_;
   int device_ = -1;
   cudaStream_t stream_ = nullptr;
@@ -165,6 +191,10 @@ private:
   DescriptorRing ring_;
   SymmArena arena_;
   bool arena_tried_ = false;
+  int64_t heap_off_ = 0;     // start of the symmetric heap inside the arena
+  int64_t heap_bytes_ = 0;
+  std::atomic<int64_t> heap_used_{0};
+  char* heap_base_ = nullptr;  // local address of heap_off_
   kern::KernelStatus* status_host_ = nullptr;  // mapped pinned memory
   int* status_dev_ = nullptr;
   std::map<int32_t, std::unique_ptr<SymmSet>> sets_;

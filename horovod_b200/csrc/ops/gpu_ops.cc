@@ -127,6 +127,7 @@ GpuOps::GpuOps(GlobalState& s) : state_(s), events_(new DoneEventPool()) {
   forced_ctas_ = static_cast<int>(EnvInt(HVD_ENV_COMM_CTAS, 0));
   forced_algo_ = EnvString(HVD_ENV_ALGO, "auto");
   timing_ = EnvBool("HOROVOD_GPU_OP_TIMING", false);
+  inline_descriptors_ = EnvBool("HOROVOD_INLINE_DESCRIPTORS", true);
   g_current = this;
 }
 
@@ -167,7 +168,8 @@ void GpuOps::EnsureArena(ProcessSet& ps) {
   size_t mb = static_cast<size_t>(EnvInt(HVD_ENV_SYMM_BUFFER_MB, 512));
   // The token doubles as socket-name salt: distinct per job and per init.
   uint64_t token = state_.config.token ^ 0x9e3779b97f4a7c15ull;
-  Status st = arena_.Create(ps.comm, device_, mb << 20, want_nvls_, token);
+  size_t heap_mb = static_cast<size_t>(EnvInt("HOROVOD_SYMM_HEAP_MB", 2048));
+  Status st = arena_.Create(ps.comm, device_, (mb + heap_mb) << 20, want_nvls_, token);
   if (!st.ok()) {
     HVD_LOG(WARNING) << st.reason()
                      << " -- device collectives fall back to NCCL.";
@@ -176,10 +178,14 @@ void GpuOps::EnsureArena(ProcessSet& ps) {
     return;
   }
   const SymmArenaInfo& a = arena_.info();
+  heap_off_ = static_cast<int64_t>(mb << 20);
+  heap_bytes_ = static_cast<int64_t>(heap_mb << 20);
+  heap_used_ = 0;
+  heap_base_ = static_cast<char*>(a.local) + heap_off_;
   SetGpuBackendDescription(
       "symm ranks=" + std::to_string(a.world) + " nvls=" +
-      std::to_string(a.multicast ? 1 : 0) + " staging_mb=" +
-      std::to_string(a.data_bytes >> 20));
+      std::to_string(a.multicast ? 1 : 0) + " staging_mb=" + std::to_string(mb) +
+      " heap_mb=" + std::to_string(heap_mb));
   HVD_LOG(INFO) << "symmetric memory ready: " << GpuBackendDescription();
 }
 
@@ -193,19 +199,30 @@ SymmSet* GpuOps::GetSymmSet(ProcessSet& ps) {
   const auto& ranks = ps.ranks();  // global == arena ranks on one node
   set->world = static_cast<int>(ranks.size());
   set->rank = ps.comm.rank();
-  set->data_bytes = a.data_bytes;
-  const size_t region = static_cast<size_t>(SYMM_FLAG_BANKS) * SYMM_MAX_RANKS *
-                        SYMM_MAX_BLOCKS;  // uint32 words per set
+  set->data_bytes = static_cast<size_t>(heap_off_);  // staging part only
+  // Room for the two one-shot regions (kept out of the general staging area
+  // for every set, so that no other kernel ever writes there).
+  const int64_t region = RoundUp(oneshot_max_ + 4096, 4096);
+  if (static_cast<int64_t>(set->data_bytes) > 4 * region) {
+    set->data_bytes = set->data_bytes - 2 * region;
+    if (ps.id == 0) {
+      set->oneshot_bytes = region;
+      set->oneshot_off[0] = static_cast<int64_t>(set->data_bytes);
+      set->oneshot_off[1] = static_cast<int64_t>(set->data_bytes) + region;
+    }
+  }
+  const size_t flag_words = static_cast<size_t>(SYMM_FLAG_BANKS) * SYMM_MAX_RANKS *
+                            SYMM_MAX_BLOCKS;  // uint32 words per set
   for (int i = 0; i < set->world; ++i) {
     set->peers[i] = static_cast<char*>(a.peers[ranks[i]]);
-    set->flags_peers[i] = a.flags[ranks[i]] + region * ps.id;
+    set->flags_peers[i] = a.flags[ranks[i]] + flag_words * ps.id;
   }
   set->local = set->peers[set->rank];
   set->flags_local = set->flags_peers[set->rank];
   set->nvls = a.multicast && set->world == a.world;
   set->mc = set->nvls ? static_cast<char*>(a.mc) : nullptr;
   // Fresh flag words for this set, agreed before anyone signals.
-  HVD_CUDA(cudaMemsetAsync(set->flags_local, 0, region * sizeof(uint32_t), stream_));
+  HVD_CUDA(cudaMemsetAsync(set->flags_local, 0, flag_words * sizeof(uint32_t), stream_));
   HVD_CUDA(cudaStreamSynchronize(stream_));
   ps.comm.Barrier();
   SymmSet* raw = set.get();
@@ -213,17 +230,19 @@ SymmSet* GpuOps::GetSymmSet(ProcessSet& ps) {
   return raw;
 }
 
-kern::SymmCtx GpuOps::MakeCtx(SymmSet& set, uint32_t epochs) {
+kern::SymmCtx GpuOps::MakeCtx(SymmSet& set, uint32_t epochs, int64_t staging_off,
+                              bool skip_end_barrier) {
   kern::SymmCtx c;
   std::memset(&c, 0, sizeof(c));
   c.rank = set.rank;
   c.world = set.world;
-  c.local = set.local;
+  c.local = set.local + staging_off;
   for (int i = 0; i < set.world; ++i) {
-    c.peers[i] = set.peers[i];
+    c.peers[i] = set.peers[i] + staging_off;
     c.flags_peers[i] = set.flags_peers[i];
   }
-  c.mc = set.mc;
+  c.mc = set.mc ? set.mc + staging_off : nullptr;
+  c.skip_end_barrier = skip_end_barrier ? 1 : 0;
   c.flags_local = set.flags_local;
   c.epoch = set.epoch;
   c.timeout_ns = timeout_ns_;
@@ -262,7 +281,10 @@ kern::Algo GpuOps::PickAlgo(const SymmSet& set, DataType wire,
   if (forced_algo_ == "twoshot") return kern::Algo::TWOSHOT;
   if (forced_algo_ == "nvls" && set.nvls && nvls_type) return kern::Algo::NVLS;
   if (bytes <= oneshot_max_) return kern::Algo::ONESHOT;
-  if (set.nvls && nvls_type && bytes >= nvls_min_) return kern::Algo::NVLS;
+  // Per-GPU NVLink traffic: NVLS moves S(N+1)/N each way, two-shot over peer
+  // loads/stores 2S(N-1)/N, so the switch reduction wins from 4 ranks on.
+  if (set.nvls && nvls_type && bytes >= nvls_min_ && set.world >= 4)
+    return kern::Algo::NVLS;
   return kern::Algo::TWOSHOT;
 }
 
@@ -379,6 +401,26 @@ Status GpuOps::Execute(std::vector<TensorTableEntry>& entries,
   return nccl_->Execute(entries, response, ps);
 }
 
+void* GpuOps::SymmHeapAlloc(size_t bytes, int64_t* offset) {
+  if (!arena_.valid() || heap_bytes_ == 0) return nullptr;
+  const int64_t need = RoundUp(static_cast<int64_t>(bytes), 256);
+  int64_t at = heap_used_.fetch_add(need);
+  if (at + need > heap_bytes_) {
+    heap_used_.fetch_sub(need);
+    return nullptr;
+  }
+  if (offset) *offset = heap_off_ + at;
+  return heap_base_ + at;
+}
+
+bool GpuOps::InSymmHeap(const void* p, int64_t bytes, int64_t* offset) const {
+  if (heap_base_ == nullptr) return false;
+  const char* c = static_cast<const char*>(p);
+  if (c < heap_base_ || c + bytes > heap_base_ + heap_used_.load()) return false;
+  if (offset) *offset = heap_off_ + (c - heap_base_);
+  return true;
+}
+
 std::vector<GpuOps::OpTiming> GpuOps::DrainTimings() {
   std::vector<PendingTiming> pending;
   {
@@ -424,6 +466,8 @@ void GpuOps::Shutdown() {
     }
   }
   arena_.Destroy();
+  heap_base_ = nullptr;
+  heap_bytes_ = 0;
   ring_.Destroy();
   if (status_host_) cudaFreeHost(status_host_);
   status_host_ = nullptr;

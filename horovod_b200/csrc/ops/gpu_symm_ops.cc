@@ -39,6 +39,17 @@ Status GpuOps::SymmAllreduce(std::vector<TensorTableEntry>& entries,
 
   WaitForInputs(entries);
   tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
+  // (A response with fewer devices than ranks means somebody has joined and
+  // contributes zeros: everybody stages in that case.)
+  if (!adasum && set.world > 1 && wire == dtype &&
+      static_cast<int>(response.devices.size()) == set.world) {
+    Status st;
+    if (TryInplaceAllreduce(entries, response, set, &st)) {
+      if (!st.ok()) return st;
+      tl.ActivityEndAll(entries);
+      return Complete(entries);
+    }
+  }
 
   // Room for data; Adasum also keeps 3 doubles per tensor per level behind it.
   int64_t capacity = static_cast<int64_t>(set.data_bytes);
@@ -69,9 +80,8 @@ Status GpuOps::SymmAllreduce(std::vector<TensorTableEntry>& entries,
   while (next < pieces.size()) {
     // Greedy batch of pieces that fits the staging buffer and one
     // descriptor slot.
-    DescriptorRing::Slot slot = ring_.Acquire();
-    const size_t max_n =
-        std::min<size_t>(pieces.size() - next, (slot.capacity - 4096) / 40);
+    const size_t max_n = std::min<size_t>(pieces.size() - next,
+                                          (ring_.slot_bytes() - 4096) / 40);
     int64_t total = 0;
     size_t n = 0;
     while (n < max_n) {
@@ -80,15 +90,39 @@ Status GpuOps::SymmAllreduce(std::vector<TensorTableEntry>& entries,
       total += padded;
       ++n;
     }
-    int64_t *d_off, *d_cnt;
-    const void** d_in;
-    void** d_out;
-    int64_t* h_off = slot.Alloc<int64_t>(n + 1, &d_off);
-    int64_t* h_cnt = slot.Alloc<int64_t>(n, &d_cnt);
-    const void** h_in = slot.Alloc<const void*>(n, &d_in);
-    void** h_out = slot.Alloc<void*>(n, &d_out);
-    if (!h_off || !h_cnt || !h_in || !h_out)
-      return Status::UnknownError("descriptor slot too small");
+    // Short lists ride in the kernel parameters; long ones go through the
+    // descriptor ring (one small host-to-device copy).
+    const bool use_inline = inline_descriptors_ &&
+                            n <= static_cast<size_t>(kern::INLINE_TENSORS);
+    kern::InlineTensors inl;
+    inl.n = 0;
+    kern::TensorList list = {static_cast<int>(n), nullptr, nullptr, nullptr, nullptr};
+    DescriptorRing::Slot slot;
+    int64_t *h_off, *h_cnt;
+    const void** h_in;
+    void** h_out;
+    if (use_inline) {
+      inl.n = static_cast<int>(n);
+      h_off = inl.offsets;
+      h_cnt = inl.counts;
+      h_in = inl.in;
+      h_out = inl.out;
+    } else {
+      slot = ring_.Acquire();
+      int64_t *d_off, *d_cnt;
+      const void** d_in;
+      void** d_out;
+      h_off = slot.Alloc<int64_t>(n + 1, &d_off);
+      h_cnt = slot.Alloc<int64_t>(n, &d_cnt);
+      h_in = slot.Alloc<const void*>(n, &d_in);
+      h_out = slot.Alloc<void*>(n, &d_out);
+      if (!h_off || !h_cnt || !h_in || !h_out)
+        return Status::UnknownError("descriptor slot too small");
+      list.offsets = d_off;
+      list.counts = d_cnt;
+      list.in = d_in;
+      list.out = d_out;
+    }
     int64_t off = 0;
     for (size_t i = 0; i < n; ++i) {
       const Piece& p = pieces[next + i];
@@ -99,34 +133,56 @@ Status GpuOps::SymmAllreduce(std::vector<TensorTableEntry>& entries,
       off += RoundUp(p.count, align_elems);
     }
     h_off[n] = off;
-    ring_.Commit(slot, stream_);
+    if (!use_inline) ring_.Commit(slot, stream_);
 
-    kern::TensorList list;
-    list.n = static_cast<int>(n);
-    list.offsets = d_off;
-    list.counts = d_cnt;
-    list.in = d_in;
-    list.out = d_out;
     const int64_t bytes = off * ws;
     cudaError_t err;
     if (adasum && set.world > 1) {
+      if (use_inline) {
+        // The Adasum kernels read the list from device memory.
+        slot = ring_.Acquire();
+        int64_t *d_off, *d_cnt;
+        const void** d_in;
+        void** d_out;
+        int64_t* o = slot.Alloc<int64_t>(n + 1, &d_off);
+        int64_t* c = slot.Alloc<int64_t>(n, &d_cnt);
+        const void** ip = slot.Alloc<const void*>(n, &d_in);
+        void** op = slot.Alloc<void*>(n, &d_out);
+        std::memcpy(o, h_off, (n + 1) * sizeof(int64_t));
+        std::memcpy(c, h_cnt, n * sizeof(int64_t));
+        std::memcpy(ip, h_in, n * sizeof(void*));
+        std::memcpy(op, h_out, n * sizeof(void*));
+        list.offsets = d_off;
+        list.counts = d_cnt;
+        list.in = d_in;
+        list.out = d_out;
+        ring_.Commit(slot, stream_);
+      }
       kern::SymmCtx ctx = MakeCtx(set, kern::ADASUM_EPOCHS);
       int64_t scratch_off = RoundUp(bytes, 4096);
       err = kern::LaunchAdasum(list, dtype, response.prescale,
                                response.postscale, scratch_off, PickCtas(bytes),
                                ctx, stream_);
+      ring_.Release(slot, stream_);
     } else {
       kern::Algo algo = PickAlgo(set, wire, bytes);
-      kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH);
       int ctas = PickCtas(bytes);
       // A single rank waits for nobody: use the whole GPU for the copy.
       if (algo == kern::Algo::LOCAL && forced_ctas_ <= 0)
         ctas = static_cast<int>(std::min<int64_t>(296, std::max<int64_t>(1, bytes >> 16)));
+      int64_t staging_off = 0;
+      bool skip_end = false;
+      if (algo == kern::Algo::ONESHOT && set.oneshot_bytes >= bytes) {
+        staging_off = set.oneshot_off[set.oneshot_count++ & 1];
+        skip_end = true;
+      }
+      kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH, staging_off, skip_end);
       err = kern::LaunchFusedAllreduce(list, dtype, adasum ? dtype : wire,
                                        response.prescale, response.postscale,
-                                       algo, ctas, ctx, stream_);
+                                       algo, ctas, ctx, stream_,
+                                       use_inline ? &inl : nullptr);
+      if (!use_inline) ring_.Release(slot, stream_);
     }
-    ring_.Release(slot, stream_);
     if (err != cudaSuccess)
       return Status::UnknownError(std::string("fused allreduce launch failed: ") +
                                   cudaGetErrorString(err));
@@ -134,6 +190,86 @@ Status GpuOps::SymmAllreduce(std::vector<TensorTableEntry>& entries,
   }
   tl.ActivityEndAll(entries);
   return Complete(entries);
+}
+
+bool GpuOps::TryInplaceAllreduce(std::vector<TensorTableEntry>& entries,
+                                 const Response& response, SymmSet& set,
+                                 Status* status) {
+  const DataType dtype = response.dtype;
+  if (dtype != DataType::FLOAT32 && dtype != DataType::FLOAT16 &&
+      dtype != DataType::BFLOAT16 && dtype != DataType::FLOAT64)
+    return false;
+  const int64_t es = static_cast<int64_t>(DataTypeSize(dtype));
+  struct R { int64_t off, bytes; };
+  std::vector<R> ranges;
+  for (auto& e : entries) {
+    if (e.input == nullptr || e.input != e.output) return false;  // also joined ranks
+    int64_t off = 0, bytes = e.num_elements() * es;
+    if (bytes == 0) continue;
+    if (!InSymmHeap(e.input, bytes, &off) || (off & 15) != 0) return false;
+    ranges.push_back({off, bytes});
+  }
+  // Every rank must take the same decision: tensors are symmetric by
+  // construction (same allocation sequence), so offsets agree; a rank whose
+  // tensor is elsewhere has a different layout on all ranks alike.
+  if (ranges.empty()) return false;
+  std::sort(ranges.begin(), ranges.end(), [](const R& a, const R& b) { return a.off < b.off; });
+  std::vector<R> merged;
+  for (auto& r : ranges) {
+    // Merge neighbours; a range with a ragged tail cannot be extended.
+    if (!merged.empty() && merged.back().off + merged.back().bytes == r.off &&
+        (merged.back().bytes & 15) == 0)
+      merged.back().bytes += r.bytes;
+    else
+      merged.push_back(r);
+  }
+  const size_t n = merged.size();
+  int64_t total_bytes = 0;
+  kern::InlineRanges inl;
+  inl.n = 0;
+  kern::RangeList list = {static_cast<int>(n), nullptr, nullptr, nullptr};
+  DescriptorRing::Slot slot;
+  const bool use_inline = inline_descriptors_ && n <= static_cast<size_t>(kern::INLINE_TENSORS);
+  int64_t *h_vs, *h_off, *h_bytes;
+  if (use_inline) {
+    inl.n = static_cast<int>(n);
+    h_vs = inl.vec_start;
+    h_off = inl.byte_off;
+    h_bytes = inl.bytes;
+  } else {
+    if ((n + 1) * 24 + 1024 > ring_.slot_bytes()) return false;
+    slot = ring_.Acquire();
+    int64_t *d_vs, *d_off, *d_bytes;
+    h_vs = slot.Alloc<int64_t>(n + 1, &d_vs);
+    h_off = slot.Alloc<int64_t>(n, &d_off);
+    h_bytes = slot.Alloc<int64_t>(n, &d_bytes);
+    list.vec_start = d_vs;
+    list.byte_off = d_off;
+    list.bytes = d_bytes;
+  }
+  int64_t v = 0;
+  for (size_t i = 0; i < n; ++i) {
+    h_vs[i] = v;
+    h_off[i] = merged[i].off;
+    h_bytes[i] = merged[i].bytes;
+    v += (merged[i].bytes + 15) / 16;
+    total_bytes += merged[i].bytes;
+  }
+  h_vs[n] = v;
+  if (!use_inline) ring_.Commit(slot, stream_);
+  const bool nvls = set.nvls && dtype != DataType::FLOAT64 && set.world >= 4 &&
+                    forced_algo_ != "twoshot" && forced_algo_ != "oneshot";
+  kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH);
+  cudaError_t err = kern::LaunchInplaceAllreduce(
+      list, dtype, response.prescale * response.postscale,
+      nvls || (forced_algo_ == "nvls" && set.nvls && dtype != DataType::FLOAT64),
+      PickCtas(total_bytes), ctx, stream_, use_inline ? &inl : nullptr);
+  if (!use_inline) ring_.Release(slot, stream_);
+  *status = err == cudaSuccess
+                ? Status::OK()
+                : Status::UnknownError(std::string("in-place allreduce launch failed: ") +
+                                       cudaGetErrorString(err));
+  return true;
 }
 
 Status GpuOps::SymmReducescatter(std::vector<TensorTableEntry>& entries,

@@ -1,5 +1,6 @@
 // Python access to device-side diagnostics and raw kernel entry points.
-#include <pybind11/pybind11.h>
+#include <torch/extension.h>
+
 #include <pybind11/stl.h>
 
 #include "../kernels/kernels.h"
@@ -13,6 +14,33 @@ namespace hvd {
 
 void BindGpuDiagnostics(py::module_& m) {
   m.def("gpu_backend", &GpuBackendDescription);
+  m.def("symm_empty", [](const std::vector<int64_t>& sizes, py::object dtype) {
+    // A tensor inside the symmetric heap (same offset on every rank when all
+    // ranks allocate the same sequence). The memory belongs to the arena: it
+    // is never freed individually and dies with hvd.shutdown().
+    GpuOps* ops = CurrentGpuOps();
+    if (ops == nullptr)
+      throw std::runtime_error("symmetric memory needs an initialised runtime with a GPU");
+    at::ScalarType st = torch::python::detail::py_object_to_dtype(dtype);
+    int64_t n = 1;
+    for (auto d : sizes) n *= d;
+    int64_t off = 0;
+    void* p = ops->SymmHeapAlloc(static_cast<size_t>(std::max<int64_t>(n, 1)) *
+                                     c10::elementSize(st), &off);
+    if (p == nullptr)
+      throw std::runtime_error(
+          "symmetric heap unavailable or exhausted (backend: " + GpuBackendDescription() +
+          "); raise HOROVOD_SYMM_HEAP_MB");
+    auto options = at::TensorOptions().dtype(st).device(at::kCUDA, ops->device());
+    return at::from_blob(p, sizes, [](void*) {}, options);
+  });
+  m.def("symm_heap_info", []() {
+    GpuOps* ops = CurrentGpuOps();
+    py::dict d;
+    d["bytes"] = ops ? ops->symm_heap_bytes() : 0;
+    d["used"] = ops ? ops->symm_heap_used() : 0;
+    return d;
+  });
   m.def("gpu_topology", []() {
     GpuTopology t = DiscoverTopology();
     py::dict d;

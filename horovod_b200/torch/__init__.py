@@ -24,7 +24,7 @@ from horovod_b200.torch.mpi_ops import (Adasum, Average, Max, Min, Product, Sum,
                                         mpi_threads_supported, nccl_built, poll, rank,
                                         reducescatter, reducescatter_async, rocm_built,
                                         shutdown, size, sparse_allreduce_async,
-                                        start_timeline, stop_timeline, synchronize,
-                                        topology)
+                                        start_timeline, stop_timeline, symmetric_empty,
+                                        synchronize, topology)
 from horovod_b200.torch.optimizer import DistributedOptimizer
 from horovod_b200.torch.sync_batch_norm import SyncBatchNorm

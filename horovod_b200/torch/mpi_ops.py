@@ -465,6 +465,27 @@ def reducescatter(tensor, name=None, compression=Compression.none, op=Average,
     return compression.decompress(out, ctx)
 
 
+def symmetric_empty(*size, dtype=torch.float32):
+    """Allocates a CUDA tensor inside the symmetric heap: memory that every
+    GPU of the box has mapped, at the same offset on every rank. Collective by
+    contract: all ranks must call it with the same sizes in the same order.
+    Allreduce on such tensors (in place, whole tensors or 16-byte aligned
+    slices) runs without any staging copy: the kernel reduces the ranks'
+    tensors directly over NVLink. The memory is never freed individually and
+    becomes invalid at hvd.shutdown(). Size the heap with
+    HOROVOD_SYMM_HEAP_MB (default 2048)."""
+    if len(size) == 1 and isinstance(size[0], (tuple, list, torch.Size)):
+        size = tuple(size[0])
+    if not gpu_backend().startswith("symm"):
+        # The arena is built by the first device collective of the job.
+        if not torch.cuda.is_available():
+            raise RuntimeError("symmetric memory needs CUDA")
+        allreduce_(torch.zeros(1, device="cuda"), op=Sum, name="hvd.symm.bootstrap")
+    if not gpu_backend().startswith("symm"):
+        raise RuntimeError("symmetric memory is not available: " + gpu_backend())
+    return _C.symm_empty([int(s) for s in size], dtype)
+
+
 def poll(handle):
     """True once the op behind ``handle`` has run (CPU) or been launched
     (GPU); synchronize() will then not block the host."""

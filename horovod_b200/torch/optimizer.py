@@ -24,9 +24,11 @@ from horovod_b200.torch.mpi_ops import (Adasum, Average, Sum, allreduce_async_,
 class _DistributedOptimizer(torch.optim.Optimizer):
     def __init__(self, params, named_parameters, compression, backward_passes_per_step=1,
                  op=Average, gradient_predivide_factor=1.0, groups=None,
-                 sparse_as_dense=False, process_set=global_process_set):
+                 sparse_as_dense=False, process_set=global_process_set,
+                 symmetric_gradients=False):
         super(self.__class__, self).__init__(params)
         self._compression = compression
+        self._symm_flats = []
         if named_parameters is not None:
             named_parameters = list(named_parameters)
         else:
@@ -95,8 +97,34 @@ class _DistributedOptimizer(torch.optim.Optimizer):
                     self._p_to_group[p] = gi
                 self._group_counts[gi] = 0
 
+        if symmetric_gradients and self.process_set.included():
+            self._setup_symmetric_gradients()
         if self.process_set.included() and size() > 1 or _force_hooks():
             self._register_hooks()
+
+    def _setup_symmetric_gradients(self):
+        """Places every dense CUDA gradient in one flat buffer inside the
+        symmetric heap (one buffer per dtype) and makes ``p.grad`` a view of
+        it, so that the gradient allreduce runs in place over NVLink with no
+        staging copies. Same parameter order on every rank (sorted by name)."""
+        from horovod_b200.torch.mpi_ops import symmetric_empty
+        by_dtype = {}
+        for p, name in sorted(self._parameter_names.items(), key=lambda kv: kv[1]):
+            if p.requires_grad and p.is_cuda and p.dtype.is_floating_point and \
+                    (p.is_contiguous() or _is_dense(p)):
+                by_dtype.setdefault(p.dtype, []).append(p)
+        for dtype, plist in sorted(by_dtype.items(), key=lambda kv: str(kv[0])):
+            es = torch.empty((), dtype=dtype).element_size()
+            slot = 256 // es  # every gradient starts on a 256-byte boundary
+            offsets, total = [], 0
+            for p in plist:
+                offsets.append(total)
+                total += (p.numel() + slot - 1) // slot * slot
+            flat = symmetric_empty(max(total, slot), dtype=dtype)
+            flat.zero_()
+            for p, off in zip(plist, offsets):
+                p.grad = torch.as_strided(flat, p.size(), p.stride(), storage_offset=off)
+            self._symm_flats.append(flat)
 
     def load_state_dict(self, *args, **kwargs):
         self._handles = {}
@@ -306,7 +334,27 @@ class _DistributedOptimizer(torch.optim.Optimizer):
                 "optimizer.zero_grad() was called after loss.backward() but before "
                 "optimizer.step() or optimizer.synchronize(). This is prohibited as it "
                 "can cause a race condition.")
+        if self._symm_flats:
+            # Gradients are views of the flat symmetric buffers: clear those
+            # (one memset each) and keep the views, whatever set_to_none says.
+            for flat in self._symm_flats:
+                flat.zero_()
+            in_flat = set()
+            for group in self.param_groups:
+                for p in group["params"]:
+                    if p.grad is not None and any(
+                            p.grad.untyped_storage().data_ptr() == f.untyped_storage().data_ptr()
+                            for f in self._symm_flats):
+                        in_flat.add(p)
+                    elif p.grad is not None:
+                        p.grad = None if kwargs.get("set_to_none", True) else p.grad.zero_()
+            return None
         return super(self.__class__, self).zero_grad(*args, **kwargs)
+
+
+def _is_dense(t):
+    return (t.dim() == 4 and t.is_contiguous(memory_format=torch.channels_last)) or \
+        (t.dim() == 5 and t.is_contiguous(memory_format=torch.channels_last_3d))
 
 
 def _force_hooks():
@@ -455,7 +503,8 @@ class _DistributedAdasumOptimizer(torch.optim.Optimizer):
 def DistributedOptimizer(optimizer, named_parameters=None, compression=Compression.none,
                          backward_passes_per_step=1, op=Average,
                          gradient_predivide_factor=1.0, num_groups=0, groups=None,
-                         sparse_as_dense=False, process_set=global_process_set):
+                         sparse_as_dense=False, process_set=global_process_set,
+                         symmetric_gradients=None):
     """Returns an optimizer of the same class as ``optimizer`` whose step()
     first combines gradients across the ranks of ``process_set``.
 
@@ -472,7 +521,17 @@ def DistributedOptimizer(optimizer, named_parameters=None, compression=Compressi
         num_groups / groups: fuse gradients into explicit groups (an int for
             that many equal groups, or a list of lists of parameters).
         sparse_as_dense: densify sparse gradients before reduction.
+        symmetric_gradients: keep gradients in the symmetric heap (one flat
+            buffer, ``p.grad`` are views) so that their allreduce runs in
+            place over NVLink without staging copies. Default: the value of
+            HOROVOD_SYMMETRIC_GRADIENTS (off). Not available in elastic jobs
+            (the heap does not survive a reset) or with Adasum.
     """
+    import os
+    if symmetric_gradients is None:
+        symmetric_gradients = os.environ.get("HOROVOD_SYMMETRIC_GRADIENTS", "0") == "1"
+    if os.environ.get("HOROVOD_ELASTIC") == "1" or not torch.cuda.is_available():
+        symmetric_gradients = False
     if gradient_predivide_factor != 1.0 and op != Average:
         raise ValueError("gradient_predivide_factor not supported with op != Average")
     if num_groups != 0:
@@ -485,7 +544,8 @@ def DistributedOptimizer(optimizer, named_parameters=None, compression=Compressi
                    dict(_DistributedOptimizer.__dict__))
         return cls(optimizer.param_groups, named_parameters, compression,
                    backward_passes_per_step, op, gradient_predivide_factor, groups,
-                   sparse_as_dense, process_set)
+                   sparse_as_dense, process_set,
+                   symmetric_gradients and size() > 1 and op != Adasum)
     if groups is not None:
         raise ValueError("groups are not supported with op == Adasum")
     cls = type(optimizer.__class__.__name__, (optimizer.__class__,),

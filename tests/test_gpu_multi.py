@@ -167,3 +167,120 @@ def _nccl_backend(rank, size):
 def test_nccl_baseline_path():
     for ok, backend in run_parallel(_nccl_backend, np=2, timeout=300):
         assert ok and backend.startswith("nccl")
+
+
+def _long_lists_and_heap(rank, size, inline):
+    os.environ["HOROVOD_INLINE_DESCRIPTORS"] = inline
+    os.environ["HOROVOD_SPIN_TIMEOUT_MS"] = "5000"
+    import horovod_b200.torch as hvd
+    hvd.init()
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    # A fused list longer than what fits the kernel parameters (descriptor ring).
+    shapes = [1, 3, 17, 255, 256, 257, 4099, 65537, 9, 300001] * 10
+    xs = [_inputs(rank * 211 + i, s, torch.float32).to(dev) for i, s in enumerate(shapes)]
+    outs = hvd.grouped_allreduce(xs, op=hvd.Sum, name="long")
+    for i, (s, o) in enumerate(zip(shapes, outs)):
+        ref = sum(_inputs(r * 211 + i, s, torch.float32).double() for r in range(size))
+        assert (o.double().cpu() - ref).abs().max().item() < 1e-5 * size, ("long", i, s)
+    # In place on the symmetric heap: one tensor, an odd length, 16-bit types.
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 4e-2), (torch.float16, 8e-3),
+                       (torch.float64, 1e-12)):
+        for n in (5, 4096, 100003, (1 << 20) + 3):
+            z = hvd.symmetric_empty(n, dtype=dtype)
+            assert z.is_cuda and z.numel() == n and z.data_ptr() % 256 == 0
+            z.copy_(_inputs(rank, n, dtype).to(dev))
+            out = hvd.allreduce_(z, op=hvd.Average, name="heap.%s.%d" % (dtype, n))
+            assert out.data_ptr() == z.data_ptr()
+            ref = sum(_inputs(r, n, dtype).double() for r in range(size)) / size
+            err = (z.double().cpu() - ref).abs().max().item()
+            assert err <= tol * max(1.0, ref.abs().max().item()) * size, (str(dtype), n, err)
+    # Many views of one flat buffer (what the optimizer reduces), unordered,
+    # with gaps and ragged lengths; neighbours merge into ranges.
+    flat = hvd.symmetric_empty(1 << 20)
+    flat.copy_(_inputs(rank + 50, 1 << 20, torch.float32).to(dev))
+    before = flat.clone()
+    cuts = [(0, 1000), (1000, 4096), (8192, 8192 + 77), (16384, 300000), (300000, 300004),
+            (400000, 1 << 20)]
+    cuts += [(320000 + 64 * i, 320000 + 64 * i + 64) for i in range(60)]
+    views = [flat[a:b] for a, b in reversed(cuts)]
+    hvd.grouped_allreduce_(views, op=hvd.Sum, name="views")
+    full = sum(_inputs(r + 50, 1 << 20, torch.float32).double() for r in range(size))
+    covered = torch.zeros(1 << 20, dtype=torch.bool)
+    for a, b in cuts:
+        covered[a:b] = True
+    got = flat.double().cpu()
+    assert (got[covered] - full[covered]).abs().max().item() < 1e-5 * size
+    assert torch.equal(flat.cpu()[~covered], before.cpu()[~covered]), "gaps were touched"
+    # A tensor outside the heap in the same group: everybody stages.
+    mixed = [flat[:128], torch.ones(64, device=dev)]
+    flat[:128] = float(rank)
+    hvd.grouped_allreduce_(mixed, op=hvd.Sum, name="mixed")
+    assert bool((mixed[0] == sum(range(size))).all()) and bool((mixed[1] == size).all())
+    info = hvd.gpu_backend()
+    torch.cuda.synchronize()
+    hvd.shutdown()
+    return info
+
+
+@pytest.mark.parametrize("inline", ["1", "0"])
+def test_long_tensor_lists_and_symmetric_heap(inline):
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    for info in run_parallel(_long_lists_and_heap, np=_world(), args=(inline,), timeout=300):
+        assert info.startswith("symm")
+
+
+def _symmetric_gradients(rank, size):
+    os.environ["HOROVOD_SPIN_TIMEOUT_MS"] = "5000"
+    import torch.nn as nn
+    import torch.nn.functional as F
+    import horovod_b200.torch as hvd
+    from horovod_b200 import _C
+    hvd.init()
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+
+    def net():
+        torch.manual_seed(0)
+        return nn.Sequential(nn.Conv2d(3, 8, 3, padding=1), nn.BatchNorm2d(8), nn.ReLU(),
+                             nn.Flatten(), nn.Linear(8 * 8 * 8, 10))
+
+    def data(r):
+        g = torch.Generator().manual_seed(7 + r)
+        return torch.randn(4, 3, 8, 8, generator=g), torch.randint(0, 10, (4,), generator=g)
+
+    model = net().to(dev).to(memory_format=torch.channels_last)
+    opt = hvd.DistributedOptimizer(torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9),
+                                   named_parameters=model.named_parameters(),
+                                   symmetric_gradients=True)
+    ptrs = {n: p.grad.data_ptr() for n, p in model.named_parameters()}
+    assert _C.symm_heap_info()["used"] > 0
+    x, y = data(rank)
+    for _ in range(3):
+        opt.zero_grad()
+        F.cross_entropy(model(x.to(dev)), y.to(dev)).backward()
+        opt.step()
+    # gradients stayed views of the flat buffer through zero_grad/backward/step
+    assert all(p.grad.data_ptr() == ptrs[n] for n, p in model.named_parameters())
+
+    ref = net()
+    ropt = torch.optim.SGD(ref.parameters(), lr=0.1, momentum=0.9)
+    for _ in range(3):
+        ropt.zero_grad()
+        for r in range(size):
+            xr, yr = data(r)
+            # per-rank batch statistics: forward each rank's batch separately
+            (F.cross_entropy(ref(xr), yr) / size).backward()
+        ropt.step()
+    ok = all(torch.allclose(a.detach().cpu(), b.detach(), atol=2e-4)
+             for a, b in zip(model.parameters(), ref.parameters()))
+    torch.cuda.synchronize()
+    hvd.shutdown()
+    return ok
+
+
+def test_optimizer_with_symmetric_gradients():
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    assert all(run_parallel(_symmetric_gradients, np=2, timeout=300))

@@ -1,6 +1,9 @@
 """Collective sweep: allreduce (fp32, bf16), reducescatter, allgather,
 broadcast and alltoall on one tensor from 1 KB to 1 GB in powers of two, plus
 a grouped allreduce of 64 fp32 tensors with log-uniform sizes in 4 KB-4 MB.
+``allreduce_symm`` / ``grouped_symm`` are the same allreduces on tensors that
+live in the symmetric heap (hvd.symmetric_empty), reduced in place without
+staging (symm backend only).
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 \
         --master-addr 127.0.0.1 --master-port 29500 bench_collectives.py \
@@ -12,8 +15,11 @@ over ranks, median over iterations. ``--backend nccl`` runs the same harness
 over the NCCL path (pack -> NCCL -> unpack as the reference issues it), which
 is the baseline of the comparison. Bus bandwidth follows the usual
 conventions: allreduce 2(N-1)/N * S / t, reducescatter/allgather (N-1)/N * S_total / t,
-broadcast S / t, alltoall (N-1)/N * S / t. The roofline for each op is its
-bytes over NVLink at the measured 770 GB/s per direction per GPU.
+broadcast S / t, alltoall (N-1)/N * S / t. The roofline for each op is the
+bytes that must cross one GPU's NVLink in one direction at the measured
+770 GB/s: allreduce 2(N-1)/N * S (the bandwidth lower bound without in-network
+reduction) or S when the NVSwitch reduces (multimem, 4+ ranks); (N-1)/N * S
+for reducescatter, allgather and alltoall; S for broadcast.
 Rank 0 prints one JSON line per (op, dtype, size).
 """
 import argparse
@@ -34,7 +40,7 @@ def main():
     p.add_argument("--iters", type=int, default=20)
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--ops", default="allreduce,allreduce_bf16,reducescatter,allgather,"
-                                    "broadcast,alltoall,grouped")
+                                    "broadcast,alltoall,grouped,allreduce_symm,grouped_symm")
     p.add_argument("--algo", default=None, help="force oneshot|twoshot|nvls")
     p.add_argument("--ctas", type=int, default=0)
     args = p.parse_args()
@@ -85,6 +91,10 @@ def main():
                           "frac_of_nvlink_roofline": round(roof_us / us, 4) if us > 0 else None,
                           "gradient_path": hvd.gpu_backend()}), flush=True)
 
+    def ar_wire(nbytes):
+        nvls = n >= 4 and "nvls=1" in hvd.gpu_backend()
+        return nbytes if nvls else 2 * nbytes * (n - 1) / n
+
     ops = args.ops.split(",")
     sizes = []
     s = args.min_kb << 10
@@ -92,15 +102,25 @@ def main():
         sizes.append(s)
         s <<= 1
 
+    heap = None
+    if args.backend == "symm" and n > 1 and ("allreduce_symm" in ops or "grouped_symm" in ops):
+        os.environ.setdefault("HOROVOD_SYMM_HEAP_MB", "2048")
+        heap = hvd.symmetric_empty(max(sizes[-1], 160 << 20) // 4)
+        heap.normal_()
+
     for nbytes in sizes:
+        if "allreduce_symm" in ops and heap is not None:
+            x = heap[:nbytes // 4]
+            us = measure(lambda: hvd.allreduce_(x, op=hvd.Average, name="sw.ars"), ALLREDUCE)
+            emit("allreduce_symm", "fp32", nbytes, us, 2 * (n - 1) / n, ar_wire(nbytes))
         if "allreduce" in ops:
             x = torch.randn(nbytes // 4, device=dev)
             us = measure(lambda: hvd.allreduce_(x, op=hvd.Sum, name="sw.ar"), ALLREDUCE)
-            emit("allreduce", "fp32", nbytes, us, 2 * (n - 1) / n, nbytes * (n - 1) / n)
+            emit("allreduce", "fp32", nbytes, us, 2 * (n - 1) / n, ar_wire(nbytes))
         if "allreduce_bf16" in ops:
             x = torch.randn(nbytes // 2, device=dev).bfloat16()
             us = measure(lambda: hvd.allreduce_(x, op=hvd.Sum, name="sw.arb"), ALLREDUCE)
-            emit("allreduce", "bf16", nbytes, us, 2 * (n - 1) / n, nbytes * (n - 1) / n)
+            emit("allreduce", "bf16", nbytes, us, 2 * (n - 1) / n, ar_wire(nbytes))
         if "reducescatter" in ops and nbytes >= 4 * n:
             x = torch.randn(nbytes // 4 // n * n, device=dev)
             us = measure(lambda: hvd.reducescatter(x, op=hvd.Sum, name="sw.rs"), REDUCESCATTER)
@@ -127,7 +147,16 @@ def main():
         xs = [torch.randn(c, device=dev) for c in counts]
         total = sum(c * 4 for c in counts)
         us = measure(lambda: hvd.grouped_allreduce_(xs, op=hvd.Sum, name="sw.grp"), ALLREDUCE)
-        emit("grouped_allreduce_64", "fp32", total, us, 2 * (n - 1) / n, total * (n - 1) / n)
+        emit("grouped_allreduce_64", "fp32", total, us, 2 * (n - 1) / n, ar_wire(total))
+        if "grouped_symm" in ops and heap is not None:
+            views, at = [], 0
+            for c in counts:
+                views.append(heap[at:at + c])
+                at += (c + 63) // 64 * 64
+            us = measure(lambda: hvd.grouped_allreduce_(views, op=hvd.Average, name="sw.grps"),
+                         ALLREDUCE)
+            emit("grouped_allreduce_64_symm", "fp32", total, us, 2 * (n - 1) / n,
+                 ar_wire(total))
 
     hvd.shutdown()
     return 0

@@ -91,6 +91,12 @@ __device__ __forceinline__ void multimem_st16(void* mc, uint4 v) {
                "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// Phase timestamp for the optional kernel trace (one thread per launch).
+__device__ __forceinline__ void trace_mark(const SymmCtx& ctx, int slot) {
+  if (ctx.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0)
+    *reinterpret_cast<volatile unsigned long long*>(ctx.trace + slot) = globaltimer_ns();
+}
+
 // ---- cross-GPU CTA barrier --------------------------------------------------
 // CTA `block` of every rank meets CTA `block` of every other rank. Flags are
 // indexed [source rank][block]; the value written is the epoch of this
@@ -104,7 +110,8 @@ __device__ __forceinline__ bool cta_barrier(const SymmCtx& ctx, uint32_t epoch,
   bool ok = true;
   if (threadIdx.x < ctx.world) {
     const int p = threadIdx.x;
-    __threadfence_system();
+    // The release is cumulative: it also publishes what the other threads of
+    // the CTA wrote before the __syncthreads() above.
     st_release_sys(ctx.flags_peers[p] + ctx.rank * SYMM_MAX_BLOCKS + block, epoch);
     const uint32_t* f = ctx.flags_local + p * SYMM_MAX_BLOCKS + block;
     const unsigned long long t0 = globaltimer_ns();
@@ -119,10 +126,51 @@ __device__ __forceinline__ bool cta_barrier(const SymmCtx& ctx, uint32_t epoch,
         st[2] = phase;
         st[3] = block;
         __threadfence_system();
-        st[0] = 1;
+        if (st[0] == 0) st[0] = 1;  // never hide an earlier, more specific report
         __threadfence_system();
         break;
       }
+    }
+  }
+  return __syncthreads_and(ok) != 0;
+}
+
+// Barrier for kernels that address symmetric-heap tensors by offset: every
+// CTA also exchanges a token derived from the offsets (and the epoch, so a stale
+// token never matches). A rank whose peers were not given the same symmetric
+// tensors reports code 2 instead of reading unrelated memory as gradients.
+__device__ __forceinline__ uint32_t symm_token(uint32_t epoch, int64_t a, int64_t b, int n) {
+  uint32_t h = epoch * 2654435761u;
+  h ^= static_cast<uint32_t>(a >> 4) + 0x9e3779b9u + (h << 6) + (h >> 2);
+  h ^= static_cast<uint32_t>(a >> 36) + 0x9e3779b9u + (h << 6) + (h >> 2);
+  h ^= static_cast<uint32_t>(b >> 4) + 0x9e3779b9u + (h << 6) + (h >> 2);
+  h ^= static_cast<uint32_t>(n) + 0x9e3779b9u + (h << 6) + (h >> 2);
+  return h;
+}
+__device__ __forceinline__ bool cta_barrier_token(const SymmCtx& ctx, uint32_t epoch,
+                                                  int block, int phase, uint32_t token) {
+  // Mailbox = flag bank 1, indexed like the flags: [source rank][block].
+  constexpr int MAILBOX = SYMM_MAX_RANKS * SYMM_MAX_BLOCKS;
+  if (threadIdx.x < ctx.world) {
+    // The same thread stores the token and then releases the flag to that peer.
+    volatile uint32_t* box =
+        ctx.flags_peers[threadIdx.x] + MAILBOX + ctx.rank * SYMM_MAX_BLOCKS + block;
+    *box = token;
+  }
+  if (!cta_barrier(ctx, epoch, block, phase)) return false;
+  bool ok = true;
+  if (threadIdx.x < ctx.world) {
+    const uint32_t theirs =
+        ld_acquire_sys(ctx.flags_local + MAILBOX + threadIdx.x * SYMM_MAX_BLOCKS + block);
+    if (theirs != token) {
+      ok = false;
+      volatile int* st = ctx.status;
+      st[1] = threadIdx.x;
+      st[2] = phase;
+      st[3] = block;
+      __threadfence_system();
+      st[0] = 2;
+      __threadfence_system();
     }
   }
   return __syncthreads_and(ok) != 0;

@@ -83,6 +83,28 @@ __device__ __forceinline__ void reduce_chunk_p2p(const SymmCtx& ctx, int64_t lo,
   }
 }
 
+// One-shot: every rank sums vectors [lo, hi) of all ranks' staging buffers
+// and scatters the result straight into its own output tensors. The adds run
+// in rank order on every GPU, so all ranks compute bitwise-identical sums.
+template <typename T, typename W, typename S, int WORLD, int UNROLL>
+__device__ __forceinline__ void oneshot_reduce(const TensorList& tl, const SymmCtx& ctx,
+                                               int64_t lo, int64_t hi, S postscale,
+                                               bool post) {
+  const uint4* src[WORLD];
+#pragma unroll
+  for (int p = 0; p < WORLD; ++p) src[p] = reinterpret_cast<const uint4*>(ctx.peers[p]);
+  scatter_range<T, W, S, THREADS, UNROLL>(tl, lo, hi, postscale, post, [&](int64_t v) {
+    uint4 in[WORLD];
+#pragma unroll
+    for (int p = 0; p < WORLD; ++p) in[p] = ld16(src[p] + v);
+    VecAcc<W> acc;
+    acc.zero();
+#pragma unroll
+    for (int p = 0; p < WORLD; ++p) acc.add(in[p]);
+    return acc.pack();
+  });
+}
+
 // INLINE: the tensor list rides in the kernel parameters (`inl`) and is
 // copied to shared memory first (parameter reads with compile-time offsets
 // only); else it is read from device memory (`tl_dev`).
@@ -118,6 +140,7 @@ fused_allreduce_kernel(const InlineTensors inl, const TensorList tl_dev,
     tl.in = s_in;
     tl.out = s_out;
   }
+  trace_mark(ctx, 0);
   const int64_t nvec = tl.offsets[tl.n] / N;
   const int world = ctx.world, rank = ctx.rank;
   const int G = gridDim.x, b = blockIdx.x;
@@ -143,23 +166,24 @@ fused_allreduce_kernel(const InlineTensors inl, const TensorList tl_dev,
   } else if constexpr (ALGO == static_cast<int>(Algo::ONESHOT)) {
     const int64_t per = (nvec + G - 1) / G;
     const int64_t lo = b * per, hi = min(lo + per, nvec);
-    pack_range<T, W, S, 1>(tl, stage, lo, hi, prescale, pre);
+    pack_range<T, W, S>(tl, stage, lo, hi, prescale, pre);
+    trace_mark(ctx, 1);
     if (!cta_barrier(ctx, ctx.epoch + 1, b, 1)) return;
-    scatter_range<T, W, S, THREADS, 1>(tl, lo, hi, postscale, post, [&](int64_t v) {
-      uint4 in[SYMM_MAX_RANKS];
-#pragma unroll
-      for (int p = 0; p < SYMM_MAX_RANKS; ++p)
-        if (p < world) in[p] = ld16(reinterpret_cast<const uint4*>(ctx.peers[p]) + v);
-      VecAcc<W> acc;
-      acc.zero();
-#pragma unroll
-      for (int p = 0; p < SYMM_MAX_RANKS; ++p)
-        if (p < world) acc.add(in[p]);
-      return acc.pack();
-    });
+    trace_mark(ctx, 2);
+    switch (world) {
+    case 2: oneshot_reduce<T, W, S, 2, 4>(tl, ctx, lo, hi, postscale, post); break;
+    case 3: oneshot_reduce<T, W, S, 3, 2>(tl, ctx, lo, hi, postscale, post); break;
+    case 4: oneshot_reduce<T, W, S, 4, 2>(tl, ctx, lo, hi, postscale, post); break;
+    case 5: oneshot_reduce<T, W, S, 5, 1>(tl, ctx, lo, hi, postscale, post); break;
+    case 6: oneshot_reduce<T, W, S, 6, 1>(tl, ctx, lo, hi, postscale, post); break;
+    case 7: oneshot_reduce<T, W, S, 7, 1>(tl, ctx, lo, hi, postscale, post); break;
+    default: oneshot_reduce<T, W, S, 8, 1>(tl, ctx, lo, hi, postscale, post); break;
+    }
     // Nobody may repack its staging buffer while a peer still reads it
     // (unless the caller alternates between two staging regions).
+    trace_mark(ctx, 3);
     if (!ctx.skip_end_barrier) cta_barrier(ctx, ctx.epoch + 2, b, 2);
+    trace_mark(ctx, 4);
     return;
   } else {
     const int64_t per_rank = (nvec + world - 1) / world;
@@ -169,7 +193,9 @@ fused_allreduce_kernel(const InlineTensors inl, const TensorList tl_dev,
       const int64_t hi = min(lo + per_cta, min((r + 1) * per_rank, nvec));
       pack_range<T, W, S>(tl, stage, lo, hi, prescale, pre);
     }
+    trace_mark(ctx, 1);
     if (!cta_barrier(ctx, ctx.epoch + 1, b, 1)) return;
+    trace_mark(ctx, 2);
     {
       const int64_t lo = rank * per_rank + b * per_cta;
       const int64_t hi = min(lo + per_cta, min((rank + 1) * per_rank, nvec));
@@ -200,12 +226,15 @@ fused_allreduce_kernel(const InlineTensors inl, const TensorList tl_dev,
         }
       }
     }
+    trace_mark(ctx, 3);
     if (!cta_barrier(ctx, ctx.epoch + 2, b, 2)) return;
+    trace_mark(ctx, 4);
     for (int r = 0; r < world; ++r) {
       const int64_t lo = r * per_rank + b * per_cta;
       const int64_t hi = min(lo + per_cta, min((r + 1) * per_rank, nvec));
       unpack_range<T, W, S>(tl, stage, lo, hi, postscale, post);
     }
+    trace_mark(ctx, 5);
   }
 }
 

@@ -167,7 +167,11 @@ inplace_allreduce_kernel(const InlineRanges inl, const RangeList list_dev,
   const int b = blockIdx.x, G = gridDim.x;
   const bool do_scale = scale != 1.0f;
   // Everybody's producers have finished once their kernel is here.
-  if (!cta_barrier(ctx, ctx.epoch + 1, b, 1)) return;
+  trace_mark(ctx, 0);
+  const uint32_t token =
+      symm_token(ctx.epoch, rl.byte_off[0], rl.vec_start[rl.n] << 4, rl.n);
+  if (!cta_barrier_token(ctx, ctx.epoch + 1, b, 1, token)) return;
+  trace_mark(ctx, 2);
 
   const int64_t total = rl.vec_start[rl.n];  // vectors, ragged tails count as one
   const int64_t per_rank = (total + ctx.world - 1) / ctx.world;
@@ -200,7 +204,9 @@ inplace_allreduce_kernel(const InlineRanges inl, const RangeList list_dev,
     }
   }
   // Results are in every rank's tensor before anyone's kernel completes.
+  trace_mark(ctx, 3);
   cta_barrier(ctx, ctx.epoch + 2, b, 2);
+  trace_mark(ctx, 4);
 }
 
 template <typename W, bool NVLS>

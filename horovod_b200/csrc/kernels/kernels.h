@@ -37,11 +37,15 @@ struct SymmCtx {
   // guarantees that the staging region used by this launch is not written
   // again before every peer has passed a later barrier (double buffering).
   int skip_end_barrier;
+  // Optional phase timestamps (HOROVOD_KERNEL_TRACE=1): thread 0 of CTA 0
+  // stores %globaltimer into trace[slot] at the kernel's phase boundaries.
+  unsigned long long* trace;
 };
+constexpr int KERNEL_TRACE_SLOTS = 8;
 
 // Written by a kernel whose bounded wait ran out. code 0 = fine.
 struct KernelStatus {
-  int code;   // 1 = timeout waiting for a peer flag
+  int code;   // 1 = timeout waiting for a peer flag, 2 = symmetric-tensor mismatch
   int peer;   // rank that never arrived
   int phase;  // which barrier inside the kernel
   int block;  // CTA that gave up
@@ -127,7 +131,12 @@ cudaError_t LaunchFusedReducescatter(const void* in, void* out, int64_t count,
                                      DataType dtype, double prescale,
                                      double postscale, bool use_nvls,
                                      int num_ctas, const SymmCtx& ctx,
-                                     cudaStream_t stream);
+                                     cudaStream_t stream, int64_t sym_in_off = -1);
+// sym_in_off >= 0: the input already lives in symmetric memory at that byte
+// offset of every rank's arena (ctx.local/peers/mc must then point at the
+// arena base, and every shard must start on a 16-byte boundary); the kernel
+// skips staging and reduces straight out of the peers' tensors. prescale is
+// ignored in that mode: fold it into postscale.
 
 // Generic "push through staging" exchange used by allgather, broadcast and
 // alltoall: phase 1 copies each outbound segment from local tensors into the

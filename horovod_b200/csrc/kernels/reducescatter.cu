@@ -17,16 +17,78 @@ namespace {
 
 constexpr int THREADS = 512;
 
+// Sum of 16-byte vector `idx` (relative to the arena base) over all ranks.
+template <typename T, bool NVLS, int WORLD>
+__device__ __forceinline__ uint4 fetch_sum(const SymmCtx& ctx, int64_t idx) {
+  if constexpr (NVLS) {
+    return Multimem<T>::ld_reduce(reinterpret_cast<const uint4*>(ctx.mc) + idx);
+  } else {
+    uint4 x[WORLD];
+#pragma unroll
+    for (int p = 0; p < WORLD; ++p)
+      x[p] = ld16(reinterpret_cast<const uint4*>(ctx.peers[p]) + idx);
+    VecAcc<T> acc;
+    acc.zero();
+#pragma unroll
+    for (int p = 0; p < WORLD; ++p) acc.add(x[p]);
+    return acc.pack();
+  }
+}
+
+// Reduces vectors [lo, hi) of this rank's shard (n elements, first vector at
+// arena vector index `base`) and writes them, postscaled, to `out`.
+template <typename T, bool NVLS, int WORLD, int UNROLL>
+__device__ __forceinline__ void reduce_shard(const SymmCtx& ctx, int64_t base, int64_t lo,
+                                             int64_t hi, int64_t n, T* out,
+                                             typename ScaleT<T>::type postscale, bool post) {
+  constexpr int N = 16 / sizeof(T);
+  auto scaled = [&](uint4 raw) {
+    if (!post) return raw;
+    WireVec<T> w;
+    w.raw = raw;
+#pragma unroll
+    for (int i = 0; i < N; ++i) w.e[i] = scale_cast<T>(w.e[i], postscale, true);
+    return w.raw;
+  };
+  const bool aligned = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  const int64_t vfull = aligned ? max(lo, min(hi, n / N)) : lo;
+  uint4* o4 = reinterpret_cast<uint4*>(out);
+  int64_t v = lo + threadIdx.x;
+  for (; v + (UNROLL - 1) * THREADS < vfull; v += UNROLL * THREADS) {
+    uint4 x[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+      x[u] = fetch_sum<T, NVLS, WORLD>(ctx, base + v + u * THREADS);
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) st16_stream(o4 + v + u * THREADS, scaled(x[u]));
+  }
+  for (; v < vfull; v += THREADS)
+    st16_stream(o4 + v, scaled(fetch_sum<T, NVLS, WORLD>(ctx, base + v)));
+  // Ragged last vector, or an output that is not 16-byte aligned.
+  for (v = vfull + threadIdx.x; v < hi; v += THREADS) {
+    WireVec<T> w;
+    w.raw = scaled(fetch_sum<T, NVLS, WORLD>(ctx, base + v));
+    const int64_t e0 = v * N;
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+      if (e0 + i < n) out[e0 + i] = w.e[i];
+  }
+}
+
+// sym_in_off >= 0: the input tensor lives in symmetric memory at that byte
+// offset of every rank's arena with 16-byte aligned shard boundaries; nothing
+// is staged and the shard is reduced straight out of the peers' tensors.
 template <typename T, bool NVLS>
 __global__ void __launch_bounds__(THREADS)
 reducescatter_kernel(const T* in, T* out, const int64_t* shard_begin,
                      SymmCtx ctx, typename ScaleT<T>::type prescale,
-                     typename ScaleT<T>::type postscale) {
+                     typename ScaleT<T>::type postscale, int64_t sym_in_off) {
   using S = typename ScaleT<T>::type;
   constexpr int N = 16 / sizeof(T);
   const int world = ctx.world, rank = ctx.rank;
   const int b = blockIdx.x, G = gridDim.x;
   const bool pre = prescale != S(1), post = postscale != S(1);
+  const bool staged = sym_in_off < 0;
 
   // Staging layout: shard r starts at vector index vbase[r].
   __shared__ int64_t sb[SYMM_MAX_RANKS + 1];
@@ -47,7 +109,7 @@ reducescatter_kernel(const T* in, T* out, const int64_t* shard_begin,
   uint4* stage = reinterpret_cast<uint4*>(ctx.local);
 
   // Phase 1: pack slice b of every shard.
-  for (int r = 0; r < world; ++r) {
+  for (int r = 0; staged && r < world; ++r) {
     const int64_t n = sb[r + 1] - sb[r];
     const int64_t vecs = (n + N - 1) / N;
     const int64_t per = (vecs + G - 1) / G;
@@ -89,7 +151,12 @@ reducescatter_kernel(const T* in, T* out, const int64_t* shard_begin,
       st16(stage + vbase[r] + v, w.raw);
     }
   }
-  if (!cta_barrier(ctx, ctx.epoch + 1, b, 1)) return;
+  if (staged) {
+    if (!cta_barrier(ctx, ctx.epoch + 1, b, 1)) return;
+  } else {
+    const uint32_t token = symm_token(ctx.epoch, sym_in_off, sb[world] << 4, world);
+    if (!cta_barrier_token(ctx, ctx.epoch + 1, b, 1, token)) return;
+  }
 
   // Phase 2: reduce slice b of my shard and write it out.
   {
@@ -97,46 +164,35 @@ reducescatter_kernel(const T* in, T* out, const int64_t* shard_begin,
     const int64_t vecs = (n + N - 1) / N;
     const int64_t per = (vecs + G - 1) / G;
     const int64_t lo = b * per, hi = min(lo + per, vecs);
-    const bool aligned = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-    for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS) {
-      WireVec<T> w;
-      if constexpr (NVLS) {
-        w.raw = Multimem<T>::ld_reduce(reinterpret_cast<const uint4*>(ctx.mc) +
-                                       vbase[rank] + v);
-      } else {
-        uint4 x[SYMM_MAX_RANKS];
-#pragma unroll
-        for (int p = 0; p < SYMM_MAX_RANKS; ++p)
-          if (p < world)
-            x[p] = ld16(reinterpret_cast<const uint4*>(ctx.peers[p]) + vbase[rank] + v);
-        VecAcc<T> acc;
-        acc.zero();
-#pragma unroll
-        for (int p = 0; p < SYMM_MAX_RANKS; ++p)
-          if (p < world) acc.add(x[p]);
-        w.raw = acc.pack();
-      }
-      const int64_t e0 = v * N;
-      if (post) {
-#pragma unroll
-        for (int i = 0; i < N; ++i) w.e[i] = scale_cast<T>(w.e[i], postscale, true);
-      }
-      if (aligned && e0 + N <= n) {
-        st16_stream(reinterpret_cast<uint4*>(out) + v, w.raw);
-      } else {
-#pragma unroll
-        for (int i = 0; i < N; ++i)
-          if (e0 + i < n) out[e0 + i] = w.e[i];
+    // ctx.local/peers/mc point at the staging area (staged) or at the arena
+    // base (symmetric input).
+    const int64_t base = staged ? vbase[rank]
+                                : (sym_in_off + sb[rank] * static_cast<int64_t>(sizeof(T))) >> 4;
+    if constexpr (NVLS) {
+      reduce_shard<T, true, 8, 4>(ctx, base, lo, hi, n, out, postscale, post);
+    } else {
+      switch (world) {
+      case 1: reduce_shard<T, false, 1, 4>(ctx, base, lo, hi, n, out, postscale, post); break;
+      case 2: reduce_shard<T, false, 2, 4>(ctx, base, lo, hi, n, out, postscale, post); break;
+      case 3: reduce_shard<T, false, 3, 2>(ctx, base, lo, hi, n, out, postscale, post); break;
+      case 4: reduce_shard<T, false, 4, 2>(ctx, base, lo, hi, n, out, postscale, post); break;
+      case 5: reduce_shard<T, false, 5, 1>(ctx, base, lo, hi, n, out, postscale, post); break;
+      case 6: reduce_shard<T, false, 6, 1>(ctx, base, lo, hi, n, out, postscale, post); break;
+      case 7: reduce_shard<T, false, 7, 1>(ctx, base, lo, hi, n, out, postscale, post); break;
+      default: reduce_shard<T, false, 8, 1>(ctx, base, lo, hi, n, out, postscale, post); break;
       }
     }
   }
+  // Peers may still be reading this rank's data: neither the staging buffer
+  // nor a symmetric input may change before everybody is through.
   cta_barrier(ctx, ctx.epoch + 2, b, 2);
 }
 
 template <typename T>
 cudaError_t LaunchTyped(const void* in, void* out, const int64_t* shard_begin,
                         double prescale, double postscale, bool nvls,
-                        int num_ctas, const SymmCtx& ctx, cudaStream_t stream) {
+                        int num_ctas, const SymmCtx& ctx, cudaStream_t stream,
+                        int64_t sym_in_off) {
   using S = typename ScaleT<T>::type;
   constexpr bool can_nvls = std::is_same<T, float>::value ||
                             std::is_same<T, __half>::value ||
@@ -145,13 +201,13 @@ cudaError_t LaunchTyped(const void* in, void* out, const int64_t* shard_begin,
     if (nvls && ctx.mc != nullptr) {
       reducescatter_kernel<T, true><<<num_ctas, THREADS, 0, stream>>>(
           static_cast<const T*>(in), static_cast<T*>(out), shard_begin, ctx,
-          static_cast<S>(prescale), static_cast<S>(postscale));
+          static_cast<S>(prescale), static_cast<S>(postscale), sym_in_off);
       return cudaGetLastError();
     }
   }
   reducescatter_kernel<T, false><<<num_ctas, THREADS, 0, stream>>>(
       static_cast<const T*>(in), static_cast<T*>(out), shard_begin, ctx,
-      static_cast<S>(prescale), static_cast<S>(postscale));
+      static_cast<S>(prescale), static_cast<S>(postscale), sym_in_off);
   return cudaGetLastError();
 }
 
@@ -162,13 +218,13 @@ cudaError_t LaunchFusedReducescatter(const void* in, void* out, int64_t count,
                                      DataType dtype, double prescale,
                                      double postscale, bool use_nvls,
                                      int num_ctas, const SymmCtx& ctx,
-                                     cudaStream_t stream) {
+                                     cudaStream_t stream, int64_t sym_in_off) {
   (void)count;
   if (num_ctas < 1 || num_ctas > SYMM_MAX_BLOCKS) return cudaErrorInvalidValue;
   CountKernelLaunches(1);
 #define HVD_RS(T)                                                             \
   return LaunchTyped<T>(in, out, shard_begin_dev, prescale, postscale,        \
-                        use_nvls, num_ctas, ctx, stream)
+                        use_nvls, num_ctas, ctx, stream, sym_in_off)
   switch (dtype) {
   case DataType::FLOAT32: HVD_RS(float);
   case DataType::FLOAT16: HVD_RS(__half);

@@ -259,7 +259,10 @@ Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries,
       recv_off[p] = recv_off[p - 1] + recv[p - 1] * slice;
     }
     for (int r = 0; r < n; ++r) {
-      for (int p = 0; p < n; ++p) {
+      // Rank r sends to r+1, r+2, ... in turn: at any time every GPU is the
+      // target of one sender instead of everybody writing to rank 0 first.
+      for (int j = 1; j <= n; ++j) {
+        const int p = (r + j) % n;
         Block b;
         b.src_rank = r;
         b.dst_rank = p;

@@ -140,6 +140,7 @@ public:
   int64_t symm_heap_bytes() const { return heap_bytes_; }
   int64_t symm_heap_used() const { return heap_used_.load(); }
   int device() const { return device_; }
+  const unsigned long long* kernel_trace() const { return trace_host_; }
 
   // Used by the NCCL path.
   cudaStream_t stream() const { return stream_; }
@@ -197,6 +198,8 @@ private:
   char* heap_base_ = nullptr;  // local address of heap_off_
   kern::KernelStatus* status_host_ = nullptr;  // mapped pinned memory
   int* status_dev_ = nullptr;
+  unsigned long long* trace_host_ = nullptr;  // mapped pinned, HOROVOD_KERNEL_TRACE=1
+  unsigned long long* trace_dev_ = nullptr;
   std::map<int32_t, std::unique_ptr<SymmSet>> sets_;
   std::unique_ptr<NcclOps> nccl_;
   bool shut_down_ = false;

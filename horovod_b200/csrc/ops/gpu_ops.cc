@@ -122,7 +122,7 @@ GpuOps::GpuOps(GlobalState& s) : state_(s), events_(new DoneEventPool()) {
   want_nvls_ = EnvBool(HVD_ENV_SYMM_NVLS, true);
   timeout_ns_ = static_cast<unsigned long long>(
                     EnvInt(HVD_ENV_SPIN_TIMEOUT_MS, 20000)) * 1000000ull;
-  oneshot_max_ = EnvInt(HVD_ENV_ONESHOT_MAX, 512 * 1024);
+  oneshot_max_ = EnvInt(HVD_ENV_ONESHOT_MAX, -1);  // -1: by world size
   nvls_min_ = EnvInt(HVD_ENV_NVLS_MIN, 512 * 1024);
   forced_ctas_ = static_cast<int>(EnvInt(HVD_ENV_COMM_CTAS, 0));
   forced_algo_ = EnvString(HVD_ENV_ALGO, "auto");
@@ -150,6 +150,13 @@ void GpuOps::EnsureDevice(int device) {
   std::memset(status_host_, 0, sizeof(kern::KernelStatus));
   HVD_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev_),
                                     status_host_, 0));
+  if (EnvBool("HOROVOD_KERNEL_TRACE", false)) {
+    HVD_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&trace_host_),
+                           kern::KERNEL_TRACE_SLOTS * sizeof(unsigned long long),
+                           cudaHostAllocMapped));
+    std::memset(trace_host_, 0, kern::KERNEL_TRACE_SLOTS * sizeof(unsigned long long));
+    HVD_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&trace_dev_), trace_host_, 0));
+  }
   finalizer_.Start(1);
   device_ = device;
 }
@@ -202,7 +209,7 @@ SymmSet* GpuOps::GetSymmSet(ProcessSet& ps) {
   set->data_bytes = static_cast<size_t>(heap_off_);  // staging part only
   // Room for the two one-shot regions (kept out of the general staging area
   // for every set, so that no other kernel ever writes there).
-  const int64_t region = RoundUp(oneshot_max_ + 4096, 4096);
+  const int64_t region = RoundUp(std::max<int64_t>(oneshot_max_, 4 << 20) + 4096, 4096);
   if (static_cast<int64_t>(set->data_bytes) > 4 * region) {
     set->data_bytes = set->data_bytes - 2 * region;
     if (ps.id == 0) {
@@ -247,11 +254,19 @@ kern::SymmCtx GpuOps::MakeCtx(SymmSet& set, uint32_t epochs, int64_t staging_off
   c.epoch = set.epoch;
   c.timeout_ns = timeout_ns_;
   c.status = status_dev_;
+  c.trace = trace_dev_;
   set.epoch += epochs;
   return c;
 }
 
 Status GpuOps::CheckKernelStatus() {
+  if (status_host_ != nullptr && status_host_->code == 2) {
+    return Status::PreconditionError(
+        "Rank " + std::to_string(status_host_->peer) +
+        " did not pass the same symmetric-memory tensors to this collective. Tensors "
+        "from hvd.symmetric_empty() must be used by all ranks alike (same allocation, "
+        "same slices).");
+  }
   if (status_host_ != nullptr && status_host_->code != 0) {
     return Status::UnknownError(
         "A collective kernel timed out waiting for rank " +
@@ -264,12 +279,15 @@ Status GpuOps::CheckKernelStatus() {
 
 int GpuOps::PickCtas(int64_t bytes) const {
   if (forced_ctas_ > 0) return std::min(forced_ctas_, SYMM_MAX_BLOCKS);
-  // Few CTAs for latency-bound sizes, more as the message grows; capped well
-  // below the SM count so backward keeps most of the GPU.
+  // Few CTAs for latency-bound sizes, more as the message grows: a CTA keeps
+  // about 32 KB of peer loads in flight, and NVLink needs a few MB in flight
+  // to run at full rate.
   if (bytes <= 64 * 1024) return 4;
-  if (bytes <= 1 << 20) return 16;
-  if (bytes <= 16 << 20) return 48;
-  return 96;
+  if (bytes <= 512 << 10) return 16;
+  if (bytes <= 2 << 20) return 32;
+  if (bytes <= 8 << 20) return 64;
+  if (bytes <= 32 << 20) return 96;
+  return 148;
 }
 
 kern::Algo GpuOps::PickAlgo(const SymmSet& set, DataType wire,
@@ -280,7 +298,13 @@ kern::Algo GpuOps::PickAlgo(const SymmSet& set, DataType wire,
   if (forced_algo_ == "oneshot") return kern::Algo::ONESHOT;
   if (forced_algo_ == "twoshot") return kern::Algo::TWOSHOT;
   if (forced_algo_ == "nvls" && set.nvls && nvls_type) return kern::Algo::NVLS;
-  if (bytes <= oneshot_max_) return kern::Algo::ONESHOT;
+  // One-shot costs one barrier less than two-shot but every rank reads all
+  // of every peer's data: (N-1)S instead of 2S(N-1)/N over NVLink. With two
+  // ranks that is the same traffic, so one-shot always wins there.
+  int64_t oneshot_max = oneshot_max_;
+  if (oneshot_max < 0)
+    oneshot_max = set.world == 2 ? INT64_MAX : set.world <= 4 ? (2 << 20) : (512 << 10);
+  if (bytes <= oneshot_max) return kern::Algo::ONESHOT;
   // Per-GPU NVLink traffic: NVLS moves S(N+1)/N each way, two-shot over peer
   // loads/stores 2S(N-1)/N, so the switch reduction wins from 4 ranks on.
   if (set.nvls && nvls_type && bytes >= nvls_min_ && set.world >= 4)
@@ -471,6 +495,9 @@ void GpuOps::Shutdown() {
   ring_.Destroy();
   if (status_host_) cudaFreeHost(status_host_);
   status_host_ = nullptr;
+  if (trace_host_) cudaFreeHost(trace_host_);
+  trace_host_ = nullptr;
+  trace_dev_ = nullptr;
   if (stream_) cudaStreamDestroy(stream_);
   stream_ = nullptr;
   SetGpuBackendDescription("none");

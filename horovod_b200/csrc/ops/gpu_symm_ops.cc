@@ -295,12 +295,19 @@ Status GpuOps::SymmReducescatter(std::vector<TensorTableEntry>& entries,
     int64_t* d_sb;
     int64_t* h_sb = slot.Alloc<int64_t>(n + 1, &d_sb);
     int64_t staged = 0;
+    bool shards_aligned = true;
     for (int r = 0; r <= n; ++r) {
       h_sb[r] = (r * base + std::min<int64_t>(r, extra)) * slice;
+      if ((h_sb[r] * es) & 15) shards_aligned = false;
       if (r > 0)
         staged += RoundUp((h_sb[r] - h_sb[r - 1]) * es, STAGING_ALIGN);
     }
-    if (staged > static_cast<int64_t>(set.data_bytes))
+    // An input inside the symmetric heap is reduced in place: no staging.
+    int64_t sym_off = -1, heap_off = 0;
+    if (n > 1 && shards_aligned && e.input != nullptr &&
+        InSymmHeap(e.input, e.num_elements() * es, &heap_off) && (heap_off & 15) == 0)
+      sym_off = heap_off;
+    if (sym_off < 0 && staged > static_cast<int64_t>(set.data_bytes))
       return Status::InvalidArgument(
           "reducescatter tensor '" + e.name + "' does not fit the symmetric "
           "staging buffer; raise HOROVOD_SYMM_BUFFER_MB.");
@@ -308,8 +315,9 @@ Status GpuOps::SymmReducescatter(std::vector<TensorTableEntry>& entries,
     kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH);
     tl.ActivityStart(e.name, HVD_ACT_FUSED_KERNEL);
     cudaError_t err = kern::LaunchFusedReducescatter(
-        e.input, out, e.num_elements(), d_sb, e.dtype, e.prescale, e.postscale,
-        set.nvls, PickCtas(staged), ctx, stream_);
+        e.input, out, e.num_elements(), d_sb, e.dtype, sym_off >= 0 ? 1.0 : e.prescale,
+        sym_off >= 0 ? e.prescale * e.postscale : e.postscale, set.nvls, PickCtas(staged),
+        ctx, stream_, sym_off);
     tl.ActivityEnd(e.name);
     ring_.Release(slot, stream_);
     if (err != cudaSuccess)

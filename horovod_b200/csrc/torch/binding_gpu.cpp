@@ -71,6 +71,16 @@ void BindGpuDiagnostics(py::module_& m) {
     for (auto& x : t) out.append(py::make_tuple(x.type, x.bytes, x.tensors, x.device_us));
     return out;
   });
+  m.def("kernel_trace", []() {
+    // %globaltimer (ns) at the phase boundaries of the last traced allreduce
+    // kernel: 0 start, 1 packed, 2 first barrier passed, 3 reduced,
+    // 4 second barrier passed, 5 unpacked. Needs HOROVOD_KERNEL_TRACE=1.
+    GpuOps* ops = CurrentGpuOps();
+    std::vector<unsigned long long> out;
+    if (ops != nullptr && ops->kernel_trace() != nullptr)
+      out.assign(ops->kernel_trace(), ops->kernel_trace() + kern::KERNEL_TRACE_SLOTS);
+    return out;
+  });
   m.def("kernel_launch_count", &kern::KernelLaunchCount,
         "Kernels of this library launched so far in this process.");
 }

@@ -108,11 +108,26 @@ class _DistributedOptimizer(torch.optim.Optimizer):
         it, so that the gradient allreduce runs in place over NVLink with no
         staging copies. Same parameter order on every rank (sorted by name)."""
         from horovod_b200.torch.mpi_ops import symmetric_empty
+        import warnings
+        try:
+            symmetric_empty(64)  # builds the arena; fails on the NCCL path
+        except RuntimeError as e:
+            warnings.warn("symmetric_gradients ignored: %s" % e)
+            return
         by_dtype = {}
         for p, name in sorted(self._parameter_names.items(), key=lambda kv: kv[1]):
             if p.requires_grad and p.is_cuda and p.dtype.is_floating_point and \
                     (p.is_contiguous() or _is_dense(p)):
                 by_dtype.setdefault(p.dtype, []).append(p)
+        from horovod_b200 import _C
+        need = sum((p.numel() * p.element_size() + 255) // 256 * 256
+                   for plist in by_dtype.values() for p in plist)
+        heap = _C.symm_heap_info()
+        if need > heap["bytes"] - heap["used"]:
+            warnings.warn("symmetric_gradients ignored: gradients need %d MB, the symmetric "
+                          "heap has %d MB left (HOROVOD_SYMM_HEAP_MB)"
+                          % (need >> 20, (heap["bytes"] - heap["used"]) >> 20))
+            return
         for dtype, plist in sorted(by_dtype.items(), key=lambda kv: str(kv[0])):
             es = torch.empty((), dtype=dtype).element_size()
             slot = 256 // es  # every gradient starts on a 256-byte boundary

@@ -217,6 +217,20 @@ def _long_lists_and_heap(rank, size, inline):
     flat[:128] = float(rank)
     hvd.grouped_allreduce_(mixed, op=hvd.Sum, name="mixed")
     assert bool((mixed[0] == sum(range(size))).all()) and bool((mixed[1] == size).all())
+    # Reduce-scatter straight out of a symmetric input (16-byte aligned shards)
+    # and through staging (ragged shards).
+    for rows, cols in ((size * 1024, 8), (size * 5 + 1, 3)):
+        src = hvd.symmetric_empty(rows, cols)
+        src.copy_(_inputs(rank + 9, rows * cols, torch.float32).view(rows, cols).to(dev))
+        keep = src.clone()
+        got = hvd.reducescatter(src, op=hvd.Average, name="heap.rs.%d" % rows)
+        full = sum(_inputs(r + 9, rows * cols, torch.float32).double()
+                   for r in range(size)).view(rows, cols) / size
+        base, extra = divmod(rows, size)
+        lo = rank * base + min(rank, extra)
+        hi = lo + base + (1 if rank < extra else 0)
+        assert (got.double().cpu() - full[lo:hi]).abs().max().item() < 1e-5
+        assert torch.equal(src, keep), "reducescatter changed its input"
     info = hvd.gpu_backend()
     torch.cuda.synchronize()
     hvd.shutdown()
@@ -284,3 +298,46 @@ def test_optimizer_with_symmetric_gradients():
     if _ngpu() < 2:
         pytest.skip("needs 2 GPUs")
     assert all(run_parallel(_symmetric_gradients, np=2, timeout=300))
+
+
+def _asymmetric_use(rank, size):
+    os.environ["HOROVOD_SPIN_TIMEOUT_MS"] = "1000"
+    import horovod_b200.torch as hvd
+    hvd.init()
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    z = hvd.symmetric_empty(4096)
+    z.fill_(1.0)
+    hvd.allreduce_(z, op=hvd.Sum, name="warm")  # both ranks symmetric: fine
+    ok = bool((z == size).all())
+    # Rank 0 hands in the symmetric tensor, rank 1 an ordinary one: the
+    # kernels notice (token mismatch / bounded wait) and both ranks get an
+    # error instead of a wrong sum.
+    x = z if rank == 0 else torch.ones(4096, device=dev)
+    try:
+        hvd.allreduce_(x, op=hvd.Sum, name="mixed.up")
+        torch.cuda.synchronize()
+        # the error may surface at the next op
+        hvd.allreduce_(torch.ones(8, device=dev), op=hvd.Sum, name="after")
+        torch.cuda.synchronize()
+        failed = False
+    except Exception as e:  # HorovodInternalError or RuntimeError
+        failed = True
+        msg = str(e)
+        if rank == 0:
+            ok = ok and "symmetric" in msg
+    try:
+        hvd.shutdown()
+    except Exception:
+        pass
+    return ok, failed
+
+
+def test_asymmetric_use_of_symmetric_memory_is_reported():
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    out = run_parallel(_asymmetric_use, np=2, timeout=300)
+    # The rank that addressed peers by symmetric offset must report it; the
+    # other rank either times out on its next collective or sees the shutdown.
+    assert out[0] == (True, True), out
+    assert out[1][0], out

@@ -210,11 +210,20 @@ def main():
         sampler.start()
     launches0 = _C.kernel_launch_count()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # With HOROVOD_BENCH_CUPROFILE=1 the timed steps are bracketed by
+    # cudaProfilerStart/Stop, so that `ncu --profile-from-start off` lists
+    # the launches of exactly this region (numbers from such a run are not
+    # bench values).
+    cuprofile = os.environ.get("HOROVOD_BENCH_CUPROFILE") == "1"
+    if cuprofile:
+        torch.cuda.profiler.start()
     start.record()
     for _ in range(args.steps):
         step(dev_x, dev_y)
     end.record()
     torch.cuda.synchronize()
+    if cuprofile:
+        torch.cuda.profiler.stop()
     launches = _C.kernel_launch_count() - launches0
     clocks = sampler.stop() if hvd.rank() == 0 else None
     barrier()

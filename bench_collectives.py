@@ -43,7 +43,12 @@ def main():
                                     "broadcast,alltoall,grouped,allreduce_symm,grouped_symm")
     p.add_argument("--algo", default=None, help="force oneshot|twoshot|nvls")
     p.add_argument("--ctas", type=int, default=0)
+    p.add_argument("--phases", action="store_true",
+                   help="also report where the time goes inside the allreduce kernels "
+                        "(device timestamps at phase boundaries, HOROVOD_KERNEL_TRACE=1)")
     args = p.parse_args()
+    if args.phases:
+        os.environ["HOROVOD_KERNEL_TRACE"] = "1"
 
     os.environ["HOROVOD_GPU_BACKEND"] = args.backend
     os.environ["HOROVOD_GPU_OP_TIMING"] = "1"
@@ -79,7 +84,25 @@ def main():
         t = hvd.allreduce(t, op=hvd.Max, name="sweep.times.%d" % len(mine))
         return statistics.median(t.tolist())
 
-    def emit(op, dtype, nbytes, us, bus_factor, wire_bytes):
+    PHASES = ("start", "packed", "barrier1", "reduced", "barrier2", "unpacked")
+
+    def phases(fn):
+        """Median offsets (us since kernel start, CTA 0 of this rank) of the
+        phase boundaries of the traced allreduce kernel, max over ranks."""
+        cols = []
+        for _ in range(args.iters):
+            fn()
+            torch.cuda.synchronize()
+            t = _C.kernel_trace()
+            cols.append([(t[i] - t[0]) / 1e3 if t[i] >= t[0] and t[i] else -1.0
+                         for i in range(len(PHASES))])
+            hvd.allreduce(torch.zeros(1), name="sweep.phase.sync")
+        med = [statistics.median(c[i] for c in cols) for i in range(len(PHASES))]
+        t = hvd.allreduce(torch.tensor(med, dtype=torch.float64), op=hvd.Max,
+                          name="sweep.phases")
+        return {k: round(v, 1) for k, v in zip(PHASES, t.tolist()) if v >= 0}
+
+    def emit(op, dtype, nbytes, us, bus_factor, wire_bytes, extra=None):
         if rank != 0:
             return
         bus = nbytes * bus_factor / (us * 1e-6) / 1e9 if us > 0 else 0.0
@@ -89,7 +112,7 @@ def main():
                           "bus_gbs": round(bus, 2),
                           "roofline_us": round(roof_us, 2),
                           "frac_of_nvlink_roofline": round(roof_us / us, 4) if us > 0 else None,
-                          "gradient_path": hvd.gpu_backend()}), flush=True)
+                          "gradient_path": hvd.gpu_backend(), **(extra or {})}), flush=True)
 
     def ar_wire(nbytes):
         nvls = n >= 4 and "nvls=1" in hvd.gpu_backend()
@@ -112,11 +135,15 @@ def main():
         if "allreduce_symm" in ops and heap is not None:
             x = heap[:nbytes // 4]
             us = measure(lambda: hvd.allreduce_(x, op=hvd.Average, name="sw.ars"), ALLREDUCE)
-            emit("allreduce_symm", "fp32", nbytes, us, 2 * (n - 1) / n, ar_wire(nbytes))
+            ph = {"phases_us": phases(lambda: hvd.allreduce_(x, op=hvd.Average, name="sw.ars"))} \
+                if args.phases else None
+            emit("allreduce_symm", "fp32", nbytes, us, 2 * (n - 1) / n, ar_wire(nbytes), ph)
         if "allreduce" in ops:
             x = torch.randn(nbytes // 4, device=dev)
             us = measure(lambda: hvd.allreduce_(x, op=hvd.Sum, name="sw.ar"), ALLREDUCE)
-            emit("allreduce", "fp32", nbytes, us, 2 * (n - 1) / n, ar_wire(nbytes))
+            ph = {"phases_us": phases(lambda: hvd.allreduce_(x, op=hvd.Sum, name="sw.ar"))} \
+                if args.phases else None
+            emit("allreduce", "fp32", nbytes, us, 2 * (n - 1) / n, ar_wire(nbytes), ph)
         if "allreduce_bf16" in ops:
             x = torch.randn(nbytes // 2, device=dev).bfloat16()
             us = measure(lambda: hvd.allreduce_(x, op=hvd.Sum, name="sw.arb"), ALLREDUCE)

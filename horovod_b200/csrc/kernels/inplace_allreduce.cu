@@ -135,13 +135,44 @@ __device__ __forceinline__ void reduce_tail(const SymmCtx& ctx, int64_t byte_off
   }
 }
 
+// Vectors [lo, hi) of the fused vector space, which may span several ranges.
+template <typename W, bool NVLS, int WORLD>
+__device__ __forceinline__ void reduce_span(const RangeList& rl, const SymmCtx& ctx,
+                                            int64_t lo, int64_t hi, float scale,
+                                            bool do_scale) {
+  if (lo >= hi) return;
+  // first range that may contain `lo`
+  int t = 0;
+  {
+    int a = 0, z = rl.n - 1;
+    while (a < z) {
+      int mid = (a + z + 1) >> 1;
+      if (rl.vec_start[mid] <= lo) a = mid; else z = mid - 1;
+    }
+    t = a;
+  }
+  for (; t < rl.n; ++t) {
+    const int64_t r0 = rl.vec_start[t];
+    if (r0 >= hi) break;
+    const int64_t r1 = rl.vec_start[t + 1];
+    const int64_t full = rl.bytes[t] >> 4;  // whole vectors in this range
+    const int64_t v0 = max(lo, r0) - r0, v1 = min(hi, r1) - r0;
+    reduce_vectors<W, NVLS, WORLD>(ctx, rl.byte_off[t], v0, min(v1, full), scale, do_scale);
+    if (v1 > full && full >= v0) {
+      // this span owns the ragged last vector of the range
+      const int tail = static_cast<int>((rl.bytes[t] & 15) / sizeof(W));
+      reduce_tail<W>(ctx, rl.byte_off[t] + (full << 4), tail, scale, do_scale);
+    }
+  }
+}
+
 // INLINE: the range list rides in the kernel parameters and is copied to
 // shared memory first (parameter reads with compile-time offsets only); else
 // it is read from device memory.
 template <typename W, bool NVLS, int WORLD, bool INLINE>
 __global__ void __launch_bounds__(THREADS)
 inplace_allreduce_kernel(const InlineRanges inl, const RangeList list_dev,
-                         SymmCtx ctx, float scale) {
+                         SymmCtx ctx, float scale, TileSchedule sched) {
   __shared__ int64_t s_vec_start[INLINE ? INLINE_TENSORS + 1 : 1];
   __shared__ int64_t s_byte_off[INLINE ? INLINE_TENSORS : 1];
   __shared__ int64_t s_bytes[INLINE ? INLINE_TENSORS : 1];
@@ -175,32 +206,29 @@ inplace_allreduce_kernel(const InlineRanges inl, const RangeList list_dev,
 
   const int64_t total = rl.vec_start[rl.n];  // vectors, ragged tails count as one
   const int64_t per_rank = (total + ctx.world - 1) / ctx.world;
-  const int64_t per_cta = (per_rank + G - 1) / G;
-  const int64_t lo = ctx.rank * per_rank + b * per_cta;
-  const int64_t hi = min(lo + per_cta, min((ctx.rank + 1) * per_rank, total));
-  if (lo < hi) {
-    // first range that may contain `lo`
-    int t = 0;
-    {
-      int a = 0, z = rl.n - 1;
-      while (a < z) {
-        int mid = (a + z + 1) >> 1;
-        if (rl.vec_start[mid] <= lo) a = mid; else z = mid - 1;
-      }
-      t = a;
-    }
-    for (; t < rl.n; ++t) {
-      const int64_t r0 = rl.vec_start[t];
-      if (r0 >= hi) break;
-      const int64_t r1 = rl.vec_start[t + 1];
-      const int64_t full = rl.bytes[t] >> 4;  // whole vectors in this range
-      const int64_t v0 = max(lo, r0) - r0, v1 = min(hi, r1) - r0;
-      reduce_vectors<W, NVLS, WORLD>(ctx, rl.byte_off[t], v0, min(v1, full), scale, do_scale);
-      if (v1 > full && full >= v0) {
-        // this CTA owns the ragged last vector of the range
-        const int tail = static_cast<int>((rl.bytes[t] & 15) / sizeof(W));
-        reduce_tail<W>(ctx, rl.byte_off[t] + (full << 4), tail, scale, do_scale);
-      }
+  const int64_t mine_lo = ctx.rank * per_rank;
+  const int64_t mine_hi = min(mine_lo + per_rank, total);
+  if (sched.counter == nullptr) {
+    // Static split: CTA b owns slice b of this rank's chunk.
+    const int64_t per_cta = (per_rank + G - 1) / G;
+    const int64_t lo = mine_lo + b * per_cta;
+    reduce_span<W, NVLS, WORLD>(rl, ctx, lo, min(lo + per_cta, mine_hi), scale, do_scale);
+  } else {
+    // Dynamic split for large messages: CTAs draw tiles from a counter, so
+    // SMs that get less NVLink or HBM bandwidth simply take fewer tiles and
+    // nobody waits for a straggler. The counter only ever grows: this launch
+    // owns the values [base, base + ntiles + gridDim.x).
+    __shared__ unsigned long long s_tile;
+    const int64_t ntiles = (mine_hi - mine_lo + sched.tile_vecs - 1) / sched.tile_vecs;
+    for (;;) {
+      if (threadIdx.x == 0) s_tile = atomicAdd(sched.counter, 1ULL) - sched.base;
+      __syncthreads();
+      const int64_t t = static_cast<int64_t>(s_tile);
+      __syncthreads();
+      if (t < 0 || t >= ntiles) break;  // t < 0: counter behind the host (failed launch)
+      const int64_t lo = mine_lo + t * sched.tile_vecs;
+      reduce_span<W, NVLS, WORLD>(rl, ctx, lo, min(lo + sched.tile_vecs, mine_hi), scale,
+                                  do_scale);
     }
   }
   // Results are in every rank's tensor before anyone's kernel completes.
@@ -211,15 +239,16 @@ inplace_allreduce_kernel(const InlineRanges inl, const RangeList list_dev,
 
 template <typename W, bool NVLS>
 cudaError_t LaunchWorld(const InlineRanges& inl, const RangeList& rl, int num_ctas,
-                        const SymmCtx& ctx, float scale, cudaStream_t stream) {
+                        const SymmCtx& ctx, float scale, cudaStream_t stream,
+                        const TileSchedule& sched) {
 #define HVD_IP(WD)                                                                      \
   do {                                                                                  \
     if (inl.n > 0)                                                                      \
       inplace_allreduce_kernel<W, NVLS, WD, true><<<num_ctas, THREADS, 0, stream>>>(    \
-          inl, rl, ctx, scale);                                                         \
+          inl, rl, ctx, scale, sched);                                                  \
     else                                                                                \
       inplace_allreduce_kernel<W, NVLS, WD, false><<<num_ctas, THREADS, 0, stream>>>(   \
-          inl, rl, ctx, scale);                                                         \
+          inl, rl, ctx, scale, sched);                                                  \
   } while (0)
   if constexpr (NVLS) {
     HVD_IP(8);  // WORLD is unused on the multimem path
@@ -244,26 +273,29 @@ cudaError_t LaunchWorld(const InlineRanges& inl, const RangeList& rl, int num_ct
 cudaError_t LaunchInplaceAllreduce(const RangeList& ranges, DataType dtype,
                                    double scale, bool use_nvls, int num_ctas,
                                    const SymmCtx& ctx, cudaStream_t stream,
-                                   const InlineRanges* inline_ranges) {
+                                   const InlineRanges* inline_ranges,
+                                   const TileSchedule* schedule) {
   if (num_ctas < 1 || num_ctas > SYMM_MAX_BLOCKS) return cudaErrorInvalidValue;
   if (ctx.world < 2) return cudaErrorInvalidValue;
   static const InlineRanges kNoInline = {};
   const InlineRanges& inl = inline_ranges ? *inline_ranges : kNoInline;
   const float s = static_cast<float>(scale);
   const bool nvls = use_nvls && ctx.mc != nullptr;
+  static const TileSchedule kStatic = {nullptr, 0, 0};
+  const TileSchedule& sched = schedule ? *schedule : kStatic;
   CountKernelLaunches(1);
   switch (dtype) {
   case DataType::FLOAT32:
-    return nvls ? LaunchWorld<float, true>(inl, ranges, num_ctas, ctx, s, stream)
-                : LaunchWorld<float, false>(inl, ranges, num_ctas, ctx, s, stream);
+    return nvls ? LaunchWorld<float, true>(inl, ranges, num_ctas, ctx, s, stream, sched)
+                : LaunchWorld<float, false>(inl, ranges, num_ctas, ctx, s, stream, sched);
   case DataType::FLOAT16:
-    return nvls ? LaunchWorld<__half, true>(inl, ranges, num_ctas, ctx, s, stream)
-                : LaunchWorld<__half, false>(inl, ranges, num_ctas, ctx, s, stream);
+    return nvls ? LaunchWorld<__half, true>(inl, ranges, num_ctas, ctx, s, stream, sched)
+                : LaunchWorld<__half, false>(inl, ranges, num_ctas, ctx, s, stream, sched);
   case DataType::BFLOAT16:
-    return nvls ? LaunchWorld<__nv_bfloat16, true>(inl, ranges, num_ctas, ctx, s, stream)
-                : LaunchWorld<__nv_bfloat16, false>(inl, ranges, num_ctas, ctx, s, stream);
+    return nvls ? LaunchWorld<__nv_bfloat16, true>(inl, ranges, num_ctas, ctx, s, stream, sched)
+                : LaunchWorld<__nv_bfloat16, false>(inl, ranges, num_ctas, ctx, s, stream, sched);
   case DataType::FLOAT64:
-    return LaunchWorld<double, false>(inl, ranges, num_ctas, ctx, s, stream);
+    return LaunchWorld<double, false>(inl, ranges, num_ctas, ctx, s, stream, sched);
   default:
     return cudaErrorInvalidValue;
   }

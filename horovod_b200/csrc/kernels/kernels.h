@@ -118,10 +118,21 @@ struct InlineRanges {
   int64_t byte_off[INLINE_TENSORS];
   int64_t bytes[INLINE_TENSORS];
 };
+// Dynamic work distribution for large in-place allreduces: CTAs draw tiles of
+// `tile_vecs` 16-byte vectors from a device counter that only ever grows. A
+// launch with T tiles and G CTAs consumes exactly T + G counter values starting
+// at `base` (every CTA draws once more than it gets). counter == nullptr: static
+// split, one slice per CTA.
+struct TileSchedule {
+  unsigned long long* counter;
+  unsigned long long base;
+  int tile_vecs;
+};
 cudaError_t LaunchInplaceAllreduce(const RangeList& ranges, DataType dtype,
                                    double scale, bool use_nvls, int num_ctas,
                                    const SymmCtx& ctx, cudaStream_t stream,
-                                   const InlineRanges* inline_ranges = nullptr);
+                                   const InlineRanges* inline_ranges = nullptr,
+                                   const TileSchedule* schedule = nullptr);
 
 // Fused reduce-scatter: like the first half of the two-shot allreduce; rank
 // r's output receives elements [shard_begin[r], shard_begin[r+1]) of the

@@ -198,6 +198,9 @@ private:
   char* heap_base_ = nullptr;  // local address of heap_off_
   kern::KernelStatus* status_host_ = nullptr;  // mapped pinned memory
   int* status_dev_ = nullptr;
+  unsigned long long* tile_counter_ = nullptr;  // device word, see kern::TileSchedule
+  unsigned long long tile_base_ = 0;
+  int64_t dynamic_min_bytes_ = 0;
   unsigned long long* trace_host_ = nullptr;  // mapped pinned, HOROVOD_KERNEL_TRACE=1
   unsigned long long* trace_dev_ = nullptr;
   std::map<int32_t, std::unique_ptr<SymmSet>> sets_;

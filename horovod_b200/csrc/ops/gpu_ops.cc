@@ -150,6 +150,10 @@ void GpuOps::EnsureDevice(int device) {
   std::memset(status_host_, 0, sizeof(kern::KernelStatus));
   HVD_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev_),
                                     status_host_, 0));
+  HVD_CUDA(cudaMalloc(reinterpret_cast<void**>(&tile_counter_), sizeof(unsigned long long)));
+  HVD_CUDA(cudaMemset(tile_counter_, 0, sizeof(unsigned long long)));
+  tile_base_ = 0;
+  dynamic_min_bytes_ = EnvInt("HOROVOD_DYNAMIC_TILES_MIN_BYTES", 8 << 20);
   if (EnvBool("HOROVOD_KERNEL_TRACE", false)) {
     HVD_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&trace_host_),
                            kern::KERNEL_TRACE_SLOTS * sizeof(unsigned long long),
@@ -287,7 +291,8 @@ int GpuOps::PickCtas(int64_t bytes) const {
   if (bytes <= 2 << 20) return 32;
   if (bytes <= 8 << 20) return 64;
   if (bytes <= 32 << 20) return 96;
-  return 148;
+  if (bytes <= 128 << 20) return 148;
+  return 296;  // two CTAs per SM: where the local copy phases peak
 }
 
 kern::Algo GpuOps::PickAlgo(const SymmSet& set, DataType wire,
@@ -495,6 +500,8 @@ void GpuOps::Shutdown() {
   ring_.Destroy();
   if (status_host_) cudaFreeHost(status_host_);
   status_host_ = nullptr;
+  if (tile_counter_) cudaFree(tile_counter_);
+  tile_counter_ = nullptr;
   if (trace_host_) cudaFreeHost(trace_host_);
   trace_host_ = nullptr;
   trace_dev_ = nullptr;

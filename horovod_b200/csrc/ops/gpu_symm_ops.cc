@@ -260,10 +260,24 @@ bool GpuOps::TryInplaceAllreduce(std::vector<TensorTableEntry>& entries,
   const bool nvls = set.nvls && dtype != DataType::FLOAT64 && set.world >= 4 &&
                     forced_algo_ != "twoshot" && forced_algo_ != "oneshot";
   kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH);
+  const int ctas = PickCtas(total_bytes);
+  // Large messages: tiles of 64 KB drawn from a counter instead of one
+  // slice per CTA (per-SM NVLink bandwidth is uneven on a two-die GPU).
+  kern::TileSchedule sched = {nullptr, 0, 0};
+  if (dynamic_min_bytes_ >= 0 && total_bytes >= dynamic_min_bytes_) {
+    sched.counter = tile_counter_;
+    sched.base = tile_base_;
+    sched.tile_vecs = 4096;
+    const int64_t per_rank = (v + set.world - 1) / set.world;
+    const int64_t mine = std::max<int64_t>(
+        0, std::min<int64_t>(per_rank, v - static_cast<int64_t>(set.rank) * per_rank));
+    tile_base_ += static_cast<unsigned long long>((mine + sched.tile_vecs - 1) / sched.tile_vecs) +
+                  static_cast<unsigned long long>(ctas);
+  }
   cudaError_t err = kern::LaunchInplaceAllreduce(
       list, dtype, response.prescale * response.postscale,
       nvls || (forced_algo_ == "nvls" && set.nvls && dtype != DataType::FLOAT64),
-      PickCtas(total_bytes), ctx, stream_, use_inline ? &inl : nullptr);
+      ctas, ctx, stream_, use_inline ? &inl : nullptr, &sched);
   if (!use_inline) ring_.Release(slot, stream_);
   *status = err == cudaSuccess
                 ? Status::OK()

@@ -61,14 +61,49 @@ adasum_pack_kernel(TensorList tl, SymmCtx ctx, float prescale, double* scratch,
                                          [stage](int64_t v, uint4 x) { st16(stage + v, x); });
 }
 
-__device__ __forceinline__ void flush_sums(double* dst, int t, double d,
-                                           double na, double nb) {
-  if (t < 0) return;
-  atomicAdd(dst + 3 * t, d);
-  atomicAdd(dst + 3 * t + 1, na);
-  atomicAdd(dst + 3 * t + 2, nb);
+// Adds one CTA's partial sums for tensor t to the level's scratch record.
+__device__ __forceinline__ void block_flush_sums(double* dst, int t, double d, double na,
+                                                 double nb) {
+  __shared__ double part[THREADS / 32][3];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    d += __shfl_down_sync(0xffffffffu, d, o);
+    na += __shfl_down_sync(0xffffffffu, na, o);
+    nb += __shfl_down_sync(0xffffffffu, nb, o);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    part[warp][0] = d;
+    part[warp][1] = na;
+    part[warp][2] = nb;
+  }
+  __syncthreads();
+  if (threadIdx.x < 3) {
+    double sum = 0;
+#pragma unroll
+    for (int w = 0; w < THREADS / 32; ++w) sum += part[w][threadIdx.x];
+    if (sum != 0.0) atomicAdd(dst + 3 * t + threadIdx.x, sum);
+  }
+  __syncthreads();  // `part` is reused for the next tensor
 }
 
+__device__ __forceinline__ void accumulate(uint4 xa, uint4 xb, double& d, double& na,
+                                           double& nb) {
+  WireVec<float> x, y;
+  x.raw = xa;
+  y.raw = xb;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const double xd = x.e[i], yd = y.e[i];
+    d += xd * yd;
+    na += xd * xd;
+    nb += yd * yd;
+  }
+}
+
+// Per tensor: dot(a,b), |a|^2, |b|^2 over this CTA's slice of the kept half,
+// tensor by tensor (tight, four-way unrolled inner loop; the padding between
+// tensors holds zeros and adds nothing).
 __global__ void __launch_bounds__(THREADS)
 adasum_dots_kernel(TensorList tl, SymmCtx ctx, int level, uint32_t epoch,
                    double* scratch_level) {
@@ -86,46 +121,30 @@ adasum_dots_kernel(TensorList tl, SymmCtx ctx, int level, uint32_t epoch,
   const int64_t len = keep.hi - keep.lo;
   const int64_t per = (len + gridDim.x - 1) / gridDim.x;
   const int64_t lo = keep.lo + blockIdx.x * per, hi = min(lo + per, keep.hi);
-  int t = -1;
-  double d = 0, na = 0, nb = 0;
-  if (lo + threadIdx.x < hi) {
-    int cur = find_tensor(tl, (lo + threadIdx.x) * N);
-    for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS) {
-      const int64_t elem = v * N;
-      while (cur + 1 < tl.n && elem >= tl.offsets[cur + 1]) ++cur;
-      if (cur != t) {
-        flush_sums(scratch_level, t, d, na, nb);
-        t = cur;
-        d = na = nb = 0;
-      }
-      WireVec<float> x, y;
-      x.raw = ld16(a + v);
-      y.raw = ld16(bb + v);
+  if (lo >= hi) return;  // whole CTA
+  for (int t = find_tensor(tl, lo * N); t < tl.n; ++t) {
+    const int64_t toff = tl.offsets[t];
+    if (toff >= hi * N) break;
+    const int64_t v0 = max(lo, toff / N), v1 = min(hi, tl.offsets[t + 1] / N);
+    double d = 0, na = 0, nb = 0;
+    int64_t v = v0 + threadIdx.x;
+    for (; v + 3 * THREADS < v1; v += 4 * THREADS) {
+      uint4 xa[4], xb[4];
 #pragma unroll
-      for (int i = 0; i < N; ++i) {
-        const double xd = x.e[i], yd = y.e[i];
-        d += xd * yd;
-        na += xd * xd;
-        nb += yd * yd;
+      for (int u = 0; u < 4; ++u) {
+        xa[u] = ld16(a + v + u * THREADS);
+        xb[u] = ld16(bb + v + u * THREADS);
       }
-    }
-  }
-  // Warp-level pre-reduction when the whole warp ended on the same tensor.
-  __syncwarp();
-  const int t0 = __shfl_sync(0xffffffffu, t, 0);
-  if (__all_sync(0xffffffffu, t == t0)) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      d += __shfl_down_sync(0xffffffffu, d, o);
-      na += __shfl_down_sync(0xffffffffu, na, o);
-      nb += __shfl_down_sync(0xffffffffu, nb, o);
+      for (int u = 0; u < 4; ++u) accumulate(xa[u], xb[u], d, na, nb);
     }
-    if ((threadIdx.x & 31) == 0) flush_sums(scratch_level, t, d, na, nb);
-  } else {
-    flush_sums(scratch_level, t, d, na, nb);
+    for (; v < v1; v += THREADS) accumulate(ld16(a + v), ld16(bb + v), d, na, nb);
+    block_flush_sums(scratch_level, t, d, na, nb);
   }
 }
 
+// kept half <- ca * a + cb * b with the per-tensor coefficients computed from
+// the sums of all ranks that jointly hold a and b.
 __global__ void __launch_bounds__(THREADS)
 adasum_combine_kernel(TensorList tl, SymmCtx ctx, int level, uint32_t epoch,
                       int64_t scratch_level_off) {
@@ -139,19 +158,17 @@ adasum_combine_kernel(TensorList tl, SymmCtx ctx, int level, uint32_t epoch,
   const uint4* theirs = reinterpret_cast<const uint4*>(ctx.peers[partner]);
   const int group = 2 << level;
   const int first = ctx.rank / group * group;
+  __shared__ float coeff[2];
 
   const int64_t len = keep.hi - keep.lo;
   const int64_t per = (len + gridDim.x - 1) / gridDim.x;
   const int64_t lo = keep.lo + blockIdx.x * per, hi = min(lo + per, keep.hi);
-  if (lo + threadIdx.x >= hi) return;
-  int cur = find_tensor(tl, (lo + threadIdx.x) * N);
-  int t = -1;
-  float ca = 1.f, cb = 1.f;
-  for (int64_t v = lo + threadIdx.x; v < hi; v += THREADS) {
-    const int64_t elem = v * N;
-    while (cur + 1 < tl.n && elem >= tl.offsets[cur + 1]) ++cur;
-    if (cur != t) {
-      t = cur;
+  if (lo >= hi) return;  // whole CTA
+  for (int t = find_tensor(tl, lo * N); t < tl.n; ++t) {
+    const int64_t toff = tl.offsets[t];
+    if (toff >= hi * N) break;
+    const int64_t v0 = max(lo, toff / N), v1 = min(hi, tl.offsets[t + 1] / N);
+    if (threadIdx.x == 0) {
       double d = 0, na = 0, nb = 0;
       for (int q = 0; q < group; ++q) {
         const volatile double* s = reinterpret_cast<const volatile double*>(
@@ -162,16 +179,32 @@ adasum_combine_kernel(TensorList tl, SymmCtx ctx, int level, uint32_t epoch,
       }
       // sqrt(DBL_MIN): below this a squared norm counts as zero.
       const double tiny = 1.4916681462400413e-154;
-      ca = static_cast<float>(na >= tiny ? 1.0 - d / (2.0 * na) : 1.0);
-      cb = static_cast<float>(nb >= tiny ? 1.0 - d / (2.0 * nb) : 1.0);
+      coeff[0] = static_cast<float>(na >= tiny ? 1.0 - d / (2.0 * na) : 1.0);
+      coeff[1] = static_cast<float>(nb >= tiny ? 1.0 - d / (2.0 * nb) : 1.0);
     }
-    WireVec<float> x, y;
-    x.raw = ld16(mine + v);
-    y.raw = ld16(theirs + v);
-    const float cm = lower ? ca : cb, ct = lower ? cb : ca;
+    __syncthreads();
+    const float cm = lower ? coeff[0] : coeff[1], ct = lower ? coeff[1] : coeff[0];
+    auto mix = [&](uint4 xm, uint4 xt) {
+      WireVec<float> x, y;
+      x.raw = xm;
+      y.raw = xt;
 #pragma unroll
-    for (int i = 0; i < N; ++i) x.e[i] = cm * x.e[i] + ct * y.e[i];
-    st16(mine + v, x.raw);
+      for (int i = 0; i < N; ++i) x.e[i] = cm * x.e[i] + ct * y.e[i];
+      return x.raw;
+    };
+    int64_t v = v0 + threadIdx.x;
+    for (; v + 3 * THREADS < v1; v += 4 * THREADS) {
+      uint4 xm[4], xt[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        xm[u] = ld16(mine + v + u * THREADS);
+        xt[u] = ld16(theirs + v + u * THREADS);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) st16(mine + v + u * THREADS, mix(xm[u], xt[u]));
+    }
+    for (; v < v1; v += THREADS) st16(mine + v, mix(ld16(mine + v), ld16(theirs + v)));
+    __syncthreads();  // `coeff` is rewritten for the next tensor
   }
 }
 

@@ -152,10 +152,21 @@ Status NcclOps::Execute(std::vector<TensorTableEntry>& entries,
   case Response::ALLGATHER: return Allgather(entries, response, ps, comm);
   case Response::ALLTOALL: return Alltoall(entries, ps, comm);
   case Response::REDUCESCATTER: return Reducescatter(entries, ps, comm);
-  case Response::ADASUM:
-    return Status::PreconditionError(
-        "Adasum on CUDA tensors runs only on the symmetric-memory backend "
-        "(one node, at most 8 ranks, fp32/fp16/bf16).");
+  case Response::ADASUM: {
+    // What the reference's GPU Adasum computes when all ranks share a node
+    // (horovod/common/ops/adasum_gpu_operations.cc:64-320 with start_level =
+    // local_size; horovod/common/operations.cc:1404-1410 folds 1/local_size
+    // into the postscale): an NCCL sum divided by the number of ranks, no
+    // Adasum arithmetic. Kept as the baseline of the device Adasum kernels.
+    if (gpu_.state().config.local_size != gpu_.state().config.size)
+      return Status::PreconditionError(
+          "Adasum on CUDA tensors across nodes is not supported on the NCCL path.");
+    Response avg = response;
+    avg.type = Response::ALLREDUCE;
+    avg.reduce_op = ReduceOp::SUM;
+    avg.postscale = response.postscale / static_cast<double>(ps.ranks().size());
+    return Allreduce(entries, avg, comm);
+  }
   default:
     return Status::InvalidArgument("unsupported NCCL collective");
   }

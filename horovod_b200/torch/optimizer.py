@@ -388,13 +388,22 @@ def _find_duplicates(lst):
 
 class _DistributedAdasumOptimizer(torch.optim.Optimizer):
     """Adasum variant: each parameter's *update* (not its gradient) is
-    combined across ranks. When a gradient is ready the wrapped optimizer
-    steps that one parameter locally, the resulting delta is Adasum-reduced,
-    and step() applies the combined delta to the value the parameter had at
-    the start of the step.
+    combined across ranks, and step() applies the combined delta to the value
+    the parameter had at the start of the step.
+
+    Two schedules compute the same per-parameter deltas:
+      * fused (default): step() runs the wrapped optimizer once on all
+        parameters, forms all deltas with multi-tensor ops and reduces them
+        in one grouped Adasum allreduce (few large fused kernels);
+      * per parameter (HOROVOD_ADASUM_PER_PARAMETER=1, the reference's
+        schedule): when a gradient is ready the wrapped optimizer steps that
+        one parameter alone and its delta is reduced asynchronously, which
+        overlaps with backward but costs one optimizer step() call and one
+        negotiation per parameter.
 
     Parity: horovod/torch/optimizer.py:335-503.
     """
+    _instances = 0
 
     def __init__(self, params, named_parameters, compression, backward_passes_per_step=1,
                  process_set=global_process_set):
@@ -424,6 +433,11 @@ class _DistributedAdasumOptimizer(torch.optim.Optimizer):
             for _, p in named_parameters
         }
         self._hook_handles = []
+        import os
+        self._fused = os.environ.get("HOROVOD_ADASUM_PER_PARAMETER", "0") != "1"
+        cls = self.__class__
+        self._group_name = "DistributedAdasumOptimizer.%d" % cls._instances
+        cls._instances += 1
         if self.process_set.included() and size() > 1 or _force_hooks():
             for group in self.param_groups:
                 for p in group["params"]:
@@ -436,6 +450,40 @@ class _DistributedAdasumOptimizer(torch.optim.Optimizer):
         self.backward_passes_per_step = passes
         for p in self._allreduce_delay:
             self._allreduce_delay[p] = self.backward_passes_per_step
+
+    def _fused_step(self):
+        """One local optimizer step on everything, all deltas at once."""
+        params = [p for group in self.param_groups for p in group["params"]
+                  if p in self._requires_update]
+        for p in params:
+            if p.grad is None:
+                p.grad = p.data.new_zeros(p.size())
+        datas = [p.data for p in params]
+        starts = [self._starting_models[p].data for p in params]
+        torch._foreach_copy_(starts, datas)
+        super(self.__class__, self).step()
+        torch._foreach_sub_(datas, starts)  # every parameter now holds its local delta
+        by_kind = {}
+        for i, d in enumerate(datas):
+            by_kind.setdefault((d.dtype, d.device), []).append(i)
+        pending = []
+        for k, (kind, idx) in enumerate(sorted(by_kind.items(), key=lambda kv: str(kv[0]))):
+            comp = [self._compression.compress(datas[i]) for i in idx]
+            handle = grouped_allreduce_async_([c[0] for c in comp],
+                                              name="%s.%d" % (self._group_name, k), op=Adasum,
+                                              process_set=self.process_set)
+            pending.append((idx, comp, handle))
+        for idx, comp, handle in pending:
+            outs = synchronize(handle)
+            for i, (tensor_compressed, cctx), out in zip(idx, comp, outs):
+                delta = self._compression.decompress(out, cctx)
+                if delta.data_ptr() != datas[i].data_ptr():
+                    datas[i].copy_(delta)
+        torch._foreach_add_(starts, datas)
+        torch._foreach_copy_(datas, starts)
+        for p in params:
+            self._allreduce_delay[p] = self.backward_passes_per_step
+        self._handles.clear()
 
     def _allreduce_grad_async(self, p):
         # Run the wrapped optimizer on this parameter alone to get its delta.
@@ -466,7 +514,7 @@ class _DistributedAdasumOptimizer(torch.optim.Optimizer):
             assert not p.grad.requires_grad
             handle, ctx = None, None
             self._allreduce_delay[p] -= 1
-            if self._allreduce_delay[p] == 0:
+            if self._allreduce_delay[p] == 0 and not self._fused:
                 handle, ctx = self._allreduce_grad_async(p)
             self._handles[p] = (handle, ctx)
         return hook
@@ -486,6 +534,9 @@ class _DistributedAdasumOptimizer(torch.optim.Optimizer):
             loss = closure()
         if not self.process_set.included():
             return super(self.__class__, self).step()
+        if self._fused:
+            self._fused_step()
+            return loss
         missing = self._requires_update - set(self._handles.keys())
         for p in missing:
             if p.grad is None:

@@ -40,7 +40,8 @@ def main():
     p.add_argument("--iters", type=int, default=20)
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--ops", default="allreduce,allreduce_bf16,reducescatter,allgather,"
-                                    "broadcast,alltoall,grouped,allreduce_symm,grouped_symm")
+                                    "broadcast,alltoall,grouped,allreduce_symm,grouped_symm,"
+                                    "reducescatter_symm")
     p.add_argument("--algo", default=None, help="force oneshot|twoshot|nvls")
     p.add_argument("--ctas", type=int, default=0)
     p.add_argument("--phases", action="store_true",
@@ -126,7 +127,8 @@ def main():
         s <<= 1
 
     heap = None
-    if args.backend == "symm" and n > 1 and ("allreduce_symm" in ops or "grouped_symm" in ops):
+    if args.backend == "symm" and n > 1 and ("allreduce_symm" in ops or "grouped_symm" in ops
+                                             or "reducescatter_symm" in ops):
         os.environ.setdefault("HOROVOD_SYMM_HEAP_MB", "2048")
         heap = hvd.symmetric_empty(max(sizes[-1], 160 << 20) // 4)
         heap.normal_()
@@ -148,6 +150,11 @@ def main():
             x = torch.randn(nbytes // 2, device=dev).bfloat16()
             us = measure(lambda: hvd.allreduce_(x, op=hvd.Sum, name="sw.arb"), ALLREDUCE)
             emit("allreduce", "bf16", nbytes, us, 2 * (n - 1) / n, ar_wire(nbytes))
+        if "reducescatter_symm" in ops and heap is not None and nbytes >= 64 * n:
+            # input in the symmetric heap, shards on 16-byte boundaries: no staging
+            x = heap[:nbytes // 4 // (4 * n) * (4 * n)]
+            us = measure(lambda: hvd.reducescatter(x, op=hvd.Sum, name="sw.rss"), REDUCESCATTER)
+            emit("reducescatter_symm", "fp32", nbytes, us, (n - 1) / n, nbytes * (n - 1) / n)
         if "reducescatter" in ops and nbytes >= 4 * n:
             x = torch.randn(nbytes // 4 // n * n, device=dev)
             us = measure(lambda: hvd.reducescatter(x, op=hvd.Sum, name="sw.rs"), REDUCESCATTER)

@@ -207,6 +207,26 @@ cudaError_t LaunchScaleBuffer(const void* in, void* out, int64_t count,
 
 // Number of kernels of this library launched so far in this process (every
 // Launch* function counts the kernels it enqueues).
+// Training-mode batch normalisation on channels-last 16-bit activations
+// ([rows, channels] row-major), fused with the residual add and the ReLU.
+// `sums_zeroed` is a zero-filled scratch of 2 * channels doubles. Forward:
+// y = act(bn(x) [+ residual]); also writes the batch mean / inverse standard
+// deviation and updates the running statistics (when given). Backward: dx,
+// optionally dresidual (= gradient through the ReLU), dweight, dbias.
+bool BatchNormSupported(int64_t rows, int channels);
+cudaError_t LaunchBatchNormForward(const void* x, const void* residual, void* y, int64_t rows,
+                                   int channels, bool bf16, double* sums_zeroed,
+                                   const float* weight, const float* bias, float eps,
+                                   float momentum, float* save_mean, float* save_invstd,
+                                   float* running_mean, float* running_var, bool relu,
+                                   cudaStream_t stream);
+cudaError_t LaunchBatchNormBackward(const void* dy, const void* y, const void* x, void* dx,
+                                    void* dresidual, int64_t rows, int channels, bool bf16,
+                                    double* sums_zeroed, const float* weight,
+                                    const float* save_mean, const float* save_invstd,
+                                    float* dweight, float* dbias, bool relu,
+                                    cudaStream_t stream);
+
 uint64_t KernelLaunchCount();
 void CountKernelLaunches(int n);
 

@@ -32,6 +32,7 @@ namespace hvd {
 void BindGpuDiagnostics(py::module_& m);
 // Defined in binding_testing.cpp.
 void BindTesting(py::module_& m);
+void BindModelOps(py::module_& m);
 
 namespace {
 
@@ -545,4 +546,5 @@ PYBIND11_MODULE(_C, m) {
 
   BindGpuDiagnostics(m);
   BindTesting(m);
+  BindModelOps(m);
 }

@@ -7,29 +7,31 @@ resnet50, which is the same v1.5 network).
 import torch
 import torch.nn as nn
 
+from horovod_b200.ops.batch_norm import BatchNormAct2d
+
 
 class Bottleneck(nn.Module):
     expansion = 4
 
     def __init__(self, inplanes, planes, stride=1, downsample=None):
         super().__init__()
+        # Each batch norm carries its ReLU (and, for the last one, the residual
+        # add): one fused kernel pair on the GPU, plain PyTorch ops elsewhere.
         self.conv1 = nn.Conv2d(inplanes, planes, 1, bias=False)
-        self.bn1 = nn.BatchNorm2d(planes)
+        self.bn1 = BatchNormAct2d(planes, relu=True)
         self.conv2 = nn.Conv2d(planes, planes, 3, stride=stride, padding=1, bias=False)
-        self.bn2 = nn.BatchNorm2d(planes)
+        self.bn2 = BatchNormAct2d(planes, relu=True)
         self.conv3 = nn.Conv2d(planes, planes * 4, 1, bias=False)
-        self.bn3 = nn.BatchNorm2d(planes * 4)
-        self.relu = nn.ReLU(inplace=True)
+        self.bn3 = BatchNormAct2d(planes * 4, relu=True)
         self.downsample = downsample
 
     def forward(self, x):
         identity = x
-        out = self.relu(self.bn1(self.conv1(x)))
-        out = self.relu(self.bn2(self.conv2(out)))
-        out = self.bn3(self.conv3(out))
+        out = self.bn1(self.conv1(x))
+        out = self.bn2(self.conv2(out))
         if self.downsample is not None:
             identity = self.downsample(x)
-        return self.relu(out + identity)
+        return self.bn3(self.conv3(out), residual=identity)
 
 
 class ResNet(nn.Module):
@@ -37,8 +39,7 @@ class ResNet(nn.Module):
         super().__init__()
         self.inplanes = width
         self.conv1 = nn.Conv2d(3, width, 7, stride=2, padding=3, bias=False)
-        self.bn1 = nn.BatchNorm2d(width)
-        self.relu = nn.ReLU(inplace=True)
+        self.bn1 = BatchNormAct2d(width, relu=True)
         self.maxpool = nn.MaxPool2d(3, stride=2, padding=1)
         self.layer1 = self._make_layer(width, layers[0])
         self.layer2 = self._make_layer(width * 2, layers[1], stride=2)
@@ -62,7 +63,7 @@ class ResNet(nn.Module):
         if stride != 1 or self.inplanes != planes * 4:
             downsample = nn.Sequential(
                 nn.Conv2d(self.inplanes, planes * 4, 1, stride=stride, bias=False),
-                nn.BatchNorm2d(planes * 4))
+                BatchNormAct2d(planes * 4, relu=False))
         layers = [Bottleneck(self.inplanes, planes, stride, downsample)]
         self.inplanes = planes * 4
         for _ in range(1, blocks):
@@ -70,7 +71,7 @@ class ResNet(nn.Module):
         return nn.Sequential(*layers)
 
     def forward(self, x):
-        x = self.maxpool(self.relu(self.bn1(self.conv1(x))))
+        x = self.maxpool(self.bn1(self.conv1(x)))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         x = torch.flatten(self.avgpool(x), 1)
         return self.fc(x)

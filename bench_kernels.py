@@ -12,6 +12,13 @@ Cases
   reducescatter reduce-scatter kernel on one rank: stage -> reduce -> write
                 (read + write staging + read staging + write = 4x bytes).
   exchange      allgather of one rank through the exchange kernel (4x bytes).
+  batch_norm    fused batch norm + residual + ReLU on a channels-last bf16
+                activation of 256 x 256 x 56 x 56 (411 MB): forward (statistics
+                pass + apply pass: read x twice, read the residual, write y =
+                4x bytes) and backward (reduce pass reads dy, y, x; apply pass
+                reads them again and writes dx and dres = 8x bytes), timed with
+                CUDA events on the current stream, next to the PyTorch eager
+                composition batch_norm -> add -> relu on the same tensors.
 
 Timing is device time of the response on the communication stream (CUDA
 events around the launches). Inputs are larger than L2 (126 MB) unless --mb
@@ -86,7 +93,7 @@ def main():
                           "frac_of_%s_hbm_copy" % peak_src: round(gbs / hbm, 3),
                           "hbm_gbs_peak": hbm}), flush=True)
 
-    cases = ["fused_local", "fused_fp16", "reducescatter", "exchange"] \
+    cases = ["fused_local", "fused_fp16", "reducescatter", "exchange", "batch_norm"] \
         if args.case == "all" else [args.case]
     if "fused_local" in cases:
         xs = [torch.randn(n, device=dev) for n in resnet50_like_sizes(nbytes // 4)]
@@ -106,6 +113,57 @@ def main():
         n = min(nbytes, 192 << 20) // 4
         x = torch.randn(n, device=dev)
         run("exchange", lambda: hvd.allgather(x, name="k.ag"), 1, 4 * n * 4)
+    if "batch_norm" in cases:
+        import torch.nn.functional as F
+        from horovod_b200.ops.batch_norm import batch_norm_act
+        n = 256 if args.mb >= 512 else 64
+        shape = (n, 256, 56, 56)
+        x = torch.randn(shape, device=dev, dtype=torch.bfloat16) \
+            .contiguous(memory_format=torch.channels_last).requires_grad_(True)
+        res = torch.randn_like(x).requires_grad_(True)
+        go = torch.randn_like(x)
+        w = torch.ones(256, device=dev, requires_grad=True)
+        b = torch.zeros(256, device=dev, requires_grad=True)
+        rm, rv = torch.zeros(256, device=dev), torch.ones(256, device=dev)
+        nbytes_act = x.numel() * 2
+
+        def timed(fn, reps):
+            for _ in range(args.warmup):
+                fn()
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(reps):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1) * 1e3)
+            return statistics.median(ts)
+
+        def report(name, us, algorithmic):
+            gbs = algorithmic / (us * 1e-6) / 1e9
+            print(json.dumps({"case": name, "shape": list(shape), "device_us": round(us, 1),
+                              "algorithmic_gbs": round(gbs, 1),
+                              "frac_of_%s_hbm_copy" % peak_src: round(gbs / hbm, 3),
+                              "hbm_gbs_peak": hbm}), flush=True)
+
+        def eager_fwd():
+            return F.relu(F.batch_norm(x, rm, rv, w, b, True, 0.1, 1e-5) + res)
+
+        def fused_fwd():
+            return batch_norm_act(x, w, b, rm, rv, residual=res, training=True, relu=True)
+
+        for name, fwd in (("batch_norm_fused", fused_fwd), ("batch_norm_eager", eager_fwd)):
+            t_f = timed(lambda: fwd(), args.iters)
+            y = fwd()
+
+            def bwd():
+                torch.autograd.grad(y, (x, res, w, b), go, retain_graph=True)
+            t_b = timed(bwd, args.iters)
+            report(name + "_forward", t_f, 4 * nbytes_act)
+            report(name + "_backward", t_b, 8 * nbytes_act)
+            del y
     hvd.shutdown()
     return 0
 

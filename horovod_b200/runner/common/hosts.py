@@ -97,3 +97,15 @@ def get_host_assignments(hosts, min_np, max_np=None):
                                   cross_rank=at_local[host.hostname], size=world_size,
                                   local_size=local_size, cross_size=len(at_local)))
     return alloc
+
+
+def host_hash(salt=None):
+    """Identifies "the same machine" for slot grouping: two processes that
+    share a hostname (and salt) share a host. Parity:
+    horovod/runner/common/util/host_hash.py:21-48."""
+    import hashlib
+    import socket
+    name = socket.gethostname().split(".")[0]
+    if salt is not None:
+        name = "%s-%s" % (name, salt)
+    return "%s-%s" % (name, hashlib.md5(name.encode("ascii", "ignore")).hexdigest())

@@ -98,15 +98,30 @@ class BasicService:
         raise NotImplementedError(req)
 
     def _get_local_addresses(self):
-        result = {"lo": [("127.0.0.1", self._port)]}
+        """{interface name: [(ipv4, port)]} for every interface that is up,
+        filtered to ``nics`` when given (loopback is always kept last so a
+        single-host job still works)."""
+        result = {}
         try:
-            host_ip = socket.gethostbyname(socket.gethostname())
-            if host_ip != "127.0.0.1":
-                result["host"] = [(host_ip, self._port)]
-        except OSError:
-            pass
-        if self._nics:
-            result = {k: v for k, v in result.items() if k in self._nics} or result
+            import psutil
+            for intf, addrs in psutil.net_if_addrs().items():
+                if self._nics and intf not in self._nics:
+                    continue
+                for a in addrs:
+                    if a.family == socket.AF_INET:
+                        result.setdefault(intf, []).append((a.address, self._port))
+        except Exception:  # noqa: BLE001 - psutil missing or unreadable: fall back below
+            result = {}
+        if not result:
+            result = {"lo": [("127.0.0.1", self._port)]}
+            try:
+                host_ip = socket.gethostbyname(socket.gethostname())
+                if host_ip != "127.0.0.1":
+                    result["host"] = [(host_ip, self._port)]
+            except OSError:
+                pass
+            if self._nics:
+                result = {k: v for k, v in result.items() if k in self._nics} or result
         return result
 
     def addresses(self):
@@ -127,6 +142,7 @@ class BasicClient:
         self._service_name = service_name
         self._wire = Wire(key)
         self._verbose = verbose
+        self._match_intf = match_intf
         self._probe_timeout = probe_timeout
         self._attempts = attempts
         self._addresses = self._probe(addresses)

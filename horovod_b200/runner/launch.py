@@ -337,6 +337,30 @@ def _run(args):
     else:
         server_ip = "127.0.0.1"
     nics = set(args.nics.split(",")) if args.nics else None
+    if remote and nics is None:
+        # Find the interfaces that are routed between all hosts (each host's
+        # task service probes the next one's); cached per host list.
+        from horovod_b200.runner.driver import driver_service
+        local = [h for h in host_names if gloo.is_local_host(h)]
+
+        def discover():
+            return sorted(driver_service.get_common_interfaces(
+                host_names, local_host_names=local, ssh_port=args.ssh_port,
+                ssh_identity_file=args.ssh_identity_file,
+                start_timeout_s=max(1, int(settings.start_timeout.remaining()))
+                if settings.start_timeout is not None else 30))
+        try:
+            if fn_cache is not None:
+                found = fn_cache.get(("nics",) + tuple(host_names))
+                if found is None:
+                    found = discover()
+                    fn_cache.put(("nics",) + tuple(host_names), found)
+            else:
+                found = discover()
+            nics = set(found)
+        except Exception as e:  # noqa: BLE001 - discovery is best effort
+            if settings.verbose:
+                print("NIC discovery failed (%s); letting the ranks pick their interface." % e)
     return gloo.gloo_run(settings, nics, env, server_ip, args.command)
 
 

@@ -241,3 +241,52 @@ def test_programmatic_run_returns_results_by_rank():
     env["PYTHONPATH"] = os.path.dirname(os.path.abspath(__file__)) + os.pathsep + env["PYTHONPATH"]
     res = horovod_b200.run(_fn, args=(10,), np=2, env=env)
     assert res == [(0, [1.0, 1.0]), (10, [1.0, 1.0])]
+
+
+def test_nic_discovery_ring_on_loopback():
+    """Three task services on this machine register with the driver, probe the
+    next one in the ring and report; loopback must be among the common
+    interfaces (parity: test/single/test_run.py network/driver-service tests)."""
+    import threading
+    from horovod_b200.runner.common import secret
+    from horovod_b200.runner.driver import driver_service as ds
+    key = secret.make_secret_key()
+    n = 3
+    driver = ds.HorovodRunDriverService(n, key)
+    try:
+        threads = [threading.Thread(target=ds.task_fn, daemon=True,
+                                    args=(i, n, driver.addresses(), key, None, 20, "host%d" % i))
+                   for i in range(n)]
+        for t in threads:
+            t.start()
+        common = ds._run_probe(driver, key, n, start_timeout_s=20)
+        for t in threads:
+            t.join(timeout=10)
+        assert "lo" in common
+        assert all(not t.is_alive() for t in threads)
+        assert sorted(driver.task_host_hash_indices()) == ["host0", "host1", "host2"]
+    finally:
+        driver.shutdown()
+    # a single-host job needs no probing
+    assert ds.get_common_interfaces(["localhost"]) == {"lo"}
+
+
+def test_rpc_rejects_wrong_key():
+    from horovod_b200.runner.common import network, secret
+    service = network.BasicService("svc", secret.make_secret_key())
+    try:
+        with pytest.raises(network.NoValidAddressesFound):
+            network.BasicClient("svc", service.addresses(), secret.make_secret_key(),
+                                probe_timeout=2, attempts=1)
+    finally:
+        service.shutdown()
+
+
+def test_lsf_hosts(monkeypatch):
+    from horovod_b200.runner.util.lsf import LSFUtils
+    monkeypatch.setenv("LSB_JOBID", "1")
+    monkeypatch.setenv("LSB_MCPU_HOSTS", "batch1 1 node1 42 node2 42")
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "0,1,2,3")
+    assert LSFUtils.using_lsf()
+    assert LSFUtils.get_compute_hosts() == ["node1", "node2"]
+    assert LSFUtils.get_num_processes() == 8

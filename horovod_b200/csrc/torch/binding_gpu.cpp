@@ -3,6 +3,8 @@
 
 #include <pybind11/stl.h>
 
+#include <cstring>
+
 #include "../kernels/kernels.h"
 #include "../ops/gpu_internal.h"
 #include "../ops/gpu_ops.h"
@@ -69,6 +71,54 @@ void BindGpuDiagnostics(py::module_& m) {
       t = ops->DrainTimings();
     }
     for (auto& x : t) out.append(py::make_tuple(x.type, x.bytes, x.tensors, x.device_us));
+    return out;
+  });
+  m.def("bounded_wait_probe", [](int device, int timeout_ms) {
+    // Runs the cross-GPU barrier kernel as rank 0 of a group of two whose
+    // second member does not exist: nothing ever sets that member's flag, so
+    // the wait must give up after timeout_ms and describe what it waited for
+    // in the status record, leaving the context usable. This is how a dead
+    // peer looks to a kernel. Returns (code, peer, phase, block, elapsed_ms).
+    cudaSetDevice(device);
+    const size_t flag_words = static_cast<size_t>(SYMM_FLAG_BANKS) * SYMM_MAX_RANKS * SYMM_MAX_BLOCKS;
+    uint32_t* flags = nullptr;
+    kern::KernelStatus* status_host = nullptr;
+    int* status_dev = nullptr;
+    if (cudaMalloc(reinterpret_cast<void**>(&flags), flag_words * sizeof(uint32_t)) != cudaSuccess)
+      throw std::runtime_error("bounded_wait_probe: cudaMalloc failed");
+    cudaMemset(flags, 0, flag_words * sizeof(uint32_t));
+    cudaHostAlloc(reinterpret_cast<void**>(&status_host), sizeof(kern::KernelStatus),
+                  cudaHostAllocMapped);
+    std::memset(status_host, 0, sizeof(kern::KernelStatus));
+    cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev), status_host, 0);
+    kern::SymmCtx ctx;
+    std::memset(&ctx, 0, sizeof(ctx));
+    ctx.rank = 0;
+    ctx.world = 2;
+    ctx.flags_local = flags;
+    ctx.flags_peers[0] = flags;
+    // The absent member's flag array: a second region of the same buffer that
+    // nobody reads, so this rank's own signal does not satisfy its own wait.
+    ctx.flags_peers[1] = flags + 2 * SYMM_MAX_RANKS * SYMM_MAX_BLOCKS;
+    ctx.epoch = 0;
+    ctx.timeout_ns = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
+    ctx.status = status_dev;
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    cudaEventRecord(e0, 0);
+    cudaError_t err = kern::LaunchBarrierOnly(1, 0, ctx, 0);
+    cudaEventRecord(e1, 0);
+    cudaError_t sync = cudaEventSynchronize(e1);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    auto out = py::make_tuple(status_host->code, status_host->peer, status_host->phase,
+                              status_host->block, ms, static_cast<int>(err),
+                              static_cast<int>(sync));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaFreeHost(status_host);
+    cudaFree(flags);
     return out;
   });
   m.def("kernel_trace", []() {

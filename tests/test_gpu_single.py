@@ -100,3 +100,19 @@ def test_compression_and_optimizer_step(hvd, monkeypatch):
         torch.testing.assert_close(a, b, rtol=1e-6, atol=1e-6)
 
 
+
+
+def test_wait_for_a_peer_that_never_arrives_is_bounded():
+    """A barrier whose second member never signals gives up after its time
+    limit, reports whom it waited for, and leaves the GPU usable (this is what
+    a dead peer looks like to a kernel; the failure is made on the host: the
+    peer simply does not exist)."""
+    from horovod_b200 import _C
+    torch.cuda.set_device(0)
+    code, peer, phase, block, ms, launch_err, sync_err = _C.bounded_wait_probe(0, 200)
+    assert launch_err == 0 and sync_err == 0
+    assert (code, peer, block) == (1, 1, 0), (code, peer, phase, block)
+    assert 150.0 <= ms < 2000.0, ms
+    # the context is intact
+    x = torch.arange(1000, device="cuda:0", dtype=torch.float32)
+    assert float(x.sum()) == 499500.0

@@ -23,6 +23,10 @@ parser.add_argument("--num-warmup-batches", type=int, default=10)
 parser.add_argument("--num-batches-per-iter", type=int, default=10)
 parser.add_argument("--num-iters", type=int, default=10)
 parser.add_argument("--no-cuda", action="store_true")
+parser.add_argument("--symmetric-gradients", action="store_true",
+                    help="keep the gradients in symmetric memory and reduce them in place")
+parser.add_argument("--bf16", action="store_true",
+                    help="channels-last bf16 autocast (the fused batch-norm kernels need it)")
 args = parser.parse_args()
 
 hvd.init()
@@ -33,22 +37,28 @@ device = torch.device("cuda", hvd.local_rank()) if cuda else torch.device("cpu")
 torch.backends.cudnn.benchmark = True
 
 model = models.resnet50().to(device)
+if args.bf16 and cuda:
+    model = model.to(memory_format=torch.channels_last)
 lr_scaler = hvd.size() if not args.use_adasum else 1
 optimizer = torch.optim.SGD(model.parameters(), lr=0.01 * lr_scaler)
 compression = hvd.Compression.fp16 if args.fp16_allreduce else hvd.Compression.none
 optimizer = hvd.DistributedOptimizer(optimizer, named_parameters=model.named_parameters(),
                                      compression=compression,
-                                     op=hvd.Adasum if args.use_adasum else hvd.Average)
+                                     op=hvd.Adasum if args.use_adasum else hvd.Average,
+                                     symmetric_gradients=args.symmetric_gradients)
 hvd.broadcast_parameters(model.state_dict(), root_rank=0)
 hvd.broadcast_optimizer_state(optimizer, root_rank=0)
 
 data = torch.randn(args.batch_size, 3, 224, 224, device=device)
+if args.bf16 and cuda:
+    data = data.contiguous(memory_format=torch.channels_last)
 target = torch.randint(0, 1000, (args.batch_size,), device=device)
 
 
 def benchmark_step():
     optimizer.zero_grad()
-    loss = F.cross_entropy(model(data), target)
+    with torch.autocast("cuda", dtype=torch.bfloat16, enabled=bool(args.bf16 and cuda)):
+        loss = F.cross_entropy(model(data), target)
     loss.backward()
     optimizer.step()
     if cuda:

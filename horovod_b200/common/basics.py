@@ -245,7 +245,9 @@ class HorovodBasics:
         return _native().is_initialized()
 
     def _check(self):
-        if not _native().is_initialized():
+        # rank()/size() stay answerable after a peer has shut the job down
+        # (collectives then fail with HorovodInternalError instead).
+        if not _native().has_topology():
             raise ValueError("Horovod has not been initialized; use hvd.init().")
 
     def size(self):

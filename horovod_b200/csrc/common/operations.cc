@@ -350,6 +350,12 @@ bool hvd_is_initialized() {
   return g_state.initialization_done.load() && !g_state.loop_exited.load();
 }
 
+// True from init() until shutdown(), also after the background loop has ended
+// because a peer shut the job down: rank()/size() stay answerable then, as in
+// the reference (horovod_rank() only checks initialization_done,
+// horovod/common/operations.cc:1043-1049).
+bool hvd_has_topology() { return g_state.initialization_done.load(); }
+
 namespace {
 void RequireInit() {
   if (!g_state.initialization_done.load())

@@ -26,6 +26,7 @@ std::string hvd_listen(const std::string& advertise_host);
 void hvd_init(const InitConfig& cfg);
 void hvd_shutdown();
 bool hvd_is_initialized();
+bool hvd_has_topology();
 
 int hvd_rank();
 int hvd_size();

@@ -507,6 +507,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("init", &Init);
   m.def("shutdown", &Shutdown);
   m.def("is_initialized", &hvd_is_initialized);
+  m.def("has_topology", &hvd_has_topology);
   m.def("rank", &hvd_rank);
   m.def("size", &hvd_size);
   m.def("local_rank", &hvd_local_rank);

@@ -69,6 +69,18 @@ handle_average_backwards_compatibility = get_average_backwards_compatibility_fun
 _handle_map = {}
 
 
+def _enqueue(native_op, *args):
+    """Hands an op to the background thread. A runtime failure at this point
+    (the job has been shut down, a peer died, a tensor name is already in
+    flight) is the same kind of event as one reported at synchronize():
+    HorovodInternalError, which elastic jobs catch and recover from
+    (horovod/torch/mpi_ops.py:137-138)."""
+    try:
+        return native_op(*args)
+    except RuntimeError as e:
+        raise HorovodInternalError(e)
+
+
 def _is_dense(tensor):
     """Contiguous in some memory format (e.g. channels_last): element-wise
     collectives only need the same dense layout on every rank."""
@@ -120,12 +132,12 @@ def _allreduce_async(tensor, output, name, op, prescale_factor, postscale_factor
     if op == Average and not (tensor.is_floating_point() or tensor.is_complex()):
         # Integer averaging: sum on the wire, floor-divide afterwards, as the
         # framework's integer division would.
-        handle = _C.allreduce_async(tensor, output, name or "", Sum, float(prescale_factor),
+        handle = _enqueue(_C.allreduce_async, tensor, output, name or "", Sum, float(prescale_factor),
                                     float(postscale_factor), _resolve(process_set))
         divisor = process_set.size() if process_set is not None else size()
         _handle_map[handle] = ("allreduce_intavg", divisor)
         return handle
-    handle = _C.allreduce_async(tensor, output, name or "", *_scaled_op(
+    handle = _enqueue(_C.allreduce_async, tensor, output, name or "", *_scaled_op(
         op, prescale_factor, postscale_factor), _resolve(process_set),
         _wire_id(tensor, wire_dtype) if op in (Average, Sum) else -1)
     _handle_map[handle] = ("allreduce", None)
@@ -202,7 +214,7 @@ def _grouped_allreduce_async(tensors, outputs, name, op, prescale_factor, postsc
     _check_adasum(op, process_set)
     int_avg = op == Average and any(not t.is_floating_point() for t in tensors)
     wire_op = Sum if int_avg else op
-    handle = _C.grouped_allreduce_async(list(tensors), list(outputs), name or "",
+    handle = _enqueue(_C.grouped_allreduce_async, list(tensors), list(outputs), name or "",
                                         int(wire_op), float(prescale_factor),
                                         float(postscale_factor), _resolve(process_set),
                                         _wire_id(tensors[0], wire_dtype)
@@ -299,7 +311,7 @@ def allgather_async(tensor, name=None, process_set=global_process_set):
     """Starts concatenating ``tensor`` from all ranks along dimension 0
     (dimension 0 may differ between ranks)."""
     _check_tensor(tensor)
-    handle = _C.allgather_async(tensor, name or "", _resolve(process_set))
+    handle = _enqueue(_C.allgather_async, tensor, name or "", _resolve(process_set))
     _handle_map[handle] = ("allgather", None)
     return handle
 
@@ -330,7 +342,7 @@ def allgather(tensor, name=None, process_set=global_process_set):
 
 def _broadcast_async(tensor, output, root_rank, name, process_set):
     _check_tensor(tensor, dense_ok=True)
-    handle = _C.broadcast_async(tensor, output, int(root_rank), name or "",
+    handle = _enqueue(_C.broadcast_async, tensor, output, int(root_rank), name or "",
                                 _resolve(process_set))
     _handle_map[handle] = ("broadcast", None)
     return handle
@@ -387,7 +399,7 @@ def alltoall_async(tensor, splits=None, name=None, process_set=global_process_se
     """Starts an all-to-all: rows ``splits[i]`` of dimension 0 go to rank i
     (an even split when ``splits`` is None)."""
     _check_tensor(tensor)
-    handle = _C.alltoall_async(tensor, _splits_list(splits), name or "",
+    handle = _enqueue(_C.alltoall_async, tensor, _splits_list(splits), name or "",
                                _resolve(process_set))
     _handle_map[handle] = ("alltoall", splits is not None)
     return handle
@@ -430,7 +442,7 @@ def reducescatter_async(tensor, name=None, op=Average, prescale_factor=1.0,
     _check_tensor(tensor)
     if op == Adasum:
         raise ValueError("reducescatter does not support Adasum")
-    handle = _C.reducescatter_async(tensor, name or "", int(op), float(prescale_factor),
+    handle = _enqueue(_C.reducescatter_async, tensor, name or "", int(op), float(prescale_factor),
                                     float(postscale_factor), _resolve(process_set))
     _handle_map[handle] = ("reducescatter", None)
     return handle
@@ -528,7 +540,7 @@ def join(device=-1, process_set=global_process_set):
     """Tells the other ranks this rank has no more data. Blocks until every
     rank has joined; meanwhile this rank contributes zeros to their
     allreduces. Returns the rank that joined last."""
-    handle = _C.join_async(_resolve(process_set))
+    handle = _enqueue(_C.join_async, _resolve(process_set))
     try:
         _, _, last = _C.wait_and_clear(handle)
     except RuntimeError as e:

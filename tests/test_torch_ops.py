@@ -311,3 +311,27 @@ def _dynamic_process_sets(rank, size):
 
 def test_dynamic_process_sets():
     assert all(run_parallel(_dynamic_process_sets, np=3))
+
+
+def _peer_leaves_early(rank, size):
+    import time
+    import horovod_b200.torch as hvd
+    from horovod_b200.common.exceptions import HorovodInternalError
+    hvd.init()
+    hvd.allreduce(torch.ones(2), name="first")
+    if rank == 0:
+        hvd.shutdown()
+        return True
+    time.sleep(0.5)  # rank 0 is gone by now and has told the job to stop
+    ok = hvd.rank() == 1 and hvd.size() == size and hvd.local_rank() == 1
+    try:
+        hvd.allreduce(torch.ones(2), name="second")
+        ok = False
+    except HorovodInternalError:
+        pass
+    hvd.shutdown()
+    return ok
+
+
+def test_rank_and_size_survive_a_peers_shutdown():
+    assert all(run_parallel(_peer_leaves_early, np=2))

@@ -60,7 +60,10 @@ void TensorQueue::GetTensorEntriesFromResponse(
       table_.erase(it);
       continue;
     }
-    if (!joined || response.type == Response::ERROR)
+    // A joined rank sees the others' error responses too (for example an
+    // allgather refused because of the join); it has nothing to fail.
+    if (joined && response.type == Response::ERROR) continue;
+    if (!joined)
       throw std::logic_error("hvd: response names tensor '" + name +
                              "' that this rank never enqueued");
     // Joined rank: stand-in that contributes zeros and discards the result.

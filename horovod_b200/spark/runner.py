@@ -1,0 +1,81 @@
+"""``horovod_b200.spark.run(fn, ...)``: runs ``fn`` on ``num_proc`` Spark tasks
+of one barrier stage as the ranks of one job and returns the results by
+rank. The tasks learn each other's hosts through the barrier context, derive
+their local/cross coordinates from them and meet at a rendezvous server on
+the driver. ``pyspark`` (3.0 or newer, for BarrierTaskContext.allGather) is
+imported at call time. Not exercised in this repository's tests: pyspark is
+not installed here.
+Parity: horovod/spark/runner.py:197-305 (run); the elastic variant and the
+Estimator API (:308-429, horovod/spark/{keras,torch,lightning}) are not built.
+"""
+import os
+import socket
+
+
+def _require_pyspark():
+    try:
+        import pyspark
+        return pyspark
+    except ImportError as e:  # pragma: no cover - depends on the environment
+        raise ImportError("horovod_b200.spark needs the `pyspark` package, which is not "
+                          "installed in this environment.") from e
+
+
+def _coordinates(hostnames, rank):
+    """(local_rank, local_size, cross_rank, cross_size) of ``rank`` given the
+    host of every rank: ranks on one host are numbered in rank order; the
+    cross rank counts the hosts (in order of first appearance) that have that
+    local rank."""
+    by_host = {}
+    for r, h in enumerate(hostnames):
+        by_host.setdefault(h, []).append(r)
+    mine = by_host[hostnames[rank]]
+    local_rank = mine.index(rank)
+    hosts_with = [h for h, ranks in by_host.items() if len(ranks) > local_rank]
+    return local_rank, len(mine), hosts_with.index(hostnames[rank]), len(hosts_with)
+
+
+def run(fn, args=(), kwargs=None, num_proc=None, extra_env=None, verbose=1):
+    """Runs ``fn(*args, **kwargs)`` on ``num_proc`` ranks inside Spark tasks;
+    returns the list of results ordered by rank."""
+    pyspark = _require_pyspark()
+    from pyspark import BarrierTaskContext
+    from horovod_b200.runner.http.http_server import RendezvousServer, local_ip_for
+    kwargs = kwargs or {}
+    spark_context = pyspark.SparkContext._active_spark_context
+    if spark_context is None:
+        raise Exception("Could not find an active SparkContext, are you running in a "
+                        "PySpark session?")
+    if num_proc is None:
+        num_proc = spark_context.defaultParallelism
+        if verbose >= 1:
+            print("Running %d processes (inferred from spark.default.parallelism)..." % num_proc)
+    server = RendezvousServer(verbose)
+    port = server.start()
+    server.init([None] * num_proc)
+    driver_ip = local_ip_for()
+    extra = dict(extra_env or {})
+
+    def task(index, _iterator):
+        ctx = BarrierTaskContext.get()
+        hostnames = ctx.allGather(socket.gethostname())
+        rank = ctx.partitionId()
+        local_rank, local_size, cross_rank, cross_size = _coordinates(hostnames, rank)
+        os.environ.update({k: str(v) for k, v in extra.items()})
+        os.environ.update({
+            "HOROVOD_RANK": str(rank), "HOROVOD_SIZE": str(len(hostnames)),
+            "HOROVOD_LOCAL_RANK": str(local_rank), "HOROVOD_LOCAL_SIZE": str(local_size),
+            "HOROVOD_CROSS_RANK": str(cross_rank), "HOROVOD_CROSS_SIZE": str(cross_size),
+            "HOROVOD_HOSTNAME": hostnames[rank],
+            "HOROVOD_GLOO_RENDEZVOUS_ADDR": driver_ip,
+            "HOROVOD_GLOO_RENDEZVOUS_PORT": str(port),
+            "HOROVOD_CONTROLLER": "gloo", "HOROVOD_CPU_OPERATIONS": "gloo",
+        })
+        yield rank, fn(*args, **kwargs)
+
+    try:
+        pairs = spark_context.range(0, numSlices=num_proc).barrier() \
+            .mapPartitionsWithIndex(task).collect()
+    finally:
+        server.stop()
+    return [result for _rank, result in sorted(pairs, key=lambda p: p[0])]

@@ -27,9 +27,11 @@ namespace hvd {
 constexpr int SYMM_MAX_RANKS = 8;
 // Flag slots per source rank in the signal pad (one per CTA of a kernel).
 constexpr int SYMM_MAX_BLOCKS = 512;
-// Independent flag banks so that kernels of different shapes never share
-// slots (bank 0: fused allreduce family, 1: gather/broadcast/alltoall,
-// 2: adasum, 3: tests).
+// Flag banks of MAX_RANKS x MAX_BLOCKS words each. Bank 0 holds the barrier
+// flags of every kernel (kernels of one process set run one after the other
+// on one stream and share an epoch counter); bank 1 is the token mailbox of
+// the kernels that address symmetric-heap tensors by offset; banks 2 and 3
+// are spare.
 constexpr int SYMM_FLAG_BANKS = 4;
 // Each process set gets its own copy of the banks (slot = set id modulo
 // this), so epochs of different sets never meet in one flag word.

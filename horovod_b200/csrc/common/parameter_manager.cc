@@ -136,6 +136,10 @@ bool ParameterManager::Update(const std::vector<std::string>& tensor_names,
   double median = scores_[scores_.size() / 2];
   scores_.clear();
   ++total_samples_;
+  // The next setting gets its own warm-up. Every rank resets it here (not in
+  // Tune(), which only the root runs) so that the sample boundaries, and with
+  // them the parameter broadcasts, stay aligned across ranks.
+  warmup_left_ = warmups_;
   if (rank_ == root_rank_) Tune(median);
   return true;
 }
@@ -156,7 +160,6 @@ void ParameterManager::LogSample(double score) {
 
 bool ParameterManager::Tune(double score) {
   LogSample(score);
-  warmup_left_ = warmups_;
   if (categorical_index_ < categorical_order_.size())
     return NextCategorical(score);
   if (!numeric_done_) return NextNumeric(score);

@@ -4,6 +4,7 @@ results (tensor * size etc.), every dtype and several ranks of tensor,
 in-place/async forms, fusion, error paths that must raise on every rank
 instead of hanging, join, autograd."""
 import itertools
+import os
 
 import pytest
 import torch
@@ -335,3 +336,36 @@ def _peer_leaves_early(rank, size):
 
 def test_rank_and_size_survive_a_peers_shutdown():
     assert all(run_parallel(_peer_leaves_early, np=2))
+
+
+def _autotune_job(rank, size, log_path):
+    os.environ["HOROVOD_AUTOTUNE"] = "1"
+    os.environ["HOROVOD_AUTOTUNE_LOG"] = log_path
+    os.environ["HOROVOD_AUTOTUNE_WARMUP_SAMPLES"] = "1"
+    os.environ["HOROVOD_AUTOTUNE_STEPS_PER_SAMPLE"] = "2"
+    os.environ["HOROVOD_AUTOTUNE_BAYES_OPT_MAX_SAMPLES"] = "3"
+    os.environ["HOROVOD_CYCLE_TIME"] = "0.5"
+    import horovod_b200.torch as hvd
+    hvd.init()
+    ok = True
+    # Many steps of a few tensors each: every step feeds the tuner's byte
+    # counter; results must stay correct while fusion threshold and cycle
+    # time change underneath, and both ranks must keep agreeing.
+    for step in range(150):
+        hs = [hvd.allreduce_async(torch.full((257,), float(rank + i)), op=hvd.Sum,
+                                  name="tune.%d" % i) for i in range(4)]
+        for i, h in enumerate(hs):
+            out = hvd.synchronize(h)
+            ok = ok and bool((out == sum(r + i for r in range(size))).all())
+    hvd.shutdown()
+    return ok
+
+
+def test_autotune_runs_end_to_end_and_logs(tmp_path):
+    import os as _os
+    log = str(tmp_path / "autotune.csv")
+    assert all(run_parallel(_autotune_job, np=2, args=(log,), timeout=300))
+    assert _os.path.exists(log), "rank 0 writes the autotune log"
+    lines = open(log).read().strip().splitlines()
+    assert len(lines) >= 2, lines  # header + at least one sample
+    assert "fusion" in lines[0].lower() and "cycle" in lines[0].lower()

@@ -1,0 +1,128 @@
+"""Four CPU ranks: what two ranks cannot show. Ring allreduce with ragged
+chunks, two-level Adasum against the pairwise oracle applied level by level,
+uneven allgather / alltoall / reducescatter, overlapping process sets used
+concurrently, join with three survivors, fusion of mixed dtypes."""
+import torch
+
+from parallel_utils import run_parallel
+
+
+def _vec(seed, n, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(n, generator=g, dtype=torch.float64).to(dtype)
+
+
+def _adasum_pair(a, b):
+    dot, na, nb = float(a @ b), float(a @ a), float(b @ b)
+    ca = 1.0 - dot / (2 * na) if na >= 1e-300 else 1.0
+    cb = 1.0 - dot / (2 * nb) if nb >= 1e-300 else 1.0
+    return ca * a + cb * b
+
+
+def _four(rank, size):
+    import horovod_b200.torch as hvd
+    hvd.init()
+    res = {}
+    # allreduce: sizes around the ring's chunk boundaries, several dtypes
+    ok = True
+    for dtype, tol in ((torch.float32, 1e-5), (torch.float64, 1e-12), (torch.int64, 0),
+                       (torch.bfloat16, 0.1), (torch.float16, 2e-2)):
+        for n in (1, 3, 4, 5, 1023, 4099):
+            x = _vec(100 * rank + n, n, torch.float64)
+            if not dtype.is_floating_point:
+                x = (x * 10).round()
+            out = hvd.allreduce(x.to(dtype), op=hvd.Sum, name="ar.%s.%d" % (dtype, n))
+            ref = sum((_vec(100 * r + n, n, torch.float64) * (1 if dtype.is_floating_point else 10))
+                      .round().to(dtype).double() if not dtype.is_floating_point
+                      else _vec(100 * r + n, n, torch.float64).to(dtype).double()
+                      for r in range(size))
+            err = (out.double() - ref).abs().max().item()
+            ok = ok and err <= tol * max(1.0, ref.abs().max().item()) * size
+    res["allreduce"] = ok
+
+    # Adasum over 4 ranks = pairs (0,1), (2,3), then the pair of results
+    n = 777
+    mine = _vec(7 + rank, n, torch.float64)
+    out = hvd.allreduce(mine.float(), op=hvd.Adasum, name="adasum4")
+    v = [_vec(7 + r, n, torch.float64).float().double() for r in range(size)]
+    ref = _adasum_pair(_adasum_pair(v[0], v[1]), _adasum_pair(v[2], v[3]))
+    res["adasum"] = (out.double() - ref).abs().max().item() < 1e-4 * max(1.0, ref.abs().max().item())
+
+    # uneven allgather / alltoall / reducescatter
+    g = hvd.allgather(torch.full((rank + 1, 2), float(rank)), name="ag4")
+    res["allgather"] = torch.equal(g, torch.cat([torch.full((r + 1, 2), float(r))
+                                                 for r in range(size)]))
+    splits = torch.tensor([(rank + p) % 3 for p in range(size)], dtype=torch.int32)
+    send = torch.arange(int(splits.sum()), dtype=torch.float32) + 100 * rank
+    recv, rsplits = hvd.alltoall(send, splits=splits, name="a2a4")
+    exp, exp_splits = [], []
+    for r in range(size):
+        s = [(r + p) % 3 for p in range(size)]
+        off = sum(s[:rank])
+        exp.append(torch.arange(sum(s), dtype=torch.float32)[off:off + s[rank]] + 100 * r)
+        exp_splits.append(s[rank])
+    res["alltoall"] = torch.equal(recv, torch.cat(exp)) and rsplits.tolist() == exp_splits
+    rows = 10  # 10 rows over 4 ranks: 3, 3, 2, 2
+    full = sum(_vec(50 + r, rows * 3, torch.float64).view(rows, 3) for r in range(size))
+    part = hvd.reducescatter(_vec(50 + rank, rows * 3, torch.float64).view(rows, 3),
+                             op=hvd.Sum, name="rs4")
+    lo = [0, 3, 6, 8, 10]
+    res["reducescatter"] = torch.allclose(part, full[lo[rank]:lo[rank + 1]], atol=1e-12)
+
+    hvd.shutdown()
+    return res
+
+
+def test_four_rank_collectives():
+    for rep in run_parallel(_four, np=4, timeout=300):
+        bad = [k for k, v in rep.items() if not v]
+        assert not bad, bad
+
+
+def _sets_and_join(rank, size):
+    import os
+    os.environ["HOROVOD_DYNAMIC_PROCESS_SETS"] = "1"
+    import horovod_b200.torch as hvd
+    hvd.init()
+    res = {}
+    front = hvd.add_process_set([0, 1, 2])
+    back = hvd.add_process_set([1, 2, 3])
+    handles = []
+    if front.included():
+        handles.append(("front", hvd.allreduce_async(torch.full((5,), float(rank)), op=hvd.Sum,
+                                                     name="ps.front", process_set=front)))
+    if back.included():
+        handles.append(("back", hvd.allreduce_async(torch.full((5,), float(rank)), op=hvd.Sum,
+                                                    name="ps.back", process_set=back)))
+    handles.append(("all", hvd.allreduce_async(torch.full((5,), float(rank)), op=hvd.Sum,
+                                               name="ps.all")))
+    expect = {"front": 3.0, "back": 6.0, "all": 6.0}
+    res["sets"] = all(float(hvd.synchronize(h)[0]) == expect[k] for k, h in handles)
+    if back.included():
+        b = hvd.broadcast(torch.full((2,), float(rank)), root_rank=3, name="ps.bc",
+                          process_set=back)
+        res["set_broadcast"] = float(b[0]) == 3.0
+    hvd.remove_process_set(front)
+    hvd.remove_process_set(back)
+
+    # join: rank r runs r+1 steps; the others' averages count the joined ranks as zeros
+    outs = []
+    for step in range(rank + 1):
+        outs.append(float(hvd.allreduce(torch.ones(3), op=hvd.Average, name="uneven")[0]))
+    last = hvd.join()
+    res["join_values"] = outs == [1.0, 0.75, 0.5, 0.25][:rank + 1]
+    res["last_joined"] = last == 3
+    # mixed dtypes submitted together still fuse per dtype and come back right
+    hs = [hvd.allreduce_async(torch.full((9,), float(rank), dtype=dt), op=hvd.Sum,
+                              name="mix.%d" % i)
+          for i, dt in enumerate([torch.float32, torch.float64, torch.float32, torch.int32,
+                                  torch.float64, torch.float32])]
+    res["mixed"] = all(float(hvd.synchronize(h)[0]) == 6.0 for h in hs)
+    hvd.shutdown()
+    return res
+
+
+def test_process_sets_join_and_mixed_dtypes_on_four_ranks():
+    for rep in run_parallel(_sets_and_join, np=4, timeout=300):
+        bad = [k for k, v in rep.items() if not v]
+        assert not bad, bad

@@ -126,3 +126,31 @@ def test_process_sets_join_and_mixed_dtypes_on_four_ranks():
     for rep in run_parallel(_sets_and_join, np=4, timeout=300):
         bad = [k for k, v in rep.items() if not v]
         assert not bad, bad
+
+
+def _threads(rank, size):
+    import threading
+    import horovod_b200.torch as hvd
+    hvd.init()
+    results = {}
+
+    def worker(tid):
+        ok = True
+        for step in range(30):
+            out = hvd.allreduce(torch.full((64,), float(rank + tid)), op=hvd.Sum,
+                                name="thr.%d" % tid)
+            ok = ok and float(out[0]) == sum(r + tid for r in range(size))
+        results[tid] = ok
+
+    threads = [threading.Thread(target=worker, args=(t,)) for t in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=120)
+    alive = any(t.is_alive() for t in threads)
+    hvd.shutdown()
+    return (not alive) and all(results.get(t) for t in range(4))
+
+
+def test_collectives_from_several_python_threads():
+    assert all(run_parallel(_threads, np=2, timeout=300))

@@ -59,6 +59,10 @@ def _nccl_include():
     return "/usr/include"
 
 
+def rule_for(src):
+    return "nvcc" if src.endswith(".cu") else "cxx"
+
+
 def write_ninja():
     import pybind11
     os.makedirs(BUILD, exist_ok=True)
@@ -75,6 +79,17 @@ def write_ninja():
                   "--expt-relaxed-constexpr -Xcompiler -fPIC "
                   "-Xcompiler -fvisibility=hidden "
                   "-D_GLIBCXX_USE_CXX11_ABI=%d" % abi)
+    # HOROVOD_B200_SANITIZE=address|undefined|thread instruments the host code
+    # (objects go to their own directory; the module is linked in place, so
+    # rebuild without the variable afterwards). Run the CPU tests with the
+    # matching runtime preloaded, e.g.
+    #   LD_PRELOAD=$(g++ -print-file-name=libasan.so) ASAN_OPTIONS=detect_leaks=0 pytest ...
+    sanitize = os.environ.get("HOROVOD_B200_SANITIZE", "")
+    link_extra = ""
+    if sanitize:
+        common = common.replace("-O2", "-O1 -g -fno-omit-frame-pointer") + \
+            " -fsanitize=%s" % sanitize
+        link_extra = " -fsanitize=%s" % sanitize
     if os.environ.get("HVD_PTXAS_VERBOSE"):
         nvcc_flags += " -Xptxas -v"
     out = os.path.join(PKG, "_C.so")
@@ -94,13 +109,14 @@ def write_ninja():
         "rule link",
         "  command = $cxx -shared $in -o $out -L%s -ltorch -ltorch_cpu "
         "-ltorch_python -lc10 -ltorch_cuda -lc10_cuda -L%s -lcudart -lpthread -ldl "
-        "-Wl,-rpath,%s -Wl,--no-undefined-version"
-        % (torch_lib, os.path.join(CUDA_HOME, "lib64"), torch_lib),
+        "-Wl,-rpath,%s -Wl,--no-undefined-version%s"
+        % (torch_lib, os.path.join(CUDA_HOME, "lib64"), torch_lib, link_extra),
     ]
     objs = []
     for src in cxx_srcs + cu_srcs:
         rel = os.path.relpath(src, CSRC).replace(os.sep, "_")
-        obj = os.path.join(BUILD, rel + ".o")
+        obj = os.path.join(BUILD, ("san_" + sanitize + "_" if sanitize and rule_for(src) == "cxx"
+                                   else "") + rel + ".o")
         objs.append(obj)
         rule = "nvcc" if src.endswith(".cu") else "cxx"
         lines.append("build %s: %s %s" % (obj, rule, src))

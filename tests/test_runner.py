@@ -290,3 +290,89 @@ def test_lsf_hosts(monkeypatch):
     assert LSFUtils.using_lsf()
     assert LSFUtils.get_compute_hosts() == ["node1", "node2"]
     assert LSFUtils.get_num_processes() == 8
+
+
+def test_rpc_service_handles_requests_concurrently_and_shuts_down_mid_request():
+    """Parity: test/single/test_service.py (concurrent requests, shutdown
+    while a request is being served)."""
+    from horovod_b200.runner.common import network, secret
+
+    class Sleep:
+        def __init__(self, seconds):
+            self.seconds = seconds
+
+    class SleepService(network.BasicService):
+        def __init__(self, key):
+            super().__init__("sleeper", key)
+            self.active = 0
+            self.max_active = 0
+            self._lock = threading.Lock()
+
+        def _handle(self, req, client_address):
+            if isinstance(req, Sleep):
+                with self._lock:
+                    self.active += 1
+                    self.max_active = max(self.max_active, self.active)
+                time.sleep(req.seconds)
+                with self._lock:
+                    self.active -= 1
+                return network.AckResponse()
+            return super()._handle(req, client_address)
+
+    key = secret.make_secret_key()
+    service = SleepService(key)
+    try:
+        client = network.BasicClient("sleeper", {"lo": [("127.0.0.1", service.get_port())]}, key)
+        t0 = time.time()
+        threads = [threading.Thread(target=client._send, args=(Sleep(0.5),)) for _ in range(4)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(timeout=10)
+        elapsed = time.time() - t0
+        assert service.max_active >= 2, "requests were serialised"
+        assert elapsed < 1.6, elapsed
+        # shutdown while a request is in flight: shutdown() returns, the client
+        # gets its answer or a connection error, nothing hangs
+        result = {}
+
+        def slow():
+            try:
+                client._send(Sleep(1.0))
+                result["outcome"] = "answered"
+            except Exception as e:  # noqa: BLE001
+                result["outcome"] = type(e).__name__
+        t = threading.Thread(target=slow)
+        t.start()
+        time.sleep(0.2)
+        t1 = time.time()
+        service.shutdown()
+        assert time.time() - t1 < 6
+        t.join(timeout=15)
+        assert not t.is_alive() and "outcome" in result
+    finally:
+        try:
+            service.shutdown()
+        except Exception:  # noqa: BLE001
+            pass
+
+
+def test_safe_shell_exec_kills_the_whole_process_tree_on_event():
+    """Parity: test/single/test_run.py safe_shell_exec tests (the shell's
+    children must die with it)."""
+    import subprocess
+    event = threading.Event()
+    marker = "hvd_sleep_marker_%d" % os.getpid()
+    out = io.StringIO()
+    cmd = "bash -c 'echo started; sleep 300 & wait' # %s" % marker
+    t = threading.Thread(target=lambda: safe_shell_exec.execute(cmd, stdout=out, events=[event]))
+    t0 = time.time()
+    t.start()
+    time.sleep(1.0)
+    event.set()
+    t.join(timeout=20)
+    assert not t.is_alive() and time.time() - t0 < 15
+    assert "started" in out.getvalue()
+    time.sleep(0.5)
+    ps = subprocess.run(["ps", "-eo", "args"], capture_output=True, text=True).stdout
+    assert not [line for line in ps.splitlines() if marker in line and "ps -eo" not in line]

@@ -189,7 +189,7 @@ def main():
     dev_x, dev_y = to_dev(host_x[0]), host_y[0].to(device)
 
     def step(x, y):
-        opt.zero_grad(set_to_none=False)
+        opt.zero_grad()
         with torch.autocast("cuda", dtype=torch.bfloat16):
             loss = loss_fn(x, y)
         loss.backward()

@@ -11,7 +11,8 @@ from horovod_b200.torch.compression import Compression
 from horovod_b200.torch.functions import (allgather_object, broadcast_object,
                                           broadcast_optimizer_state, broadcast_parameters)
 from horovod_b200.torch.mpi_ops import (Adasum, Average, Max, Min, Product, Sum, allgather,
-                                        allgather_async, allreduce, allreduce_,
+                                        allgather_async, allreduce, allreduce_, barrier,
+                                        grouped_allgather, grouped_reducescatter,
                                         allreduce_async, allreduce_async_, alltoall,
                                         alltoall_async, broadcast, broadcast_,
                                         broadcast_async, broadcast_async_, ccl_built,

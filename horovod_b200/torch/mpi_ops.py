@@ -536,6 +536,35 @@ def synchronize(handle):
     return outputs[0]
 
 
+def barrier(process_set=global_process_set):
+    """Returns once every rank of the process set has called it (and every
+    collective this rank enqueued before has been negotiated). An extension
+    that later releases of the reference also offer."""
+    synchronize(allreduce_async(torch.zeros(1), op=Sum, name=None, process_set=process_set))
+
+
+def grouped_allgather(tensors, name=None, process_set=global_process_set):
+    """Allgathers a list of tensors; the requests are issued together so that
+    they are negotiated in one cycle and fused by the controller. Returns the
+    gathered tensors in order."""
+    base = name
+    handles = [allgather_async(t, name=None if base is None else "%s.%d" % (base, i),
+                               process_set=process_set) for i, t in enumerate(tensors)]
+    return [synchronize(h) for h in handles]
+
+
+def grouped_reducescatter(tensors, name=None, op=Average, prescale_factor=1.0,
+                          postscale_factor=1.0, process_set=global_process_set):
+    """Reduce-scatters a list of tensors, issued together; returns this rank's
+    shards in order."""
+    base = name
+    handles = [reducescatter_async(t, name=None if base is None else "%s.%d" % (base, i), op=op,
+                                   prescale_factor=prescale_factor,
+                                   postscale_factor=postscale_factor, process_set=process_set)
+               for i, t in enumerate(tensors)]
+    return [synchronize(h) for h in handles]
+
+
 def join(device=-1, process_set=global_process_set):
     """Tells the other ranks this rank has no more data. Blocks until every
     rank has joined; meanwhile this rank contributes zeros to their

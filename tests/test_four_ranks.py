@@ -154,3 +154,25 @@ def _threads(rank, size):
 
 def test_collectives_from_several_python_threads():
     assert all(run_parallel(_threads, np=2, timeout=300))
+
+
+def _grouped_extras(rank, size):
+    import horovod_b200.torch as hvd
+    hvd.init()
+    gathered = hvd.grouped_allgather([torch.full((rank + 1, 2), float(rank)),
+                                      torch.full((2,), float(10 + rank))], name="gag")
+    ok = torch.equal(gathered[0], torch.cat([torch.full((r + 1, 2), float(r))
+                                             for r in range(size)]))
+    ok = ok and gathered[1].tolist() == [float(10 + r) for r in range(size) for _ in range(2)]
+    shards = hvd.grouped_reducescatter([torch.arange(size * 2, dtype=torch.float32) + rank,
+                                        torch.ones(size, 3) * (rank + 1)], op=hvd.Sum, name="grs")
+    tot = sum(range(size))
+    exp0 = (torch.arange(size * 2, dtype=torch.float32) * size + tot)[rank * 2:(rank + 1) * 2]
+    ok = ok and torch.equal(shards[0], exp0) and bool((shards[1] == sum(range(1, size + 1))).all())
+    hvd.barrier()
+    hvd.shutdown()
+    return ok
+
+
+def test_grouped_allgather_reducescatter_and_barrier():
+    assert all(run_parallel(_grouped_extras, np=3, timeout=300))

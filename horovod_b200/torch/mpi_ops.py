@@ -536,11 +536,20 @@ def synchronize(handle):
     return outputs[0]
 
 
+_barrier_counts = {}
+
+
 def barrier(process_set=global_process_set):
     """Returns once every rank of the process set has called it (and every
     collective this rank enqueued before has been negotiated). An extension
     that later releases of the reference also offer."""
-    synchronize(allreduce_async(torch.zeros(1), op=Sum, name=None, process_set=process_set))
+    ps_id = _resolve(process_set)
+    count = _barrier_counts.get(ps_id, 0)
+    _barrier_counts[ps_id] = count + 1
+    # Named by a per-set call counter, which is the same on every rank
+    # whatever else the ranks have enqueued.
+    synchronize(allreduce_async(torch.zeros(1), op=Sum, name="hvd.barrier.%d.%d" % (ps_id, count),
+                                process_set=process_set))
 
 
 def grouped_allgather(tensors, name=None, process_set=global_process_set):

@@ -22,7 +22,15 @@ from horovod_b200.torch.compression import Compression
 _basics = HorovodBasics()
 
 init = _basics.init
-shutdown = _basics.shutdown
+
+
+def shutdown():
+    """Stops the background thread and releases its resources; init() may be
+    called again afterwards."""
+    _barrier_counts.clear()  # survivors and newcomers of an elastic reset agree again
+    _basics.shutdown()
+
+
 is_initialized = _basics.is_initialized
 size = _basics.size
 local_size = _basics.local_size

@@ -30,7 +30,7 @@ def test_mnist_example_trains(tmp_path):
 
 
 def test_synthetic_benchmark_example():
-    out = _launch(2, ["examples/pytorch_synthetic_benchmark.py", "--no-cuda", "--batch-size", "2",
+    out = _launch(2, ["examples/pytorch_synthetic_benchmark.py", "--no-cuda", "--batch-size", "1",
                       "--num-warmup-batches", "1", "--num-batches-per-iter", "1",
-                      "--num-iters", "2"])
+                      "--num-iters", "1"])
     assert "Total img/sec on 2 rank(s)" in out

@@ -16,11 +16,13 @@ constexpr int64_t STAGING_ALIGN = 256;
 }
 
 void GpuOps::LaunchExchangeSegments(const std::vector<OutSeg>& out,
-                                    const std::vector<InSeg>& in, SymmSet& set) {
+                                    const std::vector<InSeg>& in, SymmSet& set,
+                                    int64_t round_bytes) {
   const size_t no = out.size(), ni = in.size();
-  int64_t bytes = 0;
-  for (auto& o : out) bytes += o.bytes;
-  for (auto& i : in) bytes += i.bytes;
+  // The grid size must be the same on every rank (CTA b meets CTA b of its
+  // peers), so it is derived from the bytes of the whole round, which all
+  // ranks know, not from this rank's share of them.
+  const int64_t bytes = round_bytes;
   kern::ExchangePlan plan;
   std::memset(&plan, 0, sizeof(plan));
   cudaError_t err;
@@ -108,7 +110,8 @@ struct Block {
 
 static void RunBlocks(GpuOps* self, std::vector<Block>& blocks, SymmSet& set,
                       const std::function<void(const std::vector<GpuOps::OutSeg>&,
-                                               const std::vector<GpuOps::InSeg>&)>& launch) {
+                                               const std::vector<GpuOps::InSeg>&,
+                                               int64_t)>& launch) {
   (void)self;
   const int64_t cap = static_cast<int64_t>(set.data_bytes);
   // Split oversized blocks.
@@ -134,6 +137,7 @@ static void RunBlocks(GpuOps* self, std::vector<Block>& blocks, SymmSet& set,
     // cursors, a point-to-point block only its destination's.
     std::vector<int64_t> cursor(set.world, 0);
     size_t n = 0;
+    int64_t round_bytes = 0;
     while (next + n < parts.size() && n < 4096) {
       const Block& b = parts[next + n];
       int64_t padded = RoundUp(b.bytes, STAGING_ALIGN);
@@ -151,10 +155,11 @@ static void RunBlocks(GpuOps* self, std::vector<Block>& blocks, SymmSet& set,
         out.push_back({b.src, off, b.bytes, b.dst_rank});
       if ((b.dst_rank < 0 || b.dst_rank == set.rank) && b.dst != nullptr)
         in.push_back({b.dst, off, b.bytes});
+      round_bytes += b.bytes;
       ++n;
     }
     if (n == 0) throw std::runtime_error("exchange block exceeds staging capacity");
-    launch(out, in);
+    launch(out, in, round_bytes);
     next += n;
   }
 }
@@ -177,8 +182,8 @@ Status GpuOps::SymmBroadcast(std::vector<TensorTableEntry>& entries,
     blocks.push_back(b);
   }
   RunBlocks(this, blocks, set,
-            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i) {
-              LaunchExchangeSegments(o, i, set);
+            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i, int64_t round_bytes) {
+              LaunchExchangeSegments(o, i, set, round_bytes);
             });
   tl.ActivityEndAll(entries);
   return Complete(entries);
@@ -218,8 +223,8 @@ Status GpuOps::SymmAllgather(std::vector<TensorTableEntry>& entries,
   }
   tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
   RunBlocks(this, blocks, set,
-            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i) {
-              LaunchExchangeSegments(o, i, set);
+            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i, int64_t round_bytes) {
+              LaunchExchangeSegments(o, i, set, round_bytes);
             });
   tl.ActivityEndAll(entries);
   return Complete(entries);
@@ -275,8 +280,8 @@ Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries,
   }
   tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
   RunBlocks(this, blocks, set,
-            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i) {
-              LaunchExchangeSegments(o, i, set);
+            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i, int64_t round_bytes) {
+              LaunchExchangeSegments(o, i, set, round_bytes);
             });
   tl.ActivityEndAll(entries);
   return Complete(entries);

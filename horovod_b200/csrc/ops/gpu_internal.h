@@ -174,7 +174,8 @@ private:
                            const Response& response, SymmSet& set, Status* status);
   // One exchange-kernel launch for the given segment lists.
   void LaunchExchangeSegments(const std::vector<OutSeg>& out,
-                              const std::vector<InSeg>& in, SymmSet& set);
+                              const std::vector<InSeg>& in, SymmSet& set,
+                              int64_t round_bytes);
 
   GlobalState& state_;
   std::shared_ptr<DoneEventPool> events_;

@@ -182,6 +182,47 @@ cudaError_t LaunchExchange(const ExchangePlan& plan, int num_ctas,
                            const SymmCtx& ctx, cudaStream_t stream,
                            const InlineExchange* inline_plan = nullptr);
 
+// Pipelined exchange for large rounds: instead of "push everything, barrier,
+// deliver everything", a CTA cuts its slice of every outbound segment into
+// chunks, publishes a running chunk counter to its peers after each chunk, and
+// delivers inbound chunks as soon as their source's counter has reached them,
+// so pushing over NVLink and the local delivery copies overlap. The plan lives
+// in device memory (descriptor ring); in_src_rank / in_wait_base tell where an
+// inbound segment comes from and how many chunks its source CTA has published
+// before it starts on that segment. A launch consumes `done_epochs` barrier
+// epochs: chunk n of a source is published as ctx.epoch + n, the trailing
+// barrier uses ctx.epoch + done_epochs (larger than any chunk count).
+struct PipelinePlan {
+  int n_out;
+  const void* const* out_src;
+  const int64_t* out_staging_off;
+  const int64_t* out_bytes;
+  const int32_t* out_dst_rank;
+  int n_in;
+  void* const* in_dst;
+  const int64_t* in_staging_off;
+  const int64_t* in_bytes;
+  const int32_t* in_src_rank;
+  const int32_t* in_wait_base;
+  int64_t chunk_bytes;
+  uint32_t done_epochs;
+};
+// Chunks into which every CTA of a launch with `num_ctas` CTAs cuts its slice
+// of a segment of `bytes` bytes (the same number for all CTAs of all ranks; a
+// CTA whose slice is shorter publishes the remaining counts without copying).
+#if defined(__CUDACC__)
+__host__ __device__
+#endif
+inline int64_t ExchangeChunkCount(int64_t bytes, int num_ctas, int64_t chunk_bytes) {
+  if (bytes <= 64 * 1024) return 1;  // small segments are owned by one CTA
+  int64_t slice = (bytes + num_ctas - 1) / num_ctas;
+  slice = (slice + 255) & ~int64_t(255);
+  int64_t k = (slice + chunk_bytes - 1) / chunk_bytes;
+  return k < 1 ? 1 : k;
+}
+cudaError_t LaunchExchangePipelined(const PipelinePlan& plan, int num_ctas,
+                                    const SymmCtx& ctx, cudaStream_t stream);
+
 // Adasum over symmetric memory. Tensors are packed into staging as fp32
 // (prescaled), combined pairwise over log2(world) levels with per-tensor
 // dot / squared norms accumulated in fp64, and scattered back. `scratch`

@@ -17,7 +17,11 @@ constexpr int64_t STAGING_ALIGN = 256;
 
 void GpuOps::LaunchExchangeSegments(const std::vector<OutSeg>& out,
                                     const std::vector<InSeg>& in, SymmSet& set,
-                                    int64_t round_bytes) {
+                                    int64_t round_bytes,
+                                    const std::vector<RoundBlock>& round) {
+  if (exchange_pipeline_ && set.world > 1 && round_bytes >= (8 << 20) &&
+      LaunchExchangePipelined(out, in, set, round_bytes, round))
+    return;
   const size_t no = out.size(), ni = in.size();
   // The grid size must be the same on every rank (CTA b meets CTA b of its
   // peers), so it is derived from the bytes of the whole round, which all
@@ -93,6 +97,87 @@ void GpuOps::LaunchExchangeSegments(const std::vector<OutSeg>& out,
                              cudaGetErrorString(err));
 }
 
+// Plan for the pipelined kernel. Every rank derives the same numbers from the
+// round's block list: the grid size, the chunks per block, how many chunks a
+// source has published before each of its blocks, and the epochs the launch
+// consumes (the largest chunk total of any rank, plus one for the final barrier).
+// Returns false (nothing launched) when the plan does not fit a descriptor slot.
+bool GpuOps::LaunchExchangePipelined(const std::vector<OutSeg>& out,
+                                     const std::vector<InSeg>& in, SymmSet& set,
+                                     int64_t round_bytes,
+                                     const std::vector<RoundBlock>& round) {
+  const size_t no = out.size(), ni = in.size();
+  const int ctas = PickCtas(round_bytes);
+  const int64_t chunk = exchange_chunk_bytes_ / 256 * 256;
+  std::vector<int64_t> published(set.world, 0);   // chunks per source so far
+  std::vector<int64_t> before(round.size(), 0);   // ... before each block
+  for (size_t i = 0; i < round.size(); ++i) {
+    const int src = round[i].src_rank;
+    if (src < 0 || src >= set.world) return false;
+    before[i] = published[src];
+    published[src] += kern::ExchangeChunkCount(round[i].bytes, ctas, chunk);
+  }
+  const int64_t most = *std::max_element(published.begin(), published.end());
+  if (most + 1 > (int64_t(1) << 30)) return false;
+
+  DescriptorRing::Slot slot = ring_.Acquire();
+  const void** d_src;
+  int64_t *d_ooff, *d_obytes, *d_ioff, *d_ibytes;
+  int32_t *d_dst_rank, *d_isrc, *d_iwait;
+  void** d_dst;
+  const void** h_src = slot.Alloc<const void*>(no + 1, &d_src);
+  int64_t* h_ooff = slot.Alloc<int64_t>(no + 1, &d_ooff);
+  int64_t* h_obytes = slot.Alloc<int64_t>(no + 1, &d_obytes);
+  int32_t* h_dst_rank = slot.Alloc<int32_t>(no + 1, &d_dst_rank);
+  void** h_dst = slot.Alloc<void*>(ni + 1, &d_dst);
+  int64_t* h_ioff = slot.Alloc<int64_t>(ni + 1, &d_ioff);
+  int64_t* h_ibytes = slot.Alloc<int64_t>(ni + 1, &d_ibytes);
+  int32_t* h_isrc = slot.Alloc<int32_t>(ni + 1, &d_isrc);
+  int32_t* h_iwait = slot.Alloc<int32_t>(ni + 1, &d_iwait);
+  if (!h_src || !h_ooff || !h_obytes || !h_dst_rank || !h_dst || !h_ioff || !h_ibytes ||
+      !h_isrc || !h_iwait) {
+    // Nothing was copied or launched: hand the slot back unused.
+    ring_.Release(slot, stream_);
+    return false;
+  }
+  for (size_t i = 0; i < no; ++i) {
+    h_src[i] = out[i].src;
+    h_ooff[i] = out[i].staging_off;
+    h_obytes[i] = out[i].bytes;
+    h_dst_rank[i] = out[i].dst;
+  }
+  for (size_t i = 0; i < ni; ++i) {
+    h_dst[i] = in[i].dst;
+    h_ioff[i] = in[i].staging_off;
+    h_ibytes[i] = in[i].bytes;
+    h_isrc[i] = in[i].src_rank;
+    h_iwait[i] = static_cast<int32_t>(before[in[i].block]);
+  }
+  ring_.Commit(slot, stream_);
+  kern::PipelinePlan plan;
+  std::memset(&plan, 0, sizeof(plan));
+  plan.n_out = static_cast<int>(no);
+  plan.out_src = d_src;
+  plan.out_staging_off = d_ooff;
+  plan.out_bytes = d_obytes;
+  plan.out_dst_rank = d_dst_rank;
+  plan.n_in = static_cast<int>(ni);
+  plan.in_dst = d_dst;
+  plan.in_staging_off = d_ioff;
+  plan.in_bytes = d_ibytes;
+  plan.in_src_rank = d_isrc;
+  plan.in_wait_base = d_iwait;
+  plan.chunk_bytes = chunk;
+  plan.done_epochs = static_cast<uint32_t>(most + 1);
+  kern::SymmCtx ctx = MakeCtx(set, plan.done_epochs);
+  cudaError_t err = kern::LaunchExchangePipelined(plan, ctas, ctx, stream_);
+  ring_.Release(slot, stream_);
+  if (err != cudaSuccess)
+    throw std::runtime_error(std::string("pipelined exchange launch failed: ") +
+                             cudaGetErrorString(err));
+  return true;
+}
+
 // Every rank builds the same global list of "blocks" (source rank, bytes,
 // who receives it); blocks are laid out in the staging buffer in order and
 // processed in rounds that fit its capacity. A block larger than the
@@ -111,7 +196,8 @@ struct Block {
 static void RunBlocks(GpuOps* self, std::vector<Block>& blocks, SymmSet& set,
                       const std::function<void(const std::vector<GpuOps::OutSeg>&,
                                                const std::vector<GpuOps::InSeg>&,
-                                               int64_t)>& launch) {
+                                               int64_t,
+                                               const std::vector<GpuOps::RoundBlock>&)>& launch) {
   (void)self;
   const int64_t cap = static_cast<int64_t>(set.data_bytes);
   // Split oversized blocks.
@@ -138,6 +224,7 @@ static void RunBlocks(GpuOps* self, std::vector<Block>& blocks, SymmSet& set,
     std::vector<int64_t> cursor(set.world, 0);
     size_t n = 0;
     int64_t round_bytes = 0;
+    std::vector<GpuOps::RoundBlock> round;
     while (next + n < parts.size() && n < 4096) {
       const Block& b = parts[next + n];
       int64_t padded = RoundUp(b.bytes, STAGING_ALIGN);
@@ -154,12 +241,13 @@ static void RunBlocks(GpuOps* self, std::vector<Block>& blocks, SymmSet& set,
       if (b.src_rank == set.rank)
         out.push_back({b.src, off, b.bytes, b.dst_rank});
       if ((b.dst_rank < 0 || b.dst_rank == set.rank) && b.dst != nullptr)
-        in.push_back({b.dst, off, b.bytes});
+        in.push_back({b.dst, off, b.bytes, b.src_rank, static_cast<int32_t>(round.size())});
+      round.push_back({b.src_rank, b.bytes});
       round_bytes += b.bytes;
       ++n;
     }
     if (n == 0) throw std::runtime_error("exchange block exceeds staging capacity");
-    launch(out, in, round_bytes);
+    launch(out, in, round_bytes, round);
     next += n;
   }
 }
@@ -182,8 +270,9 @@ Status GpuOps::SymmBroadcast(std::vector<TensorTableEntry>& entries,
     blocks.push_back(b);
   }
   RunBlocks(this, blocks, set,
-            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i, int64_t round_bytes) {
-              LaunchExchangeSegments(o, i, set, round_bytes);
+            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i, int64_t round_bytes,
+                const std::vector<RoundBlock>& round) {
+              LaunchExchangeSegments(o, i, set, round_bytes, round);
             });
   tl.ActivityEndAll(entries);
   return Complete(entries);
@@ -223,8 +312,9 @@ Status GpuOps::SymmAllgather(std::vector<TensorTableEntry>& entries,
   }
   tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
   RunBlocks(this, blocks, set,
-            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i, int64_t round_bytes) {
-              LaunchExchangeSegments(o, i, set, round_bytes);
+            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i, int64_t round_bytes,
+                const std::vector<RoundBlock>& round) {
+              LaunchExchangeSegments(o, i, set, round_bytes, round);
             });
   tl.ActivityEndAll(entries);
   return Complete(entries);
@@ -280,8 +370,9 @@ Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries,
   }
   tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
   RunBlocks(this, blocks, set,
-            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i, int64_t round_bytes) {
-              LaunchExchangeSegments(o, i, set, round_bytes);
+            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i, int64_t round_bytes,
+                const std::vector<RoundBlock>& round) {
+              LaunchExchangeSegments(o, i, set, round_bytes, round);
             });
   tl.ActivityEndAll(entries);
   return Complete(entries);

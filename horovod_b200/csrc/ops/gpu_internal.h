@@ -117,7 +117,16 @@ public:
 
   // Segments handed to the exchange kernel.
   struct OutSeg { const void* src; int64_t staging_off; int64_t bytes; int32_t dst; };
-  struct InSeg { void* dst; int64_t staging_off; int64_t bytes; };
+  struct InSeg {
+    void* dst;
+    int64_t staging_off;
+    int64_t bytes;
+    int32_t src_rank;  // set rank that writes this segment
+    int32_t block;     // index into the round's block list (RoundBlock)
+  };
+  // Every block of one exchange round, in the order all ranks process them
+  // (what the pipelined kernel's chunk counters are derived from).
+  struct RoundBlock { int32_t src_rank; int64_t bytes; };
 
   // Device-time record of one executed response (HOROVOD_GPU_OP_TIMING=1).
   struct OpTiming {
@@ -175,7 +184,10 @@ private:
   // One exchange-kernel launch for the given segment lists.
   void LaunchExchangeSegments(const std::vector<OutSeg>& out,
                               const std::vector<InSeg>& in, SymmSet& set,
-                              int64_t round_bytes);
+                              int64_t round_bytes, const std::vector<RoundBlock>& round);
+  bool LaunchExchangePipelined(const std::vector<OutSeg>& out, const std::vector<InSeg>& in,
+                               SymmSet& set, int64_t round_bytes,
+                               const std::vector<RoundBlock>& round);
 
   GlobalState& state_;
   std::shared_ptr<DoneEventPool> events_;
@@ -202,6 +214,8 @@ private:
   unsigned long long* tile_counter_ = nullptr;  // device word, see kern::TileSchedule
   unsigned long long tile_base_ = 0;
   int64_t dynamic_min_bytes_ = 0;
+  bool exchange_pipeline_ = false;     // HOROVOD_EXCHANGE_PIPELINE=1
+  int64_t exchange_chunk_bytes_ = 64 << 10;
   unsigned long long* trace_host_ = nullptr;  // mapped pinned, HOROVOD_KERNEL_TRACE=1
   unsigned long long* trace_dev_ = nullptr;
   std::map<int32_t, std::unique_ptr<SymmSet>> sets_;

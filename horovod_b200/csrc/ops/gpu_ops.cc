@@ -154,6 +154,8 @@ void GpuOps::EnsureDevice(int device) {
   HVD_CUDA(cudaMemset(tile_counter_, 0, sizeof(unsigned long long)));
   tile_base_ = 0;
   dynamic_min_bytes_ = EnvInt("HOROVOD_DYNAMIC_TILES_MIN_BYTES", 8 << 20);
+  exchange_pipeline_ = EnvBool("HOROVOD_EXCHANGE_PIPELINE", false);
+  exchange_chunk_bytes_ = std::max<int64_t>(4096, EnvInt("HOROVOD_EXCHANGE_CHUNK_KB", 64) << 10);
   if (EnvBool("HOROVOD_KERNEL_TRACE", false)) {
     HVD_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&trace_host_),
                            kern::KERNEL_TRACE_SLOTS * sizeof(unsigned long long),

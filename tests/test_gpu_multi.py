@@ -341,3 +341,49 @@ def test_asymmetric_use_of_symmetric_memory_is_reported():
     # other rank either times out on its next collective or sees the shutdown.
     assert out[0] == (True, True), out
     assert out[1][0], out
+
+
+def _pipelined_exchange(rank, size):
+    os.environ["HOROVOD_EXCHANGE_PIPELINE"] = "1"
+    os.environ["HOROVOD_EXCHANGE_CHUNK_KB"] = "16"
+    os.environ["HOROVOD_SPIN_TIMEOUT_MS"] = "5000"
+    import horovod_b200.torch as hvd
+    hvd.init()
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    n = (3 << 20) + 5  # 12 MB per rank and a ragged tail
+    # allgather with a different dim 0 on every rank
+    x = _inputs(rank, n + rank * 1001, torch.float32).to(dev)
+    got = hvd.allgather(x, name="pipe.ag")
+    exp = torch.cat([_inputs(r, n + r * 1001, torch.float32) for r in range(size)])
+    ok = torch.equal(got.cpu(), exp)
+    # broadcast from the last rank
+    b = _inputs(rank, 5 * n, torch.float32).to(dev)
+    hvd.broadcast_(b, root_rank=size - 1, name="pipe.bc")
+    ok = ok and torch.equal(b.cpu(), _inputs(size - 1, 5 * n, torch.float32))
+    # uneven alltoall
+    splits = torch.tensor([(rank + p) % 3 + 1 for p in range(size)], dtype=torch.int32)
+    rows = int(splits.sum())
+    send = _inputs(rank + 40, rows * (1 << 20), torch.float32).view(rows, 1 << 20).to(dev)
+    recv, rsplits = hvd.alltoall(send, splits=splits, name="pipe.a2a")
+    pieces = []
+    for r in range(size):
+        s = [(r + p) % 3 + 1 for p in range(size)]
+        full = _inputs(r + 40, sum(s) * (1 << 20), torch.float32).view(sum(s), 1 << 20)
+        off = sum(s[:rank])
+        pieces.append(full[off:off + s[rank]])
+    ok = ok and torch.equal(recv.cpu(), torch.cat(pieces))
+    # a small op in between still takes the two-phase kernel
+    small = hvd.allgather(torch.full((3,), float(rank), device=dev), name="pipe.small")
+    ok = ok and small.cpu().tolist() == [float(r) for r in range(size) for _ in range(3)]
+    torch.cuda.synchronize()
+    hvd.shutdown()
+    return ok
+
+
+@pytest.mark.skipif(os.environ.get("HOROVOD_EXCHANGE_PIPELINE") != "1",
+                    reason="the pipelined exchange is opt-in (HOROVOD_EXCHANGE_PIPELINE=1)")
+def test_pipelined_exchange_matches_reference():
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    assert all(run_parallel(_pipelined_exchange, np=_world(), timeout=300))

@@ -497,7 +497,13 @@ int64_t Controller::ResponseBytes(const Response& r) const {
 
 void Controller::FuseResponses(std::deque<Response>& responses,
                                ResponseList& out) {
-  const int64_t threshold = TensorFusionThresholdBytes();
+  FuseResponseQueue(responses, TensorFusionThresholdBytes(),
+                    [this](const Response& r) { return ResponseBytes(r); }, out);
+}
+
+void FuseResponseQueue(std::deque<Response>& responses, int64_t threshold,
+                       const std::function<int64_t(const Response&)>& ResponseBytes,
+                       ResponseList& out) {
   while (!responses.empty()) {
     Response r = std::move(responses.front());
     responses.pop_front();

@@ -12,6 +12,7 @@
 #pragma once
 
 #include <deque>
+#include <functional>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -35,6 +36,16 @@ struct ControllerOptions {
   // local_size * FUSION_ATOMIC_UNIT so per-rank shards stay aligned.
   int local_size = 1;
 };
+
+// The fusion policy itself: greedily merges the responses that follow a
+// fusable one while they are compatible (same type, devices, dtype, scale
+// factors, reduce op, wire type; same root for broadcasts) and the total stays
+// within `threshold`; responses that do not fit are looked past as long as
+// what was skipped would still have fitted (they keep their order).
+// `bytes_of` is the fused size of one response.
+void FuseResponseQueue(std::deque<Response>& responses, int64_t threshold,
+                       const std::function<int64_t(const Response&)>& bytes_of,
+                       ResponseList& out);
 
 class Controller {
 public:

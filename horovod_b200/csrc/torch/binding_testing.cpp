@@ -6,6 +6,7 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include "../common/controller.h"
 #include "../common/half.h"
 #include "../common/message.h"
 #include "../common/optim/bayesian_optimization.h"
@@ -85,6 +86,38 @@ void BindTesting(py::module_& root) {
                           r.group_id, static_cast<int>(r.reduce_op), back.shutdown,
                           pr.names, pr.error_message, pr.tensor_sizes, pr.last_joined_rank,
                           static_cast<int>(pr.type), blob.size());
+  });
+  // Fusion policy on a list of single-tensor responses given as tuples
+  // (type, name, elements, dtype, prescale, postscale, root_rank); sizes follow
+  // the reduction rule (each tensor rounded up to 16 bytes). Returns the
+  // fused groups as lists of names, in execution order.
+  m.def("fuse_responses", [](const std::vector<std::tuple<int, std::string, int64_t, int, double,
+                                                          double, int>>& items,
+                             int64_t threshold) {
+    std::deque<Response> q;
+    for (auto& it : items) {
+      Response r;
+      r.type = static_cast<Response::Type>(std::get<0>(it));
+      r.names.push_back(std::get<1>(it));
+      r.tensor_sizes.push_back(std::get<2>(it));
+      r.dtype = static_cast<DataType>(std::get<3>(it));
+      r.wire_dtype = r.dtype;
+      r.prescale = std::get<4>(it);
+      r.postscale = std::get<5>(it);
+      r.root_rank = std::get<6>(it);
+      r.reduce_op = ReduceOp::SUM;
+      r.devices = {CPU_DEVICE_ID, CPU_DEVICE_ID};
+      q.push_back(std::move(r));
+    }
+    ResponseList out;
+    FuseResponseQueue(q, threshold, [](const Response& r) {
+      int64_t es = static_cast<int64_t>(DataTypeSize(r.dtype)), total = 0;
+      for (auto n : r.tensor_sizes) total += (n * es + 15) / 16 * 16;
+      return total;
+    }, out);
+    std::vector<std::vector<std::string>> groups;
+    for (auto& r : out.responses) groups.push_back(r.names);
+    return groups;
   });
   m.def("wire_parse_garbage", [](py::bytes data) {
     std::string s = data;

@@ -202,3 +202,34 @@ def test_parameter_manager_tunes_and_stops(tmp_path):
     for step in range(500):
         pm2.update(["t0"], 1000)
         assert pm2.fusion_threshold() == 12345678 and pm2.cache_enabled()
+
+
+def test_fusion_policy_threshold_lookahead_and_compatibility():
+    """Parity: FuseResponses, horovod/common/controller.cc:793-930."""
+    AR, BC, F32, F16 = 0, 2, 7, 6  # Response types / dtype ids of the wire format
+
+    def item(name, n, dtype=F32, pre=1.0, post=1.0, typ=AR, root=0):
+        return (typ, name, n, dtype, pre, post, root)
+
+    # everything fits: one fused response, order kept
+    assert T.fuse_responses([item("a", 10), item("b", 20), item("c", 30)], 1 << 20) == \
+        [["a", "b", "c"]]
+    # 16-byte rounding: 3 tensors of 5 floats = 3 x 32 bytes; threshold 64 holds two
+    assert T.fuse_responses([item("a", 5), item("b", 5), item("c", 5)], 64) == [["a", "b"], ["c"]]
+    # look-ahead: an fp16 response between two fp32 ones is skipped, not a barrier,
+    # and keeps its place in the queue
+    assert T.fuse_responses([item("w1", 100), item("h", 100, F16), item("w2", 100)], 1 << 20) == \
+        [["w1", "w2"], ["h"]]
+    # look-ahead stops when the skipped bytes would not have fitted either
+    assert T.fuse_responses([item("w1", 100), item("big", 1000, F16), item("w2", 100)], 1024) == \
+        [["w1"], ["big"], ["w2"]]
+    # different scale factors do not fuse
+    assert T.fuse_responses([item("a", 10), item("b", 10, post=0.5), item("c", 10)], 1 << 20) == \
+        [["a", "c"], ["b"]]
+    # a tensor larger than the threshold travels alone
+    assert T.fuse_responses([item("huge", 1 << 20), item("s", 4)], 1024) == [["huge"], ["s"]]
+    # broadcasts fuse per root, whatever the dtype
+    assert T.fuse_responses([item("p", 8, F32, typ=BC, root=0), item("q", 8, F16, typ=BC, root=0),
+                             item("r", 8, F32, typ=BC, root=1)], 1 << 20) == [["p", "q"], ["r"]]
+    # threshold 0: nothing fuses
+    assert T.fuse_responses([item("a", 1), item("b", 1)], 0) == [["a"], ["b"]]

@@ -376,3 +376,22 @@ def test_safe_shell_exec_kills_the_whole_process_tree_on_event():
     time.sleep(0.5)
     ps = subprocess.run(["ps", "-eo", "args"], capture_output=True, text=True).stdout
     assert not [line for line in ps.splitlines() if marker in line and "ps -eo" not in line]
+
+
+def test_output_filename_writes_per_rank_files(tmp_path):
+    """Parity: --output-filename / --prefix-timestamp (runner/gloo_run.py:150-163)."""
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out_dir = str(tmp_path / "logs")
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    proc = subprocess.run(
+        [sys.executable, "-m", "horovod_b200.runner.launch", "-np", "2", "--output-filename",
+         out_dir, "--prefix-timestamp", sys.executable, "-c",
+         "import horovod_b200.torch as hvd; hvd.init(); print('hello from', hvd.rank())"],
+        cwd=root, env=env, capture_output=True, text=True, timeout=120)
+    assert proc.returncode == 0, proc.stderr[-1500:]
+    for r in range(2):
+        text = open(os.path.join(out_dir, "rank.%d" % r, "stdout")).read()
+        assert "[%d]<stdout>:hello from %d" % (r, r) in text
+        assert text.split("[")[0].strip(), "timestamp prefix missing"
+        assert os.path.exists(os.path.join(out_dir, "rank.%d" % r, "stderr"))

@@ -304,6 +304,8 @@ hvd_b200_reducescatter1_noalloc(const void* in, void* out, long long count,
                                 void* stream_v, char* err, unsigned long err_len) {
   using namespace hvd;
   using namespace hvd::kern;
+  // Validate the id before it is narrowed to the one-byte enum.
+  if (dtype < 0 || dtype > 255) return Fail(2, err, err_len, "unsupported dtype id");
   DataType dt = static_cast<DataType>(dtype);
   switch (dt) {
   case DataType::UINT8: case DataType::INT8: case DataType::INT32:
@@ -317,15 +319,16 @@ hvd_b200_reducescatter1_noalloc(const void* in, void* out, long long count,
   if (count == 0) return 0;
   if (in == nullptr || out == nullptr)
     return Fail(2, err, err_len, "null input or output pointer");
-  const unsigned long long bytes =
-      static_cast<unsigned long long>(count) * DataTypeSize(dt);
-  if (bytes > HVD_B200_NOALLOC_MAX_BYTES) {
+  // Compare element counts, not a byte product that could wrap around.
+  const unsigned long long elem_size = DataTypeSize(dt);
+  if (static_cast<unsigned long long>(count) > HVD_B200_NOALLOC_MAX_BYTES / elem_size) {
     char detail[128];
     std::snprintf(detail, sizeof(detail),
-                  " (%llu bytes requested, limit %u bytes)", bytes,
-                  static_cast<unsigned>(HVD_B200_NOALLOC_MAX_BYTES));
+                  " (%lld elements of %llu bytes requested, limit %u bytes)", count,
+                  elem_size, static_cast<unsigned>(HVD_B200_NOALLOC_MAX_BYTES));
     return Fail(1, err, err_len, "input larger than the built-in scratch", detail);
   }
+  const unsigned long long bytes = static_cast<unsigned long long>(count) * elem_size;
 
   int device = 0;
   cudaError_t e = cudaGetDevice(&device);

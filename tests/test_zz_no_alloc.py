@@ -5,9 +5,10 @@ It serves callers that cannot allocate device memory themselves (all memory
 already planned by a serving runtime or reserved by a framework allocator,
 or a code path where cudaMalloc's device-wide synchronisation is not
 acceptable). The result must equal what the library's regular reduce-scatter
-produces for a group of one, and a second call right after the first must be
-just as correct, because both share one built-in scratch array that keeps the
-first call's leftovers.
+produces for a group of one and what plain PyTorch arithmetic in fp32 gives
+for ``postscale * (prescale * x)``, and a second call right after the first
+must be just as correct, because both share one built-in scratch array that
+keeps the first call's leftovers.
 """
 import ctypes
 import os
@@ -71,8 +72,34 @@ def test_matches_regular_reducescatter_twice_in_a_row():
                 dict(rtol=1e-2, atol=1e-2)
             torch.testing.assert_close(out_b, want, **tol)
             torch.testing.assert_close(out_a, want_a, **tol)
+            # ... and against the same arithmetic done by PyTorch in fp32.
+            torch.testing.assert_close(out_b.float(), _expected(x, pre, post).float(), **tol)
+            torch.testing.assert_close(out_a.float(), _expected(other, pre, post).float(), **tol)
     finally:
         hvd.shutdown()
+
+
+def _expected(x, pre, post):
+    """postscale * (prescale * x) with each product rounded to the tensor type,
+    which is what the kernel's staging step does."""
+    return ((x.float() * pre).to(x.dtype).float() * post).to(x.dtype)
+
+
+def test_in_place_and_largest_accepted_size():
+    """The header allows in == out; and an input of exactly the maximum size
+    must be accepted. Both twice in a row, compared with PyTorch arithmetic."""
+    fn = _lib()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(1)
+    for n, pre, post in [(70001, 0.5, 4.0), (MAX_BYTES // 4, 1.0, 0.125)]:
+        for _ in range(2):
+            x = torch.randn(n, device=dev)
+            want = _expected(x, pre, post)
+            rc, msg = _call(fn, x, x, FLOAT32, pre, post)
+            assert rc == 0, msg
+            torch.cuda.synchronize()
+            torch.testing.assert_close(x, want, rtol=1e-6, atol=1e-6)
 
 
 def test_rejects_oversized_and_bad_arguments():
@@ -86,5 +113,16 @@ def test_rejects_oversized_and_bad_arguments():
     rc = fn(x.data_ptr(), x.data_ptr(), 16, 99, 1.0, 1.0, None, err, 256)
     assert rc == 2 and b"dtype" in err.value
     rc = fn(None, x.data_ptr(), 16, FLOAT32, 1.0, 1.0, None, err, 256)
+    assert rc == 2
+    # Counts whose byte size wraps around 64 bits, and dtype ids that would
+    # alias a valid one after narrowing to a byte: refused before any launch.
+    FLOAT64, INT32 = 8, 4
+    rc = fn(x.data_ptr(), x.data_ptr(), 1 << 61, FLOAT64, 1.0, 1.0, None, err, 256)
+    assert rc == 1 and b"larger than the built-in scratch" in err.value
+    rc = fn(x.data_ptr(), x.data_ptr(), 1 << 62, INT32, 1.0, 1.0, None, err, 256)
+    assert rc == 1
+    rc = fn(x.data_ptr(), x.data_ptr(), 16, 256 + FLOAT32, 1.0, 1.0, None, err, 256)
+    assert rc == 2 and b"dtype" in err.value
+    rc = fn(x.data_ptr(), x.data_ptr(), 16, 256, 1.0, 1.0, None, err, 256)
     assert rc == 2
     torch.cuda.synchronize()

@@ -330,3 +330,9 @@ class HorovodBasics:
         """Which device data path is active: "symm ..." (NVLink kernels over
         symmetric memory), "nccl" or "none"."""
         return _native().gpu_backend()
+
+    def runtime_params(self):
+        """The tunables as they are in effect now (the autotuner may have moved
+        them): fusion_threshold_bytes, cycle_time_ms, cache_enabled,
+        hierarchical_allreduce, hierarchical_allgather, autotune."""
+        return dict(_native().runtime_params())

@@ -1,13 +1,11 @@
-// Allgather, broadcast and alltoall as one "exchange" kernel: every outbound
-// segment is copied from local tensor storage straight into the destination
-// rank's staging buffer over NVLink (peer stores; a segment addressed to all
-// ranks is written once through the multicast mapping with multimem.st when
-// available), one cross-GPU barrier follows, and every inbound segment is
-// copied from the local staging buffer into its final tensor.
+// Allgather, broadcast and alltoall as one "stage locally, pull remotely"
+// exchange kernel (the protocol is described at ExchangePlan in kernels.h).
 //
-// A segment is owned by the same CTA index on the sending and the receiving
-// rank (small segments by a hash of their staging offset, large ones split
-// evenly), so CTA b only waits for CTA b of its peers.
+// A segment is owned by the same CTA index on the staging and the pulling
+// rank (small segments by a hash of their region offset, large ones split
+// evenly), so CTA b only ever waits for CTA b of the ranks it reads from.
+// Every wait is bounded: when it runs out the CTA records who it was waiting
+// for in the status word and leaves, and so does the rest of the job.
 //
 // Replaces ncclAllGather / grouped ncclBroadcast / ncclBcast per tensor /
 // grouped ncclSend+ncclRecv and the cudaMemcpyAsync loops around them
@@ -22,75 +20,207 @@ namespace {
 
 using namespace exch;
 
+// Flag bank that carries the region credits: word [rank r][0] of this bank in
+// my pad = number of the last exchange launch rank r has completed.
+constexpr int CREDIT_BANK = 2 * SYMM_MAX_RANKS * SYMM_MAX_BLOCKS;
+
+__device__ __forceinline__ void report_timeout(const SymmCtx& ctx, int peer, int phase,
+                                               int block) {
+  volatile int* st = ctx.status;
+  st[1] = peer;
+  st[2] = phase;
+  st[3] = block;
+  __threadfence_system();
+  if (st[0] == 0) st[0] = 1;
+  __threadfence_system();
+}
+
+// Thread 0 waits (bounded) until flag word `f` has reached `want`; all
+// threads call it and learn the outcome.
+__device__ __forceinline__ bool wait_word(const SymmCtx& ctx, const uint32_t* f, uint32_t want,
+                                          int peer, int phase, int block) {
+  bool ok = true;
+  if (threadIdx.x == 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    int spins = 0;
+    while (static_cast<int32_t>(ld_acquire_sys(f) - want) < 0) {
+      if ((++spins & 63) == 0 && globaltimer_ns() - t0 > ctx.timeout_ns) {
+        ok = false;
+        report_timeout(ctx, peer, phase, block);
+        break;
+      }
+    }
+  }
+  return __syncthreads_and(ok) != 0;
+}
+
 // INLINE: the plan rides in the kernel parameters and is copied to shared
 // memory first (parameter reads with compile-time offsets only); else it is
 // read from device memory.
 template <bool INLINE>
-__global__ void __launch_bounds__(THREADS)
-exchange_kernel(const InlineExchange inl, const ExchangePlan plan_dev, SymmCtx ctx) {
+__global__ void __launch_bounds__(THREADS, 2)
+exchange_kernel(const InlineExchange inl, const ExchangePlan plan_dev, const ExchangeSync sync,
+                SymmCtx ctx) {
   const int b = blockIdx.x, G = gridDim.x;
   constexpr int SEGS = INLINE ? INLINE_SEGMENTS : 1;
-  __shared__ const void* s_out_src[SEGS];
-  __shared__ int64_t s_out_off[SEGS];
-  __shared__ int64_t s_out_bytes[SEGS];
-  __shared__ int32_t s_out_rank[SEGS];
-  __shared__ void* s_in_dst[SEGS];
-  __shared__ int64_t s_in_off[SEGS];
-  __shared__ int64_t s_in_bytes[SEGS];
+  __shared__ const void* s_st_src[SEGS];
+  __shared__ void* s_st_self[SEGS];
+  __shared__ int64_t s_st_off[SEGS];
+  __shared__ int64_t s_st_bytes[SEGS];
+  __shared__ void* s_pl_dst[SEGS];
+  __shared__ int64_t s_pl_off[SEGS];
+  __shared__ int64_t s_pl_bytes[SEGS];
+  __shared__ int32_t s_pl_src[SEGS];
+  __shared__ int32_t s_pl_sig[SEGS];
+  __shared__ int32_t s_pl_wait[SEGS];
+  __shared__ int s_ready;
   ExchangePlan plan = plan_dev;
   if constexpr (INLINE) {
 #pragma unroll
     for (int i = 0; i < INLINE_SEGMENTS; ++i) {
-      if (threadIdx.x == i && i < inl.n_out) {
-        s_out_src[i] = inl.out_src[i];
-        s_out_off[i] = inl.out_staging_off[i];
-        s_out_bytes[i] = inl.out_bytes[i];
-        s_out_rank[i] = inl.out_dst_rank[i];
+      if (threadIdx.x == i && i < inl.n_stage) {
+        s_st_src[i] = inl.st_src[i];
+        s_st_self[i] = inl.st_self[i];
+        s_st_off[i] = inl.st_off[i];
+        s_st_bytes[i] = inl.st_bytes[i];
       }
-      if (threadIdx.x == 32 + i && i < inl.n_in) {
-        s_in_dst[i] = inl.in_dst[i];
-        s_in_off[i] = inl.in_staging_off[i];
-        s_in_bytes[i] = inl.in_bytes[i];
+      if (threadIdx.x == 32 + i && i < inl.n_pull) {
+        s_pl_dst[i] = inl.pl_dst[i];
+        s_pl_off[i] = inl.pl_off[i];
+        s_pl_bytes[i] = inl.pl_bytes[i];
+        s_pl_src[i] = inl.pl_src[i];
+        s_pl_sig[i] = inl.pl_sig[i];
+        s_pl_wait[i] = inl.pl_wait[i];
       }
     }
+    plan.n_stage = inl.n_stage;
+    plan.st_src = s_st_src;
+    plan.st_self = s_st_self;
+    plan.st_off = s_st_off;
+    plan.st_bytes = s_st_bytes;
+    plan.n_pull = inl.n_pull;
+    plan.pl_dst = s_pl_dst;
+    plan.pl_off = s_pl_off;
+    plan.pl_bytes = s_pl_bytes;
+    plan.pl_src = s_pl_src;
+    plan.pl_sig = s_pl_sig;
+    plan.pl_wait = s_pl_wait;
+  }
+  __syncthreads();
+
+  // The region this launch writes may still be read by peers that are behind:
+  // wait until each of them has finished the launch that used it last.
+  if (sync.credit_wait != 0) {
+    bool ok = true;
+    if (threadIdx.x < ctx.world) {
+      const uint32_t* f = ctx.flags_local + CREDIT_BANK + threadIdx.x * SYMM_MAX_BLOCKS;
+      const unsigned long long t0 = globaltimer_ns();
+      int spins = 0;
+      while (static_cast<int32_t>(ld_acquire_sys(f) - sync.credit_wait) < 0) {
+        if ((++spins & 63) == 0 && globaltimer_ns() - t0 > ctx.timeout_ns) {
+          ok = false;
+          report_timeout(ctx, threadIdx.x, 0, b);
+          break;
+        }
+      }
+    }
+    if (__syncthreads_and(ok) == 0) return;
+  }
+
+  const int64_t C = sync.chunk_bytes;
+  char* const region_w = sync.mc_push ? ctx.mc : ctx.local;  // where staged data goes
+  int so = 0, si = 0;      // current staged / pulled segment
+  int64_t ko = 0, ki = 0;  // current chunk inside it
+  uint32_t published = 0;  // chunks this CTA has made visible so far
+
+  for (;;) {
+    // ---- stage one chunk (or one whole local-only copy) --------------------
+    if (so < plan.n_stage) {
+      const int64_t off = plan.st_off[so], bytes = plan.st_bytes[so];
+      const char* src = static_cast<const char*>(plan.st_src[so]);
+      char* self = static_cast<char*>(plan.st_self[so]);
+      if (off < 0) {
+        // Local copy only (data this rank sends to itself): even split.
+        int64_t slice = (bytes + G - 1) / G;
+        slice = (slice + 255) & ~int64_t(255);
+        const int64_t lo = min(bytes, b * slice), hi = min(bytes, lo + slice);
+        if (lo < hi && self != nullptr)
+          copy_bytes<4>(src + lo, false, nullptr, false, self + lo, hi - lo);
+        ++so;
+      } else {
+        const int64_t K = ExchangeChunkCount(bytes, G, C);
+        int64_t lo, hi;
+        my_range(off, bytes, b, G, &lo, &hi);
+        const int64_t clo = lo + ko * C, chi = min(hi, clo + C);
+        if (clo < chi)
+          copy_bytes<4>(src + clo, false, region_w + off + clo, sync.mc_push != 0,
+                        self != nullptr ? self + clo : nullptr, chi - clo);
+        __syncthreads();
+        ++published;
+        if (threadIdx.x < ctx.world)
+          st_release_sys(ctx.flags_peers[threadIdx.x] + ctx.rank * SYMM_MAX_BLOCKS + b,
+                         ctx.epoch + published);
+        if (++ko == K) {
+          ko = 0;
+          ++so;
+        }
+      }
+    }
+    // ---- pull one announced chunk, then go back to staging ------------------
+    // (one for one, so that on every rank some CTAs are copying locally while
+    // others are reading over NVLink; once nothing is left to stage, the rest
+    // is pulled in order with blocking waits)
+    bool pulled = false;
+    while (si < plan.n_pull && !(pulled && so < plan.n_stage)) {
+      const int64_t off = plan.pl_off[si], bytes = plan.pl_bytes[si];
+      const int64_t K = ExchangeChunkCount(bytes, G, C);
+      int64_t lo, hi;
+      my_range(off, bytes, b, G, &lo, &hi);
+      const int64_t clo = lo + ki * C, chi = min(hi, clo + C);
+      char* dst = static_cast<char*>(plan.pl_dst[si]);
+      if (dst != nullptr && clo < chi) {
+        const int sig = plan.pl_sig[si];
+        const uint32_t* f = ctx.flags_local + sig * SYMM_MAX_BLOCKS + b;
+        const uint32_t want = ctx.epoch + static_cast<uint32_t>(plan.pl_wait[si]) +
+                              static_cast<uint32_t>(ki) + 1u;
+        if (threadIdx.x == 0)
+          s_ready = static_cast<int32_t>(ld_acquire_sys(f) - want) >= 0;
+        __syncthreads();
+        const bool ready = s_ready != 0;
+        __syncthreads();  // s_ready is rewritten by the next check
+        if (!ready) {
+          if (so < plan.n_stage) break;  // stage more first, look again afterwards
+          if (!wait_word(ctx, f, want, sig, 3, b)) return;
+        }
+        copy_bytes<8>(ctx.peers[plan.pl_src[si]] + off + clo, true, nullptr, false, dst + clo,
+                      chi - clo);
+        pulled = true;
+      }
+      if (++ki == K) {
+        ki = 0;
+        ++si;
+      }
+    }
+    if (so >= plan.n_stage && si >= plan.n_pull) break;
+  }
+
+  if (sync.credit_post != 0) {
+    // The last CTA of this rank to get here tells every peer that this
+    // launch no longer reads anybody's region.
     __syncthreads();
-    plan.n_out = inl.n_out;
-    plan.out_src = s_out_src;
-    plan.out_staging_off = s_out_off;
-    plan.out_bytes = s_out_bytes;
-    plan.out_dst_rank = s_out_rank;
-    plan.n_in = inl.n_in;
-    plan.in_dst = s_in_dst;
-    plan.in_staging_off = s_in_off;
-    plan.in_bytes = s_in_bytes;
-  }
-  for (int s = 0; s < plan.n_out; ++s) {
-    const int64_t off = plan.out_staging_off[s], bytes = plan.out_bytes[s];
-    int64_t lo, hi;
-    my_range(off, bytes, b, G, &lo, &hi);
-    if (lo >= hi) continue;
-    const char* src = static_cast<const char*>(plan.out_src[s]) + lo;
-    const int dst_rank = plan.out_dst_rank[s];
-    if (dst_rank >= 0) {
-      copy_bytes(src, ctx.peers[dst_rank] + off + lo, hi - lo, TO_PEER, ctx, off + lo);
-    } else {
-      copy_bytes(src, ctx.local + off + lo, hi - lo,
-                 ctx.mc != nullptr ? TO_ALL_MC : TO_ALL_LOOP, ctx, off + lo);
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const unsigned long long done = atomicAdd(sync.done_counter, 1ull) + 1ull;
+      if (done == sync.done_target) {
+        for (int p = 0; p < ctx.world; ++p)
+          st_release_sys(ctx.flags_peers[p] + CREDIT_BANK + ctx.rank * SYMM_MAX_BLOCKS,
+                         sync.credit_post);
+      }
     }
+  } else {
+    // Nobody rewrites its region before everybody has drained it.
+    cta_barrier(ctx, ctx.epoch + sync.done_epochs, b, 4);
   }
-  if (!cta_barrier(ctx, ctx.epoch + 1, b, 1)) return;
-  for (int s = 0; s < plan.n_in; ++s) {
-    const int64_t off = plan.in_staging_off[s], bytes = plan.in_bytes[s];
-    int64_t lo, hi;
-    my_range(off, bytes, b, G, &lo, &hi);
-    if (lo >= hi) continue;
-    char* dst = static_cast<char*>(plan.in_dst[s]);
-    if (dst == nullptr) continue;
-    copy_bytes(ctx.local + off + lo, dst + lo, hi - lo, LOCAL_COPY, ctx, 0);
-  }
-  // Keep peers from overwriting this staging buffer with their next
-  // exchange before it has been drained.
-  cta_barrier(ctx, ctx.epoch + 2, b, 2);
 }
 
 __global__ void barrier_only_kernel(SymmCtx ctx) {
@@ -99,16 +229,19 @@ __global__ void barrier_only_kernel(SymmCtx ctx) {
 
 }  // namespace
 
-cudaError_t LaunchExchange(const ExchangePlan& plan, int num_ctas,
+cudaError_t LaunchExchange(const ExchangePlan& plan, const ExchangeSync& sync, int num_ctas,
                            const SymmCtx& ctx, cudaStream_t stream,
                            const InlineExchange* inline_plan) {
   if (num_ctas < 1 || num_ctas > SYMM_MAX_BLOCKS) return cudaErrorInvalidValue;
+  if (sync.chunk_bytes < 4096 || (sync.chunk_bytes & 255) != 0) return cudaErrorInvalidValue;
+  if (sync.mc_push && ctx.mc == nullptr) return cudaErrorInvalidValue;
+  if (sync.credit_post != 0 && sync.done_counter == nullptr) return cudaErrorInvalidValue;
   CountKernelLaunches(1);
   static const InlineExchange kNoInline = {};
-  if (inline_plan != nullptr && (inline_plan->n_out > 0 || inline_plan->n_in > 0))
-    exchange_kernel<true><<<num_ctas, THREADS, 0, stream>>>(*inline_plan, plan, ctx);
+  if (inline_plan != nullptr && (inline_plan->n_stage > 0 || inline_plan->n_pull > 0))
+    exchange_kernel<true><<<num_ctas, THREADS, 0, stream>>>(*inline_plan, plan, sync, ctx);
   else
-    exchange_kernel<false><<<num_ctas, THREADS, 0, stream>>>(kNoInline, plan, ctx);
+    exchange_kernel<false><<<num_ctas, THREADS, 0, stream>>>(kNoInline, plan, sync, ctx);
   return cudaGetLastError();
 }
 

@@ -149,63 +149,65 @@ cudaError_t LaunchFusedReducescatter(const void* in, void* out, int64_t count,
 // skips staging and reduces straight out of the peers' tensors. prescale is
 // ignored in that mode: fold it into postscale.
 
-// Generic "push through staging" exchange used by allgather, broadcast and
-// alltoall: phase 1 copies each outbound segment from local tensors into the
-// staging buffer of its destination rank (peer stores, or one multimem.st
-// when a segment goes to everyone), a cross-GPU barrier follows, phase 2
-// copies inbound segments from the local staging buffer into their final
-// tensors. dst_rank[i] = -1 means "all ranks".
+// Exchange kernel behind allgather, broadcast and alltoall ("stage locally,
+// pull remotely"). Every rank copies the data it owes to others from its
+// tensors into its OWN exchange region (a local copy at HBM speed), publishes
+// how far it has got, and every receiver pulls what it needs straight out of
+// the owner's region over NVLink into its final tensor. Data crosses NVLink
+// once and lands in its destination without a second local pass. With
+// multicast a broadcast root instead writes every rank's region at once
+// (multimem.st) and the receivers copy out of their local region.
+//
+// Progress is published per CTA: CTA b cuts its slice of every staged segment
+// into chunks and, after each chunk, stores ctx.epoch + (chunks so far) into
+// flag word [its rank][b] of every peer; CTA b of a receiver pulls chunk k of
+// a segment once that word has reached ctx.epoch + pl_wait + k + 1, so staging
+// and pulling overlap and a receiver waits only for the ranks it reads from
+// (a broadcast is one-way: the root waits for nobody).
+//
+// Region reuse is guarded by credits instead of a trailing barrier: two
+// regions alternate; the last CTA of a launch tells every peer "my launch
+// number s is over" (credit_post), and a launch that is about to overwrite a
+// region first checks that every peer has finished the launch that used it
+// last (credit_wait; normally true already). credit_post == 0 selects a
+// trailing barrier instead (process sets other than the global one).
 struct ExchangePlan {
-  int n_out;
-  const void* const* out_src;     // local source pointers
-  const int64_t* out_staging_off; // byte offset in the destination staging
-  const int64_t* out_bytes;
-  const int32_t* out_dst_rank;
-  int n_in;
-  void* const* in_dst;            // local destination pointers
-  const int64_t* in_staging_off;  // byte offset in the local staging
-  const int64_t* in_bytes;
+  int n_stage;
+  const void* const* st_src;   // local source tensors
+  void* const* st_self;        // also copy to this local destination (null = no)
+  const int64_t* st_off;       // byte offset in the region; < 0: local copy to st_self only
+  const int64_t* st_bytes;
+  int n_pull;
+  void* const* pl_dst;         // local destination tensors
+  const int64_t* pl_off;       // byte offset in the owner's region
+  const int64_t* pl_bytes;
+  const int32_t* pl_src;       // rank whose region holds the data
+  const int32_t* pl_sig;       // rank whose progress counter announces it
+  const int32_t* pl_wait;      // chunks that rank has published before this segment
 };
 // Short plans can ride in the kernel parameters (no descriptor copy).
 constexpr int INLINE_SEGMENTS = 16;
 struct InlineExchange {
-  int n_out, n_in;  // both 0 = not used
-  const void* out_src[INLINE_SEGMENTS];
-  int64_t out_staging_off[INLINE_SEGMENTS];
-  int64_t out_bytes[INLINE_SEGMENTS];
-  int32_t out_dst_rank[INLINE_SEGMENTS];
-  void* in_dst[INLINE_SEGMENTS];
-  int64_t in_staging_off[INLINE_SEGMENTS];
-  int64_t in_bytes[INLINE_SEGMENTS];
+  int n_stage, n_pull;  // both 0 = not used
+  const void* st_src[INLINE_SEGMENTS];
+  void* st_self[INLINE_SEGMENTS];
+  int64_t st_off[INLINE_SEGMENTS];
+  int64_t st_bytes[INLINE_SEGMENTS];
+  void* pl_dst[INLINE_SEGMENTS];
+  int64_t pl_off[INLINE_SEGMENTS];
+  int64_t pl_bytes[INLINE_SEGMENTS];
+  int32_t pl_src[INLINE_SEGMENTS];
+  int32_t pl_sig[INLINE_SEGMENTS];
+  int32_t pl_wait[INLINE_SEGMENTS];
 };
-cudaError_t LaunchExchange(const ExchangePlan& plan, int num_ctas,
-                           const SymmCtx& ctx, cudaStream_t stream,
-                           const InlineExchange* inline_plan = nullptr);
-
-// Pipelined exchange for large rounds: instead of "push everything, barrier,
-// deliver everything", a CTA cuts its slice of every outbound segment into
-// chunks, publishes a running chunk counter to its peers after each chunk, and
-// delivers inbound chunks as soon as their source's counter has reached them,
-// so pushing over NVLink and the local delivery copies overlap. The plan lives
-// in device memory (descriptor ring); in_src_rank / in_wait_base tell where an
-// inbound segment comes from and how many chunks its source CTA has published
-// before it starts on that segment. A launch consumes `done_epochs` barrier
-// epochs: chunk n of a source is published as ctx.epoch + n, the trailing
-// barrier uses ctx.epoch + done_epochs (larger than any chunk count).
-struct PipelinePlan {
-  int n_out;
-  const void* const* out_src;
-  const int64_t* out_staging_off;
-  const int64_t* out_bytes;
-  const int32_t* out_dst_rank;
-  int n_in;
-  void* const* in_dst;
-  const int64_t* in_staging_off;
-  const int64_t* in_bytes;
-  const int32_t* in_src_rank;
-  const int32_t* in_wait_base;
-  int64_t chunk_bytes;
-  uint32_t done_epochs;
+struct ExchangeSync {
+  int64_t chunk_bytes;      // multiple of 256
+  int mc_push;              // staged segments are written to every rank's region (multimem.st)
+  uint32_t done_epochs;     // epochs this launch consumes (> chunks published by any CTA)
+  uint32_t credit_wait;     // 0 = nothing to wait for
+  uint32_t credit_post;     // 0 = end with a barrier instead
+  unsigned long long* done_counter;  // device word counting finished CTAs (monotonic)
+  unsigned long long done_target;    // its value once every CTA of this launch is through
 };
 // Chunks into which every CTA of a launch with `num_ctas` CTAs cuts its slice
 // of a segment of `bytes` bytes (the same number for all CTAs of all ranks; a
@@ -220,8 +222,9 @@ inline int64_t ExchangeChunkCount(int64_t bytes, int num_ctas, int64_t chunk_byt
   int64_t k = (slice + chunk_bytes - 1) / chunk_bytes;
   return k < 1 ? 1 : k;
 }
-cudaError_t LaunchExchangePipelined(const PipelinePlan& plan, int num_ctas,
-                                    const SymmCtx& ctx, cudaStream_t stream);
+cudaError_t LaunchExchange(const ExchangePlan& plan, const ExchangeSync& sync, int num_ctas,
+                           const SymmCtx& ctx, cudaStream_t stream,
+                           const InlineExchange* inline_plan = nullptr);
 
 // Adasum over symmetric memory. Tensors are packed into staging as fp32
 // (prescaled), combined pairwise over log2(world) levels with per-tensor

@@ -1,7 +1,7 @@
 // Broadcast, allgather and alltoall on device tensors, all expressed as
-// segment lists for the exchange kernel: outbound segments go from local
-// tensors into the staging buffer of their destination rank(s), inbound
-// segments go from the local staging buffer into the final tensors.
+// segment lists for the exchange kernel: staged segments go from local
+// tensors into this rank's exchange region, pulled segments go from the
+// owner's region (over NVLink) straight into the final tensors.
 #include <algorithm>
 #include <cstring>
 
@@ -15,81 +15,122 @@ namespace {
 constexpr int64_t STAGING_ALIGN = 256;
 }
 
-void GpuOps::LaunchExchangeSegments(const std::vector<OutSeg>& out,
-                                    const std::vector<InSeg>& in, SymmSet& set,
+// One launch of the exchange kernel. Every rank derives the same numbers from
+// the round's block list: the grid size, the chunks per block, how many chunks
+// a source has published before each of its blocks, and the epochs the launch
+// consumes (the largest chunk total of any rank, plus one for a final barrier).
+void GpuOps::LaunchExchangeSegments(const std::vector<StageSeg>& stage,
+                                    const std::vector<PullSeg>& pull, SymmSet& set,
                                     int64_t round_bytes,
-                                    const std::vector<RoundBlock>& round) {
-  if (exchange_pipeline_ && set.world > 1 && round_bytes >= (8 << 20) &&
-      LaunchExchangePipelined(out, in, set, round_bytes, round))
-    return;
-  const size_t no = out.size(), ni = in.size();
+                                    const std::vector<RoundBlock>& round, bool mc_push) {
+  const size_t ns = stage.size(), np = pull.size();
   // The grid size must be the same on every rank (CTA b meets CTA b of its
   // peers), so it is derived from the bytes of the whole round, which all
   // ranks know, not from this rank's share of them.
-  const int64_t bytes = round_bytes;
+  const int ctas = PickCtas(round_bytes);
+  const int64_t chunk = exchange_chunk_bytes_ / 256 * 256;
+  std::vector<int64_t> published(set.world, 0);  // chunks per source so far
+  std::vector<int64_t> before(round.size(), 0);  // ... before each block
+  for (size_t i = 0; i < round.size(); ++i) {
+    const int src = round[i].src_rank;
+    before[i] = published[src];
+    published[src] += kern::ExchangeChunkCount(round[i].bytes, ctas, chunk);
+  }
+  const int64_t most = *std::max_element(published.begin(), published.end());
+  if (most + 1 > (int64_t(1) << 30))
+    throw std::runtime_error("exchange round needs too many chunks");
+
+  kern::ExchangeSync sync;
+  std::memset(&sync, 0, sizeof(sync));
+  sync.chunk_bytes = chunk;
+  sync.mc_push = mc_push ? 1 : 0;
+  sync.done_epochs = static_cast<uint32_t>(most + 1);
+  int64_t region_off = 0;
+  if (set.xchg_bytes > 0) {
+    // Alternate between the two regions; launch s may overwrite what launch
+    // s - 2 left there once every peer has finished that launch.
+    const uint32_t s = ++set.xchg_seq;
+    region_off = set.xchg_off[s & 1];
+    sync.credit_wait = s > 2 ? s - 2 : 0;
+    sync.credit_post = s;
+    sync.done_counter = xchg_done_counter_;
+    xchg_done_base_ += static_cast<unsigned long long>(ctas);
+    sync.done_target = xchg_done_base_;
+  }
+
   kern::ExchangePlan plan;
   std::memset(&plan, 0, sizeof(plan));
   cudaError_t err;
-  if (no <= kern::INLINE_SEGMENTS && ni <= kern::INLINE_SEGMENTS) {
+  if (inline_descriptors_ && ns <= kern::INLINE_SEGMENTS && np <= kern::INLINE_SEGMENTS &&
+      (ns || np)) {
     // Short plan: carried in the kernel parameters.
     kern::InlineExchange inl;
-    inl.n_out = static_cast<int>(no);
-    inl.n_in = static_cast<int>(ni);
-    for (size_t i = 0; i < no; ++i) {
-      inl.out_src[i] = out[i].src;
-      inl.out_staging_off[i] = out[i].staging_off;
-      inl.out_bytes[i] = out[i].bytes;
-      inl.out_dst_rank[i] = out[i].dst;
+    inl.n_stage = static_cast<int>(ns);
+    inl.n_pull = static_cast<int>(np);
+    for (size_t i = 0; i < ns; ++i) {
+      inl.st_src[i] = stage[i].src;
+      inl.st_self[i] = stage[i].self_dst;
+      inl.st_off[i] = stage[i].off;
+      inl.st_bytes[i] = stage[i].bytes;
     }
-    for (size_t i = 0; i < ni; ++i) {
-      inl.in_dst[i] = in[i].dst;
-      inl.in_staging_off[i] = in[i].staging_off;
-      inl.in_bytes[i] = in[i].bytes;
+    for (size_t i = 0; i < np; ++i) {
+      inl.pl_dst[i] = pull[i].dst;
+      inl.pl_off[i] = pull[i].off;
+      inl.pl_bytes[i] = pull[i].bytes;
+      inl.pl_src[i] = pull[i].src_rank;
+      inl.pl_sig[i] = pull[i].sig_rank;
+      inl.pl_wait[i] = static_cast<int32_t>(before[pull[i].block]);
     }
-    if (no == 0 && ni == 0) inl.n_out = 0;
-    kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH);
-    // An empty inline plan would read as "not used": give the kernel the
-    // (equally empty) device plan in that case.
-    err = kern::LaunchExchange(plan, PickCtas(bytes), ctx, stream_,
-                               (no || ni) ? &inl : nullptr);
+    kern::SymmCtx ctx = MakeCtx(set, sync.done_epochs, region_off);
+    err = kern::LaunchExchange(plan, sync, ctas, ctx, stream_, &inl);
   } else {
     DescriptorRing::Slot slot = ring_.Acquire();
     const void** d_src;
-    int64_t *d_ooff, *d_obytes, *d_ioff, *d_ibytes;
-    int32_t* d_dst_rank;
-    void** d_dst;
-    const void** h_src = slot.Alloc<const void*>(no + 1, &d_src);
-    int64_t* h_ooff = slot.Alloc<int64_t>(no + 1, &d_ooff);
-    int64_t* h_obytes = slot.Alloc<int64_t>(no + 1, &d_obytes);
-    int32_t* h_dst_rank = slot.Alloc<int32_t>(no + 1, &d_dst_rank);
-    void** h_dst = slot.Alloc<void*>(ni + 1, &d_dst);
-    int64_t* h_ioff = slot.Alloc<int64_t>(ni + 1, &d_ioff);
-    int64_t* h_ibytes = slot.Alloc<int64_t>(ni + 1, &d_ibytes);
-    if (!h_src || !h_ooff || !h_obytes || !h_dst_rank || !h_dst || !h_ioff || !h_ibytes)
+    void **d_self, **d_dst;
+    int64_t *d_soff, *d_sbytes, *d_poff, *d_pbytes;
+    int32_t *d_psrc, *d_psig, *d_pwait;
+    const void** h_src = slot.Alloc<const void*>(ns + 1, &d_src);
+    void** h_self = slot.Alloc<void*>(ns + 1, &d_self);
+    int64_t* h_soff = slot.Alloc<int64_t>(ns + 1, &d_soff);
+    int64_t* h_sbytes = slot.Alloc<int64_t>(ns + 1, &d_sbytes);
+    void** h_dst = slot.Alloc<void*>(np + 1, &d_dst);
+    int64_t* h_poff = slot.Alloc<int64_t>(np + 1, &d_poff);
+    int64_t* h_pbytes = slot.Alloc<int64_t>(np + 1, &d_pbytes);
+    int32_t* h_psrc = slot.Alloc<int32_t>(np + 1, &d_psrc);
+    int32_t* h_psig = slot.Alloc<int32_t>(np + 1, &d_psig);
+    int32_t* h_pwait = slot.Alloc<int32_t>(np + 1, &d_pwait);
+    if (!h_src || !h_self || !h_soff || !h_sbytes || !h_dst || !h_poff || !h_pbytes ||
+        !h_psrc || !h_psig || !h_pwait)
       throw std::runtime_error("exchange plan does not fit a descriptor slot");
-    for (size_t i = 0; i < no; ++i) {
-      h_src[i] = out[i].src;
-      h_ooff[i] = out[i].staging_off;
-      h_obytes[i] = out[i].bytes;
-      h_dst_rank[i] = out[i].dst;
+    for (size_t i = 0; i < ns; ++i) {
+      h_src[i] = stage[i].src;
+      h_self[i] = stage[i].self_dst;
+      h_soff[i] = stage[i].off;
+      h_sbytes[i] = stage[i].bytes;
     }
-    for (size_t i = 0; i < ni; ++i) {
-      h_dst[i] = in[i].dst;
-      h_ioff[i] = in[i].staging_off;
-      h_ibytes[i] = in[i].bytes;
+    for (size_t i = 0; i < np; ++i) {
+      h_dst[i] = pull[i].dst;
+      h_poff[i] = pull[i].off;
+      h_pbytes[i] = pull[i].bytes;
+      h_psrc[i] = pull[i].src_rank;
+      h_psig[i] = pull[i].sig_rank;
+      h_pwait[i] = static_cast<int32_t>(before[pull[i].block]);
     }
     ring_.Commit(slot, stream_);
-    plan.n_out = static_cast<int>(no);
-    plan.out_src = d_src;
-    plan.out_staging_off = d_ooff;
-    plan.out_bytes = d_obytes;
-    plan.out_dst_rank = d_dst_rank;
-    plan.n_in = static_cast<int>(ni);
-    plan.in_dst = d_dst;
-    plan.in_staging_off = d_ioff;
-    plan.in_bytes = d_ibytes;
-    kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH);
-    err = kern::LaunchExchange(plan, PickCtas(bytes), ctx, stream_);
+    plan.n_stage = static_cast<int>(ns);
+    plan.st_src = d_src;
+    plan.st_self = d_self;
+    plan.st_off = d_soff;
+    plan.st_bytes = d_sbytes;
+    plan.n_pull = static_cast<int>(np);
+    plan.pl_dst = d_dst;
+    plan.pl_off = d_poff;
+    plan.pl_bytes = d_pbytes;
+    plan.pl_src = d_psrc;
+    plan.pl_sig = d_psig;
+    plan.pl_wait = d_pwait;
+    kern::SymmCtx ctx = MakeCtx(set, sync.done_epochs, region_off);
+    err = kern::LaunchExchange(plan, sync, ctas, ctx, stream_);
     ring_.Release(slot, stream_);
   }
   if (err != cudaSuccess)
@@ -97,92 +138,12 @@ void GpuOps::LaunchExchangeSegments(const std::vector<OutSeg>& out,
                              cudaGetErrorString(err));
 }
 
-// Plan for the pipelined kernel. Every rank derives the same numbers from the
-// round's block list: the grid size, the chunks per block, how many chunks a
-// source has published before each of its blocks, and the epochs the launch
-// consumes (the largest chunk total of any rank, plus one for the final barrier).
-// Returns false (nothing launched) when the plan does not fit a descriptor slot.
-bool GpuOps::LaunchExchangePipelined(const std::vector<OutSeg>& out,
-                                     const std::vector<InSeg>& in, SymmSet& set,
-                                     int64_t round_bytes,
-                                     const std::vector<RoundBlock>& round) {
-  const size_t no = out.size(), ni = in.size();
-  const int ctas = PickCtas(round_bytes);
-  const int64_t chunk = exchange_chunk_bytes_ / 256 * 256;
-  std::vector<int64_t> published(set.world, 0);   // chunks per source so far
-  std::vector<int64_t> before(round.size(), 0);   // ... before each block
-  for (size_t i = 0; i < round.size(); ++i) {
-    const int src = round[i].src_rank;
-    if (src < 0 || src >= set.world) return false;
-    before[i] = published[src];
-    published[src] += kern::ExchangeChunkCount(round[i].bytes, ctas, chunk);
-  }
-  const int64_t most = *std::max_element(published.begin(), published.end());
-  if (most + 1 > (int64_t(1) << 30)) return false;
-
-  DescriptorRing::Slot slot = ring_.Acquire();
-  const void** d_src;
-  int64_t *d_ooff, *d_obytes, *d_ioff, *d_ibytes;
-  int32_t *d_dst_rank, *d_isrc, *d_iwait;
-  void** d_dst;
-  const void** h_src = slot.Alloc<const void*>(no + 1, &d_src);
-  int64_t* h_ooff = slot.Alloc<int64_t>(no + 1, &d_ooff);
-  int64_t* h_obytes = slot.Alloc<int64_t>(no + 1, &d_obytes);
-  int32_t* h_dst_rank = slot.Alloc<int32_t>(no + 1, &d_dst_rank);
-  void** h_dst = slot.Alloc<void*>(ni + 1, &d_dst);
-  int64_t* h_ioff = slot.Alloc<int64_t>(ni + 1, &d_ioff);
-  int64_t* h_ibytes = slot.Alloc<int64_t>(ni + 1, &d_ibytes);
-  int32_t* h_isrc = slot.Alloc<int32_t>(ni + 1, &d_isrc);
-  int32_t* h_iwait = slot.Alloc<int32_t>(ni + 1, &d_iwait);
-  if (!h_src || !h_ooff || !h_obytes || !h_dst_rank || !h_dst || !h_ioff || !h_ibytes ||
-      !h_isrc || !h_iwait) {
-    // Nothing was copied or launched: hand the slot back unused.
-    ring_.Release(slot, stream_);
-    return false;
-  }
-  for (size_t i = 0; i < no; ++i) {
-    h_src[i] = out[i].src;
-    h_ooff[i] = out[i].staging_off;
-    h_obytes[i] = out[i].bytes;
-    h_dst_rank[i] = out[i].dst;
-  }
-  for (size_t i = 0; i < ni; ++i) {
-    h_dst[i] = in[i].dst;
-    h_ioff[i] = in[i].staging_off;
-    h_ibytes[i] = in[i].bytes;
-    h_isrc[i] = in[i].src_rank;
-    h_iwait[i] = static_cast<int32_t>(before[in[i].block]);
-  }
-  ring_.Commit(slot, stream_);
-  kern::PipelinePlan plan;
-  std::memset(&plan, 0, sizeof(plan));
-  plan.n_out = static_cast<int>(no);
-  plan.out_src = d_src;
-  plan.out_staging_off = d_ooff;
-  plan.out_bytes = d_obytes;
-  plan.out_dst_rank = d_dst_rank;
-  plan.n_in = static_cast<int>(ni);
-  plan.in_dst = d_dst;
-  plan.in_staging_off = d_ioff;
-  plan.in_bytes = d_ibytes;
-  plan.in_src_rank = d_isrc;
-  plan.in_wait_base = d_iwait;
-  plan.chunk_bytes = chunk;
-  plan.done_epochs = static_cast<uint32_t>(most + 1);
-  kern::SymmCtx ctx = MakeCtx(set, plan.done_epochs);
-  cudaError_t err = kern::LaunchExchangePipelined(plan, ctas, ctx, stream_);
-  ring_.Release(slot, stream_);
-  if (err != cudaSuccess)
-    throw std::runtime_error(std::string("pipelined exchange launch failed: ") +
-                             cudaGetErrorString(err));
-  return true;
-}
-
 // Every rank builds the same global list of "blocks" (source rank, bytes,
-// who receives it); blocks are laid out in the staging buffer in order and
-// processed in rounds that fit its capacity. A block larger than the
-// capacity is cut into parts first. All of this is deterministic, so the
-// ranks agree on rounds and offsets without talking.
+// who receives it). A block that somebody else needs is staged in its source
+// rank's exchange region; blocks are laid out there in order and processed in
+// rounds that fit the region. A block larger than half the region is cut into
+// parts first. All of this is deterministic, so the ranks agree on rounds and
+// offsets without talking.
 namespace {
 struct Block {
   int src_rank;        // set rank that owns the data
@@ -193,13 +154,13 @@ struct Block {
 };
 }  // namespace
 
-static void RunBlocks(GpuOps* self, std::vector<Block>& blocks, SymmSet& set,
-                      const std::function<void(const std::vector<GpuOps::OutSeg>&,
-                                               const std::vector<GpuOps::InSeg>&,
+static void RunBlocks(std::vector<Block>& blocks, SymmSet& set, bool mc_push,
+                      const std::function<void(const std::vector<GpuOps::StageSeg>&,
+                                               const std::vector<GpuOps::PullSeg>&,
                                                int64_t,
                                                const std::vector<GpuOps::RoundBlock>&)>& launch) {
-  (void)self;
-  const int64_t cap = static_cast<int64_t>(set.data_bytes);
+  const int64_t cap = set.xchg_bytes > 0 ? set.xchg_bytes : static_cast<int64_t>(set.data_bytes);
+  const int me = set.rank;
   // Split oversized blocks.
   std::vector<Block> parts;
   for (auto& b : blocks) {
@@ -217,37 +178,39 @@ static void RunBlocks(GpuOps* self, std::vector<Block>& blocks, SymmSet& set,
   }
   size_t next = 0;
   while (next < parts.size()) {
-    std::vector<GpuOps::OutSeg> out;
-    std::vector<GpuOps::InSeg> in;
-    // Offsets are per destination buffer: a block for everybody advances all
-    // cursors, a point-to-point block only its destination's.
+    std::vector<GpuOps::StageSeg> stage;
+    std::vector<GpuOps::PullSeg> pull;
+    // Offsets are per source region. With a multicast push the source writes
+    // the same offset of everybody's region, which is the same bookkeeping.
     std::vector<int64_t> cursor(set.world, 0);
     size_t n = 0;
     int64_t round_bytes = 0;
     std::vector<GpuOps::RoundBlock> round;
     while (next + n < parts.size() && n < 4096) {
       const Block& b = parts[next + n];
-      int64_t padded = RoundUp(b.bytes, STAGING_ALIGN);
-      int64_t off;
-      if (b.dst_rank < 0) {
-        off = *std::max_element(cursor.begin(), cursor.end());
-        if (off + padded > cap) break;
-        for (auto& c : cursor) c = off + padded;
+      const bool remote = set.world > 1 && (b.dst_rank < 0 || b.dst_rank != b.src_rank);
+      const bool wanted = (b.dst_rank < 0 || b.dst_rank == me) && b.dst != nullptr;
+      if (!remote) {
+        // Data a rank keeps for itself: a local copy, no region space.
+        if (b.src_rank == me && wanted) stage.push_back({b.src, b.dst, -1, b.bytes});
       } else {
-        off = cursor[b.dst_rank];
+        const int64_t padded = RoundUp(b.bytes, STAGING_ALIGN);
+        const int64_t off = cursor[b.src_rank];
         if (off + padded > cap) break;
-        cursor[b.dst_rank] = off + padded;
+        cursor[b.src_rank] = off + padded;
+        if (b.src_rank == me) {
+          stage.push_back({b.src, wanted ? b.dst : nullptr, off, b.bytes});
+        } else if (wanted) {
+          pull.push_back({b.dst, off, b.bytes, mc_push ? me : b.src_rank, b.src_rank,
+                          static_cast<int32_t>(round.size())});
+        }
+        round.push_back({b.src_rank, b.bytes});
       }
-      if (b.src_rank == set.rank)
-        out.push_back({b.src, off, b.bytes, b.dst_rank});
-      if ((b.dst_rank < 0 || b.dst_rank == set.rank) && b.dst != nullptr)
-        in.push_back({b.dst, off, b.bytes, b.src_rank, static_cast<int32_t>(round.size())});
-      round.push_back({b.src_rank, b.bytes});
       round_bytes += b.bytes;
       ++n;
     }
     if (n == 0) throw std::runtime_error("exchange block exceeds staging capacity");
-    launch(out, in, round_bytes, round);
+    launch(stage, pull, round_bytes, round);
     next += n;
   }
 }
@@ -269,10 +232,15 @@ Status GpuOps::SymmBroadcast(std::vector<TensorTableEntry>& entries,
     b.bytes = e.size_bytes();
     blocks.push_back(b);
   }
-  RunBlocks(this, blocks, set,
-            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i, int64_t round_bytes,
-                const std::vector<RoundBlock>& round) {
-              LaunchExchangeSegments(o, i, set, round_bytes, round);
+  // From three ranks on the root writes everybody's region at once through
+  // the multicast mapping (its NVLink egress is S instead of (N-1) S) and the
+  // receivers copy out of their own region; with two ranks the peer pulls.
+  // (Only with the credit-guarded regions: nobody else ever writes those.)
+  const bool mc_push = set.mc != nullptr && set.world >= 3 && set.xchg_bytes > 0;
+  RunBlocks(blocks, set, mc_push,
+            [&](const std::vector<StageSeg>& o, const std::vector<PullSeg>& i,
+                int64_t round_bytes, const std::vector<RoundBlock>& round) {
+              LaunchExchangeSegments(o, i, set, round_bytes, round, mc_push);
             });
   tl.ActivityEndAll(entries);
   return Complete(entries);
@@ -311,10 +279,10 @@ Status GpuOps::SymmAllgather(std::vector<TensorTableEntry>& entries,
     }
   }
   tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
-  RunBlocks(this, blocks, set,
-            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i, int64_t round_bytes,
-                const std::vector<RoundBlock>& round) {
-              LaunchExchangeSegments(o, i, set, round_bytes, round);
+  RunBlocks(blocks, set, false,
+            [&](const std::vector<StageSeg>& o, const std::vector<PullSeg>& i,
+                int64_t round_bytes, const std::vector<RoundBlock>& round) {
+              LaunchExchangeSegments(o, i, set, round_bytes, round, false);
             });
   tl.ActivityEndAll(entries);
   return Complete(entries);
@@ -369,10 +337,10 @@ Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries,
     }
   }
   tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
-  RunBlocks(this, blocks, set,
-            [&](const std::vector<OutSeg>& o, const std::vector<InSeg>& i, int64_t round_bytes,
-                const std::vector<RoundBlock>& round) {
-              LaunchExchangeSegments(o, i, set, round_bytes, round);
+  RunBlocks(blocks, set, false,
+            [&](const std::vector<StageSeg>& o, const std::vector<PullSeg>& i,
+                int64_t round_bytes, const std::vector<RoundBlock>& round) {
+              LaunchExchangeSegments(o, i, set, round_bytes, round, false);
             });
   tl.ActivityEndAll(entries);
   return Complete(entries);

@@ -102,6 +102,14 @@ struct SymmSet {
   int64_t oneshot_off[2] = {0, 0};
   int64_t oneshot_bytes = 0;
   uint32_t oneshot_count = 0;
+  // Global set only: two regions that the exchange kernel (allgather,
+  // broadcast, alltoall) alternates between. A rank stages outbound data in
+  // its own region; reuse is guarded by per-launch credits (see
+  // kern::ExchangePlan), so these launches need no trailing barrier. Other
+  // sets stage in the general area and end with a barrier.
+  int64_t xchg_off[2] = {0, 0};
+  int64_t xchg_bytes = 0;
+  uint32_t xchg_seq = 0;  // exchange launches so far (credit numbers)
 };
 
 class NcclOps;
@@ -115,17 +123,18 @@ public:
                  const Response& response, ProcessSet& ps) override;
   void Shutdown() override;
 
-  // Segments handed to the exchange kernel.
-  struct OutSeg { const void* src; int64_t staging_off; int64_t bytes; int32_t dst; };
-  struct InSeg {
+  // Segments handed to the exchange kernel (see kern::ExchangePlan).
+  struct StageSeg { const void* src; void* self_dst; int64_t off; int64_t bytes; };
+  struct PullSeg {
     void* dst;
-    int64_t staging_off;
+    int64_t off;
     int64_t bytes;
-    int32_t src_rank;  // set rank that writes this segment
+    int32_t src_rank;  // set rank whose region holds the data
+    int32_t sig_rank;  // set rank whose progress counter announces it
     int32_t block;     // index into the round's block list (RoundBlock)
   };
-  // Every block of one exchange round, in the order all ranks process them
-  // (what the pipelined kernel's chunk counters are derived from).
+  // Every staged block of one exchange round, in the order all ranks process
+  // them (what the chunk counters of the kernel are derived from).
   struct RoundBlock { int32_t src_rank; int64_t bytes; };
 
   // Device-time record of one executed response (HOROVOD_GPU_OP_TIMING=1).
@@ -181,13 +190,13 @@ private:
   // (and launches nothing) when the entries do not qualify.
   bool TryInplaceAllreduce(std::vector<TensorTableEntry>& entries,
                            const Response& response, SymmSet& set, Status* status);
-  // One exchange-kernel launch for the given segment lists.
-  void LaunchExchangeSegments(const std::vector<OutSeg>& out,
-                              const std::vector<InSeg>& in, SymmSet& set,
-                              int64_t round_bytes, const std::vector<RoundBlock>& round);
-  bool LaunchExchangePipelined(const std::vector<OutSeg>& out, const std::vector<InSeg>& in,
-                               SymmSet& set, int64_t round_bytes,
-                               const std::vector<RoundBlock>& round);
+  // One exchange-kernel launch for the given segment lists. `use_region`:
+  // which of the set's exchange regions the round was laid out for (-1: the
+  // general staging area, trailing barrier).
+  void LaunchExchangeSegments(const std::vector<StageSeg>& stage,
+                              const std::vector<PullSeg>& pull, SymmSet& set,
+                              int64_t round_bytes, const std::vector<RoundBlock>& round,
+                              bool mc_push);
 
   GlobalState& state_;
   std::shared_ptr<DoneEventPool> events_;
@@ -214,8 +223,9 @@ private:
   unsigned long long* tile_counter_ = nullptr;  // device word, see kern::TileSchedule
   unsigned long long tile_base_ = 0;
   int64_t dynamic_min_bytes_ = 0;
-  bool exchange_pipeline_ = false;     // HOROVOD_EXCHANGE_PIPELINE=1
-  int64_t exchange_chunk_bytes_ = 64 << 10;
+  int64_t exchange_chunk_bytes_ = 256 << 10;  // HOROVOD_EXCHANGE_CHUNK_KB
+  unsigned long long* xchg_done_counter_ = nullptr;  // device word, see kern::ExchangeSync
+  unsigned long long xchg_done_base_ = 0;
   unsigned long long* trace_host_ = nullptr;  // mapped pinned, HOROVOD_KERNEL_TRACE=1
   unsigned long long* trace_dev_ = nullptr;
   std::map<int32_t, std::unique_ptr<SymmSet>> sets_;

@@ -154,8 +154,11 @@ void GpuOps::EnsureDevice(int device) {
   HVD_CUDA(cudaMemset(tile_counter_, 0, sizeof(unsigned long long)));
   tile_base_ = 0;
   dynamic_min_bytes_ = EnvInt("HOROVOD_DYNAMIC_TILES_MIN_BYTES", 8 << 20);
-  exchange_pipeline_ = EnvBool("HOROVOD_EXCHANGE_PIPELINE", false);
-  exchange_chunk_bytes_ = std::max<int64_t>(4096, EnvInt("HOROVOD_EXCHANGE_CHUNK_KB", 64) << 10);
+  exchange_chunk_bytes_ =
+      std::max<int64_t>(64, EnvInt("HOROVOD_EXCHANGE_CHUNK_KB", 256)) << 10;
+  HVD_CUDA(cudaMalloc(reinterpret_cast<void**>(&xchg_done_counter_), sizeof(unsigned long long)));
+  HVD_CUDA(cudaMemset(xchg_done_counter_, 0, sizeof(unsigned long long)));
+  xchg_done_base_ = 0;
   if (EnvBool("HOROVOD_KERNEL_TRACE", false)) {
     HVD_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&trace_host_),
                            kern::KERNEL_TRACE_SLOTS * sizeof(unsigned long long),
@@ -178,7 +181,7 @@ void GpuOps::EnsureArena(ProcessSet& ps) {
   }
   if (state_.config.rank == 0)
     HVD_LOG(INFO) << "GPU topology: " << DiscoverTopology().Summary();
-  size_t mb = static_cast<size_t>(EnvInt(HVD_ENV_SYMM_BUFFER_MB, 512));
+  size_t mb = static_cast<size_t>(EnvInt(HVD_ENV_SYMM_BUFFER_MB, 1024));
   // The token doubles as socket-name salt: distinct per job and per init.
   uint64_t token = state_.config.token ^ 0x9e3779b97f4a7c15ull;
   size_t heap_mb = static_cast<size_t>(EnvInt("HOROVOD_SYMM_HEAP_MB", 2048));
@@ -222,6 +225,19 @@ SymmSet* GpuOps::GetSymmSet(ProcessSet& ps) {
       set->oneshot_bytes = region;
       set->oneshot_off[0] = static_cast<int64_t>(set->data_bytes);
       set->oneshot_off[1] = static_cast<int64_t>(set->data_bytes) + region;
+    }
+  }
+  // A quarter of what is left for each of the two exchange regions (again
+  // carved out for every set, used by the global one).
+  {
+    const int64_t xr = static_cast<int64_t>(set->data_bytes) / 4 / 4096 * 4096;
+    if (xr >= (8 << 20)) {
+      set->data_bytes -= static_cast<size_t>(2 * xr);
+      if (ps.id == 0) {
+        set->xchg_bytes = xr;
+        set->xchg_off[0] = static_cast<int64_t>(set->data_bytes);
+        set->xchg_off[1] = static_cast<int64_t>(set->data_bytes) + xr;
+      }
     }
   }
   const size_t flag_words = static_cast<size_t>(SYMM_FLAG_BANKS) * SYMM_MAX_RANKS *
@@ -504,6 +520,8 @@ void GpuOps::Shutdown() {
   status_host_ = nullptr;
   if (tile_counter_) cudaFree(tile_counter_);
   tile_counter_ = nullptr;
+  if (xchg_done_counter_) cudaFree(xchg_done_counter_);
+  xchg_done_counter_ = nullptr;
   if (trace_host_) cudaFreeHost(trace_host_);
   trace_host_ = nullptr;
   trace_dev_ = nullptr;

@@ -544,6 +544,19 @@ PYBIND11_MODULE(_C, m) {
   m.def("join_async", &JoinAsync);
   m.def("poll", &Poll);
   m.def("wait_and_clear", &WaitAndClear);
+  m.def("runtime_params", []() {
+    // The knob values in effect right now (the autotuner may have moved them).
+    py::dict d;
+    if (!hvd_is_initialized()) return d;
+    const ParameterManager& pm = hvd_state().parameter_manager;
+    d["fusion_threshold_bytes"] = pm.TensorFusionThresholdBytes();
+    d["cycle_time_ms"] = pm.CycleTimeMs();
+    d["cache_enabled"] = pm.CacheEnabled();
+    d["hierarchical_allreduce"] = pm.HierarchicalAllreduce();
+    d["hierarchical_allgather"] = pm.HierarchicalAllgather();
+    d["autotune"] = pm.IsAutoTuning();
+    return d;
+  }, "Fusion threshold, cycle time and the other tunables as they are in effect now.");
 
   BindGpuDiagnostics(m);
   BindTesting(m);

@@ -24,6 +24,7 @@ from horovod_b200.torch.mpi_ops import (Adasum, Average, Max, Min, Product, Sum,
                                         local_rank, local_size, mpi_built, mpi_enabled,
                                         mpi_threads_supported, nccl_built, poll, rank,
                                         reducescatter, reducescatter_async, rocm_built,
+                                        runtime_params,
                                         shutdown, size, sparse_allreduce_async,
                                         start_timeline, stop_timeline, symmetric_empty,
                                         synchronize, topology)

@@ -52,6 +52,7 @@ ccl_built = _basics.ccl_built
 cuda_built = _basics.cuda_built
 rocm_built = _basics.rocm_built
 gpu_backend = _basics.gpu_backend
+runtime_params = _basics.runtime_params
 topology = _basics.topology
 
 

@@ -343,29 +343,33 @@ def test_asymmetric_use_of_symmetric_memory_is_reported():
     assert out[1][0], out
 
 
-def _pipelined_exchange(rank, size):
-    os.environ["HOROVOD_EXCHANGE_PIPELINE"] = "1"
-    os.environ["HOROVOD_EXCHANGE_CHUNK_KB"] = "16"
+def _exchange_large(rank, size):
+    """Large and mixed exchange rounds with small chunks, so every launch
+    publishes many chunk counters, and enough launches in a row that both
+    exchange regions are reused several times (credit waits)."""
+    os.environ["HOROVOD_EXCHANGE_CHUNK_KB"] = "64"
     os.environ["HOROVOD_SPIN_TIMEOUT_MS"] = "5000"
     import horovod_b200.torch as hvd
     hvd.init()
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     n = (3 << 20) + 5  # 12 MB per rank and a ragged tail
-    # allgather with a different dim 0 on every rank
-    x = _inputs(rank, n + rank * 1001, torch.float32).to(dev)
-    got = hvd.allgather(x, name="pipe.ag")
-    exp = torch.cat([_inputs(r, n + r * 1001, torch.float32) for r in range(size)])
-    ok = torch.equal(got.cpu(), exp)
-    # broadcast from the last rank
-    b = _inputs(rank, 5 * n, torch.float32).to(dev)
-    hvd.broadcast_(b, root_rank=size - 1, name="pipe.bc")
-    ok = ok and torch.equal(b.cpu(), _inputs(size - 1, 5 * n, torch.float32))
+    ok = True
+    for it in range(3):
+        # allgather with a different dim 0 on every rank
+        x = _inputs(rank + it, n + rank * 1001, torch.float32).to(dev)
+        got = hvd.allgather(x, name="xl.ag")
+        exp = torch.cat([_inputs(r + it, n + r * 1001, torch.float32) for r in range(size)])
+        ok = ok and torch.equal(got.cpu(), exp)
+        # broadcast from the last rank
+        b = _inputs(rank + it, 5 * n, torch.float32).to(dev)
+        hvd.broadcast_(b, root_rank=size - 1, name="xl.bc")
+        ok = ok and torch.equal(b.cpu(), _inputs(size - 1 + it, 5 * n, torch.float32))
     # uneven alltoall
     splits = torch.tensor([(rank + p) % 3 + 1 for p in range(size)], dtype=torch.int32)
     rows = int(splits.sum())
     send = _inputs(rank + 40, rows * (1 << 20), torch.float32).view(rows, 1 << 20).to(dev)
-    recv, rsplits = hvd.alltoall(send, splits=splits, name="pipe.a2a")
+    recv, rsplits = hvd.alltoall(send, splits=splits, name="xl.a2a")
     pieces = []
     for r in range(size):
         s = [(r + p) % 3 + 1 for p in range(size)]
@@ -373,17 +377,37 @@ def _pipelined_exchange(rank, size):
         off = sum(s[:rank])
         pieces.append(full[off:off + s[rank]])
     ok = ok and torch.equal(recv.cpu(), torch.cat(pieces))
-    # a small op in between still takes the two-phase kernel
-    small = hvd.allgather(torch.full((3,), float(rank), device=dev), name="pipe.small")
+    # small tensors (20-60 KB) fused with 12 MB ones in one response, on
+    # storage that is only 4-byte aligned
+    counts = [5003, 3 << 20, 15001, (3 << 20) + 3, 9999]
+    base = [_inputs(rank * 7 + i, c + 1, torch.float32).to(dev) for i, c in enumerate(counts)]
+    handles = [hvd.allgather_async(t[1:], name="xl.mix.%d" % i) for i, t in enumerate(base)]
+    for i, (h, c) in enumerate(zip(handles, counts)):
+        got = hvd.synchronize(h)
+        exp = torch.cat([_inputs(r * 7 + i, c + 1, torch.float32)[1:] for r in range(size)])
+        ok = ok and torch.equal(got.cpu(), exp)
+    # several broadcasts in flight, one with a 40 KB tensor behind big ones
+    ts = [_inputs(rank + 90 + i, c, torch.float32).to(dev)
+          for i, c in enumerate([2 << 20, 10000, (4 << 20) + 1, 10240])]
+    hs = [hvd.broadcast_async_(t, root_rank=i % size, name="xl.bcs.%d" % i)
+          for i, t in enumerate(ts)]
+    for i, (h, t) in enumerate(zip(hs, ts)):
+        hvd.synchronize(h)
+        ok = ok and torch.equal(t.cpu(), _inputs(i % size + 90 + i, t.numel(), torch.float32))
+    # a byte tensor of odd length and odd offset
+    raw = torch.arange(100001, dtype=torch.uint8).add_(rank).to(dev)[3:]
+    got = hvd.allgather(raw, name="xl.bytes")
+    exp = torch.cat([torch.arange(100001, dtype=torch.uint8).add_(r)[3:] for r in range(size)])
+    ok = ok and torch.equal(got.cpu(), exp)
+    # a small op in between
+    small = hvd.allgather(torch.full((3,), float(rank), device=dev), name="xl.small")
     ok = ok and small.cpu().tolist() == [float(r) for r in range(size) for _ in range(3)]
     torch.cuda.synchronize()
     hvd.shutdown()
     return ok
 
 
-@pytest.mark.skipif(os.environ.get("HOROVOD_EXCHANGE_PIPELINE") != "1",
-                    reason="the pipelined exchange is opt-in (HOROVOD_EXCHANGE_PIPELINE=1)")
-def test_pipelined_exchange_matches_reference():
+def test_large_and_mixed_exchange_rounds():
     if _ngpu() < 2:
         pytest.skip("needs 2 GPUs")
-    assert all(run_parallel(_pipelined_exchange, np=_world(), timeout=300))
+    assert all(run_parallel(_exchange_large, np=_world(), timeout=300))

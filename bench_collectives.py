@@ -27,6 +27,7 @@ import json
 import os
 import statistics
 import sys
+import time
 
 ALLREDUCE, ALLGATHER, BROADCAST, ALLTOALL, REDUCESCATTER = 0, 1, 2, 5, 6
 LINK_GBS = 770.0
@@ -37,6 +38,7 @@ def main():
     p.add_argument("--backend", default="symm", choices=["symm", "nccl"])
     p.add_argument("--min-kb", type=int, default=1)
     p.add_argument("--max-mb", type=int, default=256)
+    p.add_argument("--step", type=int, default=2, help="factor between consecutive sizes")
     p.add_argument("--iters", type=int, default=20)
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--ops", default="allreduce,allreduce_bf16,reducescatter,allgather,"
@@ -69,6 +71,10 @@ def main():
     dev = torch.device("cuda", hvd.local_rank())
     torch.manual_seed(rank)
 
+    from horovod_b200.utils.clocks import ClockLog
+    clock_log = ClockLog(hvd.local_rank()) if rank == 0 else None
+    window = [0.0, 0.0]  # wall-clock bounds of the last measurement
+
     def measure(fn, want_type):
         """Runs fn() warmup+iters times, one response at a time, and returns
         the median device time (us, max over ranks) of the matching ops."""
@@ -76,9 +82,11 @@ def main():
             fn()
         torch.cuda.synchronize()
         _C.gpu_op_stats()
+        window[0] = time.time()
         for _ in range(args.iters):
             fn()
         torch.cuda.synchronize()
+        window[1] = time.time()
         mine = [t[3] for t in _C.gpu_op_stats() if t[0] == want_type]
         mine = mine[-args.iters:]
         t = torch.tensor(mine, dtype=torch.float64)
@@ -87,9 +95,11 @@ def main():
 
     PHASES = ("start", "packed", "barrier1", "reduced", "barrier2", "unpacked")
 
-    def phases(fn):
+    XPHASES = ("start", "staged", "pulled", "done")
+
+    def phases(fn, PHASES=PHASES):
         """Median offsets (us since kernel start, CTA 0 of this rank) of the
-        phase boundaries of the traced allreduce kernel, max over ranks."""
+        phase boundaries of the traced kernel, max over ranks."""
         cols = []
         for _ in range(args.iters):
             fn()
@@ -113,7 +123,9 @@ def main():
                           "bus_gbs": round(bus, 2),
                           "roofline_us": round(roof_us, 2),
                           "frac_of_nvlink_roofline": round(roof_us / us, 4) if us > 0 else None,
-                          "gradient_path": hvd.gpu_backend(), **(extra or {})}), flush=True)
+                          "gradient_path": hvd.gpu_backend(),
+                          "clocks": clock_log.window(window[0], window[1]),
+                          **(extra or {})}), flush=True)
 
     def ar_wire(nbytes):
         nvls = n >= 4 and "nvls=1" in hvd.gpu_backend()
@@ -124,7 +136,7 @@ def main():
     s = args.min_kb << 10
     while s <= args.max_mb << 20:
         sizes.append(s)
-        s <<= 1
+        s *= max(2, args.step)
 
     heap = None
     if args.backend == "symm" and n > 1 and ("allreduce_symm" in ops or "grouped_symm" in ops
@@ -162,15 +174,21 @@ def main():
         if "allgather" in ops and nbytes // n >= 4:
             x = torch.randn(nbytes // 4 // n, device=dev)
             us = measure(lambda: hvd.allgather(x, name="sw.ag"), ALLGATHER)
-            emit("allgather", "fp32", nbytes, us, (n - 1) / n, nbytes * (n - 1) / n)
+            ph = {"phases_us": phases(lambda: hvd.allgather(x, name="sw.ag"), XPHASES)} \
+                if args.phases else None
+            emit("allgather", "fp32", nbytes, us, (n - 1) / n, nbytes * (n - 1) / n, ph)
         if "broadcast" in ops:
             x = torch.randn(nbytes // 4, device=dev)
             us = measure(lambda: hvd.broadcast_(x, root_rank=0, name="sw.bc"), BROADCAST)
-            emit("broadcast", "fp32", nbytes, us, 1.0, nbytes)
+            ph = {"phases_us": phases(lambda: hvd.broadcast_(x, root_rank=0, name="sw.bc"),
+                                      XPHASES)} if args.phases else None
+            emit("broadcast", "fp32", nbytes, us, 1.0, nbytes, ph)
         if "alltoall" in ops and nbytes // n >= 4:
             x = torch.randn(nbytes // 4 // n * n, device=dev)
             us = measure(lambda: hvd.alltoall(x, name="sw.a2a"), ALLTOALL)
-            emit("alltoall", "fp32", nbytes, us, (n - 1) / n, nbytes * (n - 1) / n)
+            ph = {"phases_us": phases(lambda: hvd.alltoall(x, name="sw.a2a"), XPHASES)} \
+                if args.phases else None
+            emit("alltoall", "fp32", nbytes, us, (n - 1) / n, nbytes * (n - 1) / n, ph)
 
     if "grouped" in ops:
         g = torch.Generator().manual_seed(0)
@@ -192,6 +210,8 @@ def main():
             emit("grouped_allreduce_64_symm", "fp32", total, us, 2 * (n - 1) / n,
                  ar_wire(total))
 
+    if clock_log is not None:
+        clock_log.stop()
     hvd.shutdown()
     return 0
 

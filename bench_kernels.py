@@ -11,7 +11,8 @@ Cases
   fused_fp16    same with float16 tensors.
   reducescatter reduce-scatter kernel on one rank: stage -> reduce -> write
                 (read + write staging + read staging + write = 4x bytes).
-  exchange      allgather of one rank through the exchange kernel (4x bytes).
+  exchange      allgather of one rank through the exchange kernel: with nobody
+                to send to it is one copy into the output (2x bytes).
   batch_norm    fused batch norm + residual + ReLU on a channels-last bf16
                 activation of 256 x 256 x 56 x 56 (411 MB): forward (statistics
                 pass + apply pass: read x twice, read the residual, write y =
@@ -29,6 +30,7 @@ import json
 import os
 import statistics
 import sys
+import time
 
 os.environ["HOROVOD_GPU_OP_TIMING"] = "1"
 os.environ.setdefault("HOROVOD_FUSION_THRESHOLD", str(1 << 30))
@@ -77,21 +79,27 @@ def main():
     dev = torch.device("cuda", 0)
     nbytes = args.mb << 20
 
+    from horovod_b200.utils.clocks import ClockLog
+    clock_log = ClockLog(0)
+
     def run(name, fn, want_type, algorithmic_bytes):
         for _ in range(args.warmup):
             fn()
         torch.cuda.synchronize()
         _C.gpu_op_stats()
+        t_begin = time.time()
         for _ in range(args.iters):
             fn()
         torch.cuda.synchronize()
+        t_end = time.time()
         us = [t[3] for t in _C.gpu_op_stats() if t[0] == want_type][-args.iters:]
         med = statistics.median(us)
         gbs = algorithmic_bytes / (med * 1e-6) / 1e9
         print(json.dumps({"case": name, "payload_mb": args.mb, "device_us": round(med, 1),
                           "algorithmic_gbs": round(gbs, 1),
                           "frac_of_%s_hbm_copy" % peak_src: round(gbs / hbm, 3),
-                          "hbm_gbs_peak": hbm}), flush=True)
+                          "hbm_gbs_peak": hbm,
+                          "clocks": clock_log.window(t_begin, t_end)}), flush=True)
 
     cases = ["fused_local", "fused_fp16", "reducescatter", "exchange", "batch_norm"] \
         if args.case == "all" else [args.case]
@@ -112,7 +120,7 @@ def main():
     if "exchange" in cases:
         n = min(nbytes, 192 << 20) // 4
         x = torch.randn(n, device=dev)
-        run("exchange", lambda: hvd.allgather(x, name="k.ag"), 1, 4 * n * 4)
+        run("exchange", lambda: hvd.allgather(x, name="k.ag"), 1, 2 * n * 4)
     if "batch_norm" in cases:
         import torch.nn.functional as F
         from horovod_b200.ops.batch_norm import batch_norm_act
@@ -146,7 +154,9 @@ def main():
             print(json.dumps({"case": name, "shape": list(shape), "device_us": round(us, 1),
                               "algorithmic_gbs": round(gbs, 1),
                               "frac_of_%s_hbm_copy" % peak_src: round(gbs / hbm, 3),
-                              "hbm_gbs_peak": hbm}), flush=True)
+                              "hbm_gbs_peak": hbm,
+                              "clocks": clock_log.window(time.time() - 1.0, time.time())}),
+                  flush=True)
 
         def eager_fwd():
             return F.relu(F.batch_norm(x, rm, rv, w, b, True, 0.1, 1e-5) + res)
@@ -164,6 +174,7 @@ def main():
             report(name + "_forward", t_f, 4 * nbytes_act)
             report(name + "_backward", t_b, 8 * nbytes_act)
             del y
+    clock_log.stop()
     hvd.shutdown()
     return 0
 

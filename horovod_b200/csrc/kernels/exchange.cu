@@ -67,6 +67,7 @@ exchange_kernel(const InlineExchange inl, const ExchangePlan plan_dev, const Exc
   __shared__ void* s_st_self[SEGS];
   __shared__ int64_t s_st_off[SEGS];
   __shared__ int64_t s_st_bytes[SEGS];
+  __shared__ int32_t s_st_dst[SEGS];
   __shared__ void* s_pl_dst[SEGS];
   __shared__ int64_t s_pl_off[SEGS];
   __shared__ int64_t s_pl_bytes[SEGS];
@@ -83,6 +84,7 @@ exchange_kernel(const InlineExchange inl, const ExchangePlan plan_dev, const Exc
         s_st_self[i] = inl.st_self[i];
         s_st_off[i] = inl.st_off[i];
         s_st_bytes[i] = inl.st_bytes[i];
+        s_st_dst[i] = inl.st_dst[i];
       }
       if (threadIdx.x == 32 + i && i < inl.n_pull) {
         s_pl_dst[i] = inl.pl_dst[i];
@@ -98,6 +100,7 @@ exchange_kernel(const InlineExchange inl, const ExchangePlan plan_dev, const Exc
     plan.st_self = s_st_self;
     plan.st_off = s_st_off;
     plan.st_bytes = s_st_bytes;
+    plan.st_dst = s_st_dst;
     plan.n_pull = inl.n_pull;
     plan.pl_dst = s_pl_dst;
     plan.pl_off = s_pl_off;
@@ -127,11 +130,12 @@ exchange_kernel(const InlineExchange inl, const ExchangePlan plan_dev, const Exc
     if (__syncthreads_and(ok) == 0) return;
   }
 
+  trace_mark(ctx, 0);
   const int64_t C = sync.chunk_bytes;
-  char* const region_w = sync.mc_push ? ctx.mc : ctx.local;  // where staged data goes
   int so = 0, si = 0;      // current staged / pulled segment
   int64_t ko = 0, ki = 0;  // current chunk inside it
   uint32_t published = 0;  // chunks this CTA has made visible so far
+  bool staged_all = false;
 
   for (;;) {
     // ---- stage one chunk (or one whole local-only copy) --------------------
@@ -152,9 +156,21 @@ exchange_kernel(const InlineExchange inl, const ExchangePlan plan_dev, const Exc
         int64_t lo, hi;
         my_range(off, bytes, b, G, &lo, &hi);
         const int64_t clo = lo + ko * C, chi = min(hi, clo + C);
-        if (clo < chi)
-          copy_bytes<4>(src + clo, false, region_w + off + clo, sync.mc_push != 0,
-                        self != nullptr ? self + clo : nullptr, chi - clo);
+        if (clo < chi) {
+          const int d = plan.st_dst[so];
+          char* own = self != nullptr ? self + clo : nullptr;
+          if (d == -1 && ctx.mc == nullptr) {
+            // Every other rank's region, one peer after the other.
+            for (int p = 0; p < ctx.world; ++p) {
+              if (p == ctx.rank) continue;
+              copy_bytes<4>(src + clo, false, ctx.peers[p] + off + clo, false, own, chi - clo);
+              own = nullptr;
+            }
+          } else {
+            char* region = d == -2 ? ctx.local : d >= 0 ? ctx.peers[d] : ctx.mc;
+            copy_bytes<4>(src + clo, false, region + off + clo, d == -1, own, chi - clo);
+          }
+        }
         __syncthreads();
         ++published;
         if (threadIdx.x < ctx.world)
@@ -202,7 +218,12 @@ exchange_kernel(const InlineExchange inl, const ExchangePlan plan_dev, const Exc
       }
     }
     if (so >= plan.n_stage && si >= plan.n_pull) break;
+    if (so >= plan.n_stage && !staged_all) {
+      staged_all = true;
+      trace_mark(ctx, 1);  // everything staged and announced
+    }
   }
+  trace_mark(ctx, 2);
 
   if (sync.credit_post != 0) {
     // The last CTA of this rank to get here tells every peer that this
@@ -221,6 +242,7 @@ exchange_kernel(const InlineExchange inl, const ExchangePlan plan_dev, const Exc
     // Nobody rewrites its region before everybody has drained it.
     cta_barrier(ctx, ctx.epoch + sync.done_epochs, b, 4);
   }
+  trace_mark(ctx, 3);
 }
 
 __global__ void barrier_only_kernel(SymmCtx ctx) {
@@ -234,7 +256,6 @@ cudaError_t LaunchExchange(const ExchangePlan& plan, const ExchangeSync& sync, i
                            const InlineExchange* inline_plan) {
   if (num_ctas < 1 || num_ctas > SYMM_MAX_BLOCKS) return cudaErrorInvalidValue;
   if (sync.chunk_bytes < 4096 || (sync.chunk_bytes & 255) != 0) return cudaErrorInvalidValue;
-  if (sync.mc_push && ctx.mc == nullptr) return cudaErrorInvalidValue;
   if (sync.credit_post != 0 && sync.done_counter == nullptr) return cudaErrorInvalidValue;
   CountKernelLaunches(1);
   static const InlineExchange kNoInline = {};

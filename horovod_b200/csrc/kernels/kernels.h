@@ -149,14 +149,43 @@ cudaError_t LaunchFusedReducescatter(const void* in, void* out, int64_t count,
 // skips staging and reduces straight out of the peers' tensors. prescale is
 // ignored in that mode: fold it into postscale.
 
-// Exchange kernel behind allgather, broadcast and alltoall ("stage locally,
-// pull remotely"). Every rank copies the data it owes to others from its
-// tensors into its OWN exchange region (a local copy at HBM speed), publishes
-// how far it has got, and every receiver pulls what it needs straight out of
-// the owner's region over NVLink into its final tensor. Data crosses NVLink
-// once and lands in its destination without a second local pass. With
-// multicast a broadcast root instead writes every rank's region at once
-// (multimem.st) and the receivers copy out of their local region.
+// Reduce-scatter of a tensor in ordinary memory by pushing shards into their
+// owners' exchange regions (reducescatter_push.cu). One launch covers the
+// window [win_lo, win_hi) of element offsets inside every shard; the region of
+// every rank holds one slot of slot_bytes per sending rank. slice_vecs is the
+// number of 16-byte vectors of a shard window each CTA handles (a multiple of
+// 16, the same for all shards: derived from the largest one). The launch
+// consumes ceil(slice_vecs * 16 / chunk_bytes) + 1 epochs. Region reuse is
+// guarded by the same launch credits as the exchange kernel below.
+struct RsPushArgs {
+  int64_t shard_begin[SYMM_MAX_RANKS + 1];  // element offsets, world + 1 entries used
+  int64_t win_lo, win_hi;
+  int64_t slot_bytes;
+  int64_t slice_vecs;
+  int64_t chunk_bytes;
+  uint32_t credit_wait, credit_post;
+  unsigned long long* done_counter;
+  unsigned long long done_target;
+};
+cudaError_t LaunchReducescatterPush(const void* in, void* out, const RsPushArgs& args,
+                                    DataType dtype, double prescale, double postscale,
+                                    int num_ctas, const SymmCtx& ctx, cudaStream_t stream);
+
+// Exchange kernel behind allgather, broadcast and alltoall. Every rank copies
+// the data it owes to others from its tensors into an exchange region and
+// publishes how far it has got; every receiver copies what it needs out of a
+// region into its final tensor. Per staged segment the host picks the region:
+//   * the sender's OWN region ("stage locally, pull remotely"): a local copy
+//     at HBM speed, then the receiver pulls straight out of the owner's region
+//     over NVLink into its final tensor. Data crosses NVLink once and lands in
+//     its destination without a second local pass: the choice for large
+//     messages;
+//   * the RECEIVER's region (peer stores), or every rank's region at once
+//     (multimem.st through the switch when multicast is available): the data
+//     travels with the announcement instead of being fetched afterwards, one
+//     NVLink crossing less on the critical path: the choice for small
+//     messages and for a broadcast root with multicast (its NVLink egress is S
+//     instead of (N-1) S).
 //
 // Progress is published per CTA: CTA b cuts its slice of every staged segment
 // into chunks and, after each chunk, stores ctx.epoch + (chunks so far) into
@@ -177,6 +206,7 @@ struct ExchangePlan {
   void* const* st_self;        // also copy to this local destination (null = no)
   const int64_t* st_off;       // byte offset in the region; < 0: local copy to st_self only
   const int64_t* st_bytes;
+  const int32_t* st_dst;       // whose region: -2 this rank's, -1 every other rank's, >= 0 that rank's
   int n_pull;
   void* const* pl_dst;         // local destination tensors
   const int64_t* pl_off;       // byte offset in the owner's region
@@ -193,6 +223,7 @@ struct InlineExchange {
   void* st_self[INLINE_SEGMENTS];
   int64_t st_off[INLINE_SEGMENTS];
   int64_t st_bytes[INLINE_SEGMENTS];
+  int32_t st_dst[INLINE_SEGMENTS];
   void* pl_dst[INLINE_SEGMENTS];
   int64_t pl_off[INLINE_SEGMENTS];
   int64_t pl_bytes[INLINE_SEGMENTS];
@@ -202,7 +233,6 @@ struct InlineExchange {
 };
 struct ExchangeSync {
   int64_t chunk_bytes;      // multiple of 256
-  int mc_push;              // staged segments are written to every rank's region (multimem.st)
   uint32_t done_epochs;     // epochs this launch consumes (> chunks published by any CTA)
   uint32_t credit_wait;     // 0 = nothing to wait for
   uint32_t credit_post;     // 0 = end with a barrier instead

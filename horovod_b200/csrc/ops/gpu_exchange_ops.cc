@@ -22,7 +22,7 @@ constexpr int64_t STAGING_ALIGN = 256;
 void GpuOps::LaunchExchangeSegments(const std::vector<StageSeg>& stage,
                                     const std::vector<PullSeg>& pull, SymmSet& set,
                                     int64_t round_bytes,
-                                    const std::vector<RoundBlock>& round, bool mc_push) {
+                                    const std::vector<RoundBlock>& round) {
   const size_t ns = stage.size(), np = pull.size();
   // The grid size must be the same on every rank (CTA b meets CTA b of its
   // peers), so it is derived from the bytes of the whole round, which all
@@ -43,7 +43,6 @@ void GpuOps::LaunchExchangeSegments(const std::vector<StageSeg>& stage,
   kern::ExchangeSync sync;
   std::memset(&sync, 0, sizeof(sync));
   sync.chunk_bytes = chunk;
-  sync.mc_push = mc_push ? 1 : 0;
   sync.done_epochs = static_cast<uint32_t>(most + 1);
   int64_t region_off = 0;
   if (set.xchg_bytes > 0) {
@@ -72,6 +71,7 @@ void GpuOps::LaunchExchangeSegments(const std::vector<StageSeg>& stage,
       inl.st_self[i] = stage[i].self_dst;
       inl.st_off[i] = stage[i].off;
       inl.st_bytes[i] = stage[i].bytes;
+      inl.st_dst[i] = stage[i].dst;
     }
     for (size_t i = 0; i < np; ++i) {
       inl.pl_dst[i] = pull[i].dst;
@@ -88,11 +88,12 @@ void GpuOps::LaunchExchangeSegments(const std::vector<StageSeg>& stage,
     const void** d_src;
     void **d_self, **d_dst;
     int64_t *d_soff, *d_sbytes, *d_poff, *d_pbytes;
-    int32_t *d_psrc, *d_psig, *d_pwait;
+    int32_t *d_psrc, *d_psig, *d_pwait, *d_sdst;
     const void** h_src = slot.Alloc<const void*>(ns + 1, &d_src);
     void** h_self = slot.Alloc<void*>(ns + 1, &d_self);
     int64_t* h_soff = slot.Alloc<int64_t>(ns + 1, &d_soff);
     int64_t* h_sbytes = slot.Alloc<int64_t>(ns + 1, &d_sbytes);
+    int32_t* h_sdst = slot.Alloc<int32_t>(ns + 1, &d_sdst);
     void** h_dst = slot.Alloc<void*>(np + 1, &d_dst);
     int64_t* h_poff = slot.Alloc<int64_t>(np + 1, &d_poff);
     int64_t* h_pbytes = slot.Alloc<int64_t>(np + 1, &d_pbytes);
@@ -100,13 +101,14 @@ void GpuOps::LaunchExchangeSegments(const std::vector<StageSeg>& stage,
     int32_t* h_psig = slot.Alloc<int32_t>(np + 1, &d_psig);
     int32_t* h_pwait = slot.Alloc<int32_t>(np + 1, &d_pwait);
     if (!h_src || !h_self || !h_soff || !h_sbytes || !h_dst || !h_poff || !h_pbytes ||
-        !h_psrc || !h_psig || !h_pwait)
+        !h_psrc || !h_psig || !h_pwait || !h_sdst)
       throw std::runtime_error("exchange plan does not fit a descriptor slot");
     for (size_t i = 0; i < ns; ++i) {
       h_src[i] = stage[i].src;
       h_self[i] = stage[i].self_dst;
       h_soff[i] = stage[i].off;
       h_sbytes[i] = stage[i].bytes;
+      h_sdst[i] = stage[i].dst;
     }
     for (size_t i = 0; i < np; ++i) {
       h_dst[i] = pull[i].dst;
@@ -122,6 +124,7 @@ void GpuOps::LaunchExchangeSegments(const std::vector<StageSeg>& stage,
     plan.st_self = d_self;
     plan.st_off = d_soff;
     plan.st_bytes = d_sbytes;
+    plan.st_dst = d_sdst;
     plan.n_pull = static_cast<int>(np);
     plan.pl_dst = d_dst;
     plan.pl_off = d_poff;
@@ -136,6 +139,12 @@ void GpuOps::LaunchExchangeSegments(const std::vector<StageSeg>& stage,
   if (err != cudaSuccess)
     throw std::runtime_error(std::string("exchange kernel launch failed: ") +
                              cudaGetErrorString(err));
+}
+
+bool GpuOps::ExchangePushes(const SymmSet& set, int64_t total_bytes) const {
+  // Writing into other ranks' regions is only safe for the credit-guarded
+  // regions of the global set: nothing else ever touches those.
+  return set.world > 1 && set.xchg_bytes > 0 && total_bytes <= exchange_push_max_;
 }
 
 // Every rank builds the same global list of "blocks" (source rank, bytes,
@@ -154,7 +163,9 @@ struct Block {
 };
 }  // namespace
 
-static void RunBlocks(std::vector<Block>& blocks, SymmSet& set, bool mc_push,
+// push: staged blocks are written into the receivers' regions (one layout
+// shared by all regions) instead of the sender's own.
+static void RunBlocks(std::vector<Block>& blocks, SymmSet& set, bool push,
                       const std::function<void(const std::vector<GpuOps::StageSeg>&,
                                                const std::vector<GpuOps::PullSeg>&,
                                                int64_t,
@@ -180,8 +191,8 @@ static void RunBlocks(std::vector<Block>& blocks, SymmSet& set, bool mc_push,
   while (next < parts.size()) {
     std::vector<GpuOps::StageSeg> stage;
     std::vector<GpuOps::PullSeg> pull;
-    // Offsets are per source region. With a multicast push the source writes
-    // the same offset of everybody's region, which is the same bookkeeping.
+    // Pulling: offsets are per source region. Pushing: several sources write
+    // into one receiver's region, so one cursor lays out the whole round.
     std::vector<int64_t> cursor(set.world, 0);
     size_t n = 0;
     int64_t round_bytes = 0;
@@ -192,16 +203,18 @@ static void RunBlocks(std::vector<Block>& blocks, SymmSet& set, bool mc_push,
       const bool wanted = (b.dst_rank < 0 || b.dst_rank == me) && b.dst != nullptr;
       if (!remote) {
         // Data a rank keeps for itself: a local copy, no region space.
-        if (b.src_rank == me && wanted) stage.push_back({b.src, b.dst, -1, b.bytes});
+        if (b.src_rank == me && wanted) stage.push_back({b.src, b.dst, -1, b.bytes, -2});
       } else {
         const int64_t padded = RoundUp(b.bytes, STAGING_ALIGN);
-        const int64_t off = cursor[b.src_rank];
+        int64_t& cur = cursor[push ? 0 : b.src_rank];
+        const int64_t off = cur;
         if (off + padded > cap) break;
-        cursor[b.src_rank] = off + padded;
+        cur = off + padded;
         if (b.src_rank == me) {
-          stage.push_back({b.src, wanted ? b.dst : nullptr, off, b.bytes});
+          stage.push_back({b.src, wanted ? b.dst : nullptr, off, b.bytes,
+                           push ? b.dst_rank : -2});
         } else if (wanted) {
-          pull.push_back({b.dst, off, b.bytes, mc_push ? me : b.src_rank, b.src_rank,
+          pull.push_back({b.dst, off, b.bytes, push ? me : b.src_rank, b.src_rank,
                           static_cast<int32_t>(round.size())});
         }
         round.push_back({b.src_rank, b.bytes});
@@ -234,13 +247,17 @@ Status GpuOps::SymmBroadcast(std::vector<TensorTableEntry>& entries,
   }
   // From three ranks on the root writes everybody's region at once through
   // the multicast mapping (its NVLink egress is S instead of (N-1) S) and the
-  // receivers copy out of their own region; with two ranks the peer pulls.
-  // (Only with the credit-guarded regions: nobody else ever writes those.)
-  const bool mc_push = set.mc != nullptr && set.world >= 3 && set.xchg_bytes > 0;
-  RunBlocks(blocks, set, mc_push,
+  // receivers copy out of their own region; with two ranks the peer pulls
+  // large messages. (Only with the credit-guarded regions: nobody else ever
+  // writes those.)
+  int64_t total = 0;
+  for (auto& b : blocks) total += b.bytes;
+  const bool push = ExchangePushes(set, total) ||
+                    (set.mc != nullptr && set.world >= 3 && set.xchg_bytes > 0);
+  RunBlocks(blocks, set, push,
             [&](const std::vector<StageSeg>& o, const std::vector<PullSeg>& i,
                 int64_t round_bytes, const std::vector<RoundBlock>& round) {
-              LaunchExchangeSegments(o, i, set, round_bytes, round, mc_push);
+              LaunchExchangeSegments(o, i, set, round_bytes, round);
             });
   tl.ActivityEndAll(entries);
   return Complete(entries);
@@ -279,10 +296,12 @@ Status GpuOps::SymmAllgather(std::vector<TensorTableEntry>& entries,
     }
   }
   tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
-  RunBlocks(blocks, set, false,
+  int64_t total = 0;
+  for (auto& b : blocks) total += b.bytes;
+  RunBlocks(blocks, set, ExchangePushes(set, total),
             [&](const std::vector<StageSeg>& o, const std::vector<PullSeg>& i,
                 int64_t round_bytes, const std::vector<RoundBlock>& round) {
-              LaunchExchangeSegments(o, i, set, round_bytes, round, false);
+              LaunchExchangeSegments(o, i, set, round_bytes, round);
             });
   tl.ActivityEndAll(entries);
   return Complete(entries);
@@ -337,10 +356,12 @@ Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries,
     }
   }
   tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
-  RunBlocks(blocks, set, false,
+  int64_t total = 0;
+  for (auto& b : blocks) total += b.bytes;
+  RunBlocks(blocks, set, ExchangePushes(set, total),
             [&](const std::vector<StageSeg>& o, const std::vector<PullSeg>& i,
                 int64_t round_bytes, const std::vector<RoundBlock>& round) {
-              LaunchExchangeSegments(o, i, set, round_bytes, round, false);
+              LaunchExchangeSegments(o, i, set, round_bytes, round);
             });
   tl.ActivityEndAll(entries);
   return Complete(entries);

@@ -124,7 +124,7 @@ public:
   void Shutdown() override;
 
   // Segments handed to the exchange kernel (see kern::ExchangePlan).
-  struct StageSeg { const void* src; void* self_dst; int64_t off; int64_t bytes; };
+  struct StageSeg { const void* src; void* self_dst; int64_t off; int64_t bytes; int32_t dst; };
   struct PullSeg {
     void* dst;
     int64_t off;
@@ -190,13 +190,13 @@ private:
   // (and launches nothing) when the entries do not qualify.
   bool TryInplaceAllreduce(std::vector<TensorTableEntry>& entries,
                            const Response& response, SymmSet& set, Status* status);
-  // One exchange-kernel launch for the given segment lists. `use_region`:
-  // which of the set's exchange regions the round was laid out for (-1: the
-  // general staging area, trailing barrier).
+  // One exchange-kernel launch for the given segment lists.
   void LaunchExchangeSegments(const std::vector<StageSeg>& stage,
                               const std::vector<PullSeg>& pull, SymmSet& set,
-                              int64_t round_bytes, const std::vector<RoundBlock>& round,
-                              bool mc_push);
+                              int64_t round_bytes, const std::vector<RoundBlock>& round);
+  // Whether an exchange of `total_bytes` writes straight into the receivers'
+  // regions (small messages) instead of staging locally.
+  bool ExchangePushes(const SymmSet& set, int64_t total_bytes) const;
 
   GlobalState& state_;
   std::shared_ptr<DoneEventPool> events_;
@@ -224,6 +224,7 @@ private:
   unsigned long long tile_base_ = 0;
   int64_t dynamic_min_bytes_ = 0;
   int64_t exchange_chunk_bytes_ = 256 << 10;  // HOROVOD_EXCHANGE_CHUNK_KB
+  int64_t exchange_push_max_ = 1 << 20;       // HOROVOD_EXCHANGE_PUSH_MAX_BYTES
   unsigned long long* xchg_done_counter_ = nullptr;  // device word, see kern::ExchangeSync
   unsigned long long xchg_done_base_ = 0;
   unsigned long long* trace_host_ = nullptr;  // mapped pinned, HOROVOD_KERNEL_TRACE=1

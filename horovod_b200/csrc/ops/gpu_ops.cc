@@ -156,6 +156,7 @@ void GpuOps::EnsureDevice(int device) {
   dynamic_min_bytes_ = EnvInt("HOROVOD_DYNAMIC_TILES_MIN_BYTES", 8 << 20);
   exchange_chunk_bytes_ =
       std::max<int64_t>(64, EnvInt("HOROVOD_EXCHANGE_CHUNK_KB", 256)) << 10;
+  exchange_push_max_ = EnvInt("HOROVOD_EXCHANGE_PUSH_MAX_BYTES", 1 << 20);
   HVD_CUDA(cudaMalloc(reinterpret_cast<void**>(&xchg_done_counter_), sizeof(unsigned long long)));
   HVD_CUDA(cudaMemset(xchg_done_counter_, 0, sizeof(unsigned long long)));
   xchg_done_base_ = 0;

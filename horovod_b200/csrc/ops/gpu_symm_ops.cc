@@ -321,6 +321,47 @@ Status GpuOps::SymmReducescatter(std::vector<TensorTableEntry>& entries,
     if (n > 1 && shards_aligned && e.input != nullptr &&
         InSymmHeap(e.input, e.num_elements() * es, &heap_off) && (heap_off & 15) == 0)
       sym_off = heap_off;
+    if (sym_off < 0 && n > 1 && set.xchg_bytes > 0) {
+      // Ordinary memory: push every shard into its owner's exchange region,
+      // one window of the shards per launch.
+      ring_.Release(slot, stream_);  // the shard bounds travel in the parameters
+      const int64_t slot_bytes = set.xchg_bytes / n / STAGING_ALIGN * STAGING_ALIGN;
+      const int64_t win = slot_bytes / es;
+      const int64_t longest = (base + (extra ? 1 : 0)) * slice;
+      const int64_t chunk = exchange_chunk_bytes_ / 256 * 256;
+      tl.ActivityStart(e.name, HVD_ACT_FUSED_KERNEL);
+      for (int64_t lo = 0; lo < longest; lo += win) {
+        const int64_t n_max = std::min(longest, lo + win) - lo;
+        const int ctas = PickCtas(n_max * es * n);
+        const int64_t vecs = (n_max * es + 15) / 16;
+        kern::RsPushArgs a;
+        std::memset(&a, 0, sizeof(a));
+        for (int r = 0; r <= n; ++r) a.shard_begin[r] = h_sb[r];
+        a.win_lo = lo;
+        a.win_hi = lo + win;
+        a.slot_bytes = slot_bytes;
+        a.slice_vecs = RoundUp((vecs + ctas - 1) / ctas, 16);
+        a.chunk_bytes = chunk;
+        const uint32_t seq = ++set.xchg_seq;
+        a.credit_wait = seq > 2 ? seq - 2 : 0;
+        a.credit_post = seq;
+        a.done_counter = xchg_done_counter_;
+        xchg_done_base_ += static_cast<unsigned long long>(ctas);
+        a.done_target = xchg_done_base_;
+        const uint32_t epochs =
+            static_cast<uint32_t>((a.slice_vecs * 16 + chunk - 1) / chunk) + 1;
+        kern::SymmCtx ctx = MakeCtx(set, epochs, set.xchg_off[seq & 1]);
+        cudaError_t err = kern::LaunchReducescatterPush(e.input, out, a, e.dtype, e.prescale,
+                                                        e.postscale, ctas, ctx, stream_);
+        if (err != cudaSuccess) {
+          tl.ActivityEnd(e.name);
+          return Status::UnknownError(std::string("reducescatter launch failed: ") +
+                                      cudaGetErrorString(err));
+        }
+      }
+      tl.ActivityEnd(e.name);
+      continue;
+    }
     if (sym_off < 0 && staged > static_cast<int64_t>(set.data_bytes))
       return Status::InvalidArgument(
           "reducescatter tensor '" + e.name + "' does not fit the symmetric "

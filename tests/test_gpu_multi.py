@@ -411,3 +411,58 @@ def test_large_and_mixed_exchange_rounds():
     if _ngpu() < 2:
         pytest.skip("needs 2 GPUs")
     assert all(run_parallel(_exchange_large, np=_world(), timeout=300))
+
+
+def _reducescatter_push(rank, size):
+    """Reduce-scatter of tensors in ordinary memory: shards are pushed into the
+    owners' exchange regions. A small staging area forces several windows per
+    tensor; small chunks make every launch announce many chunks."""
+    os.environ["HOROVOD_SYMM_BUFFER_MB"] = "64"
+    os.environ["HOROVOD_EXCHANGE_CHUNK_KB"] = "64"
+    os.environ["HOROVOD_SPIN_TIMEOUT_MS"] = "5000"
+    import horovod_b200.torch as hvd
+    hvd.init()
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    ok = True
+    cases = [(torch.float32, 5 * size + 3, 700001, 1.0, 1.0),    # several windows, ragged rows
+             (torch.float32, size, 1, 1.0, 1.0),                # one element per rank
+             (torch.float32, size - 1, 5, 1.0, 1.0),            # a rank with an empty shard
+             (torch.bfloat16, 2 * size + 1, 100003, 0.5, 2.0),  # 16-bit, pre/postscale
+             (torch.float16, 3 * size, 4099, 1.0, 0.25),
+             (torch.int32, 4 * size + 1, 33333, 1.0, 1.0),
+             (torch.float64, size + 1, 77777, 1.0, 1.0)]
+    for it in range(2):
+        for ci, (dtype, rows, width, pre, post) in enumerate(cases):
+            n = rows * width
+            full = _inputs(rank * 17 + ci + it, n + 1, dtype)
+            # a view that starts one element into the allocation: not 16-byte aligned
+            x = full.to(dev)[1:].view(rows, width)
+            out = hvd.reducescatter(x, op=hvd.Sum, prescale_factor=pre, postscale_factor=post,
+                                    name="rsp.%d" % ci)
+            ref = sum((_inputs(r * 17 + ci + it, n + 1, dtype)[1:].view(rows, width).double() * pre)
+                      .to(dtype).double() for r in range(size)) * post
+            base, extra = rows // size, rows % size
+            lo = rank * base + min(rank, extra)
+            hi = lo + base + (1 if rank < extra else 0)
+            tol = {torch.float32: 1e-5, torch.float64: 1e-12, torch.int32: 0,
+                   torch.bfloat16: 4e-2, torch.float16: 8e-3}[dtype]
+            if tuple(out.shape) != (hi - lo, width):
+                ok = False
+                continue
+            if hi > lo:
+                err = (out.double().cpu() - ref[lo:hi]).abs().max().item()
+                scale = max(1.0, ref.abs().max().item())
+                ok = ok and err <= tol * scale * size
+    # interleaved with the other users of the exchange regions
+    g = hvd.allgather(torch.full((2,), float(rank), device=dev), name="rsp.ag")
+    ok = ok and g.cpu().tolist() == [float(r) for r in range(size) for _ in range(2)]
+    torch.cuda.synchronize()
+    hvd.shutdown()
+    return ok
+
+
+def test_reducescatter_from_ordinary_memory():
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    assert all(run_parallel(_reducescatter_push, np=_world(), timeout=300))

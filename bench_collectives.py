@@ -74,6 +74,7 @@ def main():
     from horovod_b200.utils.clocks import ClockLog
     clock_log = ClockLog(hvd.local_rank()) if rank == 0 else None
     window = [0.0, 0.0]  # wall-clock bounds of the last measurement
+    host_us = [0.0]      # host time inside the timed interval (rank 0, median)
 
     def measure(fn, want_type):
         """Runs fn() warmup+iters times, one response at a time, and returns
@@ -87,15 +88,16 @@ def main():
             fn()
         torch.cuda.synchronize()
         window[1] = time.time()
-        mine = [t[3] for t in _C.gpu_op_stats() if t[0] == want_type]
-        mine = mine[-args.iters:]
+        stats = [t for t in _C.gpu_op_stats() if t[0] == want_type][-args.iters:]
+        mine = [t[3] for t in stats]
+        host_us[0] = statistics.median(t[4] for t in stats) if stats else 0.0
         t = torch.tensor(mine, dtype=torch.float64)
         t = hvd.allreduce(t, op=hvd.Max, name="sweep.times.%d" % len(mine))
         return statistics.median(t.tolist())
 
     PHASES = ("start", "packed", "barrier1", "reduced", "barrier2", "unpacked")
 
-    XPHASES = ("start", "staged", "pulled", "done")
+    XPHASES = ("start", "staged", "pulled", "done", "last_cta_done")
 
     def phases(fn, PHASES=PHASES):
         """Median offsets (us since kernel start, CTA 0 of this rank) of the
@@ -120,6 +122,7 @@ def main():
         roof_us = wire_bytes / (LINK_GBS * 1e9) * 1e6
         print(json.dumps({"op": op, "dtype": dtype, "bytes": nbytes, "n_gpus": n,
                           "backend": args.backend, "device_us": round(us, 2),
+                          "host_us_between_events": round(host_us[0], 2),
                           "bus_gbs": round(bus, 2),
                           "roofline_us": round(roof_us, 2),
                           "frac_of_nvlink_roofline": round(roof_us / us, 4) if us > 0 else None,

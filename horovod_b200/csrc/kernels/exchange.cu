@@ -236,6 +236,8 @@ exchange_kernel(const InlineExchange inl, const ExchangePlan plan_dev, const Exc
         for (int p = 0; p < ctx.world; ++p)
           st_release_sys(ctx.flags_peers[p] + CREDIT_BANK + ctx.rank * SYMM_MAX_BLOCKS,
                          sync.credit_post);
+        if (ctx.trace != nullptr)  // when the slowest CTA of this rank finished
+          *reinterpret_cast<volatile unsigned long long*>(ctx.trace + 4) = globaltimer_ns();
       }
     }
   } else {

@@ -301,6 +301,39 @@ cudaError_t LaunchBatchNormBackward(const void* dy, const void* y, const void* x
                                     float* dweight, float* dbias, bool relu,
                                     cudaStream_t stream);
 
+// 3x3 / stride 2 / padding 1 max pooling on channels-last 16-bit activations
+// ([n, h, w, channels], channels a multiple of 8). Forward writes the maxima
+// and one byte per output element naming the winning window position (0..8);
+// backward gathers dy through those bytes into dx (every element written).
+bool MaxPool3s2Supported(int channels);
+cudaError_t LaunchMaxPool3s2Forward(const void* x, void* y, unsigned char* idx, int n, int h,
+                                    int w, int channels, bool bf16, cudaStream_t stream);
+cudaError_t LaunchMaxPool3s2Backward(const void* dy, const unsigned char* idx, void* dx, int n,
+                                     int h, int w, int channels, bool bf16, cudaStream_t stream);
+
+// Multi-tensor SGD step in one launch (torch.optim.SGD arithmetic: weight
+// decay added to the gradient, momentum buffer b = momentum * b + (1 -
+// dampening) * g, or b = g on the first step, optional Nesterov, then
+// p -= lr * update). Tensor i has counts[i] fp32 elements at params[i],
+// grads[i], bufs[i] (bufs may be null when momentum == 0); the three arrays of
+// a tensor must share one memory layout. chunk_tensor / chunk_start (device
+// arrays of n_chunks entries) cut the tensors into pieces of at most
+// chunk_elems elements, one per CTA iteration.
+struct SgdTensors {
+  int n;
+  float* const* params;
+  const float* const* grads;
+  float* const* bufs;
+  const int64_t* counts;
+  int n_chunks;
+  const int32_t* chunk_tensor;
+  const int64_t* chunk_start;
+  int64_t chunk_elems;
+};
+cudaError_t LaunchFusedSgd(const SgdTensors& t, float lr, float momentum, float dampening,
+                           float weight_decay, bool nesterov, bool first_step, bool maximize,
+                           cudaStream_t stream);
+
 uint64_t KernelLaunchCount();
 void CountKernelLaunches(int n);
 

@@ -143,6 +143,7 @@ public:
     int64_t bytes;   // payload bytes of the response on this rank
     int tensors;
     float device_us;
+    float host_us;   // host time between the two timing events being recorded
   };
   // Waits for the recorded ops to finish and returns (and clears) the list.
   std::vector<OpTiming> DrainTimings();
@@ -238,7 +239,13 @@ private:
     int type;
     int64_t bytes;
     int tensors;
+    double host_t0;
+    float host_us;
   };
+  // Closes the timing record of the response being executed: called by
+  // Complete() right after the last launch, before callbacks run.
+  void CloseTiming();
+  PendingTiming* open_timing_ = nullptr;
   bool timing_ = false;
   std::mutex timing_mu_;
   std::vector<PendingTiming> pending_timings_;

@@ -2,6 +2,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <chrono>
 #include <cstring>
 
 #include "../common/env.h"
@@ -346,7 +347,26 @@ void GpuOps::WaitForInputs(const std::vector<TensorTableEntry>& entries) {
   }
 }
 
+namespace {
+double HostNowUs() {
+  return std::chrono::duration<double, std::micro>(
+             std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+}  // namespace
+
+void GpuOps::CloseTiming() {
+  PendingTiming* pt = open_timing_;
+  if (pt == nullptr || pt->t1 == nullptr) return;
+  open_timing_ = nullptr;
+  cudaEventRecord(pt->t1, stream_);
+  pt->host_us = static_cast<float>(HostNowUs() - pt->host_t0);
+  std::lock_guard<std::mutex> l(timing_mu_);
+  pending_timings_.push_back(*pt);
+  pt->t1 = nullptr;
+}
+
 Status GpuOps::Complete(std::vector<TensorTableEntry>& entries) {
+  CloseTiming();
   std::shared_ptr<void> done = events_->Get();
   HVD_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(done.get()), stream_));
   Timeline& tl = state_.timeline;
@@ -409,7 +429,7 @@ Status GpuOps::Execute(std::vector<TensorTableEntry>& entries,
     }
   }
   PendingTiming pt = {nullptr, nullptr, static_cast<int>(response.type), 0,
-                      static_cast<int>(entries.size())};
+                      static_cast<int>(entries.size()), 0.0, 0.f};
   if (timing_) {
     for (auto& e : entries) pt.bytes += e.size_bytes();
     WaitForInputs(entries);  // producer wait must not count as op time
@@ -423,17 +443,18 @@ Status GpuOps::Execute(std::vector<TensorTableEntry>& entries,
       }
     }
     HVD_CUDA(cudaEventRecord(pt.t0, stream_));
+    pt.host_t0 = HostNowUs();
+    open_timing_ = &pt;
   }
+  // Normally Complete() closes the record right after the last launch; this
+  // covers the paths that return without reaching it.
   struct TimingCloser {
     GpuOps* self;
-    PendingTiming* pt;
     ~TimingCloser() {
-      if (pt->t1 == nullptr) return;
-      cudaEventRecord(pt->t1, self->stream_);
-      std::lock_guard<std::mutex> l(self->timing_mu_);
-      self->pending_timings_.push_back(*pt);
+      self->CloseTiming();
+      self->open_timing_ = nullptr;
     }
-  } closer{this, &pt};
+  } closer{this};
   if (use_symm) {
     switch (response.type) {
     case Response::ALLREDUCE: return SymmAllreduce(entries, response, *set, false);
@@ -477,7 +498,7 @@ std::vector<GpuOps::OpTiming> GpuOps::DrainTimings() {
   }
   std::vector<OpTiming> out;
   for (auto& p : pending) {
-    OpTiming t = {p.type, p.bytes, p.tensors, 0.f};
+    OpTiming t = {p.type, p.bytes, p.tensors, 0.f, p.host_us};
     float ms = 0.f;
     if (cudaEventSynchronize(p.t1) == cudaSuccess &&
         cudaEventElapsedTime(&ms, p.t0, p.t1) == cudaSuccess)

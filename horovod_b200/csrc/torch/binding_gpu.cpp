@@ -60,7 +60,8 @@ void BindGpuDiagnostics(py::module_& m) {
     return d;
   });
   m.def("gpu_op_stats", []() {
-    // (response type, payload bytes, tensors, device microseconds) of every
+    // (response type, payload bytes, tensors, device microseconds, host
+    // microseconds from the first timing event to the last launch) of every
     // device collective since the last call; needs HOROVOD_GPU_OP_TIMING=1.
     py::list out;
     GpuOps* ops = CurrentGpuOps();
@@ -70,7 +71,7 @@ void BindGpuDiagnostics(py::module_& m) {
       py::gil_scoped_release release;
       t = ops->DrainTimings();
     }
-    for (auto& x : t) out.append(py::make_tuple(x.type, x.bytes, x.tensors, x.device_us));
+    for (auto& x : t) out.append(py::make_tuple(x.type, x.bytes, x.tensors, x.device_us, x.host_us));
     return out;
   });
   m.def("bounded_wait_probe", [](int device, int timeout_ms) {

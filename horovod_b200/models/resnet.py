@@ -8,6 +8,7 @@ import torch
 import torch.nn as nn
 
 from horovod_b200.ops.batch_norm import BatchNormAct2d
+from horovod_b200.ops.pooling import MaxPool3x3s2
 
 
 class Bottleneck(nn.Module):
@@ -40,7 +41,7 @@ class ResNet(nn.Module):
         self.inplanes = width
         self.conv1 = nn.Conv2d(3, width, 7, stride=2, padding=3, bias=False)
         self.bn1 = BatchNormAct2d(width, relu=True)
-        self.maxpool = nn.MaxPool2d(3, stride=2, padding=1)
+        self.maxpool = MaxPool3x3s2()  # 3x3, stride 2, padding 1
         self.layer1 = self._make_layer(width, layers[0])
         self.layer2 = self._make_layer(width * 2, layers[1], stride=2)
         self.layer3 = self._make_layer(width * 4, layers[2], stride=2)

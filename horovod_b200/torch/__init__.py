@@ -28,5 +28,6 @@ from horovod_b200.torch.mpi_ops import (Adasum, Average, Max, Min, Product, Sum,
                                         shutdown, size, sparse_allreduce_async,
                                         start_timeline, stop_timeline, symmetric_empty,
                                         synchronize, topology)
+from horovod_b200.torch.fused_sgd import FusedSGD
 from horovod_b200.torch.optimizer import DistributedOptimizer
 from horovod_b200.torch.sync_batch_norm import SyncBatchNorm

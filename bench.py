@@ -55,6 +55,8 @@ def parse_args():
                    choices=["resnet50", "bert-large", "gpt2-medium"])
     p.add_argument("--batch", type=int, default=0, help="per-GPU batch (0 = config default)")
     p.add_argument("--backend", default=None, help="symm | nccl (HOROVOD_GPU_BACKEND)")
+    p.add_argument("--fused-optimizer", type=int, default=1,
+                   help="1: ResNet uses hvd.FusedSGD (same arithmetic as torch.optim.SGD)")
     p.add_argument("--symmetric-gradients", type=int, default=1,
                    help="1: gradients live in the symmetric heap and are reduced in place")
     return p.parse_args()
@@ -118,7 +120,11 @@ def build_workload(args, torch, device):
     if args.model == "resnet50":
         batch = args.batch or 256
         model = models.resnet50().to(device).to(memory_format=torch.channels_last)
-        opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9, weight_decay=1e-4)
+        if getattr(args, "fused_optimizer", 0) and args.impl == "ours":
+            from horovod_b200.torch.fused_sgd import FusedSGD
+            opt = FusedSGD(model.parameters(), lr=0.01, momentum=0.9, weight_decay=1e-4)
+        else:
+            opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9, weight_decay=1e-4)
         g = torch.Generator().manual_seed(1)
         host_x = [torch.randn(batch, 3, 224, 224, generator=g).pin_memory() for _ in range(2)]
         host_y = [torch.randint(0, 1000, (batch,), generator=g).pin_memory() for _ in range(2)]
@@ -129,7 +135,10 @@ def build_workload(args, torch, device):
         def loss_fn(x, y):
             return torch.nn.functional.cross_entropy(model(x), y)
         cfg = {"model": "ResNet-50 v1.5", "global_batch": batch * args.gpus, "seq_len": None,
-               "optimizer": "SGD momentum 0.9 wd 1e-4, fp32 master weights",
+               "optimizer": "SGD momentum 0.9 wd 1e-4, fp32 master weights (%s)"
+                            % ("hvd.FusedSGD: torch.optim.SGD arithmetic in one launch"
+                               if isinstance(opt, torch.optim.Optimizer) and
+                               type(opt).__name__ == "FusedSGD" else "torch.optim.SGD"),
                "memory_format": "channels_last"}
         metric, unit = "resnet50_train_images_per_sec", "images/s"
         return model, opt, host_x, host_y, to_dev, loss_fn, batch, cfg, metric, unit
@@ -405,6 +414,7 @@ def measure(args, model_name, hvd, torch, device, _C):
     e2e_ms = float(hvd.allreduce(torch.tensor([e2e_ms], dtype=torch.float64), op=hvd.Max,
                                  name="bench.e2e_ms"))
 
+    n_param_bytes = sum(p.numel() * p.element_size() for p in model.parameters())
     in_sync, n_params = (True, 0)
     if hvd.size() > 1:
         in_sync, n_params = params_in_sync(hvd, torch, model)
@@ -414,8 +424,9 @@ def measure(args, model_name, hvd, torch, device, _C):
         total = batch * args.gpus * args.steps
         value = total / (ms / 1e3)
         cfg.update({"parallelism": "dp%d" % args.gpus, "per_gpu_batch": batch,
-                    "l2": "inputs larger than L2 (%.0f MB activations+batch per step)"
-                          % (h2d / 1e6),
+                    "l2": "working set larger than L2: %.0f MB of inputs per step plus "
+                          "activations and %.0f MB of parameters"
+                          % (h2d / 1e6, n_param_bytes / 1e6),
                     "data_per_rank": "the same batch on every rank, so the loss after K steps "
                                      "must not depend on the number of GPUs",
                     "gradient_path": hvd.gpu_backend(),

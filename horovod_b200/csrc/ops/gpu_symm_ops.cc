@@ -38,6 +38,16 @@ Status GpuOps::SymmAllreduce(std::vector<TensorTableEntry>& entries,
   const int64_t align_elems = FUSION_ALIGN_BYTES / ws;
 
   WaitForInputs(entries);
+  // A group of one that reduces in place with unit scale changes nothing:
+  // no kernel at all (what a single-GPU run of a data-parallel script does
+  // for every gradient).
+  if (set.world == 1 && !adasum && wire == dtype &&
+      response.prescale * response.postscale == 1.0) {
+    bool in_place = true;
+    for (auto& e : entries)
+      if (e.input != e.output) in_place = false;
+    if (in_place) return Complete(entries);
+  }
   tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
   // (A response with fewer devices than ranks means somebody has joined and
   // contributes zeros: everybody stages in that case.)

@@ -5,6 +5,8 @@
 #include <torch/extension.h>
 
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <tuple>
 #include <vector>
 
@@ -29,6 +31,36 @@ const float* FloatPtrOrNull(const c10::optional<at::Tensor>& t, int64_t channels
                   t->numel() == channels,
               what, " must be a contiguous float32 CUDA vector with one entry per channel");
   return t->data_ptr<float>();
+}
+
+// Zero-filled scratch for the batch-norm reductions without a fill launch per
+// call: slices are handed out from a per-stream pool that is cleared with one
+// memset whenever it has been used up. Slices are consumed in stream order
+// and the memset is queued behind their consumers, so a slice is zero when
+// the kernel that was given it runs.
+double* ZeroedDoubles(int64_t count, const at::Tensor& like, cudaStream_t stream) {
+  struct Pool {
+    at::Tensor buf;
+    int64_t used = 0;
+  };
+  constexpr int64_t POOL_DOUBLES = 1 << 20;  // 8 MB
+  static std::mutex mu;
+  static std::map<std::pair<int, cudaStream_t>, Pool> pools;
+  TORCH_CHECK(count <= POOL_DOUBLES, "batch norm scratch request too large");
+  std::lock_guard<std::mutex> lock(mu);
+  Pool& p = pools[{like.get_device(), stream}];
+  if (!p.buf.defined()) {
+    p.buf = at::zeros({POOL_DOUBLES}, like.options().dtype(at::kDouble));
+    p.used = 0;
+  }
+  const int64_t need = (count + 31) / 32 * 32;  // 256-byte slices
+  if (p.used + need > POOL_DOUBLES) {
+    cudaMemsetAsync(p.buf.data_ptr(), 0, POOL_DOUBLES * sizeof(double), stream);
+    p.used = 0;
+  }
+  double* out = p.buf.data_ptr<double>() + p.used;
+  p.used += need;
+  return out;
 }
 
 }  // namespace
@@ -61,7 +93,7 @@ void BindModelOps(py::module_& m) {
     at::Tensor y = at::empty_like(x, x.options(), at::MemoryFormat::ChannelsLast);
     auto fopt = x.options().dtype(at::kFloat);
     at::Tensor mean = at::empty({C}, fopt), invstd = at::empty({C}, fopt);
-    at::Tensor sums = at::zeros({2 * C}, x.options().dtype(at::kDouble));
+    double* sums = ZeroedDoubles(2 * C, x, stream);
     float* rm = nullptr;
     float* rv = nullptr;
     if (running_mean.has_value() && running_mean->defined()) {
@@ -71,7 +103,7 @@ void BindModelOps(py::module_& m) {
     }
     cudaError_t err = kern::LaunchBatchNormForward(
         x.data_ptr(), res, y.data_ptr(), M, static_cast<int>(C),
-        x.scalar_type() == at::kBFloat16, sums.data_ptr<double>(),
+        x.scalar_type() == at::kBFloat16, sums,
         FloatPtrOrNull(weight, C, "weight"), FloatPtrOrNull(bias, C, "bias"),
         static_cast<float>(eps), static_cast<float>(momentum), mean.data_ptr<float>(),
         invstd.data_ptr<float>(), rm, rv, relu, stream);
@@ -95,11 +127,11 @@ void BindModelOps(py::module_& m) {
     if (want_dresidual) dres = at::empty_like(x, x.options(), at::MemoryFormat::ChannelsLast);
     auto fopt = x.options().dtype(at::kFloat);
     at::Tensor dweight = at::empty({C}, fopt), dbias = at::empty({C}, fopt);
-    at::Tensor sums = at::zeros({2 * C}, x.options().dtype(at::kDouble));
+    double* sums = ZeroedDoubles(2 * C, x, stream);
     cudaError_t err = kern::LaunchBatchNormBackward(
         dy.data_ptr(), relu ? y.data_ptr() : nullptr, x.data_ptr(), dx.data_ptr(),
         want_dresidual ? dres.data_ptr() : nullptr, M, static_cast<int>(C),
-        x.scalar_type() == at::kBFloat16, sums.data_ptr<double>(),
+        x.scalar_type() == at::kBFloat16, sums,
         FloatPtrOrNull(weight, C, "weight"), save_mean.data_ptr<float>(),
         save_invstd.data_ptr<float>(), dweight.data_ptr<float>(), dbias.data_ptr<float>(), relu,
         stream);

@@ -83,20 +83,26 @@ class State:
         self.check_host_updates()
 
     def check_host_updates(self):
-        """Raises HostsUpdatedInterrupt on all ranks together if the driver
-        reported a change since the last check."""
-        last = prev = self._last_updated_timestamp
-        all_update = HostUpdateResult.no_update
-        while not self._host_messages.empty():
-            timestamp, update = self._host_messages.get()
-            if timestamp > last:
-                last = timestamp
-                all_update |= update
-        # Rank 0 decides so that everybody raises at the same commit.
-        prev, self._last_updated_timestamp, all_update = self._bcast_object(
-            (prev, last, all_update), name="hvd.elastic.host_updates")
-        if self._last_updated_timestamp > prev:
-            raise HostsUpdatedInterrupt(all_update == HostUpdateResult.removed)
+        """Raises HostsUpdatedInterrupt on all ranks at the same commit if the
+        driver has reported a host change since the last check. Rank 0's view
+        is the one that counts (the driver notifies rank 0 only): it is
+        broadcast, so no rank runs ahead of the others."""
+        seen_before = self._last_updated_timestamp
+        newest, combined = seen_before, HostUpdateResult.no_update
+        try:
+            while True:
+                stamp, change = self._host_messages.get_nowait()
+                if stamp > seen_before:
+                    newest = max(newest, stamp)
+                    combined |= change
+        except queue.Empty:
+            pass
+        seen_before, newest, combined = self._bcast_object(
+            (seen_before, newest, combined), name="hvd.elastic.host_updates")
+        self._last_updated_timestamp = newest
+        if newest > seen_before:
+            # Only removals: the survivors are already in sync with each other.
+            raise HostsUpdatedInterrupt(skip_sync=combined == HostUpdateResult.removed)
 
     def save(self):
         raise NotImplementedError()
@@ -112,31 +118,26 @@ class State:
 
 
 class ObjectState(State):
-    """State made of plain picklable attributes given as keyword arguments."""
+    """State made of plain picklable attributes given as keyword arguments:
+    ``ObjectState(..., epoch=0, batch=0)`` has ``.epoch`` and ``.batch``."""
 
     def __init__(self, bcast_object, get_rank, **kwargs):
-        self._saved_state = kwargs
-        self._set_attrs()
+        self._committed = dict(kwargs)
+        self.restore()
         super().__init__(bcast_object=bcast_object, get_rank=get_rank)
 
     def save(self):
-        new_state = {}
-        for attr in self._saved_state.keys():
-            new_state[attr] = getattr(self, attr)
-        self._saved_state = new_state
+        self._committed = {name: getattr(self, name) for name in self._committed}
 
     def restore(self):
-        self._set_attrs()
+        for name, value in self._committed.items():
+            setattr(self, name, value)
 
     def sync(self):
-        if self._saved_state:
-            self._saved_state = self._bcast_object(self._saved_state,
-                                                   name="hvd.elastic.object_state")
-            self._set_attrs()
-
-    def _set_attrs(self):
-        for attr, value in self._saved_state.items():
-            setattr(self, attr, value)
+        if not self._committed:
+            return
+        self._committed = self._bcast_object(self._committed, name="hvd.elastic.object_state")
+        self.restore()
 
 
 def run_fn(func, reset):

@@ -1,104 +1,126 @@
-"""Driver side of the launcher's RPC pair: tasks (one per host) register
-their addresses here, fetch each other's, and report which of the next
-task's interfaces they could reach. Parity:
-horovod/runner/common/service/driver_service.py:22-260."""
+"""Driver side of the launcher's RPC pair used for NIC discovery.
+
+One task service runs per host. Each task tells the driver where it listens
+(``register_task``), asks where its ring neighbour listens
+(``all_task_addresses``), probes the neighbour on every interface and reports
+the subset that answered (``register_task_to_task_addresses``). The driver
+keeps one record per task and lets the launcher wait until all tasks have
+registered, and later until all probe reports are in.
+
+The RPC surface follows horovod/runner/common/service/driver_service.py:22-260
+(same three calls, same waits); here one tagged message carries all three
+calls and one record per task holds everything known about it.
+"""
 import threading
 
 from horovod_b200.runner.common import network
 
+# Message kinds.
+REGISTER, LOOKUP, PROBE_REPORT = "register", "lookup", "probe_report"
 
-class RegisterTaskRequest:
-    def __init__(self, index, task_addresses, host_hash):
+
+class TaskMessage:
+    """``kind`` selects the call; ``index`` is the task it concerns."""
+
+    def __init__(self, kind, index, addresses=None, host_hash=None):
+        self.kind = kind
         self.index = index
-        self.task_addresses = task_addresses
+        self.addresses = addresses
         self.host_hash = host_hash
 
 
-class AllTaskAddressesRequest:
-    def __init__(self, index):
-        self.index = index
+class AddressesReply:
+    def __init__(self, addresses):
+        self.addresses = addresses
 
 
-class AllTaskAddressesResponse:
-    def __init__(self, all_task_addresses):
-        self.all_task_addresses = all_task_addresses
+class _TaskRecord:
+    def __init__(self):
+        self.listening = None     # every address the task listens on, by interface
+        self.from_driver = None   # the part of them the driver can route to
+        self.from_peer = None     # the part its ring predecessor could reach
+        self.host_hash = None
 
 
-class RegisterTaskToTaskAddressesRequest:
-    def __init__(self, index, task_addresses):
-        self.index = index
-        self.task_addresses = task_addresses
+def _as_tuples(addresses):
+    return {nic: [tuple(a) for a in addrs] for nic, addrs in addresses.items()}
+
+
+def _interface_of(addresses, ip):
+    """The interface entry that contains ``ip`` (the registration arrived
+    through it, so the driver can reach the task there); everything when the
+    source address is not one the task listed (NAT, loopback aliases)."""
+    for nic, addrs in addresses.items():
+        if any(a[0] == ip for a in addrs):
+            return {nic: [tuple(a) for a in addrs]}
+    return _as_tuples(addresses)
 
 
 class BasicDriverService(network.BasicService):
     def __init__(self, num_proc, name, key, nics=None):
         super().__init__(name, key, nics)
         self._num_proc = num_proc
-        self._all_task_addresses = {}
-        self._task_addresses_for_driver = {}
-        self._task_addresses_for_tasks = {}
-        self._task_index_host_hash = {}
-        self._task_host_hash_indices = {}
-        self._wait_cond = threading.Condition()
+        self._tasks = {}
+        self._changed = threading.Condition()
+
+    def _record(self, index):
+        if not 0 <= index < self._num_proc:
+            raise ValueError("task index %r out of range (0..%d)" % (index, self._num_proc - 1))
+        return self._tasks.setdefault(index, _TaskRecord())
 
     def _handle(self, req, client_address):
-        if isinstance(req, RegisterTaskRequest):
-            with self._wait_cond:
-                assert 0 <= req.index < self._num_proc
-                self._all_task_addresses[req.index] = req.task_addresses
-                # Which of the task's addresses the driver can route to: the ones on
-                # the interface the registration arrived from.
-                self._task_addresses_for_driver[req.index] = \
-                    self._filter_by_ip(req.task_addresses, client_address[0])
-                self._task_index_host_hash[req.index] = req.host_hash
-                self._task_host_hash_indices.setdefault(req.host_hash, []).append(req.index)
-                self._task_host_hash_indices[req.host_hash].sort()
-                self._wait_cond.notify_all()
-            return network.AckResponse()
-        if isinstance(req, AllTaskAddressesRequest):
-            return AllTaskAddressesResponse(self._all_task_addresses[req.index])
-        if isinstance(req, RegisterTaskToTaskAddressesRequest):
-            with self._wait_cond:
-                self._task_addresses_for_tasks[req.index] = req.task_addresses
-                self._wait_cond.notify_all()
-            return network.AckResponse()
-        return super()._handle(req, client_address)
+        if not isinstance(req, TaskMessage):
+            return super()._handle(req, client_address)
+        with self._changed:
+            if req.kind == LOOKUP:
+                return AddressesReply(self._tasks[req.index].listening)
+            rec = self._record(req.index)
+            if req.kind == REGISTER:
+                rec.listening = req.addresses
+                rec.from_driver = _interface_of(req.addresses, client_address[0])
+                rec.host_hash = req.host_hash
+            elif req.kind == PROBE_REPORT:
+                rec.from_peer = req.addresses
+            else:
+                raise ValueError("unknown task message %r" % req.kind)
+            self._changed.notify_all()
+        return network.AckResponse()
 
-    @staticmethod
-    def _filter_by_ip(addresses, ip):
-        for intf, intf_addresses in addresses.items():
-            for address in intf_addresses:
-                if address[0] == ip:
-                    return {intf: [tuple(a) for a in intf_addresses]}
-        return {k: [tuple(a) for a in v] for k, v in addresses.items()}
-
+    # ---- what the launcher reads ----------------------------------------------
     def all_task_addresses(self, index):
-        with self._wait_cond:
-            return dict(self._all_task_addresses[index])
+        with self._changed:
+            return dict(self._tasks[index].listening)
 
     def task_addresses_for_driver(self, index):
-        with self._wait_cond:
-            return dict(self._task_addresses_for_driver[index])
+        with self._changed:
+            return dict(self._tasks[index].from_driver)
 
     def task_addresses_for_tasks(self, index):
-        with self._wait_cond:
-            return dict(self._task_addresses_for_tasks[index])
+        with self._changed:
+            return dict(self._tasks[index].from_peer)
 
     def task_host_hash_indices(self):
-        with self._wait_cond:
-            return {k: list(v) for k, v in self._task_host_hash_indices.items()}
+        """host hash -> sorted indices of the tasks that run on that host."""
+        with self._changed:
+            by_host = {}
+            for index in sorted(self._tasks):
+                rec = self._tasks[index]
+                if rec.listening is not None:
+                    by_host.setdefault(rec.host_hash, []).append(index)
+            return by_host
+
+    def _wait_until_all(self, have, timeout, activity):
+        with self._changed:
+            while sum(1 for r in self._tasks.values() if have(r)) < self._num_proc:
+                self._changed.wait(timeout.remaining())
+                timeout.check_time_out_for(activity)
 
     def wait_for_initial_registration(self, timeout):
-        with self._wait_cond:
-            while len(self._all_task_addresses) < self._num_proc:
-                self._wait_cond.wait(timeout.remaining())
-                timeout.check_time_out_for("tasks to start")
+        self._wait_until_all(lambda r: r.listening is not None, timeout, "tasks to start")
 
     def wait_for_task_to_task_address_updates(self, timeout):
-        with self._wait_cond:
-            while len(self._task_addresses_for_tasks) < self._num_proc:
-                self._wait_cond.wait(timeout.remaining())
-                timeout.check_time_out_for("tasks to update task-to-task addresses")
+        self._wait_until_all(lambda r: r.from_peer is not None, timeout,
+                             "tasks to update task-to-task addresses")
 
 
 class BasicDriverClient(network.BasicClient):
@@ -106,10 +128,10 @@ class BasicDriverClient(network.BasicClient):
         super().__init__(name, driver_addresses, key, verbose, match_intf=match_intf)
 
     def register_task(self, index, task_addresses, host_hash):
-        self._send(RegisterTaskRequest(index, task_addresses, host_hash))
+        self._send(TaskMessage(REGISTER, index, task_addresses, host_hash))
 
     def all_task_addresses(self, index):
-        return self._send(AllTaskAddressesRequest(index)).all_task_addresses
+        return self._send(TaskMessage(LOOKUP, index)).addresses
 
     def register_task_to_task_addresses(self, index, task_addresses):
-        self._send(RegisterTaskToTaskAddressesRequest(index, task_addresses))
+        self._send(TaskMessage(PROBE_REPORT, index, task_addresses))

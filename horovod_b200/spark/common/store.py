@@ -1,201 +1,162 @@
-"""Where a training run keeps its intermediate datasets, checkpoints and
-logs. ``Store.create(prefix_path)`` picks the implementation from the path;
-only plain filesystem paths (local disk, NFS, FUSE mounts) are built here:
-HDFS / DBFS / S3 URLs are refused with a clear message.
-Parity: horovod/spark/common/store.py:36-536 (Store, AbstractFilesystemStore,
-LocalStore)."""
+"""Where a training run keeps intermediate datasets, checkpoints and logs.
+
+A store is a directory tree:
+
+    <prefix>/intermediate_{train,val,test}_data[.<idx>]   datasets (Parquet)
+    <prefix>/runs/<run_id>/checkpoint                      model checkpoint
+    <prefix>/runs/<run_id>/logs/                           training logs
+
+``Store.create(prefix_path)`` returns a ``LocalStore``: only paths the
+operating system can open are supported here (local disk, NFS, FUSE mounts);
+URLs of remote object stores are refused with a message saying so. Workers
+write into a private local directory and publish it with ``sync_fn``.
+
+The method names are those of horovod/spark/common/store.py:36-536 (Store,
+AbstractFilesystemStore, LocalStore), which estimators and remote trainers
+call; the layout is data-driven here instead of one method body per path.
+"""
 import contextlib
 import os
 import shutil
 import tempfile
 
+_REMOTE_SCHEMES = ("hdfs://", "dbfs:/", "s3://", "s3a://", "gs://", "abfs://")
+_DATASETS = {"train": "intermediate_train_data", "val": "intermediate_val_data",
+             "test": "intermediate_test_data"}
+_CHECKPOINT_FILE, _LOGS_DIR = "checkpoint", "logs"
+
+
+def _local(path):
+    """file:// URLs and plain paths name the same thing."""
+    return path[len("file://"):] if path.startswith("file://") else path
+
 
 class Store:
-    """Abstract layout: <prefix>/intermediate_train_data[.idx], .../runs/<run_id>/
-    {checkpoint, logs}."""
-
-    def is_parquet_dataset(self, path):
-        raise NotImplementedError()
-
-    def get_train_data_path(self, idx=None):
-        raise NotImplementedError()
-
-    def get_val_data_path(self, idx=None):
-        raise NotImplementedError()
-
-    def get_test_data_path(self, idx=None):
-        raise NotImplementedError()
-
-    def saving_runs(self):
-        raise NotImplementedError()
-
-    def get_runs_path(self):
-        raise NotImplementedError()
-
-    def get_run_path(self, run_id):
-        raise NotImplementedError()
-
-    def get_checkpoint_path(self, run_id):
-        raise NotImplementedError()
-
-    def get_logs_path(self, run_id):
-        raise NotImplementedError()
-
-    def get_checkpoint_filename(self):
-        raise NotImplementedError()
-
-    def get_logs_subdir(self):
-        raise NotImplementedError()
-
-    def exists(self, path):
-        raise NotImplementedError()
-
-    def read(self, path):
-        raise NotImplementedError()
-
-    def write_text(self, path, text):
-        raise NotImplementedError()
-
-    def sync_fn(self, run_id):
-        """Returns fn(local_run_path) that publishes a worker's local run
-        directory (checkpoint, logs) into the store."""
-        raise NotImplementedError()
-
-    def to_remote(self, run_id, dataset_idx):
-        """A picklable view with the paths a remote trainer needs."""
-        attrs = self._remote_attrs(run_id, dataset_idx)
-
-        class RemoteStore:
-            def __init__(self):
-                self.__dict__.update(attrs)
-
-        return RemoteStore()
-
-    def _remote_attrs(self, run_id, dataset_idx):
-        return {
-            "train_data_path": self.get_train_data_path(dataset_idx),
-            "val_data_path": self.get_val_data_path(dataset_idx),
-            "test_data_path": self.get_test_data_path(dataset_idx),
-            "saving_runs": self.saving_runs(),
-            "runs_path": self.get_runs_path(),
-            "run_path": self.get_run_path(run_id),
-            "checkpoint_path": self.get_checkpoint_path(run_id),
-            "logs_path": self.get_logs_path(run_id),
-            "checkpoint_filename": self.get_checkpoint_filename(),
-            "logs_subdir": self.get_logs_subdir(),
-            "sync": self.sync_fn(run_id),
-        }
+    """Interface. ``FilesystemStore`` is the one implementation built here."""
 
     @staticmethod
     def create(prefix_path, *args, **kwargs):
-        for scheme in ("hdfs://", "dbfs:/", "s3://", "s3a://", "gs://", "abfs://"):
-            if prefix_path.startswith(scheme):
-                raise ValueError(
-                    "Only filesystem paths are supported by this build (got %r); mount the "
-                    "remote filesystem and pass the mount point." % prefix_path)
+        if prefix_path.startswith(_REMOTE_SCHEMES):
+            raise ValueError(
+                "Only filesystem paths are supported by this build (got %r); mount the "
+                "remote filesystem and pass the mount point." % prefix_path)
         return LocalStore(prefix_path, *args, **kwargs)
+
+    def to_remote(self, run_id, dataset_idx):
+        """A small picklable object with just the paths (and the sync
+        function) a trainer on another machine needs."""
+        view = _RemoteView()
+        view.train_data_path = self.get_train_data_path(dataset_idx)
+        view.val_data_path = self.get_val_data_path(dataset_idx)
+        view.test_data_path = self.get_test_data_path(dataset_idx)
+        view.saving_runs = self.saving_runs()
+        view.runs_path = self.get_runs_path()
+        view.run_path = self.get_run_path(run_id)
+        view.checkpoint_path = self.get_checkpoint_path(run_id)
+        view.logs_path = self.get_logs_path(run_id)
+        view.checkpoint_filename = self.get_checkpoint_filename()
+        view.logs_subdir = self.get_logs_subdir()
+        view.sync = self.sync_fn(run_id)
+        return view
+
+
+class _RemoteView:
+    pass
 
 
 class FilesystemStore(Store):
-    """Store over anything the operating system presents as a directory tree."""
-
     def __init__(self, prefix_path, train_path=None, val_path=None, test_path=None,
                  runs_path=None, save_runs=True):
-        self.prefix_path = self._strip(prefix_path)
-        self._train_path = train_path or self._join("intermediate_train_data")
-        self._val_path = val_path or self._join("intermediate_val_data")
-        self._test_path = test_path or self._join("intermediate_test_data")
-        self._runs_path = runs_path or self._join("runs")
+        self.prefix_path = _local(prefix_path)
+        given = {"train": train_path, "val": val_path, "test": test_path}
+        self._data = {kind: given[kind] or os.path.join(self.prefix_path, name)
+                      for kind, name in _DATASETS.items()}
+        self._runs = runs_path or os.path.join(self.prefix_path, "runs")
         self._save_runs = save_runs
 
-    @staticmethod
-    def _strip(path):
-        return path[len("file://"):] if path.startswith("file://") else path
-
-    def _join(self, *parts):
-        return os.path.join(self.prefix_path, *parts)
-
-    @staticmethod
-    def _indexed(path, idx):
-        return "%s.%s" % (path, idx) if idx is not None else path
-
-    def is_parquet_dataset(self, path):
-        path = self._strip(path)
-        if not os.path.isdir(path):
-            return False
-        return any(f.endswith(".parquet") or f == "_metadata" or f == "_common_metadata"
-                   for f in os.listdir(path))
+    # ---- datasets -----------------------------------------------------------
+    def _dataset(self, kind, idx):
+        base = self._data[kind]
+        return base if idx is None else "%s.%s" % (base, idx)
 
     def get_train_data_path(self, idx=None):
-        return self._indexed(self._train_path, idx)
+        return self._dataset("train", idx)
 
     def get_val_data_path(self, idx=None):
-        return self._indexed(self._val_path, idx)
+        return self._dataset("val", idx)
 
     def get_test_data_path(self, idx=None):
-        return self._indexed(self._test_path, idx)
+        return self._dataset("test", idx)
 
+    def is_parquet_dataset(self, path):
+        path = _local(path)
+        try:
+            names = os.listdir(path)
+        except (FileNotFoundError, NotADirectoryError):
+            return False
+        return any(n.endswith(".parquet") or n in ("_metadata", "_common_metadata")
+                   for n in names)
+
+    # ---- runs -----------------------------------------------------------------
     def saving_runs(self):
         return self._save_runs
 
     def get_runs_path(self):
-        return self._runs_path
+        return self._runs
 
     def get_run_path(self, run_id):
-        return os.path.join(self._runs_path, run_id)
-
-    def get_checkpoint_path(self, run_id):
-        return os.path.join(self.get_run_path(run_id), self.get_checkpoint_filename()) \
-            if self._save_runs else None
-
-    def get_logs_path(self, run_id):
-        return os.path.join(self.get_run_path(run_id), self.get_logs_subdir()) \
-            if self._save_runs else None
+        return os.path.join(self._runs, run_id)
 
     def get_checkpoint_filename(self):
-        return "checkpoint"
+        return _CHECKPOINT_FILE
 
     def get_logs_subdir(self):
-        return "logs"
+        return _LOGS_DIR
 
+    def _in_run(self, run_id, leaf):
+        return os.path.join(self.get_run_path(run_id), leaf) if self._save_runs else None
+
+    def get_checkpoint_path(self, run_id):
+        return self._in_run(run_id, _CHECKPOINT_FILE)
+
+    def get_logs_path(self, run_id):
+        return self._in_run(run_id, _LOGS_DIR)
+
+    # ---- file access ----------------------------------------------------------
     def exists(self, path):
-        return os.path.exists(self._strip(path))
+        return os.path.exists(_local(path))
 
     def read(self, path):
-        with open(self._strip(path), "rb") as f:
+        with open(_local(path), "rb") as f:
             return f.read()
 
     def write_text(self, path, text):
-        path = self._strip(path)
+        path = _local(path)
         os.makedirs(os.path.dirname(path), exist_ok=True)
         with open(path, "w") as f:
             f.write(text)
 
     def get_local_output_dir_fn(self, run_id):
+        """A context manager factory: a scratch directory for one worker's
+        checkpoint and logs, removed afterwards."""
         @contextlib.contextmanager
-        def local_run_path():
-            path = tempfile.mkdtemp(prefix="hvd_run_%s_" % run_id)
-            try:
+        def scratch():
+            with tempfile.TemporaryDirectory(prefix="hvd_run_%s_" % run_id) as path:
                 yield path
-            finally:
-                shutil.rmtree(path, ignore_errors=True)
-        return local_run_path
+        return scratch
 
     def sync_fn(self, run_id):
-        run_path = self.get_run_path(run_id)
+        """fn(local_dir): merges a worker's scratch directory into the run's
+        directory in the store."""
+        target = self.get_run_path(run_id)
 
-        def fn(local_run_path):
-            for root, _dirs, files in os.walk(local_run_path):
-                rel = os.path.relpath(root, local_run_path)
-                dst_dir = run_path if rel == "." else os.path.join(run_path, rel)
-                os.makedirs(dst_dir, exist_ok=True)
-                for name in files:
-                    shutil.copy2(os.path.join(root, name), os.path.join(dst_dir, name))
-        return fn
+        def publish(local_dir):
+            shutil.copytree(local_dir, target, dirs_exist_ok=True)
+        return publish
 
 
 class LocalStore(FilesystemStore):
-    """Local disk (or any mounted filesystem)."""
+    """A store on local disk (or any mounted filesystem); creates the prefix."""
 
     def __init__(self, prefix_path, *args, **kwargs):
         super().__init__(prefix_path, *args, **kwargs)

@@ -1,78 +1,75 @@
-"""Sampler that can be repartitioned when the number of workers changes and
-that remembers which samples of the current epoch were already consumed.
+"""Sampler for elastic training: it splits the samples of an epoch that have
+not been consumed yet among however many ranks there are right now, so an
+epoch can continue across a change of membership without repeating data.
 
-Parity: horovod/torch/elastic/sampler.py:24-132.
+The training loop calls ``record_batch(batch_idx, batch_size)`` after every
+batch (before ``state.commit()``) and ``set_epoch(epoch)`` when an epoch ends;
+``hvd.elastic.TorchState(sampler=...)`` merges the consumed sets of all ranks
+at every sync and calls ``reset()``.
+
+API and semantics follow horovod/torch/elastic/sampler.py:24-132 (every rank
+draws the same number of samples; the tail is padded by repeating the head).
 """
-import math
 import random
 
-import torch.utils.data.distributed
+import torch.utils.data
 
-from horovod_b200.torch.mpi_ops import rank, size
+from horovod_b200.torch.mpi_ops import is_initialized, rank, size
 
 
 class ElasticSampler(torch.utils.data.Sampler):
-    """Partitions the not-yet-processed indices of ``dataset`` among the
-    current ranks. Call ``record_batch(batch_idx, batch_size)`` after each
-    batch (before ``state.commit()``), and ``set_epoch(epoch)`` at the end of
-    each epoch."""
-
     def __init__(self, dataset, shuffle=True, seed=0):
         self.dataset = dataset
         self.shuffle = shuffle
         self.seed = seed
         self.epoch = 0
         self.processed_indices = set()
-        self.num_replicas = 0
-        self.rank = 0
-        self.remaining_indices = []
-        self.num_samples = 0
-        self.total_size = 0
+        self.indices = []
         self.reset()
 
+    # ---- bookkeeping the training loop drives --------------------------------
     def set_epoch(self, epoch):
-        """Starts a new epoch: clears the processed set and reshuffles."""
+        """A new epoch: nothing is consumed yet, and the shuffle changes."""
         self.epoch = epoch
         self.processed_indices = set()
         self.reset()
 
+    def get_indices(self, batch_idx, batch_size):
+        """Dataset indices this rank used for batch ``batch_idx`` of the
+        current pass."""
+        first = batch_idx * batch_size
+        return self.indices[first:first + batch_size]
+
     def record_batch(self, batch_idx, batch_size):
-        """Marks the indices of batch ``batch_idx`` as processed."""
         self.processed_indices.update(self.get_indices(batch_idx, batch_size))
 
-    def get_indices(self, batch_idx, batch_size):
-        start = batch_idx * batch_size
-        end = min(start + batch_size, len(self.indices))
-        return self.indices[start:end]
+    def state_dict(self):
+        return {"epoch": self.epoch, "processed_indices": set(self.processed_indices)}
 
     def load_state_dict(self, state_dict):
         self.epoch = state_dict["epoch"]
         self.processed_indices = set(state_dict["processed_indices"])
         self.reset()
 
-    def state_dict(self):
-        return dict(epoch=self.epoch, processed_indices=set(self.processed_indices))
-
+    # ---- partitioning ---------------------------------------------------------
     def reset(self):
-        """Recomputes this rank's share for the current world size."""
-        from horovod_b200.torch.mpi_ops import is_initialized
-        self.num_replicas = size() if is_initialized() else 1
-        self.rank = rank() if is_initialized() else 0
-        self.remaining_indices = [idx for idx in range(len(self.dataset))
-                                  if idx not in self.processed_indices]
-        self.num_samples = int(math.ceil(len(self.remaining_indices) * 1.0 / self.num_replicas))
+        """Re-reads the world size and recomputes what is left to share out."""
+        self.num_replicas, self.rank = (size(), rank()) if is_initialized() else (1, 0)
+        done = self.processed_indices
+        self.remaining_indices = [i for i in range(len(self.dataset)) if i not in done]
+        # ceil(remaining / replicas) samples per rank
+        self.num_samples = -(-len(self.remaining_indices) // self.num_replicas)
         self.total_size = self.num_samples * self.num_replicas
 
     def __iter__(self):
-        self.indices = self.remaining_indices[:]
+        order = list(self.remaining_indices)
         if self.shuffle:
-            random.Random(self.seed + self.epoch).shuffle(self.indices)
-        # Pad so that every rank gets the same number of samples.
-        if self.indices:
-            while len(self.indices) < self.total_size:
-                self.indices += self.indices[:(self.total_size - len(self.indices))]
-        self.indices = self.indices[self.rank:self.total_size:self.num_replicas]
-        assert len(self.indices) == self.num_samples or not self.remaining_indices
+            random.Random(self.seed + self.epoch).shuffle(order)
+        # Every rank must draw the same number of samples: wrap around.
+        short = self.total_size - len(order)
+        if order and short > 0:
+            order += [order[i % len(order)] for i in range(short)]
+        self.indices = order[self.rank:self.total_size:self.num_replicas]
         return iter(self.indices)
 
     def __len__(self):

@@ -1,20 +1,41 @@
-"""Elastic state for PyTorch: model, optimizer, sampler and plain attributes.
+"""Elastic state for PyTorch.
 
-Parity: horovod/torch/elastic/state.py:27-179.
+``TorchState(model=..., optimizer=..., sampler=..., epoch=0, batch=0)`` keeps
+an in-memory checkpoint of everything a training loop needs to continue after
+the set of workers changed: ``commit()`` snapshots it, ``restore()`` rolls
+back to the last snapshot, ``sync()`` makes every rank adopt rank 0's values.
+How a value is snapshotted and synchronised depends on its type: modules,
+optimizers and ElasticSamplers go through their ``state_dict``; anything else
+is a plain picklable attribute handled by ``ObjectState``.
+
+Behaviour follows horovod/torch/elastic/state.py:27-179; the type-to-handler
+registry (``get_handler_registry`` / ``set_handler_registry``) is kept so that
+users can add their own kinds of state.
 """
-import copy
-
 import torch
 
 from horovod_b200.common.elastic import ObjectState
 from horovod_b200.torch.elastic.sampler import ElasticSampler
-from horovod_b200.torch.functions import (broadcast_object, broadcast_optimizer_state,
-                                          broadcast_parameters)
+from horovod_b200.torch.functions import (allgather_object, broadcast_object,
+                                          broadcast_optimizer_state, broadcast_parameters)
 from horovod_b200.torch.mpi_ops import rank
 
 
+def _snapshot(obj):
+    """A private copy of a (nested) state_dict: tensors are cloned where they
+    live, containers are rebuilt, everything else is kept as it is (numbers,
+    strings, None are immutable)."""
+    if isinstance(obj, torch.Tensor):
+        return obj.detach().clone()
+    if isinstance(obj, dict):
+        return type(obj)((k, _snapshot(v)) for k, v in obj.items())
+    if isinstance(obj, (list, tuple, set, frozenset)):
+        return type(obj)(_snapshot(v) for v in obj)
+    return obj
+
+
 class StateHandler:
-    """Knows how to save/restore/sync one kind of value."""
+    """Knows how to save, restore and synchronise one kind of value."""
 
     def __init__(self, value):
         self.value = value
@@ -29,63 +50,50 @@ class StateHandler:
         raise NotImplementedError()
 
     def set_value(self, value):
+        """The attribute was re-assigned: track the new object from now on."""
         self.value = value
         self.save()
 
 
-class ModelStateHandler(StateHandler):
-    def __init__(self, model):
-        super().__init__(model)
-        self._saved = copy.deepcopy(model.state_dict())
+class _StateDictHandler(StateHandler):
+    """For anything with ``state_dict()`` / ``load_state_dict()``: the
+    checkpoint is a private copy of the state_dict."""
+
+    def __init__(self, value):
+        super().__init__(value)
+        self._checkpoint = None
+        self.save()
 
     def save(self):
-        self._saved = copy.deepcopy(self.value.state_dict())
+        self._checkpoint = _snapshot(self.value.state_dict())
 
     def restore(self):
-        self.value.load_state_dict(self._saved)
+        # load_state_dict may keep references to what it is given (optimizers
+        # do), so hand out a copy and keep the checkpoint pristine.
+        self.value.load_state_dict(_snapshot(self._checkpoint))
 
+
+class ModelStateHandler(_StateDictHandler):
     def sync(self):
         broadcast_parameters(self.value.state_dict(), root_rank=0)
 
 
-class OptimizerStateHandler(StateHandler):
-    def __init__(self, optimizer):
-        super().__init__(optimizer)
-        self._saved = copy.deepcopy(optimizer.state_dict())
-
-    def save(self):
-        self._saved = copy.deepcopy(self.value.state_dict())
-
-    def restore(self):
-        self.value.load_state_dict(self._saved)
-
+class OptimizerStateHandler(_StateDictHandler):
     def sync(self):
         broadcast_optimizer_state(self.value, root_rank=0)
 
 
-class SamplerStateHandler(StateHandler):
-    def __init__(self, sampler):
-        super().__init__(sampler)
-        self._saved = copy.deepcopy(sampler.state_dict())
-
-    def save(self):
-        self._saved = copy.deepcopy(self.value.state_dict())
-
-    def restore(self):
-        self.value.load_state_dict(self._saved)
-
+class SamplerStateHandler(_StateDictHandler):
     def sync(self):
-        # Union of what every rank processed, then repartition.
-        from horovod_b200.torch.functions import allgather_object
-        state = self.value.state_dict()
-        all_processed = allgather_object(state["processed_indices"],
-                                         name="hvd.elastic.sampler")
-        merged = set()
-        for s in all_processed:
-            merged |= set(s)
-        state["processed_indices"] = merged
-        state = broadcast_object(state, 0, name="hvd.elastic.sampler_state")
-        self.value.load_state_dict(state)
+        # What any rank has processed is processed for everybody; then all
+        # ranks take rank 0's view and repartition the rest.
+        mine = self.value.state_dict()
+        done = set()
+        for part in allgather_object(mine["processed_indices"], name="hvd.elastic.sampler"):
+            done.update(part)
+        mine["processed_indices"] = done
+        self.value.load_state_dict(
+            broadcast_object(mine, 0, name="hvd.elastic.sampler_state"))
 
 
 _handler_registry = [
@@ -104,36 +112,28 @@ def set_handler_registry(registry):
     _handler_registry = registry
 
 
-def _get_handler(v):
-    for handler_type, handler_cls in _handler_registry:
-        if isinstance(v, handler_type):
-            return handler_cls(v)
+def _handler_for(value):
+    for kind, factory in _handler_registry:
+        if isinstance(value, kind):
+            return factory(value)
     return None
 
 
-def _get_handlers(kwargs):
-    handlers, remainder = {}, {}
-    for k, v in kwargs.items():
-        h = _get_handler(v)
-        if h is not None:
-            handlers[k] = h
-        else:
-            remainder[k] = v
-    return handlers, remainder
-
-
 class TorchState(ObjectState):
-    """``TorchState(model=..., optimizer=..., sampler=..., epoch=0, batch=0)``.
-    Modules, optimizers and ElasticSamplers get dedicated handlers; everything
-    else is treated as a picklable attribute."""
-
     def __init__(self, model=None, optimizer=None, **kwargs):
-        kwargs.update(dict(model=model, optimizer=optimizer))
-        kwargs = {k: v for k, v in kwargs.items() if v is not None}
-        self._handlers, kwargs = _get_handlers(kwargs)
-        for name, handler in self._handlers.items():
-            setattr(self, name, handler.value)
-        super().__init__(bcast_object=broadcast_object, get_rank=rank, **kwargs)
+        # Only the two named arguments are optional; a user attribute that
+        # happens to be None stays an attribute.
+        named = {k: v for k, v in (("model", model), ("optimizer", optimizer)) if v is not None}
+        self._handlers = {}
+        plain = {}
+        for name, value in {**kwargs, **named}.items():
+            handler = _handler_for(value)
+            if handler is None:
+                plain[name] = value
+            else:
+                self._handlers[name] = handler
+                object.__setattr__(self, name, value)
+        super().__init__(bcast_object=broadcast_object, get_rank=rank, **plain)
 
     def save(self):
         for handler in self._handlers.values():
@@ -151,6 +151,7 @@ class TorchState(ObjectState):
         super().sync()
 
     def __setattr__(self, name, value):
-        if hasattr(self, name) and name in getattr(self, "_handlers", {}):
-            self._handlers[name].set_value(value)
+        handlers = self.__dict__.get("_handlers")
+        if handlers and name in handlers:
+            handlers[name].set_value(value)
         super().__setattr__(name, value)

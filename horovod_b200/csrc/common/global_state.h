@@ -41,6 +41,13 @@ struct GlobalState {
   InitConfig config;
   bool is_homogeneous = true;
   std::vector<int> local_sizes;  // local_size of every rank
+  // Ranks that share this rank's host (its cross_rank), and ranks with this
+  // rank's local_rank on the other hosts: the two levels of the hierarchical
+  // collectives. `hierarchy_usable` says that every host runs the same number
+  // of ranks and that global ranks are numbered host by host, which those
+  // algorithms rely on.
+  Comm local_comm, cross_comm;
+  bool hierarchy_usable = false;
 
   TcpMesh mesh;
   Timeline timeline;

@@ -180,6 +180,22 @@ void DiscoverLayout(GlobalState& s) {
   s.is_homogeneous = true;
   for (auto v : sizes)
     if (v != sizes[0]) s.is_homogeneous = false;
+  // Who sits where: (cross_rank, local_rank) of every rank.
+  std::vector<int32_t> place(static_cast<size_t>(world.size()) * 2);
+  int32_t me[2] = {s.config.cross_rank, s.config.local_rank};
+  world.Allgather(me, sizeof(me), place.data());
+  std::vector<int> same_host, same_slot;
+  bool host_major = s.is_homogeneous;
+  for (int r = 0; r < world.size(); ++r) {
+    if (place[2 * r] == s.config.cross_rank) same_host.push_back(r);
+    if (place[2 * r + 1] == s.config.local_rank) same_slot.push_back(r);
+    if (r != place[2 * r] * s.config.local_size + place[2 * r + 1]) host_major = false;
+  }
+  s.local_comm = world.Subset(same_host);
+  s.cross_comm = world.Subset(same_slot);
+  s.hierarchy_usable = host_major && s.config.local_size > 1 && s.config.cross_size > 1 &&
+                       static_cast<int>(same_host.size()) == s.config.local_size &&
+                       static_cast<int>(same_slot.size()) == s.config.cross_size;
 }
 
 void BackgroundThreadLoop(GlobalState& s) {

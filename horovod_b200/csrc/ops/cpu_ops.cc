@@ -1,9 +1,12 @@
 #include "cpu_ops.h"
 
+#include <algorithm>
 #include <cfloat>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
+#include "../common/fusion_buffer_manager.h"
 #include "../common/global_state.h"
 #include "../common/half.h"
 #include "../common/logging.h"
@@ -39,7 +42,10 @@ void StoreFromDouble(void* p, int64_t i, DataType t, double v) {
 
 class CpuOps : public OpExecutor {
 public:
-  explicit CpuOps(GlobalState& s) : state_(s) {}
+  explicit CpuOps(GlobalState& s)
+      : state_(s),
+        buffers_([](size_t n) { return std::malloc(std::max<size_t>(n, 1)); },
+                 [](void* p) { std::free(p); }) {}
 
   Status Execute(std::vector<TensorTableEntry>& entries,
                  const Response& response, ProcessSet& ps) override {
@@ -82,12 +88,13 @@ private:
       buf = e.output;
     } else {
       tl.ActivityStartAll(entries, HVD_ACT_MEMCPY_IN_FUSION_BUFFER);
-      fusion_.assign(static_cast<size_t>(total * es), 0);
+      char* fusion = Fusion(static_cast<size_t>(total * es));
+      std::memset(fusion, 0, static_cast<size_t>(total * es));
       for (size_t i = 0; i < entries.size(); ++i)
         if (entries[i].input != nullptr)
-          std::memcpy(fusion_.data() + offsets[i] * es, entries[i].input,
+          std::memcpy(fusion + offsets[i] * es, entries[i].input,
                       static_cast<size_t>(counts[i] * es));
-      buf = fusion_.data();
+      buf = fusion;
       tl.ActivityEndAll(entries);
     }
     ScaleBufferCPU(buf, total, dtype, response.prescale);
@@ -97,7 +104,11 @@ private:
       AdasumCPU(ps.comm, buf, dtype, offsets, counts, total);
     } else {
       tl.ActivityStartAll(entries, HVD_ACT_CPU_ALLREDUCE);
-      ps.comm.Allreduce(buf, total, dtype, response.reduce_op);
+      if (ps.id == 0 && state_.hierarchy_usable &&
+          state_.parameter_manager.HierarchicalAllreduce())
+        HierarchicalAllreduce(buf, total, dtype, response.reduce_op);
+      else
+        ps.comm.Allreduce(buf, total, dtype, response.reduce_op);
     }
     tl.ActivityEndAll(entries);
     ScaleBufferCPU(buf, total, dtype, response.postscale);
@@ -105,7 +116,7 @@ private:
       tl.ActivityStartAll(entries, HVD_ACT_MEMCPY_OUT_FUSION_BUFFER);
       for (size_t i = 0; i < entries.size(); ++i)
         if (entries[i].output != nullptr)
-          std::memcpy(entries[i].output, fusion_.data() + offsets[i] * es,
+          std::memcpy(entries[i].output, static_cast<char*>(buf) + offsets[i] * es,
                       static_cast<size_t>(counts[i] * es));
       tl.ActivityEndAll(entries);
     }
@@ -137,7 +148,11 @@ private:
       if (!st.ok()) return st;
       e.output = out;
       tl.ActivityStart(e.name, HVD_ACT_CPU_ALLGATHER);
-      ps.comm.Allgatherv(e.input, lens, out);
+      if (ps.id == 0 && state_.hierarchy_usable &&
+          state_.parameter_manager.HierarchicalAllgather())
+        HierarchicalAllgatherv(e.input, lens, out);
+      else
+        ps.comm.Allgatherv(e.input, lens, out);
       tl.ActivityEnd(e.name);
     }
     return Status::OK();
@@ -208,21 +223,77 @@ private:
       if (!st.ok()) return st;
       e.output = out;
       int64_t total = e.num_elements();
-      fusion_.resize(static_cast<size_t>(total * es));
-      std::memcpy(fusion_.data(), e.input, static_cast<size_t>(total * es));
-      ScaleBufferCPU(fusion_.data(), total, e.dtype, e.prescale);
+      char* fusion = Fusion(static_cast<size_t>(total * es));
+      std::memcpy(fusion, e.input, static_cast<size_t>(total * es));
+      ScaleBufferCPU(fusion, total, e.dtype, e.prescale);
       tl.ActivityStart(e.name, HVD_ACT_CPU_REDUCESCATTER);
-      ps.comm.Allreduce(fusion_.data(), total, e.dtype, e.reduce_op);
+      ps.comm.Allreduce(fusion, total, e.dtype, e.reduce_op);
       tl.ActivityEnd(e.name);
-      std::memcpy(out, fusion_.data() + my_start * slice * es,
+      std::memcpy(out, fusion + my_start * slice * es,
                   static_cast<size_t>(my_rows * slice * es));
       ScaleBufferCPU(out, my_rows * slice, e.dtype, e.postscale);
     }
     return Status::OK();
   }
 
+  // Two-level allreduce: every host first reduce-scatters among its own
+  // ranks (each ends up owning the host's partial sum of one shard), ranks
+  // with the same local rank then allreduce their shard across hosts, and the
+  // host finally allgathers the finished shards. Only 1 / local_size of the
+  // data crosses hosts per rank.
+  // Parity: horovod/common/ops/nccl_operations.cc:233-440 (same three steps).
+  void HierarchicalAllreduce(void* buf, int64_t count, DataType dtype, ReduceOp op) {
+    Comm& local = state_.local_comm;
+    Comm& cross = state_.cross_comm;
+    const int L = local.size(), me = local.rank();
+    const int64_t es = static_cast<int64_t>(DataTypeSize(dtype));
+    const int64_t base = count / L, extra = count % L;
+    std::vector<int64_t> shard_bytes(L), mine_from_each(L);
+    for (int r = 0; r < L; ++r) shard_bytes[r] = (base + (r < extra ? 1 : 0)) * es;
+    const int64_t my_count = base + (me < extra ? 1 : 0);
+    for (int r = 0; r < L; ++r) mine_from_each[r] = my_count * es;
+    // Shard r of everybody's buffer goes to local rank r.
+    std::vector<char> inbox(static_cast<size_t>(my_count * es) * L);
+    local.Alltoallv(buf, shard_bytes, inbox.data(), mine_from_each);
+    char* acc = inbox.data();
+    for (int r = 1; r < L; ++r)
+      ReduceInto(acc, inbox.data() + static_cast<size_t>(r) * my_count * es, my_count, dtype, op);
+    cross.Allreduce(acc, my_count, dtype, op);
+    local.Allgatherv(acc, shard_bytes, buf);
+  }
+
+  // Two-level allgather: blocks are first collected inside every host, then
+  // whole host blocks travel between hosts (ranks are numbered host by host,
+  // so the concatenation order is the global rank order).
+  // Parity: horovod/common/ops/mpi_operations.cc hierarchical allgather.
+  void HierarchicalAllgatherv(const void* in, const std::vector<int64_t>& lens, void* out) {
+    Comm& local = state_.local_comm;
+    Comm& cross = state_.cross_comm;
+    const int L = local.size(), H = cross.size(), host = cross.rank();
+    std::vector<int64_t> host_bytes(H, 0), host_start(H, 0);
+    int64_t pos = 0;
+    for (int h = 0; h < H; ++h) {
+      host_start[h] = pos;
+      for (int r = 0; r < L; ++r) host_bytes[h] += lens[static_cast<size_t>(h) * L + r];
+      pos += host_bytes[h];
+    }
+    std::vector<int64_t> mine(lens.begin() + static_cast<size_t>(host) * L,
+                              lens.begin() + static_cast<size_t>(host + 1) * L);
+    std::vector<char> block(static_cast<size_t>(std::max<int64_t>(host_bytes[host], 1)));
+    local.Allgatherv(in, mine, block.data());
+    cross.Allgatherv(block.data(), host_bytes, out);
+  }
+
+  // The persistent host fusion buffer, sized for the fusion threshold in
+  // effect (the autotuner may move it) or for the request if that is larger.
+  char* Fusion(size_t bytes) {
+    const size_t threshold =
+        static_cast<size_t>(std::max<int64_t>(0, state_.parameter_manager.TensorFusionThresholdBytes()));
+    return static_cast<char*>(buffers_.Get(CPU_DEVICE_ID, 0, bytes, threshold));
+  }
+
   GlobalState& state_;
-  std::vector<char> fusion_;  // persistent host fusion buffer
+  FusionBufferManager buffers_;
 };
 
 }  // namespace

@@ -93,7 +93,15 @@ ncclRedOp_t NcclOp(ReduceOp op, DataType t) {
 
 }  // namespace
 
-NcclOps::NcclOps(GpuOps& gpu) : gpu_(gpu) {
+NcclOps::NcclOps(GpuOps& gpu)
+    : gpu_(gpu),
+      buffers_(
+          [](size_t n) {
+            void* p = nullptr;
+            HVD_CUDA(cudaMalloc(&p, std::max<size_t>(n, 256)));
+            return p;
+          },
+          [](void* p) { cudaFree(p); }) {
   std::string err;
   api_ = LoadNccl(&err);
   if (api_ == nullptr) HVD_LOG(WARNING) << "NCCL path unavailable: " << err;
@@ -106,36 +114,40 @@ void NcclOps::Shutdown() {
     for (auto& kv : comms_)
       if (kv.second) api_->CommDestroy(static_cast<ncclComm_t>(kv.second));
   comms_.clear();
-  if (fusion_) cudaFree(fusion_);
-  fusion_ = nullptr;
-  fusion_bytes_ = 0;
+  buffers_.Clear();
 }
 
-void* NcclOps::CommFor(ProcessSet& ps) {
-  auto it = comms_.find(ps.id);
+void* NcclOps::CommFor(ProcessSet& ps) { return CommOver(ps.id, ps.comm); }
+
+void* NcclOps::CommOver(int32_t key, Comm& over) {
+  auto it = comms_.find(key);
   if (it != comms_.end()) return it->second;
-  // Rank 0 of the set creates the id; it travels over the control plane.
+  // Rank 0 of the group creates the id; it travels over the control plane.
   ncclUniqueId id;
   std::memset(&id, 0, sizeof(id));
-  if (ps.comm.rank() == 0) HVD_NCCL(api_->GetUniqueId(&id));
-  ps.comm.Bcast(&id, sizeof(id), 0);
+  if (over.rank() == 0) HVD_NCCL(api_->GetUniqueId(&id));
+  over.Bcast(&id, sizeof(id), 0);
   ncclComm_t comm = nullptr;
-  HVD_NCCL(api_->CommInitRank(&comm, ps.comm.size(), id, ps.comm.rank()));
-  ps.comm.Barrier();
-  comms_[ps.id] = comm;
+  HVD_NCCL(api_->CommInitRank(&comm, over.size(), id, over.rank()));
+  over.Barrier();
+  comms_[key] = comm;
   return comm;
 }
 
+bool NcclOps::UseHierarchicalAllreduce(const ProcessSet& ps) const {
+  GlobalState& s = gpu_.state();
+  return ps.id == 0 && s.hierarchy_usable && s.parameter_manager.HierarchicalAllreduce();
+}
+
+// The persistent device fusion buffer, sized for the fusion threshold in
+// effect (at least 64 MiB) or for the request if that is larger.
 void* NcclOps::Fusion(size_t bytes) {
-  if (bytes > fusion_bytes_) {
-    if (fusion_) {
-      HVD_CUDA(cudaStreamSynchronize(gpu_.stream()));
-      cudaFree(fusion_);
-    }
-    fusion_bytes_ = std::max<size_t>(bytes, 64u << 20);
-    HVD_CUDA(cudaMalloc(&fusion_, fusion_bytes_));
-  }
-  return fusion_;
+  const size_t threshold = std::max<size_t>(
+      64u << 20, static_cast<size_t>(std::max<int64_t>(
+                     0, gpu_.state().parameter_manager.TensorFusionThresholdBytes())));
+  return buffers_.Get(gpu_.device(), 0, bytes, threshold, [this] {
+    cudaStreamSynchronize(gpu_.stream());
+  });
 }
 
 Status NcclOps::Execute(std::vector<TensorTableEntry>& entries,
@@ -147,7 +159,9 @@ Status NcclOps::Execute(std::vector<TensorTableEntry>& entries,
   void* comm = CommFor(ps);
   gpu_.WaitForInputs(entries);
   switch (response.type) {
-  case Response::ALLREDUCE: return Allreduce(entries, response, comm);
+  case Response::ALLREDUCE:
+    hierarchical_ = UseHierarchicalAllreduce(ps);
+    return Allreduce(entries, response, comm);
   case Response::BROADCAST: return Broadcast(entries, comm);
   case Response::ALLGATHER: return Allgather(entries, response, ps, comm);
   case Response::ALLTOALL: return Alltoall(entries, ps, comm);
@@ -165,6 +179,7 @@ Status NcclOps::Execute(std::vector<TensorTableEntry>& entries,
     avg.type = Response::ALLREDUCE;
     avg.reduce_op = ReduceOp::SUM;
     avg.postscale = response.postscale / static_cast<double>(ps.ranks().size());
+    hierarchical_ = false;
     return Allreduce(entries, avg, comm);
   }
   default:
@@ -187,7 +202,8 @@ Status NcclOps::Allreduce(std::vector<TensorTableEntry>& entries,
   const ncclRedOp_t op = NcclOp(response.reduce_op, response.dtype);
   const int64_t es = static_cast<int64_t>(DataTypeSize(wire));
 
-  if (wire == dtype && entries.size() == 1 && entries[0].input && entries[0].output) {
+  if (!hierarchical_ && wire == dtype && entries.size() == 1 && entries[0].input &&
+      entries[0].output) {
     TensorTableEntry& e = entries[0];
     const void* src = e.input;
     if (response.prescale != 1.0) {
@@ -228,12 +244,33 @@ Status NcclOps::Allreduce(std::vector<TensorTableEntry>& entries,
   h_off[n] = off;
   gpu_.ring().Commit(slot, stream);
   kern::TensorList list = {static_cast<int>(n), d_off, d_cnt, d_in, d_out};
-  void* buf = Fusion(static_cast<size_t>(off * es));
+  // The hierarchical variant cuts the buffer into local_size equal shards.
+  GlobalState& gs = gpu_.state();
+  const int64_t local = hierarchical_ ? gs.local_comm.size() : 1;
+  const int64_t padded = RoundUp(off, local * align);
+  void* buf = Fusion(static_cast<size_t>(padded * es));
+  if (padded > off)
+    HVD_CUDA(cudaMemsetAsync(static_cast<char*>(buf) + off * es, 0,
+                             static_cast<size_t>((padded - off) * es), stream));
   tl.ActivityStartAll(entries, HVD_ACT_MEMCPY_IN_FUSION_BUFFER);
   kern::LaunchPackUnpack(list, dtype, wire, buf, response.prescale, true, off, stream);
   tl.ActivityEndAll(entries);
   tl.ActivityStartAll(entries, HVD_ACT_NCCL_ALLREDUCE);
-  HVD_NCCL(api_->AllReduce(buf, buf, off, nt, op, comm, stream));
+  if (hierarchical_) {
+    // Reduce-scatter inside the host, allreduce of each rank's shard across
+    // hosts, allgather inside the host
+    // (horovod/common/ops/nccl_operations.cc:233-440; the cross-host step is
+    // an NCCL allreduce here instead of a copy to the host and MPI).
+    ncclComm_t lc = static_cast<ncclComm_t>(CommOver(-1, gs.local_comm));
+    ncclComm_t cc = static_cast<ncclComm_t>(CommOver(-2, gs.cross_comm));
+    const int64_t shard = padded / local;
+    char* mine = static_cast<char*>(buf) + gs.local_comm.rank() * shard * es;
+    HVD_NCCL(api_->ReduceScatter(buf, mine, shard, nt, op, lc, stream));
+    HVD_NCCL(api_->AllReduce(mine, mine, shard, nt, op, cc, stream));
+    HVD_NCCL(api_->AllGather(mine, buf, shard, nt, lc, stream));
+  } else {
+    HVD_NCCL(api_->AllReduce(buf, buf, off, nt, op, comm, stream));
+  }
   tl.ActivityEndAll(entries);
   tl.ActivityStartAll(entries, HVD_ACT_MEMCPY_OUT_FUSION_BUFFER);
   kern::LaunchPackUnpack(list, dtype, wire, buf, response.postscale, false, off, stream);

@@ -11,11 +11,13 @@
 #include <memory>
 #include <vector>
 
+#include "../common/fusion_buffer_manager.h"
 #include "op_executor.h"
 
 namespace hvd {
 
 class GpuOps;
+class Comm;
 struct NcclApi;
 
 class NcclOps {
@@ -28,6 +30,11 @@ public:
 
 private:
   void* CommFor(ProcessSet& ps);
+  // NCCL communicator over the ranks of `comm` (a control-plane communicator
+  // this rank belongs to), cached under `key` (negative keys: the host-local
+  // and cross-host communicators of the hierarchical allreduce).
+  void* CommOver(int32_t key, Comm& comm);
+  bool UseHierarchicalAllreduce(const ProcessSet& ps) const;
   void* Fusion(size_t bytes);
   Status Allreduce(std::vector<TensorTableEntry>& entries,
                    const Response& response, void* comm);
@@ -42,8 +49,8 @@ private:
   GpuOps& gpu_;
   const NcclApi* api_ = nullptr;
   std::map<int32_t, void*> comms_;
-  void* fusion_ = nullptr;
-  size_t fusion_bytes_ = 0;
+  FusionBufferManager buffers_;
+  bool hierarchical_ = false;  // the allreduce being executed runs in two levels
 };
 
 }  // namespace hvd

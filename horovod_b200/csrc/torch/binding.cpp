@@ -555,6 +555,8 @@ PYBIND11_MODULE(_C, m) {
     d["hierarchical_allreduce"] = pm.HierarchicalAllreduce();
     d["hierarchical_allgather"] = pm.HierarchicalAllgather();
     d["autotune"] = pm.IsAutoTuning();
+    // Whether the rank layout allows the two-level collectives at all.
+    d["hierarchy_usable"] = hvd_state().hierarchy_usable;
     return d;
   }, "Fusion threshold, cycle time and the other tunables as they are in effect now.");
 

@@ -2,11 +2,15 @@
 // (software float conversions, wire format, Gaussian process, Bayesian
 // optimisation, parameter manager, response cache, stall inspector, CPU
 // reduction kernels, Adasum oracle).
+#include <cstdlib>
+#include <cstring>
+
 #include <pybind11/functional.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
 #include "../common/controller.h"
+#include "../common/fusion_buffer_manager.h"
 #include "../common/half.h"
 #include "../common/message.h"
 #include "../common/optim/bayesian_optimization.h"
@@ -24,6 +28,20 @@ namespace hvd {
 void BindTesting(py::module_& root) {
   py::module_ m = root.def_submodule("testing", "internal components for unit tests");
 
+  // Drives a FusionBufferManager over host memory with a list of (needed,
+  // threshold) requests; returns the buffer size after each request and the
+  // total number of (re)allocations.
+  m.def("fusion_buffer_probe", [](const std::vector<std::pair<int64_t, int64_t>>& requests) {
+    FusionBufferManager mgr([](size_t n) { return std::malloc(n ? n : 1); },
+                            [](void* p) { std::free(p); });
+    std::vector<int64_t> sizes;
+    for (auto& r : requests) {
+      void* p = mgr.Get(-1, 0, static_cast<size_t>(r.first), static_cast<size_t>(r.second));
+      if (p != nullptr && r.first > 0) std::memset(p, 0xab, static_cast<size_t>(r.first));
+      sizes.push_back(static_cast<int64_t>(mgr.SizeOf(-1, 0)));
+    }
+    return std::make_pair(sizes, mgr.reallocations());
+  });
   m.def("float_to_half_bits", &FloatToHalfBits);
   m.def("half_bits_to_float", &HalfBitsToFloat);
   m.def("float_to_bf16_bits", &FloatToBF16Bits);

@@ -77,9 +77,23 @@ ResponseList Controller::ComputeResponseList(bool shutdown_requested,
       stall_.RemoveCachedTensor(m.name);
     }
   }
-  // A rank that joined agrees to whatever cached collective the others run.
-  if (join.joined && cache_on)
-    for (auto bit : cache_.list_all_bits()) cc.record_hit(bit);
+  // A rank that joined agrees to whatever cached reduction the others run (it
+  // contributes zeros). Collectives that cannot run with a joined rank
+  // (allgather, broadcast, alltoall, reducescatter) must not take the cache
+  // fast path either: their cached responses are invalidated on every rank,
+  // so that the next request for them goes through the coordinator and gets
+  // the same error as an uncached one.
+  if (join.joined && cache_on) {
+    for (auto bit : cache_.list_all_bits()) {
+      const Response::Type t = cache_.peek_response(bit).type;
+      if (t == Response::ALLREDUCE || t == Response::ADASUM) {
+        cc.record_hit(bit);
+      } else {
+        cc.record_invalid_bit(bit);
+        cc.set_uncached_in_queue(true);
+      }
+    }
+  }
 
   bool should_shut_down = shutdown_requested;
   if (stall_.ShouldPerformCheck()) {
@@ -138,6 +152,15 @@ ResponseList Controller::ComputeResponseList(bool shutdown_requested,
       }
       for (auto gid : ready_groups) {
         std::deque<Response> group;
+        // A group is fused on its own only when every member is a common hit.
+        // If one is not (evicted from the cache, say), the members that are
+        // run below like ungrouped tensors: every rank holds the same cache
+        // and the same hit set, so all ranks take the same decision.
+        bool whole = true;
+        for (auto& name : groups_.GetGroupTensorNames(gid))
+          if (!cache_.has_name(name) || !cc.cache_hits().count(cache_.peek_cache_bit(name)))
+            whole = false;
+        if (!whole) continue;
         for (auto& name : groups_.GetGroupTensorNames(gid)) {
           uint32_t bit = cache_.peek_cache_bit(name);
           group.push_back(cache_.get_response(bit));

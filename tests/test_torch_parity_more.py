@@ -77,6 +77,38 @@ def test_join_refuses_allgather_and_broadcast():
         assert out[1] is True, (op, out)
 
 
+def _join_vs_cached_ops(rank, size):
+    """The same allgather first runs normally (and is cached), then again
+    while rank 0 has joined: the cached response must not be used."""
+    import horovod_b200.torch as hvd
+    hvd.init()
+    t = torch.full((rank + 2, 3), float(rank))
+    for _ in range(3):  # cached after the first round
+        out = hvd.allgather(t, name="jc.ag")
+        assert out.shape[0] == sum(r + 2 for r in range(size))
+    raised = None
+    if rank == 0:
+        hvd.join()
+    else:
+        try:
+            hvd.allgather(t, name="jc.ag")
+            raised = False
+        except RuntimeError:
+            raised = True
+        hvd.join()
+    # and afterwards it works again for everybody
+    out = hvd.allgather(t, name="jc.ag")
+    ok = out.shape[0] == sum(r + 2 for r in range(size))
+    hvd.shutdown()
+    return raised, ok
+
+
+def test_join_refuses_a_cached_allgather():
+    out = run_parallel(_join_vs_cached_ops, np=2)
+    assert out[1][0] is True, out
+    assert out[0][1] and out[1][1], out
+
+
 def _optimizer_corner_cases(rank, size):
     import horovod_b200.torch as hvd
     hvd.init()

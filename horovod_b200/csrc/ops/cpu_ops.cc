@@ -6,6 +6,7 @@
 #include <cstdlib>
 #include <cstring>
 
+#include "../common/cpu_vector.h"
 #include "../common/fusion_buffer_manager.h"
 #include "../common/global_state.h"
 #include "../common/half.h"
@@ -355,12 +356,20 @@ void AdasumCPU(Comm& comm, void* buffer, DataType dtype,
       int64_t s = std::max(offsets[t], keep_lo);
       int64_t e = std::min(offsets[t] + counts[t], keep_hi);
       double dot = 0, na = 0, nb = 0;
-      for (int64_t i = s; i < e; ++i) {
-        double x = LoadAsDouble(a, i - keep_lo, dtype);
-        double y = LoadAsDouble(b, i - keep_lo, dtype);
-        dot += x * y;
-        na += x * x;
-        nb += y * y;
+      if (e > s && dtype == DataType::FLOAT16) {
+        HalfDotNorms(static_cast<const uint16_t*>(a) + (s - keep_lo),
+                     static_cast<const uint16_t*>(b) + (s - keep_lo), e - s, &dot, &na, &nb);
+      } else if (e > s && dtype == DataType::BFLOAT16) {
+        BF16DotNorms(static_cast<const uint16_t*>(a) + (s - keep_lo),
+                     static_cast<const uint16_t*>(b) + (s - keep_lo), e - s, &dot, &na, &nb);
+      } else {
+        for (int64_t i = s; i < e; ++i) {
+          double x = LoadAsDouble(a, i - keep_lo, dtype);
+          double y = LoadAsDouble(b, i - keep_lo, dtype);
+          dot += x * y;
+          na += x * x;
+          nb += y * y;
+        }
       }
       stats[3 * t] = dot;
       stats[3 * t + 1] = na;
@@ -381,6 +390,16 @@ void AdasumCPU(Comm& comm, void* buffer, DataType dtype,
       double dot = stats[3 * t], na = stats[3 * t + 1], nb = stats[3 * t + 2];
       double ca = na >= tiny ? 1.0 - dot / (2 * na) : 1.0;
       double cb = nb >= tiny ? 1.0 - dot / (2 * nb) : 1.0;
+      if (e > s && (dtype == DataType::FLOAT16 || dtype == DataType::BFLOAT16)) {
+        uint16_t* o = reinterpret_cast<uint16_t*>(data + keep_lo * es) + (s - keep_lo);
+        const uint16_t* x16 = static_cast<const uint16_t*>(a) + (s - keep_lo);
+        const uint16_t* y16 = static_cast<const uint16_t*>(b) + (s - keep_lo);
+        if (dtype == DataType::FLOAT16)
+          HalfScaledAdd(o, x16, y16, e - s, ca, cb);
+        else
+          BF16ScaledAdd(o, x16, y16, e - s, ca, cb);
+        continue;
+      }
       for (int64_t i = s; i < e; ++i) {
         double x = LoadAsDouble(a, i - keep_lo, dtype);
         double y = LoadAsDouble(b, i - keep_lo, dtype);

@@ -10,6 +10,7 @@
 #include <pybind11/stl.h>
 
 #include "../common/controller.h"
+#include "../common/cpu_vector.h"
 #include "../common/fusion_buffer_manager.h"
 #include "../common/half.h"
 #include "../common/message.h"
@@ -41,6 +42,30 @@ void BindTesting(py::module_& root) {
       sizes.push_back(static_cast<int64_t>(mgr.SizeOf(-1, 0)));
     }
     return std::make_pair(sizes, mgr.reallocations());
+  });
+  m.def("cpu_has_f16c", &CpuHasF16C);
+  m.def("cpu_vector_force_scalar", &CpuVectorForceScalar);
+  // (a, b as uint16 bit patterns) -> (dot, |a|^2, |b|^2) and ca * a + cb * b.
+  m.def("dot_norms_16", [](py::bytes a, py::bytes b, bool half) {
+    std::string sa = a, sb = b;
+    double dot = 0, na = 0, nb = 0;
+    const int64_t n = static_cast<int64_t>(sa.size() / 2);
+    auto* pa = reinterpret_cast<const uint16_t*>(sa.data());
+    auto* pb = reinterpret_cast<const uint16_t*>(sb.data());
+    if (half) HalfDotNorms(pa, pb, n, &dot, &na, &nb);
+    else BF16DotNorms(pa, pb, n, &dot, &na, &nb);
+    return std::make_tuple(dot, na, nb);
+  });
+  m.def("scaled_add_16", [](py::bytes a, py::bytes b, double ca, double cb, bool half) {
+    std::string sa = a, sb = b;
+    const int64_t n = static_cast<int64_t>(sa.size() / 2);
+    std::string out(sa.size(), '\0');
+    auto* pa = reinterpret_cast<const uint16_t*>(sa.data());
+    auto* pb = reinterpret_cast<const uint16_t*>(sb.data());
+    auto* po = reinterpret_cast<uint16_t*>(&out[0]);
+    if (half) HalfScaledAdd(po, pa, pb, n, ca, cb);
+    else BF16ScaledAdd(po, pa, pb, n, ca, cb);
+    return py::bytes(out);
   });
   m.def("float_to_half_bits", &FloatToHalfBits);
   m.def("half_bits_to_float", &HalfBitsToFloat);

@@ -16,6 +16,7 @@
 #include <sys/socket.h>
 #include <unistd.h>
 
+#include "../common/cpu_vector.h"
 #include "../common/half.h"
 #include "../common/logging.h"
 
@@ -543,28 +544,21 @@ inline float Combine(float a, float b, ReduceOp op) {
   }
 }
 
-#if defined(__x86_64__)
-__attribute__((target("avx2,f16c"))) void HalfSumF16C(uint16_t* d,
-                                                      const uint16_t* s,
-                                                      int64_t n);
-#endif
-
 void ReduceHalf(uint16_t* d, const uint16_t* s, int64_t n, ReduceOp op) {
-#if defined(__x86_64__)
-  static const bool f16c =
-      __builtin_cpu_supports("avx2") && __builtin_cpu_supports("f16c");
-  if (f16c && (op == ReduceOp::SUM || op == ReduceOp::AVERAGE ||
-               op == ReduceOp::ADASUM)) {
-    HalfSumF16C(d, s, n);
+  if (op == ReduceOp::SUM || op == ReduceOp::AVERAGE || op == ReduceOp::ADASUM) {
+    HalfSum(d, s, n);  // AVX2 + F16C when the CPU has them
     return;
   }
-#endif
   for (int64_t i = 0; i < n; ++i)
     d[i] = FloatToHalfBits(
         Combine(HalfBitsToFloat(d[i]), HalfBitsToFloat(s[i]), op));
 }
 
 void ReduceBF16(uint16_t* d, const uint16_t* s, int64_t n, ReduceOp op) {
+  if (op == ReduceOp::SUM || op == ReduceOp::AVERAGE || op == ReduceOp::ADASUM) {
+    BF16Sum(d, s, n);
+    return;
+  }
   for (int64_t i = 0; i < n; ++i)
     d[i] = FloatToBF16Bits(
         Combine(BF16BitsToFloat(d[i]), BF16BitsToFloat(s[i]), op));
@@ -584,27 +578,6 @@ template <typename T> void ScaleTyped(T* p, int64_t n, double f) {
 }  // namespace
 
 }  // namespace hvd
-
-#if defined(__x86_64__)
-#include <immintrin.h>
-namespace hvd {
-namespace {
-__attribute__((target("avx2,f16c"))) void HalfSumF16C(uint16_t* d,
-                                                      const uint16_t* s,
-                                                      int64_t n) {
-  int64_t i = 0;
-  for (; i + 8 <= n; i += 8) {
-    __m256 a = _mm256_cvtph_ps(_mm_loadu_si128(reinterpret_cast<const __m128i*>(d + i)));
-    __m256 b = _mm256_cvtph_ps(_mm_loadu_si128(reinterpret_cast<const __m128i*>(s + i)));
-    __m128i r = _mm256_cvtps_ph(_mm256_add_ps(a, b), _MM_FROUND_TO_NEAREST_INT);
-    _mm_storeu_si128(reinterpret_cast<__m128i*>(d + i), r);
-  }
-  for (; i < n; ++i)
-    d[i] = FloatToHalfBits(HalfBitsToFloat(d[i]) + HalfBitsToFloat(s[i]));
-}
-}  // namespace
-}  // namespace hvd
-#endif
 
 namespace hvd {
 
@@ -663,20 +636,12 @@ void ScaleBufferCPU(void* buf, int64_t count, DataType dtype, double factor) {
     break;
   }
   case DataType::FLOAT64: ScaleTyped(static_cast<double*>(buf), count, factor); break;
-  case DataType::FLOAT16: {
-    uint16_t* p = static_cast<uint16_t*>(buf);
-    float f = static_cast<float>(factor);
-    for (int64_t i = 0; i < count; ++i)
-      p[i] = FloatToHalfBits(HalfBitsToFloat(p[i]) * f);
+  case DataType::FLOAT16:
+    HalfScale(static_cast<uint16_t*>(buf), count, static_cast<float>(factor));
     break;
-  }
-  case DataType::BFLOAT16: {
-    uint16_t* p = static_cast<uint16_t*>(buf);
-    float f = static_cast<float>(factor);
-    for (int64_t i = 0; i < count; ++i)
-      p[i] = FloatToBF16Bits(BF16BitsToFloat(p[i]) * f);
+  case DataType::BFLOAT16:
+    BF16Scale(static_cast<uint16_t*>(buf), count, static_cast<float>(factor));
     break;
-  }
   case DataType::BOOL: break;
   }
 }

@@ -23,6 +23,7 @@ HOROVOD_STALL_CHECK_TIME_SECONDS = "HOROVOD_STALL_CHECK_TIME_SECONDS"
 HOROVOD_STALL_SHUTDOWN_TIME_SECONDS = "HOROVOD_STALL_SHUTDOWN_TIME_SECONDS"
 HOROVOD_LOG_LEVEL = "HOROVOD_LOG_LEVEL"
 HOROVOD_LOG_HIDE_TIME = "HOROVOD_LOG_HIDE_TIME"
+HOROVOD_GLOO_TIMEOUT_SECONDS = "HOROVOD_GLOO_TIMEOUT_SECONDS"
 HOROVOD_NUM_NCCL_STREAMS = "HOROVOD_NUM_NCCL_STREAMS"
 HOROVOD_THREAD_AFFINITY = "HOROVOD_THREAD_AFFINITY"
 HOROVOD_GPU_BACKEND = "HOROVOD_GPU_BACKEND"
@@ -71,11 +72,14 @@ def set_args_from_config(args, config, override_args):
     if library:
         _set_arg_from_config(args, "num_nccl_streams", override_args, library)
         _set_arg_from_config(args, "thread_affinity", override_args, library)
+        _set_arg_from_config(args, "gloo_timeout_seconds", override_args, library)
         _set_arg_from_config(args, "gpu_backend", override_args, library)
     logging = config.get("logging")
     if logging:
         _set_arg_from_config(args, "level", override_args, logging, arg_prefix="log_")
         _set_arg_from_config(args, "hide_timestamp", override_args, logging, arg_prefix="log_")
+        if "with_timestamp" in logging and "log_hide_timestamp" not in override_args:
+            args.log_hide_timestamp = not logging["with_timestamp"]
 
 
 def validate_config_args(args):
@@ -99,6 +103,9 @@ def validate_config_args(args):
         need(0 <= v <= 1, "autotune_gaussian_process_noise must be in [0, 1]")
     w = getattr(args, "stall_check_warning_time_seconds", None)
     s = getattr(args, "stall_check_shutdown_time_seconds", None)
+    t = getattr(args, "gloo_timeout_seconds", None)
+    if t is not None:
+        need(t >= 0, "gloo_timeout_seconds must be >= 0")
     if w is not None:
         need(w >= 0, "stall_check_warning_time_seconds must be >= 0")
     if s is not None:
@@ -135,6 +142,7 @@ def set_env_from_args(env, args):
     _add(env, HOROVOD_STALL_SHUTDOWN_TIME_SECONDS, g("stall_check_shutdown_time_seconds"))
     _add(env, HOROVOD_NUM_NCCL_STREAMS, g("num_nccl_streams"))
     _add(env, HOROVOD_THREAD_AFFINITY, g("thread_affinity"))
+    _add(env, HOROVOD_GLOO_TIMEOUT_SECONDS, g("gloo_timeout_seconds"))
     _add(env, HOROVOD_GPU_BACKEND, g("gpu_backend"))
     _add(env, HOROVOD_LOG_LEVEL, g("log_level"))
     _add(env, HOROVOD_LOG_HIDE_TIME, g("log_hide_timestamp"), lambda v: "1")

@@ -189,6 +189,9 @@ def parse_args(argv=None):
     g = parser.add_argument_group("library arguments")
     g.add_argument("--num-nccl-streams", type=int, dest="num_nccl_streams",
                    action=make_override_action(override_args))
+    g.add_argument("--gloo-timeout-seconds", type=int, dest="gloo_timeout_seconds",
+                   action=make_override_action(override_args),
+                   help="Timeout of the control-plane (TCP mesh) operations, default 30.")
     g.add_argument("--thread-affinity", type=int, dest="thread_affinity",
                    action=make_override_action(override_args))
     g.add_argument("--gpu-backend", dest="gpu_backend", choices=["symm", "nccl"],
@@ -198,12 +201,21 @@ def parse_args(argv=None):
     g = parser.add_argument_group("logging arguments")
     g.add_argument("--log-level", dest="log_level", choices=config_parser.LOG_LEVELS,
                    action=make_override_action(override_args))
+    # Timestamps inside the library's own log lines: the positive and the
+    # negative spelling, plus the older "hide" pair with the opposite sense.
+    g.add_argument("--log-with-timestamp", dest="log_hide_timestamp",
+                   action=make_override_false_action(override_args),
+                   help="Keep the timestamp in the library's log messages (the default).")
+    g.add_argument("--log-without-timestamp", dest="log_hide_timestamp",
+                   action=make_override_true_action(override_args),
+                   help="Hide the timestamp from the library's log messages.")
     g.add_argument("--log-hide-timestamp", dest="log_hide_timestamp",
-                   action=make_override_true_action(override_args))
+                   action=make_override_true_action(override_args), help=argparse.SUPPRESS)
     g.add_argument("--no-log-hide-timestamp", dest="log_hide_timestamp",
-                   action=make_override_false_action(override_args))
-    g.add_argument("--prefix-timestamp", dest="prefix_output_with_timestamp",
-                   action="store_true")
+                   action=make_override_false_action(override_args), help=argparse.SUPPRESS)
+    g.add_argument("-prefix-timestamp", "--prefix-output-with-timestamp", "--prefix-timestamp",
+                   dest="prefix_output_with_timestamp", action="store_true",
+                   help="Timestamp each line of the workers' output.")
 
     g = parser.add_argument_group("host arguments")
     hx = g.add_mutually_exclusive_group()

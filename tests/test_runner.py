@@ -43,6 +43,17 @@ def test_args_map_to_env():
     assert env["HOROVOD_LOG_LEVEL"] == "INFO" and env["HOROVOD_LOG_HIDE_TIME"] == "1"
     assert env["HOROVOD_GPU_BACKEND"] == "nccl"
     assert args.command == ["python", "train.py"]
+    # the spellings of the timestamp and timeout options
+    args = launch.parse_args(["-np", "2", "--gloo-timeout-seconds", "7",
+                              "--log-without-timestamp", "--prefix-output-with-timestamp",
+                              "python", "train.py"])
+    env = config_parser.set_env_from_args({}, args)
+    assert env["HOROVOD_GLOO_TIMEOUT_SECONDS"] == "7" and env["HOROVOD_LOG_HIDE_TIME"] == "1"
+    assert args.prefix_output_with_timestamp
+    args = launch.parse_args(["-np", "2", "--log-with-timestamp", "-prefix-timestamp",
+                              "python", "train.py"])
+    assert "HOROVOD_LOG_HIDE_TIME" not in config_parser.set_env_from_args({}, args)
+    assert args.prefix_output_with_timestamp
 
 
 def test_config_file_loses_to_explicit_flags(tmp_path):

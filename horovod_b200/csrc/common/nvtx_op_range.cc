@@ -49,4 +49,32 @@ void NvtxRangeEnd(NvtxRangeId id) {
   nvtxDomainRangeEnd(g_domain, id);
 }
 
+namespace {
+nvtxDomainHandle_t TimelineDomain(bool activity) {
+  static nvtxDomainHandle_t ops = nvtxDomainCreateA("HorovodTimelineOps");
+  static nvtxDomainHandle_t acts = nvtxDomainCreateA("HorovodTimelineActivities");
+  return activity ? acts : ops;
+}
+}  // namespace
+
+NvtxRangeId NvtxTimelineRangeStart(bool activity, const std::string& tensor,
+                                   const std::string& name) {
+  if (!g_enabled.load(std::memory_order_relaxed)) return 0;
+  nvtxDomainHandle_t domain = TimelineDomain(activity);
+  if (domain == nullptr) return 0;
+  const std::string label = activity ? name : tensor + " " + name;
+  nvtxEventAttributes_t attr = {};
+  attr.version = NVTX_VERSION;
+  attr.size = NVTX_EVENT_ATTRIB_STRUCT_SIZE;
+  attr.messageType = NVTX_MESSAGE_TYPE_ASCII;
+  attr.message.ascii = label.c_str();
+  return nvtxDomainRangeStartEx(domain, &attr);
+}
+
+void NvtxTimelineRangeEnd(bool activity, NvtxRangeId id) {
+  if (id == 0) return;
+  nvtxDomainHandle_t domain = TimelineDomain(activity);
+  if (domain != nullptr) nvtxDomainRangeEnd(domain, id);
+}
+
 }  // namespace hvd

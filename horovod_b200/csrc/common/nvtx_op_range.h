@@ -31,4 +31,13 @@ NvtxRangeId NvtxRangeStart(NvtxOp op, const std::string& tensor_name,
                            int64_t payload_bytes);
 void NvtxRangeEnd(NvtxRangeId id);
 
+// Mirror of the timeline in NVTX: one domain for whole ops
+// ("HorovodTimelineOps": tensor name + collective type from start to end of
+// its execution), one for the activities inside them
+// ("HorovodTimelineActivities"). Returns 0 when ranges are disabled.
+// Parity: horovod/common/timeline.cc:332-425.
+NvtxRangeId NvtxTimelineRangeStart(bool activity, const std::string& tensor,
+                                   const std::string& name);
+void NvtxTimelineRangeEnd(bool activity, NvtxRangeId id);
+
 }  // namespace hvd

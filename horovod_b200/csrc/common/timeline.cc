@@ -1,6 +1,7 @@
 #include "timeline.h"
 
 #include "logging.h"
+#include "nvtx_op_range.h"
 
 namespace hvd {
 
@@ -62,8 +63,8 @@ void Timeline::Shutdown() {
 }
 
 void Timeline::Emit(char phase, const std::string& tensor,
-                    const std::string& name, const std::string& args) {
-  Record r{phase, tensor, name, args, NowMicros() - start_us_};
+                    const std::string& name, const std::string& args, int64_t abs_us) {
+  Record r{phase, tensor, name, args, (abs_us >= 0 ? abs_us : NowMicros()) - start_us_};
   {
     std::lock_guard<std::mutex> l(q_mu_);
     queue_.push_back(std::move(r));
@@ -120,10 +121,16 @@ void Timeline::Start(const std::string& tensor, Response::Type type,
   std::string args;
   if (size_bytes > 0) args = "\"bytes\": " + std::to_string(size_bytes);
   Emit('B', tensor, Response::TypeName(type), args);
+  NvtxPush(false, tensor, Response::TypeName(type));
 }
 
 void Timeline::ActivityStart(const std::string& tensor,
                              const std::string& activity) {
+  ActivityStartAt(tensor, activity, -1);
+}
+
+void Timeline::ActivityStartAt(const std::string& tensor, const std::string& activity,
+                               int64_t abs_us) {
   if (!Initialized()) return;
   {
     std::lock_guard<std::mutex> l(state_mu_);
@@ -131,10 +138,13 @@ void Timeline::ActivityStart(const std::string& tensor,
     if (it == states_.end() || it->second != State::TOP_LEVEL) return;
     it->second = State::ACTIVITY;
   }
-  Emit('B', tensor, activity);
+  Emit('B', tensor, activity, "", abs_us);
+  NvtxPush(true, tensor, activity);
 }
 
-void Timeline::ActivityEnd(const std::string& tensor) {
+void Timeline::ActivityEnd(const std::string& tensor) { ActivityEndAt(tensor, -1); }
+
+void Timeline::ActivityEndAt(const std::string& tensor, int64_t abs_us) {
   if (!Initialized()) return;
   {
     std::lock_guard<std::mutex> l(state_mu_);
@@ -142,7 +152,8 @@ void Timeline::ActivityEnd(const std::string& tensor) {
     if (it == states_.end() || it->second != State::ACTIVITY) return;
     it->second = State::TOP_LEVEL;
   }
-  Emit('E', tensor, "");
+  Emit('E', tensor, "", "", abs_us);
+  NvtxPop(true, tensor);
 }
 
 void Timeline::ActivityStartAll(const std::vector<TensorTableEntry>& entries,
@@ -156,7 +167,9 @@ void Timeline::ActivityEndAll(const std::vector<TensorTableEntry>& entries) {
   for (auto& e : entries) ActivityEnd(e.name);
 }
 
-void Timeline::End(const std::string& tensor) {
+void Timeline::End(const std::string& tensor) { EndAt(tensor, -1); }
+
+void Timeline::EndAt(const std::string& tensor, int64_t abs_us) {
   if (!Initialized()) return;
   bool close_activity = false;
   {
@@ -167,8 +180,35 @@ void Timeline::End(const std::string& tensor) {
     else if (it->second != State::TOP_LEVEL) return;
     states_.erase(it);
   }
-  if (close_activity) Emit('E', tensor, "");
-  Emit('E', tensor, "");
+  if (close_activity) {
+    Emit('E', tensor, "", "", abs_us);
+    NvtxPop(true, tensor);
+  }
+  Emit('E', tensor, "", "", abs_us);
+  NvtxPop(false, tensor);
+}
+
+void Timeline::NvtxPush(bool activity, const std::string& tensor, const std::string& name) {
+  const uint64_t id = NvtxTimelineRangeStart(activity, tensor, name);
+  if (id == 0) return;
+  std::lock_guard<std::mutex> l(state_mu_);
+  auto& open = activity ? nvtx_activities_ : nvtx_ops_;
+  auto it = open.find(tensor);
+  if (it != open.end()) NvtxTimelineRangeEnd(activity, it->second);
+  open[tensor] = id;
+}
+
+void Timeline::NvtxPop(bool activity, const std::string& tensor) {
+  uint64_t id = 0;
+  {
+    std::lock_guard<std::mutex> l(state_mu_);
+    auto& open = activity ? nvtx_activities_ : nvtx_ops_;
+    auto it = open.find(tensor);
+    if (it == open.end()) return;
+    id = it->second;
+    open.erase(it);
+  }
+  NvtxTimelineRangeEnd(activity, id);
 }
 
 void Timeline::MarkCycleStart() {

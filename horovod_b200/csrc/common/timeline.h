@@ -68,6 +68,13 @@ public:
   void ActivityEndAll(const std::vector<TensorTableEntry>& entries);
   void End(const std::string& tensor);
   void MarkCycleStart();
+  // The same three transitions with a time stamp supplied by the caller
+  // (microseconds on the NowMicros() clock): the device executor replays the
+  // phases of an op with the times at which the GPU actually went through
+  // them, taken from CUDA events, after the op has finished.
+  void ActivityStartAt(const std::string& tensor, const std::string& activity, int64_t abs_us);
+  void ActivityEndAt(const std::string& tensor, int64_t abs_us);
+  void EndAt(const std::string& tensor, int64_t abs_us);
 
 private:
   enum class State { UNKNOWN, NEGOTIATING, TOP_LEVEL, ACTIVITY };
@@ -78,8 +85,14 @@ private:
     std::string args;      // raw JSON object body or empty
     int64_t ts_us;
   };
+  // abs_us < 0: now.
   void Emit(char phase, const std::string& tensor, const std::string& name,
-            const std::string& args = "");
+            const std::string& args = "", int64_t abs_us = -1);
+  // Mirrors of the trace in two NVTX domains (ops, and the activities inside
+  // them), so that Nsight shows the same structure as the Chrome trace.
+  void NvtxPush(bool activity, const std::string& tensor, const std::string& name);
+  void NvtxPop(bool activity, const std::string& tensor);
+  std::unordered_map<std::string, uint64_t> nvtx_ops_, nvtx_activities_;  // under state_mu_
   void WriterLoop();
   void WriteRecord(const Record& r);
 

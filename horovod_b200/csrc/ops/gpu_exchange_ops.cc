@@ -232,7 +232,7 @@ Status GpuOps::SymmBroadcast(std::vector<TensorTableEntry>& entries,
                              SymmSet& set) {
   Timeline& tl = state_.timeline;
   WaitForInputs(entries);
-  tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
+  ActStart(entries, HVD_ACT_FUSED_KERNEL);
   std::vector<Block> blocks;
   for (auto& e : entries) {
     Block b;
@@ -259,7 +259,7 @@ Status GpuOps::SymmBroadcast(std::vector<TensorTableEntry>& entries,
                 int64_t round_bytes, const std::vector<RoundBlock>& round) {
               LaunchExchangeSegments(o, i, set, round_bytes, round);
             });
-  tl.ActivityEndAll(entries);
+  ActEnd(entries);
   return Complete(entries);
 }
 
@@ -295,7 +295,7 @@ Status GpuOps::SymmAllgather(std::vector<TensorTableEntry>& entries,
       blocks.push_back(b);
     }
   }
-  tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
+  ActStart(entries, HVD_ACT_FUSED_KERNEL);
   int64_t total = 0;
   for (auto& b : blocks) total += b.bytes;
   RunBlocks(blocks, set, ExchangePushes(set, total),
@@ -303,7 +303,7 @@ Status GpuOps::SymmAllgather(std::vector<TensorTableEntry>& entries,
                 int64_t round_bytes, const std::vector<RoundBlock>& round) {
               LaunchExchangeSegments(o, i, set, round_bytes, round);
             });
-  tl.ActivityEndAll(entries);
+  ActEnd(entries);
   return Complete(entries);
 }
 
@@ -355,7 +355,7 @@ Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries,
       }
     }
   }
-  tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
+  ActStart(entries, HVD_ACT_FUSED_KERNEL);
   int64_t total = 0;
   for (auto& b : blocks) total += b.bytes;
   RunBlocks(blocks, set, ExchangePushes(set, total),
@@ -363,7 +363,7 @@ Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries,
                 int64_t round_bytes, const std::vector<RoundBlock>& round) {
               LaunchExchangeSegments(o, i, set, round_bytes, round);
             });
-  tl.ActivityEndAll(entries);
+  ActEnd(entries);
   return Complete(entries);
 }
 

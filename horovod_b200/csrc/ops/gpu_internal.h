@@ -161,6 +161,19 @@ public:
   int device() const { return device_; }
   const unsigned long long* kernel_trace() const { return trace_host_; }
 
+  // Timeline activities of device work. With the timeline on, the start and
+  // the end of a phase are CUDA events recorded on the communication stream;
+  // after the op has finished, the finalizer thread turns them into time
+  // stamps (event time relative to a calibration event whose host time is
+  // known) and replays them into the timeline, so the trace shows when the
+  // GPU went through each phase, not when the host queued it.
+  // Parity: horovod/common/ops/gpu_operations.h:69-129 (event queue replayed
+  // by the finalizer), horovod/common/ops/cuda_operations.cc:102-148.
+  void ActStart(const std::vector<TensorTableEntry>& entries, const char* activity);
+  void ActEnd(const std::vector<TensorTableEntry>& entries);
+  void ActStart(const std::string& tensor, const char* activity);
+  void ActEnd(const std::string& tensor);
+
   // Used by the NCCL path.
   cudaStream_t stream() const { return stream_; }
   DescriptorRing& ring() { return ring_; }
@@ -246,6 +259,22 @@ private:
   // Complete() right after the last launch, before callbacks run.
   void CloseTiming();
   PendingTiming* open_timing_ = nullptr;
+  struct ActivityMark {
+    std::vector<std::string> tensors;
+    std::string activity;  // empty: the activity ends here
+    cudaEvent_t event;
+  };
+  void PushMark(std::vector<std::string> tensors, const char* activity);
+  cudaEvent_t TimedEvent();
+  // Host time (NowMicros clock) at which `ev` completed on the device.
+  int64_t EventHostMicros(cudaEvent_t ev);
+  void Calibrate();
+  std::vector<ActivityMark> marks_;           // of the op being executed
+  std::mutex timed_mu_;
+  std::vector<cudaEvent_t> timed_events_;     // free list (timing enabled)
+  cudaEvent_t calib_event_ = nullptr;
+  int64_t calib_host_us_ = 0;
+
   bool timing_ = false;
   std::mutex timing_mu_;
   std::vector<PendingTiming> pending_timings_;

@@ -354,6 +354,74 @@ double HostNowUs() {
 }
 }  // namespace
 
+cudaEvent_t GpuOps::TimedEvent() {
+  {
+    std::lock_guard<std::mutex> l(timed_mu_);
+    if (!timed_events_.empty()) {
+      cudaEvent_t e = timed_events_.back();
+      timed_events_.pop_back();
+      return e;
+    }
+  }
+  cudaEvent_t e = nullptr;
+  HVD_CUDA(cudaEventCreate(&e));
+  return e;
+}
+
+void GpuOps::Calibrate() {
+  // A completed event whose host time is known: later events are placed on
+  // the host clock by their elapsed time since this one. Renewed every few
+  // seconds so that the two clocks cannot drift apart noticeably.
+  if (calib_event_ == nullptr) HVD_CUDA(cudaEventCreate(&calib_event_));
+  HVD_CUDA(cudaEventRecord(calib_event_, stream_));
+  HVD_CUDA(cudaEventSynchronize(calib_event_));
+  calib_host_us_ = NowMicros();
+}
+
+int64_t GpuOps::EventHostMicros(cudaEvent_t ev) {
+  float ms = 0.f;
+  if (calib_event_ == nullptr || cudaEventElapsedTime(&ms, calib_event_, ev) != cudaSuccess) {
+    cudaGetLastError();
+    return NowMicros();
+  }
+  return calib_host_us_ + static_cast<int64_t>(ms * 1000.0);
+}
+
+void GpuOps::PushMark(std::vector<std::string> tensors, const char* activity) {
+  if (marks_.empty() && (calib_event_ == nullptr || NowMicros() - calib_host_us_ > 5000000))
+    Calibrate();
+  ActivityMark m;
+  m.tensors = std::move(tensors);
+  m.activity = activity != nullptr ? activity : "";
+  m.event = TimedEvent();
+  HVD_CUDA(cudaEventRecord(m.event, stream_));
+  marks_.push_back(std::move(m));
+}
+
+void GpuOps::ActStart(const std::vector<TensorTableEntry>& entries, const char* activity) {
+  if (!state_.timeline.Initialized()) return;
+  std::vector<std::string> names;
+  for (auto& e : entries) names.push_back(e.name);
+  PushMark(std::move(names), activity);
+}
+
+void GpuOps::ActEnd(const std::vector<TensorTableEntry>& entries) {
+  if (!state_.timeline.Initialized()) return;
+  std::vector<std::string> names;
+  for (auto& e : entries) names.push_back(e.name);
+  PushMark(std::move(names), nullptr);
+}
+
+void GpuOps::ActStart(const std::string& tensor, const char* activity) {
+  if (!state_.timeline.Initialized()) return;
+  PushMark({tensor}, activity);
+}
+
+void GpuOps::ActEnd(const std::string& tensor) {
+  if (!state_.timeline.Initialized()) return;
+  PushMark({tensor}, nullptr);
+}
+
 void GpuOps::CloseTiming() {
   PendingTiming* pt = open_timing_;
   if (pt == nullptr || pt->t1 == nullptr) return;
@@ -379,14 +447,39 @@ Status GpuOps::Complete(std::vector<TensorTableEntry>& entries) {
   // so errors and timeline end times belong to this very op.
   auto shared = std::make_shared<std::vector<TensorTableEntry>>(std::move(entries));
   entries.clear();
-  finalizer_.Submit([this, shared, done] {
+  auto marks = std::make_shared<std::vector<ActivityMark>>(std::move(marks_));
+  marks_.clear();
+  cudaEvent_t finished = nullptr;
+  if (tl.Initialized()) {
+    finished = TimedEvent();
+    HVD_CUDA(cudaEventRecord(finished, stream_));
+  }
+  finalizer_.Submit([this, shared, done, marks, finished] {
     cudaError_t err = cudaEventSynchronize(static_cast<cudaEvent_t>(done.get()));
     Status st = err == cudaSuccess
                     ? CheckKernelStatus()
                     : Status::UnknownError(std::string("CUDA error: ") +
                                            cudaGetErrorString(err));
+    // Replay the phases with the times the device went through them.
+    Timeline& timeline = state_.timeline;
+    for (auto& m : *marks) {
+      const int64_t at = err == cudaSuccess ? EventHostMicros(m.event) : -1;
+      for (auto& name : m.tensors) {
+        if (m.activity.empty())
+          timeline.ActivityEndAt(name, at);
+        else
+          timeline.ActivityStartAt(name, m.activity, at);
+      }
+    }
+    const int64_t end_at =
+        finished != nullptr && err == cudaSuccess ? EventHostMicros(finished) : -1;
+    {
+      std::lock_guard<std::mutex> l(timed_mu_);
+      for (auto& m : *marks) timed_events_.push_back(m.event);
+      if (finished != nullptr) timed_events_.push_back(finished);
+    }
     for (auto& e : *shared) {
-      state_.timeline.End(e.name);
+      timeline.EndAt(e.name, end_at);
       e.Finish(st, done);
     }
   });

@@ -48,7 +48,7 @@ Status GpuOps::SymmAllreduce(std::vector<TensorTableEntry>& entries,
       if (e.input != e.output) in_place = false;
     if (in_place) return Complete(entries);
   }
-  tl.ActivityStartAll(entries, HVD_ACT_FUSED_KERNEL);
+  ActStart(entries, HVD_ACT_FUSED_KERNEL);
   // (A response with fewer devices than ranks means somebody has joined and
   // contributes zeros: everybody stages in that case.)
   if (!adasum && set.world > 1 && wire == dtype &&
@@ -56,7 +56,7 @@ Status GpuOps::SymmAllreduce(std::vector<TensorTableEntry>& entries,
     Status st;
     if (TryInplaceAllreduce(entries, response, set, &st)) {
       if (!st.ok()) return st;
-      tl.ActivityEndAll(entries);
+      ActEnd(entries);
       return Complete(entries);
     }
   }
@@ -198,7 +198,7 @@ Status GpuOps::SymmAllreduce(std::vector<TensorTableEntry>& entries,
                                   cudaGetErrorString(err));
     next += n;
   }
-  tl.ActivityEndAll(entries);
+  ActEnd(entries);
   return Complete(entries);
 }
 
@@ -339,7 +339,7 @@ Status GpuOps::SymmReducescatter(std::vector<TensorTableEntry>& entries,
       const int64_t win = slot_bytes / es;
       const int64_t longest = (base + (extra ? 1 : 0)) * slice;
       const int64_t chunk = exchange_chunk_bytes_ / 256 * 256;
-      tl.ActivityStart(e.name, HVD_ACT_FUSED_KERNEL);
+      ActStart(e.name, HVD_ACT_FUSED_KERNEL);
       for (int64_t lo = 0; lo < longest; lo += win) {
         const int64_t n_max = std::min(longest, lo + win) - lo;
         const int ctas = PickCtas(n_max * es * n);
@@ -364,12 +364,12 @@ Status GpuOps::SymmReducescatter(std::vector<TensorTableEntry>& entries,
         cudaError_t err = kern::LaunchReducescatterPush(e.input, out, a, e.dtype, e.prescale,
                                                         e.postscale, ctas, ctx, stream_);
         if (err != cudaSuccess) {
-          tl.ActivityEnd(e.name);
+          ActEnd(e.name);
           return Status::UnknownError(std::string("reducescatter launch failed: ") +
                                       cudaGetErrorString(err));
         }
       }
-      tl.ActivityEnd(e.name);
+      ActEnd(e.name);
       continue;
     }
     if (sym_off < 0 && staged > static_cast<int64_t>(set.data_bytes))
@@ -378,12 +378,12 @@ Status GpuOps::SymmReducescatter(std::vector<TensorTableEntry>& entries,
           "staging buffer; raise HOROVOD_SYMM_BUFFER_MB.");
     ring_.Commit(slot, stream_);
     kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH);
-    tl.ActivityStart(e.name, HVD_ACT_FUSED_KERNEL);
+    ActStart(e.name, HVD_ACT_FUSED_KERNEL);
     cudaError_t err = kern::LaunchFusedReducescatter(
         e.input, out, e.num_elements(), d_sb, e.dtype, sym_off >= 0 ? 1.0 : e.prescale,
         sym_off >= 0 ? e.prescale * e.postscale : e.postscale, set.nvls, PickCtas(staged),
         ctx, stream_, sym_off);
-    tl.ActivityEnd(e.name);
+    ActEnd(e.name);
     ring_.Release(slot, stream_);
     if (err != cudaSuccess)
       return Status::UnknownError(std::string("reducescatter launch failed: ") +

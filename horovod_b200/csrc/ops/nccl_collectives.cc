@@ -25,10 +25,10 @@ Status NcclOps::Broadcast(std::vector<TensorTableEntry>& entries, void* comm_v) 
   cudaStream_t stream = gpu_.stream();
   Timeline& tl = gpu_.state().timeline;
   for (auto& e : entries) {
-    tl.ActivityStart(e.name, HVD_ACT_NCCL_BCAST);
+    gpu_.ActStart(e.name, HVD_ACT_NCCL_BCAST);
     HVD_NCCL(api_->Broadcast(e.input, e.output, static_cast<size_t>(e.size_bytes()),
                              ncclChar, e.root_rank, comm, stream));
-    tl.ActivityEnd(e.name);
+    gpu_.ActEnd(e.name);
   }
   return gpu_.Complete(entries);
 }
@@ -56,7 +56,7 @@ Status NcclOps::Allgather(std::vector<TensorTableEntry>& entries,
     Status st = e.context->AllocateOutput(TensorShape(dims), stream, &out);
     if (!st.ok()) return st;
     e.output = out;
-    tl.ActivityStart(e.name, HVD_ACT_NCCL_ALLGATHER);
+    gpu_.ActStart(e.name, HVD_ACT_NCCL_ALLGATHER);
     if (equal) {
       HVD_NCCL(api_->AllGather(e.input, out,
                                static_cast<size_t>(response.tensor_sizes[i * n] * slice),
@@ -76,7 +76,7 @@ Status NcclOps::Allgather(std::vector<TensorTableEntry>& entries,
       }
       HVD_NCCL(api_->GroupEnd());
     }
-    tl.ActivityEnd(e.name);
+    gpu_.ActEnd(e.name);
   }
   return gpu_.Complete(entries);
 }
@@ -102,7 +102,7 @@ Status NcclOps::Alltoall(std::vector<TensorTableEntry>& entries, ProcessSet& ps,
     if (!st.ok()) return st;
     e.output = out;
     e.context->SetReceivedSplits(recv);
-    tl.ActivityStart(e.name, HVD_ACT_NCCL_ALLTOALL);
+    gpu_.ActStart(e.name, HVD_ACT_NCCL_ALLTOALL);
     HVD_NCCL(api_->GroupStart());
     int64_t soff = 0, roff = 0;
     for (int p = 0; p < n; ++p) {
@@ -117,7 +117,7 @@ Status NcclOps::Alltoall(std::vector<TensorTableEntry>& entries, ProcessSet& ps,
       roff += rb;
     }
     HVD_NCCL(api_->GroupEnd());
-    tl.ActivityEnd(e.name);
+    gpu_.ActEnd(e.name);
   }
   return gpu_.Complete(entries);
 }
@@ -166,7 +166,7 @@ Status NcclOps::Reducescatter(std::vector<TensorTableEntry>& entries,
       kern::LaunchScaleBuffer(e.input, tmp, total, e.dtype, e.prescale, stream);
       src = tmp;
     }
-    tl.ActivityStart(e.name, HVD_ACT_NCCL_REDUCESCATTER);
+    gpu_.ActStart(e.name, HVD_ACT_NCCL_REDUCESCATTER);
     if (extra == 0) {
       HVD_NCCL(api_->ReduceScatter(src, out, static_cast<size_t>(base * slice), nt,
                                    op, comm, stream));
@@ -177,7 +177,7 @@ Status NcclOps::Reducescatter(std::vector<TensorTableEntry>& entries,
                                static_cast<size_t>(my_rows * slice * es),
                                cudaMemcpyDeviceToDevice, stream));
     }
-    tl.ActivityEnd(e.name);
+    gpu_.ActEnd(e.name);
     if (e.postscale != 1.0)
       kern::LaunchScaleBuffer(out, out, my_rows * slice, e.dtype, e.postscale, stream);
   }

@@ -211,9 +211,9 @@ Status NcclOps::Allreduce(std::vector<TensorTableEntry>& entries,
                               response.prescale, stream);
       src = e.output;
     }
-    tl.ActivityStart(e.name, HVD_ACT_NCCL_ALLREDUCE);
+    gpu_.ActStart(e.name, HVD_ACT_NCCL_ALLREDUCE);
     HVD_NCCL(api_->AllReduce(src, e.output, e.num_elements(), nt, op, comm, stream));
-    tl.ActivityEnd(e.name);
+    gpu_.ActEnd(e.name);
     if (response.postscale != 1.0)
       kern::LaunchScaleBuffer(e.output, e.output, e.num_elements(), dtype,
                               response.postscale, stream);
@@ -252,10 +252,10 @@ Status NcclOps::Allreduce(std::vector<TensorTableEntry>& entries,
   if (padded > off)
     HVD_CUDA(cudaMemsetAsync(static_cast<char*>(buf) + off * es, 0,
                              static_cast<size_t>((padded - off) * es), stream));
-  tl.ActivityStartAll(entries, HVD_ACT_MEMCPY_IN_FUSION_BUFFER);
+  gpu_.ActStart(entries, HVD_ACT_MEMCPY_IN_FUSION_BUFFER);
   kern::LaunchPackUnpack(list, dtype, wire, buf, response.prescale, true, off, stream);
-  tl.ActivityEndAll(entries);
-  tl.ActivityStartAll(entries, HVD_ACT_NCCL_ALLREDUCE);
+  gpu_.ActEnd(entries);
+  gpu_.ActStart(entries, HVD_ACT_NCCL_ALLREDUCE);
   if (hierarchical_) {
     // Reduce-scatter inside the host, allreduce of each rank's shard across
     // hosts, allgather inside the host
@@ -271,10 +271,10 @@ Status NcclOps::Allreduce(std::vector<TensorTableEntry>& entries,
   } else {
     HVD_NCCL(api_->AllReduce(buf, buf, off, nt, op, comm, stream));
   }
-  tl.ActivityEndAll(entries);
-  tl.ActivityStartAll(entries, HVD_ACT_MEMCPY_OUT_FUSION_BUFFER);
+  gpu_.ActEnd(entries);
+  gpu_.ActStart(entries, HVD_ACT_MEMCPY_OUT_FUSION_BUFFER);
   kern::LaunchPackUnpack(list, dtype, wire, buf, response.postscale, false, off, stream);
-  tl.ActivityEndAll(entries);
+  gpu_.ActEnd(entries);
   gpu_.ring().Release(slot, stream);
   return gpu_.Complete(entries);
 }

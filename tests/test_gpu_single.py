@@ -116,3 +116,53 @@ def test_wait_for_a_peer_that_never_arrives_is_bounded():
     # the context is intact
     x = torch.arange(1000, device="cuda:0", dtype=torch.float32)
     assert float(x.sum()) == 499500.0
+
+
+def test_timeline_shows_device_times_of_the_kernel(hvd, tmp_path):
+    """With the timeline on, the FUSED_NVLINK_KERNEL activity of an op is
+    replayed from CUDA events: its length is the time the GPU spent in the
+    kernel (large for 512 MB, tiny for 4 KB), not the time the host took to
+    queue it, and it lies inside the op's span."""
+    import json
+    import time
+    path = str(tmp_path / "timeline.json")
+    big = torch.randn(128 << 20, device=_dev())    # 512 MB: hundreds of microseconds
+    small = torch.randn(1024, device=_dev())
+    torch.cuda.synchronize()
+    hvd.start_timeline(path, mark_cycles=False)
+    time.sleep(0.05)
+    for i in range(3):
+        hvd.allreduce(big, op=hvd.Sum, postscale_factor=0.5, name="tl.big")
+        hvd.allreduce(small, op=hvd.Sum, postscale_factor=0.5, name="tl.small")
+    torch.cuda.synchronize()
+    hvd.stop_timeline()
+    time.sleep(0.2)
+    events = json.load(open(path))
+    pids = {e["args"]["name"]: e["pid"] for e in events
+            if e.get("name") == "process_name"}
+    spans = {}
+    for name in ("tl.big", "tl.small"):
+        stack, found = [], []
+        for e in (e for e in events if e.get("pid") == pids[name] and e["ph"] in "BE"):
+            if e["ph"] == "B":
+                stack.append(e)
+            else:
+                b = stack.pop()
+                found.append((b["name"], b["ts"], e["ts"], len(stack)))
+        assert not stack
+        spans[name] = found
+    for name in ("tl.big", "tl.small"):
+        kernels = [(t0, t1) for n, t0, t1, depth in spans[name]
+                   if n == "FUSED_NVLINK_KERNEL" and depth == 1]
+        ops = [(t0, t1) for n, t0, t1, depth in spans[name] if n == "ALLREDUCE"]
+        assert len(kernels) == 3 and len(ops) == 3, spans[name]
+        for (k0, k1), (o0, o1) in zip(sorted(kernels), sorted(ops)):
+            assert k0 <= k1 and o0 <= k0 + 50 and k1 <= o1 + 50, (name, kernels, ops)
+    big_us = sorted(t1 - t0 for t0, t1 in
+                    [(a, b) for n, a, b, d in spans["tl.big"] if n == "FUSED_NVLINK_KERNEL"])
+    small_us = sorted(t1 - t0 for t0, t1 in
+                      [(a, b) for n, a, b, d in spans["tl.small"] if n == "FUSED_NVLINK_KERNEL"])
+    # 1 GB of traffic cannot take less than 100 us on any GPU; 4 KB is over
+    # in a few microseconds however long the host needed to launch it.
+    assert big_us[1] > 100, big_us
+    assert small_us[1] < 60, small_us

@@ -227,18 +227,21 @@ exchange_kernel(const InlineExchange inl, const ExchangePlan plan_dev, const Exc
 
   if (sync.credit_post != 0) {
     // The last CTA of this rank to get here tells every peer that this
-    // launch no longer reads anybody's region.
+    // launch no longer reads anybody's region. (Every CTA's loads have
+    // returned by now: their values were stored before the barrier below. No
+    // fence is needed to order loads that have completed, and a fence here
+    // would wait for the acknowledgement of every remote store first.)
+    __shared__ int s_last;
     __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence();
-      const unsigned long long done = atomicAdd(sync.done_counter, 1ull) + 1ull;
-      if (done == sync.done_target) {
-        for (int p = 0; p < ctx.world; ++p)
-          st_release_sys(ctx.flags_peers[p] + CREDIT_BANK + ctx.rank * SYMM_MAX_BLOCKS,
-                         sync.credit_post);
-        if (ctx.trace != nullptr)  // when the slowest CTA of this rank finished
-          *reinterpret_cast<volatile unsigned long long*>(ctx.trace + 4) = globaltimer_ns();
-      }
+    if (threadIdx.x == 0)
+      s_last = atomicAdd(sync.done_counter, 1ull) + 1ull == sync.done_target;
+    __syncthreads();
+    if (s_last != 0) {
+      if (threadIdx.x < ctx.world)  // one store per peer, in parallel
+        st_release_sys(ctx.flags_peers[threadIdx.x] + CREDIT_BANK + ctx.rank * SYMM_MAX_BLOCKS,
+                       sync.credit_post);
+      if (ctx.trace != nullptr && threadIdx.x == 0)  // when this rank's slowest CTA finished
+        *reinterpret_cast<volatile unsigned long long*>(ctx.trace + 4) = globaltimer_ns();
     }
   } else {
     // Nobody rewrites its region before everybody has drained it.

@@ -186,53 +186,110 @@ fused_allreduce_kernel(const InlineTensors inl, const TensorList tl_dev,
     trace_mark(ctx, 4);
     return;
   } else {
+    // Two-shot / NVLS, software-pipelined over sub-chunks: CTA b owns slice b
+    // of every rank's chunk and walks it in K steps. In step k it packs
+    // sub-chunk k (of all `world` rank chunks) and announces it, reduces
+    // sub-chunk k - 1 of its own rank's chunk once every peer has announced
+    // that one, writes the sums into everybody's staging buffer and announces
+    // them, and unpacks sub-chunk k - 2 once every peer has announced its
+    // sums. Packing and unpacking (local HBM traffic) thereby overlap the
+    // reduction (NVLink traffic) of the neighbouring sub-chunks. Two counters
+    // per (rank, CTA) carry the announcements: "packed" in flag bank 0,
+    // "reduced" in bank 3, both counting from ctx.epoch. After the last wait
+    // nobody reads or writes this rank's staging buffer any more, so no
+    // trailing barrier is needed; the launch consumes K + 1 epochs.
+    constexpr int REDUCED_BANK = 3 * SYMM_MAX_RANKS * SYMM_MAX_BLOCKS;
     const int64_t per_rank = (nvec + world - 1) / world;
     const int64_t per_cta = (per_rank + G - 1) / G;
-    for (int r = 0; r < world; ++r) {
-      const int64_t lo = r * per_rank + b * per_cta;
-      const int64_t hi = min(lo + per_cta, min((r + 1) * per_rank, nvec));
-      pack_range<T, W, S>(tl, stage, lo, hi, prescale, pre);
-    }
-    trace_mark(ctx, 1);
-    if (!cta_barrier(ctx, ctx.epoch + 1, b, 1)) return;
-    trace_mark(ctx, 2);
-    {
-      const int64_t lo = rank * per_rank + b * per_cta;
-      const int64_t hi = min(lo + per_cta, min((rank + 1) * per_rank, nvec));
-      if constexpr (ALGO == static_cast<int>(Algo::NVLS)) {
-        uint4* mc = reinterpret_cast<uint4*>(ctx.mc);
-        int64_t v = lo + threadIdx.x;
-        for (; v + 3 * THREADS < hi; v += 4 * THREADS) {
-          uint4 x0 = Multimem<W>::ld_reduce(mc + v);
-          uint4 x1 = Multimem<W>::ld_reduce(mc + v + THREADS);
-          uint4 x2 = Multimem<W>::ld_reduce(mc + v + 2 * THREADS);
-          uint4 x3 = Multimem<W>::ld_reduce(mc + v + 3 * THREADS);
-          multimem_st16(mc + v, x0);
-          multimem_st16(mc + v + THREADS, x1);
-          multimem_st16(mc + v + 2 * THREADS, x2);
-          multimem_st16(mc + v + 3 * THREADS, x3);
-        }
-        for (; v < hi; v += THREADS)
-          multimem_st16(mc + v, Multimem<W>::ld_reduce(mc + v));
-      } else {
-        switch (world) {
-        case 2: reduce_chunk_p2p<W, 2, 4>(ctx, lo, hi); break;
-        case 3: reduce_chunk_p2p<W, 3, 2>(ctx, lo, hi); break;
-        case 4: reduce_chunk_p2p<W, 4, 2>(ctx, lo, hi); break;
-        case 5: reduce_chunk_p2p<W, 5, 1>(ctx, lo, hi); break;
-        case 6: reduce_chunk_p2p<W, 6, 1>(ctx, lo, hi); break;
-        case 7: reduce_chunk_p2p<W, 7, 1>(ctx, lo, hi); break;
-        default: reduce_chunk_p2p<W, 8, 1>(ctx, lo, hi); break;
+    const int64_t C = ctx.sub_chunk_vecs > 0 ? ctx.sub_chunk_vecs : per_cta;
+    const int64_t K = max(int64_t(1), (per_cta + C - 1) / C);
+    auto announce = [&](int bank, uint32_t value) {
+      __syncthreads();
+      if (threadIdx.x < world)
+        st_release_sys(ctx.flags_peers[threadIdx.x] + bank + rank * SYMM_MAX_BLOCKS + b, value);
+    };
+    auto await = [&](int bank, uint32_t value, int phase) {
+      bool ok = true;
+      if (threadIdx.x < world) {
+        const uint32_t* f = ctx.flags_local + bank + threadIdx.x * SYMM_MAX_BLOCKS + b;
+        const unsigned long long t0 = globaltimer_ns();
+        int spins = 0;
+        while (static_cast<int32_t>(ld_acquire_sys(f) - value) < 0) {
+          if ((++spins & 63) == 0 && globaltimer_ns() - t0 > ctx.timeout_ns) {
+            ok = false;
+            volatile int* st = ctx.status;
+            st[1] = threadIdx.x;
+            st[2] = phase;
+            st[3] = b;
+            __threadfence_system();
+            if (st[0] == 0) st[0] = 1;
+            __threadfence_system();
+            break;
+          }
         }
       }
-    }
-    trace_mark(ctx, 3);
-    if (!cta_barrier(ctx, ctx.epoch + 2, b, 2)) return;
-    trace_mark(ctx, 4);
-    for (int r = 0; r < world; ++r) {
-      const int64_t lo = r * per_rank + b * per_cta;
-      const int64_t hi = min(lo + per_cta, min((r + 1) * per_rank, nvec));
-      unpack_range<T, W, S>(tl, stage, lo, hi, postscale, post);
+      return __syncthreads_and(ok) != 0;
+    };
+    // Vector range of sub-chunk k inside rank r's chunk, for this CTA.
+    auto sub = [&](int r, int64_t k, int64_t* lo, int64_t* hi) {
+      const int64_t base = r * per_rank + b * per_cta;
+      const int64_t end = min(base + per_cta, min((r + 1) * per_rank, nvec));
+      *lo = min(end, base + k * C);
+      *hi = min(end, base + (k + 1) * C);
+    };
+    for (int64_t k = 0; k < K + 2; ++k) {
+      if (k < K) {
+        for (int r = 0; r < world; ++r) {
+          int64_t lo, hi;
+          sub(r, k, &lo, &hi);
+          pack_range<T, W, S>(tl, stage, lo, hi, prescale, pre);
+        }
+        announce(0, ctx.epoch + static_cast<uint32_t>(k) + 1u);
+        if (k == K - 1) trace_mark(ctx, 1);
+      }
+      if (k >= 1 && k <= K) {
+        if (!await(0, ctx.epoch + static_cast<uint32_t>(k), 1)) return;
+        if (k == 1) trace_mark(ctx, 2);
+        int64_t lo, hi;
+        sub(rank, k - 1, &lo, &hi);
+        if constexpr (ALGO == static_cast<int>(Algo::NVLS)) {
+          uint4* mc = reinterpret_cast<uint4*>(ctx.mc);
+          int64_t v = lo + threadIdx.x;
+          for (; v + 3 * THREADS < hi; v += 4 * THREADS) {
+            uint4 x0 = Multimem<W>::ld_reduce(mc + v);
+            uint4 x1 = Multimem<W>::ld_reduce(mc + v + THREADS);
+            uint4 x2 = Multimem<W>::ld_reduce(mc + v + 2 * THREADS);
+            uint4 x3 = Multimem<W>::ld_reduce(mc + v + 3 * THREADS);
+            multimem_st16(mc + v, x0);
+            multimem_st16(mc + v + THREADS, x1);
+            multimem_st16(mc + v + 2 * THREADS, x2);
+            multimem_st16(mc + v + 3 * THREADS, x3);
+          }
+          for (; v < hi; v += THREADS)
+            multimem_st16(mc + v, Multimem<W>::ld_reduce(mc + v));
+        } else {
+          switch (world) {
+          case 2: reduce_chunk_p2p<W, 2, 4>(ctx, lo, hi); break;
+          case 3: reduce_chunk_p2p<W, 3, 2>(ctx, lo, hi); break;
+          case 4: reduce_chunk_p2p<W, 4, 2>(ctx, lo, hi); break;
+          case 5: reduce_chunk_p2p<W, 5, 1>(ctx, lo, hi); break;
+          case 6: reduce_chunk_p2p<W, 6, 1>(ctx, lo, hi); break;
+          case 7: reduce_chunk_p2p<W, 7, 1>(ctx, lo, hi); break;
+          default: reduce_chunk_p2p<W, 8, 1>(ctx, lo, hi); break;
+          }
+        }
+        announce(REDUCED_BANK, ctx.epoch + static_cast<uint32_t>(k));
+        if (k == K) trace_mark(ctx, 3);
+      }
+      if (k >= 2) {
+        if (!await(REDUCED_BANK, ctx.epoch + static_cast<uint32_t>(k) - 1u, 2)) return;
+        if (k == K + 1) trace_mark(ctx, 4);
+        for (int r = 0; r < world; ++r) {
+          int64_t lo, hi;
+          sub(r, k - 2, &lo, &hi);
+          unpack_range<T, W, S>(tl, stage, lo, hi, postscale, post);
+        }
+      }
     }
     trace_mark(ctx, 5);
   }

@@ -37,6 +37,10 @@ struct SymmCtx {
   // guarantees that the staging region used by this launch is not written
   // again before every peer has passed a later barrier (double buffering).
   int skip_end_barrier;
+  // Two-shot / NVLS fused allreduce: 16-byte vectors per pipeline step of one
+  // CTA inside one rank's chunk (0 = no pipelining: one step). The launch
+  // consumes ceil(per-CTA slice / sub_chunk_vecs) + 1 epochs.
+  int64_t sub_chunk_vecs;
   // Optional phase timestamps (HOROVOD_KERNEL_TRACE=1): thread 0 of CTA 0
   // stores %globaltimer into trace[slot] at the kernel's phase boundaries.
   unsigned long long* trace;
@@ -82,8 +86,19 @@ struct InlineTensors {
   void* out[INLINE_TENSORS];
 };
 
-// Number of barrier epochs a launch of each kernel consumes.
+// Number of barrier epochs a launch of each kernel consumes (the pipelined
+// two-shot / NVLS allreduce and the exchange kernels consume more: one per
+// sub-chunk, see their launch code).
 constexpr uint32_t EPOCHS_PER_LAUNCH = 4;
+// Epochs of a two-shot / NVLS fused allreduce launch over `total_vecs`
+// 16-byte vectors with `num_ctas` CTAs and `sub_chunk_vecs` per step.
+inline uint32_t FusedAllreduceEpochs(int64_t total_vecs, int world, int num_ctas,
+                                     int64_t sub_chunk_vecs) {
+  const int64_t per_rank = (total_vecs + world - 1) / world;
+  const int64_t per_cta = (per_rank + num_ctas - 1) / num_ctas;
+  const int64_t k = sub_chunk_vecs > 0 ? (per_cta + sub_chunk_vecs - 1) / sub_chunk_vecs : 1;
+  return static_cast<uint32_t>((k < 1 ? 1 : k) + 1);
+}
 // The Adasum driver launches 2 * log2(world) + 2 kernels, one epoch each.
 constexpr uint32_t ADASUM_EPOCHS = 16;
 

@@ -201,11 +201,13 @@ reducescatter_push_kernel(const T* in, T* out, const RsPushArgs args, SymmCtx ct
         }
         for (; v < v1; v += THREADS)
           st16(slot + (v << 4), load_elems<T>(base, v * N, n, aligned, prescale, pre));
-        __syncthreads();
-        if (threadIdx.x == 0)
-          st_release_sys(ctx.flags_peers[p] + rank * SYMM_MAX_BLOCKS + b,
-                         ctx.epoch + static_cast<uint32_t>(c) + 1u);
       }
+      // One barrier for the chunk of all peers, then one announcing thread per
+      // peer, so the release fences overlap instead of queueing up.
+      __syncthreads();
+      if (threadIdx.x < world && threadIdx.x != rank)
+        st_release_sys(ctx.flags_peers[threadIdx.x] + rank * SYMM_MAX_BLOCKS + b,
+                       ctx.epoch + static_cast<uint32_t>(c) + 1u);
     }
     if (c > 0) {
       // Sum chunk c - 1 of my shard once every sender has announced it.
@@ -252,16 +254,16 @@ reducescatter_push_kernel(const T* in, T* out, const RsPushArgs args, SymmCtx ct
   }
 
   if (args.credit_post != 0) {
+    // The last CTA of this rank to finish tells every peer that this launch
+    // no longer reads its region (completed loads need no fence).
+    __shared__ int s_last;
     __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence();
-      const unsigned long long done = atomicAdd(args.done_counter, 1ull) + 1ull;
-      if (done == args.done_target) {
-        for (int p = 0; p < world; ++p)
-          st_release_sys(ctx.flags_peers[p] + CREDIT_BANK + rank * SYMM_MAX_BLOCKS,
-                         args.credit_post);
-      }
-    }
+    if (threadIdx.x == 0)
+      s_last = atomicAdd(args.done_counter, 1ull) + 1ull == args.done_target;
+    __syncthreads();
+    if (s_last != 0 && threadIdx.x < world)
+      st_release_sys(ctx.flags_peers[threadIdx.x] + CREDIT_BANK + rank * SYMM_MAX_BLOCKS,
+                     args.credit_post);
   }
 }
 

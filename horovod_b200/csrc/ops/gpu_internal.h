@@ -116,7 +116,9 @@ class NcclOps;
 
 class GpuOps : public OpExecutor {
 public:
-  explicit GpuOps(GlobalState& s);
+  // `slot`: which of this process's devices (in order of first use) this
+  // executor serves; see MultiDeviceGpuOps.
+  explicit GpuOps(GlobalState& s, int slot = 0);
   ~GpuOps() override;
 
   Status Execute(std::vector<TensorTableEntry>& entries,
@@ -213,6 +215,7 @@ private:
   bool ExchangePushes(const SymmSet& set, int64_t total_bytes) const;
 
   GlobalState& state_;
+  int slot_ = 0;
   std::shared_ptr<DoneEventPool> events_;
   std::string backend_pref_;
   bool async_completion_ = true;
@@ -239,6 +242,8 @@ private:
   int64_t dynamic_min_bytes_ = 0;
   int64_t exchange_chunk_bytes_ = 256 << 10;  // HOROVOD_EXCHANGE_CHUNK_KB
   int64_t exchange_push_max_ = 1 << 20;       // HOROVOD_EXCHANGE_PUSH_MAX_BYTES
+  int64_t allreduce_subchunk_bytes_ = 64 << 10;  // HOROVOD_ALLREDUCE_SUBCHUNK_KB, 0 = off
+  int64_t allreduce_pipeline_min_ = 8 << 20;     // HOROVOD_ALLREDUCE_PIPELINE_MIN_BYTES
   unsigned long long* xchg_done_counter_ = nullptr;  // device word, see kern::ExchangeSync
   unsigned long long xchg_done_base_ = 0;
   unsigned long long* trace_host_ = nullptr;  // mapped pinned, HOROVOD_KERNEL_TRACE=1
@@ -279,6 +284,21 @@ private:
   std::mutex timing_mu_;
   std::vector<PendingTiming> pending_timings_;
   std::vector<cudaEvent_t> timing_events_;  // free list
+};
+
+// Routes every response to the executor of the device its tensors live on.
+class MultiDeviceGpuOps : public OpExecutor {
+public:
+  explicit MultiDeviceGpuOps(GlobalState& s) : state_(s) {}
+  Status Execute(std::vector<TensorTableEntry>& entries, const Response& response,
+                 ProcessSet& ps) override;
+  void Shutdown() override;
+
+private:
+  static constexpr size_t kMaxDevices = 8;
+  GlobalState& state_;
+  std::vector<int> devices_;  // device ordinal of each executor
+  std::vector<std::unique_ptr<GpuOps>> executors_;
 };
 
 // The executor of the running job (null when there is none); used by the

@@ -41,8 +41,49 @@ void RegisterGpuOps() {
       return nullptr;
     }
     SetGpuBackendDescription("pending (no device collective has run yet)");
-    return std::unique_ptr<OpExecutor>(new GpuOps(s));
+    return std::unique_ptr<OpExecutor>(new MultiDeviceGpuOps(s));
   });
+}
+
+// ---------------------------------------------------------------------------
+// One GpuOps per device a process hands tensors from. The usual job has one
+// GPU per process and therefore one executor; a process that spreads a model
+// over several of its GPUs (layers on two devices of one rank, every rank
+// alike) gets one executor, with its own stream, arena and flags, per device.
+// Executors are numbered in the order their devices first appear: responses
+// are executed in the same order on every rank, so "the second device" means
+// the same model stage everywhere, whatever the local device ordinals are.
+// Parity: test/parallel/test_torch.py:1860-1904 (model parallelism inside a
+// rank is tolerated; the reference keeps one NCCL communicator per device
+// vector, horovod/common/ops/nccl_operations.h:40-49).
+
+Status MultiDeviceGpuOps::Execute(std::vector<TensorTableEntry>& entries,
+                                  const Response& response, ProcessSet& ps) {
+  int device = -1;
+  for (auto& e : entries)
+    if (e.device != CPU_DEVICE_ID && (e.input || e.output)) device = e.device;
+  size_t slot = 0;
+  if (device >= 0) {
+    for (; slot < devices_.size(); ++slot)
+      if (devices_[slot] == device) break;
+    if (slot == devices_.size()) {
+      if (slot >= kMaxDevices)
+        return Status::PreconditionError(
+            "This process uses more than " + std::to_string(kMaxDevices) +
+            " CUDA devices with Horovod.");
+      devices_.push_back(device);
+      executors_.emplace_back(new GpuOps(state_, static_cast<int>(slot)));
+    }
+  } else if (executors_.empty()) {
+    // A joined rank's stand-in has no device of its own: use the default.
+    devices_.push_back(-1);
+    executors_.emplace_back(new GpuOps(state_, 0));
+  }
+  return executors_[std::min(slot, executors_.size() - 1)]->Execute(entries, response, ps);
+}
+
+void MultiDeviceGpuOps::Shutdown() {
+  for (auto& e : executors_) e->Shutdown();
 }
 
 // ---------------------------------------------------------------------------
@@ -117,7 +158,8 @@ void DescriptorRing::Release(const Slot& slot, cudaStream_t stream) {
 
 // ---------------------------------------------------------------------------
 
-GpuOps::GpuOps(GlobalState& s) : state_(s), events_(new DoneEventPool()) {
+GpuOps::GpuOps(GlobalState& s, int slot)
+    : state_(s), slot_(slot), events_(new DoneEventPool()) {
   backend_pref_ = EnvString(HVD_ENV_GPU_BACKEND, "symm");
   async_completion_ = EnvBool(HVD_ENV_ENABLE_ASYNC_COMPLETION, !s.elastic_enabled);
   want_nvls_ = EnvBool(HVD_ENV_SYMM_NVLS, true);
@@ -129,7 +171,7 @@ GpuOps::GpuOps(GlobalState& s) : state_(s), events_(new DoneEventPool()) {
   forced_algo_ = EnvString(HVD_ENV_ALGO, "auto");
   timing_ = EnvBool("HOROVOD_GPU_OP_TIMING", false);
   inline_descriptors_ = EnvBool("HOROVOD_INLINE_DESCRIPTORS", true);
-  g_current = this;
+  if (slot == 0) g_current = this;  // diagnostics and the symmetric heap use the first
 }
 
 GpuOps::~GpuOps() { Shutdown(); }
@@ -138,9 +180,8 @@ void GpuOps::EnsureDevice(int device) {
   if (device_ == device) return;
   if (device_ >= 0)
     throw std::runtime_error(
-        "All CUDA tensors given to Horovod by one process must live on one "
-        "device (first saw cuda:" + std::to_string(device_) + ", now cuda:" +
-        std::to_string(device) + ").");
+        "internal error: device executor for cuda:" + std::to_string(device_) +
+        " was handed a tensor on cuda:" + std::to_string(device));
   HVD_CUDA(cudaSetDevice(device));
   int lo = 0, hi = 0;
   HVD_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
@@ -158,6 +199,9 @@ void GpuOps::EnsureDevice(int device) {
   exchange_chunk_bytes_ =
       std::max<int64_t>(64, EnvInt("HOROVOD_EXCHANGE_CHUNK_KB", 256)) << 10;
   exchange_push_max_ = EnvInt("HOROVOD_EXCHANGE_PUSH_MAX_BYTES", 1 << 20);
+  allreduce_pipeline_min_ = EnvInt("HOROVOD_ALLREDUCE_PIPELINE_MIN_BYTES", 8 << 20);
+  allreduce_subchunk_bytes_ =
+      std::max<int64_t>(0, EnvInt("HOROVOD_ALLREDUCE_SUBCHUNK_KB", 64)) * 1024 / 256 * 256;
   HVD_CUDA(cudaMalloc(reinterpret_cast<void**>(&xchg_done_counter_), sizeof(unsigned long long)));
   HVD_CUDA(cudaMemset(xchg_done_counter_, 0, sizeof(unsigned long long)));
   xchg_done_base_ = 0;
@@ -184,8 +228,10 @@ void GpuOps::EnsureArena(ProcessSet& ps) {
   if (state_.config.rank == 0)
     HVD_LOG(INFO) << "GPU topology: " << DiscoverTopology().Summary();
   size_t mb = static_cast<size_t>(EnvInt(HVD_ENV_SYMM_BUFFER_MB, 1024));
-  // The token doubles as socket-name salt: distinct per job and per init.
-  uint64_t token = state_.config.token ^ 0x9e3779b97f4a7c15ull;
+  // The token doubles as socket-name salt: distinct per job, per init and per
+  // device executor of this process.
+  uint64_t token = (state_.config.token ^ 0x9e3779b97f4a7c15ull) +
+                   0x100000001b3ull * static_cast<uint64_t>(slot_);
   size_t heap_mb = static_cast<size_t>(EnvInt("HOROVOD_SYMM_HEAP_MB", 2048));
   Status st = arena_.Create(ps.comm, device_, (mb + heap_mb) << 20, want_nvls_, token);
   if (!st.ok()) {

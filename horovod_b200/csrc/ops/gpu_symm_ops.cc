@@ -186,7 +186,18 @@ Status GpuOps::SymmAllreduce(std::vector<TensorTableEntry>& entries,
         staging_off = set.oneshot_off[set.oneshot_count++ & 1];
         skip_end = true;
       }
-      kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH, staging_off, skip_end);
+      // Two-shot / NVLS launches of 8 MB and more run as a pipeline over
+      // sub-chunks (pack, reduce and unpack of neighbouring sub-chunks
+      // overlap); every rank derives the same step count from the same sizes.
+      int64_t sub_vecs = 0;
+      uint32_t epochs = kern::EPOCHS_PER_LAUNCH;
+      if (algo == kern::Algo::TWOSHOT || algo == kern::Algo::NVLS) {
+        if (bytes >= allreduce_pipeline_min_ && allreduce_subchunk_bytes_ > 0)
+          sub_vecs = allreduce_subchunk_bytes_ / 16;
+        epochs = std::max(epochs, kern::FusedAllreduceEpochs(bytes / 16, set.world, ctas, sub_vecs));
+      }
+      kern::SymmCtx ctx = MakeCtx(set, epochs, staging_off, skip_end);
+      ctx.sub_chunk_vecs = sub_vecs;
       err = kern::LaunchFusedAllreduce(list, dtype, adasum ? dtype : wire,
                                        response.prescale, response.postscale,
                                        algo, ctas, ctx, stream_,

@@ -466,3 +466,108 @@ def test_reducescatter_from_ordinary_memory():
     if _ngpu() < 2:
         pytest.skip("needs 2 GPUs")
     assert all(run_parallel(_reducescatter_push, np=_world(), timeout=300))
+
+
+def _two_devices_per_rank(rank, size):
+    """Every rank spreads a two-layer model over two of the box's GPUs (layer
+    one on the first, layer two on the second) and trains it through
+    DistributedOptimizer; gradients arrive from both devices. Compared with
+    the same model trained in one piece on the concatenated batch."""
+    os.environ["HOROVOD_SPIN_TIMEOUT_MS"] = "5000"
+    import horovod_b200.torch as hvd
+    hvd.init()
+    d0, d1 = torch.device("cuda", 2 * rank), torch.device("cuda", 2 * rank + 1)
+    torch.manual_seed(0)
+    l1, l2 = torch.nn.Linear(16, 32), torch.nn.Linear(32, 4)
+    ref1, ref2 = torch.nn.Linear(16, 32), torch.nn.Linear(32, 4)
+    ref1.load_state_dict(l1.state_dict())
+    ref2.load_state_dict(l2.state_dict())
+    l1.to(d0)
+    l2.to(d1)
+    params = [("l1." + n, p) for n, p in l1.named_parameters()] + \
+             [("l2." + n, p) for n, p in l2.named_parameters()]
+    opt = hvd.DistributedOptimizer(torch.optim.SGD([p for _, p in params], lr=0.1),
+                                   named_parameters=params)
+    hvd.broadcast_parameters(dict(params), root_rank=0)
+    ref_opt = torch.optim.SGD(list(ref1.parameters()) + list(ref2.parameters()), lr=0.1)
+    ok = True
+    for step in range(3):
+        g = torch.Generator().manual_seed(100 + step)
+        full = torch.randn(4 * size, 16, generator=g)
+        mine = full[4 * rank:4 * rank + 4]
+        opt.zero_grad()
+        out = l2(torch.relu(l1(mine.to(d0))).to(d1))
+        out.square().mean().backward()
+        opt.step()
+        ref_opt.zero_grad()
+        ref2(torch.relu(ref1(full))).square().mean().backward()
+        ref_opt.step()
+    for (n, p), q in zip(params, list(ref1.parameters()) + list(ref2.parameters())):
+        ok = ok and torch.allclose(p.detach().cpu(), q.detach(), rtol=1e-5, atol=1e-6)
+    # plain collectives on both devices, interleaved
+    for i, dev in enumerate((d0, d1, d0, d1)):
+        x = torch.full((1000,), float(rank + 1), device=dev)
+        s = hvd.allreduce(x, op=hvd.Sum, prescale_factor=0.5, name="md.ar.%d" % i)
+        ok = ok and s.device == dev and \
+            torch.allclose(s.cpu(), torch.full((1000,), 0.5 * sum(range(1, size + 1))))
+        g = hvd.allgather(torch.full((2,), float(rank), device=dev), name="md.ag.%d" % i)
+        ok = ok and g.cpu().tolist() == [float(r) for r in range(size) for _ in range(2)]
+    torch.cuda.synchronize(d0)
+    torch.cuda.synchronize(d1)
+    hvd.shutdown()
+    return ok
+
+
+def test_two_devices_in_one_rank():
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    ranks = 2 if _ngpu() >= 4 else 1
+    assert all(run_parallel(_two_devices_per_rank, np=ranks, timeout=300))
+
+
+def _allreduce_pipelined(rank, size, algo):
+    """The two-shot / NVLS fused allreduce as a pipeline of many small steps
+    (tiny sub-chunks, pipelining from 64 KB on), over fused groups and large
+    single tensors, several launches in a row."""
+    os.environ["HOROVOD_ALLREDUCE_ALGO"] = algo
+    os.environ["HOROVOD_ALLREDUCE_PIPELINE_MIN_BYTES"] = str(64 << 10)
+    os.environ["HOROVOD_ALLREDUCE_SUBCHUNK_KB"] = "4"
+    os.environ["HOROVOD_SPIN_TIMEOUT_MS"] = "5000"
+    import horovod_b200.torch as hvd
+    hvd.init()
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    ok = True
+    for it in range(3):
+        for dtype, n, tol in ((torch.float32, (3 << 20) + 5, 1e-5), (torch.bfloat16, 1 << 20, 4e-2),
+                              (torch.float32, 70001, 1e-5), (torch.float16, 300007, 8e-3)):
+            x = _inputs(rank + 10 * it, n, dtype).to(dev)
+            out = hvd.allreduce(x, op=hvd.Sum, name="pl.%s.%d" % (dtype, n))
+            ref = sum(_inputs(r + 10 * it, n, dtype).double() for r in range(size))
+            err = (out.double().cpu() - ref).abs().max().item()
+            ok = ok and err <= tol * size * max(1.0, ref.abs().max().item())
+        shapes = [3, 129, 200001, 77777, 5, 1 << 19]
+        xs = [_inputs(rank * 31 + i + it, s, torch.float32).to(dev) for i, s in enumerate(shapes)]
+        outs = hvd.grouped_allreduce(xs, op=hvd.Average, name="pl.grp")
+        for i, (s, o) in enumerate(zip(shapes, outs)):
+            ref = sum(_inputs(r * 31 + i + it, s, torch.float32).double()
+                      for r in range(size)) / size
+            ok = ok and (o.double().cpu() - ref).abs().max().item() < 1e-5
+        # fp32 tensors on a 16-bit wire
+        xs = [_inputs(rank * 13 + i + it, s, torch.float32).to(dev) for i, s in enumerate(shapes)]
+        hvd.synchronize(hvd.grouped_allreduce_async_(xs, op=hvd.Average,
+                                                     wire_dtype=torch.bfloat16, name="pl.wire"))
+        for i, (s, o) in enumerate(zip(shapes, xs)):
+            ref = sum(_inputs(r * 13 + i + it, s, torch.float32).bfloat16().double()
+                      for r in range(size)) / size
+            ok = ok and (o.double().cpu() - ref).abs().max().item() < 4e-2 * size
+    torch.cuda.synchronize()
+    hvd.shutdown()
+    return ok
+
+
+@pytest.mark.parametrize("algo", ["twoshot", "nvls"])
+def test_pipelined_fused_allreduce(algo):
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    assert all(run_parallel(_allreduce_pipelined, np=_world(), args=(algo,), timeout=300))

@@ -99,6 +99,9 @@ class TorchReadyEvent : public ReadyEvent {
 public:
   explicit TorchReadyEvent(int device) : device_(device) {
     event_ = Events().Get(device);
+    // The default stream's handle means "the default stream of the current
+    // device", so that device must be current while the event is recorded.
+    c10::cuda::CUDAGuard guard(device);
     auto stream = at::cuda::getCurrentCUDAStream(device);
     if (cudaEventRecord(event_, stream.stream()) != cudaSuccess)
       throw std::runtime_error("hvd: cudaEventRecord failed");
@@ -458,6 +461,7 @@ py::tuple WaitAndClear(int handle) {
   Handles().Release(handle);
   ThrowIfError(rec->status);
   if (rec->done_event && rec->device != CPU_DEVICE_ID) {
+    c10::cuda::CUDAGuard guard(rec->device);  // see TorchReadyEvent
     auto stream = at::cuda::getCurrentCUDAStream(rec->device);
     cudaStreamWaitEvent(stream.stream(),
                         static_cast<cudaEvent_t>(rec->done_event.get()), 0);

@@ -97,7 +97,7 @@ def main():
 
     PHASES = ("start", "packed", "barrier1", "reduced", "barrier2", "unpacked")
 
-    XPHASES = ("start", "staged", "pulled", "done", "last_cta_done")
+    XPHASES = ("start", "staged", "pulled", "done", "last_cta_done", "credit_wait")
 
     def phases(fn, PHASES=PHASES):
         """Median offsets (us since kernel start, CTA 0 of this rank) of the
@@ -107,7 +107,10 @@ def main():
             fn()
             torch.cuda.synchronize()
             t = _C.kernel_trace()
-            cols.append([(t[i] - t[0]) / 1e3 if t[i] >= t[0] and t[i] else -1.0
+            # ("credit_wait": from kernel entry to "start", i.e. the wait for the
+            # exchange region to be free)
+            cols.append([(t[0] - t[i]) / 1e3 if PHASES[i] == "credit_wait" and t[i]
+                         else (t[i] - t[0]) / 1e3 if t[i] >= t[0] and t[i] else -1.0
                          for i in range(len(PHASES))])
             hvd.allreduce(torch.zeros(1), name="sweep.phase.sync")
         med = [statistics.median(c[i] for c in cols) for i in range(len(PHASES))]

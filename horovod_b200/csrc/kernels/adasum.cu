@@ -106,7 +106,7 @@ __device__ __forceinline__ void accumulate(uint4 xa, uint4 xb, double& d, double
 // tensors holds zeros and adds nothing).
 __global__ void __launch_bounds__(THREADS)
 adasum_dots_kernel(TensorList tl, SymmCtx ctx, int level, uint32_t epoch,
-                   double* scratch_level) {
+                   double* scratch_level, int64_t copy_off) {
   constexpr int N = 4;
   if (!cta_barrier(ctx, epoch, blockIdx.x, 10 + 2 * level)) return;
   const int64_t nvec = tl.offsets[tl.n] / N;
@@ -115,8 +115,10 @@ adasum_dots_kernel(TensorList tl, SymmCtx ctx, int level, uint32_t epoch,
   const bool lower = ((ctx.rank >> level) & 1) == 0;
   const uint4* mine = reinterpret_cast<const uint4*>(ctx.local);
   const uint4* theirs = reinterpret_cast<const uint4*>(ctx.peers[partner]);
-  const uint4* a = lower ? mine : theirs;
-  const uint4* bb = lower ? theirs : mine;
+  // The partner's half crosses NVLink once: while it is read for the dot
+  // products it is also written to a local copy (vector v of the kept range
+  // at copy[v - keep.lo]) that the combine kernel reads instead.
+  uint4* copy = copy_off >= 0 ? reinterpret_cast<uint4*>(ctx.local + copy_off) - keep.lo : nullptr;
 
   const int64_t len = keep.hi - keep.lo;
   const int64_t per = (len + gridDim.x - 1) / gridDim.x;
@@ -129,16 +131,29 @@ adasum_dots_kernel(TensorList tl, SymmCtx ctx, int level, uint32_t epoch,
     double d = 0, na = 0, nb = 0;
     int64_t v = v0 + threadIdx.x;
     for (; v + 3 * THREADS < v1; v += 4 * THREADS) {
-      uint4 xa[4], xb[4];
+      uint4 xm[4], xt[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        xa[u] = ld16(a + v + u * THREADS);
-        xb[u] = ld16(bb + v + u * THREADS);
+        xm[u] = ld16(mine + v + u * THREADS);
+        xt[u] = ld16(theirs + v + u * THREADS);
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) accumulate(xa[u], xb[u], d, na, nb);
+      for (int u = 0; u < 4; ++u) {
+        if (copy != nullptr) st16(copy + v + u * THREADS, xt[u]);
+        if (lower)
+          accumulate(xm[u], xt[u], d, na, nb);
+        else
+          accumulate(xt[u], xm[u], d, na, nb);
+      }
     }
-    for (; v < v1; v += THREADS) accumulate(ld16(a + v), ld16(bb + v), d, na, nb);
+    for (; v < v1; v += THREADS) {
+      const uint4 xm = ld16(mine + v), xt = ld16(theirs + v);
+      if (copy != nullptr) st16(copy + v, xt);
+      if (lower)
+        accumulate(xm, xt, d, na, nb);
+      else
+        accumulate(xt, xm, d, na, nb);
+    }
     block_flush_sums(scratch_level, t, d, na, nb);
   }
 }
@@ -147,7 +162,7 @@ adasum_dots_kernel(TensorList tl, SymmCtx ctx, int level, uint32_t epoch,
 // the sums of all ranks that jointly hold a and b.
 __global__ void __launch_bounds__(THREADS)
 adasum_combine_kernel(TensorList tl, SymmCtx ctx, int level, uint32_t epoch,
-                      int64_t scratch_level_off) {
+                      int64_t scratch_level_off, int64_t copy_off) {
   constexpr int N = 4;
   if (!cta_barrier(ctx, epoch, blockIdx.x, 11 + 2 * level)) return;
   const int64_t nvec = tl.offsets[tl.n] / N;
@@ -155,10 +170,14 @@ adasum_combine_kernel(TensorList tl, SymmCtx ctx, int level, uint32_t epoch,
   const int partner = ctx.rank ^ (1 << level);
   const bool lower = ((ctx.rank >> level) & 1) == 0;
   uint4* mine = reinterpret_cast<uint4*>(ctx.local);
-  const uint4* theirs = reinterpret_cast<const uint4*>(ctx.peers[partner]);
+  // The partner's half: the local copy the dots kernel made, if there is one.
+  const uint4* theirs =
+      copy_off >= 0 ? reinterpret_cast<const uint4*>(ctx.local + copy_off) - keep.lo
+                    : reinterpret_cast<const uint4*>(ctx.peers[partner]);
   const int group = 2 << level;
   const int first = ctx.rank / group * group;
   __shared__ float coeff[2];
+  __shared__ double s_sums[3 * SYMM_MAX_RANKS];
 
   const int64_t len = keep.hi - keep.lo;
   const int64_t per = (len + gridDim.x - 1) / gridDim.x;
@@ -168,14 +187,21 @@ adasum_combine_kernel(TensorList tl, SymmCtx ctx, int level, uint32_t epoch,
     const int64_t toff = tl.offsets[t];
     if (toff >= hi * N) break;
     const int64_t v0 = max(lo, toff / N), v1 = min(hi, tl.offsets[t + 1] / N);
+    // The three sums of every rank of the group, one peer read per thread
+    // (all in flight together), then summed in rank order.
+    if (threadIdx.x < 3 * group) {
+      const int q = threadIdx.x / 3, c = threadIdx.x % 3;
+      const volatile double* s = reinterpret_cast<const volatile double*>(
+          ctx.peers[first + q] + scratch_level_off);
+      s_sums[threadIdx.x] = s[3 * t + c];
+    }
+    __syncthreads();
     if (threadIdx.x == 0) {
       double d = 0, na = 0, nb = 0;
       for (int q = 0; q < group; ++q) {
-        const volatile double* s = reinterpret_cast<const volatile double*>(
-            ctx.peers[first + q] + scratch_level_off);
-        d += s[3 * t];
-        na += s[3 * t + 1];
-        nb += s[3 * t + 2];
+        d += s_sums[3 * q];
+        na += s_sums[3 * q + 1];
+        nb += s_sums[3 * q + 2];
       }
       // sqrt(DBL_MIN): below this a squared norm counts as zero.
       const double tiny = 1.4916681462400413e-154;
@@ -231,8 +257,8 @@ adasum_gather_kernel(TensorList tl, SymmCtx ctx, int levels, uint32_t epoch,
 
 template <typename T>
 cudaError_t LaunchTyped(const TensorList& tl, double prescale, double postscale,
-                        int64_t scratch_off, int num_ctas, const SymmCtx& ctx,
-                        cudaStream_t stream) {
+                        int64_t scratch_off, int64_t copy_off, int num_ctas,
+                        const SymmCtx& ctx, cudaStream_t stream) {
   int levels = 0;
   while ((1 << levels) < ctx.world) ++levels;
   CountKernelLaunches(2 * levels + 2);
@@ -243,10 +269,10 @@ cudaError_t LaunchTyped(const TensorList& tl, double prescale, double postscale,
   uint32_t epoch = ctx.epoch;
   for (int l = 0; l < levels; ++l) {
     adasum_dots_kernel<<<num_ctas, THREADS, 0, stream>>>(
-        tl, ctx, l, ++epoch, scratch + static_cast<int64_t>(l) * per_level);
+        tl, ctx, l, ++epoch, scratch + static_cast<int64_t>(l) * per_level, copy_off);
     adasum_combine_kernel<<<num_ctas, THREADS, 0, stream>>>(
         tl, ctx, l, ++epoch,
-        scratch_off + static_cast<int64_t>(l) * per_level * sizeof(double));
+        scratch_off + static_cast<int64_t>(l) * per_level * sizeof(double), copy_off);
   }
   ++epoch;
   adasum_gather_kernel<T><<<num_ctas, THREADS, 0, stream>>>(
@@ -258,16 +284,16 @@ cudaError_t LaunchTyped(const TensorList& tl, double prescale, double postscale,
 
 cudaError_t LaunchAdasum(const TensorList& tl, DataType dtype, double prescale,
                          double postscale, int64_t scratch_off, int num_ctas,
-                         const SymmCtx& ctx, cudaStream_t stream) {
+                         const SymmCtx& ctx, cudaStream_t stream, int64_t copy_off) {
   if (num_ctas < 1 || num_ctas > SYMM_MAX_BLOCKS) return cudaErrorInvalidValue;
   if ((ctx.world & (ctx.world - 1)) != 0) return cudaErrorInvalidValue;
   switch (dtype) {
   case DataType::FLOAT32:
-    return LaunchTyped<float>(tl, prescale, postscale, scratch_off, num_ctas, ctx, stream);
+    return LaunchTyped<float>(tl, prescale, postscale, scratch_off, copy_off, num_ctas, ctx, stream);
   case DataType::FLOAT16:
-    return LaunchTyped<__half>(tl, prescale, postscale, scratch_off, num_ctas, ctx, stream);
+    return LaunchTyped<__half>(tl, prescale, postscale, scratch_off, copy_off, num_ctas, ctx, stream);
   case DataType::BFLOAT16:
-    return LaunchTyped<__nv_bfloat16>(tl, prescale, postscale, scratch_off, num_ctas, ctx, stream);
+    return LaunchTyped<__nv_bfloat16>(tl, prescale, postscale, scratch_off, copy_off, num_ctas, ctx, stream);
   default:
     return cudaErrorInvalidValue;
   }

@@ -276,10 +276,14 @@ cudaError_t LaunchExchange(const ExchangePlan& plan, const ExchangeSync& sync, i
 // dot / squared norms accumulated in fp64, and scattered back. `scratch`
 // holds 3 * n doubles per level per rank inside the staging area (offset
 // given in bytes, 256-byte aligned).
+// copy_off >= 0: byte offset (256-byte aligned, inside the staging area) of
+// room for half of the packed data: the partner's half is then copied there
+// while the dot products read it, and the combine step reads the copy, so
+// every level moves its data over NVLink once instead of twice.
 cudaError_t LaunchAdasum(const TensorList& tensors, DataType dtype,
                          double prescale, double postscale,
                          int64_t scratch_off, int num_ctas, const SymmCtx& ctx,
-                         cudaStream_t stream);
+                         cudaStream_t stream, int64_t copy_off = -1);
 
 // Stand-alone helpers (NCCL path and odd cases).
 // Batched (optionally scaled / casting) copy between tensor storage and a

@@ -118,7 +118,9 @@ class GpuOps : public OpExecutor {
 public:
   // `slot`: which of this process's devices (in order of first use) this
   // executor serves; see MultiDeviceGpuOps.
-  explicit GpuOps(GlobalState& s, int slot = 0);
+  // `lane` of `lanes`: which of the communication streams of that device
+  // (HOROVOD_NUM_NCCL_STREAMS) this executor is.
+  explicit GpuOps(GlobalState& s, int slot = 0, int lane = 0, int lanes = 1);
   ~GpuOps() override;
 
   Status Execute(std::vector<TensorTableEntry>& entries,
@@ -216,6 +218,7 @@ private:
 
   GlobalState& state_;
   int slot_ = 0;
+  int lane_ = 0, lanes_ = 1;
   std::shared_ptr<DoneEventPool> events_;
   std::string backend_pref_;
   bool async_completion_ = true;
@@ -289,17 +292,27 @@ private:
 // Routes every response to the executor of the device its tensors live on.
 class MultiDeviceGpuOps : public OpExecutor {
 public:
-  explicit MultiDeviceGpuOps(GlobalState& s) : state_(s) {}
+  explicit MultiDeviceGpuOps(GlobalState& s);
   Status Execute(std::vector<TensorTableEntry>& entries, const Response& response,
                  ProcessSet& ps) override;
   void Shutdown() override;
 
 private:
   static constexpr size_t kMaxDevices = 8;
+  static constexpr int kMaxStreams = 4;
   GlobalState& state_;
-  std::vector<int> devices_;  // device ordinal of each executor
-  std::vector<std::unique_ptr<GpuOps>> executors_;
+  int num_streams_ = 1;       // HOROVOD_NUM_NCCL_STREAMS
+  size_t next_lane_ = 0;
+  std::vector<int> devices_;  // device ordinal behind each row of executors_
+  // executors_[device slot][lane]: one executor, with its own stream, arena,
+  // flag words, NCCL communicators and finalizer thread, per device and
+  // communication stream
+  // (horovod/common/global_state.h:92-95, operations.cc:436-449).
+  std::vector<std::vector<std::unique_ptr<GpuOps>>> executors_;
 };
+
+// Timings of every executor of the process (HOROVOD_GPU_OP_TIMING=1).
+std::vector<GpuOps::OpTiming> DrainAllGpuTimings();
 
 // The executor of the running job (null when there is none); used by the
 // diagnostics binding.

@@ -22,6 +22,19 @@ std::atomic<GpuOps*> g_current{nullptr};
 
 GpuOps* CurrentGpuOps() { return g_current.load(); }
 
+namespace {
+// Every live executor (one per device and communication stream), for the
+// diagnostics that sum over them.
+std::mutex& g_registry_mu_ref() {
+  static std::mutex mu;
+  return mu;
+}
+std::vector<GpuOps*>& g_registry_ref() {
+  static std::vector<GpuOps*> v;
+  return v;
+}
+}  // namespace
+
 void SetGpuBackendDescription(const std::string& s) {
   std::lock_guard<std::mutex> l(g_desc_mu);
   g_backend_desc = s;
@@ -57,6 +70,11 @@ void RegisterGpuOps() {
 // rank is tolerated; the reference keeps one NCCL communicator per device
 // vector, horovod/common/ops/nccl_operations.h:40-49).
 
+MultiDeviceGpuOps::MultiDeviceGpuOps(GlobalState& s) : state_(s) {
+  num_streams_ = static_cast<int>(
+      std::min<int64_t>(kMaxStreams, std::max<int64_t>(1, EnvInt(HVD_ENV_NUM_STREAMS, 1))));
+}
+
 Status MultiDeviceGpuOps::Execute(std::vector<TensorTableEntry>& entries,
                                   const Response& response, ProcessSet& ps) {
   int device = -1;
@@ -72,18 +90,51 @@ Status MultiDeviceGpuOps::Execute(std::vector<TensorTableEntry>& entries,
             "This process uses more than " + std::to_string(kMaxDevices) +
             " CUDA devices with Horovod.");
       devices_.push_back(device);
-      executors_.emplace_back(new GpuOps(state_, static_cast<int>(slot)));
+      executors_.emplace_back();
     }
   } else if (executors_.empty()) {
     // A joined rank's stand-in has no device of its own: use the default.
     devices_.push_back(-1);
-    executors_.emplace_back(new GpuOps(state_, 0));
+    executors_.emplace_back();
   }
-  return executors_[std::min(slot, executors_.size() - 1)]->Execute(entries, response, ps);
+  slot = std::min(slot, executors_.size() - 1);
+  auto& lanes = executors_[slot];
+  // Several communication streams: responses take the lanes in turn (every
+  // rank executes the same responses in the same order, so all ranks pick the
+  // same lane for a response). Tensors in the symmetric heap belong to the
+  // first lane, whose arena holds that heap.
+  size_t lane = 0;
+  if (num_streams_ > 1) {
+    lane = next_lane_++ % static_cast<size_t>(num_streams_);
+    if (!lanes.empty() && lanes[0] != nullptr)
+      for (auto& e : entries)
+        if (e.input != nullptr && lanes[0]->InSymmHeap(e.input, 1, nullptr)) lane = 0;
+  }
+  if (lanes.size() <= lane) lanes.resize(lane + 1);
+  if (lanes[lane] == nullptr)
+    lanes[lane].reset(new GpuOps(state_, static_cast<int>(slot), static_cast<int>(lane),
+                                 num_streams_));
+  return lanes[lane]->Execute(entries, response, ps);
 }
 
 void MultiDeviceGpuOps::Shutdown() {
-  for (auto& e : executors_) e->Shutdown();
+  for (auto& lanes : executors_)
+    for (auto& e : lanes)
+      if (e) e->Shutdown();
+}
+
+std::vector<GpuOps::OpTiming> DrainAllGpuTimings() {
+  std::vector<GpuOps*> all;
+  {
+    std::lock_guard<std::mutex> l(g_registry_mu_ref());
+    all = g_registry_ref();
+  }
+  std::vector<GpuOps::OpTiming> out;
+  for (GpuOps* ops : all) {
+    auto part = ops->DrainTimings();
+    out.insert(out.end(), part.begin(), part.end());
+  }
+  return out;
 }
 
 // ---------------------------------------------------------------------------
@@ -158,8 +209,9 @@ void DescriptorRing::Release(const Slot& slot, cudaStream_t stream) {
 
 // ---------------------------------------------------------------------------
 
-GpuOps::GpuOps(GlobalState& s, int slot)
-    : state_(s), slot_(slot), events_(new DoneEventPool()) {
+GpuOps::GpuOps(GlobalState& s, int slot, int lane, int lanes)
+    : state_(s), slot_(slot), lane_(lane), lanes_(std::max(1, lanes)),
+      events_(new DoneEventPool()) {
   backend_pref_ = EnvString(HVD_ENV_GPU_BACKEND, "symm");
   async_completion_ = EnvBool(HVD_ENV_ENABLE_ASYNC_COMPLETION, !s.elastic_enabled);
   want_nvls_ = EnvBool(HVD_ENV_SYMM_NVLS, true);
@@ -171,7 +223,9 @@ GpuOps::GpuOps(GlobalState& s, int slot)
   forced_algo_ = EnvString(HVD_ENV_ALGO, "auto");
   timing_ = EnvBool("HOROVOD_GPU_OP_TIMING", false);
   inline_descriptors_ = EnvBool("HOROVOD_INLINE_DESCRIPTORS", true);
-  if (slot == 0) g_current = this;  // diagnostics and the symmetric heap use the first
+  if (slot == 0 && lane == 0) g_current = this;  // diagnostics and the symmetric heap
+  std::lock_guard<std::mutex> l(g_registry_mu_ref());
+  g_registry_ref().push_back(this);
 }
 
 GpuOps::~GpuOps() { Shutdown(); }
@@ -231,8 +285,9 @@ void GpuOps::EnsureArena(ProcessSet& ps) {
   // The token doubles as socket-name salt: distinct per job, per init and per
   // device executor of this process.
   uint64_t token = (state_.config.token ^ 0x9e3779b97f4a7c15ull) +
-                   0x100000001b3ull * static_cast<uint64_t>(slot_);
-  size_t heap_mb = static_cast<size_t>(EnvInt("HOROVOD_SYMM_HEAP_MB", 2048));
+                   0x100000001b3ull * static_cast<uint64_t>(slot_ * 16 + lane_);
+  // Only the first lane of a device carries the symmetric heap.
+  size_t heap_mb = lane_ == 0 ? static_cast<size_t>(EnvInt("HOROVOD_SYMM_HEAP_MB", 4096)) : 0;
   Status st = arena_.Create(ps.comm, device_, (mb + heap_mb) << 20, want_nvls_, token);
   if (!st.ok()) {
     HVD_LOG(WARNING) << st.reason()
@@ -349,16 +404,22 @@ Status GpuOps::CheckKernelStatus() {
 
 int GpuOps::PickCtas(int64_t bytes) const {
   if (forced_ctas_ > 0) return std::min(forced_ctas_, SYMM_MAX_BLOCKS);
+  // With several communication streams, kernels of different lanes may run
+  // at the same time and each waits for its peers: all of them must be able
+  // to be resident together (2 CTAs of 512 threads per SM on 148 SMs), or two
+  // GPUs could each fill up with the kernel the other one is not running.
+  const int cap = 296 / lanes_;
+  auto capped = [cap](int n) { return std::min(n, cap); };
   // Few CTAs for latency-bound sizes, more as the message grows: a CTA keeps
   // about 32 KB of peer loads in flight, and NVLink needs a few MB in flight
   // to run at full rate.
-  if (bytes <= 64 * 1024) return 4;
-  if (bytes <= 512 << 10) return 16;
-  if (bytes <= 2 << 20) return 32;
-  if (bytes <= 8 << 20) return 64;
-  if (bytes <= 32 << 20) return 96;
-  if (bytes <= 128 << 20) return 148;
-  return 296;  // two CTAs per SM: where the local copy phases peak
+  if (bytes <= 64 * 1024) return capped(4);
+  if (bytes <= 512 << 10) return capped(16);
+  if (bytes <= 2 << 20) return capped(32);
+  if (bytes <= 8 << 20) return capped(64);
+  if (bytes <= 32 << 20) return capped(96);
+  if (bytes <= 128 << 20) return capped(148);
+  return capped(296);  // two CTAs per SM: where the local copy phases peak
 }
 
 kern::Algo GpuOps::PickAlgo(const SymmSet& set, DataType wire,
@@ -655,6 +716,11 @@ void GpuOps::Shutdown() {
   shut_down_ = true;
   GpuOps* self = this;
   g_current.compare_exchange_strong(self, nullptr);
+  {
+    std::lock_guard<std::mutex> l(g_registry_mu_ref());
+    auto& reg = g_registry_ref();
+    reg.erase(std::remove(reg.begin(), reg.end(), this), reg.end());
+  }
   if (device_ >= 0) {
     cudaSetDevice(device_);
     if (stream_) cudaStreamSynchronize(stream_);

@@ -170,9 +170,14 @@ Status GpuOps::SymmAllreduce(std::vector<TensorTableEntry>& entries,
       }
       kern::SymmCtx ctx = MakeCtx(set, kern::ADASUM_EPOCHS);
       int64_t scratch_off = RoundUp(bytes, 4096);
+      // Room behind the scratch for a local copy of the partner's half, if
+      // the staging area has it.
+      const int64_t scratch_bytes = RoundUp(int64_t(n) * 3 * 8 * 4 + 4096, 4096);
+      int64_t copy_off = scratch_off + scratch_bytes;
+      if (copy_off + bytes / 2 + 4096 > static_cast<int64_t>(set.data_bytes)) copy_off = -1;
       err = kern::LaunchAdasum(list, dtype, response.prescale,
                                response.postscale, scratch_off, PickCtas(bytes),
-                               ctx, stream_);
+                               ctx, stream_, copy_off);
       ring_.Release(slot, stream_);
     } else {
       kern::Algo algo = PickAlgo(set, wire, bytes);

@@ -64,12 +64,10 @@ void BindGpuDiagnostics(py::module_& m) {
     // microseconds from the first timing event to the last launch) of every
     // device collective since the last call; needs HOROVOD_GPU_OP_TIMING=1.
     py::list out;
-    GpuOps* ops = CurrentGpuOps();
-    if (ops == nullptr) return out;
     std::vector<GpuOps::OpTiming> t;
     {
       py::gil_scoped_release release;
-      t = ops->DrainTimings();
+      t = DrainAllGpuTimings();
     }
     for (auto& x : t) out.append(py::make_tuple(x.type, x.bytes, x.tensors, x.device_us, x.host_us));
     return out;

@@ -576,3 +576,121 @@ def test_pipelined_fused_allreduce(algo):
     if _ngpu() < 2:
         pytest.skip("needs 2 GPUs")
     assert all(run_parallel(_allreduce_pipelined, np=_world(), args=(algo,), timeout=300))
+
+
+def _shrink_between_steps(rank, size):
+    """Ranks leave between steps: the job shuts down cleanly at a step
+    boundary (no kernel or collective in flight), the upper half of the ranks
+    exits, and the survivors initialise again with a smaller world. The
+    symmetric arena, its peer mappings and flag words are rebuilt for the new
+    membership and the kernels must give correct results at both sizes.
+    Multicast is off (plain peer loads and stores) so that no departing
+    process is bound to a multicast object."""
+    os.environ["HOROVOD_SYMM_NVLS"] = "0"
+    os.environ["HOROVOD_SPIN_TIMEOUT_MS"] = "5000"
+    import horovod_b200.torch as hvd
+    from horovod_b200.runner.http.http_server import RendezvousServer
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+
+    def work(tag, n_ranks):
+        ok = hvd.size() == n_ranks
+        for n in (1000, (1 << 20) + 3):
+            x = _inputs(rank, n, torch.float32).to(dev)
+            out = hvd.allreduce(x, op=hvd.Sum, name="%s.ar.%d" % (tag, n))
+            ref = sum(_inputs(r, n, torch.float32).double() for r in range(n_ranks))
+            ok = ok and (out.double().cpu() - ref).abs().max().item() < 1e-4
+        heap = hvd.symmetric_empty(70000)
+        heap.copy_(_inputs(rank + 50, 70000, torch.float32))
+        hvd.allreduce_(heap, op=hvd.Average, name="%s.inplace" % tag)
+        ref = sum(_inputs(r + 50, 70000, torch.float32).double() for r in range(n_ranks)) / n_ranks
+        ok = ok and (heap.double().cpu() - ref).abs().max().item() < 1e-5
+        g = hvd.allgather(torch.full((rank + 1, 2), float(rank), device=dev), name="%s.ag" % tag)
+        ok = ok and torch.equal(g.cpu(), torch.cat([torch.full((r + 1, 2), float(r))
+                                                     for r in range(n_ranks)]))
+        rs = hvd.reducescatter(torch.ones(4 * n_ranks, 3, device=dev) * (rank + 1),
+                               op=hvd.Sum, name="%s.rs" % tag)
+        ok = ok and torch.allclose(rs.cpu(), torch.full((4, 3), float(sum(range(1, n_ranks + 1)))))
+        torch.cuda.synchronize()
+        # the arena in use was built for exactly this membership
+        return ok and hvd.gpu_backend().startswith("symm ranks=%d " % n_ranks)
+
+    hvd.init()
+    ok = work("first", size)
+    # The survivors meet again through a second rendezvous server that rank 0
+    # starts now; its port travels over the first session.
+    survivors = max(1, size // 2)
+    server = None
+    port = 0
+    if rank == 0:
+        server = RendezvousServer()
+        port = server.start()
+        server.init([None] * survivors)
+    port = hvd.broadcast_object(port, root_rank=0, name="shrink.port")
+    hvd.shutdown()  # a step boundary: nothing in flight on any rank
+    if rank >= survivors:
+        return ok
+    os.environ.update({"HOROVOD_SIZE": str(survivors), "HOROVOD_LOCAL_SIZE": str(survivors),
+                       "HOROVOD_GLOO_RENDEZVOUS_PORT": str(port)})
+    hvd.init()
+    ok = ok and work("second", survivors)
+    hvd.shutdown()
+    if server is not None:
+        server.stop()
+    return ok
+
+
+def test_ranks_leave_between_steps_and_the_arena_is_rebuilt():
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    n = 4 if _ngpu() >= 4 else 2
+    assert all(run_parallel(_shrink_between_steps, np=n, timeout=300))
+
+
+def _two_streams(rank, size, backend):
+    """HOROVOD_NUM_NCCL_STREAMS=2: responses alternate between two
+    communication streams (each with its own arena, flag words and, on the
+    NCCL path, communicator); many collectives in flight at once must still
+    give the right answers, and symmetric-heap tensors keep working."""
+    os.environ["HOROVOD_NUM_NCCL_STREAMS"] = "2"
+    os.environ["HOROVOD_GPU_BACKEND"] = backend
+    os.environ["HOROVOD_SPIN_TIMEOUT_MS"] = "5000"
+    os.environ["HOROVOD_FUSION_THRESHOLD"] = str(1 << 20)  # many separate responses
+    import horovod_b200.torch as hvd
+    hvd.init()
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    ok = True
+    for it in range(3):
+        sizes = [1000, (1 << 20) + 3, 50000, 3 << 20, 17, 700001]
+        xs = [_inputs(rank + i + 10 * it, n, torch.float32).to(dev) for i, n in enumerate(sizes)]
+        hs = [hvd.allreduce_async(x, op=hvd.Sum, name="ts.ar.%d" % i) for i, x in enumerate(xs)]
+        g = hvd.allgather_async(torch.full((rank + 1, 3), float(rank), device=dev), name="ts.ag")
+        b = torch.arange(5000, device=dev, dtype=torch.float32) * (rank + 1)
+        bh = hvd.broadcast_async_(b, root_rank=size - 1, name="ts.bc")
+        for i, (h, n) in enumerate(zip(hs, sizes)):
+            out = hvd.synchronize(h)
+            ref = sum(_inputs(r + i + 10 * it, n, torch.float32).double() for r in range(size))
+            ok = ok and (out.double().cpu() - ref).abs().max().item() < 1e-4
+        got = hvd.synchronize(g)
+        ok = ok and torch.equal(got.cpu(), torch.cat([torch.full((r + 1, 3), float(r))
+                                                       for r in range(size)]))
+        hvd.synchronize(bh)
+        ok = ok and torch.equal(b.cpu(), torch.arange(5000, dtype=torch.float32) * size)
+    if backend == "symm":
+        heap = hvd.symmetric_empty(100000)
+        for it in range(4):  # whichever lane is next, heap tensors go to the first
+            heap.copy_(_inputs(rank + it, 100000, torch.float32))
+            hvd.allreduce_(heap, op=hvd.Average, name="ts.heap")
+            ref = sum(_inputs(r + it, 100000, torch.float32).double() for r in range(size)) / size
+            ok = ok and (heap.double().cpu() - ref).abs().max().item() < 1e-5
+    torch.cuda.synchronize()
+    hvd.shutdown()
+    return ok
+
+
+@pytest.mark.parametrize("backend", ["symm", "nccl"])
+def test_two_communication_streams(backend):
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    assert all(run_parallel(_two_streams, np=_world(), args=(backend,), timeout=300))

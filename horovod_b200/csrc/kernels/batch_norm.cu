@@ -32,6 +32,11 @@ namespace kern {
 namespace {
 
 constexpr int BN_THREADS = 256;
+// Resident CTAs per SM the compiler must leave room for (register budget):
+// these are streaming kernels whose throughput is set by the bytes in flight
+// per SM, i.e. by occupancy.
+constexpr int BN_MIN_BLOCKS_APPLY = 3;   // <= 85 registers per thread
+constexpr int BN_MIN_BLOCKS_REDUCE = 4;  // <= 64 registers per thread
 constexpr int VEC = 8;  // 16-bit elements per 16-byte access
 
 template <typename T> __device__ __forceinline__ float bn_to_float(T v);
@@ -107,7 +112,7 @@ __device__ __forceinline__ void reduce_to_global(const Tile& t, float (&acc)[NV]
 }
 
 template <typename T>
-__global__ void __launch_bounds__(BN_THREADS)
+__global__ void __launch_bounds__(BN_THREADS, BN_MIN_BLOCKS_REDUCE)
 bn_stats_kernel(const T* __restrict__ x, int64_t M, int C, double* __restrict__ sum,
                 double* __restrict__ sumsq) {
   const Tile t(C);
@@ -167,7 +172,7 @@ __device__ __forceinline__ void channel_affine(const double* sum, const double* 
 }
 
 template <typename T, bool RELU, bool RES>
-__global__ void __launch_bounds__(BN_THREADS)
+__global__ void __launch_bounds__(BN_THREADS, BN_MIN_BLOCKS_APPLY)
 bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ res, T* __restrict__ y,
                 int64_t M, int C, const double* __restrict__ sum,
                 const double* __restrict__ sumsq, const float* __restrict__ weight,
@@ -230,7 +235,7 @@ bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ res, T* __restric
 
 // sum(dz) and sum(dz * xhat) per channel.
 template <typename T, bool RELU>
-__global__ void __launch_bounds__(BN_THREADS)
+__global__ void __launch_bounds__(BN_THREADS, BN_MIN_BLOCKS_REDUCE)
 bn_backward_reduce_kernel(const T* __restrict__ dy, const T* __restrict__ y,
                           const T* __restrict__ x, int64_t M, int C,
                           const float* __restrict__ save_mean,
@@ -284,7 +289,7 @@ bn_backward_reduce_kernel(const T* __restrict__ dy, const T* __restrict__ y,
 }
 
 template <typename T, bool RELU, bool RES>
-__global__ void __launch_bounds__(BN_THREADS)
+__global__ void __launch_bounds__(BN_THREADS, BN_MIN_BLOCKS_APPLY)
 bn_backward_apply_kernel(const T* __restrict__ dy, const T* __restrict__ y,
                          const T* __restrict__ x, T* __restrict__ dx, T* __restrict__ dres,
                          int64_t M, int C, const float* __restrict__ weight,

@@ -126,7 +126,10 @@ def build_workload(args, torch, device):
         else:
             opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9, weight_decay=1e-4)
         g = torch.Generator().manual_seed(1)
-        host_x = [torch.randn(batch, 3, 224, 224, generator=g).pin_memory() for _ in range(2)]
+        # fp32 images in channels-last layout in pinned memory: the copy to the
+        # device lands in the layout the model runs in, no conversion pass.
+        host_x = [torch.randn(batch, 3, 224, 224, generator=g)
+                  .contiguous(memory_format=torch.channels_last).pin_memory() for _ in range(2)]
         host_y = [torch.randint(0, 1000, (batch,), generator=g).pin_memory() for _ in range(2)]
 
         def to_dev(x):

@@ -21,6 +21,15 @@ Cases
                 CUDA events on the current stream, next to the PyTorch eager
                 composition batch_norm -> add -> relu on the same tensors.
 
+  max_pool      3x3 / stride 2 / padding 1 max pooling on the ResNet stem
+                activation 256 x 64 x 112 x 112 bf16 (411 MB): forward reads x,
+                writes y (1/4 of x) and one index byte per output element
+                (1/8 of x): 1.375x; backward reads dy and the indices and
+                writes dx: 1.375x. Next to PyTorch's max_pool2d.
+  fused_sgd     hvd.FusedSGD step (momentum + weight decay) over 161
+                ResNet-50-shaped fp32 tensors: reads p, g, m, writes p, m
+                (5x bytes). Next to torch.optim.SGD on the same tensors.
+
 Timing is device time of the response on the communication stream (CUDA
 events around the launches). Inputs are larger than L2 (126 MB) unless --mb
 says otherwise. Prints one JSON line per case.
@@ -101,8 +110,31 @@ def main():
                           "hbm_gbs_peak": hbm,
                           "clocks": clock_log.window(t_begin, t_end)}), flush=True)
 
-    cases = ["fused_local", "fused_fp16", "reducescatter", "exchange", "batch_norm"] \
-        if args.case == "all" else [args.case]
+    cases = ["fused_local", "fused_fp16", "reducescatter", "exchange", "batch_norm", "max_pool",
+             "fused_sgd"] if args.case == "all" else [args.case]
+
+    def timed_events(fn, reps):
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        return statistics.median(ts)
+
+    def report_line(name, us, algorithmic, extra=None):
+        gbs = algorithmic / (us * 1e-6) / 1e9
+        print(json.dumps({"case": name, "device_us": round(us, 1),
+                          "algorithmic_gbs": round(gbs, 1),
+                          "frac_of_%s_hbm_copy" % peak_src: round(gbs / hbm, 3),
+                          "hbm_gbs_peak": hbm,
+                          "clocks": clock_log.window(time.time() - 1.0, time.time()),
+                          **(extra or {})}), flush=True)
     if "fused_local" in cases:
         xs = [torch.randn(n, device=dev) for n in resnet50_like_sizes(nbytes // 4)]
         total = sum(x.numel() * 4 for x in xs)
@@ -174,6 +206,34 @@ def main():
             report(name + "_forward", t_f, 4 * nbytes_act)
             report(name + "_backward", t_b, 8 * nbytes_act)
             del y
+    if "max_pool" in cases:
+        import torch.nn.functional as F
+        from horovod_b200.ops.pooling import max_pool_3x3_s2
+        n = 256 if args.mb >= 512 else 32
+        x = torch.relu(torch.randn(n, 64, 112, 112, device=dev)).bfloat16() \
+            .contiguous(memory_format=torch.channels_last).requires_grad_(True)
+        xbytes = x.numel() * 2
+        for name, fwd in (("max_pool_fused", max_pool_3x3_s2),
+                          ("max_pool_torch", lambda t: F.max_pool2d(t, 3, stride=2, padding=1))):
+            t_f = timed_events(lambda: fwd(x), args.iters)
+            y = fwd(x)
+            go = torch.randn_like(y)
+            t_b = timed_events(lambda: torch.autograd.grad(y, x, go, retain_graph=True), args.iters)
+            report_line(name + "_forward", t_f, 1.375 * xbytes, {"shape": list(x.shape)})
+            report_line(name + "_backward", t_b, 1.375 * xbytes, {"shape": list(x.shape)})
+            del y
+    if "fused_sgd" in cases:
+        from horovod_b200.torch.fused_sgd import FusedSGD
+        sizes = resnet50_like_sizes(min(nbytes, 256 << 20) // 4)
+        total = sum(sizes) * 4
+        for name, cls in (("fused_sgd", FusedSGD), ("torch_sgd", torch.optim.SGD)):
+            ps = [torch.randn(n, device=dev, requires_grad=True) for n in sizes]
+            for p in ps:
+                p.grad = torch.randn_like(p)
+            opt = cls(ps, lr=0.01, momentum=0.9, weight_decay=1e-4)
+            opt.step()  # creates the momentum buffers
+            us = timed_events(opt.step, args.iters)
+            report_line(name, us, 5 * total, {"tensors": len(sizes), "payload_mb": total >> 20})
     clock_log.stop()
     hvd.shutdown()
     return 0

@@ -252,6 +252,13 @@ exchange_kernel(const InlineExchange inl, const ExchangePlan plan_dev, const Exc
   trace_mark(ctx, 3);
 }
 
+__global__ void credit_post_kernel(SymmCtx ctx, uint32_t value) {
+  // The copies that read the peers' regions were queued on this stream before
+  // this launch, so they have completed; one release store per peer.
+  if (threadIdx.x < ctx.world)
+    st_release_sys(ctx.flags_peers[threadIdx.x] + CREDIT_BANK + ctx.rank * SYMM_MAX_BLOCKS, value);
+}
+
 __global__ void barrier_only_kernel(SymmCtx ctx) {
   cta_barrier(ctx, ctx.epoch + 1, blockIdx.x, 1);
 }
@@ -270,6 +277,12 @@ cudaError_t LaunchExchange(const ExchangePlan& plan, const ExchangeSync& sync, i
     exchange_kernel<true><<<num_ctas, THREADS, 0, stream>>>(*inline_plan, plan, sync, ctx);
   else
     exchange_kernel<false><<<num_ctas, THREADS, 0, stream>>>(kNoInline, plan, sync, ctx);
+  return cudaGetLastError();
+}
+
+cudaError_t LaunchCreditPost(uint32_t value, const SymmCtx& ctx, cudaStream_t stream) {
+  CountKernelLaunches(1);
+  credit_post_kernel<<<1, 32, 0, stream>>>(ctx, value);
   return cudaGetLastError();
 }
 

@@ -357,6 +357,12 @@ uint64_t KernelLaunchCount();
 void CountKernelLaunches(int n);
 
 // Test hook: a kernel that runs one cross-GPU barrier and nothing else.
+// Tells every peer that this rank no longer reads the exchange region of
+// launch number `value` (the word the exchange kernel's credit wait polls).
+// For rounds whose transfers are copy-engine copies queued on the stream
+// before this launch.
+cudaError_t LaunchCreditPost(uint32_t value, const SymmCtx& ctx, cudaStream_t stream);
+
 cudaError_t LaunchBarrierOnly(int num_ctas, int bank, const SymmCtx& ctx,
                               cudaStream_t stream);
 

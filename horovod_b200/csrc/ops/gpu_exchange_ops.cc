@@ -22,7 +22,43 @@ constexpr int64_t STAGING_ALIGN = 256;
 void GpuOps::LaunchExchangeSegments(const std::vector<StageSeg>& stage,
                                     const std::vector<PullSeg>& pull, SymmSet& set,
                                     int64_t round_bytes,
-                                    const std::vector<RoundBlock>& round) {
+                                    const std::vector<RoundBlock>& round,
+                                    bool copy_engine) {
+  if (copy_engine && set.xchg_bytes > 0) {
+    // Large blocks: the kernel only stages this rank's blocks in its own
+    // region (and copies what it keeps) and ends with the barrier over all
+    // ranks; the copy engines then read the peers' regions into the final
+    // tensors at full NVLink rate while the SMs are free, and a one-warp
+    // launch returns the region credit once those copies are done.
+    static const std::vector<PullSeg> kNoPulls;
+    const uint32_t s = set.xchg_seq + 1;  // the number the staging launch takes
+    LaunchExchangeKernel(stage, kNoPulls, set, round_bytes, round, /*post_credit=*/false);
+    const int64_t region_off = set.xchg_off[s & 1];
+    for (const PullSeg& p : pull) {
+      if (p.dst == nullptr || p.bytes == 0) continue;
+      cudaError_t e = cudaMemcpyAsync(p.dst, set.peers[p.src_rank] + region_off + p.off,
+                                      static_cast<size_t>(p.bytes), cudaMemcpyDeviceToDevice,
+                                      stream_);
+      if (e != cudaSuccess)
+        throw std::runtime_error(std::string("exchange peer copy failed: ") +
+                                 cudaGetErrorString(e));
+    }
+    kern::SymmCtx ctx = MakeCtx(set, 0, region_off);
+    cudaError_t e = kern::LaunchCreditPost(s, ctx, stream_);
+    if (e != cudaSuccess)
+      throw std::runtime_error(std::string("exchange credit launch failed: ") +
+                               cudaGetErrorString(e));
+    return;
+  }
+  LaunchExchangeKernel(stage, pull, set, round_bytes, round, /*post_credit=*/true);
+}
+
+// post_credit: the kernel's last CTA returns the region credit; otherwise the
+// kernel ends with a barrier over all ranks and the caller returns the credit.
+void GpuOps::LaunchExchangeKernel(const std::vector<StageSeg>& stage,
+                                  const std::vector<PullSeg>& pull, SymmSet& set,
+                                  int64_t round_bytes, const std::vector<RoundBlock>& round,
+                                  bool post_credit) {
   const size_t ns = stage.size(), np = pull.size();
   // The grid size must be the same on every rank (CTA b meets CTA b of its
   // peers), so it is derived from the bytes of the whole round, which all
@@ -53,10 +89,12 @@ void GpuOps::LaunchExchangeSegments(const std::vector<StageSeg>& stage,
     const uint32_t s = ++set.xchg_seq;
     region_off = set.xchg_off[s & 1];
     sync.credit_wait = s > 2 ? s - 2 : 0;
-    sync.credit_post = s;
-    sync.done_counter = xchg_done_counter_;
-    xchg_done_base_ += static_cast<unsigned long long>(ctas);
-    sync.done_target = xchg_done_base_;
+    if (post_credit) {
+      sync.credit_post = s;
+      sync.done_counter = xchg_done_counter_;
+      xchg_done_base_ += static_cast<unsigned long long>(ctas);
+      sync.done_target = xchg_done_base_;
+    }
   }
 
   kern::ExchangePlan plan;
@@ -155,6 +193,15 @@ bool GpuOps::ExchangePushes(const SymmSet& set, int64_t total_bytes) const {
   return set.world >= 3 && exchange_push_max_ != 0;
 }
 
+bool GpuOps::ExchangeUsesCopyEngine(const SymmSet& set, int64_t total_bytes, int64_t smallest,
+                                    size_t remote_blocks) const {
+  // SM-driven NVLink traffic measured 430-530 GB/s per direction on B200 (this
+  // kernel and NCCL alike); copy-engine peer copies reach 770 GB/s. Worth the
+  // extra local staging pass and barrier for large blocks only.
+  return set.world > 1 && set.xchg_bytes > 0 && exchange_ce_min_ > 0 &&
+         total_bytes >= exchange_ce_min_ && smallest >= (256 << 10) && remote_blocks <= 256;
+}
+
 // Every rank builds the same global list of "blocks" (source rank, bytes,
 // who receives it). A block that somebody else needs is staged in its source
 // rank's exchange region; blocks are laid out there in order and processed in
@@ -184,10 +231,20 @@ static void RunBlocks(std::vector<Block>& blocks, SymmSet& set, bool push,
   // not fit the region, every block is cut into the same number of slices and
   // the rounds go slice by slice: round k moves slice k of every block, so
   // every rank is busy in every round and all NVLink links stay in use.
+  // Pulling fills the source's region; pushing fills the receiver's region
+  // (every region, for a block that goes to everybody).
   std::vector<int64_t> staged(set.world, 0);
   for (auto& b : blocks) {
     const bool remote = set.world > 1 && (b.dst_rank < 0 || b.dst_rank != b.src_rank);
-    if (remote) staged[push ? 0 : b.src_rank] += RoundUp(b.bytes, STAGING_ALIGN) + STAGING_ALIGN;
+    if (!remote) continue;
+    const int64_t need = RoundUp(b.bytes, STAGING_ALIGN) + STAGING_ALIGN;
+    if (!push) {
+      staged[b.src_rank] += need;
+    } else if (b.dst_rank >= 0) {
+      staged[b.dst_rank] += need;
+    } else {
+      for (auto& s : staged) s += need;
+    }
   }
   const int64_t most = *std::max_element(staged.begin(), staged.end());
   const int64_t slices = std::max<int64_t>(1, (most + cap - 1) / cap);
@@ -209,8 +266,9 @@ static void RunBlocks(std::vector<Block>& blocks, SymmSet& set, bool push,
   while (next < parts.size()) {
     std::vector<GpuOps::StageSeg> stage;
     std::vector<GpuOps::PullSeg> pull;
-    // Pulling: offsets are per source region. Pushing: several sources write
-    // into one receiver's region, so one cursor lays out the whole round.
+    // One cursor per region. Pulling: a block sits in its source's region.
+    // Pushing: in its receiver's region, or, when it goes to everybody, at
+    // one offset that is free in every region.
     std::vector<int64_t> cursor(set.world, 0);
     size_t n = 0;
     int64_t round_bytes = 0;
@@ -224,10 +282,16 @@ static void RunBlocks(std::vector<Block>& blocks, SymmSet& set, bool push,
         if (b.src_rank == me && wanted) stage.push_back({b.src, b.dst, -1, b.bytes, -2});
       } else {
         const int64_t padded = RoundUp(b.bytes, STAGING_ALIGN);
-        int64_t& cur = cursor[push ? 0 : b.src_rank];
-        const int64_t off = cur;
+        const bool everywhere = push && b.dst_rank < 0;
+        const int region = push ? b.dst_rank : b.src_rank;
+        const int64_t off = everywhere ? *std::max_element(cursor.begin(), cursor.end())
+                                       : cursor[region];
         if (off + padded > cap) break;
-        cur = off + padded;
+        if (everywhere) {
+          std::fill(cursor.begin(), cursor.end(), off + padded);
+        } else {
+          cursor[region] = off + padded;
+        }
         if (b.src_rank == me) {
           stage.push_back({b.src, wanted ? b.dst : nullptr, off, b.bytes,
                            push ? b.dst_rank : -2});
@@ -245,6 +309,22 @@ static void RunBlocks(std::vector<Block>& blocks, SymmSet& set, bool push,
     next += n;
   }
 }
+
+namespace {
+// Totals over the blocks that cross NVLink (the same on every rank).
+struct RemoteStats { int64_t total = 0, smallest = 0; size_t count = 0; };
+RemoteStats RemoteBlockStats(const std::vector<Block>& blocks, int world) {
+  RemoteStats st;
+  for (auto& b : blocks) {
+    st.total += b.bytes;
+    const bool remote = world > 1 && (b.dst_rank < 0 || b.dst_rank != b.src_rank);
+    if (!remote || b.bytes == 0) continue;
+    st.smallest = st.count == 0 ? b.bytes : std::min(st.smallest, b.bytes);
+    ++st.count;
+  }
+  return st;
+}
+}  // namespace
 
 Status GpuOps::SymmBroadcast(std::vector<TensorTableEntry>& entries,
                              SymmSet& set) {
@@ -268,14 +348,16 @@ Status GpuOps::SymmBroadcast(std::vector<TensorTableEntry>& entries,
   // receivers copy out of their own region; with two ranks the peer pulls
   // large messages. (Only with the credit-guarded regions: nobody else ever
   // writes those.)
-  int64_t total = 0;
-  for (auto& b : blocks) total += b.bytes;
-  const bool push = ExchangePushes(set, total) ||
+  const RemoteStats rs = RemoteBlockStats(blocks, set.world);
+  const bool push = ExchangePushes(set, rs.total) ||
                     (set.mc != nullptr && set.world >= 3 && set.xchg_bytes > 0);
+  // (A pulled broadcast would cost the root N-1 times the message on its
+  // NVLink egress, so the copy engines only serve the two-rank case.)
+  const bool ce = !push && ExchangeUsesCopyEngine(set, rs.total, rs.smallest, rs.count);
   RunBlocks(blocks, set, push,
             [&](const std::vector<StageSeg>& o, const std::vector<PullSeg>& i,
                 int64_t round_bytes, const std::vector<RoundBlock>& round) {
-              LaunchExchangeSegments(o, i, set, round_bytes, round);
+              LaunchExchangeSegments(o, i, set, round_bytes, round, ce);
             });
   ActEnd(entries);
   return Complete(entries);
@@ -314,12 +396,12 @@ Status GpuOps::SymmAllgather(std::vector<TensorTableEntry>& entries,
     }
   }
   ActStart(entries, HVD_ACT_FUSED_KERNEL);
-  int64_t total = 0;
-  for (auto& b : blocks) total += b.bytes;
-  RunBlocks(blocks, set, ExchangePushes(set, total),
+  const RemoteStats rs = RemoteBlockStats(blocks, set.world);
+  const bool ce = ExchangeUsesCopyEngine(set, rs.total, rs.smallest, rs.count);
+  RunBlocks(blocks, set, !ce && ExchangePushes(set, rs.total),
             [&](const std::vector<StageSeg>& o, const std::vector<PullSeg>& i,
                 int64_t round_bytes, const std::vector<RoundBlock>& round) {
-              LaunchExchangeSegments(o, i, set, round_bytes, round);
+              LaunchExchangeSegments(o, i, set, round_bytes, round, ce);
             });
   ActEnd(entries);
   return Complete(entries);
@@ -374,12 +456,12 @@ Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries,
     }
   }
   ActStart(entries, HVD_ACT_FUSED_KERNEL);
-  int64_t total = 0;
-  for (auto& b : blocks) total += b.bytes;
-  RunBlocks(blocks, set, ExchangePushes(set, total),
+  const RemoteStats rs = RemoteBlockStats(blocks, set.world);
+  const bool ce = ExchangeUsesCopyEngine(set, rs.total, rs.smallest, rs.count);
+  RunBlocks(blocks, set, !ce && ExchangePushes(set, rs.total),
             [&](const std::vector<StageSeg>& o, const std::vector<PullSeg>& i,
                 int64_t round_bytes, const std::vector<RoundBlock>& round) {
-              LaunchExchangeSegments(o, i, set, round_bytes, round);
+              LaunchExchangeSegments(o, i, set, round_bytes, round, ce);
             });
   ActEnd(entries);
   return Complete(entries);

@@ -211,10 +211,20 @@ private:
   // One exchange-kernel launch for the given segment lists.
   void LaunchExchangeSegments(const std::vector<StageSeg>& stage,
                               const std::vector<PullSeg>& pull, SymmSet& set,
-                              int64_t round_bytes, const std::vector<RoundBlock>& round);
+                              int64_t round_bytes, const std::vector<RoundBlock>& round,
+                              bool copy_engine = false);
+  void LaunchExchangeKernel(const std::vector<StageSeg>& stage,
+                            const std::vector<PullSeg>& pull, SymmSet& set,
+                            int64_t round_bytes, const std::vector<RoundBlock>& round,
+                            bool post_credit);
   // Whether an exchange of `total_bytes` writes straight into the receivers'
   // regions (small messages) instead of staging locally.
   bool ExchangePushes(const SymmSet& set, int64_t total_bytes) const;
+  // Whether an exchange of `total_bytes` in remote blocks of at least
+  // `smallest` bytes each moves its data across NVLink with copy-engine
+  // copies (stage locally, barrier, one peer copy per block).
+  bool ExchangeUsesCopyEngine(const SymmSet& set, int64_t total_bytes, int64_t smallest,
+                              size_t remote_blocks) const;
 
   GlobalState& state_;
   int slot_ = 0;
@@ -245,6 +255,7 @@ private:
   int64_t dynamic_min_bytes_ = 0;
   int64_t exchange_chunk_bytes_ = 256 << 10;  // HOROVOD_EXCHANGE_CHUNK_KB
   int64_t exchange_push_max_ = 1 << 20;       // HOROVOD_EXCHANGE_PUSH_MAX_BYTES
+  int64_t exchange_ce_min_ = 32 << 20;        // HOROVOD_EXCHANGE_COPY_ENGINE_MIN_BYTES (0 = never)
   int64_t allreduce_subchunk_bytes_ = 64 << 10;  // HOROVOD_ALLREDUCE_SUBCHUNK_KB, 0 = off
   int64_t allreduce_pipeline_min_ = 8 << 20;     // HOROVOD_ALLREDUCE_PIPELINE_MIN_BYTES
   unsigned long long* xchg_done_counter_ = nullptr;  // device word, see kern::ExchangeSync

@@ -419,6 +419,18 @@ void Comm::Allgatherv(const void* send, const std::vector<int64_t>& lens,
   if (lens[rank_] > 0 && out + offs[rank_] != send)
     std::memcpy(out + offs[rank_], send, static_cast<size_t>(lens[rank_]));
   if (n <= 1) return;
+  int64_t largest = 0;
+  for (auto l : lens) largest = std::max(largest, l);
+  if (largest <= 4096) {
+    // Small blocks (split tables, handles): every rank hands its block to
+    // every peer directly, so no block waits for a neighbour to forward it.
+    for (int s = 1; s < n; ++s) {
+      const int to = (rank_ + s) % n, from = (rank_ - s + n) % n;
+      mesh_->SendRecv(g(to), out + offs[rank_], static_cast<size_t>(lens[rank_]),
+                      g(from), out + offs[from], static_cast<size_t>(lens[from]));
+    }
+    return;
+  }
   int right = (rank_ + 1) % n, left = (rank_ - 1 + n) % n;
   for (int s = 0; s < n - 1; ++s) {
     int sb = (rank_ - s + n) % n;      // block forwarded this step

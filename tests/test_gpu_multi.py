@@ -343,11 +343,14 @@ def test_asymmetric_use_of_symmetric_memory_is_reported():
     assert out[1][0], out
 
 
-def _exchange_large(rank, size):
+def _exchange_large(rank, size, copy_engine_min):
     """Large and mixed exchange rounds with small chunks, so every launch
     publishes many chunk counters, and enough launches in a row that both
-    exchange regions are reused several times (credit waits)."""
+    exchange regions are reused several times (credit waits).
+    copy_engine_min: from how many bytes the rounds move their blocks with
+    copy-engine peer copies ("0": never, so the kernel pulls or pushes)."""
     os.environ["HOROVOD_EXCHANGE_CHUNK_KB"] = "64"
+    os.environ["HOROVOD_EXCHANGE_COPY_ENGINE_MIN_BYTES"] = copy_engine_min
     os.environ["HOROVOD_SPIN_TIMEOUT_MS"] = "5000"
     import horovod_b200.torch as hvd
     hvd.init()
@@ -407,10 +410,11 @@ def _exchange_large(rank, size):
     return ok
 
 
-def test_large_and_mixed_exchange_rounds():
+@pytest.mark.parametrize("copy_engine_min", ["0", str(1 << 20)])
+def test_large_and_mixed_exchange_rounds(copy_engine_min):
     if _ngpu() < 2:
         pytest.skip("needs 2 GPUs")
-    assert all(run_parallel(_exchange_large, np=_world(), timeout=300))
+    assert all(run_parallel(_exchange_large, np=_world(), args=(copy_engine_min,), timeout=300))
 
 
 def _reducescatter_push(rank, size):

@@ -494,7 +494,7 @@ Response Controller::ConstructResponse(const std::string& name,
 int64_t Controller::ResponseBytes(const Response& r) const {
   int64_t es = static_cast<int64_t>(DataTypeSize(r.dtype));
   int64_t total = 0;
-  if (IsReduction(r.type)) {
+  if (IsReduction(r.type) || r.type == Response::REDUCESCATTER) {
     int64_t ws = r.type == Response::ALLREDUCE
                      ? static_cast<int64_t>(DataTypeSize(r.wire_dtype)) : es;
     for (auto n : r.tensor_sizes) total += RoundUp(n * ws, FUSION_ALIGN_BYTES);
@@ -530,7 +530,10 @@ void FuseResponseQueue(std::deque<Response>& responses, int64_t threshold,
   while (!responses.empty()) {
     Response r = std::move(responses.front());
     responses.pop_front();
-    const bool reduction = IsReduction(r.type);
+    // Reduce-scatters fuse like allreduces (same dtype, scaling and op): the
+    // ops take a fused response as a list of tensors to shard one by one, or,
+    // on a device, in one launch.
+    const bool reduction = IsReduction(r.type) || r.type == Response::REDUCESCATTER;
     const bool fusable = reduction || r.type == Response::ALLGATHER ||
                          r.type == Response::BROADCAST;
     if (fusable) {

@@ -647,6 +647,69 @@ Status EnqueueTensorReducescatter(TensorTableEntry entry, ReduceOp op,
   return ps->tensor_queue.AddToTensorQueue(std::move(entry), std::move(q));
 }
 
+namespace {
+// Enqueues several entries of one kind as a group: the controller keeps the
+// members together, so they are negotiated in one cycle and fused into one
+// response (horovod/common/operations.cc EnqueueTensorAllreduces registers
+// its groups the same way).
+Status EnqueueGroup(ProcessSet* ps, std::vector<TensorTableEntry>& entries,
+                    Request::Type type, NvtxOp nvtx) {
+  int32_t group_id = NULL_GROUP_ID;
+  if (entries.size() > 1) {
+    std::vector<std::string> names;
+    for (auto& e : entries) names.push_back(e.name);
+    group_id = ps->group_table.RegisterGroup(std::move(names));
+  }
+  std::vector<Request> requests;
+  const int64_t now = NowMicros();
+  for (auto& e : entries) {
+    e.group_id = group_id;
+    e.enqueue_us = now;
+    AttachNvtxRange(e, nvtx);
+    requests.push_back(MakeRequest(e, type, ps->comm.rank()));
+  }
+  Status st = ps->tensor_queue.AddToTensorQueueMulti(entries, requests);
+  if (!st.ok() && group_id != NULL_GROUP_ID) {
+    std::vector<std::string> names;
+    for (auto& q : requests) names.push_back(q.name);
+    ps->group_table.DeregisterGroups(names);
+  }
+  return st;
+}
+}  // namespace
+
+Status EnqueueTensorAllgathers(std::vector<TensorTableEntry>& entries,
+                               int32_t process_set_id) {
+  ProcessSet* ps = nullptr;
+  Status st = FindSet(process_set_id, &ps);
+  if (!st.ok()) return st;
+  if (entries.empty()) return Status::OK();
+  for (auto& e : entries) e.process_set_id = process_set_id;
+  return EnqueueGroup(ps, entries, Request::ALLGATHER, NvtxOp::ALLGATHER);
+}
+
+Status EnqueueTensorReducescatters(std::vector<TensorTableEntry>& entries, ReduceOp op,
+                                   double prescale, double postscale,
+                                   int32_t process_set_id) {
+  ProcessSet* ps = nullptr;
+  Status st = FindSet(process_set_id, &ps);
+  if (!st.ok()) return st;
+  if (entries.empty()) return Status::OK();
+  if (op == ReduceOp::ADASUM)
+    return Status::InvalidArgument("reducescatter does not support Adasum.");
+  if (op == ReduceOp::AVERAGE) {
+    op = ReduceOp::SUM;
+    postscale /= ps->comm.size();
+  }
+  for (auto& e : entries) {
+    e.reduce_op = op;
+    e.prescale = prescale;
+    e.postscale = postscale;
+    e.process_set_id = process_set_id;
+  }
+  return EnqueueGroup(ps, entries, Request::REDUCESCATTER, NvtxOp::REDUCESCATTER);
+}
+
 Status EnqueueJoin(TensorTableEntry entry, int32_t process_set_id) {
   ProcessSet* ps = nullptr;
   Status st = FindSet(process_set_id, &ps);

@@ -60,6 +60,13 @@ Status EnqueueTensorAllreduces(std::vector<TensorTableEntry>& entries,
                                ReduceOp op, double prescale, double postscale,
                                int32_t process_set_id);
 Status EnqueueTensorAllgather(TensorTableEntry entry, int32_t process_set_id);
+// Several tensors as one group: negotiated together and fused into one
+// response per dtype (subject to the fusion threshold).
+Status EnqueueTensorAllgathers(std::vector<TensorTableEntry>& entries,
+                               int32_t process_set_id);
+Status EnqueueTensorReducescatters(std::vector<TensorTableEntry>& entries, ReduceOp op,
+                                   double prescale, double postscale,
+                                   int32_t process_set_id);
 Status EnqueueTensorBroadcast(TensorTableEntry entry, int root_rank,
                               int32_t process_set_id);
 Status EnqueueTensorAlltoall(TensorTableEntry entry, int32_t process_set_id);

@@ -186,6 +186,33 @@ cudaError_t LaunchReducescatterPush(const void* in, void* out, const RsPushArgs&
                                     DataType dtype, double prescale, double postscale,
                                     int num_ctas, const SymmCtx& ctx, cudaStream_t stream);
 
+// The same for several tensors of one dtype in one launch (a fused
+// reducescatter response): the whole shard of every tensor must fit a sender
+// slot of the region (tensor t at byte slot_off, a multiple of 256). Rank p
+// owns rows [p * base_rows + min(p, extra_rows), ...) of row_elems elements.
+// The launch consumes total_chunks + 1 epochs, total_chunks being the sum over
+// the tensors of ceil(slice_vecs * 16 / chunk_bytes).
+struct RsGroupTensor {
+  const void* in;
+  void* out;           // this rank's shard
+  int64_t base_rows, extra_rows, row_elems;
+  int64_t slot_off;
+  int64_t slice_vecs;  // 16-byte vectors of the largest shard per CTA, multiple of 16
+};
+struct RsGroupArgs {
+  const RsGroupTensor* tensors;  // device-visible
+  int n_tensors;
+  uint32_t total_chunks;
+  int64_t slot_bytes;
+  int64_t chunk_bytes;
+  uint32_t credit_wait, credit_post;
+  unsigned long long* done_counter;
+  unsigned long long done_target;
+};
+cudaError_t LaunchReducescatterPushGroup(const RsGroupArgs& args, DataType dtype, double prescale,
+                                         double postscale, int num_ctas, const SymmCtx& ctx,
+                                         cudaStream_t stream);
+
 // Exchange kernel behind allgather, broadcast and alltoall. Every rank copies
 // the data it owes to others from its tensors into an exchange region and
 // publishes how far it has got; every receiver copies what it needs out of a

@@ -8,6 +8,7 @@
 #include "../common/logging.h"
 #include "../common/process_set.h"
 #include "gpu_internal.h"
+#include "host_trace.h"
 
 namespace hvd {
 
@@ -34,7 +35,15 @@ void GpuOps::LaunchExchangeSegments(const std::vector<StageSeg>& stage,
     const uint32_t s = set.xchg_seq + 1;  // the number the staging launch takes
     LaunchExchangeKernel(stage, kNoPulls, set, round_bytes, round, /*post_credit=*/false);
     const int64_t region_off = set.xchg_off[s & 1];
-    for (const PullSeg& p : pull) {
+    // Every rank starts with its right-hand neighbour and goes round, so at
+    // any time each source is read by one peer (all ranks reading rank 0
+    // first would share its NVLink egress).
+    std::vector<PullSeg> ordered(pull);
+    std::stable_sort(ordered.begin(), ordered.end(), [&](const PullSeg& a, const PullSeg& b) {
+      return (a.src_rank - set.rank + set.world) % set.world <
+             (b.src_rank - set.rank + set.world) % set.world;
+    });
+    for (const PullSeg& p : ordered) {
       if (p.dst == nullptr || p.bytes == 0) continue;
       cudaError_t e = cudaMemcpyAsync(p.dst, set.peers[p.src_rank] + region_off + p.off,
                                       static_cast<size_t>(p.bytes), cudaMemcpyDeviceToDevice,
@@ -122,7 +131,9 @@ void GpuOps::LaunchExchangeKernel(const std::vector<StageSeg>& stage,
       inl.pl_wait[i] = static_cast<int32_t>(before[pull[i].block]);
     }
     kern::SymmCtx ctx = MakeCtx(set, sync.done_epochs, region_off);
+    host_trace::Mark("plan");
     err = kern::LaunchExchange(plan, sync, ctas, ctx, stream_, &inl);
+    host_trace::Mark("launch");
   } else {
     DescriptorRing::Slot slot = ring_.Acquire();
     const void** d_src;
@@ -173,7 +184,9 @@ void GpuOps::LaunchExchangeKernel(const std::vector<StageSeg>& stage,
     plan.pl_sig = d_psig;
     plan.pl_wait = d_pwait;
     kern::SymmCtx ctx = MakeCtx(set, sync.done_epochs, region_off);
+    host_trace::Mark("plan (ring)");
     err = kern::LaunchExchange(plan, sync, ctas, ctx, stream_);
+    host_trace::Mark("launch");
     ring_.Release(slot, stream_);
   }
   if (err != cudaSuccess)
@@ -330,6 +343,7 @@ Status GpuOps::SymmBroadcast(std::vector<TensorTableEntry>& entries,
                              SymmSet& set) {
   Timeline& tl = state_.timeline;
   WaitForInputs(entries);
+  host_trace::Mark("inputs");
   ActStart(entries, HVD_ACT_FUSED_KERNEL);
   std::vector<Block> blocks;
   for (auto& e : entries) {
@@ -368,6 +382,7 @@ Status GpuOps::SymmAllgather(std::vector<TensorTableEntry>& entries,
   Timeline& tl = state_.timeline;
   const int n = set.world;
   WaitForInputs(entries);
+  host_trace::Mark("inputs");
   std::vector<Block> blocks;
   for (size_t i = 0; i < entries.size(); ++i) {
     TensorTableEntry& e = entries[i];
@@ -395,6 +410,7 @@ Status GpuOps::SymmAllgather(std::vector<TensorTableEntry>& entries,
       blocks.push_back(b);
     }
   }
+  host_trace::Mark("outputs");
   ActStart(entries, HVD_ACT_FUSED_KERNEL);
   const RemoteStats rs = RemoteBlockStats(blocks, set.world);
   const bool ce = ExchangeUsesCopyEngine(set, rs.total, rs.smallest, rs.count);
@@ -419,7 +435,9 @@ Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries,
     // Full split matrix over the control plane: all[r * n + p] = rows rank r
     // sends to rank p.
     std::vector<int32_t> all(static_cast<size_t>(n) * n);
+    host_trace::Mark("inputs");
     ps.comm.Allgather(e.splits.data(), sizeof(int32_t) * n, all.data());
+    host_trace::Mark("splits");
     std::vector<int32_t> recv(n);
     int64_t rows = 0;
     for (int r = 0; r < n; ++r) {

@@ -198,6 +198,8 @@ private:
   Status SymmAllreduce(std::vector<TensorTableEntry>& entries,
                        const Response& response, SymmSet& set, bool adasum);
   Status SymmBroadcast(std::vector<TensorTableEntry>& entries, SymmSet& set);
+  Status GroupedReducescatterPush(std::vector<TensorTableEntry>& entries, SymmSet& set,
+                                  bool* done);
   Status SymmAllgather(std::vector<TensorTableEntry>& entries,
                        const Response& response, SymmSet& set);
   Status SymmAlltoall(std::vector<TensorTableEntry>& entries, ProcessSet& ps,
@@ -255,7 +257,7 @@ private:
   int64_t dynamic_min_bytes_ = 0;
   int64_t exchange_chunk_bytes_ = 256 << 10;  // HOROVOD_EXCHANGE_CHUNK_KB
   int64_t exchange_push_max_ = 1 << 20;       // HOROVOD_EXCHANGE_PUSH_MAX_BYTES
-  int64_t exchange_ce_min_ = 32 << 20;        // HOROVOD_EXCHANGE_COPY_ENGINE_MIN_BYTES (0 = never)
+  int64_t exchange_ce_min_ = 0;               // HOROVOD_EXCHANGE_COPY_ENGINE_MIN_BYTES (0 = never)
   int64_t allreduce_subchunk_bytes_ = 64 << 10;  // HOROVOD_ALLREDUCE_SUBCHUNK_KB, 0 = off
   int64_t allreduce_pipeline_min_ = 8 << 20;     // HOROVOD_ALLREDUCE_PIPELINE_MIN_BYTES
   unsigned long long* xchg_done_counter_ = nullptr;  // device word, see kern::ExchangeSync

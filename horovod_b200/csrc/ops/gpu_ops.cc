@@ -11,6 +11,7 @@
 #include "gpu_internal.h"
 #include "../symm/topology.h"
 #include "nccl_ops.h"
+#include "host_trace.h"
 
 namespace hvd {
 
@@ -253,7 +254,7 @@ void GpuOps::EnsureDevice(int device) {
   exchange_chunk_bytes_ =
       std::max<int64_t>(64, EnvInt("HOROVOD_EXCHANGE_CHUNK_KB", 256)) << 10;
   exchange_push_max_ = EnvInt("HOROVOD_EXCHANGE_PUSH_MAX_BYTES", 1 << 20);
-  exchange_ce_min_ = EnvInt("HOROVOD_EXCHANGE_COPY_ENGINE_MIN_BYTES", 32 << 20);
+  exchange_ce_min_ = EnvInt("HOROVOD_EXCHANGE_COPY_ENGINE_MIN_BYTES", 0);
   allreduce_pipeline_min_ = EnvInt("HOROVOD_ALLREDUCE_PIPELINE_MIN_BYTES", 8 << 20);
   allreduce_subchunk_bytes_ =
       std::max<int64_t>(0, EnvInt("HOROVOD_ALLREDUCE_SUBCHUNK_KB", 64)) * 1024 / 256 * 256;
@@ -534,7 +535,9 @@ void GpuOps::CloseTiming() {
   PendingTiming* pt = open_timing_;
   if (pt == nullptr || pt->t1 == nullptr) return;
   open_timing_ = nullptr;
+  host_trace::Mark("rest");
   cudaEventRecord(pt->t1, stream_);
+  host_trace::Mark("end event");
   pt->host_us = static_cast<float>(HostNowUs() - pt->host_t0);
   std::lock_guard<std::mutex> l(timing_mu_);
   pending_timings_.push_back(*pt);
@@ -646,6 +649,7 @@ Status GpuOps::Execute(std::vector<TensorTableEntry>& entries,
     HVD_CUDA(cudaEventRecord(pt.t0, stream_));
     pt.host_t0 = HostNowUs();
     open_timing_ = &pt;
+    host_trace::Begin(static_cast<int>(response.type) + (use_symm ? 0 : 100));
   }
   // Normally Complete() closes the record right after the last launch; this
   // covers the paths that return without reaching it.
@@ -715,6 +719,7 @@ std::vector<GpuOps::OpTiming> GpuOps::DrainTimings() {
 void GpuOps::Shutdown() {
   if (shut_down_) return;
   shut_down_ = true;
+  if (slot_ == 0 && lane_ == 0) host_trace::Report(state_.config.rank);
   GpuOps* self = this;
   g_current.compare_exchange_strong(self, nullptr);
   {

@@ -7,6 +7,7 @@
 #include "../common/logging.h"
 #include "../common/process_set.h"
 #include "gpu_internal.h"
+#include "host_trace.h"
 
 namespace hvd {
 
@@ -203,10 +204,12 @@ Status GpuOps::SymmAllreduce(std::vector<TensorTableEntry>& entries,
       }
       kern::SymmCtx ctx = MakeCtx(set, epochs, staging_off, skip_end);
       ctx.sub_chunk_vecs = sub_vecs;
+      host_trace::Mark("plan");
       err = kern::LaunchFusedAllreduce(list, dtype, adasum ? dtype : wire,
                                        response.prescale, response.postscale,
                                        algo, ctas, ctx, stream_,
                                        use_inline ? &inl : nullptr);
+      host_trace::Mark("launch");
       if (!use_inline) ring_.Release(slot, stream_);
     }
     if (err != cudaSuccess)
@@ -300,10 +303,12 @@ bool GpuOps::TryInplaceAllreduce(std::vector<TensorTableEntry>& entries,
     tile_base_ += static_cast<unsigned long long>((mine + sched.tile_vecs - 1) / sched.tile_vecs) +
                   static_cast<unsigned long long>(ctas);
   }
+  host_trace::Mark("plan (in place)");
   cudaError_t err = kern::LaunchInplaceAllreduce(
       list, dtype, response.prescale * response.postscale,
       nvls || (forced_algo_ == "nvls" && set.nvls && dtype != DataType::FLOAT64),
       ctas, ctx, stream_, use_inline ? &inl : nullptr, &sched);
+  host_trace::Mark("launch");
   if (!use_inline) ring_.Release(slot, stream_);
   *status = err == cudaSuccess
                 ? Status::OK()
@@ -312,10 +317,120 @@ bool GpuOps::TryInplaceAllreduce(std::vector<TensorTableEntry>& entries,
   return true;
 }
 
+// A fused reducescatter response (several tensors of one dtype and one
+// scaling) whose shards all fit one sender slot of the exchange region, none
+// of them inside the symmetric heap: one launch for the whole group.
+// *done stays false when the group does not qualify (the caller then runs the
+// tensors one by one).
+Status GpuOps::GroupedReducescatterPush(std::vector<TensorTableEntry>& entries, SymmSet& set,
+                                        bool* done) {
+  Timeline& tl = state_.timeline;
+  const int n = set.world, me = set.rank;
+  if (n <= 1 || set.xchg_bytes <= 0) return Status::OK();
+  const TensorTableEntry& first = entries[0];
+  const int64_t es = static_cast<int64_t>(DataTypeSize(first.dtype));
+  const int64_t slot_bytes = set.xchg_bytes / n / STAGING_ALIGN * STAGING_ALIGN;
+  struct Geo { int64_t base, extra, slice, longest_bytes; };
+  std::vector<Geo> geo;
+  int64_t need = 0;
+  for (auto& e : entries) {
+    if (e.dtype != first.dtype || e.prescale != first.prescale ||
+        e.postscale != first.postscale || e.reduce_op != first.reduce_op)
+      return Status::OK();
+    int64_t heap_off = 0;
+    if (e.input != nullptr && InSymmHeap(e.input, e.num_elements() * es, &heap_off))
+      return Status::OK();
+    int64_t rows = e.shape.dim_size(0), slice = 1;
+    for (int d = 1; d < e.shape.dims(); ++d) slice *= e.shape.dim_size(d);
+    Geo g;
+    g.base = rows / n;
+    g.extra = rows % n;
+    g.slice = slice;
+    g.longest_bytes = RoundUp((g.base + (g.extra ? 1 : 0)) * slice * es, STAGING_ALIGN);
+    need += g.longest_bytes;
+    geo.push_back(g);
+  }
+  if (need > slot_bytes || entries.size() > 2048) return Status::OK();
+
+  for (size_t i = 0; i < entries.size(); ++i) {
+    TensorTableEntry& e = entries[i];
+    std::vector<int64_t> dims = e.shape.to_vector();
+    dims[0] = geo[i].base + (me < geo[i].extra ? 1 : 0);
+    tl.ActivityStart(e.name, HVD_ACT_ALLOCATE_OUTPUT);
+    void* out = nullptr;
+    Status st = e.context->AllocateOutput(TensorShape(dims), stream_, &out);
+    tl.ActivityEnd(e.name);
+    if (!st.ok()) return st;
+    e.output = out;
+  }
+
+  const int ctas = PickCtas(need * n);
+  const int64_t chunk = exchange_chunk_bytes_ / 256 * 256;
+  DescriptorRing::Slot slot = ring_.Acquire();
+  kern::RsGroupTensor* d_desc;
+  kern::RsGroupTensor* h_desc = slot.Alloc<kern::RsGroupTensor>(entries.size(), &d_desc);
+  if (h_desc == nullptr) {
+    ring_.Release(slot, stream_);
+    return Status::OK();  // too many tensors for a descriptor slot: one by one
+  }
+  int count = 0;
+  int64_t off = 0, total_chunks = 0;
+  for (size_t i = 0; i < entries.size(); ++i) {
+    if (geo[i].longest_bytes == 0) continue;  // nothing to reduce
+    kern::RsGroupTensor& d = h_desc[count++];
+    d.in = entries[i].input;
+    d.out = entries[i].output;
+    d.base_rows = geo[i].base;
+    d.extra_rows = geo[i].extra;
+    d.row_elems = geo[i].slice;
+    d.slot_off = off;
+    const int64_t vecs = geo[i].longest_bytes / 16;
+    d.slice_vecs = RoundUp((vecs + ctas - 1) / ctas, 16);
+    total_chunks += (d.slice_vecs * 16 + chunk - 1) / chunk;
+    off += geo[i].longest_bytes;
+  }
+  if (count == 0) {
+    ring_.Release(slot, stream_);
+    *done = true;
+    return Status::OK();
+  }
+  ring_.Commit(slot, stream_);
+  kern::RsGroupArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.tensors = d_desc;
+  a.n_tensors = count;
+  a.total_chunks = static_cast<uint32_t>(total_chunks);
+  a.slot_bytes = slot_bytes;
+  a.chunk_bytes = chunk;
+  const uint32_t seq = ++set.xchg_seq;
+  a.credit_wait = seq > 2 ? seq - 2 : 0;
+  a.credit_post = seq;
+  a.done_counter = xchg_done_counter_;
+  xchg_done_base_ += static_cast<unsigned long long>(ctas);
+  a.done_target = xchg_done_base_;
+  kern::SymmCtx ctx = MakeCtx(set, static_cast<uint32_t>(total_chunks) + 1, set.xchg_off[seq & 1]);
+  ActStart(entries, HVD_ACT_FUSED_KERNEL);
+  cudaError_t err = kern::LaunchReducescatterPushGroup(a, first.dtype, first.prescale,
+                                                       first.postscale, ctas, ctx, stream_);
+  ActEnd(entries);
+  ring_.Release(slot, stream_);
+  if (err != cudaSuccess)
+    return Status::UnknownError(std::string("grouped reducescatter launch failed: ") +
+                                cudaGetErrorString(err));
+  *done = true;
+  return Status::OK();
+}
+
 Status GpuOps::SymmReducescatter(std::vector<TensorTableEntry>& entries,
                                  SymmSet& set) {
   Timeline& tl = state_.timeline;
   WaitForInputs(entries);
+  if (entries.size() > 1) {
+    bool done = false;
+    Status st = GroupedReducescatterPush(entries, set, &done);
+    if (!st.ok()) return st;
+    if (done) return Complete(entries);
+  }
   for (auto& e : entries) {
     const int64_t es = static_cast<int64_t>(DataTypeSize(e.dtype));
     const int n = set.world, me = set.rank;
@@ -331,9 +446,7 @@ Status GpuOps::SymmReducescatter(std::vector<TensorTableEntry>& entries,
     if (!st.ok()) return st;
     e.output = out;
 
-    DescriptorRing::Slot slot = ring_.Acquire();
-    int64_t* d_sb;
-    int64_t* h_sb = slot.Alloc<int64_t>(n + 1, &d_sb);
+    int64_t h_sb[SYMM_MAX_RANKS + 1];
     int64_t staged = 0;
     bool shards_aligned = true;
     for (int r = 0; r <= n; ++r) {
@@ -350,7 +463,6 @@ Status GpuOps::SymmReducescatter(std::vector<TensorTableEntry>& entries,
     if (sym_off < 0 && n > 1 && set.xchg_bytes > 0) {
       // Ordinary memory: push every shard into its owner's exchange region,
       // one window of the shards per launch.
-      ring_.Release(slot, stream_);  // the shard bounds travel in the parameters
       const int64_t slot_bytes = set.xchg_bytes / n / STAGING_ALIGN * STAGING_ALIGN;
       const int64_t win = slot_bytes / es;
       const int64_t longest = (base + (extra ? 1 : 0)) * slice;
@@ -392,6 +504,11 @@ Status GpuOps::SymmReducescatter(std::vector<TensorTableEntry>& entries,
       return Status::InvalidArgument(
           "reducescatter tensor '" + e.name + "' does not fit the symmetric "
           "staging buffer; raise HOROVOD_SYMM_BUFFER_MB.");
+    // This kernel reads the shard bounds from device memory.
+    DescriptorRing::Slot slot = ring_.Acquire();
+    int64_t* d_sb;
+    int64_t* ring_sb = slot.Alloc<int64_t>(n + 1, &d_sb);
+    std::memcpy(ring_sb, h_sb, sizeof(int64_t) * (n + 1));
     ring_.Commit(slot, stream_);
     kern::SymmCtx ctx = MakeCtx(set, kern::EPOCHS_PER_LAUNCH);
     ActStart(e.name, HVD_ACT_FUSED_KERNEL);

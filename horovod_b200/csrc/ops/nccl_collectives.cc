@@ -9,6 +9,7 @@
 #include "gpu_internal.h"
 #include "nccl_api.h"
 #include "nccl_ops.h"
+#include "host_trace.h"
 
 namespace hvd {
 
@@ -26,8 +27,10 @@ Status NcclOps::Broadcast(std::vector<TensorTableEntry>& entries, void* comm_v) 
   Timeline& tl = gpu_.state().timeline;
   for (auto& e : entries) {
     gpu_.ActStart(e.name, HVD_ACT_NCCL_BCAST);
+    host_trace::Mark("before call");
     HVD_NCCL(api_->Broadcast(e.input, e.output, static_cast<size_t>(e.size_bytes()),
                              ncclChar, e.root_rank, comm, stream));
+    host_trace::Mark("nccl call");
     gpu_.ActEnd(e.name);
   }
   return gpu_.Complete(entries);
@@ -58,9 +61,11 @@ Status NcclOps::Allgather(std::vector<TensorTableEntry>& entries,
     e.output = out;
     gpu_.ActStart(e.name, HVD_ACT_NCCL_ALLGATHER);
     if (equal) {
+      host_trace::Mark("before call");
       HVD_NCCL(api_->AllGather(e.input, out,
                                static_cast<size_t>(response.tensor_sizes[i * n] * slice),
                                ncclChar, comm, stream));
+      host_trace::Mark("nccl call");
     } else {
       // Unequal contributions: one broadcast per rank, grouped.
       HVD_NCCL(api_->GroupStart());

@@ -9,6 +9,7 @@
 #include "../common/process_set.h"
 #include "gpu_internal.h"
 #include "nccl_api.h"
+#include "host_trace.h"
 
 namespace hvd {
 
@@ -253,7 +254,9 @@ Status NcclOps::Allreduce(std::vector<TensorTableEntry>& entries,
     HVD_CUDA(cudaMemsetAsync(static_cast<char*>(buf) + off * es, 0,
                              static_cast<size_t>((padded - off) * es), stream));
   gpu_.ActStart(entries, HVD_ACT_MEMCPY_IN_FUSION_BUFFER);
+  host_trace::Mark("plan");
   kern::LaunchPackUnpack(list, dtype, wire, buf, response.prescale, true, off, stream);
+  host_trace::Mark("pack launch");
   gpu_.ActEnd(entries);
   gpu_.ActStart(entries, HVD_ACT_NCCL_ALLREDUCE);
   if (hierarchical_) {
@@ -271,9 +274,11 @@ Status NcclOps::Allreduce(std::vector<TensorTableEntry>& entries,
   } else {
     HVD_NCCL(api_->AllReduce(buf, buf, off, nt, op, comm, stream));
   }
+  host_trace::Mark("nccl call");
   gpu_.ActEnd(entries);
   gpu_.ActStart(entries, HVD_ACT_MEMCPY_OUT_FUSION_BUFFER);
   kern::LaunchPackUnpack(list, dtype, wire, buf, response.postscale, false, off, stream);
+  host_trace::Mark("unpack launch");
   gpu_.ActEnd(entries);
   gpu_.ring().Release(slot, stream);
   return gpu_.Complete(entries);

@@ -182,9 +182,11 @@ StatusCallback MakeCallback(std::shared_ptr<HandleRecord> rec) {
 
 class TorchOpContext : public OpContext {
 public:
+  // index >= 0: the output takes that position of the handle's output list
+  // (grouped ops, whose members may complete in any order).
   TorchOpContext(std::shared_ptr<HandleRecord> rec, at::TensorOptions options,
-                 int device)
-      : rec_(std::move(rec)), options_(options), device_(device) {}
+                 int device, int index = -1)
+      : rec_(std::move(rec)), options_(options), device_(device), index_(index) {}
 
   Status AllocateOutput(const TensorShape& shape, void* stream,
                         void** data) override {
@@ -198,7 +200,10 @@ public:
       }
       *data = out.data_ptr();
       std::lock_guard<std::mutex> l(rec_->mu);
-      rec_->outputs.push_back(std::move(out));
+      if (index_ >= 0 && index_ < static_cast<int>(rec_->outputs.size()))
+        rec_->outputs[index_] = std::move(out);
+      else
+        rec_->outputs.push_back(std::move(out));
       return Status::OK();
     } catch (const std::exception& e) {
       return Status::UnknownError(std::string("output allocation failed: ") +
@@ -215,6 +220,7 @@ private:
   std::shared_ptr<HandleRecord> rec_;
   at::TensorOptions options_;
   int device_;
+  int index_;
 };
 
 void ThrowIfError(const Status& s) {
@@ -431,6 +437,83 @@ int ReducescatterAsync(const at::Tensor& tensor, const std::string& name,
   return handle;
 }
 
+// Grouped allgather / reducescatter: one handle for the list; the outputs
+// (allocated by the ops) come back in order.
+namespace {
+std::vector<TensorTableEntry> GroupEntries(const std::vector<at::Tensor>& tensors,
+                                           const std::shared_ptr<HandleRecord>& rec,
+                                           const std::string& base, const char* op) {
+  std::vector<TensorTableEntry> entries;
+  std::shared_ptr<ReadyEvent> shared_ready;
+  rec->outputs.resize(tensors.size());
+  for (size_t i = 0; i < tensors.size(); ++i) {
+    if (DeviceOf(tensors[i]) != rec->device)
+      throw std::invalid_argument(std::string(op) +
+                                  ": all tensors must be on the same device");
+    CheckLayout(tensors[i], nullptr, /*dense_ok=*/false);
+    TensorTableEntry e;
+    e.input = tensors[i].data_ptr();
+    e.shape = TensorShape(tensors[i].sizes().vec());
+    e.dtype = ToDataType(tensors[i].scalar_type());
+    e.wire_dtype = e.dtype;
+    e.device = rec->device;
+    e.context = std::make_shared<TorchOpContext>(rec, tensors[i].options(), e.device,
+                                                 static_cast<int>(i));
+    if (e.device != CPU_DEVICE_ID) {
+      if (!shared_ready) shared_ready = std::make_shared<TorchReadyEvent>(e.device);
+      e.ready = shared_ready;
+    }
+    e.callback = MakeCallback(rec);
+    e.name = base + "_" + std::to_string(i + 1) + "of" + std::to_string(tensors.size());
+    entries.push_back(std::move(e));
+  }
+  return entries;
+}
+}  // namespace
+
+int GroupedAllgatherAsync(const std::vector<at::Tensor>& tensors, const std::string& name,
+                          int process_set) {
+  auto rec = std::make_shared<HandleRecord>();
+  rec->pending = static_cast<int>(tensors.size());
+  rec->device = tensors.empty() ? CPU_DEVICE_ID : DeviceOf(tensors[0]);
+  rec->inputs = tensors;
+  int handle = Handles().Allocate(rec);
+  if (tensors.empty()) return handle;
+  std::vector<TensorTableEntry> entries;
+  try {
+    entries = GroupEntries(tensors, rec, NameOrDefault(name, "grouped_allgather", handle),
+                           "grouped_allgather");
+  } catch (...) {
+    Handles().Release(handle);
+    throw;
+  }
+  Status st = EnqueueTensorAllgathers(entries, process_set);
+  if (!st.ok()) FailHandle(handle, st);
+  return handle;
+}
+
+int GroupedReducescatterAsync(const std::vector<at::Tensor>& tensors, const std::string& name,
+                              int op, double prescale, double postscale, int process_set) {
+  auto rec = std::make_shared<HandleRecord>();
+  rec->pending = static_cast<int>(tensors.size());
+  rec->device = tensors.empty() ? CPU_DEVICE_ID : DeviceOf(tensors[0]);
+  rec->inputs = tensors;
+  int handle = Handles().Allocate(rec);
+  if (tensors.empty()) return handle;
+  std::vector<TensorTableEntry> entries;
+  try {
+    entries = GroupEntries(tensors, rec, NameOrDefault(name, "grouped_reducescatter", handle),
+                           "grouped_reducescatter");
+  } catch (...) {
+    Handles().Release(handle);
+    throw;
+  }
+  Status st = EnqueueTensorReducescatters(entries, static_cast<ReduceOp>(op), prescale,
+                                          postscale, process_set);
+  if (!st.ok()) FailHandle(handle, st);
+  return handle;
+}
+
 int JoinAsync(int process_set) {
   auto rec = std::make_shared<HandleRecord>();
   int handle = Handles().Allocate(rec);
@@ -538,6 +621,11 @@ PYBIND11_MODULE(_C, m) {
   m.def("allreduce_async", &AllreduceAsync, py::arg("tensor"), py::arg("output"),
         py::arg("name"), py::arg("op"), py::arg("prescale"), py::arg("postscale"),
         py::arg("process_set"), py::arg("wire_dtype") = -1);
+  m.def("grouped_allgather_async", &GroupedAllgatherAsync, py::arg("tensors"),
+        py::arg("name") = "", py::arg("process_set") = 0);
+  m.def("grouped_reducescatter_async", &GroupedReducescatterAsync, py::arg("tensors"),
+        py::arg("name") = "", py::arg("op") = 1, py::arg("prescale") = 1.0,
+        py::arg("postscale") = 1.0, py::arg("process_set") = 0);
   m.def("grouped_allreduce_async", &GroupedAllreduceAsync, py::arg("tensors"),
         py::arg("outputs"), py::arg("name"), py::arg("op"), py::arg("prescale"),
         py::arg("postscale"), py::arg("process_set"), py::arg("wire_dtype") = -1);

@@ -13,6 +13,7 @@ from horovod_b200.torch.functions import (allgather_object, broadcast_object,
 from horovod_b200.torch.mpi_ops import (Adasum, Average, Max, Min, Product, Sum, allgather,
                                         allgather_async, allreduce, allreduce_, barrier,
                                         grouped_allgather, grouped_reducescatter,
+                                        grouped_allgather_async, grouped_reducescatter_async,
                                         allreduce_async, allreduce_async_, alltoall,
                                         alltoall_async, broadcast, broadcast_,
                                         broadcast_async, broadcast_async_, ccl_built,

@@ -561,26 +561,47 @@ def barrier(process_set=global_process_set):
                                 process_set=process_set))
 
 
+def grouped_allgather_async(tensors, name=None, process_set=global_process_set):
+    """Starts the allgather of a list of tensors as one group: the controller
+    negotiates the members together and fuses them, so tensors of one dtype
+    travel in one kernel launch. ``synchronize`` returns the list of gathered
+    tensors in order."""
+    tensors = list(tensors)
+    for t in tensors:
+        _check_tensor(t)
+    handle = _enqueue(_C.grouped_allgather_async, tensors, name or "", _resolve(process_set))
+    _handle_map[handle] = ("grouped", None)
+    return handle
+
+
 def grouped_allgather(tensors, name=None, process_set=global_process_set):
-    """Allgathers a list of tensors; the requests are issued together so that
-    they are negotiated in one cycle and fused by the controller. Returns the
-    gathered tensors in order."""
-    base = name
-    handles = [allgather_async(t, name=None if base is None else "%s.%d" % (base, i),
-                               process_set=process_set) for i, t in enumerate(tensors)]
-    return [synchronize(h) for h in handles]
+    """Allgathers a list of tensors as one group. Returns the gathered tensors
+    in order."""
+    return synchronize(grouped_allgather_async(tensors, name, process_set))
+
+
+def grouped_reducescatter_async(tensors, name=None, op=Average, prescale_factor=1.0,
+                                postscale_factor=1.0, process_set=global_process_set):
+    """Starts the reduce-scatter of a list of tensors as one group (one fused
+    response and, for device tensors of one dtype, one kernel launch).
+    ``synchronize`` returns this rank's shards in order."""
+    tensors = list(tensors)
+    for t in tensors:
+        _check_tensor(t)
+    if op == Adasum:
+        raise ValueError("reducescatter does not support Adasum")
+    handle = _enqueue(_C.grouped_reducescatter_async, tensors, name or "", int(op),
+                      float(prescale_factor), float(postscale_factor), _resolve(process_set))
+    _handle_map[handle] = ("grouped", None)
+    return handle
 
 
 def grouped_reducescatter(tensors, name=None, op=Average, prescale_factor=1.0,
                           postscale_factor=1.0, process_set=global_process_set):
-    """Reduce-scatters a list of tensors, issued together; returns this rank's
+    """Reduce-scatters a list of tensors as one group; returns this rank's
     shards in order."""
-    base = name
-    handles = [reducescatter_async(t, name=None if base is None else "%s.%d" % (base, i), op=op,
-                                   prescale_factor=prescale_factor,
-                                   postscale_factor=postscale_factor, process_set=process_set)
-               for i, t in enumerate(tensors)]
-    return [synchronize(h) for h in handles]
+    return synchronize(grouped_reducescatter_async(tensors, name, op, prescale_factor,
+                                                   postscale_factor, process_set))
 
 
 def join(device=-1, process_set=global_process_set):

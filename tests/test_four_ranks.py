@@ -169,6 +169,21 @@ def _grouped_extras(rank, size):
     tot = sum(range(size))
     exp0 = (torch.arange(size * 2, dtype=torch.float32) * size + tot)[rank * 2:(rank + 1) * 2]
     ok = ok and torch.equal(shards[0], exp0) and bool((shards[1] == sum(range(1, size + 1))).all())
+    # mixed dtypes in one group: the outputs keep the order of the inputs
+    mixed = hvd.grouped_reducescatter([torch.full((size, 2), float(rank + 1)),
+                                       torch.full((2 * size,), rank + 1, dtype=torch.int32),
+                                       torch.full((size,), float(rank + 1), dtype=torch.float64)],
+                                      op=hvd.Sum, name="grs.mixed")
+    tot = size * (size + 1) // 2
+    ok = ok and [m.dtype for m in mixed] == [torch.float32, torch.int32, torch.float64]
+    ok = ok and [tuple(m.shape) for m in mixed] == [(1, 2), (2,), (1,)]
+    ok = ok and all(bool((m.double() == tot).all()) for m in mixed)
+    h = hvd.grouped_allgather_async([torch.full((1,), rank, dtype=torch.int64),
+                                     torch.full((rank + 1,), float(rank))], name="gag.mixed")
+    got = hvd.synchronize(h)
+    ok = ok and got[0].tolist() == list(range(size))
+    ok = ok and got[1].tolist() == [float(r) for r in range(size) for _ in range(r + 1)]
+    ok = ok and hvd.grouped_allgather([], name="gag.none") == []
     hvd.barrier()
     hvd.shutdown()
     return ok

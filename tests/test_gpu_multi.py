@@ -472,6 +472,86 @@ def test_reducescatter_from_ordinary_memory():
     assert all(run_parallel(_reducescatter_push, np=_world(), timeout=300))
 
 
+def _grouped_push(rank, size):
+    """grouped_reducescatter / grouped_allgather of device tensors: the group
+    is negotiated as one unit; the tensors of one dtype leave in one kernel
+    launch; results against an fp64 PyTorch sum of the same inputs."""
+    os.environ["HOROVOD_SPIN_TIMEOUT_MS"] = "5000"
+    os.environ["HOROVOD_EXCHANGE_CHUNK_KB"] = "64"
+    import horovod_b200.torch as hvd
+    from horovod_b200 import _C
+    hvd.init()
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    bad = []  # labels of the checks that failed
+    shapes = [(5 * size + 3, 1001), (size, 1), (size - 1, 5), (3 * size, 4099), (2, 3),
+              (7 * size + 1, 33333)]
+    for it in range(3):
+        for dtype, pre, post in [(torch.float32, 1.0, 1.0), (torch.bfloat16, 0.5, 2.0)]:
+            def make(r):
+                return [_inputs(r * 31 + i + it, rows * w + 1, dtype)[1:].view(rows, w)
+                        for i, (rows, w) in enumerate(shapes)]
+            # views that start one element into their allocation: not 16-byte aligned
+            xs = [_inputs(rank * 31 + i + it, rows * w + 1, dtype).to(dev)[1:].view(rows, w)
+                  for i, (rows, w) in enumerate(shapes)]
+            hvd.allreduce(torch.zeros(1, device=dev), name="gp.sync")  # drain earlier work
+            torch.cuda.synchronize()
+            before = _C.kernel_launch_count()
+            outs = hvd.grouped_reducescatter(xs, op=hvd.Sum, prescale_factor=pre,
+                                             postscale_factor=post, name="gp.rs.%d.%s" % (it, str(dtype)[6:]))
+            torch.cuda.synchronize()
+            launches = _C.kernel_launch_count() - before
+            if launches != 1:
+                bad.append("launches=%d it=%d %s" % (launches, it, dtype))
+            everyone = [make(r) for r in range(size)]
+            tol = 1e-5 if dtype == torch.float32 else 4e-2
+            for i, (rows, w) in enumerate(shapes):
+                ref = sum((everyone[r][i].double() * pre).to(dtype).double()
+                          for r in range(size)) * post
+                base, extra = rows // size, rows % size
+                lo = rank * base + min(rank, extra)
+                hi = lo + base + (1 if rank < extra else 0)
+                if tuple(outs[i].shape) != (hi - lo, w) or outs[i].dtype != dtype:
+                    bad.append("shape %s it=%d tensor=%d" % (tuple(outs[i].shape), it, i))
+                    continue
+                if hi > lo:
+                    err = (outs[i].double().cpu() - ref[lo:hi]).abs().max().item()
+                    if err > tol * max(1.0, ref.abs().max().item()) * size:
+                        bad.append("value err=%g it=%d tensor=%d %s" % (err, it, i, dtype))
+    # mixed dtypes in one group: outputs come back in the order of the inputs
+    mixed = [torch.full((size, 2), float(rank + 1), device=dev),
+             torch.full((2 * size,), rank + 1, dtype=torch.int32, device=dev),
+             torch.full((size, 3), float(rank + 1), dtype=torch.float16, device=dev)]
+    outs = hvd.grouped_reducescatter(mixed, op=hvd.Sum, name="gp.mixed")
+    tot = size * (size + 1) // 2
+    if [o.dtype for o in outs] != [torch.float32, torch.int32, torch.float16]:
+        bad.append("mixed dtypes %s" % [o.dtype for o in outs])
+    if [tuple(o.shape) for o in outs] != [(1, 2), (2,), (1, 3)]:
+        bad.append("mixed shapes %s" % [tuple(o.shape) for o in outs])
+    if not all(bool((o.cpu().double() == tot).all()) for o in outs):
+        bad.append("mixed values")
+    gathered = hvd.grouped_allgather([torch.full((rank + 1, 3), float(rank), device=dev),
+                                      torch.arange(4, device=dev) + rank,
+                                      torch.full((2,), float(rank), device=dev)], name="gp.ag")
+    if not torch.equal(gathered[0].cpu(), torch.cat([torch.full((r + 1, 3), float(r))
+                                                     for r in range(size)])):
+        bad.append("allgather 0")
+    if not torch.equal(gathered[1].cpu(), torch.cat([torch.arange(4) + r for r in range(size)])):
+        bad.append("allgather 1")
+    if gathered[2].cpu().tolist() != [float(r) for r in range(size) for _ in range(2)]:
+        bad.append("allgather 2")
+    torch.cuda.synchronize()
+    hvd.shutdown()
+    return bad
+
+
+def test_grouped_reducescatter_is_one_launch():
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    failures = run_parallel(_grouped_push, np=_world(), timeout=300)
+    assert all(f == [] for f in failures), failures
+
+
 def _two_devices_per_rank(rank, size):
     """Every rank spreads a two-layer model over two of the box's GPUs (layer
     one on the first, layer two on the second) and trains it through

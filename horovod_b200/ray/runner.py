@@ -145,7 +145,8 @@ class RayExecutor:
 
     def __init__(self, settings=None, num_workers=None, num_hosts=None,
                  num_workers_per_host=1, cpus_per_worker=1, use_gpu=False,
-                 gpus_per_worker=None):
+                 gpus_per_worker=None, use_placement_group=True,
+                 placement_group_timeout_s=100):
         if num_workers is None and num_hosts is None:
             raise ValueError("Either `num_workers` or `num_hosts` must be specified.")
         if num_workers is not None and num_hosts is not None:
@@ -161,13 +162,29 @@ class RayExecutor:
         self.gpus_per_worker = gpus_per_worker or (1 if use_gpu else 0)
         self.workers = []
         self.coordinator = None
+        # Where the actors go (horovod/ray/strategy.py): packed, or a fixed
+        # number per host with every host on its own node.
+        from horovod_b200.ray import strategy
+        if num_workers is not None:
+            self.plan = strategy.plan_packed(self.num_workers, cpus_per_worker,
+                                             self.gpus_per_worker)
+        else:
+            self.plan = strategy.plan_colocated(num_hosts, num_workers_per_host,
+                                                cpus_per_worker, self.gpus_per_worker)
+        self.use_placement_group = use_placement_group
+        self.placement_group_timeout_s = placement_group_timeout_s
+        self.placement = None
 
     def start(self, executable_cls=None, executable_args=None, executable_kwargs=None,
               extra_env_vars=None):
         ray = _require_ray()
-        remote_cls = ray.remote(num_cpus=self.cpus_per_worker,
-                                num_gpus=self.gpus_per_worker)(_Worker)
-        self.workers = [remote_cls.remote(world_rank=r) for r in range(self.num_workers)]
+        from horovod_b200.ray.strategy import PlacementGroupHandle
+        self.placement = PlacementGroupHandle(ray, self.plan)
+        if self.use_placement_group:
+            self.placement.create(self.placement_group_timeout_s)
+        remote_cls = ray.remote(_Worker)
+        self.workers = [remote_cls.options(**self.placement.actor_options(r)).remote(world_rank=r)
+                        for r in range(self.num_workers)]
         hostnames = ray.get([w.hostname.remote() for w in self.workers])
         node_ids = ray.get([w.node_id.remote() for w in self.workers])
         self.coordinator = Coordinator(self.settings)
@@ -201,5 +218,9 @@ class RayExecutor:
         for w in self.workers:
             ray.kill(w)
         self.workers = []
+        if self.placement is not None:
+            self.placement.remove()
+            self.placement = None
         if self.coordinator is not None:
             self.coordinator.shutdown()
+            self.coordinator = None

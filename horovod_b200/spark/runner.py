@@ -3,8 +3,8 @@ of one barrier stage as the ranks of one job and returns the results by
 rank. The tasks learn each other's hosts through the barrier context, derive
 their local/cross coordinates from them and meet at a rendezvous server on
 the driver. ``pyspark`` (3.0 or newer, for BarrierTaskContext.allGather) is
-imported at call time. Not exercised in this repository's tests: pyspark is
-not installed here.
+imported at call time; the tests drive run() through a stand-in pyspark
+module, since pyspark itself is not installed here.
 Parity: horovod/spark/runner.py:197-305 (run); the elastic variant and the
 Estimator API (:308-429, horovod/spark/{keras,torch,lightning}) are not built.
 """

@@ -233,3 +233,11 @@ def test_fusion_policy_threshold_lookahead_and_compatibility():
                              item("r", 8, F32, typ=BC, root=1)], 1 << 20) == [["p", "q"], ["r"]]
     # threshold 0: nothing fuses
     assert T.fuse_responses([item("a", 1), item("b", 1)], 0) == [["a"], ["b"]]
+    # reduce-scatters fuse among themselves under the rules of a reduction
+    # (dtype and scaling must agree), never with an allreduce; alltoalls never fuse
+    RS, A2A = 6, 5
+    assert T.fuse_responses([item("r1", 10, typ=RS), item("x", 10), item("r2", 10, typ=RS),
+                             item("r3", 10, typ=RS, post=0.5), item("r4", 10, F16, typ=RS)],
+                            1 << 20) == [["r1", "r2"], ["x"], ["r3"], ["r4"]]
+    assert T.fuse_responses([item("t1", 10, typ=A2A), item("t2", 10, typ=A2A)], 1 << 20) == \
+        [["t1"], ["t2"]]

@@ -113,3 +113,252 @@ def test_filesystem_store_layout_and_sync(tmp_path):
     assert quiet.get_checkpoint_path("r") is None and not quiet.saving_runs()
     with pytest.raises(ValueError):
         Store.create("hdfs://namenode/path")
+
+
+def test_ray_placement_plans():
+    from horovod_b200.ray import plan_colocated, plan_packed
+    p = plan_packed(3, cpus_per_worker=2, gpus_per_worker=1)
+    assert p.strategy == "PACK" and p.bundles == [{"CPU": 2, "GPU": 1}] * 3
+    assert p.bundle_of_rank == [0, 1, 2] and p.num_workers == 3
+    c = plan_colocated(2, 4, cpus_per_worker=1, gpus_per_worker=1)
+    assert c.strategy == "STRICT_SPREAD" and c.bundles == [{"CPU": 4, "GPU": 4}] * 2
+    assert c.bundle_of_rank == [0, 0, 0, 0, 1, 1, 1, 1]
+    assert plan_packed(1).bundles == [{"CPU": 1}]  # no GPU key without GPUs
+    with pytest.raises(ValueError):
+        plan_colocated(0, 2)
+
+
+class _FakeRef:
+    def __init__(self, value=None, error=None):
+        self.value, self.error = value, error
+
+
+def _fake_ray(node_ids, nodes=None):
+    """A stand-in ``ray`` module that runs actor methods and tasks in this
+    process: enough to drive the executors' orchestration. Actor r reports
+    node_ids[r]; placement requests and task options are recorded."""
+    ray = types.ModuleType("ray")
+    ray.calls = {"options": [], "groups": [], "removed": 0, "killed": 0, "tasks": []}
+    state = {"next_actor": 0}
+
+    class Method:
+        def __init__(self, bound):
+            self.bound = bound
+
+        def remote(self, *a, **kw):
+            try:
+                return _FakeRef(self.bound(*a, **kw))
+            except Exception as e:  # surfaces at ray.get, as in Ray
+                return _FakeRef(error=e)
+
+    class Actor:
+        def __init__(self, obj, index):
+            self._obj, self._index = obj, index
+
+        def __getattr__(self, name):
+            if name == "node_id":
+                return Method(lambda: node_ids[self._index])
+            return Method(getattr(self._obj, name))
+
+    class RemoteClass:
+        def __init__(self, cls):
+            self.cls = cls
+
+        def options(self, **opts):
+            ray.calls["options"].append(opts)
+            return self
+
+        def remote(self, *a, **kw):
+            index = state["next_actor"]
+            state["next_actor"] += 1
+            return Actor(self.cls(*a, **kw), index)
+
+    class RemoteFunction:
+        def __init__(self, fn):
+            self.fn = fn
+
+        def options(self, **opts):
+            ray.calls["tasks"].append(opts)
+            return self
+
+        def remote(self, *a, **kw):
+            return Method(self.fn).remote(*a, **kw)
+
+    def remote(target):
+        return RemoteClass(target) if isinstance(target, type) else RemoteFunction(target)
+
+    def get(refs):
+        def one(r):
+            if r.error is not None:
+                raise r.error
+            return r.value
+        return [one(r) for r in refs] if isinstance(refs, list) else one(refs)
+
+    ray.remote = remote
+    ray.get = get
+    ray.wait = lambda refs, timeout=None: (list(refs), [])
+    ray.kill = lambda actor: ray.calls.__setitem__("killed", ray.calls["killed"] + 1)
+    ray.cancel = lambda ref, force=False: None
+    ray.nodes = lambda: nodes or []
+    ray.available_resources = lambda: {}
+    util = types.ModuleType("ray.util")
+    util.get_node_ip_address = lambda: "127.0.0.1"
+
+    class Group:
+        def ready(self):
+            return _FakeRef(True)
+
+    def placement_group(bundles, strategy="PACK"):
+        ray.calls["groups"].append((bundles, strategy))
+        return Group()
+
+    def remove_placement_group(group):
+        ray.calls["removed"] += 1
+
+    util.placement_group = placement_group
+    util.remove_placement_group = remove_placement_group
+    ray.util = util
+    return ray, util
+
+
+def test_ray_executor_orchestration_with_a_stand_in_ray(monkeypatch):
+    """start() reserves the placement group, creates one actor per rank in its
+    bundle, hands every rank its coordinates and the rendezvous address;
+    run()/execute() reach every actor; shutdown() releases everything."""
+    from horovod_b200.ray import RayExecutor
+    ray, util = _fake_ray(["n0", "n0", "n1", "n1"])
+    monkeypatch.setitem(sys.modules, "ray", ray)
+    monkeypatch.setitem(sys.modules, "ray.util", util)
+    saved = dict(os.environ)
+    ex = RayExecutor(num_hosts=2, num_workers_per_host=2, use_gpu=True)
+    try:
+        class Exe:
+            def __init__(self, base):
+                self.base = base
+        ex.start(executable_cls=Exe, executable_args=[10], extra_env_vars={"MY_FLAG": "1"})
+        assert ray.calls["groups"] == [([{"CPU": 2, "GPU": 2}] * 2, "STRICT_SPREAD")]
+        assert [o["placement_group_bundle_index"] for o in ray.calls["options"]] == [0, 0, 1, 1]
+        assert all(o["num_gpus"] == 1 and o["num_cpus"] == 1 for o in ray.calls["options"])
+        # The stand-in runs every actor in this process, so the environment
+        # seen afterwards is that of the last rank.
+        env = ex.run(lambda: dict(os.environ))[3]
+        assert (env["HOROVOD_RANK"], env["HOROVOD_SIZE"], env["HOROVOD_LOCAL_RANK"],
+                env["HOROVOD_LOCAL_SIZE"], env["HOROVOD_CROSS_RANK"],
+                env["HOROVOD_CROSS_SIZE"]) == ("3", "4", "1", "2", "1", "2")
+        assert env["MY_FLAG"] == "1" and env["HOROVOD_GLOO_RENDEZVOUS_ADDR"] == "127.0.0.1"
+        assert ex.execute(lambda exe: exe.base + 1) == [11] * 4
+        assert ex.execute_single(lambda exe: exe.base) == 10
+        assert ex.run(lambda a, b=0: a + b, args=[1], kwargs={"b": 2}) == [3] * 4
+    finally:
+        ex.shutdown()
+        os.environ.clear()
+        os.environ.update(saved)
+    assert ray.calls["killed"] == 4 and ray.calls["removed"] == 1 and ex.coordinator is None
+
+
+def test_elastic_ray_executor_runs_a_round_with_a_stand_in_ray(monkeypatch):
+    """The elastic executor discovers the cluster's slots, starts one task per
+    slot pinned to its node with that slot's coordinates, and returns the
+    workers' values by rank."""
+    from horovod_b200.ray import ElasticRayExecutor
+    nodes = [{"alive": True, "NodeManagerAddress": "10.0.0.1", "Resources": {"CPU": 4, "GPU": 2}},
+             {"alive": True, "NodeManagerAddress": "10.0.0.2", "Resources": {"CPU": 4, "GPU": 2}}]
+    ray, util = _fake_ray([], nodes)
+    monkeypatch.setitem(sys.modules, "ray", ray)
+    monkeypatch.setitem(sys.modules, "ray.util", util)
+    saved = dict(os.environ)
+    try:
+        with pytest.raises(ValueError):
+            ElasticRayExecutor(ElasticRayExecutor.create_settings(), gpus_per_slot=1)
+        settings = ElasticRayExecutor.create_settings(min_np=4, max_np=4, elastic_timeout=20,
+                                                      verbose=0)
+        ex = ElasticRayExecutor(settings, use_gpu=True, cpus_per_slot=2,
+                                env_vars={"MY_FLAG": "1"})
+        ex.start(advertise_ip="127.0.0.1")
+
+        def worker():
+            return (int(os.environ["HOROVOD_RANK"]), os.environ["HOROVOD_HOSTNAME"],
+                    os.environ["HOROVOD_ELASTIC"], os.environ["MY_FLAG"],
+                    os.environ["HOROVOD_SIZE"])
+        results = ex.run(worker)
+        assert [r[0] for r in results] == [0, 1, 2, 3]
+        assert sorted(r[1] for r in results) == ["10.0.0.1"] * 2 + ["10.0.0.2"] * 2
+        assert all(r[2:] == ("1", "1", "4") for r in results)
+        pinned = sorted(list(t["resources"])[0] for t in ray.calls["tasks"])
+        assert pinned == ["node:10.0.0.1"] * 2 + ["node:10.0.0.2"] * 2
+        assert all(t["num_gpus"] == 1 and t["num_cpus"] == 2 for t in ray.calls["tasks"])
+    finally:
+        os.environ.clear()
+        os.environ.update(saved)
+
+
+def test_spark_run_with_a_stand_in_pyspark(monkeypatch):
+    """run() starts one barrier task per rank; every task derives its
+    coordinates from the hosts gathered through the barrier context, finds the
+    rendezvous server of the driver in its environment, and the results come
+    back ordered by rank. The stand-in runs the tasks one after the other in
+    this process, in reverse partition order."""
+    from horovod_b200.spark.runner import run
+    hosts = ["a", "b", "a", "b"]
+    current = {"partition": None}
+    pyspark = types.ModuleType("pyspark")
+
+    class BarrierTaskContext:
+        @staticmethod
+        def get():
+            return BarrierTaskContext()
+
+        def allGather(self, message):
+            return list(hosts)
+
+        def partitionId(self):
+            return current["partition"]
+
+    class RDD:
+        def __init__(self, n):
+            self.n = n
+            self.barrier_used = False
+
+        def barrier(self):
+            self.barrier_used = True
+            return self
+
+        def mapPartitionsWithIndex(self, task):
+            self.task = task
+            return self
+
+        def collect(self):
+            assert self.barrier_used
+            out = []
+            for index in reversed(range(self.n)):
+                current["partition"] = index
+                out.extend(self.task(index, iter([index])))
+            return out
+
+    class SparkContext:
+        _active_spark_context = None
+        defaultParallelism = 4
+
+        def range(self, start, numSlices=None):
+            return RDD(numSlices)
+
+    pyspark.BarrierTaskContext = BarrierTaskContext
+    pyspark.SparkContext = SparkContext
+    monkeypatch.setitem(sys.modules, "pyspark", pyspark)
+    with pytest.raises(Exception, match="SparkContext"):
+        run(lambda: 0, num_proc=2)
+    SparkContext._active_spark_context = SparkContext()
+    saved = dict(os.environ)
+    try:
+        def fn(tag):
+            e = os.environ
+            return (tag, int(e["HOROVOD_RANK"]), int(e["HOROVOD_SIZE"]),
+                    int(e["HOROVOD_LOCAL_RANK"]), int(e["HOROVOD_LOCAL_SIZE"]),
+                    int(e["HOROVOD_CROSS_RANK"]), int(e["HOROVOD_CROSS_SIZE"]),
+                    e["HOROVOD_HOSTNAME"], int(e["HOROVOD_GLOO_RENDEZVOUS_PORT"]) > 0, e["EXTRA"])
+        results = run(fn, args=("t",), extra_env={"EXTRA": "x"}, verbose=0)  # num_proc inferred
+    finally:
+        os.environ.clear()
+        os.environ.update(saved)
+    assert results == [("t", 0, 4, 0, 2, 0, 2, "a", True, "x"), ("t", 1, 4, 0, 2, 1, 2, "b", True, "x"),
+                       ("t", 2, 4, 1, 2, 0, 2, "a", True, "x"), ("t", 3, 4, 1, 2, 1, 2, "b", True, "x")]

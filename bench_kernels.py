@@ -233,7 +233,54 @@ def main():
             opt = cls(ps, lr=0.01, momentum=0.9, weight_decay=1e-4)
             opt.step()  # creates the momentum buffers
             us = timed_events(opt.step, args.iters)
-            report_line(name, us, 5 * total, {"tensors": len(sizes), "payload_mb": total >> 20})
+            report_line(name + "_step_call", us, 5 * total,
+                        {"tensors": len(sizes), "payload_mb": total >> 20,
+                         "note": "optimizer.step() as called by a training loop: bounded by "
+                                 "its Python work when the GPU is otherwise idle"})
+            if cls is FusedSGD:
+                # The kernel alone, through the plan that step() cached.
+                plan, n, n_chunks = next(iter(opt._plans.values()))[1]
+
+                def kernel_only():
+                    _C.sgd_step(plan, n, n_chunks, opt.CHUNK, True, 0.01, 0.9, 0.0, 1e-4, False,
+                                False, False)
+                us = timed_events(kernel_only, args.iters)
+                report_line("fused_sgd_kernel", us, 5 * total,
+                            {"tensors": len(sizes), "payload_mb": total >> 20})
+    if "peer_copy" in cases and torch.cuda.device_count() >= 2:
+        # Copy-engine copy between GPU 0 and GPU 1 over NVLink, issued on a
+        # stream of the source GPU (push) or of the destination GPU (pull): the
+        # link rate that the SM-driven exchange kernels are compared with.
+        import ctypes
+        rt = ctypes.CDLL("libcudart.so.12")
+        n = min(nbytes, 256 << 20)
+        a = torch.empty(n, dtype=torch.uint8, device="cuda:0").fill_(1)
+        b = torch.empty(n, dtype=torch.uint8, device="cuda:1")
+        b.copy_(a)  # turns peer access on
+        torch.cuda.synchronize(0)
+        torch.cuda.synchronize(1)
+        for name, d in (("peer_copy_push", 0), ("peer_copy_pull", 1)):
+            with torch.cuda.device(d):
+                stream = torch.cuda.Stream(device=d)
+
+                def copy():
+                    rc = rt.cudaMemcpyAsync(ctypes.c_void_p(b.data_ptr()),
+                                            ctypes.c_void_p(a.data_ptr()), ctypes.c_size_t(n),
+                                            ctypes.c_int(3), ctypes.c_void_p(stream.cuda_stream))
+                    assert rc == 0, rc
+                for _ in range(args.warmup):
+                    copy()
+                stream.synchronize()
+                e0 = torch.cuda.Event(enable_timing=True)
+                e1 = torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(args.iters):
+                    copy()
+                e1.record(stream)
+                e1.synchronize()
+                us = e0.elapsed_time(e1) * 1e3 / args.iters
+            print(json.dumps({"case": name, "payload_mb": n >> 20, "device_us": round(us, 1),
+                              "nvlink_gbs_one_direction": round(n / us / 1e3, 1)}), flush=True)
     clock_log.stop()
     hvd.shutdown()
     return 0

@@ -58,9 +58,9 @@ __device__ __forceinline__ bool wait_word(const SymmCtx& ctx, const uint32_t* f,
 // memory first (parameter reads with compile-time offsets only); else it is
 // read from device memory.
 template <bool INLINE>
-__global__ void __launch_bounds__(THREADS, 2)
-exchange_kernel(const InlineExchange inl, const ExchangePlan plan_dev, const ExchangeSync sync,
-                SymmCtx ctx) {
+__device__ __forceinline__ void exchange_body(const InlineExchange& inl,
+                                              const ExchangePlan& plan_dev,
+                                              const ExchangeSync& sync, const SymmCtx& ctx) {
   const int b = blockIdx.x, G = gridDim.x;
   constexpr int SEGS = INLINE ? INLINE_SEGMENTS : 1;
   __shared__ const void* s_st_src[SEGS];
@@ -252,6 +252,24 @@ exchange_kernel(const InlineExchange inl, const ExchangePlan plan_dev, const Exc
   trace_mark(ctx, 3);
 }
 
+template <bool INLINE>
+__global__ void __launch_bounds__(THREADS, 2)
+exchange_kernel(const InlineExchange inl, const ExchangePlan plan_dev, const ExchangeSync sync,
+                SymmCtx ctx) {
+  exchange_body<INLINE>(inl, plan_dev, sync, ctx);
+}
+
+// Stands in for the inline plan of the variant that does not read it.
+__device__ InlineExchange g_no_inline_plan;
+
+// Several ranks on one GPU (tests): row y of a cooperative launch runs the
+// kernel of rank y (see EmuAllreduceRank).
+__global__ void __launch_bounds__(THREADS, 2)
+exchange_emulated_kernel(const EmuExchangeRank* ranks) {
+  const EmuExchangeRank& r = ranks[blockIdx.y];
+  exchange_body<false>(g_no_inline_plan, r.plan, r.sync, r.ctx);
+}
+
 __global__ void credit_post_kernel(SymmCtx ctx, uint32_t value) {
   // The copies that read the peers' regions were queued on this stream before
   // this launch, so they have completed; one release store per peer.
@@ -269,7 +287,8 @@ cudaError_t LaunchExchange(const ExchangePlan& plan, const ExchangeSync& sync, i
                            const SymmCtx& ctx, cudaStream_t stream,
                            const InlineExchange* inline_plan) {
   if (num_ctas < 1 || num_ctas > SYMM_MAX_BLOCKS) return cudaErrorInvalidValue;
-  if (sync.chunk_bytes < 4096 || (sync.chunk_bytes & 255) != 0) return cudaErrorInvalidValue;
+  // A segment of up to 64 KB is one chunk of one CTA, so a chunk must hold it.
+  if (sync.chunk_bytes < 64 * 1024 || (sync.chunk_bytes & 255) != 0) return cudaErrorInvalidValue;
   if (sync.credit_post != 0 && sync.done_counter == nullptr) return cudaErrorInvalidValue;
   CountKernelLaunches(1);
   static const InlineExchange kNoInline = {};
@@ -278,6 +297,16 @@ cudaError_t LaunchExchange(const ExchangePlan& plan, const ExchangeSync& sync, i
   else
     exchange_kernel<false><<<num_ctas, THREADS, 0, stream>>>(kNoInline, plan, sync, ctx);
   return cudaGetLastError();
+}
+
+cudaError_t LaunchExchangeEmulated(const EmuExchangeRank* ranks, int world, int num_ctas,
+                                   cudaStream_t stream) {
+  if (num_ctas < 1 || num_ctas > SYMM_MAX_BLOCKS || world < 1 || world > SYMM_MAX_RANKS)
+    return cudaErrorInvalidValue;
+  CountKernelLaunches(1);
+  void* args[] = {&ranks};
+  return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(&exchange_emulated_kernel),
+                                     dim3(num_ctas, world), dim3(THREADS), args, 0, stream);
 }
 
 cudaError_t LaunchCreditPost(uint32_t value, const SymmCtx& ctx, cudaStream_t stream) {

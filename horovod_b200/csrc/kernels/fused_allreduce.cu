@@ -109,10 +109,11 @@ __device__ __forceinline__ void oneshot_reduce(const TensorList& tl, const SymmC
 // copied to shared memory first (parameter reads with compile-time offsets
 // only); else it is read from device memory (`tl_dev`).
 template <typename T, typename W, int ALGO, bool INLINE>
-__global__ void __launch_bounds__(THREADS)
-fused_allreduce_kernel(const InlineTensors inl, const TensorList tl_dev,
-                       SymmCtx ctx, typename ScaleT<T>::type prescale,
-                       typename ScaleT<T>::type postscale) {
+__device__ __forceinline__ void fused_allreduce_body(const InlineTensors& inl,
+                                                     const TensorList& tl_dev,
+                                                     const SymmCtx& ctx,
+                                                     typename ScaleT<T>::type prescale,
+                                                     typename ScaleT<T>::type postscale) {
   using S = typename ScaleT<T>::type;
   constexpr int N = 16 / sizeof(W);
   __shared__ int64_t s_offsets[INLINE ? INLINE_TENSORS + 1 : 1];
@@ -295,6 +296,30 @@ fused_allreduce_kernel(const InlineTensors inl, const TensorList tl_dev,
   }
 }
 
+template <typename T, typename W, int ALGO, bool INLINE>
+__global__ void __launch_bounds__(THREADS)
+fused_allreduce_kernel(const InlineTensors inl, const TensorList tl_dev,
+                       SymmCtx ctx, typename ScaleT<T>::type prescale,
+                       typename ScaleT<T>::type postscale) {
+  fused_allreduce_body<T, W, ALGO, INLINE>(inl, tl_dev, ctx, prescale, postscale);
+}
+
+// Stands in for the inline list of the variant that does not read it.
+__device__ InlineTensors g_no_inline_list;
+
+// Several ranks on one GPU (tests): one cooperative launch whose grid is
+// (CTAs per rank, ranks); row y runs the kernel of rank y with that rank's
+// tensor list and context, so the rows can wait for one another like the
+// kernels of different GPUs do.
+template <typename T, typename W, int ALGO>
+__global__ void __launch_bounds__(THREADS)
+fused_allreduce_emulated_kernel(const EmuAllreduceRank* ranks,
+                                typename ScaleT<T>::type prescale,
+                                typename ScaleT<T>::type postscale) {
+  const EmuAllreduceRank& r = ranks[blockIdx.y];
+  fused_allreduce_body<T, W, ALGO, false>(g_no_inline_list, r.tl, r.ctx, prescale, postscale);
+}
+
 template <typename T, typename W, bool INLINE>
 cudaError_t LaunchAlgo(const InlineTensors& inl, const TensorList& tl, Algo algo,
                        int num_ctas, const SymmCtx& ctx, cudaStream_t stream,
@@ -334,7 +359,53 @@ cudaError_t LaunchTyped(const TensorList& tl, double prescale, double postscale,
   return LaunchAlgo<T, W, false>(kNoInline, tl, algo, num_ctas, ctx, stream, pre, post);
 }
 
+template <typename T, typename W>
+cudaError_t LaunchEmulatedTyped(const EmuAllreduceRank* ranks, int world, double prescale,
+                                double postscale, Algo algo, int num_ctas,
+                                cudaStream_t stream) {
+  using S = typename ScaleT<T>::type;
+  S pre = static_cast<S>(prescale), post = static_cast<S>(postscale);
+  void* args[] = {&ranks, &pre, &post};
+  const dim3 grid(num_ctas, world);
+  const void* fn = nullptr;
+  if (algo == Algo::ONESHOT)
+    fn = reinterpret_cast<const void*>(&fused_allreduce_emulated_kernel<T, W, 1>);
+  else if (algo == Algo::TWOSHOT)
+    fn = reinterpret_cast<const void*>(&fused_allreduce_emulated_kernel<T, W, 2>);
+  else
+    return cudaErrorInvalidValue;  // multimem needs a multicast object over several GPUs
+  // Cooperative: fails instead of deadlocking when the rows do not all fit on
+  // the GPU at once.
+  return cudaLaunchCooperativeKernel(fn, grid, dim3(THREADS), args, 0, stream);
+}
+
 }  // namespace
+
+cudaError_t LaunchFusedAllreduceEmulated(const EmuAllreduceRank* ranks, int world,
+                                         DataType dtype, DataType wire, double prescale,
+                                         double postscale, Algo algo, int num_ctas,
+                                         cudaStream_t stream) {
+  if (num_ctas < 1 || num_ctas > SYMM_MAX_BLOCKS || world < 1 || world > SYMM_MAX_RANKS)
+    return cudaErrorInvalidValue;
+  CountKernelLaunches(1);
+  if (dtype == DataType::FLOAT32 && wire == DataType::BFLOAT16)
+    return LaunchEmulatedTyped<float, __nv_bfloat16>(ranks, world, prescale, postscale, algo,
+                                                     num_ctas, stream);
+  if (dtype != wire) return cudaErrorInvalidValue;
+  switch (dtype) {
+  case DataType::FLOAT32:
+    return LaunchEmulatedTyped<float, float>(ranks, world, prescale, postscale, algo, num_ctas,
+                                             stream);
+  case DataType::BFLOAT16:
+    return LaunchEmulatedTyped<__nv_bfloat16, __nv_bfloat16>(ranks, world, prescale, postscale,
+                                                             algo, num_ctas, stream);
+  case DataType::INT32:
+    return LaunchEmulatedTyped<int32_t, int32_t>(ranks, world, prescale, postscale, algo,
+                                                 num_ctas, stream);
+  default:
+    return cudaErrorInvalidValue;
+  }
+}
 
 cudaError_t LaunchFusedAllreduce(const TensorList& tl, DataType dtype,
                                  DataType wire, double prescale,

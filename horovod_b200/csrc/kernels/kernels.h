@@ -116,6 +116,23 @@ cudaError_t LaunchFusedAllreduce(const TensorList& tensors, DataType dtype,
                                  const SymmCtx& ctx, cudaStream_t stream,
                                  const InlineTensors* inline_list = nullptr);
 
+// Several ranks on ONE GPU, for tests of the cross-rank protocols where only
+// one GPU is available: the kernels of all "ranks" run as one cooperative
+// launch (grid = CTAs per rank x ranks, rank = blockIdx.y), so that their CTAs
+// are resident together and can wait for one another, which separate launches
+// on one GPU could not guarantee. Every rank's context points at that rank's
+// slice of one device allocation (staging, flags); `ranks` is an array of
+// `world` entries in device memory. One-shot and two-shot only (multimem
+// needs a multicast object over several GPUs).
+struct EmuAllreduceRank {
+  TensorList tl;  // arrays in device memory
+  SymmCtx ctx;
+};
+cudaError_t LaunchFusedAllreduceEmulated(const EmuAllreduceRank* ranks, int world,
+                                         DataType dtype, DataType wire, double prescale,
+                                         double postscale, Algo algo, int num_ctas,
+                                         cudaStream_t stream);
+
 // In-place allreduce (sum, then scale) of byte ranges of the symmetric arena:
 // range i covers bytes [byte_off[i], byte_off[i] + bytes[i]) of every rank's
 // arena (offsets from the arena base, 16-byte aligned starts); vec_start is
@@ -185,6 +202,18 @@ struct RsPushArgs {
 cudaError_t LaunchReducescatterPush(const void* in, void* out, const RsPushArgs& args,
                                     DataType dtype, double prescale, double postscale,
                                     int num_ctas, const SymmCtx& ctx, cudaStream_t stream);
+
+// Several ranks on one GPU (see EmuAllreduceRank). Every rank needs its own
+// done_counter word.
+struct EmuRsPushRank {
+  const void* in;
+  void* out;
+  RsPushArgs args;
+  SymmCtx ctx;
+};
+cudaError_t LaunchReducescatterPushEmulated(const EmuRsPushRank* ranks, int world,
+                                            DataType dtype, double prescale, double postscale,
+                                            int num_ctas, cudaStream_t stream);
 
 // The same for several tensors of one dtype in one launch (a fused
 // reducescatter response): the whole shard of every tensor must fit a sender
@@ -384,6 +413,16 @@ uint64_t KernelLaunchCount();
 void CountKernelLaunches(int n);
 
 // Test hook: a kernel that runs one cross-GPU barrier and nothing else.
+// Several ranks on one GPU (see EmuAllreduceRank): the plan arrays live in
+// device memory; every rank needs its own done_counter word.
+struct EmuExchangeRank {
+  ExchangePlan plan;
+  ExchangeSync sync;
+  SymmCtx ctx;
+};
+cudaError_t LaunchExchangeEmulated(const EmuExchangeRank* ranks, int world, int num_ctas,
+                                   cudaStream_t stream);
+
 // Tells every peer that this rank no longer reads the exchange region of
 // launch number `value` (the word the exchange kernel's credit wait polls).
 // For rounds whose transfers are copy-engine copies queued on the stream

@@ -48,16 +48,19 @@ union Idx8 {
   unsigned char e[8];
 };
 
-template <typename T>
+// I: type of the flat vector index. Tensors of fewer than 2^31 vectors (every
+// practical activation) use 32-bit index arithmetic: the three divisions per
+// thread cost several times the pooling itself when done in 64 bits.
+template <typename T, typename I>
 __global__ void __launch_bounds__(256)
 maxpool3s2_forward_kernel(const T* __restrict__ x, T* __restrict__ y,
                           unsigned char* __restrict__ idx, int N, int H, int W, int C8, int Ho,
                           int Wo) {
-  const long long total = static_cast<long long>(N) * Ho * Wo * C8;
-  for (long long t = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; t < total;
-       t += static_cast<long long>(gridDim.x) * blockDim.x) {
+  const I total = static_cast<I>(N) * Ho * Wo * C8;
+  for (I t = blockIdx.x * static_cast<I>(blockDim.x) + threadIdx.x; t < total;
+       t += static_cast<I>(gridDim.x) * blockDim.x) {
     const int c8 = static_cast<int>(t % C8);
-    long long r = t / C8;
+    I r = t / C8;
     const int ow = static_cast<int>(r % Wo);
     r /= Wo;
     const int oh = static_cast<int>(r % Ho);
@@ -78,7 +81,7 @@ maxpool3s2_forward_kernel(const T* __restrict__ x, T* __restrict__ y,
         if (w < 0 || w >= W) continue;
         Vec8<T> v;
         v.raw = __ldg(reinterpret_cast<const uint4*>(x) +
-                      ((static_cast<long long>(n) * H + h) * W + w) * C8 + c8);
+                      ((static_cast<I>(n) * H + h) * W + w) * C8 + c8);
         const unsigned char pos = static_cast<unsigned char>(kh * 3 + kw);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -105,15 +108,15 @@ maxpool3s2_forward_kernel(const T* __restrict__ x, T* __restrict__ y,
   }
 }
 
-template <typename T>
+template <typename T, typename I>
 __global__ void __launch_bounds__(256)
 maxpool3s2_backward_kernel(const T* __restrict__ dy, const unsigned char* __restrict__ idx,
                            T* __restrict__ dx, int N, int H, int W, int C8, int Ho, int Wo) {
-  const long long total = static_cast<long long>(N) * H * W * C8;
-  for (long long t = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; t < total;
-       t += static_cast<long long>(gridDim.x) * blockDim.x) {
+  const I total = static_cast<I>(N) * H * W * C8;
+  for (I t = blockIdx.x * static_cast<I>(blockDim.x) + threadIdx.x; t < total;
+       t += static_cast<I>(gridDim.x) * blockDim.x) {
     const int c8 = static_cast<int>(t % C8);
-    long long r = t / C8;
+    I r = t / C8;
     const int w = static_cast<int>(r % W);
     r /= W;
     const int h = static_cast<int>(r % H);
@@ -130,7 +133,7 @@ maxpool3s2_backward_kernel(const T* __restrict__ dy, const unsigned char* __rest
         if (ow >= Wo) continue;
         const unsigned char pos =
             static_cast<unsigned char>((h - (oh * 2 - 1)) * 3 + (w - (ow * 2 - 1)));
-        const long long o = ((static_cast<long long>(n) * Ho + oh) * Wo + ow) * C8 + c8;
+        const I o = ((static_cast<I>(n) * Ho + oh) * Wo + ow) * C8 + c8;
         Idx8 oi;
         oi.raw = __ldg(reinterpret_cast<const uint2*>(idx) + o);
         Vec8<T> g;
@@ -152,6 +155,12 @@ int GridFor(long long total) {
   return static_cast<int>(blocks < 148 * 32 ? (blocks < 1 ? 1 : blocks) : 148 * 32);
 }
 
+// Whether every vector index of the larger tensor, plus one grid stride, fits
+// a 32-bit int.
+bool Fits32(long long input_vectors) {
+  return input_vectors + 148LL * 32 * 256 < (1LL << 31);
+}
+
 }  // namespace
 
 bool MaxPool3s2Supported(int channels) { return channels > 0 && channels % 8 == 0; }
@@ -163,14 +172,16 @@ cudaError_t LaunchMaxPool3s2Forward(const void* x, void* y, unsigned char* idx, 
   const long long total = static_cast<long long>(n) * ho * wo * (channels / 8);
   if (total == 0) return cudaSuccess;
   CountKernelLaunches(1);
-  if (bf16)
-    maxpool3s2_forward_kernel<__nv_bfloat16><<<GridFor(total), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), idx, n, h, w,
-        channels / 8, ho, wo);
-  else
-    maxpool3s2_forward_kernel<__half><<<GridFor(total), 256, 0, stream>>>(
-        static_cast<const __half*>(x), static_cast<__half*>(y), idx, n, h, w, channels / 8, ho,
-        wo);
+  const bool small = Fits32(static_cast<long long>(n) * h * w * (channels / 8));
+#define HVD_POOL_FWD(T, I)                                                                   \
+  maxpool3s2_forward_kernel<T, I><<<GridFor(total), 256, 0, stream>>>(                       \
+      static_cast<const T*>(x), static_cast<T*>(y), idx, n, h, w, channels / 8, ho, wo)
+  if (bf16) {
+    if (small) HVD_POOL_FWD(__nv_bfloat16, int); else HVD_POOL_FWD(__nv_bfloat16, long long);
+  } else {
+    if (small) HVD_POOL_FWD(__half, int); else HVD_POOL_FWD(__half, long long);
+  }
+#undef HVD_POOL_FWD
   return cudaGetLastError();
 }
 
@@ -182,14 +193,16 @@ cudaError_t LaunchMaxPool3s2Backward(const void* dy, const unsigned char* idx, v
   const long long total = static_cast<long long>(n) * h * w * (channels / 8);
   if (total == 0) return cudaSuccess;
   CountKernelLaunches(1);
-  if (bf16)
-    maxpool3s2_backward_kernel<__nv_bfloat16><<<GridFor(total), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(dy), idx, static_cast<__nv_bfloat16*>(dx), n, h, w,
-        channels / 8, ho, wo);
-  else
-    maxpool3s2_backward_kernel<__half><<<GridFor(total), 256, 0, stream>>>(
-        static_cast<const __half*>(dy), idx, static_cast<__half*>(dx), n, h, w, channels / 8, ho,
-        wo);
+  const bool small = Fits32(total);
+#define HVD_POOL_BWD(T, I)                                                                   \
+  maxpool3s2_backward_kernel<T, I><<<GridFor(total), 256, 0, stream>>>(                      \
+      static_cast<const T*>(dy), idx, static_cast<T*>(dx), n, h, w, channels / 8, ho, wo)
+  if (bf16) {
+    if (small) HVD_POOL_BWD(__nv_bfloat16, int); else HVD_POOL_BWD(__nv_bfloat16, long long);
+  } else {
+    if (small) HVD_POOL_BWD(__half, int); else HVD_POOL_BWD(__half, long long);
+  }
+#undef HVD_POOL_BWD
   return cudaGetLastError();
 }
 

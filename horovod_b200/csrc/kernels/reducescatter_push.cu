@@ -151,10 +151,11 @@ __device__ __forceinline__ void send_range(const T* base, int64_t n, int64_t v0,
 }
 
 template <typename T>
-__global__ void __launch_bounds__(THREADS, 2)
-reducescatter_push_kernel(const T* in, T* out, const RsPushArgs args, SymmCtx ctx,
-                          typename ScaleT<T>::type prescale,
-                          typename ScaleT<T>::type postscale) {
+__device__ __forceinline__ void reducescatter_push_body(const T* in, T* out,
+                                                        const RsPushArgs& args,
+                                                        const SymmCtx& ctx,
+                                                        typename ScaleT<T>::type prescale,
+                                                        typename ScaleT<T>::type postscale) {
   using S = typename ScaleT<T>::type;
   constexpr int N = 16 / sizeof(T);
   const int world = ctx.world, rank = ctx.rank;
@@ -276,6 +277,26 @@ reducescatter_push_kernel(const T* in, T* out, const RsPushArgs args, SymmCtx ct
       st_release_sys(ctx.flags_peers[threadIdx.x] + CREDIT_BANK + rank * SYMM_MAX_BLOCKS,
                      args.credit_post);
   }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS, 2)
+reducescatter_push_kernel(const T* in, T* out, const RsPushArgs args, SymmCtx ctx,
+                          typename ScaleT<T>::type prescale,
+                          typename ScaleT<T>::type postscale) {
+  reducescatter_push_body<T>(in, out, args, ctx, prescale, postscale);
+}
+
+// Several ranks on one GPU (tests): row y of a cooperative launch runs the
+// kernel of rank y (see EmuAllreduceRank).
+template <typename T>
+__global__ void __launch_bounds__(THREADS, 2)
+reducescatter_push_emulated_kernel(const EmuRsPushRank* ranks,
+                                   typename ScaleT<T>::type prescale,
+                                   typename ScaleT<T>::type postscale) {
+  const EmuRsPushRank& r = ranks[blockIdx.y];
+  reducescatter_push_body<T>(static_cast<const T*>(r.in), static_cast<T*>(r.out), r.args, r.ctx,
+                             prescale, postscale);
 }
 
 // Several tensors in one launch. The steps of the launch are the chunks of
@@ -459,6 +480,31 @@ cudaError_t LaunchReducescatterPush(const void* in, void* out, const RsPushArgs&
   default: return cudaErrorInvalidValue;
   }
 #undef HVD_RSP
+}
+
+cudaError_t LaunchReducescatterPushEmulated(const EmuRsPushRank* ranks, int world,
+                                            DataType dtype, double prescale, double postscale,
+                                            int num_ctas, cudaStream_t stream) {
+  if (num_ctas < 1 || num_ctas > SYMM_MAX_BLOCKS || world < 1 || world > SYMM_MAX_RANKS)
+    return cudaErrorInvalidValue;
+  CountKernelLaunches(1);
+  const dim3 grid(num_ctas, world);
+#define HVD_RSE(T)                                                                         \
+  {                                                                                        \
+    typename ScaleT<T>::type pre = static_cast<typename ScaleT<T>::type>(prescale);        \
+    typename ScaleT<T>::type post = static_cast<typename ScaleT<T>::type>(postscale);      \
+    void* args[] = {&ranks, &pre, &post};                                                  \
+    return cudaLaunchCooperativeKernel(                                                    \
+        reinterpret_cast<const void*>(&reducescatter_push_emulated_kernel<T>), grid,       \
+        dim3(THREADS), args, 0, stream);                                                   \
+  }
+  switch (dtype) {
+  case DataType::FLOAT32: HVD_RSE(float)
+  case DataType::BFLOAT16: HVD_RSE(__nv_bfloat16)
+  case DataType::INT32: HVD_RSE(int32_t)
+  default: return cudaErrorInvalidValue;
+  }
+#undef HVD_RSE
 }
 
 cudaError_t LaunchReducescatterPushGroup(const RsGroupArgs& args, DataType dtype, double prescale,

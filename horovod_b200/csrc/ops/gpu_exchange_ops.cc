@@ -7,6 +7,7 @@
 
 #include "../common/logging.h"
 #include "../common/process_set.h"
+#include "exchange_plan.h"
 #include "gpu_internal.h"
 #include "host_trace.h"
 
@@ -76,14 +77,9 @@ void GpuOps::LaunchExchangeKernel(const std::vector<StageSeg>& stage,
   // Larger rounds publish in larger chunks (fewer fences per byte).
   const int64_t chunk = (round_bytes >= (64 << 20) ? std::max<int64_t>(exchange_chunk_bytes_, 1 << 20)
                                                    : exchange_chunk_bytes_) / 256 * 256;
-  std::vector<int64_t> published(set.world, 0);  // chunks per source so far
-  std::vector<int64_t> before(round.size(), 0);  // ... before each block
-  for (size_t i = 0; i < round.size(); ++i) {
-    const int src = round[i].src_rank;
-    before[i] = published[src];
-    published[src] += kern::ExchangeChunkCount(round[i].bytes, ctas, chunk);
-  }
-  const int64_t most = *std::max_element(published.begin(), published.end());
+  const ExchangeRoundSync rsync = ComputeExchangeRoundSync(round, set.world, ctas, chunk);
+  const std::vector<int64_t>& before = rsync.before;
+  const int64_t most = static_cast<int64_t>(rsync.done_epochs) - 1;
   if (most + 1 > (int64_t(1) << 30))
     throw std::runtime_error("exchange round needs too many chunks");
 
@@ -194,6 +190,12 @@ void GpuOps::LaunchExchangeKernel(const std::vector<StageSeg>& stage,
                              cudaGetErrorString(err));
 }
 
+namespace {
+int64_t ExchangeRegionBytes(const SymmSet& set) {
+  return set.xchg_bytes > 0 ? set.xchg_bytes : static_cast<int64_t>(set.data_bytes);
+}
+}  // namespace
+
 bool GpuOps::ExchangePushes(const SymmSet& set, int64_t total_bytes) const {
   // Writing into other ranks' regions is only safe for the credit-guarded
   // regions of the global set: nothing else ever touches those. Measured on
@@ -215,118 +217,10 @@ bool GpuOps::ExchangeUsesCopyEngine(const SymmSet& set, int64_t total_bytes, int
          total_bytes >= exchange_ce_min_ && smallest >= (256 << 10) && remote_blocks <= 256;
 }
 
-// Every rank builds the same global list of "blocks" (source rank, bytes,
-// who receives it). A block that somebody else needs is staged in its source
-// rank's exchange region; blocks are laid out there in order and processed in
-// rounds that fit the region. A block larger than half the region is cut into
-// parts first. All of this is deterministic, so the ranks agree on rounds and
-// offsets without talking.
-namespace {
-struct Block {
-  int src_rank;        // set rank that owns the data
-  int dst_rank;        // receiving set rank, or -1 for everybody
-  const char* src;     // valid on src_rank only
-  char* dst;           // where this rank wants the data (null = not wanted)
-  int64_t bytes;
-};
-}  // namespace
-
-// push: staged blocks are written into the receivers' regions (one layout
-// shared by all regions) instead of the sender's own.
-static void RunBlocks(std::vector<Block>& blocks, SymmSet& set, bool push,
-                      const std::function<void(const std::vector<GpuOps::StageSeg>&,
-                                               const std::vector<GpuOps::PullSeg>&,
-                                               int64_t,
-                                               const std::vector<GpuOps::RoundBlock>&)>& launch) {
-  const int64_t cap = set.xchg_bytes > 0 ? set.xchg_bytes : static_cast<int64_t>(set.data_bytes);
-  const int me = set.rank;
-  // When the staged data of a source (pulling) or of everybody (pushing) does
-  // not fit the region, every block is cut into the same number of slices and
-  // the rounds go slice by slice: round k moves slice k of every block, so
-  // every rank is busy in every round and all NVLink links stay in use.
-  // Pulling fills the source's region; pushing fills the receiver's region
-  // (every region, for a block that goes to everybody).
-  std::vector<int64_t> staged(set.world, 0);
-  for (auto& b : blocks) {
-    const bool remote = set.world > 1 && (b.dst_rank < 0 || b.dst_rank != b.src_rank);
-    if (!remote) continue;
-    const int64_t need = RoundUp(b.bytes, STAGING_ALIGN) + STAGING_ALIGN;
-    if (!push) {
-      staged[b.src_rank] += need;
-    } else if (b.dst_rank >= 0) {
-      staged[b.dst_rank] += need;
-    } else {
-      for (auto& s : staged) s += need;
-    }
-  }
-  const int64_t most = *std::max_element(staged.begin(), staged.end());
-  const int64_t slices = std::max<int64_t>(1, (most + cap - 1) / cap);
-  std::vector<Block> parts;
-  for (int64_t k = 0; k < slices; ++k) {
-    for (auto& b : blocks) {
-      if (b.bytes == 0) continue;
-      const int64_t per = RoundUp((b.bytes + slices - 1) / slices, STAGING_ALIGN);
-      const int64_t pos = k * per;
-      if (pos >= b.bytes) continue;
-      Block p = b;
-      p.src = b.src ? b.src + pos : nullptr;
-      p.dst = b.dst ? b.dst + pos : nullptr;
-      p.bytes = std::min(per, b.bytes - pos);
-      parts.push_back(p);
-    }
-  }
-  size_t next = 0;
-  while (next < parts.size()) {
-    std::vector<GpuOps::StageSeg> stage;
-    std::vector<GpuOps::PullSeg> pull;
-    // One cursor per region. Pulling: a block sits in its source's region.
-    // Pushing: in its receiver's region, or, when it goes to everybody, at
-    // one offset that is free in every region.
-    std::vector<int64_t> cursor(set.world, 0);
-    size_t n = 0;
-    int64_t round_bytes = 0;
-    std::vector<GpuOps::RoundBlock> round;
-    while (next + n < parts.size() && n < 4096) {
-      const Block& b = parts[next + n];
-      const bool remote = set.world > 1 && (b.dst_rank < 0 || b.dst_rank != b.src_rank);
-      const bool wanted = (b.dst_rank < 0 || b.dst_rank == me) && b.dst != nullptr;
-      if (!remote) {
-        // Data a rank keeps for itself: a local copy, no region space.
-        if (b.src_rank == me && wanted) stage.push_back({b.src, b.dst, -1, b.bytes, -2});
-      } else {
-        const int64_t padded = RoundUp(b.bytes, STAGING_ALIGN);
-        const bool everywhere = push && b.dst_rank < 0;
-        const int region = push ? b.dst_rank : b.src_rank;
-        const int64_t off = everywhere ? *std::max_element(cursor.begin(), cursor.end())
-                                       : cursor[region];
-        if (off + padded > cap) break;
-        if (everywhere) {
-          std::fill(cursor.begin(), cursor.end(), off + padded);
-        } else {
-          cursor[region] = off + padded;
-        }
-        if (b.src_rank == me) {
-          stage.push_back({b.src, wanted ? b.dst : nullptr, off, b.bytes,
-                           push ? b.dst_rank : -2});
-        } else if (wanted) {
-          pull.push_back({b.dst, off, b.bytes, push ? me : b.src_rank, b.src_rank,
-                          static_cast<int32_t>(round.size())});
-        }
-        round.push_back({b.src_rank, b.bytes});
-      }
-      round_bytes += b.bytes;
-      ++n;
-    }
-    if (n == 0) throw std::runtime_error("exchange block exceeds staging capacity");
-    launch(stage, pull, round_bytes, round);
-    next += n;
-  }
-}
-
 namespace {
 // Totals over the blocks that cross NVLink (the same on every rank).
 struct RemoteStats { int64_t total = 0, smallest = 0; size_t count = 0; };
-RemoteStats RemoteBlockStats(const std::vector<Block>& blocks, int world) {
+RemoteStats RemoteBlockStats(const std::vector<ExchangeBlock>& blocks, int world) {
   RemoteStats st;
   for (auto& b : blocks) {
     st.total += b.bytes;
@@ -345,9 +239,9 @@ Status GpuOps::SymmBroadcast(std::vector<TensorTableEntry>& entries,
   WaitForInputs(entries);
   host_trace::Mark("inputs");
   ActStart(entries, HVD_ACT_FUSED_KERNEL);
-  std::vector<Block> blocks;
+  std::vector<ExchangeBlock> blocks;
   for (auto& e : entries) {
-    Block b;
+    ExchangeBlock b;
     b.src_rank = e.root_rank;
     b.dst_rank = -1;
     b.src = static_cast<const char*>(e.input);
@@ -368,7 +262,7 @@ Status GpuOps::SymmBroadcast(std::vector<TensorTableEntry>& entries,
   // (A pulled broadcast would cost the root N-1 times the message on its
   // NVLink egress, so the copy engines only serve the two-rank case.)
   const bool ce = !push && ExchangeUsesCopyEngine(set, rs.total, rs.smallest, rs.count);
-  RunBlocks(blocks, set, push,
+  PlanExchangeRounds(blocks, set.rank, set.world, ExchangeRegionBytes(set), push,
             [&](const std::vector<StageSeg>& o, const std::vector<PullSeg>& i,
                 int64_t round_bytes, const std::vector<RoundBlock>& round) {
               LaunchExchangeSegments(o, i, set, round_bytes, round, ce);
@@ -383,7 +277,7 @@ Status GpuOps::SymmAllgather(std::vector<TensorTableEntry>& entries,
   const int n = set.world;
   WaitForInputs(entries);
   host_trace::Mark("inputs");
-  std::vector<Block> blocks;
+  std::vector<ExchangeBlock> blocks;
   for (size_t i = 0; i < entries.size(); ++i) {
     TensorTableEntry& e = entries[i];
     int64_t slice = static_cast<int64_t>(DataTypeSize(e.dtype));
@@ -400,7 +294,7 @@ Status GpuOps::SymmAllgather(std::vector<TensorTableEntry>& entries,
     e.output = out;
     int64_t disp = 0;
     for (int r = 0; r < n; ++r) {
-      Block b;
+      ExchangeBlock b;
       b.src_rank = r;
       b.dst_rank = -1;
       b.src = r == set.rank ? static_cast<const char*>(e.input) : nullptr;
@@ -414,7 +308,8 @@ Status GpuOps::SymmAllgather(std::vector<TensorTableEntry>& entries,
   ActStart(entries, HVD_ACT_FUSED_KERNEL);
   const RemoteStats rs = RemoteBlockStats(blocks, set.world);
   const bool ce = ExchangeUsesCopyEngine(set, rs.total, rs.smallest, rs.count);
-  RunBlocks(blocks, set, !ce && ExchangePushes(set, rs.total),
+  PlanExchangeRounds(blocks, set.rank, set.world, ExchangeRegionBytes(set),
+                     !ce && ExchangePushes(set, rs.total),
             [&](const std::vector<StageSeg>& o, const std::vector<PullSeg>& i,
                 int64_t round_bytes, const std::vector<RoundBlock>& round) {
               LaunchExchangeSegments(o, i, set, round_bytes, round, ce);
@@ -428,7 +323,7 @@ Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries,
   Timeline& tl = state_.timeline;
   const int n = set.world, me = set.rank;
   WaitForInputs(entries);
-  std::vector<Block> blocks;
+  std::vector<ExchangeBlock> blocks;
   for (auto& e : entries) {
     int64_t slice = static_cast<int64_t>(DataTypeSize(e.dtype));
     for (int d = 1; d < e.shape.dims(); ++d) slice *= e.shape.dim_size(d);
@@ -463,7 +358,7 @@ Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries,
       // target of one sender instead of everybody writing to rank 0 first.
       for (int j = 1; j <= n; ++j) {
         const int p = (r + j) % n;
-        Block b;
+        ExchangeBlock b;
         b.src_rank = r;
         b.dst_rank = p;
         b.bytes = static_cast<int64_t>(all[r * n + p]) * slice;
@@ -476,7 +371,8 @@ Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries,
   ActStart(entries, HVD_ACT_FUSED_KERNEL);
   const RemoteStats rs = RemoteBlockStats(blocks, set.world);
   const bool ce = ExchangeUsesCopyEngine(set, rs.total, rs.smallest, rs.count);
-  RunBlocks(blocks, set, !ce && ExchangePushes(set, rs.total),
+  PlanExchangeRounds(blocks, set.rank, set.world, ExchangeRegionBytes(set),
+                     !ce && ExchangePushes(set, rs.total),
             [&](const std::vector<StageSeg>& o, const std::vector<PullSeg>& i,
                 int64_t round_bytes, const std::vector<RoundBlock>& round) {
               LaunchExchangeSegments(o, i, set, round_bytes, round, ce);

@@ -18,6 +18,7 @@
 #include "../kernels/kernels.h"
 #include "../symm/symm_arena.h"
 #include "op_executor.h"
+#include "exchange_plan.h"
 
 namespace hvd {
 
@@ -127,19 +128,10 @@ public:
                  const Response& response, ProcessSet& ps) override;
   void Shutdown() override;
 
-  // Segments handed to the exchange kernel (see kern::ExchangePlan).
-  struct StageSeg { const void* src; void* self_dst; int64_t off; int64_t bytes; int32_t dst; };
-  struct PullSeg {
-    void* dst;
-    int64_t off;
-    int64_t bytes;
-    int32_t src_rank;  // set rank whose region holds the data
-    int32_t sig_rank;  // set rank whose progress counter announces it
-    int32_t block;     // index into the round's block list (RoundBlock)
-  };
-  // Every staged block of one exchange round, in the order all ranks process
-  // them (what the chunk counters of the kernel are derived from).
-  struct RoundBlock { int32_t src_rank; int64_t bytes; };
+  // Segments handed to the exchange kernel (see exchange_plan.h).
+  using StageSeg = ExchangeStageSeg;
+  using PullSeg = ExchangePullSeg;
+  using RoundBlock = ExchangeRoundBlock;
 
   // Device-time record of one executed response (HOROVOD_GPU_OP_TIMING=1).
   struct OpTiming {

@@ -33,6 +33,7 @@ void BindGpuDiagnostics(py::module_& m);
 // Defined in binding_testing.cpp.
 void BindTesting(py::module_& m);
 void BindModelOps(py::module_& m);
+void BindEmulation(py::module_& m);
 
 namespace {
 
@@ -655,4 +656,5 @@ PYBIND11_MODULE(_C, m) {
   BindGpuDiagnostics(m);
   BindTesting(m);
   BindModelOps(m);
+  BindEmulation(m);
 }

@@ -19,7 +19,9 @@
 #include "../common/response_cache.h"
 #include "../common/stall_inspector.h"
 #include "../common/tensor_queue.h"
+#include "../kernels/kernels.h"
 #include "../ops/cpu_ops.h"
+#include "../ops/exchange_plan.h"
 #include "../transport/mesh.h"
 
 namespace py = pybind11;
@@ -161,6 +163,43 @@ void BindTesting(py::module_& root) {
     std::vector<std::vector<std::string>> groups;
     for (auto& r : out.responses) groups.push_back(r.names);
     return groups;
+  });
+  // The exchange planner on plain numbers: blocks are (src_rank, dst_rank,
+  // src address or 0, dst address or 0, bytes) as rank `rank` sees them;
+  // returns one entry per round: (stage segments (src, self_dst, off, bytes,
+  // dst), pull segments (dst, off, bytes, src_rank, sig_rank, chunks published
+  // before), round_bytes, epochs). Addresses are opaque integers here, so a
+  // test can replay the copies on arrays of its own.
+  m.def("plan_exchange", [](const std::vector<std::tuple<int, int, uint64_t, uint64_t, int64_t>>&
+                                blocks,
+                            int rank, int world, int64_t region_bytes, bool push, int ctas,
+                            int64_t chunk_bytes) {
+    std::vector<ExchangeBlock> bl;
+    for (auto& b : blocks) {
+      ExchangeBlock e;
+      e.src_rank = std::get<0>(b);
+      e.dst_rank = std::get<1>(b);
+      e.src = reinterpret_cast<const char*>(static_cast<uintptr_t>(std::get<2>(b)));
+      e.dst = reinterpret_cast<char*>(static_cast<uintptr_t>(std::get<3>(b)));
+      e.bytes = std::get<4>(b);
+      bl.push_back(e);
+    }
+    py::list rounds;
+    PlanExchangeRounds(bl, rank, world, region_bytes, push,
+                       [&](const std::vector<ExchangeStageSeg>& stage,
+                           const std::vector<ExchangePullSeg>& pull, int64_t round_bytes,
+                           const std::vector<ExchangeRoundBlock>& round) {
+      const ExchangeRoundSync rs = ComputeExchangeRoundSync(round, world, ctas, chunk_bytes);
+      py::list st, pl;
+      for (auto& g : stage)
+        st.append(py::make_tuple(reinterpret_cast<uintptr_t>(g.src),
+                                 reinterpret_cast<uintptr_t>(g.self_dst), g.off, g.bytes, g.dst));
+      for (auto& g : pull)
+        pl.append(py::make_tuple(reinterpret_cast<uintptr_t>(g.dst), g.off, g.bytes, g.src_rank,
+                                 g.sig_rank, rs.before[g.block]));
+      rounds.append(py::make_tuple(st, pl, round_bytes, rs.done_epochs));
+    });
+    return rounds;
   });
   m.def("wire_parse_garbage", [](py::bytes data) {
     std::string s = data;

@@ -68,6 +68,13 @@ struct GlobalState {
   // Requests from API threads handled on the background thread.
   std::mutex ctl_mu;
   std::condition_variable ctl_cv;
+  // Threads blocked in synchronize() on an op that has not been executed yet.
+  // While there are any, the background loop does not sleep out its cycle
+  // time: what the caller waits for is negotiated at once (HOROVOD_FLUSH_ON_WAIT).
+  std::atomic<int> sync_waiters{0};
+  std::mutex wake_mu;
+  std::condition_variable wake_cv;
+  bool flush_on_wait = true;
   std::string pending_timeline_file;   // non-empty: start; with stop flag: stop
   bool pending_timeline_start = false;
   bool pending_timeline_stop = false;

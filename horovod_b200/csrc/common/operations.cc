@@ -130,7 +130,23 @@ bool RunLoopOnce(GlobalState& s,
   auto next = last_cycle +
               std::chrono::duration_cast<std::chrono::steady_clock::duration>(cycle);
   auto now = std::chrono::steady_clock::now();
-  if (next > now) std::this_thread::sleep_until(next);
+  if (next > now) {
+    if (s.flush_on_wait) {
+      // Sleep out the cycle unless somebody blocks in synchronize(): then the
+      // next negotiation starts at once (after a short pause, so that a long
+      // wait does not turn into a busy loop of control-plane rounds). The
+      // cycle time exists to batch tensors for fusion; a caller that is
+      // already waiting has nothing more to add to the batch.
+      const auto floor = last_cycle + std::chrono::microseconds(50);
+      std::unique_lock<std::mutex> l(s.wake_mu);
+      s.wake_cv.wait_until(l, next, [&s] { return s.sync_waiters.load() > 0; });
+      l.unlock();
+      now = std::chrono::steady_clock::now();
+      if (now < floor) std::this_thread::sleep_until(floor);
+    } else {
+      std::this_thread::sleep_until(next);
+    }
+  }
   last_cycle = std::chrono::steady_clock::now();
 
   {
@@ -217,6 +233,7 @@ void BackgroundThreadLoop(GlobalState& s) {
     pm.SetTensorFusionThresholdBytes(
         EnvInt(HVD_ENV_FUSION_THRESHOLD, 128ll * 1024 * 1024),
         EnvIsSet(HVD_ENV_FUSION_THRESHOLD));
+    s.flush_on_wait = EnvBool("HOROVOD_FLUSH_ON_WAIT", true);
     pm.SetCycleTimeMs(EnvDouble(HVD_ENV_CYCLE_TIME, 1.0),
                       EnvIsSet(HVD_ENV_CYCLE_TIME));
     uint32_t cache_capacity =
@@ -361,6 +378,17 @@ void hvd_shutdown() {
   s.initialization_done = false;
   s.process_sets.Clear();
 }
+
+void hvd_waiter_enter() {
+  GlobalState& s = g_state;
+  {
+    std::lock_guard<std::mutex> l(s.wake_mu);
+    s.sync_waiters.fetch_add(1);
+  }
+  s.wake_cv.notify_all();
+}
+
+void hvd_waiter_exit() { g_state.sync_waiters.fetch_sub(1); }
 
 bool hvd_is_initialized() {
   return g_state.initialization_done.load() && !g_state.loop_exited.load();

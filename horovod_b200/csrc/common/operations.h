@@ -25,6 +25,10 @@ std::string hvd_listen(const std::string& advertise_host);
 // hvd_shutdown() starts a fresh runtime (elastic reset).
 void hvd_init(const InitConfig& cfg);
 void hvd_shutdown();
+// A thread starts / stops waiting for an op that the background loop has not
+// executed yet (see GlobalState::sync_waiters).
+void hvd_waiter_enter();
+void hvd_waiter_exit();
 bool hvd_is_initialized();
 bool hvd_has_topology();
 

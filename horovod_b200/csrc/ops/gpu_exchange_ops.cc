@@ -209,12 +209,19 @@ bool GpuOps::ExchangePushes(const SymmSet& set, int64_t total_bytes) const {
 }
 
 bool GpuOps::ExchangeUsesCopyEngine(const SymmSet& set, int64_t total_bytes, int64_t smallest,
-                                    size_t remote_blocks) const {
-  // SM-driven NVLink traffic measured 430-530 GB/s per direction on B200 (this
-  // kernel and NCCL alike); copy-engine peer copies reach 770 GB/s. Worth the
-  // extra local staging pass and barrier for large blocks only.
-  return set.world > 1 && set.xchg_bytes > 0 && exchange_ce_min_ > 0 &&
-         total_bytes >= exchange_ce_min_ && smallest >= (256 << 10) && remote_blocks <= 256;
+                                    size_t remote_blocks, bool allgather) const {
+  // A copy-engine peer copy reaches 750-765 GB/s per direction on B200;
+  // SM-driven NVLink traffic (this kernel and NCCL alike) 430-530 GB/s. But
+  // staging, barrier and copies run one after the other, so the copy engines
+  // only win where the kernel is furthest from the link rate: measured at 4
+  // ranks, allgather 256 MB 385 us (kernel 463, NCCL path 394), 1 GB 1358 us
+  // (1851, 1413); at 64 MB and for every alltoall size the kernel is faster,
+  // and at 2 ranks the two tie. HOROVOD_EXCHANGE_COPY_ENGINE_MIN_BYTES
+  // overrides for all exchange ops (0 = never).
+  if (set.world <= 1 || set.xchg_bytes <= 0 || smallest < (256 << 10) || remote_blocks > 256)
+    return false;
+  if (exchange_ce_min_ >= 0) return exchange_ce_min_ > 0 && total_bytes >= exchange_ce_min_;
+  return allgather && set.world >= 3 && total_bytes >= (int64_t(128) << 20);
 }
 
 namespace {
@@ -261,7 +268,7 @@ Status GpuOps::SymmBroadcast(std::vector<TensorTableEntry>& entries,
                     (set.mc != nullptr && set.world >= 3 && set.xchg_bytes > 0);
   // (A pulled broadcast would cost the root N-1 times the message on its
   // NVLink egress, so the copy engines only serve the two-rank case.)
-  const bool ce = !push && ExchangeUsesCopyEngine(set, rs.total, rs.smallest, rs.count);
+  const bool ce = !push && ExchangeUsesCopyEngine(set, rs.total, rs.smallest, rs.count, false);
   PlanExchangeRounds(blocks, set.rank, set.world, ExchangeRegionBytes(set), push,
             [&](const std::vector<StageSeg>& o, const std::vector<PullSeg>& i,
                 int64_t round_bytes, const std::vector<RoundBlock>& round) {
@@ -307,7 +314,7 @@ Status GpuOps::SymmAllgather(std::vector<TensorTableEntry>& entries,
   host_trace::Mark("outputs");
   ActStart(entries, HVD_ACT_FUSED_KERNEL);
   const RemoteStats rs = RemoteBlockStats(blocks, set.world);
-  const bool ce = ExchangeUsesCopyEngine(set, rs.total, rs.smallest, rs.count);
+  const bool ce = ExchangeUsesCopyEngine(set, rs.total, rs.smallest, rs.count, true);
   PlanExchangeRounds(blocks, set.rank, set.world, ExchangeRegionBytes(set),
                      !ce && ExchangePushes(set, rs.total),
             [&](const std::vector<StageSeg>& o, const std::vector<PullSeg>& i,
@@ -370,7 +377,7 @@ Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries,
   }
   ActStart(entries, HVD_ACT_FUSED_KERNEL);
   const RemoteStats rs = RemoteBlockStats(blocks, set.world);
-  const bool ce = ExchangeUsesCopyEngine(set, rs.total, rs.smallest, rs.count);
+  const bool ce = ExchangeUsesCopyEngine(set, rs.total, rs.smallest, rs.count, false);
   PlanExchangeRounds(blocks, set.rank, set.world, ExchangeRegionBytes(set),
                      !ce && ExchangePushes(set, rs.total),
             [&](const std::vector<StageSeg>& o, const std::vector<PullSeg>& i,

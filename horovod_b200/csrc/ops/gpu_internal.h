@@ -218,7 +218,7 @@ private:
   // `smallest` bytes each moves its data across NVLink with copy-engine
   // copies (stage locally, barrier, one peer copy per block).
   bool ExchangeUsesCopyEngine(const SymmSet& set, int64_t total_bytes, int64_t smallest,
-                              size_t remote_blocks) const;
+                              size_t remote_blocks, bool allgather) const;
 
   GlobalState& state_;
   int slot_ = 0;
@@ -249,7 +249,7 @@ private:
   int64_t dynamic_min_bytes_ = 0;
   int64_t exchange_chunk_bytes_ = 256 << 10;  // HOROVOD_EXCHANGE_CHUNK_KB
   int64_t exchange_push_max_ = 1 << 20;       // HOROVOD_EXCHANGE_PUSH_MAX_BYTES
-  int64_t exchange_ce_min_ = 0;               // HOROVOD_EXCHANGE_COPY_ENGINE_MIN_BYTES (0 = never)
+  int64_t exchange_ce_min_ = -1;              // HOROVOD_EXCHANGE_COPY_ENGINE_MIN_BYTES (-1 = by op and size)
   int64_t allreduce_subchunk_bytes_ = 64 << 10;  // HOROVOD_ALLREDUCE_SUBCHUNK_KB, 0 = off
   int64_t allreduce_pipeline_min_ = 8 << 20;     // HOROVOD_ALLREDUCE_PIPELINE_MIN_BYTES
   unsigned long long* xchg_done_counter_ = nullptr;  // device word, see kern::ExchangeSync

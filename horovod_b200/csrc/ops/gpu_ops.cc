@@ -254,7 +254,7 @@ void GpuOps::EnsureDevice(int device) {
   exchange_chunk_bytes_ =
       std::max<int64_t>(64, EnvInt("HOROVOD_EXCHANGE_CHUNK_KB", 256)) << 10;
   exchange_push_max_ = EnvInt("HOROVOD_EXCHANGE_PUSH_MAX_BYTES", 1 << 20);
-  exchange_ce_min_ = EnvInt("HOROVOD_EXCHANGE_COPY_ENGINE_MIN_BYTES", 0);
+  exchange_ce_min_ = EnvInt("HOROVOD_EXCHANGE_COPY_ENGINE_MIN_BYTES", -1);
   allreduce_pipeline_min_ = EnvInt("HOROVOD_ALLREDUCE_PIPELINE_MIN_BYTES", 8 << 20);
   allreduce_subchunk_bytes_ =
       std::max<int64_t>(0, EnvInt("HOROVOD_ALLREDUCE_SUBCHUNK_KB", 64)) * 1024 / 256 * 256;

@@ -540,7 +540,13 @@ py::tuple WaitAndClear(int handle) {
   {
     py::gil_scoped_release release;
     std::unique_lock<std::mutex> l(rec->mu);
-    rec->cv.wait(l, [&] { return rec->pending <= 0; });
+    if (rec->pending > 0) {
+      // Tell the background loop that somebody is waiting, so that it
+      // negotiates now instead of sleeping out its cycle.
+      hvd_waiter_enter();
+      rec->cv.wait(l, [&] { return rec->pending <= 0; });
+      hvd_waiter_exit();
+    }
   }
   Handles().Release(handle);
   ThrowIfError(rec->status);

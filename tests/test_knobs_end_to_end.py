@@ -95,3 +95,38 @@ def _no_fusion_no_cache(rank, size, fusion, cache):
 def test_results_do_not_depend_on_fusion_or_cache():
     for fusion, cache in (("0", "1024"), (str(64 << 20), "0"), ("0", "0"), ("64", "2")):
         assert all(run_parallel(_no_fusion_no_cache, np=2, args=(fusion, cache))), (fusion, cache)
+
+
+def _blocking_latency(rank, size, flush):
+    """Ten blocking allreduces under a 100 ms cycle time."""
+    os.environ["HOROVOD_CYCLE_TIME"] = "100"
+    os.environ["HOROVOD_FLUSH_ON_WAIT"] = flush
+    import horovod_b200.torch as hvd
+    hvd.init()
+    hvd.allreduce(torch.ones(2), name="warm")
+    t0 = time.time()
+    ok = True
+    for i in range(10):
+        out = hvd.allreduce(torch.full((4,), float(rank + i)), op=hvd.Sum, name="lat.%d" % i)
+        ok = ok and out.tolist() == [float(sum(r + i for r in range(size)))] * 4
+    # asynchronous ops issued together still travel together (one cycle, fused)
+    hs = [hvd.allreduce_async(torch.ones(3) * (rank + 1), op=hvd.Sum, name="lat.async.%d" % i)
+          for i in range(20)]
+    for h in hs:
+        ok = ok and hvd.synchronize(h).tolist() == [float(size * (size + 1) // 2)] * 3
+    elapsed = time.time() - t0
+    hvd.shutdown()
+    return ok, elapsed
+
+
+def test_a_blocked_caller_does_not_wait_out_the_cycle_time():
+    """synchronize() on an op that has not been negotiated yet makes the
+    background loop negotiate at once instead of sleeping out its cycle
+    (HOROVOD_FLUSH_ON_WAIT, on by default): ten blocking allreduces under a
+    100 ms cycle take far less than ten cycles; with the knob off they take
+    about one cycle each, as in the reference."""
+    fast = run_parallel(_blocking_latency, np=2, args=("1",), timeout=120)
+    slow = run_parallel(_blocking_latency, np=2, args=("0",), timeout=120)
+    assert all(ok for ok, _ in fast) and all(ok for ok, _ in slow)
+    assert max(t for _, t in fast) < 0.5, fast
+    assert min(t for _, t in slow) > 0.7, slow

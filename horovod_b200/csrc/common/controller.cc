@@ -421,7 +421,9 @@ Response Controller::ConstructResponse(const std::string& name,
         }
       }
     }
-    if (!bad && type == Request::ALLGATHER)
+    // First dimension of every rank's tensor, in rank order (for an alltoall:
+    // what even splits are derived from).
+    if (!bad)
       for (auto& q : reqs) tensor_sizes.push_back(q.shape[0]);
   }
   if (!bad && (type == Request::ALLREDUCE || type == Request::ADASUM ||
@@ -478,6 +480,12 @@ Response Controller::ConstructResponse(const std::string& name,
   resp.postscale = first.postscale;
   resp.reduce_op = first.reduce_op;
   resp.root_rank = first.root_rank;
+  if (type == Request::ALLTOALL) {
+    // 1 only when every rank asked for an even split.
+    resp.root_rank = 1;
+    for (auto& q : reqs)
+      if (q.root_rank != 1) resp.root_rank = 0;
+  }
   resp.wire_dtype = (type == Request::ALLREDUCE) ? first.wire_dtype : first.dtype;
   switch (type) {
   case Request::ALLREDUCE: resp.type = Response::ALLREDUCE; break;

@@ -156,4 +156,20 @@ public:
   static ResponseList Parse(const char* data, size_t len);
 };
 
+// An ALLTOALL response whose ranks all left the splits to the library (even
+// split) carries every rank's first dimension, so that every rank knows the
+// whole split table: rank r sends rows[r] rows to each peer. Returns false
+// when the ranks passed explicit splits and have to exchange them.
+inline bool AlltoallEvenRows(const Response& response, int ranks, std::vector<int32_t>* rows) {
+  if (response.type != Response::ALLTOALL || response.root_rank != 1 ||
+      response.names.size() != 1 || static_cast<int>(response.tensor_sizes.size()) != ranks)
+    return false;
+  rows->resize(ranks);
+  for (int r = 0; r < ranks; ++r) {
+    if (response.tensor_sizes[r] % ranks != 0) return false;
+    (*rows)[r] = static_cast<int32_t>(response.tensor_sizes[r] / ranks);
+  }
+  return true;
+}
+
 }  // namespace hvd

@@ -625,6 +625,11 @@ Status EnqueueTensorAlltoall(TensorTableEntry entry, int32_t process_set_id) {
   if (entry.shape.dims() == 0)
     return Status::InvalidArgument("alltoall needs a tensor of rank 1 or more.");
   int64_t rows = entry.shape.dim_size(0);
+  // For an alltoall the root_rank field of the request says whether this rank
+  // left the splits to the library (1: even split). When every rank did, the
+  // response carries every rank's first dimension and nobody has to exchange
+  // split tables before the data.
+  entry.root_rank = entry.splits.empty() ? 1 : 0;
   if (entry.splits.empty()) {
     if (rows % n != 0)
       return Status::InvalidArgument(

@@ -40,7 +40,8 @@ ResponseCache::CacheState ResponseCache::cached(const Request& q) const {
               p.device == q.device && p.prescale == q.prescale &&
               p.postscale == q.postscale && p.reduce_op == q.reduce_op &&
               (q.type != Request::ALLREDUCE || p.wire_dtype == q.wire_dtype) &&
-              (q.type != Request::BROADCAST || p.root_rank == q.root_rank);
+              ((q.type != Request::BROADCAST && q.type != Request::ALLTOALL) ||
+               p.root_rank == q.root_rank);  // alltoall: "even split" flag
   return same ? CacheState::HIT : CacheState::INVALID;
 }
 

@@ -55,7 +55,7 @@ public:
     case Response::ADASUM: return Allreduce(entries, response, ps, true);
     case Response::ALLGATHER: return Allgather(entries, response, ps);
     case Response::BROADCAST: return Broadcast(entries, ps);
-    case Response::ALLTOALL: return Alltoall(entries, ps);
+    case Response::ALLTOALL: return Alltoall(entries, response, ps);
     case Response::REDUCESCATTER: return Reducescatter(entries, ps);
     default:
       return Status::InvalidArgument("hvd: unsupported CPU collective");
@@ -172,7 +172,8 @@ private:
     return Status::OK();
   }
 
-  Status Alltoall(std::vector<TensorTableEntry>& entries, ProcessSet& ps) {
+  Status Alltoall(std::vector<TensorTableEntry>& entries, const Response& response,
+                  ProcessSet& ps) {
     Timeline& tl = state_.timeline;
     const int n = ps.comm.size();
     for (auto& e : entries) {
@@ -181,8 +182,10 @@ private:
       int64_t slice_bytes = slice * static_cast<int64_t>(DataTypeSize(e.dtype));
       // Every rank tells every peer how many rows to expect.
       std::vector<int32_t> recv_splits(n);
-      std::vector<int64_t> four(n, 4);
-      ps.comm.Alltoallv(e.splits.data(), four, recv_splits.data(), four);
+      if (!AlltoallEvenRows(response, n, &recv_splits)) {
+        std::vector<int64_t> four(n, 4);
+        ps.comm.Alltoallv(e.splits.data(), four, recv_splits.data(), four);
+      }
       std::vector<int64_t> send_lens(n), recv_lens(n);
       int64_t rows = 0;
       for (int r = 0; r < n; ++r) {

@@ -325,7 +325,7 @@ Status GpuOps::SymmAllgather(std::vector<TensorTableEntry>& entries,
   return Complete(entries);
 }
 
-Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries,
+Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries, const Response& response,
                             ProcessSet& ps, SymmSet& set) {
   Timeline& tl = state_.timeline;
   const int n = set.world, me = set.rank;
@@ -338,7 +338,15 @@ Status GpuOps::SymmAlltoall(std::vector<TensorTableEntry>& entries,
     // sends to rank p.
     std::vector<int32_t> all(static_cast<size_t>(n) * n);
     host_trace::Mark("inputs");
-    ps.comm.Allgather(e.splits.data(), sizeof(int32_t) * n, all.data());
+    std::vector<int32_t> even;
+    if (AlltoallEvenRows(response, n, &even)) {
+      // Every rank asked for an even split and the response carries every
+      // rank's first dimension: the table is known without an exchange.
+      for (int r = 0; r < n; ++r)
+        for (int p = 0; p < n; ++p) all[r * n + p] = even[r];
+    } else {
+      ps.comm.Allgather(e.splits.data(), sizeof(int32_t) * n, all.data());
+    }
     host_trace::Mark("splits");
     std::vector<int32_t> recv(n);
     int64_t rows = 0;

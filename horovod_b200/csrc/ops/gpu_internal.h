@@ -194,8 +194,8 @@ private:
                                   bool* done);
   Status SymmAllgather(std::vector<TensorTableEntry>& entries,
                        const Response& response, SymmSet& set);
-  Status SymmAlltoall(std::vector<TensorTableEntry>& entries, ProcessSet& ps,
-                      SymmSet& set);
+  Status SymmAlltoall(std::vector<TensorTableEntry>& entries, const Response& response,
+                      ProcessSet& ps, SymmSet& set);
   Status SymmReducescatter(std::vector<TensorTableEntry>& entries,
                            SymmSet& set);
   // Zero-copy path for tensors living in the symmetric heap. Returns false

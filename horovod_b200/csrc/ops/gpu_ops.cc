@@ -666,7 +666,7 @@ Status GpuOps::Execute(std::vector<TensorTableEntry>& entries,
     case Response::ADASUM: return SymmAllreduce(entries, response, *set, true);
     case Response::BROADCAST: return SymmBroadcast(entries, *set);
     case Response::ALLGATHER: return SymmAllgather(entries, response, *set);
-    case Response::ALLTOALL: return SymmAlltoall(entries, ps, *set);
+    case Response::ALLTOALL: return SymmAlltoall(entries, response, ps, *set);
     case Response::REDUCESCATTER: return SymmReducescatter(entries, *set);
     default: break;
     }

@@ -86,8 +86,8 @@ Status NcclOps::Allgather(std::vector<TensorTableEntry>& entries,
   return gpu_.Complete(entries);
 }
 
-Status NcclOps::Alltoall(std::vector<TensorTableEntry>& entries, ProcessSet& ps,
-                         void* comm_v) {
+Status NcclOps::Alltoall(std::vector<TensorTableEntry>& entries, const Response& response,
+                         ProcessSet& ps, void* comm_v) {
   ncclComm_t comm = static_cast<ncclComm_t>(comm_v);
   cudaStream_t stream = gpu_.stream();
   Timeline& tl = gpu_.state().timeline;
@@ -96,8 +96,10 @@ Status NcclOps::Alltoall(std::vector<TensorTableEntry>& entries, ProcessSet& ps,
     int64_t slice = static_cast<int64_t>(DataTypeSize(e.dtype));
     for (int d = 1; d < e.shape.dims(); ++d) slice *= e.shape.dim_size(d);
     std::vector<int32_t> recv(n);
-    std::vector<int64_t> four(n, 4);
-    ps.comm.Alltoallv(e.splits.data(), four, recv.data(), four);
+    if (!AlltoallEvenRows(response, n, &recv)) {
+      std::vector<int64_t> four(n, 4);
+      ps.comm.Alltoallv(e.splits.data(), four, recv.data(), four);
+    }
     int64_t rows = 0;
     for (int r = 0; r < n; ++r) rows += recv[r];
     std::vector<int64_t> dims = e.shape.to_vector();

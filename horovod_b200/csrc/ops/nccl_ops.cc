@@ -165,7 +165,7 @@ Status NcclOps::Execute(std::vector<TensorTableEntry>& entries,
     return Allreduce(entries, response, comm);
   case Response::BROADCAST: return Broadcast(entries, comm);
   case Response::ALLGATHER: return Allgather(entries, response, ps, comm);
-  case Response::ALLTOALL: return Alltoall(entries, ps, comm);
+  case Response::ALLTOALL: return Alltoall(entries, response, ps, comm);
   case Response::REDUCESCATTER: return Reducescatter(entries, ps, comm);
   case Response::ADASUM: {
     // What the reference's GPU Adasum computes when all ranks share a node

@@ -41,7 +41,8 @@ private:
   Status Broadcast(std::vector<TensorTableEntry>& entries, void* comm);
   Status Allgather(std::vector<TensorTableEntry>& entries,
                    const Response& response, ProcessSet& ps, void* comm);
-  Status Alltoall(std::vector<TensorTableEntry>& entries, ProcessSet& ps,
+  Status Alltoall(std::vector<TensorTableEntry>& entries, const Response& response,
+                  ProcessSet& ps,
                   void* comm);
   Status Reducescatter(std::vector<TensorTableEntry>& entries, ProcessSet& ps,
                        void* comm);

@@ -191,3 +191,36 @@ def _grouped_extras(rank, size):
 
 def test_grouped_allgather_reducescatter_and_barrier():
     assert all(run_parallel(_grouped_extras, np=3, timeout=300))
+
+
+def _alltoall_even_and_explicit(rank, size):
+    """An alltoall without splits (every rank's first dimension travels in the
+    response, so no split table is exchanged) with a different dim 0 on every
+    rank, repeated (cached response), then the same name with explicit splits
+    and back again: the cached "even split" response must not be reused for
+    explicit splits."""
+    import horovod_b200.torch as hvd
+    hvd.init()
+    ok = True
+    for it in range(3):
+        rows = size * (rank + 1)  # rank r sends r + 1 rows to every peer
+        x = (torch.arange(rows * 3, dtype=torch.float32).view(rows, 3) + 1000 * rank + it)
+        out = hvd.alltoall(x, name="a2a.same")
+        want = torch.cat([(torch.arange(size * (r + 1) * 3, dtype=torch.float32)
+                           .view(size * (r + 1), 3) + 1000 * r + it)[rank * (r + 1):(rank + 1) * (r + 1)]
+                          for r in range(size)])
+        ok = ok and torch.equal(out, want)
+        # explicit, uneven splits under the same name
+        splits = torch.tensor([(rank + p) % 3 for p in range(size)], dtype=torch.int32)
+        y = torch.full((int(splits.sum()), 2), float(rank))
+        out2, rsplits = hvd.alltoall(y, splits=splits, name="a2a.same")
+        exp_splits = [(r + rank) % 3 for r in range(size)]
+        ok = ok and rsplits.tolist() == exp_splits
+        ok = ok and out2[:, 0].tolist() == [float(r) for r in range(size)
+                                            for _ in range(exp_splits[r])]
+    hvd.shutdown()
+    return ok
+
+
+def test_alltoall_even_split_needs_no_split_exchange_and_mixes_with_explicit_splits():
+    assert all(run_parallel(_alltoall_even_and_explicit, np=4, timeout=300))

@@ -6,6 +6,7 @@ import math
 import struct
 
 import numpy as np
+import pytest
 import torch
 
 from horovod_b200 import _C
@@ -241,3 +242,24 @@ def test_fusion_policy_threshold_lookahead_and_compatibility():
                             1 << 20) == [["r1", "r2"], ["x"], ["r3"], ["r4"]]
     assert T.fuse_responses([item("t1", 10, typ=A2A), item("t2", 10, typ=A2A)], 1 << 20) == \
         [["t1"], ["t2"]]
+
+
+def test_build_and_extension_queries(monkeypatch):
+    """Parity: horovod/common/util.py:33-211 (extension path and check, build
+    feature queries, env context manager)."""
+    import os
+    import horovod_b200
+    from horovod_b200.common import util
+    path = util.get_extension_full_path(horovod_b200.__file__, "_C")
+    assert os.path.exists(path) and path.endswith(".so")
+    util.check_extension("horovod_b200.torch", "HOROVOD_WITH_PYTORCH", horovod_b200.__file__, "_C")
+    with pytest.raises(ImportError, match="build_ext"):
+        util.check_extension("horovod_b200.nope", "HOROVOD_WITH_NOPE", horovod_b200.__file__, "_nope")
+    assert util.extension_available() and util.gloo_built() and util.nccl_built()
+    assert not util.mpi_built() and not util.ddl_built() and not util.ccl_built()
+    monkeypatch.delenv("HVD_UTIL_PROBE", raising=False)
+    with util.env(HVD_UTIL_PROBE=3):
+        assert os.environ["HVD_UTIL_PROBE"] == "3"
+    assert "HVD_UTIL_PROBE" not in os.environ
+    import horovod_b200.torch as hvd
+    assert hvd.check_extension is util.check_extension

@@ -34,3 +34,47 @@ def test_synthetic_benchmark_example():
                       "--num-warmup-batches", "1", "--num-batches-per-iter", "1",
                       "--num-iters", "1"])
     assert "Total img/sec on 2 rank(s)" in out
+
+
+def test_imagenet_style_example_trains_checkpoints_and_resumes(tmp_path):
+    fmt = str(tmp_path / "ckpt-{epoch}.pt")
+    common = ["examples/pytorch_imagenet_resnet50.py", "--no-cuda", "--model", "tiny",
+              "--image-size", "32", "--num-classes", "10", "--synthetic-samples", "64",
+              "--batch-size", "8", "--batches-per-allreduce", "2", "--warmup-epochs", "1",
+              "--checkpoint-format", fmt]
+    out = _launch(2, common + ["--epochs", "2"], timeout=600)
+    assert len(re.findall(r"epoch \d+ train loss", out)) == 2, out[-1500:]
+    assert len(re.findall(r"epoch \d+ val loss", out)) == 2
+    assert os.path.exists(fmt.format(epoch=2))
+    # a second run with more epochs starts from the newest checkpoint
+    out = _launch(2, common + ["--epochs", "3"], timeout=600)
+    assert re.findall(r"epoch (\d+) train loss", out) == ["3"], out[-1500:]
+
+
+def test_adasum_example_runs_both_reductions():
+    out = _launch(2, ["examples/pytorch_adasum.py", "--no-cuda", "--steps", "30"])
+    rows = dict(re.findall(r"(average|adasum) \(.*?\)\s+first loss ([0-9.]+) last loss [0-9.]+", out))
+    assert set(rows) == {"average", "adasum"}, out[-1500:]
+    last = {k: float(v) for k, v in re.findall(r"(average|adasum) .*? last loss ([0-9.]+)", out)}
+    first = {k: float(v) for k, v in rows.items()}
+    assert all(last[k] < first[k] for k in last), out[-1500:]
+
+
+def test_elastic_synthetic_benchmark_example():
+    out = _launch(2, ["examples/pytorch_synthetic_benchmark_elastic.py", "--no-cuda", "--model",
+                      "tiny", "--image-size", "32", "--batch-size", "2", "--num-warmup-batches",
+                      "1", "--num-batches-per-iter", "1", "--num-iters", "2"])
+    assert len(re.findall(r"Iter #\d+: [0-9.]+ img/sec per rank, 2 rank\(s\)", out)) == 2, out[-1500:]
+    assert "Total img/sec over 2 iteration(s)" in out
+
+
+def test_ray_and_spark_examples_are_importable_without_their_frameworks():
+    """Their bodies need ray / pyspark; importing them (what a user's editor
+    and the launcher do first) must not."""
+    import importlib.util
+    for name in ("ray_basic", "spark_basic"):
+        spec = importlib.util.spec_from_file_location(name, os.path.join(ROOT, "examples",
+                                                                         name + ".py"))
+        module = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(module)
+        assert callable(module.train)

@@ -5,8 +5,9 @@ their local/cross coordinates from them and meet at a rendezvous server on
 the driver. ``pyspark`` (3.0 or newer, for BarrierTaskContext.allGather) is
 imported at call time; the tests drive run() through a stand-in pyspark
 module, since pyspark itself is not installed here.
-Parity: horovod/spark/runner.py:197-305 (run); the elastic variant and the
-Estimator API (:308-429, horovod/spark/{keras,torch,lightning}) are not built.
+Parity: horovod/spark/runner.py:197-305 (run). The elastic variant is in
+horovod_b200/spark/elastic.py; the Estimator API
+(horovod/spark/{keras,torch,lightning}) is not built.
 """
 import os
 import socket

@@ -362,3 +362,57 @@ def test_spark_run_with_a_stand_in_pyspark(monkeypatch):
         os.environ.update(saved)
     assert results == [("t", 0, 4, 0, 2, 0, 2, "a", True, "x"), ("t", 1, 4, 0, 2, 1, 2, "b", True, "x"),
                        ("t", 2, 4, 1, 2, 0, 2, "a", True, "x"), ("t", 3, 4, 1, 2, 1, 2, "b", True, "x")]
+
+
+def test_spark_run_elastic_with_tasks_as_child_processes(monkeypatch):
+    """run_elastic() against a stand-in pyspark whose stage runs every task in
+    a forked child process: the tasks register with the coordinator over the
+    signed RPC, the elastic driver sees them as slots of one host, hands each a
+    slot's environment, and the values the function returned come back ordered
+    by rank; afterwards every task is told that the job is over."""
+    import multiprocessing as mp
+    from horovod_b200.spark import run_elastic
+    pyspark = types.ModuleType("pyspark")
+
+    class RDD:
+        def __init__(self, n):
+            self.n = n
+
+        def mapPartitionsWithIndex(self, task):
+            self.task = task
+            return self
+
+        def collect(self):
+            ctx = mp.get_context("fork")
+            procs = [ctx.Process(target=lambda i=i: list(self.task(i, iter([i]))))
+                     for i in range(self.n)]
+            for p in procs:
+                p.start()
+            for p in procs:
+                p.join(120)
+            assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+            return list(range(self.n))
+
+    class SparkContext:
+        _active_spark_context = None
+        defaultParallelism = 3
+
+        def range(self, start, numSlices=None):
+            return RDD(numSlices)
+
+    pyspark.SparkContext = SparkContext
+    monkeypatch.setitem(sys.modules, "pyspark", pyspark)
+    with pytest.raises(Exception, match="SparkContext"):
+        run_elastic(lambda: 0, num_proc=2)
+    SparkContext._active_spark_context = SparkContext()
+    with pytest.raises(ValueError):
+        run_elastic(lambda: 0, num_proc=2, min_np=3, max_np=4)
+
+    def fn(tag):
+        e = os.environ
+        return (tag, int(e["HOROVOD_RANK"]), int(e["HOROVOD_SIZE"]), e["HOROVOD_ELASTIC"],
+                e["EXTRA"], int(e["HOROVOD_GLOO_RENDEZVOUS_PORT"]) > 0)
+
+    results = run_elastic(fn, args=("t",), num_proc=3, min_np=2, max_np=3, env={"EXTRA": "x"},
+                          elastic_timeout=30, verbose=0)
+    assert results == [("t", r, 3, "1", "x", True) for r in range(3)]

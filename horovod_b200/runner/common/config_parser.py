@@ -24,6 +24,7 @@ HOROVOD_STALL_SHUTDOWN_TIME_SECONDS = "HOROVOD_STALL_SHUTDOWN_TIME_SECONDS"
 HOROVOD_LOG_LEVEL = "HOROVOD_LOG_LEVEL"
 HOROVOD_LOG_HIDE_TIME = "HOROVOD_LOG_HIDE_TIME"
 HOROVOD_GLOO_TIMEOUT_SECONDS = "HOROVOD_GLOO_TIMEOUT_SECONDS"
+HOROVOD_MPI_THREADS_DISABLE = "HOROVOD_MPI_THREADS_DISABLE"
 HOROVOD_NUM_NCCL_STREAMS = "HOROVOD_NUM_NCCL_STREAMS"
 HOROVOD_THREAD_AFFINITY = "HOROVOD_THREAD_AFFINITY"
 HOROVOD_GPU_BACKEND = "HOROVOD_GPU_BACKEND"
@@ -48,6 +49,9 @@ def set_args_from_config(args, config, override_args):
         for k in ("fusion_threshold_mb", "cycle_time_ms", "cache_capacity",
                   "hierarchical_allreduce", "hierarchical_allgather"):
             _set_arg_from_config(args, k, override_args, params)
+    library_options = config.get("library_options")
+    if library_options:
+        _set_arg_from_config(args, "mpi_threads_disable", override_args, library_options)
     autotune = config.get("autotune")
     if autotune:
         args.autotune = autotune.get("enabled", False) \
@@ -140,6 +144,7 @@ def set_env_from_args(env, args):
     _add(env, HOROVOD_STALL_CHECK_DISABLE, g("no_stall_check"), lambda v: "1")
     _add(env, HOROVOD_STALL_CHECK_TIME_SECONDS, g("stall_check_warning_time_seconds"))
     _add(env, HOROVOD_STALL_SHUTDOWN_TIME_SECONDS, g("stall_check_shutdown_time_seconds"))
+    _add(env, HOROVOD_MPI_THREADS_DISABLE, g("mpi_threads_disable"), lambda v: "1")
     _add(env, HOROVOD_NUM_NCCL_STREAMS, g("num_nccl_streams"))
     _add(env, HOROVOD_THREAD_AFFINITY, g("thread_affinity"))
     _add(env, HOROVOD_GLOO_TIMEOUT_SECONDS, g("gloo_timeout_seconds"))

@@ -231,6 +231,13 @@ def parse_args(argv=None):
     cx.add_argument("--gloo", action="store_true", dest="use_gloo")
     cx.add_argument("--mpi", action="store_true", dest="use_mpi")
     cx.add_argument("--jsrun", action="store_true", dest="use_jsrun")
+    tx = g.add_mutually_exclusive_group()
+    tx.add_argument("--mpi-threads-disable", dest="mpi_threads_disable",
+                    action=make_override_true_action(override_args),
+                    help="Passed on as HOROVOD_MPI_THREADS_DISABLE; only meaningful for jobs "
+                         "started through mpirun, this runtime has no MPI threads of its own.")
+    tx.add_argument("--no-mpi-threads-disable", dest="mpi_threads_disable",
+                    action=make_override_false_action(override_args), help=argparse.SUPPRESS)
     g.add_argument("--mpi-args", dest="mpi_args")
     g.add_argument("--tcp", action="store_true", dest="tcp_flag")
     g.add_argument("--binding-args", dest="binding_args")

@@ -54,6 +54,11 @@ def test_args_map_to_env():
                               "python", "train.py"])
     assert "HOROVOD_LOG_HIDE_TIME" not in config_parser.set_env_from_args({}, args)
     assert args.prefix_output_with_timestamp
+    # library options (horovod/runner/launch.py:423-431)
+    args = launch.parse_args(["-np", "2", "--mpi-threads-disable", "python", "train.py"])
+    assert config_parser.set_env_from_args({}, args)["HOROVOD_MPI_THREADS_DISABLE"] == "1"
+    args = launch.parse_args(["-np", "2", "--no-mpi-threads-disable", "python", "train.py"])
+    assert "HOROVOD_MPI_THREADS_DISABLE" not in config_parser.set_env_from_args({}, args)
 
 
 def test_config_file_loses_to_explicit_flags(tmp_path):

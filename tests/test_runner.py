@@ -411,3 +411,68 @@ def test_output_filename_writes_per_rank_files(tmp_path):
         assert "[%d]<stdout>:hello from %d" % (r, r) in text
         assert text.split("[")[0].strip(), "timestamp prefix missing"
         assert os.path.exists(os.path.join(out_dir, "rank.%d" % r, "stderr"))
+
+
+def test_small_launcher_utilities(monkeypatch):
+    """codec, env, tiny_shell_exec, http_client, util.network / remote /
+    streams (parity: horovod/runner/common/util/{codec,env,tiny_shell_exec}.py,
+    horovod/runner/http/http_client.py, horovod/runner/util/{network,remote,streams}.py)."""
+    import threading
+    from horovod_b200.runner.common import codec, env as env_util, tiny_shell_exec
+    from horovod_b200.runner.http import http_client
+    from horovod_b200.runner.http.http_server import RendezvousServer
+    from horovod_b200.runner.util import network, remote, streams
+
+    obj = {"fn": lambda x: x + 1, "n": [1, 2, 3]}
+    text = codec.dumps_base64(obj)
+    assert isinstance(text, str) and codec.loads_base64(text)["fn"](2) == 3
+    assert isinstance(codec.dumps_base64(obj, to_ascii=False), bytes)
+
+    assert env_util.is_exportable("PATH") and not env_util.is_exportable("BASH_FUNC_x%%")
+    assert not env_util.is_exportable("_HOROVOD_SECRET_KEY")
+    for name in ("HOROVOD_RANK", "HOROVOD_SIZE", "OMPI_COMM_WORLD_RANK", "OMPI_COMM_WORLD_SIZE",
+                 "PMI_RANK", "PMI_SIZE", "OMPI_MCA_plm_rsh_agent"):
+        monkeypatch.delenv(name, raising=False)
+    assert env_util.get_env_rank_and_size() == (0, 1)
+    monkeypatch.setenv("OMPI_COMM_WORLD_RANK", "3")
+    with pytest.raises(RuntimeError):
+        env_util.get_env_rank_and_size()
+    monkeypatch.setenv("OMPI_COMM_WORLD_SIZE", "8")
+    assert env_util.get_env_rank_and_size() == (3, 8)
+
+    out, code = tiny_shell_exec.execute("echo hello; echo oops 1>&2; exit 3")
+    assert code == 3 and "hello" in out and "oops" in out
+
+    server = RendezvousServer(0)
+    port = server.start()
+    try:
+        http_client.put_data_into_kvstore("127.0.0.1", port, "scope", "key", {"a": (1, 2)})
+        assert http_client.read_data_from_kvstore("127.0.0.1", port, "scope", "key") == {"a": (1, 2)}
+        with pytest.raises(RuntimeError):
+            http_client.read_data_from_kvstore("127.0.0.1", port, "scope", "absent")
+    finally:
+        server.stop()
+
+    assert "127.0.0.1" in network.get_local_host_addresses()
+    assert network.filter_local_addresses(["127.0.0.1", "no-such-host.invalid"]) == \
+        ["no-such-host.invalid"]
+    assert network.resolve_host_address("no-such-host.invalid") is None
+
+    cmd = remote.get_ssh_command("ls", "h1", port=2222, identity_file="/k", timeout_s=5)
+    assert cmd.startswith("ssh -o PasswordAuthentication=no") and cmd.endswith(" ls")
+    assert " h1 " in cmd and "-p 2222" in cmd and "-i /k" in cmd and "ConnectTimeout=5" in cmd
+    monkeypatch.setenv("OMPI_MCA_plm_rsh_agent", env_util.KUBEFLOW_MPI_EXEC)
+    assert remote.get_remote_command("ls", "h1") == "/etc/mpi/kubexec.sh h1 ls"
+
+    pipe = streams.Pipe()
+    got = []
+    reader = threading.Thread(target=lambda: [got.append(pipe.read(3)) for _ in range(3)])
+    reader.start()
+    pipe.write("abcde")
+    pipe.write(b"xy")
+    reader.join(10)
+    assert got == ["abc", "de", b"xy"]
+    pipe.close()
+    assert pipe.read() is None
+    with pytest.raises(RuntimeError):
+        pipe.write("late")

@@ -552,6 +552,59 @@ def test_grouped_reducescatter_is_one_launch():
     assert all(f == [] for f in failures), failures
 
 
+def _two_hosts_on_gpus(rank, size):
+    """Four GPUs laid out as two hosts of two ranks (distinct cross ranks on
+    one box): local_size != size, so the NCCL path is selected, and with
+    HOROVOD_HIERARCHICAL_ALLREDUCE=1 every fused allreduce runs as
+    ncclReduceScatter inside the host, ncclAllReduce across the hosts and
+    ncclAllGather inside the host. Results against an fp64 sum."""
+    local = 2
+    os.environ.update({
+        "HOROVOD_LOCAL_RANK": str(rank % local), "HOROVOD_LOCAL_SIZE": str(local),
+        "HOROVOD_CROSS_RANK": str(rank // local), "HOROVOD_CROSS_SIZE": str(size // local),
+        "HOROVOD_HOSTNAME": "host-%d" % (rank // local),
+        "HOROVOD_HIERARCHICAL_ALLREDUCE": "1",
+        "NCCL_NVLS_ENABLE": "0",
+    })
+    import horovod_b200.torch as hvd
+    hvd.init()
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    ok = hvd.runtime_params()["hierarchy_usable"] and hvd.local_size() == local
+    for it in range(2):
+        for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 4e-2), (torch.int32, 0)):
+            for n in (1, 3, 1001, (1 << 20) + 5):
+                host = [_inputs(13 * r + n % 97 + it, n, dtype) for r in range(size)]
+                out = hvd.allreduce(host[rank].to(dev), op=hvd.Sum,
+                                    name="hier.%s.%d" % (str(dtype)[6:], n))
+                ref = sum(h.double() for h in host)
+                err = (out.double().cpu() - ref).abs().max().item()
+                ok = ok and err <= tol * max(1.0, ref.abs().max().item()) * size
+        # a fused group, averaged
+        xs = [_inputs(rank * 5 + i + it, s, torch.float32).to(dev)
+              for i, s in enumerate((3, 129, 77, 40000, 5))]
+        outs = hvd.grouped_allreduce(xs, op=hvd.Average, name="hier.grp")
+        for i, (s, o) in enumerate(zip((3, 129, 77, 40000, 5), outs)):
+            ref = sum(_inputs(r * 5 + i + it, s, torch.float32).double() for r in range(size)) / size
+            ok = ok and (o.double().cpu() - ref).abs().max().item() < 1e-5
+    ok = ok and "nccl" in hvd.gpu_backend()
+    torch.cuda.synchronize()
+    hvd.shutdown()
+    return ok
+
+
+def test_hierarchical_allreduce_on_the_nccl_path():
+    if _ngpu() < 4:
+        pytest.skip("needs 4 GPUs")
+    if os.environ.get("HOROVOD_TEST_HIERARCHICAL_NCCL") != "1":
+        # The host-side twin (tests/test_hierarchical.py) runs everywhere; this
+        # variant has not completed a run on GPUs yet (its first attempt was cut
+        # short by the time limit of the call, before any result), so it is
+        # opt-in until it has.
+        pytest.skip("opt-in: set HOROVOD_TEST_HIERARCHICAL_NCCL=1")
+    assert all(run_parallel(_two_hosts_on_gpus, np=4, timeout=300))
+
+
 def _two_devices_per_rank(rank, size):
     """Every rank spreads a two-layer model over two of the box's GPUs (layer
     one on the first, layer two on the second) and trains it through

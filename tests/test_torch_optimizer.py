@@ -282,3 +282,63 @@ def _sync_bn(rank, size):
 
 def test_sync_batch_norm_matches_full_batch():
     assert all(run_parallel(_sync_bn, np=2))
+
+
+def _force_allreduce_every_optimizer(rank, size):
+    """Every rank back-propagates through a different part of the model (rank 0
+    never touches the last layer), for every optimizer class PyTorch ships:
+    step() must reduce all gradients, the missing ones as zeros, and leave
+    identical parameters on all ranks (parity: test_force_allreduce,
+    test/parallel/test_torch.py:1791-1858)."""
+    import inspect
+    import torch.nn.functional as F
+    import horovod_b200.torch as hvd
+    hvd.init()
+    torch.manual_seed(3)
+    x, y = torch.randn(16, 20), torch.randn(16, 5)
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc1 = torch.nn.Linear(20, 8)
+            self.fc2 = torch.nn.Linear(8, 5)
+            self.fc3 = torch.nn.Linear(5, 5)
+
+        def forward(self, inp):
+            hidden = F.relu(self.fc1(inp))
+            first = self.fc2(hidden)
+            return first, self.fc3(F.relu(first))
+
+    classes = sorted((c for c in torch.optim.Optimizer.__subclasses__()
+                      if c.__module__.startswith("torch.optim")
+                      and c not in (torch.optim.LBFGS, torch.optim.SparseAdam)),
+                     key=lambda c: c.__name__)
+    failures = []
+    for cls in classes:
+        for wanted in (dict(lr=0.2, momentum=0.9, weight_decay=0.1, centered=True), dict(lr=0.2)):
+            accepted = inspect.signature(cls.__init__).parameters
+            kwargs = {k: v for k, v in wanted.items() if k in accepted}
+            model = Net()
+            hvd.broadcast_parameters(model.state_dict(), root_rank=0)
+            try:
+                base = cls(model.parameters(), **kwargs)
+            except ValueError:
+                continue  # an optimizer that refuses this model (matrices only, say)
+            opt = hvd.DistributedOptimizer(base, named_parameters=model.named_parameters())
+            first, second = model(x)
+            loss = F.mse_loss(first if rank == 0 else second, y, reduction="sum")
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+            flat = torch.cat([p.detach().flatten() for p in model.parameters()])
+            same = hvd.allreduce(flat, op=hvd.Average, name="fa.%s.%d" % (cls.__name__,
+                                                                          len(kwargs)))
+            if not torch.allclose(same, flat, atol=1e-5, equal_nan=True):
+                failures.append(cls.__name__)
+    hvd.shutdown()
+    return failures, len(classes)
+
+
+def test_step_reduces_every_gradient_for_every_optimizer_class():
+    for failures, n in run_parallel(_force_allreduce_every_optimizer, np=2, timeout=600):
+        assert n >= 8 and failures == [], failures

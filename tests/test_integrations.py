@@ -111,8 +111,10 @@ def test_filesystem_store_layout_and_sync(tmp_path):
     assert store.is_parquet_dataset(store.get_train_data_path())
     quiet = LocalStore(str(tmp_path / "q"), save_runs=False)
     assert quiet.get_checkpoint_path("r") is None and not quiet.saving_runs()
-    with pytest.raises(ValueError):
+    with pytest.raises(RuntimeError, match="(?i)hdfs"):  # no Hadoop client on this machine
         Store.create("hdfs://namenode/path")
+    with pytest.raises(ValueError):
+        Store.create("gs://bucket/path")
 
 
 def test_ray_placement_plans():
@@ -416,3 +418,50 @@ def test_spark_run_elastic_with_tasks_as_child_processes(monkeypatch):
     results = run_elastic(fn, args=("t",), num_proc=3, min_np=2, max_np=3, env={"EXTRA": "x"},
                           elastic_timeout=30, verbose=0)
     assert results == [("t", r, 3, "1", "x", True) for r in range(3)]
+
+
+def test_dbfs_and_arrow_filesystem_stores(tmp_path):
+    """dbfs:/ paths map onto the local DBFS mount; the same store layout works
+    over a pyarrow filesystem (what the HDFS store is built on); hdfs:// URLs
+    without a Hadoop client fail with a message that names the cause."""
+    from horovod_b200.spark import ArrowFilesystemStore, DBFSLocalStore, HDFSStore, Store
+    root = str(tmp_path / "mount")
+    store = DBFSLocalStore("dbfs:/ml/exp", root=root)
+    assert store.prefix_path == root + "/ml/exp" and os.path.isdir(store.prefix_path)
+    assert DBFSLocalStore.matches("dbfs:/x") and DBFSLocalStore.matches("/dbfs/x")
+    assert not DBFSLocalStore.matches("/data/x")
+    assert store.normalize("dbfs:///a/b") == root + "/a/b"
+    assert store.normalize("/dbfs/a/b") == root + "/a/b"
+    ckpt = store.get_checkpoint_path("r1")
+    assert ckpt == root + "/ml/exp/runs/r1/checkpoint"
+    with store.get_local_output_dir_fn("r1")() as local:
+        with open(os.path.join(local, "checkpoint"), "wb") as f:
+            f.write(b"w")
+        store.sync_fn("r1")(local)
+    assert store.exists("dbfs:/ml/exp/runs/r1/checkpoint") and store.read(ckpt) == b"w"
+
+    fs = pytest.importorskip("pyarrow.fs")
+    base = str(tmp_path / "arrow")
+    os.makedirs(base)
+    arrow = ArrowFilesystemStore(fs.SubTreeFileSystem(base, fs.LocalFileSystem()), "exp")
+    assert os.path.isdir(os.path.join(base, "exp"))
+    assert not arrow.exists(arrow.get_checkpoint_path("r2"))
+    with arrow.get_local_output_dir_fn("r2")() as local:
+        os.makedirs(os.path.join(local, "logs"))
+        with open(os.path.join(local, "checkpoint"), "wb") as f:
+            f.write(b"weights")
+        with open(os.path.join(local, "logs", "e.txt"), "w") as f:
+            f.write("step 1")
+        arrow.sync_fn("r2")(local)
+    assert arrow.read(arrow.get_checkpoint_path("r2")) == b"weights"
+    assert arrow.exists(arrow.get_logs_path("r2") + "/e.txt")
+    arrow.write_text(arrow.get_train_data_path() + "/part-0.parquet", "")
+    assert arrow.is_parquet_dataset(arrow.get_train_data_path())
+    assert not arrow.is_parquet_dataset(arrow.get_val_data_path())
+    assert callable(arrow.to_remote("r2", None).sync)
+
+    with pytest.raises((RuntimeError, OSError), match="(?i)hdfs"):
+        HDFSStore("hdfs://namenode:8020/x")
+    with pytest.raises(ValueError):
+        Store.create("s3://bucket/x")
+    assert isinstance(Store.create("dbfs:/q", root=root), DBFSLocalStore)

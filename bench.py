@@ -254,6 +254,15 @@ def collective_checks(hvd, torch, device):
         full = _seeded(600 + r, sum(sp) * width, torch.float32, torch).view(-1, width)
         pieces.append(full[sum(sp[:rank]):sum(sp[:rank]) + sp[rank]])
     check("alltoall_uneven", torch.equal(recv.cpu(), torch.cat(pieces)))
+    # alltoall without splits (even split; no split table is exchanged): rank r
+    # holds n * (r + 1) rows and sends r + 1 of them to every peer
+    width = 1024
+    send = _seeded(800 + rank, n * (rank + 1) * width, torch.float32, torch) \
+        .view(n * (rank + 1), width)
+    recv = hvd.alltoall(send.to(device), name="check.a2a.even")
+    pieces = [_seeded(800 + r, n * (r + 1) * width, torch.float32, torch)
+              .view(n * (r + 1), width)[rank * (r + 1):(rank + 1) * (r + 1)] for r in range(n)]
+    check("alltoall_even", torch.equal(recv.cpu(), torch.cat(pieces)))
     # every rank must agree on the verdict
     mine = torch.tensor([float(len(failed))])
     worst = float(hvd.allreduce(mine, op=hvd.Max, name="check.verdict"))

@@ -82,6 +82,17 @@ def _collectives(rank, size, algo):
     assert recv.tolist() == [rank + 1] * size
     exp = torch.cat([torch.full((rank + 1, 2), float(r * 100 + rank)) for r in range(size)])
     assert torch.equal(out.cpu(), exp)
+    # alltoall without splits (even split, no split table exchanged): rank r
+    # holds size * (r + 1) rows and sends r + 1 of them to every peer; twice,
+    # the second time from the cached response
+    for it in range(2):
+        mine = (torch.arange(size * (rank + 1) * 3, dtype=torch.float32) + 1000 * rank + it) \
+            .view(size * (rank + 1), 3)
+        out = hvd.alltoall(mine.to(dev), name="a2a.even")
+        exp = torch.cat([((torch.arange(size * (r + 1) * 3, dtype=torch.float32) + 1000 * r + it)
+                          .view(size * (r + 1), 3))[rank * (r + 1):(rank + 1) * (r + 1)]
+                         for r in range(size)])
+        assert torch.equal(out.cpu(), exp)
     # reducescatter with ragged shards
     rs_rows = 2 * size + 1
     x = _inputs(rank + 500, rs_rows * 5, torch.float32).view(rs_rows, 5).to(dev)

@@ -25,7 +25,9 @@ inputs, before the timed region), "params_in_sync" (fp64 checksums of every
 parameter after the timed steps, equal on all ranks) and "loss_vs_single" (a
 small language model trained for a few steps on rank-specific batches through
 the same gradient path, against plain SGD on the concatenated batch in one
-process). Any mismatch makes the exit code non-zero.
+process). Any mismatch makes the exit code non-zero. "allreduce_bus" is the
+bus bandwidth of a 256 MB fp32 allreduce (in place on the symmetric heap and
+staged), the third metric of record.
 
 --impl ddp runs the same model, batch and autocast through
 torch.nn.parallel.DistributedDataParallel over NCCL: an independent arm for
@@ -269,6 +271,50 @@ def collective_checks(hvd, torch, device):
     if worst > 0 and not failed:
         failed.append("a check failed on another rank")
     return passed, failed
+
+
+def allreduce_bus_bandwidth(hvd, torch, device, nbytes=256 << 20, reps=5):
+    """Bus bandwidth of one large fp32 allreduce, the third metric of record:
+    in place on the symmetric heap (the path of the ResNet gradients) and
+    staged from ordinary memory (the path of every other tensor). Timed with
+    CUDA events on the caller's stream, which waits for the op, so the host
+    launch path is inside the figure; max over ranks. bus = 2 (N-1)/N S / t."""
+    import statistics
+    import time
+    n = hvd.size()
+    count = nbytes // 4
+    on_gpu = device.type == "cuda"
+
+    def timed(x, name):
+        for _ in range(3):
+            hvd.allreduce_(x, op=hvd.Average, name=name)
+        samples = []
+        for _ in range(reps):
+            if on_gpu:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                hvd.allreduce_(x, op=hvd.Average, name=name)
+                e1.record()
+                e1.synchronize()
+                samples.append(e0.elapsed_time(e1) * 1e3)
+            else:
+                t0 = time.perf_counter()
+                hvd.allreduce_(x, op=hvd.Average, name=name)
+                samples.append((time.perf_counter() - t0) * 1e6)
+        us = float(hvd.allreduce(torch.tensor([statistics.median(samples)], dtype=torch.float64),
+                                 op=hvd.Max, name=name + ".us"))
+        return {"us": round(us, 1),
+                "bus_gbs": round(nbytes * 2.0 * (n - 1) / n / (us * 1e-6) / 1e9, 1)}
+
+    out = {"bytes": nbytes, "dtype": "fp32", "n_gpus": n,
+           "formula": "2 (N-1)/N x bytes / time, time = median of %d, max over ranks" % reps}
+    staged = torch.ones(count, device=device)
+    out["staged"] = timed(staged, "bus.staged")
+    if hvd.gpu_backend().startswith("symm"):
+        heap = hvd.symmetric_empty(count)
+        heap.fill_(1.0)
+        out["in_place_on_symmetric_heap"] = timed(heap, "bus.inplace")
+    return out
 
 
 def params_in_sync(hvd, torch, model):
@@ -621,7 +667,15 @@ def main():
                           "DistributedOptimizer vs plain SGD on the concatenated batch"}
         if not worst <= 1e-4:
             rc = 3
+    bus = None
+    if hvd.size() > 1:
+        try:
+            bus = allreduce_bus_bandwidth(hvd, torch, device)
+        except Exception as e:  # the flagship line must survive
+            bus = {"error": "%s: %s" % (type(e).__name__, e)}
     if hvd.rank() == 0:
+        if bus is not None:
+            out["allreduce_bus"] = bus
         if checks is not None:
             out["collective_checks"] = checks
         if single is not None:

@@ -598,6 +598,31 @@ def main_ddp(args):
     t_end.record()
     torch.cuda.synchronize()
     e2e_ms = allmax(max(t_start.elapsed_time(t_end), (time.perf_counter() - wall0) * 1e3))
+    bus = None
+    if world > 1:
+        # The same figure as this library's arm prints: a 256 MB fp32
+        # allreduce, CUDA events on the caller's stream, max over ranks.
+        try:
+            import statistics
+            nbytes = 256 << 20
+            buf = torch.ones(nbytes // 4, device=device)
+            for _ in range(3):
+                dist.all_reduce(buf, op=dist.ReduceOp.AVG)
+            samples = []
+            for _ in range(5):
+                b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                b0.record()
+                dist.all_reduce(buf, op=dist.ReduceOp.AVG)
+                b1.record()
+                b1.synchronize()
+                samples.append(b0.elapsed_time(b1) * 1e3)
+            us = allmax(statistics.median(samples))
+            bus = {"bytes": nbytes, "dtype": "fp32", "n_gpus": world,
+                   "nccl_all_reduce": {"us": round(us, 1),
+                                       "bus_gbs": round(nbytes * 2.0 * (world - 1) / world
+                                                        / (us * 1e-6) / 1e9, 1)}}
+        except Exception as e:  # the throughput line must survive
+            bus = {"error": "%s: %s" % (type(e).__name__, e)}
     if rank == 0:
         total = batch * args.gpus * args.steps
         cfg.update({"parallelism": "dp%d" % args.gpus, "per_gpu_batch": batch,
@@ -611,7 +636,8 @@ def main_ddp(args):
             "impl": "ddp", "config": cfg, "clocks": clocks,
             "e2e": {"value": round(total / (e2e_ms / 1e3), 2), "unit": unit,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
-            "gpu_launches": 0, "final_loss": float(loss_host.item())}))
+            "gpu_launches": 0, "final_loss": float(loss_host.item()),
+            **({"allreduce_bus": bus} if bus is not None else {})}))
     dist.destroy_process_group()
     return 0
 

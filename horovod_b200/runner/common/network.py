@@ -1,12 +1,18 @@
 """Minimal authenticated RPC used between the launcher, the elastic driver
-and workers: length-prefixed cloudpickle messages over TCP, each carrying an
-HMAC-SHA256 digest computed with a per-job secret. A service answers a
-request object with a response object; a client tries all advertised
-addresses of a service and keeps the ones that answer.
+and workers. One request and one response per TCP connection; each message is
+a frame of a fixed header (body length and HMAC-SHA256 of the body, keyed with
+the job's secret) followed by the cloudpickled object. A service answers a
+request object with a response object; a client learns at construction which
+of a service's advertised addresses reach it and uses those afterwards.
 
-Parity: horovod/runner/common/util/network.py:56-306.
+What callers rely on (and what horovod/runner/common/util/network.py:56-306
+offers its callers): ``BasicService`` with an overridable ``_handle``,
+``addresses()``, ``get_port()``, ``shutdown()``; ``BasicClient`` with
+``_send(request)`` and ``addresses()``; ``PingRequest`` / ``PingResponse`` /
+``AckResponse``; ``NoValidAddressesFound``; ``find_port``.
 """
-import queue
+import concurrent.futures
+import contextlib
 import socket
 import socketserver
 import struct
@@ -18,11 +24,7 @@ from horovod_b200.runner.common import secret
 
 
 class PingRequest:
-    pass
-
-
-class NoValidAddressesFound(Exception):
-    pass
+    """Answered by every service with its name and the caller's address."""
 
 
 class PingResponse:
@@ -32,100 +34,103 @@ class PingResponse:
 
 
 class AckResponse:
+    """The answer of requests that have nothing to return."""
+
+
+class NoValidAddressesFound(Exception):
     pass
 
 
 class Wire:
-    """Message framing: 4-byte length, 32-byte digest, pickled body."""
+    """Frames: ``!I`` body length, then the digest, then the body."""
+
+    _LENGTH = struct.Struct("!I")
 
     def __init__(self, key):
         self._key = key
 
     def write(self, obj, wfile):
-        message = cloudpickle.dumps(obj)
-        digest = secret.compute_digest(self._key, message)
-        wfile.write(struct.pack("i", len(message)))
-        wfile.write(digest)
-        wfile.write(message)
+        body = cloudpickle.dumps(obj)
+        wfile.write(self._LENGTH.pack(len(body)) + secret.compute_digest(self._key, body) + body)
         wfile.flush()
 
     def read(self, rfile):
-        header = rfile.read(4)
-        if len(header) < 4:
+        head = rfile.read(self._LENGTH.size + secret.DIGEST_LENGTH)
+        if len(head) < self._LENGTH.size + secret.DIGEST_LENGTH:
             raise EOFError("connection closed")
-        (length,) = struct.unpack("i", header)
-        digest = rfile.read(secret.DIGEST_LENGTH)
-        message = rfile.read(length)
-        if not secret.check_digest(self._key, message, digest):
+        (length,) = self._LENGTH.unpack_from(head)
+        body = rfile.read(length)
+        if len(body) < length:
+            raise EOFError("connection closed inside a message")
+        if not secret.check_digest(self._key, body, head[self._LENGTH.size:]):
             raise Exception("Security error: digest did not match the message.")
-        return cloudpickle.loads(message)
+        return cloudpickle.loads(body)
+
+
+def _ipv4_by_interface(port, nics=None):
+    """{interface: [(address, port)]} of this machine, restricted to ``nics``
+    when given; at least the loopback (and the host name's address) when the
+    interfaces cannot be listed."""
+    found = {}
+    try:
+        import psutil
+        for name, infos in psutil.net_if_addrs().items():
+            if nics and name not in nics:
+                continue
+            ips = [(i.address, port) for i in infos if i.family == socket.AF_INET]
+            if ips:
+                found[name] = ips
+    except Exception:  # noqa: BLE001 - psutil missing or unreadable
+        found = {}
+    if found:
+        return found
+    fallback = {"lo": [("127.0.0.1", port)]}
+    with contextlib.suppress(OSError):
+        host_ip = socket.gethostbyname(socket.gethostname())
+        if host_ip != "127.0.0.1":
+            fallback["host"] = [(host_ip, port)]
+    if nics:
+        wanted = {k: v for k, v in fallback.items() if k in nics}
+        return wanted or fallback
+    return fallback
 
 
 class BasicService:
+    """A threaded TCP server that reads one request per connection, passes it
+    to ``_handle`` and writes back what that returns. Subclasses extend
+    ``_handle`` and call the base for requests they do not know."""
+
     def __init__(self, service_name, key, nics=None):
         self._service_name = service_name
         self._wire = Wire(key)
         self._nics = nics
-        self._server, _ = find_port(lambda addr: socketserver.ThreadingTCPServer(
-            addr, self._make_handler()))
+        service = self
+
+        class Connection(socketserver.StreamRequestHandler):
+            def handle(self):
+                # A bad or truncated message ends this connection, never the service.
+                with contextlib.suppress(Exception):
+                    request = service._wire.read(self.rfile)
+                    response = service._handle(request, self.client_address)
+                    if response is None:
+                        raise Exception("Handler did not return a response.")
+                    service._wire.write(response, self.wfile)
+
+        self._server, self._port = find_port(
+            lambda address: socketserver.ThreadingTCPServer(address, Connection))
         self._server.daemon_threads = True
-        self._port = self._server.socket.getsockname()[1]
-        self._addresses = self._get_local_addresses()
+        self._addresses = _ipv4_by_interface(self._port, nics)
         self._thread = threading.Thread(target=self._server.serve_forever, daemon=True,
                                         name="hvd-service-" + service_name)
         self._thread.start()
-
-    def _make_handler(self):
-        server = self
-
-        class _Handler(socketserver.StreamRequestHandler):
-            def handle(self):
-                try:
-                    req = server._wire.read(self.rfile)
-                    resp = server._handle(req, self.client_address)
-                    if resp is None:
-                        raise Exception("Handler did not return a response.")
-                    server._wire.write(resp, self.wfile)
-                except (EOFError, ConnectionError):
-                    pass
-                except Exception:  # noqa: BLE001 - a bad message must not kill the service
-                    pass
-        return _Handler
 
     def _handle(self, req, client_address):
         if isinstance(req, PingRequest):
             return PingResponse(self._service_name, client_address[0])
         raise NotImplementedError(req)
 
-    def _get_local_addresses(self):
-        """{interface name: [(ipv4, port)]} for every interface that is up,
-        filtered to ``nics`` when given (loopback is always kept last so a
-        single-host job still works)."""
-        result = {}
-        try:
-            import psutil
-            for intf, addrs in psutil.net_if_addrs().items():
-                if self._nics and intf not in self._nics:
-                    continue
-                for a in addrs:
-                    if a.family == socket.AF_INET:
-                        result.setdefault(intf, []).append((a.address, self._port))
-        except Exception:  # noqa: BLE001 - psutil missing or unreadable: fall back below
-            result = {}
-        if not result:
-            result = {"lo": [("127.0.0.1", self._port)]}
-            try:
-                host_ip = socket.gethostbyname(socket.gethostname())
-                if host_ip != "127.0.0.1":
-                    result["host"] = [(host_ip, self._port)]
-            except OSError:
-                pass
-            if self._nics:
-                result = {k: v for k, v in result.items() if k in self._nics} or result
-        return result
-
     def addresses(self):
-        return {k: list(v) for k, v in self._addresses.items()}
+        return {name: list(pairs) for name, pairs in self._addresses.items()}
 
     def get_port(self):
         return self._port
@@ -137,6 +142,10 @@ class BasicService:
 
 
 class BasicClient:
+    """Talks to one service. ``addresses`` is the service's
+    ``{interface: [(ip, port)]}``; the constructor pings all of them at once
+    and keeps those that answer with the right service name."""
+
     def __init__(self, service_name, addresses, key, verbose=0, match_intf=False,
                  probe_timeout=20, attempts=3):
         self._service_name = service_name
@@ -145,81 +154,65 @@ class BasicClient:
         self._match_intf = match_intf
         self._probe_timeout = probe_timeout
         self._attempts = attempts
-        self._addresses = self._probe(addresses)
+        self._addresses = self._reachable(addresses)
         if not self._addresses:
             raise NoValidAddressesFound(
                 "horovodrun was unable to connect to %s on any of the following addresses: %s"
                 % (service_name, addresses))
 
-    def _probe(self, addresses):
-        result_queue = queue.Queue()
-        threads = []
-        for intf, intf_addresses in addresses.items():
-            for addr in intf_addresses:
-                t = threading.Thread(target=self._probe_one, args=(intf, addr, result_queue),
-                                     daemon=True)
-                t.start()
-                threads.append(t)
-        for t in threads:
-            t.join()
-        result = {}
-        while not result_queue.empty():
-            intf, addr = result_queue.get()
-            result.setdefault(intf, []).append(addr)
-        return result
+    def _exchange(self, address, request):
+        """One connection: send ``request``, return the response."""
+        with socket.create_connection(tuple(address), timeout=self._probe_timeout) as sock:
+            with sock.makefile("rb") as rfile, sock.makefile("wb") as wfile:
+                self._wire.write(request, wfile)
+                return self._wire.read(rfile)
 
-    def _probe_one(self, intf, addr, result_queue):
+    def _with_retries(self, address, request):
+        error = None
         for _ in range(self._attempts):
             try:
-                sock = socket.create_connection(tuple(addr), timeout=self._probe_timeout)
-                rfile, wfile = sock.makefile("rb"), sock.makefile("wb")
-                try:
-                    self._wire.write(PingRequest(), wfile)
-                    resp = self._wire.read(rfile)
-                    if resp.service_name == self._service_name:
-                        result_queue.put((intf, addr))
-                    return
-                finally:
-                    rfile.close()
-                    wfile.close()
-                    sock.close()
-            except Exception:  # noqa: BLE001 - try again / give up on this address
-                pass
+                return self._exchange(address, request)
+            except Exception as e:  # noqa: BLE001 - refused, reset, bad digest: try again
+                error = e
+        raise error
 
-    def _send_one(self, addr, req):
-        last = None
-        for _ in range(self._attempts):
-            try:
-                sock = socket.create_connection(tuple(addr), timeout=self._probe_timeout)
-                rfile, wfile = sock.makefile("rb"), sock.makefile("wb")
-                try:
-                    self._wire.write(req, wfile)
-                    return self._wire.read(rfile)
-                finally:
-                    rfile.close()
-                    wfile.close()
-                    sock.close()
-            except Exception as e:  # noqa: BLE001
-                last = e
-        raise last
+    def _answers(self, address):
+        try:
+            reply = self._with_retries(address, PingRequest())
+        except Exception:  # noqa: BLE001 - unreachable from here
+            return False
+        return getattr(reply, "service_name", None) == self._service_name
+
+    def _reachable(self, addresses):
+        candidates = [(name, pair) for name, pairs in addresses.items() for pair in pairs]
+        if not candidates:
+            return {}
+        with concurrent.futures.ThreadPoolExecutor(max_workers=len(candidates)) as pool:
+            verdicts = list(pool.map(lambda c: self._answers(c[1]), candidates))
+        kept = {}
+        for (name, pair), ok in zip(candidates, verdicts):
+            if ok:
+                kept.setdefault(name, []).append(pair)
+        return kept
 
     def _send(self, req):
-        for addrs in self._addresses.values():
-            for addr in addrs:
-                return self._send_one(addr, req)
+        for pairs in self._addresses.values():
+            for pair in pairs:
+                return self._with_retries(pair, req)
         raise NoValidAddressesFound(self._service_name)
 
     def addresses(self):
         return self._addresses
 
 
-def find_port(server_factory, start=1024 + 0, attempts=200):
-    """Binds a server on an ephemeral port."""
-    last = None
+def find_port(server_factory, attempts=200):
+    """Lets the operating system pick a free port for the server that
+    ``server_factory((host, port))`` creates; returns (server, port)."""
+    error = None
     for _ in range(attempts):
         try:
             server = server_factory(("0.0.0.0", 0))
             return server, server.socket.getsockname()[1]
         except OSError as e:
-            last = e
-    raise Exception("Unable to find a port to bind to: %s" % last)
+            error = e
+    raise Exception("Unable to find a port to bind to: %s" % error)

@@ -2,6 +2,8 @@
 chunks, two-level Adasum against the pairwise oracle applied level by level,
 uneven allgather / alltoall / reducescatter, overlapping process sets used
 concurrently, join with three survivors, fusion of mixed dtypes."""
+import os
+
 import torch
 
 from parallel_utils import run_parallel
@@ -156,34 +158,39 @@ def test_collectives_from_several_python_threads():
     assert all(run_parallel(_threads, np=2, timeout=300))
 
 
-def _grouped_extras(rank, size):
+def _grouped_extras(rank, size, groups_on_their_own=False):
+    if groups_on_their_own:
+        # every group is fused by itself, never with tensors outside it
+        os.environ["HOROVOD_DISABLE_GROUP_FUSION"] = "1"
     import horovod_b200.torch as hvd
     hvd.init()
-    gathered = hvd.grouped_allgather([torch.full((rank + 1, 2), float(rank)),
-                                      torch.full((2,), float(10 + rank))], name="gag")
-    ok = torch.equal(gathered[0], torch.cat([torch.full((r + 1, 2), float(r))
-                                             for r in range(size)]))
-    ok = ok and gathered[1].tolist() == [float(10 + r) for r in range(size) for _ in range(2)]
-    shards = hvd.grouped_reducescatter([torch.arange(size * 2, dtype=torch.float32) + rank,
-                                        torch.ones(size, 3) * (rank + 1)], op=hvd.Sum, name="grs")
-    tot = sum(range(size))
-    exp0 = (torch.arange(size * 2, dtype=torch.float32) * size + tot)[rank * 2:(rank + 1) * 2]
-    ok = ok and torch.equal(shards[0], exp0) and bool((shards[1] == sum(range(1, size + 1))).all())
-    # mixed dtypes in one group: the outputs keep the order of the inputs
-    mixed = hvd.grouped_reducescatter([torch.full((size, 2), float(rank + 1)),
-                                       torch.full((2 * size,), rank + 1, dtype=torch.int32),
-                                       torch.full((size,), float(rank + 1), dtype=torch.float64)],
-                                      op=hvd.Sum, name="grs.mixed")
-    tot = size * (size + 1) // 2
-    ok = ok and [m.dtype for m in mixed] == [torch.float32, torch.int32, torch.float64]
-    ok = ok and [tuple(m.shape) for m in mixed] == [(1, 2), (2,), (1,)]
-    ok = ok and all(bool((m.double() == tot).all()) for m in mixed)
-    h = hvd.grouped_allgather_async([torch.full((1,), rank, dtype=torch.int64),
-                                     torch.full((rank + 1,), float(rank))], name="gag.mixed")
-    got = hvd.synchronize(h)
-    ok = ok and got[0].tolist() == list(range(size))
-    ok = ok and got[1].tolist() == [float(r) for r in range(size) for _ in range(r + 1)]
-    ok = ok and hvd.grouped_allgather([], name="gag.none") == []
+    ok = True
+    for _ in range(2):  # the second pass finds the responses in the cache
+        gathered = hvd.grouped_allgather([torch.full((rank + 1, 2), float(rank)),
+                                          torch.full((2,), float(10 + rank))], name="gag")
+        ok = ok and torch.equal(gathered[0], torch.cat([torch.full((r + 1, 2), float(r))
+                                                 for r in range(size)]))
+        ok = ok and gathered[1].tolist() == [float(10 + r) for r in range(size) for _ in range(2)]
+        shards = hvd.grouped_reducescatter([torch.arange(size * 2, dtype=torch.float32) + rank,
+                                            torch.ones(size, 3) * (rank + 1)], op=hvd.Sum, name="grs")
+        tot = sum(range(size))
+        exp0 = (torch.arange(size * 2, dtype=torch.float32) * size + tot)[rank * 2:(rank + 1) * 2]
+        ok = ok and torch.equal(shards[0], exp0) and bool((shards[1] == sum(range(1, size + 1))).all())
+        # mixed dtypes in one group: the outputs keep the order of the inputs
+        mixed = hvd.grouped_reducescatter([torch.full((size, 2), float(rank + 1)),
+                                           torch.full((2 * size,), rank + 1, dtype=torch.int32),
+                                           torch.full((size,), float(rank + 1), dtype=torch.float64)],
+                                          op=hvd.Sum, name="grs.mixed")
+        tot = size * (size + 1) // 2
+        ok = ok and [m.dtype for m in mixed] == [torch.float32, torch.int32, torch.float64]
+        ok = ok and [tuple(m.shape) for m in mixed] == [(1, 2), (2,), (1,)]
+        ok = ok and all(bool((m.double() == tot).all()) for m in mixed)
+        h = hvd.grouped_allgather_async([torch.full((1,), rank, dtype=torch.int64),
+                                         torch.full((rank + 1,), float(rank))], name="gag.mixed")
+        got = hvd.synchronize(h)
+        ok = ok and got[0].tolist() == list(range(size))
+        ok = ok and got[1].tolist() == [float(r) for r in range(size) for _ in range(r + 1)]
+        ok = ok and hvd.grouped_allgather([], name="gag.none") == []
     hvd.barrier()
     hvd.shutdown()
     return ok
@@ -191,6 +198,12 @@ def _grouped_extras(rank, size):
 
 def test_grouped_allgather_reducescatter_and_barrier():
     assert all(run_parallel(_grouped_extras, np=3, timeout=300))
+
+
+def test_grouped_ops_with_groups_fused_on_their_own():
+    """HOROVOD_DISABLE_GROUP_FUSION=1: the same results, twice in one job so
+    that the second pass goes through the cached responses."""
+    assert all(run_parallel(_grouped_extras, np=3, args=(True,), timeout=300))
 
 
 def _alltoall_even_and_explicit(rank, size):

@@ -6,8 +6,8 @@ the driver. ``pyspark`` (3.0 or newer, for BarrierTaskContext.allGather) is
 imported at call time; the tests drive run() through a stand-in pyspark
 module, since pyspark itself is not installed here.
 Parity: horovod/spark/runner.py:197-305 (run). The elastic variant is in
-horovod_b200/spark/elastic.py; the Estimator API
-(horovod/spark/{keras,torch,lightning}) is not built.
+horovod_b200/spark/elastic.py, the estimator for PyTorch models in
+horovod_b200/spark/torch.
 """
 import os
 import socket

@@ -78,3 +78,16 @@ def test_ray_and_spark_examples_are_importable_without_their_frameworks():
         module = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(module)
         assert callable(module.train)
+
+
+def test_estimator_example_on_pandas(tmp_path):
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""),
+               CUDA_VISIBLE_DEVICES="")
+    proc = subprocess.run([sys.executable, "examples/spark_torch_estimator.py", "--num-proc", "2",
+                           "--rows", "512", "--epochs", "3", "--no-cuda", "--work-dir",
+                           str(tmp_path)], cwd=ROOT, env=env, capture_output=True, text=True,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    losses = [float(v) for v in re.findall(r"epoch \d+: train loss ([0-9.]+)", proc.stdout)]
+    assert len(losses) == 3 and losses[-1] < losses[0], proc.stdout[-1500:]
+    assert "label__output" in proc.stdout

@@ -72,7 +72,8 @@ class TorchEstimator(_Settings):
         label_cols=None, label_shapes=None, callbacks=None, batch_size=32, val_batch_size=None,
         epochs=1, verbose=1, shuffle=True, partitions_per_process=10, run_id=None,
         train_minibatch_fn=None, train_steps_per_epoch=None, validation_steps_per_epoch=None,
-        transformation_fn=None, inmemory_cache_all=False, random_seed=None, no_cuda=False)
+        transformation_fn=None, inmemory_cache_all=False, async_loader_queue_size=8,
+        random_seed=None, no_cuda=False)
 
     def __init__(self, **settings):
         super().__init__(**settings)
@@ -171,7 +172,7 @@ class TorchEstimator(_Settings):
             "gradient_compression", "batch_size", "val_batch_size", "epochs", "verbose",
             "shuffle", "train_minibatch_fn", "train_steps_per_epoch",
             "validation_steps_per_epoch", "transformation_fn", "inmemory_cache_all",
-            "random_seed", "callbacks", "no_cuda")}
+            "random_seed", "callbacks", "no_cuda", "async_loader_queue_size")}
         spec.update(run_id=run_id, metadata=metadata, train_rows=train_rows, val_rows=val_rows,
                     train_path=store.get_train_data_path(dataset_idx),
                     val_path=store.get_val_data_path(dataset_idx))

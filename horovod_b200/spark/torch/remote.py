@@ -84,41 +84,36 @@ def _train(spec, blob, cloudpickle, np, torch, hvd, dataset):
     columns = list(feature_cols) + list(label_cols) + ([weight_col] if weight_col else [])
     transformation = spec.get("transformation_fn")
 
-    def reader(path, batch, shuffle):
-        return iter(dataset.ParquetShardReader(
-            store, path, columns, batch, rank=hvd.rank(), size=hvd.size(), shuffle=shuffle,
-            seed=seed or 0, cache=spec.get("inmemory_cache_all", False),
-            transform=transformation))
+    def loader(path, rows, batch, shuffle, limit):
+        from horovod_b200.spark.data_loaders import AsyncParquetDataLoader
+        return AsyncParquetDataLoader(
+            store, path, columns, batch, rows, rank=hvd.rank(), size=hvd.size(), shuffle=shuffle,
+            seed=seed or 0, cache=spec.get("inmemory_cache_all", False), transform=transformation,
+            limit_step_per_epoch=limit, to_tensors=tensors,
+            async_loader_queue_size=spec.get("async_loader_queue_size", 8))
 
     batch_size = spec["batch_size"]
     val_batch_size = spec.get("val_batch_size") or batch_size
-    train_batches = reader(spec["train_path"], batch_size, spec.get("shuffle", True))
-    train_steps = dataset.steps_per_epoch(spec["train_rows"], batch_size, hvd.size(),
-                                          spec.get("train_steps_per_epoch"))
     validate = spec.get("val_rows", 0) > 0
-    if validate:
-        val_batches = reader(spec["val_path"], val_batch_size, False)
-        val_steps = dataset.steps_per_epoch(spec["val_rows"], val_batch_size, hvd.size(),
-                                            spec.get("validation_steps_per_epoch"))
+
+    def from_numpy(array):
+        array = np.ascontiguousarray(array)
+        return torch.from_numpy(array if array.flags.writeable else array.copy())
 
     def tensors(batch):
         def feature(i, col):
-            t = torch.from_numpy(np.ascontiguousarray(batch[col])).float()
+            t = from_numpy(batch[col]).float()
             if input_shapes:
-                t = t.reshape([-1] + [d for d in list(input_shapes[i])[1:]]) \
-                    if list(input_shapes[i])[0] == -1 else t.reshape(list(input_shapes[i]))
+                t = t.reshape(list(input_shapes[i]))
             elif t.dim() == 1 and metadata[col]["shape"] == ():
                 t = t.unsqueeze(1)
             return t.to(device)
 
         def label(col):
-            t = torch.from_numpy(np.ascontiguousarray(batch[col]))
+            t = from_numpy(batch[col])
             return (t.float() if t.dtype == torch.float64 else t).to(device)
 
-        sample_weights = None
-        if weight_col:
-            sample_weights = torch.from_numpy(np.ascontiguousarray(batch[weight_col])) \
-                .float().to(device)
+        sample_weights = from_numpy(batch[weight_col]).float().to(device) if weight_col else None
         return ([feature(i, c) for i, c in enumerate(feature_cols)],
                 [label(c) for c in label_cols], sample_weights)
 
@@ -167,12 +162,11 @@ def _train(spec, blob, cloudpickle, np, torch, hvd, dataset):
         from horovod_b200.parallel.data_parallel import average_metrics
         return average_metrics({k: v / max(steps, 1) for k, v in sums.items()})
 
-    def run_epoch(batches, steps, training):
+    def run_epoch(batches, training):
         sums = {"loss": 0.0}
         sums.update({n: 0.0 for n in metric_names()})
         model.train(training)
-        for _ in range(steps):
-            inputs, labels, sample_weights = tensors(next(batches))
+        for inputs, labels, sample_weights in batches:
             if training:
                 outputs, loss = minibatch(model, optimizer, transform_outputs, loss_fn, inputs,
                                           labels, sample_weights)
@@ -186,7 +180,7 @@ def _train(spec, blob, cloudpickle, np, torch, hvd, dataset):
                 for name, fn in zip(metric_names(), metrics):
                     sums[name] += float(fn(*[o.detach() for o in outputs], *labels)
                                         if len(outputs) > 1 else fn(outputs[0].detach(), labels[0]))
-        return summarize(sums, steps)
+        return summarize(sums, len(batches))
 
     def checkpoint_bytes():
         buffer = io.BytesIO()
@@ -194,6 +188,11 @@ def _train(spec, blob, cloudpickle, np, torch, hvd, dataset):
                     "optimizer": optimizer.state_dict()}, buffer)
         return buffer.getvalue()
 
+    train_batches = loader(spec["train_path"], spec["train_rows"], batch_size,
+                           spec.get("shuffle", True), spec.get("train_steps_per_epoch"))
+    if validate:
+        val_batches = loader(spec["val_path"], spec["val_rows"], val_batch_size, False,
+                             spec.get("validation_steps_per_epoch"))
     history = []
     callbacks = _as_list(spec.get("callbacks"))
     scratch = store.get_local_output_dir_fn(run_id)
@@ -201,9 +200,9 @@ def _train(spec, blob, cloudpickle, np, torch, hvd, dataset):
         log_path = os.path.join(out_dir, store.get_logs_subdir(), "history.jsonl")
         os.makedirs(os.path.dirname(log_path), exist_ok=True)
         for epoch in range(spec["epochs"]):
-            entry = {"epoch": epoch, "train": run_epoch(train_batches, train_steps, True)}
+            entry = {"epoch": epoch, "train": run_epoch(train_batches, True)}
             if validate:
-                entry["validation"] = run_epoch(val_batches, val_steps, False)
+                entry["validation"] = run_epoch(val_batches, False)
             history.append(entry)
             if verbose:
                 print("epoch %d: %s" % (epoch, entry), flush=True)

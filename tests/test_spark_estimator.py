@@ -319,3 +319,20 @@ def test_spark_paths_against_stand_ins(tmp_path, monkeypatch):
     assert backend.num_processes() == 3
     with pytest.raises(ImportError, match="pyspark"):
         SparkBackend().num_processes()
+
+
+def test_epoch_loaders_continue_where_the_last_epoch_stopped(tmp_path):
+    from horovod_b200.spark.data_loaders import AsyncParquetDataLoader, ParquetDataLoader
+    store = LocalStore(str(tmp_path))
+    dataset._write_pandas(store, _frame(10)[["row"]], store.get_train_data_path(), 2)
+    plain = ParquetDataLoader(store, store.get_train_data_path(), ["row"], 4, total_rows=10,
+                              shuffle=False, to_tensors=lambda b: b["row"].tolist())
+    assert len(plain) == 3
+    assert list(plain) == [[0, 1, 2, 3], [4, 5, 6, 7], [8, 9, 0, 1]]
+    assert list(plain) == [[2, 3, 4, 5], [6, 7, 8, 9], [0, 1, 2, 3]]
+    ahead = AsyncParquetDataLoader(store, store.get_train_data_path(), ["row"], 4, total_rows=10,
+                                   shuffle=False, limit_step_per_epoch=2,
+                                   async_loader_queue_size=2)
+    assert [b["row"].tolist() for b in ahead] == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    assert [b["row"].tolist() for b in ahead] == [[8, 9, 0, 1], [2, 3, 4, 5]]
+    ahead.close_async_loader()

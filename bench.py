@@ -666,13 +666,8 @@ def main():
     device = torch.device("cuda", hvd.local_rank())
     torch.backends.cudnn.benchmark = True
 
+    # The flagship measurement comes first; what follows it must not cost the line.
     rc = 0
-    checks = None
-    if hvd.size() > 1:
-        passed, failed = collective_checks(hvd, torch, device)
-        checks = {"passed": passed, "failed": failed}
-        if failed:
-            rc = 3
     out, in_sync = measure(args, args.model, hvd, torch, device, _C)
     if not in_sync:
         rc = 3
@@ -684,21 +679,30 @@ def main():
                 rc = 3
         except Exception as e:  # the flagship line must survive
             secondary = {"error": "%s: %s" % (type(e).__name__, e)}
-    single = None
+    single = bus = checks = None
     if hvd.size() > 1:
-        worst = loss_vs_single(hvd, torch, device,
-                               bool(args.symmetric_gradients and args.model == "resnet50"))
-        single = {"max_rel_diff_of_step_losses": worst, "tolerance": 1e-4, "steps": 5,
-                  "what": "2-layer causal LM, fp32, rank-specific batches through "
-                          "DistributedOptimizer vs plain SGD on the concatenated batch"}
-        if not worst <= 1e-4:
+        try:
+            worst = loss_vs_single(hvd, torch, device,
+                                   bool(args.symmetric_gradients and args.model == "resnet50"))
+            single = {"max_rel_diff_of_step_losses": worst, "tolerance": 1e-4, "steps": 5,
+                      "what": "2-layer causal LM, fp32, rank-specific batches through "
+                              "DistributedOptimizer vs plain SGD on the concatenated batch"}
+            if not worst <= 1e-4:
+                rc = 3
+        except Exception as e:  # the flagship line must survive
+            single = {"error": "%s: %s" % (type(e).__name__, e)}
             rc = 3
-    bus = None
-    if hvd.size() > 1:
         try:
             bus = allreduce_bus_bandwidth(hvd, torch, device)
         except Exception as e:  # the flagship line must survive
             bus = {"error": "%s: %s" % (type(e).__name__, e)}
+        try:
+            passed, failed = collective_checks(hvd, torch, device)
+            checks = {"passed": passed, "failed": failed}
+        except Exception as e:  # the flagship line must survive
+            checks = {"passed": 0, "failed": ["%s: %s" % (type(e).__name__, e)]}
+        if checks["failed"]:
+            rc = 3
     if hvd.rank() == 0:
         if bus is not None:
             out["allreduce_bus"] = bus

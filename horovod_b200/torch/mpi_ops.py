@@ -494,7 +494,7 @@ def symmetric_empty(*size, dtype=torch.float32):
     slices) runs without any staging copy: the kernel reduces the ranks'
     tensors directly over NVLink. The memory is never freed individually and
     becomes invalid at hvd.shutdown(). Size the heap with
-    HOROVOD_SYMM_HEAP_MB (default 2048)."""
+    HOROVOD_SYMM_HEAP_MB (default 4096)."""
     if len(size) == 1 and isinstance(size[0], (tuple, list, torch.Size)):
         size = tuple(size[0])
     if not gpu_backend().startswith("symm"):

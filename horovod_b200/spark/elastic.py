@@ -210,6 +210,12 @@ def run_elastic(fn, args=(), kwargs=None, num_proc=None, min_np=None, max_np=Non
 
     def spark_stage():
         def task(index, _iterator):
+            from horovod_b200.spark import task as task_info
+            try:
+                from pyspark import TaskContext
+                task_info.set_resources(task_info.resources_of(TaskContext.get()))
+            except ImportError:  # a pyspark without TaskContext: no resource information
+                task_info.set_resources({})
             _task_loop(index, addresses, key, fn, args, kwargs)
             yield index
         spark_context.range(0, numSlices=max_np).mapPartitionsWithIndex(task).collect()

@@ -61,6 +61,8 @@ def run(fn, args=(), kwargs=None, num_proc=None, extra_env=None, verbose=1):
         ctx = BarrierTaskContext.get()
         hostnames = ctx.allGather(socket.gethostname())
         rank = ctx.partitionId()
+        from horovod_b200.spark import task as task_info
+        task_info.set_resources(task_info.resources_of(ctx))
         local_rank, local_size, cross_rank, cross_size = _coordinates(hostnames, rank)
         os.environ.update({k: str(v) for k, v in extra.items()})
         os.environ.update({

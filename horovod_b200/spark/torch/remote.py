@@ -55,8 +55,12 @@ def _train(spec, blob, cloudpickle, np, torch, hvd, dataset):
     use_cuda = torch.cuda.is_available() and hvd.cuda_built() and not spec.get("no_cuda")
     device = torch.device("cpu")
     if use_cuda:
-        torch.cuda.set_device(hvd.local_rank())
-        device = torch.device("cuda", hvd.local_rank())
+        # a GPU that Spark's resource scheduling gave this task, else one per local rank
+        from horovod_b200.spark.task import get_available_devices
+        assigned = get_available_devices()
+        index = int(assigned[0]) if assigned else hvd.local_rank()
+        torch.cuda.set_device(index)
+        device = torch.device("cuda", index)
         model.to(device)
         for state in optimizer.state.values():
             for key, value in state.items():

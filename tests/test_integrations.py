@@ -300,6 +300,7 @@ def test_spark_run_with_a_stand_in_pyspark(monkeypatch):
     rendezvous server of the driver in its environment, and the results come
     back ordered by rank. The stand-in runs the tasks one after the other in
     this process, in reverse partition order."""
+    import horovod_b200.spark.task
     from horovod_b200.spark.runner import run
     hosts = ["a", "b", "a", "b"]
     current = {"partition": None}
@@ -315,6 +316,10 @@ def test_spark_run_with_a_stand_in_pyspark(monkeypatch):
 
         def partitionId(self):
             return current["partition"]
+
+        def resources(self):
+            # Spark's resource scheduling: one GPU address per task
+            return {"gpu": types.SimpleNamespace(addresses=[str(current["partition"] + 4)])}
 
     class RDD:
         def __init__(self, n):
@@ -357,13 +362,18 @@ def test_spark_run_with_a_stand_in_pyspark(monkeypatch):
             return (tag, int(e["HOROVOD_RANK"]), int(e["HOROVOD_SIZE"]),
                     int(e["HOROVOD_LOCAL_RANK"]), int(e["HOROVOD_LOCAL_SIZE"]),
                     int(e["HOROVOD_CROSS_RANK"]), int(e["HOROVOD_CROSS_SIZE"]),
-                    e["HOROVOD_HOSTNAME"], int(e["HOROVOD_GLOO_RENDEZVOUS_PORT"]) > 0, e["EXTRA"])
+                    e["HOROVOD_HOSTNAME"], int(e["HOROVOD_GLOO_RENDEZVOUS_PORT"]) > 0, e["EXTRA"],
+                    horovod_b200.spark.task.get_available_devices())
         results = run(fn, args=("t",), extra_env={"EXTRA": "x"}, verbose=0)  # num_proc inferred
     finally:
         os.environ.clear()
         os.environ.update(saved)
-    assert results == [("t", 0, 4, 0, 2, 0, 2, "a", True, "x"), ("t", 1, 4, 0, 2, 1, 2, "b", True, "x"),
-                       ("t", 2, 4, 1, 2, 0, 2, "a", True, "x"), ("t", 3, 4, 1, 2, 1, 2, "b", True, "x")]
+    assert results == [("t", 0, 4, 0, 2, 0, 2, "a", True, "x", ["4"]),
+                       ("t", 1, 4, 0, 2, 1, 2, "b", True, "x", ["5"]),
+                       ("t", 2, 4, 1, 2, 0, 2, "a", True, "x", ["6"]),
+                       ("t", 3, 4, 1, 2, 1, 2, "b", True, "x", ["7"])]
+    horovod_b200.spark.task.set_resources(None)
+    assert horovod_b200.spark.task.get_available_devices() == []
 
 
 def test_spark_run_elastic_with_tasks_as_child_processes(monkeypatch):

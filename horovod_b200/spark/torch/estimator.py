@@ -221,35 +221,9 @@ class TorchModel(_Settings):
 
     # ---- prediction ---------------------------------------------------------------
     def _predict_pandas(self, pdf, model=None):
-        import numpy as np
-        import torch
         v = self._values
-        model = model or v["model"]
-        model.eval()
-        outputs = [[] for _ in v["output_cols"]]
-        for start in range(0, len(pdf), v["batch_size"]):
-            part = pdf.iloc[start:start + v["batch_size"]]
-            inputs = []
-            for i, col in enumerate(v["feature_columns"]):
-                values = part[col].to_numpy()
-                if values.dtype == object:
-                    values = np.stack([np.asarray(x) for x in values])
-                t = torch.tensor(np.asarray(values), dtype=torch.float32)
-                if v["input_shapes"]:
-                    t = t.reshape(list(v["input_shapes"][i]))
-                elif t.dim() == 1:
-                    t = t.unsqueeze(1)
-                inputs.append(t)
-            with torch.no_grad():
-                result = model(*inputs)
-            result = list(result) if isinstance(result, (tuple, list)) else [result]
-            for sink, value in zip(outputs, result):
-                sink.append(value.reshape(len(part), -1).cpu().numpy())
-        scored = pdf.copy()
-        for name, chunks in zip(v["output_cols"], outputs):
-            joined = np.concatenate(chunks) if chunks else np.zeros((0, 1), dtype=np.float32)
-            scored[name] = joined[:, 0] if joined.shape[1] == 1 else list(joined)
-        return scored
+        return _predict(pdf, model or v["model"], v["feature_columns"], v["input_shapes"],
+                        v["output_cols"], v["batch_size"])
 
     def transform(self, df, params=None):
         """Returns ``df`` with one prediction column per label column
@@ -269,13 +243,15 @@ class TorchModel(_Settings):
             kinds.append("%s %s" % (name, "array<double>" if hasattr(first, "__len__") else "double"))
         schema = ", ".join(["%s %s" % (f.name, f.dataType.simpleString())
                             for f in df.schema.fields] + kinds)
-        me = self
+        # only what scoring needs travels to the executors
+        features, shapes = v["feature_columns"], v["input_shapes"]
+        outputs, batch = v["output_cols"], v["batch_size"]
 
         def score(frames):
             model = cloudpickle.loads(blob)
             for pdf in frames:
-                scored = me._predict_pandas(pdf, model)
-                for name in v["output_cols"]:
+                scored = _predict(pdf, model, features, shapes, outputs, batch)
+                for name in outputs:
                     scored[name] = [x.astype("float64").tolist() if hasattr(x, "__len__")
                                     else float(x) for x in scored[name]]
                 yield scored
@@ -296,3 +272,34 @@ class TorchModel(_Settings):
         import cloudpickle
         with open(path, "rb") as f:
             return cls(**cloudpickle.load(f))
+
+
+def _predict(pdf, model, feature_columns, input_shapes, output_cols, batch_size):
+    """``pdf`` plus the model's outputs as new columns, computed in batches."""
+    import numpy as np
+    import torch
+    model.eval()
+    outputs = [[] for _ in output_cols]
+    for start in range(0, len(pdf), batch_size):
+        part = pdf.iloc[start:start + batch_size]
+        inputs = []
+        for i, col in enumerate(feature_columns):
+            values = part[col].to_numpy()
+            if values.dtype == object:
+                values = np.stack([np.asarray(x) for x in values])
+            t = torch.tensor(np.asarray(values), dtype=torch.float32)
+            if input_shapes:
+                t = t.reshape(list(input_shapes[i]))
+            elif t.dim() == 1:
+                t = t.unsqueeze(1)
+            inputs.append(t)
+        with torch.no_grad():
+            result = model(*inputs)
+        result = list(result) if isinstance(result, (tuple, list)) else [result]
+        for sink, value in zip(outputs, result):
+            sink.append(value.reshape(len(part), -1).cpu().numpy())
+    scored = pdf.copy()
+    for name, chunks in zip(output_cols, outputs):
+        joined = np.concatenate(chunks) if chunks else np.zeros((0, 1), dtype=np.float32)
+        scored[name] = joined[:, 0] if joined.shape[1] == 1 else list(joined)
+    return scored

@@ -173,7 +173,7 @@ def _task_loop(index, addresses, key, fn, args, kwargs, poll=0.2):
 
 
 def run_elastic(fn, args=(), kwargs=None, num_proc=None, min_np=None, max_np=None,
-                start_timeout=60, elastic_timeout=600, reset_limit=None, env=None, nics=None,
+                start_timeout=None, elastic_timeout=600, reset_limit=None, env=None, nics=None,
                 verbose=1):
     """Runs ``fn(*args, **kwargs)`` (which uses ``hvd.elastic.run`` inside) on
     between ``min_np`` and ``max_np`` Spark tasks and returns the results of
@@ -185,6 +185,9 @@ def run_elastic(fn, args=(), kwargs=None, num_proc=None, min_np=None, max_np=Non
     from horovod_b200.runner.http.http_server import RendezvousServer, local_ip_for
     pyspark = _require_pyspark()
     kwargs = kwargs or {}
+    if start_timeout is None:
+        # how long to wait for min_np tasks to register (horovod/spark/runner.py:219-223)
+        start_timeout = int(os.environ.get("HOROVOD_SPARK_START_TIMEOUT", "600"))
     spark_context = pyspark.SparkContext._active_spark_context
     if spark_context is None:
         raise Exception("Could not find an active SparkContext, are you running in a "

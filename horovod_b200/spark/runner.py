@@ -36,13 +36,21 @@ def _coordinates(hostnames, rank):
     return local_rank, len(mine), hosts_with.index(hostnames[rank]), len(hosts_with)
 
 
-def run(fn, args=(), kwargs=None, num_proc=None, extra_env=None, verbose=1):
+def run(fn, args=(), kwargs=None, num_proc=None, start_timeout=None, extra_env=None, verbose=1):
     """Runs ``fn(*args, **kwargs)`` on ``num_proc`` ranks inside Spark tasks;
-    returns the list of results ordered by rank."""
+    returns the list of results ordered by rank. If the tasks have not all
+    started within ``start_timeout`` seconds (default: the environment
+    variable HOROVOD_SPARK_START_TIMEOUT, else 600) the Spark job is cancelled
+    and an exception says that the cluster lacks the resources for
+    ``num_proc`` simultaneous tasks."""
+    import threading
     pyspark = _require_pyspark()
     from pyspark import BarrierTaskContext
+    from horovod_b200.runner.http.http_client import put_data_into_kvstore
     from horovod_b200.runner.http.http_server import RendezvousServer, local_ip_for
     kwargs = kwargs or {}
+    if start_timeout is None:
+        start_timeout = int(os.environ.get("HOROVOD_SPARK_START_TIMEOUT", "600"))
     spark_context = pyspark.SparkContext._active_spark_context
     if spark_context is None:
         raise Exception("Could not find an active SparkContext, are you running in a "
@@ -61,6 +69,8 @@ def run(fn, args=(), kwargs=None, num_proc=None, extra_env=None, verbose=1):
         ctx = BarrierTaskContext.get()
         hostnames = ctx.allGather(socket.gethostname())
         rank = ctx.partitionId()
+        # the barrier has let every task through: tell the driver that the job has started
+        put_data_into_kvstore(driver_ip, port, _STARTED_SCOPE, str(rank), b"1")
         from horovod_b200.spark import task as task_info
         task_info.set_resources(task_info.resources_of(ctx))
         local_rank, local_size, cross_rank, cross_size = _coordinates(hostnames, rank)
@@ -76,9 +86,48 @@ def run(fn, args=(), kwargs=None, num_proc=None, extra_env=None, verbose=1):
         })
         yield rank, fn(*args, **kwargs)
 
+    group = "horovod_b200.spark.run.%d" % port
+    outcome = {}
+
+    def stage():
+        try:
+            if hasattr(spark_context, "setJobGroup"):
+                spark_context.setJobGroup(group, "horovod_b200.spark.run", interruptOnCancel=True)
+            outcome["pairs"] = spark_context.range(0, numSlices=num_proc).barrier() \
+                .mapPartitionsWithIndex(task).collect()
+        except BaseException as e:  # noqa: BLE001 - re-raised in the caller's thread
+            outcome["error"] = e
+
+    worker = threading.Thread(target=stage, daemon=True, name="hvd-spark-stage")
     try:
-        pairs = spark_context.range(0, numSlices=num_proc).barrier() \
-            .mapPartitionsWithIndex(task).collect()
+        worker.start()
+        if not _wait_for_start(server, worker, start_timeout):
+            if hasattr(spark_context, "cancelJobGroup"):
+                spark_context.cancelJobGroup(group)
+            raise Exception(
+                "Timed out waiting for the Spark tasks to start. Please check that you have "
+                "enough resources to run all %d processes at the same time: each process runs "
+                "in its own Spark task. Raise start_timeout (now %d s) if the cluster is only "
+                "slow to hand out executors." % (num_proc, start_timeout))
+        worker.join()
     finally:
         server.stop()
-    return [result for _rank, result in sorted(pairs, key=lambda p: p[0])]
+    if "error" in outcome:
+        raise outcome["error"]
+    return [result for _rank, result in sorted(outcome["pairs"], key=lambda p: p[0])]
+
+
+_STARTED_SCOPE = "spark_task_started"
+
+
+def _wait_for_start(server, worker, timeout, poll=0.05):
+    """True once a task has checked in (the barrier releases all of them
+    together) or the stage has ended; False when ``timeout`` seconds passed
+    first."""
+    import time
+    deadline = time.monotonic() + timeout
+    while time.monotonic() < deadline:
+        if not worker.is_alive() or server.get(_STARTED_SCOPE, "0") is not None:
+            return True
+        time.sleep(poll)
+    return not worker.is_alive() or server.get(_STARTED_SCOPE, "0") is not None

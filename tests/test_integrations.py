@@ -376,6 +376,51 @@ def test_spark_run_with_a_stand_in_pyspark(monkeypatch):
     assert horovod_b200.spark.task.get_available_devices() == []
 
 
+def test_spark_run_gives_up_when_the_tasks_do_not_start(monkeypatch):
+    """A cluster without room for num_proc simultaneous tasks never starts the
+    barrier stage: run() cancels its job group after start_timeout and says
+    what to check."""
+    import threading
+    from horovod_b200.spark.runner import run
+    released = threading.Event()
+    cancelled = []
+    pyspark = types.ModuleType("pyspark")
+
+    class RDD:
+        def barrier(self):
+            return self
+
+        def mapPartitionsWithIndex(self, task):
+            return self
+
+        def collect(self):
+            released.wait(10)  # the scheduler never finds the slots
+            raise RuntimeError("job group cancelled")
+
+    class SparkContext:
+        _active_spark_context = None
+        defaultParallelism = 2
+
+        def range(self, start, numSlices=None):
+            return RDD()
+
+        def setJobGroup(self, group, description, interruptOnCancel=False):
+            self.group = group
+
+        def cancelJobGroup(self, group):
+            cancelled.append(group == self.group)
+            released.set()
+
+    pyspark.BarrierTaskContext = object
+    pyspark.SparkContext = SparkContext
+    SparkContext._active_spark_context = SparkContext()
+    monkeypatch.setitem(sys.modules, "pyspark", pyspark)
+    monkeypatch.setenv("HOROVOD_SPARK_START_TIMEOUT", "1")
+    with pytest.raises(Exception, match="enough resources to run all 2 processes"):
+        run(lambda: 0, verbose=0)
+    assert cancelled == [True]
+
+
 def test_spark_run_elastic_with_tasks_as_child_processes(monkeypatch):
     """run_elastic() against a stand-in pyspark whose stage runs every task in
     a forked child process: the tasks register with the coordinator over the

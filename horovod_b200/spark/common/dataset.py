@@ -172,6 +172,34 @@ def _split(df, validation, seed):
     return train, val
 
 
+_prepared = {}  # cache key -> (train_rows, val_rows, metadata, row_bytes)
+_prepared_frames = {}  # cache key -> weak reference to the pandas frame it was made from
+
+
+def clear_training_cache():
+    """Forgets which DataFrames are already in a store, so that the next fit
+    writes its data again (horovod/spark/common/util.py clear_training_cache)."""
+    _prepared.clear()
+    _prepared_frames.clear()
+
+
+def _frame_key(df):
+    """Identifies the content of a DataFrame cheaply: Spark's hash of the
+    logical plan, or the object and shape of a pandas frame."""
+    if _is_pandas(df):
+        return ("pandas", id(df), df.shape, tuple(df.columns))
+    plan_hash = getattr(df, "semanticHash", None)
+    return ("spark", plan_hash() if callable(plan_hash) else id(df))
+
+
+def _same_frame(key, df):
+    """An object id can be handed out again after its frame was collected."""
+    if not _is_pandas(df):
+        return True
+    ref = _prepared_frames.get(key)
+    return ref is not None and ref() is df
+
+
 @contextlib.contextmanager
 def prepare_data(num_proc, store, df, label_columns, feature_columns, validation=None,
                  sample_weight_col=None, partitions_per_process=10, dataset_idx=None,
@@ -185,6 +213,14 @@ def prepare_data(num_proc, store, df, label_columns, feature_columns, validation
     files = max(1, int(num_proc) * int(partitions_per_process))
     train_path = store.get_train_data_path(dataset_idx)
     val_path = store.get_val_data_path(dataset_idx)
+    # The same DataFrame prepared the same way is not written twice (repeated
+    # fits of a parameter search); the files must still be there.
+    key = (_frame_key(df), tuple(keep), repr(validation), files, train_path, seed)
+    if key in _prepared and _same_frame(key, df) and dataset_exists(store, train_path):
+        if verbose:
+            print("using the training data already at %s" % train_path)
+        yield _prepared[key]
+        return
     if _is_pandas(df):
         absent = [c for c in keep if c not in df.columns]
         if absent:
@@ -208,7 +244,13 @@ def prepare_data(num_proc, store, df, label_columns, feature_columns, validation
             val_rows = read_metadata(store, val_path, columns)[0]
     if verbose:
         print("train_rows=%d val_rows=%d avg_row_size=%d" % (train_rows, val_rows, row_bytes))
-    yield train_rows, val_rows, metadata, row_bytes
+    for stale in [k for k in _prepared if k[4] == train_path]:
+        del _prepared[stale]  # the path now holds this data
+    _prepared[key] = (train_rows, val_rows, metadata, row_bytes)
+    if _is_pandas(df):
+        import weakref
+        _prepared_frames[key] = weakref.ref(df)
+    yield _prepared[key]
 
 
 class ParquetShardReader:

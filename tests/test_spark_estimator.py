@@ -56,6 +56,17 @@ def test_prepare_data_writes_shards_and_describes_columns(tmp_path):
     # a fraction picks about that share of the rows; writing again replaces the data
     with dataset.prepare_data(1, store, df, ["y"], ["z"], validation=0.25, seed=3) as (tr, va, _m, _b):
         assert tr + va == 100 and 10 <= va <= 40
+    # the same frame prepared the same way again is served from the cache: no file is rewritten
+    def stamp():
+        path = store.get_train_data_path()
+        return sorted((n, os.stat(os.path.join(path, n)).st_mtime_ns) for n in os.listdir(path))
+    with dataset.prepare_data(1, store, df, ["y"], ["z"], validation=0.25, seed=3) as first:
+        written = stamp()
+    with dataset.prepare_data(1, store, df, ["y"], ["z"], validation=0.25, seed=3) as second:
+        assert second == first and stamp() == written
+    dataset.clear_training_cache()
+    with dataset.prepare_data(1, store, df, ["y"], ["z"], validation=0.25, seed=3) as third:
+        assert third == first and stamp() != written
     with pytest.raises(ValueError, match="not in the DataFrame"):
         with dataset.prepare_data(1, store, df, ["nope"], ["z"]):
             pass

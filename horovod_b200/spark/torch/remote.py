@@ -200,25 +200,31 @@ def _train(spec, blob, cloudpickle, np, torch, hvd, dataset):
     history = []
     callbacks = _as_list(spec.get("callbacks"))
     scratch = store.get_local_output_dir_fn(run_id)
-    with scratch() as out_dir:
-        log_path = os.path.join(out_dir, store.get_logs_subdir(), "history.jsonl")
-        os.makedirs(os.path.dirname(log_path), exist_ok=True)
-        for epoch in range(spec["epochs"]):
-            entry = {"epoch": epoch, "train": run_epoch(train_batches, True)}
-            if validate:
-                entry["validation"] = run_epoch(val_batches, False)
-            history.append(entry)
-            if verbose:
-                print("epoch %d: %s" % (epoch, entry), flush=True)
-            for callback in callbacks:
-                callback(epoch, entry, model, optimizer)
-            if hvd.rank() == 0 and store.saving_runs():
-                import json
-                with open(os.path.join(out_dir, store.get_checkpoint_filename()), "wb") as f:
-                    f.write(checkpoint_bytes())
-                with open(log_path, "a") as f:
-                    f.write(json.dumps(entry) + "\n")
-                store.sync_fn(run_id)(out_dir)
-        if hvd.rank() == 0:
-            return history, checkpoint_bytes()
+    try:
+        with scratch() as out_dir:
+            log_path = os.path.join(out_dir, store.get_logs_subdir(), "history.jsonl")
+            os.makedirs(os.path.dirname(log_path), exist_ok=True)
+            for epoch in range(spec["epochs"]):
+                entry = {"epoch": epoch, "train": run_epoch(train_batches, True)}
+                if validate:
+                    entry["validation"] = run_epoch(val_batches, False)
+                history.append(entry)
+                if verbose:
+                    print("epoch %d: %s" % (epoch, entry), flush=True)
+                for callback in callbacks:
+                    callback(epoch, entry, model, optimizer)
+                if hvd.rank() == 0 and store.saving_runs():
+                    import json
+                    with open(os.path.join(out_dir, store.get_checkpoint_filename()), "wb") as f:
+                        f.write(checkpoint_bytes())
+                    with open(log_path, "a") as f:
+                        f.write(json.dumps(entry) + "\n")
+                    store.sync_fn(run_id)(out_dir)
+            if hvd.rank() == 0:
+                return history, checkpoint_bytes()
+    finally:
+        # an error in the middle of an epoch must not leave a reader thread behind
+        train_batches.close_async_loader()
+        if validate:
+            val_batches.close_async_loader()
     return None

@@ -36,14 +36,21 @@ def _coordinates(hostnames, rank):
     return local_rank, len(mine), hosts_with.index(hostnames[rank]), len(hosts_with)
 
 
-def run(fn, args=(), kwargs=None, num_proc=None, start_timeout=None, extra_env=None, verbose=1):
+def run(fn, args=(), kwargs=None, num_proc=None, start_timeout=None, use_mpi=None, use_gloo=None,
+        env=None, extra_env=None, nics=None, verbose=1):
     """Runs ``fn(*args, **kwargs)`` on ``num_proc`` ranks inside Spark tasks;
     returns the list of results ordered by rank. If the tasks have not all
     started within ``start_timeout`` seconds (default: the environment
     variable HOROVOD_SPARK_START_TIMEOUT, else 600) the Spark job is cancelled
     and an exception says that the cluster lacks the resources for
-    ``num_proc`` simultaneous tasks."""
+    ``num_proc`` simultaneous tasks. ``env`` (or ``extra_env``) is added to
+    every rank's environment; ``nics`` names the network interfaces the ranks
+    may use; the ranks always meet through this package's TCP rendezvous, so
+    ``use_mpi=True`` is refused."""
     import threading
+    if use_mpi:
+        raise ValueError("horovod_b200.spark.run has no MPI controller; leave use_mpi unset "
+                         "(the ranks rendezvous over TCP, as with use_gloo=True).")
     pyspark = _require_pyspark()
     from pyspark import BarrierTaskContext
     from horovod_b200.runner.http.http_client import put_data_into_kvstore
@@ -63,7 +70,12 @@ def run(fn, args=(), kwargs=None, num_proc=None, start_timeout=None, extra_env=N
     port = server.start()
     server.init([None] * num_proc)
     driver_ip = local_ip_for()
-    extra = dict(extra_env or {})
+    extra = dict(env or {})
+    extra.update(extra_env or {})
+    if nics:
+        names = ",".join(sorted(nics)) if not isinstance(nics, str) else nics
+        extra.setdefault("HOROVOD_GLOO_IFACE", names.split(",")[0])
+        extra.setdefault("NCCL_SOCKET_IFNAME", names)
 
     def task(index, _iterator):
         ctx = BarrierTaskContext.get()

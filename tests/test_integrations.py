@@ -364,7 +364,11 @@ def test_spark_run_with_a_stand_in_pyspark(monkeypatch):
                     int(e["HOROVOD_CROSS_RANK"]), int(e["HOROVOD_CROSS_SIZE"]),
                     e["HOROVOD_HOSTNAME"], int(e["HOROVOD_GLOO_RENDEZVOUS_PORT"]) > 0, e["EXTRA"],
                     horovod_b200.spark.task.get_available_devices())
-        results = run(fn, args=("t",), extra_env={"EXTRA": "x"}, verbose=0)  # num_proc inferred
+        with pytest.raises(ValueError, match="MPI"):
+            run(fn, use_mpi=True)
+        results = run(fn, args=("t",), env={"EXTRA": "overridden"}, extra_env={"EXTRA": "x"},
+                      use_gloo=True, nics=["eth7"], verbose=0)  # num_proc inferred
+        assert os.environ["HOROVOD_GLOO_IFACE"] == "eth7"
     finally:
         os.environ.clear()
         os.environ.update(saved)

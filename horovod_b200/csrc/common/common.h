@@ -256,8 +256,11 @@ struct TensorTableEntry {
 
 int64_t NowMicros();
 
-// Pins the calling thread to one CPU core (HOROVOD_THREAD_AFFINITY).
+// Pins the calling thread to one CPU core (HOROVOD_THREAD_AFFINITY); a
+// negative core leaves the thread alone.
 void SetThreadAffinity(int core);
+// The core that a HOROVOD_THREAD_AFFINITY value names for `local_rank`, or -1.
+int AffinityCore(const std::string& spec, int local_rank);
 
 inline int64_t RoundUp(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 

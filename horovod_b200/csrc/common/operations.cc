@@ -217,7 +217,7 @@ void DiscoverLayout(GlobalState& s) {
 void BackgroundThreadLoop(GlobalState& s) {
   SetLogRank(s.config.rank);
   try {
-    SetThreadAffinity(static_cast<int>(EnvInt(HVD_ENV_THREAD_AFFINITY, -1)));
+    SetThreadAffinity(AffinityCore(EnvString(HVD_ENV_THREAD_AFFINITY), s.config.local_rank));
     double timeout = EnvDouble(HVD_ENV_TIMEOUT_SECONDS, 30.0);
     s.mesh.set_timeout(timeout);
     if (s.config.size > 1) {

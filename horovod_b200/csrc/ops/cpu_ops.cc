@@ -7,6 +7,7 @@
 #include <cstring>
 
 #include "../common/cpu_vector.h"
+#include "../common/env.h"
 #include "../common/fusion_buffer_manager.h"
 #include "../common/global_state.h"
 #include "../common/half.h"
@@ -320,6 +321,25 @@ void AdasumCombineReference(const double* a, const double* b, double* out,
   for (int64_t i = 0; i < n; ++i) out[i] = ca * a[i] + cb * b[i];
 }
 
+namespace {
+// Exchanges with `peer` in pieces of at most HOROVOD_ADASUM_MPI_CHUNK_SIZE
+// bytes (default 1 GiB; horovod/common/ops/adasum/adasum_mpi.cc:29-125 caps
+// its MPI messages the same way). Both sides walk the same number of pieces:
+// what one sends the other receives.
+void ChunkedSendRecv(Comm& comm, int peer, const char* sbuf, size_t slen, char* rbuf,
+                     size_t rlen) {
+  static const size_t chunk =
+      static_cast<size_t>(std::max<int64_t>(1, EnvInt(HVD_ENV_ADASUM_CHUNK, int64_t{1} << 30)));
+  size_t so = 0, ro = 0;
+  do {
+    size_t sn = std::min(chunk, slen - so), rn = std::min(chunk, rlen - ro);
+    comm.SendRecv(peer, sbuf + so, sn, peer, rbuf + ro, rn);
+    so += sn;
+    ro += rn;
+  } while (so < slen || ro < rlen);
+}
+}  // namespace
+
 void AdasumCPU(Comm& comm, void* buffer, DataType dtype,
                const std::vector<int64_t>& offsets,
                const std::vector<int64_t>& counts, int64_t total) {
@@ -347,9 +367,9 @@ void AdasumCPU(Comm& comm, void* buffer, DataType dtype,
     int64_t send_lo = lower ? mid : lo, send_hi = lower ? hi : mid;
     int64_t keep_n = keep_hi - keep_lo;
     recv.resize(static_cast<size_t>(keep_n * es));
-    comm.SendRecv(peer, data + send_lo * es,
-                  static_cast<size_t>((send_hi - send_lo) * es), peer,
-                  recv.data(), static_cast<size_t>(keep_n * es));
+    ChunkedSendRecv(comm, peer, data + send_lo * es,
+                    static_cast<size_t>((send_hi - send_lo) * es), recv.data(),
+                    static_cast<size_t>(keep_n * es));
     // "a" is always the lower group's vector, "b" the upper group's.
     const char* mine = data + keep_lo * es;
     const void* a = lower ? static_cast<const void*>(mine) : recv.data();
@@ -422,9 +442,8 @@ void AdasumCPU(Comm& comm, void* buffer, DataType dtype,
     int64_t mid = range.first + (range.second - range.first) / 2;
     int64_t other_lo = lower ? mid : range.first;
     int64_t other_hi = lower ? range.second : mid;
-    comm.SendRecv(peer, data + lo * es, static_cast<size_t>((hi - lo) * es),
-                  peer, data + other_lo * es,
-                  static_cast<size_t>((other_hi - other_lo) * es));
+    ChunkedSendRecv(comm, peer, data + lo * es, static_cast<size_t>((hi - lo) * es),
+                    data + other_lo * es, static_cast<size_t>((other_hi - other_lo) * es));
     lo = range.first;
     hi = range.second;
   }

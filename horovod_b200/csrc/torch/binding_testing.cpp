@@ -164,6 +164,9 @@ void BindTesting(py::module_& root) {
     for (auto& r : out.responses) groups.push_back(r.names);
     return groups;
   });
+  m.def("affinity_core", [](const std::string& spec, int local_rank) {
+    return AffinityCore(spec, local_rank);
+  }, "Core that a HOROVOD_THREAD_AFFINITY value names for a local rank (-1: none).");
   // The exchange planner on plain numbers: blocks are (src_rank, dst_rank,
   // src address or 0, dst address or 0, bytes) as rank `rank` sees them;
   // returns one entry per round: (stage segments (src, self_dst, off, bytes,

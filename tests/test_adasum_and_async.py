@@ -65,6 +65,31 @@ def test_adasum_closed_forms_and_stability():
         assert not bad, bad
 
 
+def _adasum_in_small_pieces(rank, size):
+    import os
+    # 100-byte pieces: every exchange of halves takes several, of uneven length
+    os.environ["HOROVOD_ADASUM_MPI_CHUNK_SIZE"] = "100"
+    import horovod_b200.torch as hvd
+    hvd.init()
+    n = 1000 + 7
+    mine = torch.randn(n, generator=torch.Generator().manual_seed(40 + rank), dtype=torch.float64)
+    got = hvd.allreduce(mine.clone(), op=hvd.Adasum, name="pieces")
+    vectors = [torch.randn(n, generator=torch.Generator().manual_seed(40 + r), dtype=torch.float64)
+               for r in range(size)]
+    while len(vectors) > 1:  # the same pairwise tree on whole vectors
+        nxt = []
+        for a, b in zip(vectors[0::2], vectors[1::2]):
+            dot, na, nb = float(a @ b), float(a @ a), float(b @ b)
+            nxt.append((1 - dot / (2 * na)) * a + (1 - dot / (2 * nb)) * b)
+        vectors = nxt
+    hvd.shutdown()
+    return bool(torch.allclose(got, vectors[0], rtol=1e-10, atol=1e-12))
+
+
+def test_adasum_exchanges_in_pieces_of_the_chunk_size():
+    assert all(run_parallel(_adasum_in_small_pieces, np=4, timeout=300))
+
+
 def _async_fused(rank, size):
     import time
     import horovod_b200.torch as hvd

@@ -263,3 +263,12 @@ def test_build_and_extension_queries(monkeypatch):
     assert "HVD_UTIL_PROBE" not in os.environ
     import horovod_b200.torch as hvd
     assert hvd.check_extension is util.check_extension
+
+
+def test_thread_affinity_value_is_one_core_or_one_per_local_rank():
+    t = _C.testing
+    assert t.affinity_core("", 0) == -1
+    assert t.affinity_core("5", 0) == 5 and t.affinity_core("5", 3) == 5
+    assert [t.affinity_core("0,2,4,6", r) for r in range(4)] == [0, 2, 4, 6]
+    assert t.affinity_core("0,2", 2) == -1          # no entry for this local rank
+    assert t.affinity_core("0,x", 1) == -1 and t.affinity_core("-3", 0) == -1

@@ -224,6 +224,10 @@ GpuOps::GpuOps(GlobalState& s, int slot, int lane, int lanes)
   forced_algo_ = EnvString(HVD_ENV_ALGO, "auto");
   timing_ = EnvBool("HOROVOD_GPU_OP_TIMING", false);
   inline_descriptors_ = EnvBool("HOROVOD_INLINE_DESCRIPTORS", true);
+  if (slot == 0 && lane == 0 && !EnvBool(HVD_ENV_BATCH_D2D_MEMCOPIES, true))
+    HVD_LOG(WARNING) << HVD_ENV_BATCH_D2D_MEMCOPIES
+                     << "=0 has no effect: fused tensors are always moved by one kernel per "
+                        "response (there is no per-tensor copy path).";
   if (slot == 0 && lane == 0) g_current = this;  // diagnostics and the symmetric heap
   std::lock_guard<std::mutex> l(g_registry_mu_ref());
   g_registry_ref().push_back(this);

@@ -569,12 +569,33 @@ Status GpuOps::Complete(std::vector<TensorTableEntry>& entries) {
     finished = TimedEvent();
     HVD_CUDA(cudaEventRecord(finished, stream_));
   }
-  finalizer_.Submit([this, shared, done, marks, finished] {
-    cudaError_t err = cudaEventSynchronize(static_cast<cudaEvent_t>(done.get()));
-    Status st = err == cudaSuccess
-                    ? CheckKernelStatus()
-                    : Status::UnknownError(std::string("CUDA error: ") +
-                                           cudaGetErrorString(err));
+  // Elastic jobs with NCCL communicators: poll instead of blocking, and ask
+  // NCCL for asynchronous errors meanwhile; a peer that died then ends this
+  // wait with an error (the communicators are aborted) instead of hanging it.
+  NcclOps* watch = state_.elastic_enabled && nccl_ && nccl_->HasCommunicators() ? nccl_.get()
+                                                                               : nullptr;
+  finalizer_.Submit([this, shared, done, marks, finished, watch] {
+    cudaEvent_t done_event = static_cast<cudaEvent_t>(done.get());
+    cudaError_t err = cudaSuccess;
+    Status async_status = Status::OK();
+    if (watch != nullptr) {
+      async_status = WaitPolling(
+          [&] {
+            cudaError_t q = cudaEventQuery(done_event);
+            if (q == cudaSuccess) return 1;
+            if (q == cudaErrorNotReady) return 0;
+            err = q;
+            return -1;
+          },
+          [&] { return watch->CheckAsyncErrors(); }, std::chrono::microseconds(200),
+          std::chrono::milliseconds(5000));
+    } else {
+      err = cudaEventSynchronize(done_event);
+    }
+    Status st = err != cudaSuccess ? Status::UnknownError(std::string("CUDA error: ") +
+                                                          cudaGetErrorString(err))
+                : !async_status.ok() ? async_status
+                                     : CheckKernelStatus();
     // Replay the phases with the times the device went through them.
     Timeline& timeline = state_.timeline;
     for (auto& m : *marks) {

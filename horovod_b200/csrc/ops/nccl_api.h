@@ -11,6 +11,7 @@ struct NcclApi {
   ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int);
   ncclResult_t (*CommDestroy)(ncclComm_t);
   ncclResult_t (*CommAbort)(ncclComm_t);
+  ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*);
   const char* (*GetErrorString)(ncclResult_t);
   ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t,
                             ncclRedOp_t, ncclComm_t, cudaStream_t);

@@ -41,6 +41,7 @@ const NcclApi* LoadNccl(std::string* error) {
       HVD_NCCL_SYM(CommInitRank, "ncclCommInitRank");
       HVD_NCCL_SYM(CommDestroy, "ncclCommDestroy");
       HVD_NCCL_SYM(CommAbort, "ncclCommAbort");
+      HVD_NCCL_SYM(CommGetAsyncError, "ncclCommGetAsyncError");
       HVD_NCCL_SYM(GetErrorString, "ncclGetErrorString");
       HVD_NCCL_SYM(AllReduce, "ncclAllReduce");
       HVD_NCCL_SYM(Broadcast, "ncclBroadcast");
@@ -106,23 +107,20 @@ NcclOps::NcclOps(GpuOps& gpu)
   std::string err;
   api_ = LoadNccl(&err);
   if (api_ == nullptr) HVD_LOG(WARNING) << "NCCL path unavailable: " << err;
+  comms_.set_api(api_);
 }
 
 NcclOps::~NcclOps() { Shutdown(); }
 
 void NcclOps::Shutdown() {
-  if (api_ != nullptr)
-    for (auto& kv : comms_)
-      if (kv.second) api_->CommDestroy(static_cast<ncclComm_t>(kv.second));
-  comms_.clear();
+  comms_.DestroyAll();
   buffers_.Clear();
 }
 
 void* NcclOps::CommFor(ProcessSet& ps) { return CommOver(ps.id, ps.comm); }
 
 void* NcclOps::CommOver(int32_t key, Comm& over) {
-  auto it = comms_.find(key);
-  if (it != comms_.end()) return it->second;
+  if (void* cached = comms_.Find(key)) return cached;
   // Rank 0 of the group creates the id; it travels over the control plane.
   ncclUniqueId id;
   std::memset(&id, 0, sizeof(id));
@@ -131,7 +129,7 @@ void* NcclOps::CommOver(int32_t key, Comm& over) {
   ncclComm_t comm = nullptr;
   HVD_NCCL(api_->CommInitRank(&comm, over.size(), id, over.rank()));
   over.Barrier();
-  comms_[key] = comm;
+  comms_.Put(key, comm);
   return comm;
 }
 
@@ -157,6 +155,12 @@ Status NcclOps::Execute(std::vector<TensorTableEntry>& entries,
     return Status::PreconditionError(
         "This collective needs NCCL (symmetric memory is not usable for it) "
         "but libnccl.so.2 could not be loaded.");
+  if (comms_.failed())
+    return Status::UnknownError(
+        "NCCL communicators were aborted after an asynchronous error; the job has to "
+        "re-initialise (hvd.shutdown() / hvd.init(), which elastic jobs do by themselves).");
+  // No abort while this response's calls are being issued.
+  std::lock_guard<std::mutex> issuing(comms_.issue_mutex());
   void* comm = CommFor(ps);
   gpu_.WaitForInputs(entries);
   switch (response.type) {

@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "../common/fusion_buffer_manager.h"
+#include "nccl_comm_set.h"
 #include "op_executor.h"
 
 namespace hvd {
@@ -27,6 +28,10 @@ public:
   Status Execute(std::vector<TensorTableEntry>& entries,
                  const Response& response, ProcessSet& ps);
   void Shutdown();
+  // For the thread that waits for a collective in an elastic job: whether
+  // there is anything to watch, and the check itself (nccl_comm_set.h).
+  bool HasCommunicators() { return !comms_.empty(); }
+  Status CheckAsyncErrors() { return comms_.CheckAsyncErrors(); }
 
 private:
   void* CommFor(ProcessSet& ps);
@@ -49,7 +54,7 @@ private:
 
   GpuOps& gpu_;
   const NcclApi* api_ = nullptr;
-  std::map<int32_t, void*> comms_;
+  NcclCommSet comms_;
   FusionBufferManager buffers_;
   bool hierarchical_ = false;  // the allreduce being executed runs in two levels
 };

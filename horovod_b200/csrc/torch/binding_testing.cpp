@@ -22,11 +22,23 @@
 #include "../kernels/kernels.h"
 #include "../ops/cpu_ops.h"
 #include "../ops/exchange_plan.h"
+#include "../ops/nccl_api.h"
+#include "../ops/nccl_comm_set.h"
 #include "../transport/mesh.h"
 
 namespace py = pybind11;
 
 namespace hvd {
+
+namespace {
+// A stand-in for NCCL's error reporting: communicator `failing` starts to
+// report an error at its `fail_at`-th query; aborts are counted.
+struct FakeNcclState {
+  int queries = 0, fail_at = 0, aborted = 0, destroyed = 0;
+  ncclComm_t failing = nullptr;
+};
+FakeNcclState g_fake_nccl;
+}  // namespace
 
 void BindTesting(py::module_& root) {
   py::module_ m = root.def_submodule("testing", "internal components for unit tests");
@@ -163,6 +175,53 @@ void BindTesting(py::module_& root) {
     std::vector<std::vector<std::string>> groups;
     for (auto& r : out.responses) groups.push_back(r.names);
     return groups;
+  });
+  // The wait of an elastic job for a device collective, on fakes: `comms`
+  // communicators, of which number `failing` (or none: -1) reports an error
+  // from its `fail_at`-th query on; the device work is done after
+  // `ready_after` polls, or `ready_after_abort` polls after an abort.
+  // Returns (ok, message, polls, queries, aborted, set empty, set failed,
+  // destroyed by the final DestroyAll).
+  m.def("nccl_async_wait", [](int comms, int failing, int fail_at, int ready_after,
+                              int ready_after_abort) {
+    g_fake_nccl = FakeNcclState();
+    g_fake_nccl.fail_at = fail_at;
+    NcclApi api{};
+    api.CommGetAsyncError = [](ncclComm_t c, ncclResult_t* out) {
+      if (c == g_fake_nccl.failing) ++g_fake_nccl.queries;
+      *out = (c == g_fake_nccl.failing && g_fake_nccl.queries >= g_fake_nccl.fail_at)
+                 ? ncclSystemError
+                 : ncclSuccess;
+      return ncclSuccess;
+    };
+    api.CommAbort = [](ncclComm_t) {
+      ++g_fake_nccl.aborted;
+      return ncclSuccess;
+    };
+    api.CommDestroy = [](ncclComm_t) {
+      ++g_fake_nccl.destroyed;
+      return ncclSuccess;
+    };
+    api.GetErrorString = [](ncclResult_t) -> const char* { return "peer is gone (fake)"; };
+    NcclCommSet set(&api);
+    for (int i = 0; i < comms; ++i)
+      set.Put(i, reinterpret_cast<void*>(static_cast<uintptr_t>(0x1000 + i)));
+    if (failing >= 0)
+      g_fake_nccl.failing = reinterpret_cast<ncclComm_t>(static_cast<uintptr_t>(0x1000 + failing));
+    int polls = 0, polls_after_abort = 0;
+    Status st = WaitPolling(
+        [&] {
+          ++polls;
+          if (g_fake_nccl.aborted > 0) return ++polls_after_abort >= ready_after_abort ? 1 : 0;
+          return polls >= ready_after ? 1 : 0;
+        },
+        [&] { return set.CheckAsyncErrors(); }, std::chrono::microseconds(50),
+        std::chrono::milliseconds(200));
+    bool empty = set.empty(), failed = set.failed();
+    int aborted = g_fake_nccl.aborted;
+    set.DestroyAll();
+    return py::make_tuple(st.ok(), st.reason(), polls, g_fake_nccl.queries, aborted, empty, failed,
+                          g_fake_nccl.destroyed, set.failed());
   });
   m.def("affinity_core", [](const std::string& spec, int local_rank) {
     return AffinityCore(spec, local_rank);

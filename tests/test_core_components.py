@@ -272,3 +272,27 @@ def test_thread_affinity_value_is_one_core_or_one_per_local_rank():
     assert [t.affinity_core("0,2,4,6", r) for r in range(4)] == [0, 2, 4, 6]
     assert t.affinity_core("0,2", 2) == -1          # no entry for this local rank
     assert t.affinity_core("0,x", 1) == -1 and t.affinity_core("-3", 0) == -1
+
+
+def test_elastic_wait_polls_nccl_for_asynchronous_errors_and_aborts():
+    """The host-side wait of an elastic job for a device collective, with a
+    stand-in for NCCL's error reporting (no GPU, no fault): without an error
+    it ends when the work is done and touches nothing; when a communicator
+    reports an error, all are aborted once, the wait ends with that error
+    after the aborted work has drained (or after the grace period), and the
+    set stays marked failed until it is destroyed."""
+    t = _C.testing
+    ok, msg, polls, queries, aborted, empty, failed, destroyed, failed_after = \
+        t.nccl_async_wait(3, -1, 0, 5, 0)
+    assert (ok, msg, polls, aborted, empty, failed) == (True, "", 5, 0, False, False)
+    assert destroyed == 3 and not failed_after
+    # communicator 1 fails at its 4th query: 4 polls without completion, then the abort
+    ok, msg, polls, queries, aborted, empty, failed, destroyed, failed_after = \
+        t.nccl_async_wait(3, 1, 4, 10 ** 9, 3)
+    assert not ok and "asynchronous error" in msg and "peer is gone (fake)" in msg
+    assert queries == 4 and aborted == 3 and empty and failed
+    assert polls == 4 + 3          # three more polls until the aborted work has drained
+    assert destroyed == 0 and not failed_after   # nothing left to destroy; the mark is cleared
+    # the work never drains: the wait still ends, after the grace period, with the error
+    ok, msg, polls, *_ = t.nccl_async_wait(1, 0, 1, 10 ** 9, 10 ** 9)
+    assert not ok and "aborted" in msg and polls > 3

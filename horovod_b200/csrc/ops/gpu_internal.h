@@ -318,6 +318,9 @@ private:
 
 // Timings of every executor of the process (HOROVOD_GPU_OP_TIMING=1).
 std::vector<GpuOps::OpTiming> DrainAllGpuTimings();
+// Device responses executed so far by the symmetric-memory kernels and by
+// the NCCL path (all executors of the process).
+void GpuResponsePathCounts(unsigned long long* symm, unsigned long long* nccl);
 
 // The executor of the running job (null when there is none); used by the
 // diagnostics binding.

@@ -24,6 +24,17 @@ std::atomic<GpuOps*> g_current{nullptr};
 GpuOps* CurrentGpuOps() { return g_current.load(); }
 
 namespace {
+// Responses executed per device data path since the process started:
+// [0] symmetric-memory kernels, [1] NCCL.
+std::atomic<unsigned long long> g_path_counts[2];
+}  // namespace
+
+void GpuResponsePathCounts(unsigned long long* symm, unsigned long long* nccl) {
+  *symm = g_path_counts[0].load();
+  *nccl = g_path_counts[1].load();
+}
+
+namespace {
 // Every live executor (one per device and communication stream), for the
 // diagnostics that sum over them.
 std::mutex& g_registry_mu_ref() {
@@ -656,6 +667,18 @@ Status GpuOps::Execute(std::vector<TensorTableEntry>& entries,
     default:
       break;
     }
+  }
+  g_path_counts[use_symm ? 0 : 1].fetch_add(1, std::memory_order_relaxed);
+  if (!use_symm && set != nullptr) {
+    // The arena is there but this response cannot use it: say so once per kind.
+    static std::atomic<unsigned> told{0};
+    const unsigned bit = 1u << (static_cast<unsigned>(response.type) & 31u);
+    if ((told.fetch_or(bit) & bit) == 0)
+      HVD_LOG(INFO) << Response::TypeName(response.type) << " with reduce op "
+                    << static_cast<int>(response.reduce_op) << " and dtype "
+                    << DataTypeName(response.dtype)
+                    << " runs on the NCCL path (the symmetric-memory kernels cover sum-like "
+                       "reductions of every type but bool and 16-bit integers).";
   }
   PendingTiming pt = {nullptr, nullptr, static_cast<int>(response.type), 0,
                       static_cast<int>(entries.size()), 0.0, 0.f};

@@ -72,6 +72,14 @@ void BindGpuDiagnostics(py::module_& m) {
     for (auto& x : t) out.append(py::make_tuple(x.type, x.bytes, x.tensors, x.device_us, x.host_us));
     return out;
   });
+  m.def("gpu_response_paths", []() {
+    unsigned long long symm = 0, nccl = 0;
+    GpuResponsePathCounts(&symm, &nccl);
+    py::dict d;
+    d["symm"] = symm;
+    d["nccl"] = nccl;
+    return d;
+  }, "Device responses executed so far per data path: symmetric-memory kernels, NCCL.");
   m.def("bounded_wait_probe", [](int device, int timeout_ms) {
     // Runs the cross-GPU barrier kernel as rank 0 of a group of two whose
     // second member does not exist: nothing ever sets that member's flag, so

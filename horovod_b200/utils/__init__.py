@@ -23,6 +23,15 @@ def op_timings():
     return _ext().gpu_op_stats()
 
 
+def response_paths():
+    """``{"symm": n, "nccl": m}``: how many device responses this process has
+    executed with the symmetric-memory kernels and on the NCCL path (Min /
+    Max / Product, bool and 16-bit integer reductions, process sets with id 8
+    or more, jobs that span hosts). Read it before and after a call to see
+    which path that call took."""
+    return dict(_ext().gpu_response_paths())
+
+
 def kernel_launch_count():
     """Kernels of this library launched so far in this process."""
     return _ext().kernel_launch_count()

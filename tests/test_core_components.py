@@ -296,3 +296,10 @@ def test_elastic_wait_polls_nccl_for_asynchronous_errors_and_aborts():
     # the work never drains: the wait still ends, after the grace period, with the error
     ok, msg, polls, *_ = t.nccl_async_wait(1, 0, 1, 10 ** 9, 10 ** 9)
     assert not ok and "aborted" in msg and polls > 3
+
+
+def test_response_path_counters_are_readable_without_a_gpu():
+    import horovod_b200.utils as utils
+    paths = utils.response_paths()
+    assert set(paths) == {"symm", "nccl"} and all(isinstance(v, int) and v >= 0
+                                                  for v in paths.values())

@@ -63,7 +63,7 @@ setup(
     package_data={"horovod_b200": ["_C.so", "csrc/**/*"]},
     python_requires=">=3.9",
     install_requires=["torch", "cloudpickle", "psutil", "pyyaml"],
-    extras_require={"ray": ["ray"], "spark": ["pyspark>=3.0"]},
+    extras_require={"ray": ["ray"], "spark": ["pyspark>=3.0", "pyarrow", "pandas", "numpy"]},
     entry_points={"console_scripts": ["horovodrun = horovod_b200.runner.launch:run_commandline"]},
     cmdclass={"build_ext": build_ext, "build_py": build_py, "build_native": build_native},
 )

@@ -35,7 +35,7 @@ from horovod_b200.torch.mpi_ops import (Adasum, Average, Max, Min, Product, Sum,
                                         runtime_params,
                                         shutdown, size, sparse_allreduce_async,
                                         start_timeline, stop_timeline, symmetric_empty,
-                                        synchronize, topology)
+                                        synchronize, topology, set_shadow_check, ShadowMismatch)
 from horovod_b200.torch.fused_sgd import FusedSGD
 from horovod_b200.torch.optimizer import DistributedOptimizer
 from horovod_b200.torch.sync_batch_norm import SyncBatchNorm

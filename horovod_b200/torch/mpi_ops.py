@@ -9,6 +9,8 @@ issued in the same order on every rank.
 Parity: horovod/torch/mpi_ops.py:63-903. Extensions: reducescatter, bf16,
 Min/Max/Product, process_set on every op.
 """
+import os
+
 import torch
 
 from horovod_b200 import _C
@@ -134,10 +136,92 @@ def _wire_id(tensor, wire_dtype):
     return _WIRE_IDS.get(wire_dtype, -1)
 
 
+# ---- shadow check ------------------------------------------------------------
+# HOROVOD_SHADOW_CHECK=1: every allreduce of a CUDA tensor is also computed on
+# fp64 host copies of the inputs by the CPU data plane (an independent
+# implementation: TCP mesh, no kernels of this library), and synchronize()
+# compares the two. A debugging aid: it synchronises the stream at every call
+# and moves every tensor a second time. "all" shadows CPU tensors as well
+# (catches what a narrow accumulation type loses).
+_shadow_mode = os.environ.get("HOROVOD_SHADOW_CHECK", "0").lower()
+_shadow_map = {}     # handle of the checked op -> (handle of its shadow, dtype, wire dtype)
+_shadow_counter = [0]
+
+
+class ShadowMismatch(RuntimeError):
+    """The device result of a collective differs from its host shadow."""
+
+
+def set_shadow_check(mode):
+    """``False`` / ``True`` / ``"all"`` at run time; the same on every rank."""
+    global _shadow_mode
+    _shadow_mode = {False: "0", True: "1"}.get(mode, str(mode).lower())
+
+
+def _shadow_wanted(tensor, op):
+    if _shadow_mode in ("0", "", "false", "off") or op == Adasum:
+        return False
+    return tensor.is_cuda or _shadow_mode == "all"
+
+
+def _shadow_tolerance(dtype, wire_dtype, ranks):
+    """(rtol, atol factor of the largest magnitude) for a result of ``dtype``."""
+    narrow = dtype in (torch.float16, torch.bfloat16) or wire_dtype in (torch.float16,
+                                                                         torch.bfloat16)
+    if not dtype.is_floating_point:
+        return 0.0, 0.0
+    if narrow:
+        return 2e-2, 1e-2 * ranks
+    return (1e-5, 1e-6 * ranks) if dtype == torch.float32 else (1e-12, 1e-13 * ranks)
+
+
+def _start_shadow(handle, tensor, op, prescale_factor, postscale_factor, process_set, wire_dtype):
+    wide = tensor.detach().to("cpu", torch.float64 if tensor.is_floating_point() else tensor.dtype,
+                              copy=True).contiguous()
+    _shadow_counter[0] += 1
+    shadow = _enqueue(_C.allreduce_async, wide, torch.empty_like(wide),
+                      "hvd.shadow.allreduce.%d" % _shadow_counter[0],
+                      *_scaled_op(op, prescale_factor, postscale_factor), _resolve(process_set), -1)
+    _shadow_map[handle] = (shadow, tensor.dtype, wire_dtype,
+                           process_set.size() if process_set is not None else size())
+
+
+def _finish_shadow(handle, result):
+    shadow, dtype, wire_dtype, ranks = _shadow_map.pop(handle)
+    try:
+        expected = _C.wait_and_clear(shadow)[0][0]
+    except RuntimeError as e:
+        raise HorovodInternalError(e)
+    got = result.detach().to("cpu", expected.dtype)
+    rtol, atol_factor = _shadow_tolerance(dtype, wire_dtype, ranks)
+    scale = float(expected.abs().max()) if expected.numel() else 0.0
+    bad = (got - expected).abs() > rtol * expected.abs() + atol_factor * max(scale, 1e-30)
+    if bool(bad.any()):
+        worst = float((got - expected).abs().max())
+        raise ShadowMismatch(
+            "allreduce result differs from its host shadow in %d of %d elements (largest "
+            "difference %.3e, largest expected magnitude %.3e, dtype %s)"
+            % (int(bad.sum()), expected.numel(), worst, scale, dtype))
+
+
 def _allreduce_async(tensor, output, name, op, prescale_factor, postscale_factor, process_set,
                      wire_dtype=None):
     _check_tensor(tensor, dense_ok=True)
     _check_adasum(op, process_set)
+    if _shadow_wanted(tensor, op) and (op != Average or tensor.is_floating_point()):
+        # the copy comes first: an in-place op overwrites its input
+        wide_input = tensor.detach().clone() if tensor is output else tensor
+        handle = _allreduce_async_unchecked(tensor, output, name, op, prescale_factor,
+                                            postscale_factor, process_set, wire_dtype)
+        _start_shadow(handle, wide_input, op, prescale_factor, postscale_factor, process_set,
+                      wire_dtype)
+        return handle
+    return _allreduce_async_unchecked(tensor, output, name, op, prescale_factor, postscale_factor,
+                                      process_set, wire_dtype)
+
+
+def _allreduce_async_unchecked(tensor, output, name, op, prescale_factor, postscale_factor,
+                               process_set, wire_dtype=None):
     if op == Average and not (tensor.is_floating_point() or tensor.is_complex()):
         # Integer averaging: sum on the wire, floor-divide afterwards, as the
         # framework's integer division would.
@@ -524,6 +608,8 @@ def synchronize(handle):
     except RuntimeError as e:
         raise HorovodInternalError(e)
     if kind == "allreduce":
+        if handle in _shadow_map:
+            _finish_shadow(handle, outputs[0])
         return outputs[0]
     if kind == "allreduce_intavg":
         outputs[0].copy_(torch.div(outputs[0], extra, rounding_mode="floor"))

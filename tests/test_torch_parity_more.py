@@ -203,3 +203,42 @@ def test_optimizer_corner_cases():
     for rep in run_parallel(_optimizer_corner_cases, np=2, timeout=300):
         bad = [k for k, v in rep.items() if not v]
         assert not bad, bad
+
+
+def _shadow_checks(rank, size):
+    import os
+    os.environ["HOROVOD_SHADOW_CHECK"] = "all"   # CPU tensors too; on a GPU box "1" checks the kernels
+    import horovod_b200.torch as hvd
+    from horovod_b200.torch import mpi_ops
+    hvd.init()
+    res = {}
+    x = torch.randn(1000, generator=torch.Generator().manual_seed(rank))
+    expect = sum(torch.randn(1000, generator=torch.Generator().manual_seed(r)) for r in range(size))
+    res["sum"] = torch.allclose(hvd.allreduce(x, op=hvd.Sum, name="s.sum"), expect, atol=1e-5)
+    y = x.clone()
+    hvd.allreduce_(y, op=hvd.Average, prescale_factor=2.0, name="s.inplace")
+    res["inplace_scaled"] = torch.allclose(y, 2.0 * expect / size, atol=1e-5)
+    res["ints"] = hvd.allreduce(torch.arange(5) + rank, op=hvd.Sum, name="s.int").tolist() == \
+        [size * i + sum(range(size)) for i in range(5)]
+    res["half"] = float(hvd.allreduce(torch.ones(8).half(), op=hvd.Sum, name="s.half")[0]) == size
+    res["shadows_done"] = not mpi_ops._shadow_map and mpi_ops._shadow_counter[0] == 4
+    # a result that differs from the fp64 shadow is reported: 1 + 2^-9 is not a bf16 number
+    mpi_ops._shadow_tolerance = lambda dtype, wire, ranks: (0.0, 0.0)
+    z = torch.tensor([1.0 if rank == 0 else 2.0 ** -9]).bfloat16()
+    try:
+        hvd.allreduce(z, op=hvd.Sum, name="s.lossy")
+        res["mismatch_reported"] = False
+    except hvd.ShadowMismatch as e:
+        res["mismatch_reported"] = "1 of 1 elements" in str(e)
+    hvd.set_shadow_check(False)
+    before = mpi_ops._shadow_counter[0]
+    hvd.allreduce(z, op=hvd.Sum, name="s.off")
+    res["switched_off"] = mpi_ops._shadow_counter[0] == before
+    hvd.shutdown()
+    return res
+
+
+def test_shadow_check_recomputes_allreduces_on_the_host_and_reports_differences():
+    for rep in run_parallel(_shadow_checks, np=2, timeout=300):
+        bad = [k for k, v in rep.items() if not v]
+        assert not bad, bad

@@ -607,10 +607,12 @@ Status GpuOps::Complete(std::vector<TensorTableEntry>& entries) {
                                                           cudaGetErrorString(err))
                 : !async_status.ok() ? async_status
                                      : CheckKernelStatus();
-    // Replay the phases with the times the device went through them.
+    // Replay the phases with the times the device went through them (none
+    // after an error: the events may never have completed).
+    const bool timed = err == cudaSuccess && async_status.ok();
     Timeline& timeline = state_.timeline;
     for (auto& m : *marks) {
-      const int64_t at = err == cudaSuccess ? EventHostMicros(m.event) : -1;
+      const int64_t at = timed ? EventHostMicros(m.event) : -1;
       for (auto& name : m.tensors) {
         if (m.activity.empty())
           timeline.ActivityEndAt(name, at);
@@ -619,7 +621,7 @@ Status GpuOps::Complete(std::vector<TensorTableEntry>& entries) {
       }
     }
     const int64_t end_at =
-        finished != nullptr && err == cudaSuccess ? EventHostMicros(finished) : -1;
+        finished != nullptr && timed ? EventHostMicros(finished) : -1;
     {
       std::lock_guard<std::mutex> l(timed_mu_);
       for (auto& m : *marks) timed_events_.push_back(m.event);

@@ -175,24 +175,28 @@ def _shadow_tolerance(dtype, wire_dtype, ranks):
     return (1e-5, 1e-6 * ranks) if dtype == torch.float32 else (1e-12, 1e-13 * ranks)
 
 
-def _start_shadow(handle, tensor, op, prescale_factor, postscale_factor, process_set, wire_dtype):
-    wide = tensor.detach().to("cpu", torch.float64 if tensor.is_floating_point() else tensor.dtype,
-                              copy=True).contiguous()
+def _start_shadow(handle, tensors, op, prescale_factor, postscale_factor, process_set, wire_dtype):
+    """``tensors``: the inputs of the op behind ``handle`` (one, or the list of
+    a grouped op, which is shadowed as one flat vector)."""
+    floating = tensors[0].is_floating_point()
+    wide = torch.cat([t.detach().reshape(-1).to("cpu", torch.float64 if floating else t.dtype)
+                      for t in tensors]).contiguous()
     _shadow_counter[0] += 1
     shadow = _enqueue(_C.allreduce_async, wide, torch.empty_like(wide),
                       "hvd.shadow.allreduce.%d" % _shadow_counter[0],
                       *_scaled_op(op, prescale_factor, postscale_factor), _resolve(process_set), -1)
-    _shadow_map[handle] = (shadow, tensor.dtype, wire_dtype,
+    narrow = [t.dtype for t in tensors if t.dtype in (torch.float16, torch.bfloat16)]
+    _shadow_map[handle] = (shadow, narrow[0] if narrow else tensors[0].dtype, wire_dtype,
                            process_set.size() if process_set is not None else size())
 
 
-def _finish_shadow(handle, result):
+def _finish_shadow(handle, results):
     shadow, dtype, wire_dtype, ranks = _shadow_map.pop(handle)
     try:
         expected = _C.wait_and_clear(shadow)[0][0]
     except RuntimeError as e:
         raise HorovodInternalError(e)
-    got = result.detach().to("cpu", expected.dtype)
+    got = torch.cat([r.detach().reshape(-1).to("cpu", expected.dtype) for r in results])
     rtol, atol_factor = _shadow_tolerance(dtype, wire_dtype, ranks)
     scale = float(expected.abs().max()) if expected.numel() else 0.0
     bad = (got - expected).abs() > rtol * expected.abs() + atol_factor * max(scale, 1e-30)
@@ -204,6 +208,14 @@ def _finish_shadow(handle, result):
             % (int(bad.sum()), expected.numel(), worst, scale, dtype))
 
 
+def _shadow_group_ok(tensors, op):
+    """A grouped op is shadowed when its tensors can share one flat vector."""
+    if not tensors or not _shadow_wanted(tensors[0], op):
+        return False
+    kinds = {t.is_floating_point() for t in tensors}
+    return len(kinds) == 1 and (True in kinds or len({t.dtype for t in tensors}) == 1)
+
+
 def _allreduce_async(tensor, output, name, op, prescale_factor, postscale_factor, process_set,
                      wire_dtype=None):
     _check_tensor(tensor, dense_ok=True)
@@ -213,7 +225,7 @@ def _allreduce_async(tensor, output, name, op, prescale_factor, postscale_factor
         wide_input = tensor.detach().clone() if tensor is output else tensor
         handle = _allreduce_async_unchecked(tensor, output, name, op, prescale_factor,
                                             postscale_factor, process_set, wire_dtype)
-        _start_shadow(handle, wide_input, op, prescale_factor, postscale_factor, process_set,
+        _start_shadow(handle, [wide_input], op, prescale_factor, postscale_factor, process_set,
                       wire_dtype)
         return handle
     return _allreduce_async_unchecked(tensor, output, name, op, prescale_factor, postscale_factor,
@@ -307,6 +319,10 @@ def _grouped_allreduce_async(tensors, outputs, name, op, prescale_factor, postsc
     _check_adasum(op, process_set)
     int_avg = op == Average and any(not t.is_floating_point() for t in tensors)
     wire_op = Sum if int_avg else op
+    shadowed = None
+    if not int_avg and _shadow_group_ok(tensors, op):
+        # copies first: an in-place group overwrites its inputs
+        shadowed = [t.detach().clone() if any(t is o for o in outputs) else t for t in tensors]
     handle = _enqueue(_C.grouped_allreduce_async, list(tensors), list(outputs), name or "",
                                         int(wire_op), float(prescale_factor),
                                         float(postscale_factor), _resolve(process_set),
@@ -319,6 +335,9 @@ def _grouped_allreduce_async(tensors, outputs, name, op, prescale_factor, postsc
         _handle_map[handle] = ("grouped_intavg", divisor)
     else:
         _handle_map[handle] = ("grouped", None)
+    if shadowed is not None:
+        _start_shadow(handle, shadowed, op, prescale_factor, postscale_factor, process_set,
+                      wire_dtype)
     return handle
 
 
@@ -609,12 +628,14 @@ def synchronize(handle):
         raise HorovodInternalError(e)
     if kind == "allreduce":
         if handle in _shadow_map:
-            _finish_shadow(handle, outputs[0])
+            _finish_shadow(handle, [outputs[0]])
         return outputs[0]
     if kind == "allreduce_intavg":
         outputs[0].copy_(torch.div(outputs[0], extra, rounding_mode="floor"))
         return outputs[0]
     if kind == "grouped":
+        if handle in _shadow_map:
+            _finish_shadow(handle, list(outputs))
         return list(outputs)
     if kind == "grouped_intavg":
         for o in outputs:

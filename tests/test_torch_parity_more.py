@@ -221,7 +221,13 @@ def _shadow_checks(rank, size):
     res["ints"] = hvd.allreduce(torch.arange(5) + rank, op=hvd.Sum, name="s.int").tolist() == \
         [size * i + sum(range(size)) for i in range(5)]
     res["half"] = float(hvd.allreduce(torch.ones(8).half(), op=hvd.Sum, name="s.half")[0]) == size
-    res["shadows_done"] = not mpi_ops._shadow_map and mpi_ops._shadow_counter[0] == 4
+    group = [torch.full((3,), float(rank + 1)), torch.full((2, 2), 2.0 * (rank + 1)).half()]
+    out = hvd.grouped_allreduce(group, op=hvd.Sum, name="s.group")
+    tot = sum(range(1, size + 1))
+    res["group"] = out[0].tolist() == [float(tot)] * 3 and float(out[1][0, 0]) == 2.0 * tot
+    hvd.grouped_allreduce_(group, op=hvd.Average, name="s.group.inplace")
+    res["group_inplace"] = group[0].tolist() == [tot / size] * 3
+    res["shadows_done"] = not mpi_ops._shadow_map and mpi_ops._shadow_counter[0] == 6
     # a result that differs from the fp64 shadow is reported: 1 + 2^-9 is not a bf16 number
     mpi_ops._shadow_tolerance = lambda dtype, wire, ranks: (0.0, 0.0)
     z = torch.tensor([1.0 if rank == 0 else 2.0 ** -9]).bfloat16()

@@ -237,3 +237,51 @@ def _alltoall_even_and_explicit(rank, size):
 
 def test_alltoall_even_split_needs_no_split_exchange_and_mixes_with_explicit_splits():
     assert all(run_parallel(_alltoall_even_and_explicit, np=4, timeout=300))
+
+
+def _randomised_sets(rank, size):
+    """Rounds of randomly sized, typed and scaled allreduces (single and
+    grouped, in place and not), all in flight together so that the controller
+    fuses what it can; every result is checked by the fp64 host shadow."""
+    os.environ["HOROVOD_SHADOW_CHECK"] = "all"
+    import random
+    import horovod_b200.torch as hvd
+    hvd.init()
+    plan = random.Random(1234)            # the same plan on every rank
+    data = torch.Generator().manual_seed(99 + rank)   # different values
+    dtypes = [torch.float32, torch.float64, torch.float16, torch.bfloat16, torch.int32, torch.int64]
+    checked = 0
+    for rnd in range(6):
+        handles = []
+        for i in range(plan.randint(3, 12)):
+            dtype = plan.choice(dtypes)
+            shape = [plan.randint(1, 40) for _ in range(plan.randint(1, 3))]
+            op = plan.choice([hvd.Sum, hvd.Average] if dtype.is_floating_point else [hvd.Sum])
+            pre = plan.choice([1.0, 0.5, 2.0]) if dtype.is_floating_point else 1.0
+
+            def make():
+                if dtype.is_floating_point:
+                    return torch.randn(shape, generator=data).to(dtype)
+                return torch.randint(-50, 50, shape, generator=data, dtype=dtype)
+            name = "rand.%d.%d" % (rnd, i)
+            kind = plan.choice(["single", "inplace", "group"])
+            if kind == "single":
+                handles.append(hvd.allreduce_async(make(), op=op, prescale_factor=pre, name=name))
+            elif kind == "inplace":
+                handles.append(hvd.allreduce_async_(make(), op=op, prescale_factor=pre, name=name))
+            else:
+                members = [make() for _ in range(plan.randint(2, 4))]
+                handles.append(hvd.grouped_allreduce_async(members, op=op, prescale_factor=pre,
+                                                           name=name))
+        plan.shuffle(handles)             # waited for in another order than issued
+        for h in handles:
+            hvd.synchronize(h)            # raises ShadowMismatch on a wrong result
+            checked += 1
+    from horovod_b200.torch import mpi_ops
+    ok = checked >= 18 and not mpi_ops._shadow_map and mpi_ops._shadow_counter[0] == checked
+    hvd.shutdown()
+    return ok
+
+
+def test_randomised_tensor_sets_against_the_host_shadow():
+    assert all(run_parallel(_randomised_sets, np=3, timeout=600))

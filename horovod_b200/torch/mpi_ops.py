@@ -159,7 +159,7 @@ def set_shadow_check(mode):
 
 
 def _shadow_wanted(tensor, op):
-    if _shadow_mode in ("0", "", "false", "off") or op == Adasum:
+    if _shadow_mode in ("0", "", "false", "off") or (op is not None and op == Adasum):
         return False
     return tensor.is_cuda or _shadow_mode == "all"
 
@@ -175,37 +175,59 @@ def _shadow_tolerance(dtype, wire_dtype, ranks):
     return (1e-5, 1e-6 * ranks) if dtype == torch.float32 else (1e-12, 1e-13 * ranks)
 
 
-def _start_shadow(handle, tensors, op, prescale_factor, postscale_factor, process_set, wire_dtype):
-    """``tensors``: the inputs of the op behind ``handle`` (one, or the list of
-    a grouped op, which is shadowed as one flat vector)."""
-    floating = tensors[0].is_floating_point()
-    wide = torch.cat([t.detach().reshape(-1).to("cpu", torch.float64 if floating else t.dtype)
-                      for t in tensors]).contiguous()
+def _shadow_name(label):
     _shadow_counter[0] += 1
-    shadow = _enqueue(_C.allreduce_async, wide, torch.empty_like(wide),
-                      "hvd.shadow.allreduce.%d" % _shadow_counter[0],
+    return "hvd.shadow.%s.%d" % (label, _shadow_counter[0])
+
+
+def _host_copy(tensor, widen):
+    target = torch.float64 if widen and tensor.is_floating_point() else tensor.dtype
+    return tensor.detach().to("cpu", target, copy=True).contiguous()
+
+
+def _start_shadow(handle, tensors, op, prescale_factor, postscale_factor, process_set, wire_dtype):
+    """``tensors``: the inputs of the allreduce behind ``handle`` (one, or the
+    list of a grouped op, which is shadowed as one flat vector)."""
+    wide = torch.cat([_host_copy(t, True).reshape(-1) for t in tensors]).contiguous()
+    shadow = _enqueue(_C.allreduce_async, wide, torch.empty_like(wide), _shadow_name("allreduce"),
                       *_scaled_op(op, prescale_factor, postscale_factor), _resolve(process_set), -1)
     narrow = [t.dtype for t in tensors if t.dtype in (torch.float16, torch.bfloat16)]
-    _shadow_map[handle] = (shadow, narrow[0] if narrow else tensors[0].dtype, wire_dtype,
-                           process_set.size() if process_set is not None else size())
+    _shadow_map[handle] = (shadow, "allreduce", narrow[0] if narrow else tensors[0].dtype,
+                           wire_dtype, process_set.size() if process_set is not None else size())
+
+
+def _start_exact_shadow(handle, label, enqueue_twin):
+    """For the ops that only move data: ``enqueue_twin(name)`` starts the
+    same op on host copies; the results must be equal."""
+    _shadow_map[handle] = (enqueue_twin(_shadow_name(label)), label, None, None, 1)
 
 
 def _finish_shadow(handle, results):
-    shadow, dtype, wire_dtype, ranks = _shadow_map.pop(handle)
+    shadow, label, dtype, wire_dtype, ranks = _shadow_map.pop(handle)
     try:
         expected = _C.wait_and_clear(shadow)[0][0]
     except RuntimeError as e:
         raise HorovodInternalError(e)
-    got = torch.cat([r.detach().reshape(-1).to("cpu", expected.dtype) for r in results])
-    rtol, atol_factor = _shadow_tolerance(dtype, wire_dtype, ranks)
-    scale = float(expected.abs().max()) if expected.numel() else 0.0
-    bad = (got - expected).abs() > rtol * expected.abs() + atol_factor * max(scale, 1e-30)
+    flat = [r.detach().reshape(-1) for r in results]
+    if len(results) == 1 and label != "allreduce" and tuple(results[0].shape) != tuple(expected.shape):
+        raise ShadowMismatch("%s result has shape %s, its host shadow %s"
+                             % (label, tuple(results[0].shape), tuple(expected.shape)))
+    expected = expected.reshape(-1)
+    got = torch.cat([r.to("cpu", expected.dtype) for r in flat])
+    rtol, atol_factor = (0.0, 0.0) if dtype is None else _shadow_tolerance(dtype, wire_dtype, ranks)
+    scale = float(expected.abs().max()) if expected.numel() and expected.dtype != torch.bool else 0.0
+    if expected.dtype == torch.bool:
+        bad = got != expected
+        worst = float(bad.any())
+    else:
+        diff = (got - expected).abs()
+        bad = diff > rtol * expected.abs() + atol_factor * max(scale, 1e-30)
+        worst = float(diff.max()) if diff.numel() else 0.0
     if bool(bad.any()):
-        worst = float((got - expected).abs().max())
         raise ShadowMismatch(
-            "allreduce result differs from its host shadow in %d of %d elements (largest "
+            "%s result differs from its host shadow in %d of %d elements (largest "
             "difference %.3e, largest expected magnitude %.3e, dtype %s)"
-            % (int(bad.sum()), expected.numel(), worst, scale, dtype))
+            % (label, int(bad.sum()), expected.numel(), worst, scale, dtype or results[0].dtype))
 
 
 def _shadow_group_ok(tensors, op):
@@ -425,6 +447,10 @@ def allgather_async(tensor, name=None, process_set=global_process_set):
     _check_tensor(tensor)
     handle = _enqueue(_C.allgather_async, tensor, name or "", _resolve(process_set))
     _handle_map[handle] = ("allgather", None)
+    if _shadow_wanted(tensor, None):
+        twin = _host_copy(tensor, False)
+        _start_exact_shadow(handle, "allgather", lambda shadow_name: _enqueue(
+            _C.allgather_async, twin, shadow_name, _resolve(process_set)))
     return handle
 
 
@@ -454,9 +480,13 @@ def allgather(tensor, name=None, process_set=global_process_set):
 
 def _broadcast_async(tensor, output, root_rank, name, process_set):
     _check_tensor(tensor, dense_ok=True)
+    twin = _host_copy(tensor, False) if _shadow_wanted(tensor, None) else None  # before an in-place op
     handle = _enqueue(_C.broadcast_async, tensor, output, int(root_rank), name or "",
                                 _resolve(process_set))
     _handle_map[handle] = ("broadcast", None)
+    if twin is not None:
+        _start_exact_shadow(handle, "broadcast", lambda shadow_name: _enqueue(
+            _C.broadcast_async, twin, twin, int(root_rank), shadow_name, _resolve(process_set)))
     return handle
 
 
@@ -514,6 +544,10 @@ def alltoall_async(tensor, splits=None, name=None, process_set=global_process_se
     handle = _enqueue(_C.alltoall_async, tensor, _splits_list(splits), name or "",
                                _resolve(process_set))
     _handle_map[handle] = ("alltoall", splits is not None)
+    if _shadow_wanted(tensor, None):
+        twin = _host_copy(tensor, False)
+        _start_exact_shadow(handle, "alltoall", lambda shadow_name: _enqueue(
+            _C.alltoall_async, twin, _splits_list(splits), shadow_name, _resolve(process_set)))
     return handle
 
 
@@ -557,6 +591,12 @@ def reducescatter_async(tensor, name=None, op=Average, prescale_factor=1.0,
     handle = _enqueue(_C.reducescatter_async, tensor, name or "", int(op), float(prescale_factor),
                                     float(postscale_factor), _resolve(process_set))
     _handle_map[handle] = ("reducescatter", None)
+    if _shadow_wanted(tensor, op) and (op != Average or tensor.is_floating_point()):
+        wide = _host_copy(tensor, True)
+        shadow = _enqueue(_C.reducescatter_async, wide, _shadow_name("reducescatter"), int(op),
+                          float(prescale_factor), float(postscale_factor), _resolve(process_set))
+        _shadow_map[handle] = (shadow, "reducescatter", tensor.dtype, None,
+                               process_set.size() if process_set is not None else size())
     return handle
 
 
@@ -644,6 +684,8 @@ def synchronize(handle):
             else:
                 o.div_(extra)
         return list(outputs)
+    if handle in _shadow_map:  # allgather, broadcast, alltoall, reducescatter
+        _finish_shadow(handle, [outputs[0]])
     if kind == "alltoall":
         out = outputs[0]
         if extra:

@@ -227,7 +227,18 @@ def _shadow_checks(rank, size):
     res["group"] = out[0].tolist() == [float(tot)] * 3 and float(out[1][0, 0]) == 2.0 * tot
     hvd.grouped_allreduce_(group, op=hvd.Average, name="s.group.inplace")
     res["group_inplace"] = group[0].tolist() == [tot / size] * 3
-    res["shadows_done"] = not mpi_ops._shadow_map and mpi_ops._shadow_counter[0] == 6
+    # the ops that only move data are shadowed too and must match exactly
+    g = hvd.allgather(torch.full((rank + 1, 2), float(rank)), name="s.ag")
+    res["allgather"] = g.shape[0] == sum(range(1, size + 1))
+    b = torch.full((4,), float(rank))
+    hvd.broadcast_(b, root_rank=size - 1, name="s.bc")
+    res["broadcast"] = b.tolist() == [float(size - 1)] * 4
+    a, rs = hvd.alltoall(torch.arange(size * 2.0) + 10 * rank,
+                         splits=torch.tensor([2] * size, dtype=torch.int32), name="s.a2a")
+    res["alltoall"] = a.tolist() == [10.0 * r + 2 * rank + j for r in range(size) for j in range(2)]
+    r_ = hvd.reducescatter(torch.ones(size * 3, 2) * (rank + 1), op=hvd.Sum, name="s.rs")
+    res["reducescatter"] = tuple(r_.shape) == (3, 2) and float(r_[0, 0]) == tot
+    res["shadows_done"] = not mpi_ops._shadow_map and mpi_ops._shadow_counter[0] == 10
     # a result that differs from the fp64 shadow is reported: 1 + 2^-9 is not a bf16 number
     mpi_ops._shadow_tolerance = lambda dtype, wire, ranks: (0.0, 0.0)
     z = torch.tensor([1.0 if rank == 0 else 2.0 ** -9]).bfloat16()

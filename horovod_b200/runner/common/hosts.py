@@ -51,6 +51,13 @@ def parse_hosts(hosts_string):
     return [HostInfo.from_string(s) for s in hosts_string.split(",") if s.strip()]
 
 
+def parse_hosts_and_slots(hosts_string):
+    """'h1:2,h2:4' -> (['h1', 'h2'], {'h1': 2, 'h2': 4}); a host without a
+    count has one slot."""
+    parsed = parse_hosts(hosts_string)
+    return [h.hostname for h in parsed], {h.hostname: h.slots for h in parsed}
+
+
 def parse_host_files(filename):
     """Hostfile lines 'hostname slots=N' -> 'hostname:N,...'."""
     hosts = []

@@ -39,6 +39,12 @@ class LSFUtils:
         return int(os.environ.get("HOROVOD_LSF_THREADS_PER_CORE", "4"))
 
 
+def is_jsrun_installed():
+    """Whether the LSF launcher ``jsrun`` is on PATH."""
+    import shutil
+    return shutil.which("jsrun") is not None
+
+
 def generate_jsrun_rankfile(settings, path=None):
     """One resource set (one GPU and its share of cores) per rank."""
     cores = LSFUtils.get_num_cores() // max(1, LSFUtils.get_num_gpus())

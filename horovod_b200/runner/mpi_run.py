@@ -71,6 +71,22 @@ def mpi_available(env=None):
     return _get_mpi_implementation(env) not in (_UNKNOWN_IMPL, _MISSING_IMPL)
 
 
+def is_open_mpi(env=None):
+    return _get_mpi_implementation(env) == _OMPI_IMPL
+
+
+def is_spectrum_mpi(env=None):
+    return _get_mpi_implementation(env) == _SMPI_IMPL
+
+
+def is_mpich(env=None):
+    return _get_mpi_implementation(env) == _MPICH_IMPL
+
+
+def is_intel_mpi(env=None):
+    return _get_mpi_implementation(env) == _IMPI_IMPL
+
+
 def build_mpi_command(settings, nics, env, command, impl_flags, binding_args, impl,
                       rendezvous_addr, rendezvous_port):
     """Returns the full mpirun command line as a string."""

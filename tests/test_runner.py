@@ -476,3 +476,22 @@ def test_small_launcher_utilities(monkeypatch):
     assert pipe.read() is None
     with pytest.raises(RuntimeError):
         pipe.write("late")
+
+
+def test_mpi_flavour_queries_and_host_helpers(monkeypatch):
+    from horovod_b200.runner import js_run, mpi_run
+    banners = {"Open MPI": "mpirun (Open MPI) 4.1.4", "IBM Spectrum MPI": "IBM Spectrum MPI 10.3",
+               "MPICH": "HYDRA build details: MPICH 4.0", "Intel": "Intel(R) MPI Library 2021.6"}
+    answers = {}
+    for key, banner in banners.items():
+        monkeypatch.setattr(mpi_run, "_exec", lambda command, banner=banner: (banner, 0))
+        answers[key] = (mpi_run.is_open_mpi(), mpi_run.is_spectrum_mpi(), mpi_run.is_mpich(),
+                        mpi_run.is_intel_mpi(), mpi_run.mpi_available())
+    assert answers == {"Open MPI": (True, False, False, False, True),
+                       "IBM Spectrum MPI": (False, True, False, False, True),
+                       "MPICH": (False, False, True, False, True),
+                       "Intel": (False, False, False, True, True)}
+    monkeypatch.setattr(mpi_run, "_exec", lambda command: (None, 1))   # no mpirun on PATH
+    assert not mpi_run.mpi_available() and not mpi_run.is_open_mpi()
+    assert isinstance(js_run.is_jsrun_installed(), bool)
+    assert hosts.parse_hosts_and_slots("a:2,b,c:4") == (["a", "b", "c"], {"a": 2, "b": 1, "c": 4})

@@ -91,3 +91,11 @@ def test_estimator_example_on_pandas(tmp_path):
     losses = [float(v) for v in re.findall(r"epoch \d+: train loss ([0-9.]+)", proc.stdout)]
     assert len(losses) == 3 and losses[-1] < losses[0], proc.stdout[-1500:]
     assert "label__output" in proc.stdout
+
+
+def test_elastic_mnist_example_trains():
+    out = _launch(2, ["examples/pytorch_mnist_elastic.py", "--epochs", "2", "--samples", "1024",
+                      "--batch-size", "64", "--no-cuda"])
+    rows = re.findall(r"epoch (\d+): loss ([0-9.]+) accuracy ([0-9.]+) on 2 rank\(s\)", out)
+    assert [r[0] for r in rows] == ["0", "1"], out[-1500:]
+    assert float(rows[1][1]) < float(rows[0][1]) and float(rows[1][2]) > float(rows[0][2])

@@ -72,7 +72,8 @@ def train(state):
             state.sampler.set_epoch(state.epoch)
         model.train()
         seen, correct, loss_sum = 0, 0, 0.0
-        for batch_idx, (x, y) in enumerate(loader, start=state.batch):
+        first = state.batch                 # > 0 when an epoch is resumed after a reset
+        for idx, (x, y) in enumerate(loader):
             x, y = x.to(device), y.to(device)
             optimizer.zero_grad()
             out = model(x)
@@ -82,8 +83,9 @@ def train(state):
             seen += y.numel()
             correct += (out.argmax(1) == y).sum().item()
             loss_sum += loss.item() * y.numel()
-            state.batch = batch_idx + 1
-            state.sampler.record_batch(batch_idx, args.batch_size)
+            state.batch = first + idx + 1
+            # positions count from the start of this pass over what was left
+            state.sampler.record_batch(idx, args.batch_size)
             if state.batch % args.batches_per_commit == 0:
                 state.commit()      # snapshot; also where membership changes are noticed
         stats = hvd.allreduce(torch.tensor([loss_sum / max(seen, 1), correct / max(seen, 1)]),

@@ -123,21 +123,26 @@ class ObjectState(State):
 
     def __init__(self, bcast_object, get_rank, **kwargs):
         self._committed = dict(kwargs)
-        self.restore()
+        self._apply_committed()
         super().__init__(bcast_object=bcast_object, get_rank=get_rank)
 
     def save(self):
         self._committed = {name: getattr(self, name) for name in self._committed}
 
-    def restore(self):
+    def _apply_committed(self):
         for name, value in self._committed.items():
             setattr(self, name, value)
+
+    def restore(self):
+        self._apply_committed()
 
     def sync(self):
         if not self._committed:
             return
         self._committed = self._bcast_object(self._committed, name="hvd.elastic.object_state")
-        self.restore()
+        # Only the attributes: restore() of a subclass would also roll back
+        # what the subclass has just synchronised by other means.
+        self._apply_committed()
 
 
 def run_fn(func, reset):
@@ -145,8 +150,10 @@ def run_fn(func, reset):
 
     @functools.wraps(func)
     def wrapper(state, *args, **kwargs):
-        notification_manager.init()
+        # listener first: the driver may answer the registration with a host
+        # change that it could not deliver earlier
         notification_manager.register_listener(state)
+        notification_manager.init()
         skip_sync = False
         try:
             while True:

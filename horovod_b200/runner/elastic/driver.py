@@ -92,6 +92,7 @@ class ElasticDriver:
         self._threads = []
         self._spawn = None
         self._notify_clients = {}
+        self._undelivered_change = HostUpdateResult.no_update
         self._stop_event = threading.Event()  # handed to workers: the job is ending
 
         self._poller = threading.Thread(target=self._poll_discovery, daemon=True,
@@ -175,6 +176,11 @@ class ElasticDriver:
         client = WorkerNotificationClient(addresses, secret_key, self._verbose)
         with self._cv:
             self._notify_clients[(host, slot)] = client
+            missed = self._undelivered_change
+        if missed != HostUpdateResult.no_update:
+            # Hosts changed while rank 0 could not be told yet (it had not
+            # started its notification service): tell it now.
+            self._placement_may_change(missed)
 
     def get_worker_client(self, slot_info):
         with self._cv:
@@ -344,12 +350,16 @@ class ElasticDriver:
             planned = self._plan(view)
         with self._cv:
             if planned == self._round.slots:
+                self._undelivered_change = HostUpdateResult.no_update
                 return
             rank0 = self._round.by_rank.get(0)
             client = self._notify_clients.get((rank0.hostname, rank0.local_rank)) \
                 if rank0 is not None else None
-        if client is None:
-            return
+            if client is None:
+                # kept for register_worker_server(): rank 0 is not listening yet
+                self._undelivered_change |= change
+                return
+            self._undelivered_change = HostUpdateResult.no_update
         try:
             client.notify_hosts_updated(int(time.time()), change)
         except Exception:  # noqa: BLE001

@@ -148,6 +148,9 @@ class TorchState(ObjectState):
     def sync(self):
         for handler in self._handlers.values():
             handler.sync()
+            # what rank 0 sent is the new rollback point, on a worker that has
+            # just joined as much as on the others
+            handler.save()
         super().sync()
 
     def __setattr__(self, name, value):

@@ -373,8 +373,13 @@ def _is_dense(t):
 
 
 def _force_hooks():
+    """Gradient hooks although the job has one rank now: asked for
+    (HOROVOD_FORCE_HOOKS, benchmarks at N=1), or an elastic job, which may
+    grow later while this optimizer object lives on
+    (horovod/torch/optimizer.py:128-131)."""
     import os
-    return os.environ.get("HOROVOD_FORCE_HOOKS", "0") == "1"
+    return os.environ.get("HOROVOD_FORCE_HOOKS", "0") == "1" or \
+        os.environ.get("HOROVOD_ELASTIC", "0") == "1"
 
 
 def _find_duplicates(lst):

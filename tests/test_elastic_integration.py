@@ -90,3 +90,32 @@ def test_reset_limit_stops_the_job(tmp_path):
             [sys.executable, SCRIPT, "--log", log, "--epochs", "5", "--exit-at",
              "1:127.0.0.1:1"],
             gloo_run._exec_slot, settings, _env(), None)
+
+
+def test_elastic_mnist_example_takes_on_a_second_host_mid_training(tmp_path, capfd):
+    """examples/pytorch_mnist_elastic.py under the elastic driver: a second
+    "host" appears some seconds into the run (possibly before rank 0 listens
+    for host changes: the driver then tells it as soon as it does); the job
+    grows from 1 to 2 ranks at a commit, goes on from there (ElasticSampler
+    hands out what is left of the epoch; the new worker takes over rank 0's
+    weights) and reports every epoch exactly once."""
+    import re
+    import time
+    example = os.path.join(os.path.dirname(HERE), "examples", "pytorch_mnist_elastic.py")
+    script = tmp_path / "discover.sh"
+    script.write_text("#!/bin/bash\necho localhost:1\n"
+                      "if [ $(( $(date +%%s) - %d )) -ge 9 ]; then echo 127.0.0.1:1; fi\n"
+                      % int(time.time()))
+    script.chmod(script.stat().st_mode | stat.S_IEXEC)
+    disc = discovery.HostDiscoveryScript(str(script), slots=1)
+    settings = _settings(disc, np=1, min_np=1, max_np=2)
+    gloo_run.launch_gloo_elastic(
+        [sys.executable, example, "--epochs", "12", "--samples", "2048", "--batch-size", "32",
+         "--batches-per-commit", "4", "--no-cuda"],
+        gloo_run._exec_slot, settings, _env(), None)
+    out = capfd.readouterr().out
+    rows = re.findall(r"epoch (\d+): loss ([0-9.]+) accuracy ([0-9.]+) on (\d) rank\(s\)", out)
+    assert [int(r[0]) for r in rows] == list(range(12)), out[-2000:]
+    ranks = [int(r[3]) for r in rows]
+    assert ranks[-1] == 2 and ranks == sorted(ranks), ranks
+    assert float(rows[-1][2]) > 0.9, rows[-1]   # still converges across the change

@@ -12,6 +12,7 @@ from horovod_b200.common.elastic import HostUpdateResult
 from horovod_b200.runner.elastic import driver as driver_mod
 from horovod_b200.runner.elastic.discovery import FixedHosts, HostManager
 from horovod_b200.runner.elastic.driver import ElasticDriver
+from parallel_utils import run_parallel
 
 
 @pytest.fixture(autouse=True)
@@ -180,3 +181,48 @@ def test_torch_state_commit_restore_and_sampler():
         assert list(shuffled) != a
     finally:
         hvd.shutdown()
+
+
+def _joiner_takes_over_rank0_state(rank, size):
+    """What a worker that joins a running job must end up with after
+    state.sync(): rank 0's weights, optimizer state, sampler progress and
+    attributes, and these as its rollback point too."""
+    import horovod_b200.torch as hvd
+    hvd.init()
+    torch.manual_seed(100 + rank)                     # every rank starts from other weights
+    model = torch.nn.Linear(6, 3)
+    opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
+    data = torch.utils.data.TensorDataset(torch.arange(40.0).view(40, 1))
+    sampler = hvd.elastic.ElasticSampler(data, shuffle=False)
+    state = hvd.elastic.TorchState(model, opt, sampler=sampler, epoch=0, batch=0)
+    if rank == 0:                                     # the old-timer has trained and committed
+        model(torch.ones(2, 6)).sum().backward()
+        opt.step()
+        list(iter(sampler))
+        sampler.record_batch(0, 8)
+        state.epoch, state.batch = 3, 1
+        state.save()                                  # commit() without its collective check
+    state.sync()
+    flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    momentum = torch.cat([opt.state[p]["momentum_buffer"].reshape(-1) for p in model.parameters()])
+    everyone = hvd.allgather(torch.cat([flat, momentum]).unsqueeze(0), name="joiner.check")
+    same = bool((everyone == everyone[0]).all())
+    progress = (state.epoch, state.batch, len(sampler.processed_indices), len(sampler))
+    # a rollback returns to the synchronised state, not to the pre-join one
+    with torch.no_grad():
+        for p in model.parameters():
+            p.add_(1.0)
+    state.epoch = 9
+    state.restore()
+    after = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    rolled_back = bool(torch.equal(after, flat)) and state.epoch == 3 and \
+        len(sampler.processed_indices) == 8
+    hvd.shutdown()
+    return same, progress, rolled_back
+
+
+def test_a_joining_worker_takes_over_rank0_state_on_sync():
+    for same, progress, rolled_back in run_parallel(_joiner_takes_over_rank0_state, np=2,
+                                                    timeout=90):
+        assert same and rolled_back
+        assert progress == (3, 1, 8, 16)              # 32 samples left for 2 ranks

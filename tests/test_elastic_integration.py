@@ -119,3 +119,36 @@ def test_elastic_mnist_example_takes_on_a_second_host_mid_training(tmp_path, cap
     ranks = [int(r[3]) for r in rows]
     assert ranks[-1] == 2 and ranks == sorted(ranks), ranks
     assert float(rows[-1][2]) > 0.9, rows[-1]   # still converges across the change
+
+
+def test_elastic_mnist_example_survives_a_worker_that_dies_mid_epoch(tmp_path, capfd):
+    """The same example, with one line added that makes the worker on the
+    second "host" exit in the middle of epoch 1 (a host-side failure): the
+    survivor's next collective fails, it rolls back to its last commit
+    (weights, optimizer, sampler progress, batch counter), re-forms the job
+    alone and finishes every epoch exactly once."""
+    import re
+    example = os.path.join(os.path.dirname(HERE), "examples", "pytorch_mnist_elastic.py")
+    source = open(example).read()
+    hook = "            optimizer.zero_grad()\n"
+    assert source.count(hook) == 1
+    marker = str(tmp_path / "died")
+    dying = source.replace(hook, hook + (
+        "            import os\n"
+        "            if state.epoch == 1 and idx == 5 and hvd.rank() == 1 and not os.path.exists(%r):\n"
+        "                open(%r, 'w').close()\n"
+        "                os._exit(1)\n" % (marker, marker)), 1)
+    script = tmp_path / "mnist_dying.py"
+    script.write_text(dying)
+    disc = discovery.FixedHosts({"localhost": 1, "127.0.0.1": 1})
+    settings = _settings(disc, np=2, min_np=1, max_np=2)
+    gloo_run.launch_gloo_elastic(
+        [sys.executable, str(script), "--epochs", "5", "--samples", "2048", "--batch-size", "32",
+         "--batches-per-commit", "4", "--no-cuda"],
+        gloo_run._exec_slot, settings, _env(), None)
+    out = capfd.readouterr().out
+    assert os.path.exists(marker)
+    rows = re.findall(r"epoch (\d+): loss ([0-9.]+) accuracy ([0-9.]+) on (\d) rank\(s\)", out)
+    assert [int(r[0]) for r in rows] == list(range(5)), out[-2000:]
+    assert [int(r[3]) for r in rows] == [2, 1, 1, 1, 1]
+    assert float(rows[-1][2]) > 0.9, rows[-1]

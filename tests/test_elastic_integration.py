@@ -152,3 +152,30 @@ def test_elastic_mnist_example_survives_a_worker_that_dies_mid_epoch(tmp_path, c
     assert [int(r[0]) for r in rows] == list(range(5)), out[-2000:]
     assert [int(r[3]) for r in rows] == [2, 1, 1, 1, 1]
     assert float(rows[-1][2]) > 0.9, rows[-1]
+
+
+def test_elastic_mnist_example_gives_up_a_host_that_disappears(tmp_path, capfd):
+    """The discovery script stops listing the second "host" some seconds into
+    the run: its worker is told that it was removed, the other one goes on
+    alone from where the job was (no rollback) and every epoch is reported
+    exactly once."""
+    import re
+    import time
+    example = os.path.join(os.path.dirname(HERE), "examples", "pytorch_mnist_elastic.py")
+    script = tmp_path / "discover.sh"
+    script.write_text("#!/bin/bash\necho localhost:1\n"
+                      "if [ $(( $(date +%%s) - %d )) -lt 9 ]; then echo 127.0.0.1:1; fi\n"
+                      % int(time.time()))
+    script.chmod(script.stat().st_mode | stat.S_IEXEC)
+    disc = discovery.HostDiscoveryScript(str(script), slots=1)
+    settings = _settings(disc, np=2, min_np=1, max_np=2)
+    gloo_run.launch_gloo_elastic(
+        [sys.executable, example, "--epochs", "30", "--samples", "2048", "--batch-size", "32",
+         "--batches-per-commit", "4", "--no-cuda"],
+        gloo_run._exec_slot, settings, _env(), None)
+    out = capfd.readouterr().out
+    rows = re.findall(r"epoch (\d+): loss ([0-9.]+) accuracy ([0-9.]+) on (\d) rank\(s\)", out)
+    assert [int(r[0]) for r in rows] == list(range(30)), out[-2000:]
+    ranks = [int(r[3]) for r in rows]
+    assert ranks[-1] == 1 and ranks == sorted(ranks, reverse=True), ranks
+    assert float(rows[-1][2]) > 0.9, rows[-1]

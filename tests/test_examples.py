@@ -99,3 +99,52 @@ def test_elastic_mnist_example_trains():
     rows = re.findall(r"epoch (\d+): loss ([0-9.]+) accuracy ([0-9.]+) on 2 rank\(s\)", out)
     assert [r[0] for r in rows] == ["0", "1"], out[-1500:]
     assert float(rows[1][1]) < float(rows[0][1]) and float(rows[1][2]) > float(rows[0][2])
+
+
+def test_elastic_example_through_the_command_line_with_a_discovery_script(tmp_path):
+    """horovodrun --min-np/--max-np --host-discovery-script: the elastic
+    driver behind the command line, on one "host" with two slots."""
+    script = tmp_path / "discover.sh"
+    script.write_text("#!/bin/bash\necho localhost:2\n")
+    script.chmod(0o755)
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""),
+               CUDA_VISIBLE_DEVICES="")
+    proc = subprocess.run([sys.executable, "-m", "horovod_b200.runner.launch", "-np", "2",
+                           "--min-np", "1", "--max-np", "2", "--host-discovery-script",
+                           str(script), sys.executable, "examples/pytorch_mnist_elastic.py",
+                           "--epochs", "2", "--samples", "512", "--no-cuda"],
+                          cwd=ROOT, env=env, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    assert len(re.findall(r"epoch \d+: loss [0-9.]+ accuracy [0-9.]+ on 2 rank\(s\)",
+                          proc.stdout)) == 2, proc.stdout[-1500:]
+
+
+def _elastic_sum(tag):
+    import torch
+    import horovod_b200.torch as hvd
+    hvd.init()
+
+    @hvd.elastic.run
+    def train(state):
+        for state.step in range(state.step, 5):
+            state.total += float(hvd.allreduce(torch.ones(1), op=hvd.Sum, name="s"))
+            state.commit()
+        return state.total
+
+    total = train(hvd.elastic.ObjectState(hvd.broadcast_object, hvd.rank, step=0, total=0.0))
+    result = (tag, hvd.rank(), hvd.size(), total)
+    hvd.shutdown()
+    return result
+
+
+def test_programmatic_run_with_elastic_arguments(tmp_path):
+    import cloudpickle
+    import horovod_b200.runner as runner
+    cloudpickle.register_pickle_by_value(sys.modules[__name__])
+    script = tmp_path / "discover.sh"
+    script.write_text("#!/bin/bash\necho localhost:2\n")
+    script.chmod(0o755)
+    results = runner.run(_elastic_sum, args=("x",), np=2, min_np=1, max_np=2,
+                         host_discovery_script=str(script),
+                         env={"CUDA_VISIBLE_DEVICES": "", "PYTHONPATH": ROOT})
+    assert results == [("x", 0, 2, 10.0), ("x", 1, 2, 10.0)]

@@ -22,7 +22,7 @@ import time
 import urllib.error
 import urllib.request
 
-from horovod_b200.common.exceptions import HorovodInternalError
+from horovod_b200.common.exceptions import HorovodInternalError, WorkerRemovedError
 
 _GENERATION = [0]
 _TORCH_STORE = [None]
@@ -126,7 +126,7 @@ def _layout_from_env():
             reply = kv.get("rank_and_size", key, timeout=timeout).decode()
             vals = [int(v) for v in reply.split(",")]
             if vals[0] < 0:
-                raise HorovodInternalError(
+                raise WorkerRemovedError(
                     "This worker was removed from the job by the elastic driver.")
             names = ["rank", "size", "local_rank", "local_size", "cross_rank", "cross_size"]
             layout = dict(zip(names, vals[:6]))

@@ -7,7 +7,8 @@ Parity: horovod/common/elastic.py:26-175.
 import functools
 import queue
 
-from horovod_b200.common.exceptions import HorovodInternalError, HostsUpdatedInterrupt
+from horovod_b200.common.exceptions import (HorovodInternalError, HostsUpdatedInterrupt,
+                                             WorkerRemovedError)
 
 
 class HostUpdateResult:
@@ -166,7 +167,14 @@ def run_fn(func, reset):
                     skip_sync = False
                 except HostsUpdatedInterrupt as e:
                     skip_sync = e.skip_sync
-                reset()
+                try:
+                    reset()
+                except WorkerRemovedError as e:
+                    # Nothing is left for this process to do; its exit is not
+                    # part of the job's outcome.
+                    import sys
+                    print(str(e), file=sys.stderr, flush=True)
+                    raise SystemExit(0)
                 state.on_reset()
         finally:
             notification_manager.remove_listener(state)

@@ -10,6 +10,12 @@ class HorovodInternalError(RuntimeError):
     last committed state and re-initialises."""
 
 
+class WorkerRemovedError(HorovodInternalError):
+    """The elastic driver no longer has a place for this worker (its host
+    left the job). Raised by ``init()`` after a reset; the elastic retry loop
+    ends the process quietly with exit code 0 when it sees it."""
+
+
 class HostsUpdatedInterrupt(RuntimeError):
     """The set of hosts changed; raised at a commit point so every rank can
     re-rendezvous. ``skip_sync`` is true when only removals happened, in which

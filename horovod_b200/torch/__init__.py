@@ -9,7 +9,8 @@ from horovod_b200.common.util import check_extension
 # (horovod/torch/__init__.py:17-31).
 check_extension("horovod_b200.torch", "HOROVOD_WITH_PYTORCH", _pkg.__file__, "_C")
 
-from horovod_b200.common.exceptions import HorovodInternalError, HostsUpdatedInterrupt  # noqa: E402
+from horovod_b200.common.exceptions import (HorovodInternalError, HostsUpdatedInterrupt,  # noqa: E402
+                                             WorkerRemovedError)
 from horovod_b200.common.process_sets import (ProcessSet, add_process_set,
                                               global_process_set, process_set_ids,
                                               remove_process_set)

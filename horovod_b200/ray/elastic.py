@@ -102,7 +102,14 @@ class ElasticRayExecutor:
         def remote_body(env, fn):
             import os
             os.environ.update(env)
-            return fn()
+            try:
+                return fn()
+            except SystemExit as e:
+                # an elastic worker that was removed from the job ends with exit
+                # code 0; the Ray worker process must not go down with it
+                if e.code in (0, None):
+                    return None
+                raise RuntimeError("the worker function exited with code %r" % (e.code,))
 
         def run_slot(slot_info, events):
             env = dict(self._run_env)

@@ -18,9 +18,17 @@ def main(addr, port):
     rank = int(os.environ.get("HOROVOD_RANK", "0"))
     try:
         result = (True, func(*args, **kwargs), None)
+    except SystemExit as e:
+        if e.code in (0, None):
+            # e.g. an elastic worker whose host left the job: it has no rank
+            # any more and nothing to report
+            return 0
+        result = (False, traceback.format_exc(), None)
     except BaseException:
         result = (False, traceback.format_exc(), None)
-    # The world size can change in elastic jobs; report the final one.
+    # Rank and world size can change in elastic jobs (every re-initialisation
+    # rewrites the environment): report under the final ones.
+    rank = int(os.environ.get("HOROVOD_RANK", rank))
     size = int(os.environ.get("HOROVOD_SIZE", "1"))
     try:
         import horovod_b200.torch as hvd

@@ -167,6 +167,10 @@ def _task_loop(index, addresses, key, fn, args, kwargs, poll=0.2):
         os.environ.update(assignment.env)
         try:
             result, code = fn(*args, **kwargs), 0
+        except SystemExit as e:
+            # the function ended its "process" (an elastic worker that was removed
+            # exits with 0): the Spark task itself lives on for later assignments
+            result, code = None, (e.code if isinstance(e.code, int) else 0 if e.code is None else 1)
         except Exception as e:  # noqa: BLE001 - the driver decides what a failure means
             result, code = repr(e), 1
         client.report(index, code, result)

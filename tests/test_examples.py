@@ -148,3 +148,43 @@ def test_programmatic_run_with_elastic_arguments(tmp_path):
                          host_discovery_script=str(script),
                          env={"CUDA_VISIBLE_DEVICES": "", "PYTHONPATH": ROOT})
     assert results == [("x", 0, 2, 10.0), ("x", 1, 2, 10.0)]
+
+
+def _elastic_sizes():
+    import time
+    import torch
+    import horovod_b200.torch as hvd
+    hvd.init()
+
+    @hvd.elastic.run
+    def train(state):
+        for state.step in range(state.step, 60):
+            size_now = int(hvd.allreduce(torch.ones(1), op=hvd.Sum, name="s"))
+            time.sleep(0.2)
+            state.sizes.append(size_now)
+            state.commit()
+        return state.sizes
+
+    sizes = train(hvd.elastic.ObjectState(hvd.broadcast_object, hvd.rank, step=0, sizes=[]))
+    result = (hvd.rank(), hvd.size(), sizes[-1], len(sizes) >= 60)
+    hvd.shutdown()
+    return result
+
+
+def test_programmatic_elastic_run_reports_the_ranks_of_the_last_round(tmp_path):
+    """A host disappears while run() is under way: its worker leaves quietly,
+    the survivor finishes, and the results are those of the ranks that
+    existed at the end (the survivor under its new rank 0)."""
+    import time
+    import cloudpickle
+    import horovod_b200.runner as runner
+    cloudpickle.register_pickle_by_value(sys.modules[__name__])
+    script = tmp_path / "discover.sh"
+    script.write_text("#!/bin/bash\necho localhost:1\n"
+                      "if [ $(( $(date +%%s) - %d )) -lt 10 ]; then echo 127.0.0.1:1; fi\n"
+                      % int(time.time()))
+    script.chmod(0o755)
+    results = runner.run(_elastic_sizes, np=2, min_np=1, max_np=2,
+                         host_discovery_script=str(script),
+                         env={"CUDA_VISIBLE_DEVICES": "", "PYTHONPATH": ROOT})
+    assert results == [(0, 1, 1, True)]

@@ -121,9 +121,10 @@ def test_elastic_mnist_example_takes_on_a_second_host_mid_training(tmp_path, cap
     assert float(rows[-1][2]) > 0.9, rows[-1]   # still converges across the change
 
 
-def test_elastic_mnist_example_survives_a_worker_that_dies_mid_epoch(tmp_path, capfd):
-    """The same example, with one line added that makes the worker on the
-    second "host" exit in the middle of epoch 1 (a host-side failure): the
+@pytest.mark.parametrize("dying_rank", [1, 0])
+def test_elastic_mnist_example_survives_a_worker_that_dies_mid_epoch(tmp_path, capfd, dying_rank):
+    """The same example, with one line added that makes one worker (rank 1, or
+    rank 0, the coordinator) exit in the middle of epoch 1 (a host-side failure): the
     survivor's next collective fails, it rolls back to its last commit
     (weights, optimizer, sampler progress, batch counter), re-forms the job
     alone and finishes every epoch exactly once."""
@@ -135,9 +136,9 @@ def test_elastic_mnist_example_survives_a_worker_that_dies_mid_epoch(tmp_path, c
     marker = str(tmp_path / "died")
     dying = source.replace(hook, hook + (
         "            import os\n"
-        "            if state.epoch == 1 and idx == 5 and hvd.rank() == 1 and not os.path.exists(%r):\n"
+        "            if state.epoch == 1 and idx == 5 and hvd.rank() == %d and not os.path.exists(%r):\n"
         "                open(%r, 'w').close()\n"
-        "                os._exit(1)\n" % (marker, marker)), 1)
+        "                os._exit(1)\n" % (dying_rank, marker, marker)), 1)
     script = tmp_path / "mnist_dying.py"
     script.write_text(dying)
     disc = discovery.FixedHosts({"localhost": 1, "127.0.0.1": 1})

@@ -285,3 +285,44 @@ def _randomised_sets(rank, size):
 
 def test_randomised_tensor_sets_against_the_host_shadow():
     assert all(run_parallel(_randomised_sets, np=3, timeout=600))
+
+
+def _two_models_on_two_process_sets(rank, size):
+    """Ranks {0, 1} and {2, 3} train their own model at the same time, each
+    with a DistributedOptimizer restricted to its set: parameters agree
+    inside a set, differ between the sets, and match what one process
+    computes from the set's combined batches."""
+    import horovod_b200.torch as hvd
+    sets = [hvd.ProcessSet([0, 1]), hvd.ProcessSet([2, 3])]
+    hvd.init(process_sets=sets)
+    mine = sets[rank // 2]
+    torch.manual_seed(7 + rank // 2)                 # one initialisation per set
+    model = torch.nn.Linear(5, 2)
+    reference = torch.nn.Linear(5, 2)
+    reference.load_state_dict(model.state_dict())
+    opt = hvd.DistributedOptimizer(torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9),
+                                   named_parameters=model.named_parameters(), process_set=mine)
+    hvd.broadcast_parameters(model.state_dict(), root_rank=mine.ranks[0], process_set=mine)
+    hvd.broadcast_optimizer_state(opt, root_rank=mine.ranks[0], process_set=mine)
+    ref_opt = torch.optim.SGD(reference.parameters(), lr=0.1, momentum=0.9)
+    for step in range(4):
+        batches = [torch.randn(6, 5, generator=torch.Generator().manual_seed(1000 * step + r))
+                   for r in mine.ranks]
+        opt.zero_grad()
+        model(batches[mine.rank()]).pow(2).mean().backward()
+        opt.step()
+        ref_opt.zero_grad()
+        reference(torch.cat(batches)).pow(2).mean().backward()
+        ref_opt.step()
+    flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    expect = torch.cat([p.detach().reshape(-1) for p in reference.parameters()])
+    everyone = hvd.allgather(flat.unsqueeze(0), name="ps.models")
+    ok = bool(torch.allclose(flat, expect, atol=1e-6))
+    ok = ok and bool(torch.equal(everyone[0], everyone[1]) and torch.equal(everyone[2], everyone[3]))
+    ok = ok and not bool(torch.allclose(everyone[0], everyone[2]))
+    hvd.shutdown()
+    return ok
+
+
+def test_two_models_train_side_by_side_on_two_process_sets():
+    assert all(run_parallel(_two_models_on_two_process_sets, np=4, timeout=300))

@@ -326,3 +326,33 @@ def _two_models_on_two_process_sets(rank, size):
 
 def test_two_models_train_side_by_side_on_two_process_sets():
     assert all(run_parallel(_two_models_on_two_process_sets, np=4, timeout=300))
+
+
+def _uneven_batches_with_join(rank, size):
+    """Every rank has another number of batches: the ones that run out call
+    join() and stand in with zeros while the others go on training; the rank
+    that joined last holds the newest weights and hands them out."""
+    import horovod_b200.torch as hvd
+    hvd.init()
+    torch.manual_seed(3)
+    model = torch.nn.Linear(4, 1)
+    opt = hvd.DistributedOptimizer(torch.optim.SGD(model.parameters(), lr=0.05),
+                                   named_parameters=model.named_parameters())
+    hvd.broadcast_parameters(model.state_dict(), root_rank=0)
+    steps = 2 + 2 * rank                               # rank size-1 trains longest
+    for step in range(steps):
+        opt.zero_grad()
+        x = torch.randn(3, 4, generator=torch.Generator().manual_seed(50 * step + rank))
+        model(x).pow(2).mean().backward()
+        opt.step()
+    last = hvd.join()
+    hvd.broadcast_parameters(model.state_dict(), root_rank=last)
+    flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    everyone = hvd.allgather(flat.unsqueeze(0), name="join.models")
+    ok = last == size - 1 and all(bool(torch.equal(everyone[0], everyone[r])) for r in range(size))
+    hvd.shutdown()
+    return ok
+
+
+def test_training_with_uneven_batches_ends_with_join():
+    assert all(run_parallel(_uneven_batches_with_join, np=3, timeout=300))

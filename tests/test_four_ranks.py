@@ -356,3 +356,41 @@ def _uneven_batches_with_join(rank, size):
 
 def test_training_with_uneven_batches_ends_with_join():
     assert all(run_parallel(_uneven_batches_with_join, np=3, timeout=300))
+
+
+def _more_names_than_cache_entries(rank, size):
+    """A working set of tensor names three times the response cache: entries
+    are evicted and their bit positions reused all the time, in an order that
+    differs from pass to pass, while results stay right (Average of rank-
+    dependent values) and repeated names still hit the cache."""
+    os.environ["HOROVOD_CACHE_CAPACITY"] = "16"
+    import random
+    import horovod_b200.torch as hvd
+    hvd.init()
+    names = ["t%02d" % i for i in range(48)]
+    ok = True
+    for rnd in range(5):
+        order = list(names)
+        random.Random(rnd).shuffle(order)              # the same order on every rank
+        handles = []
+        for i, name in enumerate(order):
+            shape = (1 + int(name[1:]) % 7,)            # a name keeps its shape
+            value = torch.full(shape, float(rank + int(name[1:])))
+            handles.append((name, hvd.allreduce_async(value, op=hvd.Average, name=name)))
+            if i % 5 == 4:                              # waited for in small bursts
+                for n, h in handles:
+                    got = hvd.synchronize(h)
+                    ok = ok and bool((got == (size - 1) / 2.0 + int(n[1:])).all())
+                handles = []
+        for n, h in handles:
+            ok = ok and bool((hvd.synchronize(h) == (size - 1) / 2.0 + int(n[1:])).all())
+    # a small hot set that fits the cache keeps working after all the churn
+    for rnd in range(20):
+        got = hvd.allreduce(torch.ones(3) * rank, op=hvd.Sum, name="hot%d" % (rnd % 4))
+        ok = ok and bool((got == sum(range(size))).all())
+    hvd.shutdown()
+    return ok
+
+
+def test_more_tensor_names_than_response_cache_entries():
+    assert all(run_parallel(_more_names_than_cache_entries, np=3, timeout=300))

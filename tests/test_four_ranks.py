@@ -394,3 +394,33 @@ def _more_names_than_cache_entries(rank, size):
 
 def test_more_tensor_names_than_response_cache_entries():
     assert all(run_parallel(_more_names_than_cache_entries, np=3, timeout=300))
+
+
+def _a_name_changes_shape_type_and_op(rank, size):
+    """The cached response of a name stops fitting (other shape, dtype,
+    scale factor, op, or another collective altogether): every rank sees the
+    same invalidation and the new request is negotiated afresh."""
+    import horovod_b200.torch as hvd
+    hvd.init()
+    ok = True
+    total = sum(range(1, size + 1))
+    for shape, dtype, pre in [((4,), torch.float32, 1.0), ((4,), torch.float32, 1.0),
+                              ((6,), torch.float32, 1.0), ((6,), torch.float64, 1.0),
+                              ((6,), torch.float64, 0.5), ((2, 3), torch.float64, 0.5),
+                              ((4,), torch.float32, 1.0)]:
+        got = hvd.allreduce(torch.full(shape, float(rank + 1), dtype=dtype), op=hvd.Sum,
+                            prescale_factor=pre, name="same.name")
+        ok = ok and got.dtype == dtype and tuple(got.shape) == shape and \
+            bool((got == pre * total).all())
+    got = hvd.allreduce(torch.full((4,), float(rank + 1)), op=hvd.Max, name="same.name")
+    ok = ok and bool((got == size).all())
+    gathered = hvd.allgather(torch.full((1, 2), float(rank)), name="same.name")
+    ok = ok and gathered[:, 0].tolist() == [float(r) for r in range(size)]
+    got = hvd.allreduce(torch.full((4,), float(rank + 1)), op=hvd.Sum, name="same.name")
+    ok = ok and bool((got == total).all())
+    hvd.shutdown()
+    return ok
+
+
+def test_a_cached_name_that_changes_shape_type_scale_op_and_collective():
+    assert all(run_parallel(_a_name_changes_shape_type_and_op, np=3, timeout=300))

@@ -99,7 +99,7 @@ class _DistributedOptimizer(torch.optim.Optimizer):
 
         if symmetric_gradients and self.process_set.included():
             self._setup_symmetric_gradients()
-        if self.process_set.included() and size() > 1 or _force_hooks():
+        if self.process_set.included() and (size() > 1 or _force_hooks()):
             self._register_hooks()
 
     def _setup_symmetric_gradients(self):
@@ -443,7 +443,7 @@ class _DistributedAdasumOptimizer(torch.optim.Optimizer):
         cls = self.__class__
         self._group_name = "DistributedAdasumOptimizer.%d" % cls._instances
         cls._instances += 1
-        if self.process_set.included() and size() > 1 or _force_hooks():
+        if self.process_set.included() and (size() > 1 or _force_hooks()):
             for group in self.param_groups:
                 for p in group["params"]:
                     if p.requires_grad:

@@ -110,12 +110,12 @@ def test_elastic_mnist_example_takes_on_a_second_host_mid_training(tmp_path, cap
     disc = discovery.HostDiscoveryScript(str(script), slots=1)
     settings = _settings(disc, np=1, min_np=1, max_np=2)
     gloo_run.launch_gloo_elastic(
-        [sys.executable, example, "--epochs", "12", "--samples", "2048", "--batch-size", "32",
+        [sys.executable, example, "--epochs", "40", "--samples", "2048", "--batch-size", "32",
          "--batches-per-commit", "4", "--no-cuda"],
         gloo_run._exec_slot, settings, _env(), None)
     out = capfd.readouterr().out
     rows = re.findall(r"epoch (\d+): loss ([0-9.]+) accuracy ([0-9.]+) on (\d) rank\(s\)", out)
-    assert [int(r[0]) for r in rows] == list(range(12)), out[-2000:]
+    assert [int(r[0]) for r in rows] == list(range(40)), out[-2000:]
     ranks = [int(r[3]) for r in rows]
     assert ranks[-1] == 2 and ranks == sorted(ranks), ranks
     assert float(rows[-1][2]) > 0.9, rows[-1]   # still converges across the change

@@ -175,9 +175,18 @@ def _shadow_tolerance(dtype, wire_dtype, ranks):
     return (1e-5, 1e-6 * ranks) if dtype == torch.float32 else (1e-12, 1e-13 * ranks)
 
 
-def _shadow_name(label):
+_shadow_per_set = {}  # process set id -> shadows of unnamed ops started on that set
+
+
+def _shadow_name(label, name=None, process_set=None):
+    """The shadow of a named op is named after it; shadows of unnamed ops are
+    numbered per process set, whose members all issue the same sequence."""
     _shadow_counter[0] += 1
-    return "hvd.shadow.%s.%d" % (label, _shadow_counter[0])
+    if name:
+        return "hvd.shadow.%s.%s" % (label, name)
+    ps_id = _resolve(process_set)
+    _shadow_per_set[ps_id] = _shadow_per_set.get(ps_id, 0) + 1
+    return "hvd.shadow.%s.noname.%d.%d" % (label, ps_id, _shadow_per_set[ps_id])
 
 
 def _host_copy(tensor, widen):
@@ -185,21 +194,24 @@ def _host_copy(tensor, widen):
     return tensor.detach().to("cpu", target, copy=True).contiguous()
 
 
-def _start_shadow(handle, tensors, op, prescale_factor, postscale_factor, process_set, wire_dtype):
+def _start_shadow(handle, tensors, op, prescale_factor, postscale_factor, process_set, wire_dtype,
+                  name=None):
     """``tensors``: the inputs of the allreduce behind ``handle`` (one, or the
     list of a grouped op, which is shadowed as one flat vector)."""
     wide = torch.cat([_host_copy(t, True).reshape(-1) for t in tensors]).contiguous()
-    shadow = _enqueue(_C.allreduce_async, wide, torch.empty_like(wide), _shadow_name("allreduce"),
+    shadow = _enqueue(_C.allreduce_async, wide, torch.empty_like(wide),
+                      _shadow_name("allreduce", name, process_set),
                       *_scaled_op(op, prescale_factor, postscale_factor), _resolve(process_set), -1)
     narrow = [t.dtype for t in tensors if t.dtype in (torch.float16, torch.bfloat16)]
     _shadow_map[handle] = (shadow, "allreduce", narrow[0] if narrow else tensors[0].dtype,
                            wire_dtype, process_set.size() if process_set is not None else size())
 
 
-def _start_exact_shadow(handle, label, enqueue_twin):
+def _start_exact_shadow(handle, label, enqueue_twin, name=None, process_set=None):
     """For the ops that only move data: ``enqueue_twin(name)`` starts the
     same op on host copies; the results must be equal."""
-    _shadow_map[handle] = (enqueue_twin(_shadow_name(label)), label, None, None, 1)
+    _shadow_map[handle] = (enqueue_twin(_shadow_name(label, name, process_set)), label, None,
+                           None, 1)
 
 
 def _finish_shadow(handle, results):
@@ -248,7 +260,7 @@ def _allreduce_async(tensor, output, name, op, prescale_factor, postscale_factor
         handle = _allreduce_async_unchecked(tensor, output, name, op, prescale_factor,
                                             postscale_factor, process_set, wire_dtype)
         _start_shadow(handle, [wide_input], op, prescale_factor, postscale_factor, process_set,
-                      wire_dtype)
+                      wire_dtype, name)
         return handle
     return _allreduce_async_unchecked(tensor, output, name, op, prescale_factor, postscale_factor,
                                       process_set, wire_dtype)
@@ -359,7 +371,7 @@ def _grouped_allreduce_async(tensors, outputs, name, op, prescale_factor, postsc
         _handle_map[handle] = ("grouped", None)
     if shadowed is not None:
         _start_shadow(handle, shadowed, op, prescale_factor, postscale_factor, process_set,
-                      wire_dtype)
+                      wire_dtype, name)
     return handle
 
 
@@ -450,7 +462,7 @@ def allgather_async(tensor, name=None, process_set=global_process_set):
     if _shadow_wanted(tensor, None):
         twin = _host_copy(tensor, False)
         _start_exact_shadow(handle, "allgather", lambda shadow_name: _enqueue(
-            _C.allgather_async, twin, shadow_name, _resolve(process_set)))
+            _C.allgather_async, twin, shadow_name, _resolve(process_set)), name, process_set)
     return handle
 
 
@@ -486,7 +498,8 @@ def _broadcast_async(tensor, output, root_rank, name, process_set):
     _handle_map[handle] = ("broadcast", None)
     if twin is not None:
         _start_exact_shadow(handle, "broadcast", lambda shadow_name: _enqueue(
-            _C.broadcast_async, twin, twin, int(root_rank), shadow_name, _resolve(process_set)))
+            _C.broadcast_async, twin, twin, int(root_rank), shadow_name, _resolve(process_set)),
+            name, process_set)
     return handle
 
 
@@ -547,7 +560,8 @@ def alltoall_async(tensor, splits=None, name=None, process_set=global_process_se
     if _shadow_wanted(tensor, None):
         twin = _host_copy(tensor, False)
         _start_exact_shadow(handle, "alltoall", lambda shadow_name: _enqueue(
-            _C.alltoall_async, twin, _splits_list(splits), shadow_name, _resolve(process_set)))
+            _C.alltoall_async, twin, _splits_list(splits), shadow_name, _resolve(process_set)),
+            name, process_set)
     return handle
 
 
@@ -593,7 +607,8 @@ def reducescatter_async(tensor, name=None, op=Average, prescale_factor=1.0,
     _handle_map[handle] = ("reducescatter", None)
     if _shadow_wanted(tensor, op) and (op != Average or tensor.is_floating_point()):
         wide = _host_copy(tensor, True)
-        shadow = _enqueue(_C.reducescatter_async, wide, _shadow_name("reducescatter"), int(op),
+        shadow = _enqueue(_C.reducescatter_async, wide,
+                          _shadow_name("reducescatter", name, process_set), int(op),
                           float(prescale_factor), float(postscale_factor), _resolve(process_set))
         _shadow_map[handle] = (shadow, "reducescatter", tensor.dtype, None,
                                process_set.size() if process_set is not None else size())

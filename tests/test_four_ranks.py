@@ -424,3 +424,41 @@ def _a_name_changes_shape_type_and_op(rank, size):
 
 def test_a_cached_name_that_changes_shape_type_scale_op_and_collective():
     assert all(run_parallel(_a_name_changes_shape_type_and_op, np=3, timeout=300))
+
+
+def _eight_ranks(rank, size):
+    """Every collective, Adasum over three levels and ten process sets (ids
+    beyond the eight that the device kernels serve) on eight ranks, each
+    result also checked by the host shadow."""
+    os.environ["HOROVOD_SHADOW_CHECK"] = "all"
+    import horovod_b200.torch as hvd
+    hvd.init()
+    ok = True
+    ok &= hvd.allreduce(torch.ones(1000) * rank, op=hvd.Sum, name="a").eq(sum(range(size))).all().item()
+    g = hvd.allgather(torch.full((rank + 1, 3), float(rank)), name="g")
+    ok &= g.shape[0] == size * (size + 1) // 2
+    a = hvd.alltoall(torch.arange(size * 2.0) + 100 * rank, name="a2a")
+    ok &= a.tolist() == [100.0 * r + 2 * rank + j for r in range(size) for j in range(2)]
+    r = hvd.reducescatter(torch.ones(size * 2 + 3, 4) * (rank + 1), op=hvd.Sum, name="rs")
+    ok &= float(r[0, 0]) == size * (size + 1) / 2 and r.shape[0] == (3 if rank < 3 else 2)
+    b = torch.full((5,), float(rank)); hvd.broadcast_(b, root_rank=5, name="b"); ok &= b.tolist() == [5.0] * 5
+    ad = hvd.allreduce(torch.ones(64) * (rank + 1), op=hvd.Adasum, name="ad")
+    ok &= bool(torch.isfinite(ad).all())
+    sets = []
+    os.environ["HOROVOD_DYNAMIC_PROCESS_SETS"] = "1"
+    hvd.shutdown()
+    hvd.init()
+    for i in range(10):                       # ids beyond 8
+        sets.append(hvd.add_process_set([i % size, (i + 1) % size, (i + 3 + i // 8) % size]))
+    for i, ps in enumerate(sets):
+        if ps.included():
+            got = hvd.allreduce(torch.ones(4), op=hvd.Sum, name="ps%d" % i, process_set=ps)
+            ok &= bool((got == 3).all())
+    hvd.barrier()
+    hvd.shutdown()
+    return bool(ok)
+
+
+
+def test_every_collective_and_many_process_sets_on_eight_ranks():
+    assert all(run_parallel(_eight_ranks, np=8, timeout=400))

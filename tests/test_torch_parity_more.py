@@ -210,7 +210,8 @@ def _shadow_checks(rank, size):
     os.environ["HOROVOD_SHADOW_CHECK"] = "all"   # CPU tensors too; on a GPU box "1" checks the kernels
     import horovod_b200.torch as hvd
     from horovod_b200.torch import mpi_ops
-    hvd.init()
+    only_first = hvd.ProcessSet([0])
+    hvd.init(process_sets=[only_first])
     res = {}
     x = torch.randn(1000, generator=torch.Generator().manual_seed(rank))
     expect = sum(torch.randn(1000, generator=torch.Generator().manual_seed(r)) for r in range(size))
@@ -239,6 +240,12 @@ def _shadow_checks(rank, size):
     r_ = hvd.reducescatter(torch.ones(size * 3, 2) * (rank + 1), op=hvd.Sum, name="s.rs")
     res["reducescatter"] = tuple(r_.shape) == (3, 2) and float(r_[0, 0]) == tot
     res["shadows_done"] = not mpi_ops._shadow_map and mpi_ops._shadow_counter[0] == 10
+    # an op that only some ranks issue (a process set) must not shift the names of later
+    # shadows: they are named after their ops, not numbered per process
+    if rank == 0:
+        hvd.allreduce(torch.ones(2), op=hvd.Sum, name="s.alone", process_set=only_first)
+    res["set_named"] = float(hvd.allreduce(torch.ones(2) * rank, op=hvd.Sum, name="s.all")[0]) == \
+        sum(range(size))
     # a result that differs from the fp64 shadow is reported: 1 + 2^-9 is not a bf16 number
     mpi_ops._shadow_tolerance = lambda dtype, wire, ranks: (0.0, 0.0)
     z = torch.tensor([1.0 if rank == 0 else 2.0 ** -9]).bfloat16()
